@@ -1,0 +1,280 @@
+/*
+ * splatad_b200 - C ABI of the B200 (sm_100a) render hot path of SplatAD.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (cudaStream_t passed
+ * as void*; NULL = the legacy default stream), enqueues its kernels on that stream, allocates
+ * nothing and returns a status code. All tensors are contiguous, row-major FP32 unless noted;
+ * ids are int32 (flatten ids, offsets, radii of the camera) or int64 (isect ids, packed
+ * camera/gaussian ids). Optional pointers may be NULL where the comment says so. Outputs and
+ * workspaces are owned by the caller.
+ *
+ * Each declaration names the function of the reference (carlinds/splatad, a gsplat fork) whose
+ * pybind11 binding it replaces: gsplat/cuda/csrc/ext.cpp:4-52 registers them and
+ * gsplat/cuda/csrc/bindings.h declares their torch::Tensor signatures.
+ */
+#ifndef SPLATAD_B200_H
+#define SPLATAD_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SPLATAD_B200_VERSION 100
+
+/* status codes */
+#define SPLATAD_OK 0
+#define SPLATAD_ERR_BAD_ARG 1   /* null pointer, bad shape or size            -> ValueError / AssertionError */
+#define SPLATAD_ERR_CHANNELS 2  /* unsupported channel count                  -> ValueError                  */
+#define SPLATAD_ERR_KEY_BITS 3  /* sensor bits + tile bits exceed 32          -> RuntimeError                */
+#define SPLATAD_ERR_WORKSPACE 4 /* workspace missing or too small             -> RuntimeError                */
+#define SPLATAD_ERR_CUDA 5      /* a CUDA runtime call or launch failed       -> RuntimeError                */
+#define SPLATAD_ERR_OVERFLOW 6  /* more intersections than the given capacity -> RuntimeError                */
+
+/* Largest channel count one compositing launch renders; callers chunk above it
+ * (gsplat/rendering.py:362-392 and 733-773 chunk at 32 as well). */
+#define SPLATAD_MAX_CHANNELS 32
+
+/* Message of the last error raised on the calling thread ("" if none). */
+const char *splatad_last_error(void);
+int splatad_version(void);
+
+/* FP32 FMA throughput probe used to measure the CUDA-core roofline of the compositing
+ * kernels: grid blocks x 256 threads x iters x 128 FMAs. `out` holds grid*256 floats.
+ * No counterpart in the reference. */
+int splatad_fma_probe(float *out, int32_t grid, int32_t iters, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Projection
+ * ---------------------------------------------------------------------------------------- */
+
+/* fully_fused_lidar_projection_fwd_tensor - gsplat/cuda/csrc/bindings.h (lidar projection),
+ * host function gsplat/cuda/csrc/projection.cu:2631-2713, kernel 2268-2417.
+ * means [N,3]; covars [N,6] or NULL; quats [N,4], scales [N,3] (used when covars is NULL);
+ * velocities [N,3] or NULL; viewmats [C,4,4]; linear/angular_velocity [C,3];
+ * rolling_shutter_time [C].
+ * Outputs [C,N,..]: radii [.,2] float degrees, means2d [.,2], depths (range), conics [.,3],
+ * compensations (NULL = not computed), pix_vels [.,3], depth_compensations [.,2].
+ * Entries of culled pairs are zero. */
+int splatad_lidar_projection_fwd(
+    uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
+    const float *scales, const float *velocities, const float *viewmats, float min_elevation,
+    float max_elevation, float min_azimuth, float max_azimuth, const float *linear_velocity,
+    const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
+    float near_plane, float far_plane, float radius_clip, float *radii, float *means2d,
+    float *depths, float *conics, float *compensations, float *pix_vels,
+    float *depth_compensations, void *stream);
+
+/* fully_fused_lidar_projection_bwd_tensor - gsplat/cuda/csrc/projection.cu:2715-2826, kernel
+ * 2419-2629. Gradient outputs are overwritten (not accumulated) except v_viewmats [C,4,4],
+ * which must be zero-initialised by the caller when requested. v_covars / (v_quats, v_scales),
+ * v_viewmats and v_velocities may be NULL. v_velocities [N,3] is the gradient the reference
+ * computes and discards (projection.cu:2538-2541). */
+int splatad_lidar_projection_bwd(
+    uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
+    const float *scales, const float *velocities, const float *viewmats,
+    const float *linear_velocity, const float *angular_velocity,
+    const float *rolling_shutter_time, float eps2d, const float *radii, const float *conics,
+    const float *compensations, const float *v_means2d, const float *v_depths,
+    const float *v_conics, const float *v_compensations, const float *v_pix_vels,
+    const float *v_depth_compensations, float *v_means, float *v_covars, float *v_quats,
+    float *v_scales, float *v_viewmats, float *v_velocities, void *stream);
+
+/* fully_fused_projection_fwd_tensor - gsplat/cuda/csrc/projection.cu:966-1045, kernel 605-751.
+ * Ks [C,3,3]. Outputs [C,N,..]: radii [.,2] int32 pixels, means2d, depths (z), conics,
+ * compensations (NULL = not computed), pix_vels [.,2]. */
+int splatad_projection_fwd(
+    uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
+    const float *scales, const float *velocities, const float *viewmats, const float *Ks,
+    int32_t image_width, int32_t image_height, const float *linear_velocity,
+    const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
+    float near_plane, float far_plane, float radius_clip, int32_t *radii, float *means2d,
+    float *depths, float *conics, float *compensations, float *pix_vels, void *stream);
+
+/* fully_fused_projection_bwd_tensor - gsplat/cuda/csrc/projection.cu:1047-1155, kernel 753-964. */
+int splatad_projection_bwd(
+    uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
+    const float *scales, const float *velocities, const float *viewmats, const float *Ks,
+    int32_t image_width, int32_t image_height, const float *linear_velocity,
+    const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
+    const int32_t *radii, const float *conics, const float *compensations,
+    const float *v_means2d, const float *v_depths, const float *v_conics,
+    const float *v_compensations, const float *v_pix_vels, float *v_means, float *v_covars,
+    float *v_quats, float *v_scales, float *v_viewmats, float *v_velocities, void *stream);
+
+/* fully_fused_projection_packed_fwd_tensor - gsplat/cuda/csrc/projection.cu:1355-1464, kernel
+ * 1157-1353. The reference sizes its outputs after a device->host read of nnz; here that is a
+ * two-call protocol: _count writes indptr [C+1] and *nnz_device (int64, device memory; the
+ * caller copies it to the host), _fill writes the nnz rows (camera-major, Gaussian-minor).
+ * The same workspace must be passed to both calls. */
+size_t splatad_projection_packed_workspace_bytes(uint32_t C, uint32_t N);
+int splatad_projection_packed_count(
+    uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
+    const float *scales, const float *velocities, const float *viewmats, const float *Ks,
+    int32_t image_width, int32_t image_height, const float *linear_velocity,
+    const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
+    float near_plane, float far_plane, float radius_clip, void *workspace,
+    size_t workspace_bytes, int32_t *indptr, int64_t *nnz_device, void *stream);
+int splatad_projection_packed_fill(
+    uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
+    const float *scales, const float *velocities, const float *viewmats, const float *Ks,
+    int32_t image_width, int32_t image_height, const float *linear_velocity,
+    const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
+    float near_plane, float far_plane, float radius_clip, const void *workspace,
+    int64_t *camera_ids, int64_t *gaussian_ids, int32_t *radii, float *means2d, float *depths,
+    float *conics, float *compensations, float *pix_vels, void *stream);
+
+/* fully_fused_projection_packed_bwd_tensor - gsplat/cuda/csrc/projection.cu:1718-1838, kernel
+ * 1466-1716. sparse_grad != 0: parameter gradients are [nnz,..] rows (plain stores);
+ * otherwise [N,..] accumulated with atomics, so the caller zero-initialises them.
+ * v_viewmats (optional) is always accumulated. */
+int splatad_projection_packed_bwd(
+    uint32_t C, uint32_t N, uint32_t nnz, const float *means, const float *covars,
+    const float *quats, const float *scales, const float *velocities, const float *viewmats,
+    const float *Ks, int32_t image_width, int32_t image_height, const float *linear_velocity,
+    const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
+    const int64_t *camera_ids, const int64_t *gaussian_ids, const float *conics,
+    const float *compensations, const float *v_means2d, const float *v_depths,
+    const float *v_conics, const float *v_compensations, const float *v_pix_vels,
+    int32_t sparse_grad, float *v_means, float *v_covars, float *v_quats, float *v_scales,
+    float *v_viewmats, float *v_velocities, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Spherical harmonics
+ * ---------------------------------------------------------------------------------------- */
+
+/* compute_sh_fwd_tensor - gsplat/cuda/csrc/sh.cu:408-433. dirs [n,3], coeffs [n,K,3],
+ * masks [n] bytes (bool) or NULL, colors [n,3]. Masked-out rows are written as zero. */
+int splatad_sh_fwd(uint32_t n_elems, uint32_t K, uint32_t degrees_to_use, const float *dirs,
+                   const float *coeffs, const uint8_t *masks, float *colors, void *stream);
+
+/* compute_sh_bwd_tensor - gsplat/cuda/csrc/sh.cu:435-468. v_coeffs [n,K,3] and v_dirs [n,3]
+ * (NULL = not wanted) are overwritten. */
+int splatad_sh_bwd(uint32_t n_elems, uint32_t K, uint32_t degrees_to_use, const float *dirs,
+                   const float *coeffs, const uint8_t *masks, const float *v_colors,
+                   float *v_coeffs, float *v_dirs, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Tile intersection
+ *
+ * isect_tiles_tensor (gsplat/cuda/csrc/rasterization.cu:92-216) and isect_lidar_tiles_tensor
+ * (397-529) read the intersection count back to the host in the middle to size their outputs.
+ * Here each is a two-call protocol on one stream:
+ *   _plan  writes tiles_per_gauss, orders the visible Gaussians by depth, and copies
+ *          host_counts[0..3] = {n_isects, n_visible, status bits, 0} to the host (pinned memory
+ *          recommended; valid once the stream has reached that point).
+ *   _fill  writes isect_ids [capacity] int64 and flatten_ids [capacity] int32, sorted by
+ *          (sensor, tile, depth bits, flatten index) when sort != 0, in flatten-index order
+ *          otherwise. capacity >= n_isects; if it is smaller, status bit 1 is set in
+ *          host_counts[2] (copied again by _fill) and the outputs are incomplete.
+ * `total_elems` is C*N for the [C,N] layout (camera_ids NULL) or nnz for the packed layout
+ * (camera_ids [nnz] int64 gives the sensor of each row, N is ignored).
+ * Depths must be non-negative: their bit patterns are ordered as unsigned integers.
+ * ---------------------------------------------------------------------------------------- */
+size_t splatad_isect_plan_workspace_bytes(uint64_t total_elems);
+size_t splatad_isect_fill_workspace_bytes(uint64_t capacity);
+
+int splatad_isect_tiles_plan(
+    uint32_t C, uint32_t N, uint64_t total_elems, const float *means2d, const int32_t *radii,
+    const float *depths, const int64_t *camera_ids, uint32_t tile_size, uint32_t tile_width,
+    uint32_t tile_height, int32_t sort, int32_t *tiles_per_gauss, void *workspace,
+    size_t workspace_bytes, int64_t *host_counts, void *stream);
+int splatad_isect_tiles_fill(
+    uint32_t C, uint32_t N, uint64_t total_elems, const float *means2d, const int32_t *radii,
+    const float *depths, const int64_t *camera_ids, uint32_t tile_size, uint32_t tile_width,
+    uint32_t tile_height, int32_t sort, const int32_t *tiles_per_gauss, void *plan_workspace,
+    void *fill_workspace, size_t fill_workspace_bytes, int64_t capacity, int64_t *isect_ids,
+    int32_t *flatten_ids, int64_t *host_counts, void *stream);
+
+/* elev_boundaries [n_boundaries] = tile boundaries in elevation (n_boundaries - 1 tile rows);
+ * the number of azimuth tiles is ceil(360 / tile_azim_resolution) as in
+ * gsplat/cuda/csrc/rasterization.cu:435. */
+int splatad_isect_lidar_tiles_plan(
+    uint32_t C, uint32_t N, uint64_t total_elems, const float *means2d, const float *radii,
+    const float *depths, const int64_t *camera_ids, const float *elev_boundaries,
+    uint32_t n_boundaries, float tile_azim_resolution, float min_azim, int32_t sort,
+    int32_t *tiles_per_gauss, void *workspace, size_t workspace_bytes, int64_t *host_counts,
+    void *stream);
+int splatad_isect_lidar_tiles_fill(
+    uint32_t C, uint32_t N, uint64_t total_elems, const float *means2d, const float *radii,
+    const float *depths, const int64_t *camera_ids, const float *elev_boundaries,
+    uint32_t n_boundaries, float tile_azim_resolution, float min_azim, int32_t sort,
+    const int32_t *tiles_per_gauss, void *plan_workspace, void *fill_workspace,
+    size_t fill_workspace_bytes, int64_t capacity, int64_t *isect_ids, int32_t *flatten_ids,
+    int64_t *host_counts, void *stream);
+
+/* isect_offset_encode_tensor - gsplat/cuda/csrc/rasterization.cu:264-285.
+ * offsets [C, tile_height, tile_width] int32. */
+int splatad_isect_offset_encode(const int64_t *isect_ids, int64_t n_isects, uint32_t C,
+                                uint32_t tile_width, uint32_t tile_height, int32_t *offsets,
+                                void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Compositing. `channels` is the true channel count (1..SPLATAD_MAX_CHANNELS): no padding to
+ * a supported size is needed, unlike gsplat/cuda/_wrapper.py:876-921.
+ * ---------------------------------------------------------------------------------------- */
+
+/* rasterize_to_pixels_fwd_tensor - gsplat/cuda/csrc/rasterization.cu:1520-2019, kernel
+ * 1360-1518. Inputs are [C,N,..] or packed [nnz,..] (flatten_ids index either);
+ * backgrounds [C,channels] or NULL. Outputs: render_colors [C,H,W,channels],
+ * render_alphas [C,H,W], last_ids [C,H,W] int32; every pixel is written. */
+int splatad_rasterize_to_pixels_fwd(
+    uint32_t C, int64_t n_isects, const float *means2d, const float *conics, const float *colors,
+    uint32_t channels, const float *opacities, const float *pix_vels,
+    const float *rolling_shutter_time, const float *backgrounds, uint32_t image_width,
+    uint32_t image_height, uint32_t tile_size, uint32_t tile_width, uint32_t tile_height,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, float *render_colors,
+    float *render_alphas, int32_t *last_ids, void *stream);
+
+/* rasterize_to_pixels_bwd_tensor - gsplat/cuda/csrc/rasterization.cu:3091-3726, kernel
+ * 2833-3089. Gradient outputs are accumulated with atomics: zero-initialise them.
+ * v_means2d_abs may be NULL. */
+int splatad_rasterize_to_pixels_bwd(
+    uint32_t C, int64_t n_isects, const float *means2d, const float *conics, const float *colors,
+    uint32_t channels, const float *opacities, const float *pix_vels,
+    const float *rolling_shutter_time, const float *backgrounds, uint32_t image_width,
+    uint32_t image_height, uint32_t tile_size, uint32_t tile_width, uint32_t tile_height,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, const float *render_alphas,
+    const int32_t *last_ids, const float *v_render_colors, const float *v_render_alphas,
+    float *v_means2d_abs, float *v_means2d, float *v_conics, float *v_colors, float *v_opacities,
+    float *v_pix_vels, void *stream);
+
+/* rasterize_to_points_fwd_tensor - gsplat/cuda/csrc/rasterization.cu:2221-2831, kernel
+ * 2021-2219. raster_pts [C,H,W,4] = (azimuth deg, elevation deg, range m, time offset s);
+ * points with range <= 0 are not rendered and produce zeros. pix_vels [.,3],
+ * depth_compensations [.,2]. depth_channel_idx names the channel that holds the Gaussian's
+ * range. alpha_sum_until_points may be NULL when compute_alpha_sum_until_points == 0. */
+int splatad_rasterize_to_points_fwd(
+    uint32_t C, int64_t n_isects, const float *means2d, const float *conics,
+    const float *lidar_features, uint32_t channels, const float *opacities,
+    const float *pix_vels, const float *depth_compensations, const float *backgrounds,
+    const float *raster_pts, uint32_t image_width, uint32_t image_height, uint32_t tile_width,
+    uint32_t tile_height, uint32_t tile_grid_width, uint32_t tile_grid_height,
+    int32_t compute_alpha_sum_until_points, float alpha_sum_threshold,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, uint32_t depth_channel_idx,
+    float *render_features, float *render_alphas, float *alpha_sum_until_points,
+    int32_t *last_ids, float *median_depths, void *stream);
+
+/* rasterize_to_points_bwd_tensor - gsplat/cuda/csrc/rasterization.cu:4056-4851, kernel
+ * 3728-4054. v_alpha_sum_until_points may be NULL (treated as zero). Gradient outputs are
+ * accumulated with atomics: zero-initialise them. */
+int splatad_rasterize_to_points_bwd(
+    uint32_t C, int64_t n_isects, const float *means2d, const float *conics,
+    const float *lidar_features, uint32_t channels, const float *opacities,
+    const float *pix_vels, const float *depth_compensations, const float *backgrounds,
+    const float *raster_pts, uint32_t image_width, uint32_t image_height, uint32_t tile_width,
+    uint32_t tile_height, uint32_t tile_grid_width, uint32_t tile_grid_height,
+    int32_t compute_alpha_sum_until_points, float alpha_sum_threshold,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, uint32_t depth_channel_idx,
+    const float *render_alphas, const int32_t *last_ids, const float *v_render_features,
+    const float *v_render_alphas, const float *v_alpha_sum_until_points, float *v_means2d_abs,
+    float *v_means2d, float *v_conics, float *v_features, float *v_opacities, float *v_pix_vels,
+    float *v_depth_compensations, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SPLATAD_B200_H */

@@ -1,0 +1,35 @@
+"""splatad_b200: the SplatAD render hot path (camera ``rasterization`` and lidar
+``lidar_rasterization``, forward and backward) for NVIDIA B200 (sm_100a).
+
+The public names are those the reference exports for this path (gsplat/__init__.py:4-18);
+everything runs in hand-written CUDA behind the C ABI declared in ``include/splatad_b200.h``.
+"""
+
+from .ops import (
+    fully_fused_lidar_projection,
+    fully_fused_projection,
+    isect_lidar_tiles,
+    isect_offset_encode,
+    isect_tiles,
+    rasterize_to_pixels,
+    rasterize_to_points,
+    spherical_harmonics,
+    velocity_grads,
+)
+from .rendering import lidar_rasterization, rasterization
+
+__all__ = [
+    "rasterization",
+    "lidar_rasterization",
+    "fully_fused_projection",
+    "fully_fused_lidar_projection",
+    "isect_tiles",
+    "isect_lidar_tiles",
+    "isect_offset_encode",
+    "rasterize_to_pixels",
+    "rasterize_to_points",
+    "spherical_harmonics",
+    "velocity_grads",
+]
+
+__version__ = "0.1.0"

@@ -1,0 +1,163 @@
+"""Loader for ``libsplatad_b200.so`` (the C-ABI CUDA library) and small helpers around it.
+
+The argument types of every entry point are derived from ``include/splatad_b200.h`` so the
+Python bindings cannot drift from the header. There is no CPU fallback: if the shared library
+is missing, or an entry point is called with tensors that are not on a CUDA device, an
+exception is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import re
+import subprocess
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+_REPO_DIR = os.path.dirname(_PKG_DIR)
+LIB_PATH = os.path.join(_PKG_DIR, "libsplatad_b200.so")
+HEADER_PATH = os.path.join(_REPO_DIR, "include", "splatad_b200.h")
+CSRC_DIR = os.path.join(_PKG_DIR, "csrc")
+
+OK = 0
+ERR_BAD_ARG = 1
+ERR_CHANNELS = 2
+ERR_KEY_BITS = 3
+ERR_WORKSPACE = 4
+ERR_CUDA = 5
+ERR_OVERFLOW = 6
+MAX_CHANNELS = 32
+
+_SCALARS = {
+    "int": ctypes.c_int,
+    "int32_t": ctypes.c_int32,
+    "uint32_t": ctypes.c_uint32,
+    "int64_t": ctypes.c_int64,
+    "uint64_t": ctypes.c_uint64,
+    "size_t": ctypes.c_size_t,
+    "float": ctypes.c_float,
+}
+
+
+def parse_header(path: str = HEADER_PATH) -> Dict[str, Tuple[object, List[object]]]:
+    """Returns {symbol: (restype, [argtypes])} for every function declared in the header."""
+    text = open(path).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    text = re.sub(r"^\s*#.*$", "", text, flags=re.M)
+    text = text.replace('extern "C" {', "")
+    decls = {}
+    for m in re.finditer(r"([\w\s\*]+?)\b(splatad_\w+)\s*\(([^;{]*?)\)\s*;", text, flags=re.S):
+        ret, name, args = m.group(1).strip(), m.group(2), m.group(3).strip()
+        if "*" in ret:
+            restype = ctypes.c_char_p if "char" in ret else ctypes.c_void_p
+        else:
+            restype = _SCALARS[ret.replace("const", "").strip()]
+        argtypes = []
+        if args and args != "void":
+            for a in args.split(","):
+                a = a.strip()
+                if "*" in a:
+                    argtypes.append(ctypes.c_void_p)
+                else:
+                    ty = a.replace("const", "").split()[0]
+                    argtypes.append(_SCALARS[ty])
+        decls[name] = (restype, argtypes)
+    return decls
+
+
+def build(verbose: bool = False) -> str:
+    """Compiles the CUDA sources for sm_100a into ``libsplatad_b200.so`` (nvcc, in-tree)."""
+    cmd = ["make", "-C", CSRC_DIR, "-j", str(os.cpu_count() or 4)]
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if verbose or proc.returncode != 0:
+        print(proc.stdout)
+    if proc.returncode != 0:
+        raise RuntimeError("building libsplatad_b200.so failed:\n" + proc.stdout[-4000:])
+    return LIB_PATH
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def load() -> ctypes.CDLL:
+    """Loads the shared library (once) and sets the ctypes signatures from the header."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: the CUDA extension has not been built "
+            "(run `python -c 'import __graft_entry__ as g; g.build()'` or `make -C splatad_b200/csrc`). "
+            "splatad_b200 has no CPU fallback."
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in parse_header().items():
+        fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().splatad_last_error().decode("utf-8", "replace")
+
+
+def check(status: int) -> None:
+    """Maps a status code to the exception type the reference raises for the same condition."""
+    if status == OK:
+        return
+    msg = last_error() or f"splatad_b200 error {status}"
+    if status in (ERR_BAD_ARG, ERR_CHANNELS):
+        raise ValueError(msg)
+    raise RuntimeError(msg)
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    """Device pointer of a contiguous CUDA tensor (None stays NULL)."""
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError("splatad_b200 ops need CUDA tensors (there is no CPU fallback)")
+    if not t.is_contiguous():
+        raise RuntimeError("splatad_b200 ops need contiguous tensors")
+    return t.data_ptr()
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+# ---------------------------------------------------------------------------------------------
+# Grow-only per-device workspaces and pinned host slots (the library itself never allocates).
+# ---------------------------------------------------------------------------------------------
+_workspaces: Dict[Tuple[str, int], torch.Tensor] = {}
+_pinned: Dict[Tuple[str, int], torch.Tensor] = {}
+
+
+def workspace(tag: str, nbytes: int, device: torch.device) -> torch.Tensor:
+    key = (tag, device.index if device.index is not None else torch.cuda.current_device())
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        # grow with headroom so slowly growing scenes do not reallocate every frame
+        size = max(int(nbytes * 1.25) + 1024, 1 << 16)
+        buf = torch.empty(size, dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def pinned_counts(tag: str, device: torch.device, n: int = 4) -> torch.Tensor:
+    key = (tag, device.index if device.index is not None else torch.cuda.current_device())
+    buf = _pinned.get(key)
+    if buf is None or buf.numel() < n:
+        buf = torch.zeros(n, dtype=torch.int64).pin_memory()
+        _pinned[key] = buf
+    return buf
+
+
+def release_workspaces() -> None:
+    _workspaces.clear()
+    _pinned.clear()

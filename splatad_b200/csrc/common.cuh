@@ -1,0 +1,65 @@
+// Shared launch helpers, status codes and the last-error slot for the C-ABI library.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/splatad_b200.h"
+
+namespace splatad {
+
+constexpr int kThreads = 256;
+// B200 has 148 SMs; persistent kernels use a fixed grid that is a multiple of it.
+constexpr int kNumSMs = 148;
+
+void set_last_error(const char *fmt, ...);
+
+inline int check_launch(const char *what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_last_error("%s: %s", what, cudaGetErrorString(e));
+        return SPLATAD_ERR_CUDA;
+    }
+    return SPLATAD_OK;
+}
+
+#define SPL_REQUIRE(cond, code, ...)                                                             \
+    do {                                                                                         \
+        if (!(cond)) {                                                                           \
+            ::splatad::set_last_error(__VA_ARGS__);                                              \
+            return (code);                                                                       \
+        }                                                                                        \
+    } while (0)
+
+inline uint32_t div_up(uint64_t a, uint64_t b) { return (uint32_t)((a + b - 1) / b); }
+
+// Cooperative copy of `nfl` contiguous floats global -> shared with 128-bit loads when the
+// source is 16-byte aligned (it is whenever the tensor base is, because block slabs start at
+// multiples of 256 rows).
+__device__ __forceinline__ void stage_in(const float *__restrict__ src, float *smem, uint32_t nfl) {
+    if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+        const uint32_t nvec = nfl >> 2;
+        const float4 *s4 = reinterpret_cast<const float4 *>(src);
+        float4 *d4 = reinterpret_cast<float4 *>(smem);
+        for (uint32_t i = threadIdx.x; i < nvec; i += blockDim.x) d4[i] = __ldg(s4 + i);
+        for (uint32_t i = (nvec << 2) + threadIdx.x; i < nfl; i += blockDim.x) smem[i] = __ldg(src + i);
+    } else {
+        for (uint32_t i = threadIdx.x; i < nfl; i += blockDim.x) smem[i] = __ldg(src + i);
+    }
+}
+
+// Cooperative copy shared -> global, 128-bit stores when aligned.
+__device__ __forceinline__ void stage_out(float *__restrict__ dst, const float *smem, uint32_t nfl) {
+    if ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+        const uint32_t nvec = nfl >> 2;
+        float4 *d4 = reinterpret_cast<float4 *>(dst);
+        const float4 *s4 = reinterpret_cast<const float4 *>(smem);
+        for (uint32_t i = threadIdx.x; i < nvec; i += blockDim.x) d4[i] = s4[i];
+        for (uint32_t i = (nvec << 2) + threadIdx.x; i < nfl; i += blockDim.x) dst[i] = smem[i];
+    } else {
+        for (uint32_t i = threadIdx.x; i < nfl; i += blockDim.x) dst[i] = smem[i];
+    }
+}
+
+} // namespace splatad

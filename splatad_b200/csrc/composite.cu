@@ -1,0 +1,824 @@
+// Front-to-back alpha compositing of the depth-sorted per-tile Gaussian lists, to camera
+// pixels (rasterize_to_pixels) and to lidar points (rasterize_to_points), forward and
+// backward. FP32 on the CUDA cores; there is no dense contraction in this path.
+//
+// One CTA per tile, one thread per pixel / lidar point. A CTA walks its tile's list in
+// batches of blockDim Gaussians staged into shared memory as two float4 (+ extras for lidar),
+// stops as soon as every pixel of the tile is saturated, and a warp whose 32 pixels are all
+// saturated skips the batch body. The backward pass starts at the last list position any
+// pixel of the tile actually consumed instead of the end of the list.
+//
+// Semantics follow the reference kernels
+//   pixels fwd  gsplat/cuda/csrc/rasterization.cu:1360-1518     bwd 2833-3089
+//   points fwd  gsplat/cuda/csrc/rasterization.cu:2021-2219     bwd 3728-4054
+//   angle wrap  gsplat/cuda/csrc/utils.cuh:552-555
+// Thresholds kept: alpha cap 0.999, alpha < 1/255 skipped, sigma < 0 skipped, a pixel stops
+// (exclusively) when T*(1-alpha) <= 1e-4, median depth where T crosses 0.5, points with
+// range <= 0 are not rendered.
+#include "common.cuh"
+
+namespace splatad {
+
+constexpr float kAlphaMax = 0.999f;
+constexpr float kAlphaMin = 1.f / 255.f;
+constexpr float kTStop = 1e-4f;
+
+// Exactly fmodf((a - b + 180), 360) - 180 with the reference's final fix-up, but without the
+// fmodf call whenever |a - b + 180| stays within one turn of [0, 360).
+__device__ __forceinline__ float angle_difference(float a, float b) {
+    const float x = a - b + 180.f;
+    float r;
+    if (fabsf(x) < 360.f) r = x;
+    else if (x >= 360.f && x < 720.f) r = x - 360.f;
+    else r = fmodf(x, 360.f);
+    const float d = r - 180.f;
+    return d < -180.f ? d + 360.f : d;
+}
+
+struct TileRange { int32_t start, end; };
+
+__device__ __forceinline__ TileRange tile_range(const int32_t *__restrict__ offsets, uint32_t tile,
+                                                uint32_t n_tiles_total, int64_t n_isects) {
+    TileRange r;
+    r.start = offsets[tile];
+    r.end = (tile + 1 == n_tiles_total) ? (int32_t)n_isects : offsets[tile + 1];
+    return r;
+}
+
+// ---------------------------------------------------------------------------------------
+// Camera forward
+// ---------------------------------------------------------------------------------------
+template <int CDIM>
+__global__ void rasterize_to_pixels_fwd_kernel(
+    uint32_t C, int64_t n_isects, const float2 *__restrict__ means2d,
+    const float *__restrict__ conics, const float *__restrict__ colors, uint32_t channels,
+    const float *__restrict__ opacities, const float2 *__restrict__ pix_vels,
+    const float *__restrict__ rs_time, const float *__restrict__ backgrounds, uint32_t W,
+    uint32_t H, uint32_t tile_size, uint32_t tile_w, uint32_t tile_h,
+    const int32_t *__restrict__ offsets, const int32_t *__restrict__ flatten_ids,
+    float *__restrict__ render_colors, float *__restrict__ render_alphas,
+    int32_t *__restrict__ last_ids) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const uint32_t bs = blockDim.x;
+    float4 *sA = reinterpret_cast<float4 *>(smem_raw);   // x, y, vx, vy
+    float4 *sB = sA + bs;                                // conic a, b, c, opacity
+    int32_t *sId = reinterpret_cast<int32_t *>(sB + bs);
+
+    const uint32_t tiles_per_cam = tile_w * tile_h;
+    const uint32_t cam = blockIdx.x / tiles_per_cam;
+    const uint32_t tile = blockIdx.x - cam * tiles_per_cam;
+    const uint32_t ty = tile / tile_w, tx = tile - ty * tile_w;
+    const uint32_t tr = threadIdx.x;
+    const uint32_t i = ty * tile_size + tr / tile_size;
+    const uint32_t j = tx * tile_size + tr % tile_size;
+    const bool inside = (tr < tile_size * tile_size) && (i < H && j < W);
+    const float px = (float)j + 0.5f, py = (float)i + 0.5f;
+    const float roll = rs_time[cam] * ((py - 0.5f) / (float)(H - 1) - 0.5f);
+
+    const TileRange range = tile_range(offsets, blockIdx.x, C * tiles_per_cam, n_isects);
+    const uint32_t num_batches = (uint32_t)(range.end - range.start + bs - 1) / bs;
+
+    bool done = !inside;
+    float T = 1.f;
+    uint32_t cur_idx = 0;
+    float pix_out[CDIM];
+#pragma unroll
+    for (int k = 0; k < CDIM; ++k) pix_out[k] = 0.f;
+
+    for (uint32_t b = 0; b < num_batches; ++b) {
+        if (__syncthreads_count(done) >= (int)bs) break;
+        const uint32_t batch_start = (uint32_t)range.start + bs * b;
+        const uint32_t idx = batch_start + tr;
+        if (idx < (uint32_t)range.end) {
+            const int32_t g = flatten_ids[idx];
+            const float2 xy = means2d[g];
+            const float2 v = pix_vels[g];
+            sA[tr] = make_float4(xy.x, xy.y, v.x, v.y);
+            sB[tr] = make_float4(conics[3 * (size_t)g], conics[3 * (size_t)g + 1],
+                                 conics[3 * (size_t)g + 2], opacities[g]);
+            sId[tr] = g;
+        }
+        __syncthreads();
+        if (__all_sync(0xffffffffu, done)) continue;
+        const uint32_t batch_size = min(bs, (uint32_t)range.end - batch_start);
+        for (uint32_t t = 0; t < batch_size && !done; ++t) {
+            const float4 A = sA[t];
+            const float4 B = sB[t];
+            const float dx = A.x + roll * A.z - px;
+            const float dy = A.y + roll * A.w - py;
+            const float sigma = 0.5f * (B.x * dx * dx + B.z * dy * dy) + B.y * dx * dy;
+            const float alpha = fminf(kAlphaMax, B.w * __expf(-sigma));
+            if (sigma < 0.f || alpha < kAlphaMin) continue;
+            const float next_T = T * (1.f - alpha);
+            if (next_T <= kTStop) { done = true; break; }
+            const float vis = alpha * T;
+            const float *c_ptr = colors + (size_t)sId[t] * channels;
+#pragma unroll
+            for (int k = 0; k < CDIM; ++k)
+                if ((uint32_t)k < channels) pix_out[k] += __ldg(c_ptr + k) * vis;
+            cur_idx = batch_start + t;
+            T = next_T;
+        }
+    }
+    if (inside) {
+        const size_t pix = ((size_t)cam * H + i) * W + j;
+        render_alphas[pix] = 1.f - T;
+        const float *bg = backgrounds ? backgrounds + (size_t)cam * channels : nullptr;
+#pragma unroll
+        for (int k = 0; k < CDIM; ++k)
+            if ((uint32_t)k < channels)
+                render_colors[pix * channels + k] = bg ? (pix_out[k] + T * bg[k]) : pix_out[k];
+        last_ids[pix] = (int32_t)cur_idx;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Lidar forward
+// ---------------------------------------------------------------------------------------
+template <int CDIM>
+__global__ void rasterize_to_points_fwd_kernel(
+    uint32_t C, int64_t n_isects, const float2 *__restrict__ means2d,
+    const float *__restrict__ conics, const float *__restrict__ colors, uint32_t channels,
+    const float *__restrict__ opacities, const float *__restrict__ pix_vels /* [.,3] */,
+    const float2 *__restrict__ depth_comps, const float *__restrict__ backgrounds,
+    const float4 *__restrict__ raster_pts, uint32_t W, uint32_t H, uint32_t tile_width,
+    uint32_t tile_height, uint32_t grid_w, uint32_t grid_h, int compute_alpha_sum,
+    float alpha_sum_threshold, const int32_t *__restrict__ offsets,
+    const int32_t *__restrict__ flatten_ids, uint32_t depth_idx,
+    float *__restrict__ render_colors, float *__restrict__ render_alphas,
+    float *__restrict__ alpha_sum_out, int32_t *__restrict__ last_ids,
+    float *__restrict__ median_depths) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const uint32_t bs = blockDim.x;
+    float4 *sA = reinterpret_cast<float4 *>(smem_raw);   // az, el, v_az, v_el
+    float4 *sB = sA + bs;                                // conic a, b, c, opacity
+    float4 *sC = sB + bs;                                // v_range, dc.x, dc.y, range (depth channel)
+    int32_t *sId = reinterpret_cast<int32_t *>(sC + bs);
+
+    const uint32_t tiles_per_cam = grid_w * grid_h;
+    const uint32_t cam = blockIdx.x / tiles_per_cam;
+    const uint32_t tile = blockIdx.x - cam * tiles_per_cam;
+    const uint32_t ty = tile / grid_w, tx = tile - ty * grid_w;
+    const uint32_t tr = threadIdx.x;
+    const uint32_t i = ty * tile_height + tr / tile_width;
+    const uint32_t j = tx * tile_width + tr % tile_width;
+    const bool in_image = (tr < tile_width * tile_height) && (i < H && j < W);
+    bool inside = in_image;
+    const size_t pix = ((size_t)cam * H + i) * W + j;
+    float px = 0.f, py = 0.f, pz = 0.f, roll = 0.f;
+    if (inside) {
+        const float4 rp = raster_pts[pix];
+        px = rp.x; py = rp.y; pz = rp.z; roll = rp.w;
+        if (pz <= 0.f) inside = false;
+    }
+
+    const TileRange range = tile_range(offsets, blockIdx.x, C * tiles_per_cam, n_isects);
+    const uint32_t num_batches = (uint32_t)(range.end - range.start + bs - 1) / bs;
+
+    bool done = !inside;
+    float T = 1.f;
+    uint32_t cur_idx = 0;
+    float depth_extra = 0.f, alpha_sum = 0.f, median = 0.f;
+    float pix_out[CDIM];
+#pragma unroll
+    for (int k = 0; k < CDIM; ++k) pix_out[k] = 0.f;
+
+    for (uint32_t b = 0; b < num_batches; ++b) {
+        if (__syncthreads_count(done) >= (int)bs) break;
+        const uint32_t batch_start = (uint32_t)range.start + bs * b;
+        const uint32_t idx = batch_start + tr;
+        if (idx < (uint32_t)range.end) {
+            const int32_t g = flatten_ids[idx];
+            const float2 xy = means2d[g];
+            const float *v = pix_vels + 3 * (size_t)g;
+            const float2 dc = depth_comps[g];
+            sA[tr] = make_float4(xy.x, xy.y, v[0], v[1]);
+            sB[tr] = make_float4(conics[3 * (size_t)g], conics[3 * (size_t)g + 1],
+                                 conics[3 * (size_t)g + 2], opacities[g]);
+            sC[tr] = make_float4(v[2], dc.x, dc.y, colors[(size_t)g * channels + depth_idx]);
+            sId[tr] = g;
+        }
+        __syncthreads();
+        if (__all_sync(0xffffffffu, done)) continue;
+        const uint32_t batch_size = min(bs, (uint32_t)range.end - batch_start);
+        for (uint32_t t = 0; t < batch_size && !done; ++t) {
+            const float4 A = sA[t];
+            const float4 B = sB[t];
+            const float dx = angle_difference(A.x + roll * A.z, px);
+            const float dy = angle_difference(A.y + roll * A.w, py);
+            const float sigma = 0.5f * (B.x * dx * dx + B.z * dy * dy) + B.y * dx * dy;
+            const float alpha = fminf(kAlphaMax, B.w * __expf(-sigma));
+            if (sigma < 0.f || alpha < kAlphaMin) continue;
+            const float next_T = T * (1.f - alpha);
+            if (next_T <= kTStop) { done = true; break; }
+            const float vis = alpha * T;
+            const float4 Cc = sC[t];
+            const float *c_ptr = colors + (size_t)sId[t] * channels;
+#pragma unroll
+            for (int k = 0; k < CDIM; ++k)
+                if ((uint32_t)k < channels) pix_out[k] += __ldg(c_ptr + k) * vis;
+            const float dterm = Cc.y * dx + Cc.z * dy + Cc.x * roll;
+            depth_extra += dterm * vis;
+            if (T > 0.5f && next_T <= 0.5f) median = Cc.w + dterm;
+            if (compute_alpha_sum && Cc.w < (pz - alpha_sum_threshold)) alpha_sum += alpha;
+            cur_idx = batch_start + t;
+            T = next_T;
+        }
+    }
+    if (in_image) {
+        // points that are not rendered (range <= 0) produce zeros everywhere
+        render_alphas[pix] = inside ? 1.f - T : 0.f;
+        const float *bg = backgrounds ? backgrounds + (size_t)cam * channels : nullptr;
+#pragma unroll
+        for (int k = 0; k < CDIM; ++k)
+            if ((uint32_t)k < channels) {
+                float v = pix_out[k];
+                if ((uint32_t)k == depth_idx) v += depth_extra;
+                if (bg) v += T * bg[k];
+                render_colors[pix * channels + k] = inside ? v : 0.f;
+            }
+        last_ids[pix] = inside ? (int32_t)cur_idx : 0;
+        median_depths[pix] = inside ? median : 0.f;
+        if (alpha_sum_out != nullptr) alpha_sum_out[pix] = inside ? alpha_sum : 0.f;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Backward helpers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+__device__ __forceinline__ int block_max_int(int v, int *red /* [32] */) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, off));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    int m = red[0];
+    for (uint32_t w = 1; w < (blockDim.x + 31) / 32; ++w) m = max(m, red[w]);
+    __syncthreads();
+    return m;
+}
+
+// ---------------------------------------------------------------------------------------
+// Camera backward
+// ---------------------------------------------------------------------------------------
+template <int CDIM>
+__global__ void rasterize_to_pixels_bwd_kernel(
+    uint32_t C, int64_t n_isects, const float2 *__restrict__ means2d,
+    const float *__restrict__ conics, const float *__restrict__ colors, uint32_t channels,
+    const float *__restrict__ opacities, const float2 *__restrict__ pix_vels,
+    const float *__restrict__ rs_time, const float *__restrict__ backgrounds, uint32_t W,
+    uint32_t H, uint32_t tile_size, uint32_t tile_w, uint32_t tile_h,
+    const int32_t *__restrict__ offsets, const int32_t *__restrict__ flatten_ids,
+    const float *__restrict__ render_alphas, const int32_t *__restrict__ last_ids,
+    const float *__restrict__ v_render_colors, const float *__restrict__ v_render_alphas,
+    float *__restrict__ v_means2d_abs, float *__restrict__ v_means2d,
+    float *__restrict__ v_conics, float *__restrict__ v_colors, float *__restrict__ v_opacities,
+    float *__restrict__ v_pix_vels) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int red[32];
+    const uint32_t bs = blockDim.x;
+    float4 *sA = reinterpret_cast<float4 *>(smem_raw);
+    float4 *sB = sA + bs;
+    int32_t *sId = reinterpret_cast<int32_t *>(sB + bs);
+    float *sRgb = reinterpret_cast<float *>(sId + bs);   // [bs * channels]
+
+    const uint32_t tiles_per_cam = tile_w * tile_h;
+    const uint32_t cam = blockIdx.x / tiles_per_cam;
+    const uint32_t tile = blockIdx.x - cam * tiles_per_cam;
+    const uint32_t ty = tile / tile_w, tx = tile - ty * tile_w;
+    const uint32_t tr = threadIdx.x;
+    const uint32_t i = ty * tile_size + tr / tile_size;
+    const uint32_t j = tx * tile_size + tr % tile_size;
+    const bool inside = (tr < tile_size * tile_size) && (i < H && j < W);
+    const float px = (float)j + 0.5f, py = (float)i + 0.5f;
+    const float roll = rs_time[cam] * ((py - 0.5f) / (float)(H - 1) - 0.5f);
+    const size_t pix = ((size_t)cam * H + min(i, H - 1)) * W + min(j, W - 1);
+
+    const TileRange range = tile_range(offsets, blockIdx.x, C * tiles_per_cam, n_isects);
+
+    const float T_final = 1.f - render_alphas[pix];
+    float T = T_final;
+    const int32_t bin_final = inside ? last_ids[pix] : 0;
+    float buffer[CDIM], v_render_c[CDIM];
+    float bg_dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < CDIM; ++k) {
+        buffer[k] = 0.f;
+        v_render_c[k] = ((uint32_t)k < channels && inside) ? v_render_colors[pix * channels + k] : 0.f;
+        if (backgrounds != nullptr && (uint32_t)k < channels)
+            bg_dot += backgrounds[(size_t)cam * channels + k] * v_render_c[k];
+    }
+    const float v_render_a = inside ? v_render_alphas[pix] : 0.f;
+
+    // last list position consumed by any pixel of this tile
+    const int32_t tile_last = block_max_int(bin_final, red);
+    int32_t warp_bin_final = bin_final;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+        warp_bin_final = max(warp_bin_final, __shfl_xor_sync(0xffffffffu, warp_bin_final, off));
+    const int32_t eff_end = min(range.end, tile_last + 1);
+    if (eff_end <= range.start) return;
+    const uint32_t num_batches = (uint32_t)(eff_end - range.start + bs - 1) / bs;
+    const uint32_t lane = tr & 31;
+
+    for (uint32_t b = 0; b < num_batches; ++b) {
+        __syncthreads();
+        const int32_t batch_end = eff_end - 1 - (int32_t)(bs * b);
+        const int32_t batch_size = min((int32_t)bs, batch_end + 1 - range.start);
+        const int32_t idx = batch_end - (int32_t)tr;
+        if (idx >= range.start) {
+            const int32_t g = flatten_ids[idx];
+            const float2 xy = means2d[g];
+            const float2 v = pix_vels[g];
+            sA[tr] = make_float4(xy.x, xy.y, v.x, v.y);
+            sB[tr] = make_float4(conics[3 * (size_t)g], conics[3 * (size_t)g + 1],
+                                 conics[3 * (size_t)g + 2], opacities[g]);
+            sId[tr] = g;
+            for (uint32_t k = 0; k < channels; ++k) sRgb[tr * channels + k] = colors[(size_t)g * channels + k];
+        }
+        __syncthreads();
+        for (int32_t t = max(0, batch_end - warp_bin_final); t < batch_size; ++t) {
+            bool valid = inside && (batch_end - t <= bin_final);
+            float alpha = 0.f, opac = 0.f, vis = 0.f, dx = 0.f, dy = 0.f;
+            float4 B = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (valid) {
+                const float4 A = sA[t];
+                B = sB[t];
+                opac = B.w;
+                dx = A.x + roll * A.z - px;
+                dy = A.y + roll * A.w - py;
+                const float sigma = 0.5f * (B.x * dx * dx + B.z * dy * dy) + B.y * dx * dy;
+                vis = __expf(-sigma);
+                alpha = fminf(kAlphaMax, opac * vis);
+                if (sigma < 0.f || alpha < kAlphaMin) valid = false;
+            }
+            if (!__any_sync(0xffffffffu, valid)) continue;
+            float v_rgb[CDIM];
+#pragma unroll
+            for (int k = 0; k < CDIM; ++k) v_rgb[k] = 0.f;
+            float v_conic_x = 0.f, v_conic_y = 0.f, v_conic_z = 0.f;
+            float v_x = 0.f, v_y = 0.f, v_ax = 0.f, v_ay = 0.f, v_vx = 0.f, v_vy = 0.f, v_o = 0.f;
+            if (valid) {
+                const float ra = 1.f / (1.f - alpha);
+                T *= ra;
+                const float fac = alpha * T;
+                float v_alpha = 0.f;
+                const float *rgb = sRgb + (uint32_t)t * channels;
+#pragma unroll
+                for (int k = 0; k < CDIM; ++k)
+                    if ((uint32_t)k < channels) {
+                        v_rgb[k] = fac * v_render_c[k];
+                        v_alpha += (rgb[k] * T - buffer[k] * ra) * v_render_c[k];
+                    }
+                v_alpha += T_final * ra * v_render_a;
+                if (backgrounds != nullptr) v_alpha += -T_final * ra * bg_dot;
+                if (opac * vis <= kAlphaMax) {
+                    const float v_sigma = -opac * vis * v_alpha;
+                    v_conic_x = 0.5f * v_sigma * dx * dx;
+                    v_conic_y = v_sigma * dx * dy;
+                    v_conic_z = 0.5f * v_sigma * dy * dy;
+                    v_x = v_sigma * (B.x * dx + B.y * dy);
+                    v_y = v_sigma * (B.y * dx + B.z * dy);
+                    v_vx = v_x * roll;
+                    v_vy = v_y * roll;
+                    v_ax = fabsf(v_x);
+                    v_ay = fabsf(v_y);
+                    v_o = vis * v_alpha;
+                }
+#pragma unroll
+                for (int k = 0; k < CDIM; ++k)
+                    if ((uint32_t)k < channels) buffer[k] += rgb[k] * fac;
+            }
+#pragma unroll
+            for (int k = 0; k < CDIM; ++k)
+                if ((uint32_t)k < channels) v_rgb[k] = warp_sum(v_rgb[k]);
+            v_conic_x = warp_sum(v_conic_x); v_conic_y = warp_sum(v_conic_y); v_conic_z = warp_sum(v_conic_z);
+            v_x = warp_sum(v_x); v_y = warp_sum(v_y);
+            v_vx = warp_sum(v_vx); v_vy = warp_sum(v_vy);
+            v_o = warp_sum(v_o);
+            if (v_means2d_abs != nullptr) { v_ax = warp_sum(v_ax); v_ay = warp_sum(v_ay); }
+            if (lane == 0) {
+                const size_t g = (size_t)sId[t];
+#pragma unroll
+                for (int k = 0; k < CDIM; ++k)
+                    if ((uint32_t)k < channels) atomicAdd(v_colors + g * channels + k, v_rgb[k]);
+                atomicAdd(v_conics + 3 * g, v_conic_x);
+                atomicAdd(v_conics + 3 * g + 1, v_conic_y);
+                atomicAdd(v_conics + 3 * g + 2, v_conic_z);
+                atomicAdd(v_means2d + 2 * g, v_x);
+                atomicAdd(v_means2d + 2 * g + 1, v_y);
+                if (v_means2d_abs != nullptr) {
+                    atomicAdd(v_means2d_abs + 2 * g, v_ax);
+                    atomicAdd(v_means2d_abs + 2 * g + 1, v_ay);
+                }
+                atomicAdd(v_pix_vels + 2 * g, v_vx);
+                atomicAdd(v_pix_vels + 2 * g + 1, v_vy);
+                atomicAdd(v_opacities + g, v_o);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Lidar backward
+// ---------------------------------------------------------------------------------------
+template <int CDIM>
+__global__ void rasterize_to_points_bwd_kernel(
+    uint32_t C, int64_t n_isects, const float2 *__restrict__ means2d,
+    const float *__restrict__ conics, const float *__restrict__ colors, uint32_t channels,
+    const float *__restrict__ opacities, const float *__restrict__ pix_vels,
+    const float2 *__restrict__ depth_comps, const float *__restrict__ backgrounds,
+    const float4 *__restrict__ raster_pts, uint32_t W, uint32_t H, uint32_t tile_width,
+    uint32_t tile_height, uint32_t grid_w, uint32_t grid_h, int compute_alpha_sum,
+    float alpha_sum_threshold, const int32_t *__restrict__ offsets,
+    const int32_t *__restrict__ flatten_ids, uint32_t depth_idx,
+    const float *__restrict__ render_alphas, const int32_t *__restrict__ last_ids,
+    const float *__restrict__ v_render_colors, const float *__restrict__ v_render_alphas,
+    const float *__restrict__ v_alpha_sum, float *__restrict__ v_means2d_abs,
+    float *__restrict__ v_means2d, float *__restrict__ v_conics, float *__restrict__ v_colors,
+    float *__restrict__ v_opacities, float *__restrict__ v_pix_vels,
+    float *__restrict__ v_depth_comps) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int red[32];
+    const uint32_t bs = blockDim.x;
+    float4 *sA = reinterpret_cast<float4 *>(smem_raw);
+    float4 *sB = sA + bs;
+    float4 *sC = sB + bs;   // v_range, dc.x, dc.y, unused
+    int32_t *sId = reinterpret_cast<int32_t *>(sC + bs);
+    float *sRgb = reinterpret_cast<float *>(sId + bs);
+
+    const uint32_t tiles_per_cam = grid_w * grid_h;
+    const uint32_t cam = blockIdx.x / tiles_per_cam;
+    const uint32_t tile = blockIdx.x - cam * tiles_per_cam;
+    const uint32_t ty = tile / grid_w, tx = tile - ty * grid_w;
+    const uint32_t tr = threadIdx.x;
+    const uint32_t i = ty * tile_height + tr / tile_width;
+    const uint32_t j = tx * tile_width + tr % tile_width;
+    bool inside = (tr < tile_width * tile_height) && (i < H && j < W);
+    const size_t pix = ((size_t)cam * H + min(i, H - 1)) * W + min(j, W - 1);
+    float px = 0.f, py = 0.f, pz = 0.f, roll = 0.f;
+    if (inside) {
+        const float4 rp = raster_pts[pix];
+        px = rp.x; py = rp.y; pz = rp.z; roll = rp.w;
+        if (pz <= 0.f) inside = false;
+    }
+
+    const TileRange range = tile_range(offsets, blockIdx.x, C * tiles_per_cam, n_isects);
+
+    const float T_final = 1.f - render_alphas[pix];
+    float T = T_final;
+    const int32_t bin_final = inside ? last_ids[pix] : 0;
+    float buffer[CDIM], v_render_c[CDIM];
+    float buffer_extra = 0.f;   // depth-compensation part of the depth channel's buffer
+    float bg_dot = 0.f, v_depth_c = 0.f;
+#pragma unroll
+    for (int k = 0; k < CDIM; ++k) {
+        buffer[k] = 0.f;
+        v_render_c[k] = ((uint32_t)k < channels && inside) ? v_render_colors[pix * channels + k] : 0.f;
+        if ((uint32_t)k == depth_idx) v_depth_c = v_render_c[k];
+        if (backgrounds != nullptr && (uint32_t)k < channels)
+            bg_dot += backgrounds[(size_t)cam * channels + k] * v_render_c[k];
+    }
+    const float v_render_a = inside ? v_render_alphas[pix] : 0.f;
+    const float v_asum = (inside && v_alpha_sum != nullptr) ? v_alpha_sum[pix] : 0.f;
+
+    const int32_t tile_last = block_max_int(bin_final, red);
+    int32_t warp_bin_final = bin_final;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1)
+        warp_bin_final = max(warp_bin_final, __shfl_xor_sync(0xffffffffu, warp_bin_final, off));
+    const int32_t eff_end = min(range.end, tile_last + 1);
+    if (eff_end <= range.start) return;
+    const uint32_t num_batches = (uint32_t)(eff_end - range.start + bs - 1) / bs;
+    const uint32_t lane = tr & 31;
+
+    for (uint32_t b = 0; b < num_batches; ++b) {
+        __syncthreads();
+        const int32_t batch_end = eff_end - 1 - (int32_t)(bs * b);
+        const int32_t batch_size = min((int32_t)bs, batch_end + 1 - range.start);
+        const int32_t idx = batch_end - (int32_t)tr;
+        if (idx >= range.start) {
+            const int32_t g = flatten_ids[idx];
+            const float2 xy = means2d[g];
+            const float *v = pix_vels + 3 * (size_t)g;
+            const float2 dc = depth_comps[g];
+            sA[tr] = make_float4(xy.x, xy.y, v[0], v[1]);
+            sB[tr] = make_float4(conics[3 * (size_t)g], conics[3 * (size_t)g + 1],
+                                 conics[3 * (size_t)g + 2], opacities[g]);
+            sC[tr] = make_float4(v[2], dc.x, dc.y, 0.f);
+            sId[tr] = g;
+            for (uint32_t k = 0; k < channels; ++k) sRgb[tr * channels + k] = colors[(size_t)g * channels + k];
+        }
+        __syncthreads();
+        for (int32_t t = max(0, batch_end - warp_bin_final); t < batch_size; ++t) {
+            bool valid = inside && (batch_end - t <= bin_final);
+            float alpha = 0.f, opac = 0.f, vis = 0.f, dx = 0.f, dy = 0.f;
+            float4 B = make_float4(0.f, 0.f, 0.f, 0.f), Cc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (valid) {
+                const float4 A = sA[t];
+                B = sB[t];
+                Cc = sC[t];
+                opac = B.w;
+                dx = angle_difference(A.x + roll * A.z, px);
+                dy = angle_difference(A.y + roll * A.w, py);
+                const float sigma = 0.5f * (B.x * dx * dx + B.z * dy * dy) + B.y * dx * dy;
+                vis = __expf(-sigma);
+                alpha = fminf(kAlphaMax, opac * vis);
+                if (sigma < 0.f || alpha < kAlphaMin) valid = false;
+            }
+            if (!__any_sync(0xffffffffu, valid)) continue;
+            float v_rgb[CDIM];
+#pragma unroll
+            for (int k = 0; k < CDIM; ++k) v_rgb[k] = 0.f;
+            float v_conic_x = 0.f, v_conic_y = 0.f, v_conic_z = 0.f;
+            float v_x = 0.f, v_y = 0.f, v_ax = 0.f, v_ay = 0.f, v_o = 0.f;
+            float v_vx = 0.f, v_vy = 0.f, v_vz = 0.f, v_dcx = 0.f, v_dcy = 0.f;
+            if (valid) {
+                const float ra = 1.f / (1.f - alpha);
+                T *= ra;
+                const float fac = alpha * T;
+                const float dterm = Cc.y * dx + Cc.z * dy + Cc.x * roll;
+                float v_alpha = 0.f;
+                const float *rgb = sRgb + (uint32_t)t * channels;
+#pragma unroll
+                for (int k = 0; k < CDIM; ++k)
+                    if ((uint32_t)k < channels) {
+                        v_rgb[k] = fac * v_render_c[k];
+                        float bk = buffer[k];
+                        if ((uint32_t)k == depth_idx) bk += buffer_extra;
+                        v_alpha += (rgb[k] * T - bk * ra) * v_render_c[k];
+                    }
+                const float v_rgb_depth = fac * v_depth_c;
+                v_alpha += dterm * T * v_depth_c;
+                v_alpha += T_final * ra * v_render_a;
+                if (backgrounds != nullptr) v_alpha += -T_final * ra * bg_dot;
+                if (opac * vis <= kAlphaMax) {
+                    v_dcx = v_rgb_depth * dx;
+                    v_dcy = v_rgb_depth * dy;
+                    v_vz = v_rgb_depth * roll;
+                    const float v_sigma = -opac * vis * v_alpha;
+                    v_conic_x = 0.5f * v_sigma * dx * dx;
+                    v_conic_y = v_sigma * dx * dy;
+                    v_conic_z = 0.5f * v_sigma * dy * dy;
+                    v_x = v_sigma * (B.x * dx + B.y * dy) + v_rgb_depth * Cc.y;
+                    v_y = v_sigma * (B.y * dx + B.z * dy) + v_rgb_depth * Cc.z;
+                    v_vx = v_x * roll;
+                    v_vy = v_y * roll;
+                    v_ax = fabsf(v_x);
+                    v_ay = fabsf(v_y);
+                    v_o = vis * v_alpha;
+                }
+#pragma unroll
+                for (int k = 0; k < CDIM; ++k)
+                    if ((uint32_t)k < channels) buffer[k] += rgb[k] * fac;
+                buffer_extra += dterm * fac;
+
+                const float g_depth = rgb[depth_idx];
+                if (compute_alpha_sum && g_depth < (pz - alpha_sum_threshold)) {
+                    const float vs = v_asum * -opac * vis;
+                    const float ux = vs * (B.x * dx + B.y * dy);
+                    const float uy = vs * (B.y * dx + B.z * dy);
+                    v_x += ux; v_y += uy;
+                    v_vx += ux * roll; v_vy += uy * roll;
+                    v_ax += fabsf(ux); v_ay += fabsf(uy);
+                    v_conic_x += vs * 0.5f * dx * dx;
+                    v_conic_y += vs * dx * dy;
+                    v_conic_z += vs * 0.5f * dy * dy;
+                    v_o += v_asum * vis;
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < CDIM; ++k)
+                if ((uint32_t)k < channels) v_rgb[k] = warp_sum(v_rgb[k]);
+            v_conic_x = warp_sum(v_conic_x); v_conic_y = warp_sum(v_conic_y); v_conic_z = warp_sum(v_conic_z);
+            v_x = warp_sum(v_x); v_y = warp_sum(v_y);
+            v_vx = warp_sum(v_vx); v_vy = warp_sum(v_vy); v_vz = warp_sum(v_vz);
+            v_dcx = warp_sum(v_dcx); v_dcy = warp_sum(v_dcy);
+            v_o = warp_sum(v_o);
+            if (v_means2d_abs != nullptr) { v_ax = warp_sum(v_ax); v_ay = warp_sum(v_ay); }
+            if (lane == 0) {
+                const size_t g = (size_t)sId[t];
+#pragma unroll
+                for (int k = 0; k < CDIM; ++k)
+                    if ((uint32_t)k < channels) atomicAdd(v_colors + g * channels + k, v_rgb[k]);
+                atomicAdd(v_conics + 3 * g, v_conic_x);
+                atomicAdd(v_conics + 3 * g + 1, v_conic_y);
+                atomicAdd(v_conics + 3 * g + 2, v_conic_z);
+                atomicAdd(v_means2d + 2 * g, v_x);
+                atomicAdd(v_means2d + 2 * g + 1, v_y);
+                if (v_means2d_abs != nullptr) {
+                    atomicAdd(v_means2d_abs + 2 * g, v_ax);
+                    atomicAdd(v_means2d_abs + 2 * g + 1, v_ay);
+                }
+                atomicAdd(v_pix_vels + 3 * g, v_vx);
+                atomicAdd(v_pix_vels + 3 * g + 1, v_vy);
+                atomicAdd(v_pix_vels + 3 * g + 2, v_vz);
+                atomicAdd(v_depth_comps + 2 * g, v_dcx);
+                atomicAdd(v_depth_comps + 2 * g + 1, v_dcy);
+                atomicAdd(v_opacities + g, v_o);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Dispatch on the channel count
+// ---------------------------------------------------------------------------------------
+#define SPL_DISPATCH_CDIM(channels, CALL)                                                        \
+    do {                                                                                         \
+        if ((channels) <= 4) { CALL(4); }                                                        \
+        else if ((channels) <= 8) { CALL(8); }                                                   \
+        else if ((channels) <= 16) { CALL(16); }                                                 \
+        else if ((channels) <= 20) { CALL(20); }                                                 \
+        else { CALL(32); }                                                                       \
+    } while (0)
+
+template <typename K>
+static int set_smem(K kernel, size_t bytes, const char *what) {
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) {
+            set_last_error("%s: cannot reserve %zu bytes of shared memory: %s", what, bytes,
+                           cudaGetErrorString(e));
+            return SPLATAD_ERR_CUDA;
+        }
+    }
+    return SPLATAD_OK;
+}
+
+} // namespace splatad
+
+using namespace splatad;
+
+extern "C" int splatad_rasterize_to_pixels_fwd(
+    uint32_t C, int64_t n_isects, const float *means2d, const float *conics, const float *colors,
+    uint32_t channels, const float *opacities, const float *pix_vels,
+    const float *rolling_shutter_time, const float *backgrounds, uint32_t image_width,
+    uint32_t image_height, uint32_t tile_size, uint32_t tile_width, uint32_t tile_height,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, float *render_colors,
+    float *render_alphas, int32_t *last_ids, void *stream) {
+    SPL_REQUIRE(channels >= 1 && channels <= SPLATAD_MAX_CHANNELS, SPLATAD_ERR_CHANNELS,
+                "rasterize_to_pixels_fwd: unsupported channel count %u (1..%d)", channels,
+                SPLATAD_MAX_CHANNELS);
+    SPL_REQUIRE(tile_size >= 1 && tile_size * tile_size <= 1024, SPLATAD_ERR_BAD_ARG,
+                "rasterize_to_pixels_fwd: tile_size^2 must be <= 1024");
+    SPL_REQUIRE(render_colors && render_alphas && last_ids && tile_offsets && rolling_shutter_time,
+                SPLATAD_ERR_BAD_ARG, "rasterize_to_pixels_fwd: null argument");
+    SPL_REQUIRE(n_isects == 0 || (means2d && conics && colors && opacities && pix_vels && flatten_ids),
+                SPLATAD_ERR_BAD_ARG, "rasterize_to_pixels_fwd: null input");
+    const uint32_t blocks = C * tile_width * tile_height;
+    if (blocks == 0 || image_width == 0 || image_height == 0) return SPLATAD_OK;
+    const uint32_t bs = ((tile_size * tile_size + 31) / 32) * 32;   // whole warps
+    const size_t smem = (size_t)bs * (2 * sizeof(float4) + sizeof(int32_t));
+#define CALL(D)                                                                                   \
+    {                                                                                             \
+        int rc = set_smem(rasterize_to_pixels_fwd_kernel<D>, smem, "rasterize_to_pixels_fwd");    \
+        if (rc != SPLATAD_OK) return rc;                                                          \
+        rasterize_to_pixels_fwd_kernel<D><<<blocks, bs, smem, (cudaStream_t)stream>>>(            \
+            C, n_isects, (const float2 *)means2d, conics, colors, channels, opacities,            \
+            (const float2 *)pix_vels, rolling_shutter_time, backgrounds, image_width,             \
+            image_height, tile_size, tile_width, tile_height, tile_offsets, flatten_ids,          \
+            render_colors, render_alphas, last_ids);                                              \
+    }
+    SPL_DISPATCH_CDIM(channels, CALL);
+#undef CALL
+    return check_launch("rasterize_to_pixels_fwd");
+}
+
+extern "C" int splatad_rasterize_to_pixels_bwd(
+    uint32_t C, int64_t n_isects, const float *means2d, const float *conics, const float *colors,
+    uint32_t channels, const float *opacities, const float *pix_vels,
+    const float *rolling_shutter_time, const float *backgrounds, uint32_t image_width,
+    uint32_t image_height, uint32_t tile_size, uint32_t tile_width, uint32_t tile_height,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, const float *render_alphas,
+    const int32_t *last_ids, const float *v_render_colors, const float *v_render_alphas,
+    float *v_means2d_abs, float *v_means2d, float *v_conics, float *v_colors, float *v_opacities,
+    float *v_pix_vels, void *stream) {
+    SPL_REQUIRE(channels >= 1 && channels <= SPLATAD_MAX_CHANNELS, SPLATAD_ERR_CHANNELS,
+                "rasterize_to_pixels_bwd: unsupported channel count %u (1..%d)", channels,
+                SPLATAD_MAX_CHANNELS);
+    SPL_REQUIRE(tile_size >= 1 && tile_size * tile_size <= 1024, SPLATAD_ERR_BAD_ARG,
+                "rasterize_to_pixels_bwd: tile_size^2 must be <= 1024");
+    const uint32_t blocks = C * tile_width * tile_height;
+    if (blocks == 0 || n_isects == 0 || image_width == 0 || image_height == 0) return SPLATAD_OK;
+    SPL_REQUIRE(means2d && conics && colors && opacities && pix_vels && flatten_ids &&
+                    tile_offsets && render_alphas && last_ids && v_render_colors &&
+                    v_render_alphas && v_means2d && v_conics && v_colors && v_opacities &&
+                    v_pix_vels && rolling_shutter_time,
+                SPLATAD_ERR_BAD_ARG, "rasterize_to_pixels_bwd: null argument");
+    const uint32_t bs = ((tile_size * tile_size + 31) / 32) * 32;   // whole warps
+    const size_t smem = (size_t)bs * (2 * sizeof(float4) + sizeof(int32_t) + channels * sizeof(float));
+#define CALL(D)                                                                                   \
+    {                                                                                             \
+        int rc = set_smem(rasterize_to_pixels_bwd_kernel<D>, smem, "rasterize_to_pixels_bwd");    \
+        if (rc != SPLATAD_OK) return rc;                                                          \
+        rasterize_to_pixels_bwd_kernel<D><<<blocks, bs, smem, (cudaStream_t)stream>>>(            \
+            C, n_isects, (const float2 *)means2d, conics, colors, channels, opacities,            \
+            (const float2 *)pix_vels, rolling_shutter_time, backgrounds, image_width,             \
+            image_height, tile_size, tile_width, tile_height, tile_offsets, flatten_ids,          \
+            render_alphas, last_ids, v_render_colors, v_render_alphas, v_means2d_abs, v_means2d,  \
+            v_conics, v_colors, v_opacities, v_pix_vels);                                         \
+    }
+    SPL_DISPATCH_CDIM(channels, CALL);
+#undef CALL
+    return check_launch("rasterize_to_pixels_bwd");
+}
+
+extern "C" int splatad_rasterize_to_points_fwd(
+    uint32_t C, int64_t n_isects, const float *means2d, const float *conics,
+    const float *lidar_features, uint32_t channels, const float *opacities,
+    const float *pix_vels, const float *depth_compensations, const float *backgrounds,
+    const float *raster_pts, uint32_t image_width, uint32_t image_height, uint32_t tile_width,
+    uint32_t tile_height, uint32_t tile_grid_width, uint32_t tile_grid_height,
+    int32_t compute_alpha_sum_until_points, float alpha_sum_threshold,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, uint32_t depth_channel_idx,
+    float *render_features, float *render_alphas, float *alpha_sum_until_points,
+    int32_t *last_ids, float *median_depths, void *stream) {
+    SPL_REQUIRE(channels >= 1 && channels <= SPLATAD_MAX_CHANNELS, SPLATAD_ERR_CHANNELS,
+                "rasterize_to_points_fwd: unsupported channel count %u (1..%d)", channels,
+                SPLATAD_MAX_CHANNELS);
+    SPL_REQUIRE(depth_channel_idx < channels, SPLATAD_ERR_BAD_ARG,
+                "rasterize_to_points_fwd: depth channel out of range");
+    SPL_REQUIRE(tile_width >= 1 && tile_height >= 1 && tile_width * tile_height <= 1024,
+                SPLATAD_ERR_BAD_ARG, "rasterize_to_points_fwd: tile must have <= 1024 points");
+    SPL_REQUIRE(render_features && render_alphas && last_ids && median_depths && tile_offsets &&
+                    raster_pts,
+                SPLATAD_ERR_BAD_ARG, "rasterize_to_points_fwd: null argument");
+    SPL_REQUIRE(!compute_alpha_sum_until_points || alpha_sum_until_points, SPLATAD_ERR_BAD_ARG,
+                "rasterize_to_points_fwd: alpha-sum output missing");
+    SPL_REQUIRE(n_isects == 0 || (means2d && conics && lidar_features && opacities && pix_vels &&
+                                  depth_compensations && flatten_ids),
+                SPLATAD_ERR_BAD_ARG, "rasterize_to_points_fwd: null input");
+    const uint32_t blocks = C * tile_grid_width * tile_grid_height;
+    if (blocks == 0 || image_width == 0 || image_height == 0) return SPLATAD_OK;
+    const uint32_t bs = ((tile_width * tile_height + 31) / 32) * 32;   // whole warps
+    const size_t smem = (size_t)bs * (3 * sizeof(float4) + sizeof(int32_t));
+#define CALL(D)                                                                                   \
+    {                                                                                             \
+        int rc = set_smem(rasterize_to_points_fwd_kernel<D>, smem, "rasterize_to_points_fwd");    \
+        if (rc != SPLATAD_OK) return rc;                                                          \
+        rasterize_to_points_fwd_kernel<D><<<blocks, bs, smem, (cudaStream_t)stream>>>(            \
+            C, n_isects, (const float2 *)means2d, conics, lidar_features, channels, opacities,    \
+            pix_vels, (const float2 *)depth_compensations, backgrounds,                           \
+            (const float4 *)raster_pts, image_width, image_height, tile_width, tile_height,       \
+            tile_grid_width, tile_grid_height, compute_alpha_sum_until_points,                    \
+            alpha_sum_threshold, tile_offsets, flatten_ids, depth_channel_idx, render_features,   \
+            render_alphas, alpha_sum_until_points, last_ids, median_depths);                      \
+    }
+    SPL_DISPATCH_CDIM(channels, CALL);
+#undef CALL
+    return check_launch("rasterize_to_points_fwd");
+}
+
+extern "C" int splatad_rasterize_to_points_bwd(
+    uint32_t C, int64_t n_isects, const float *means2d, const float *conics,
+    const float *lidar_features, uint32_t channels, const float *opacities,
+    const float *pix_vels, const float *depth_compensations, const float *backgrounds,
+    const float *raster_pts, uint32_t image_width, uint32_t image_height, uint32_t tile_width,
+    uint32_t tile_height, uint32_t tile_grid_width, uint32_t tile_grid_height,
+    int32_t compute_alpha_sum_until_points, float alpha_sum_threshold,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, uint32_t depth_channel_idx,
+    const float *render_alphas, const int32_t *last_ids, const float *v_render_features,
+    const float *v_render_alphas, const float *v_alpha_sum_until_points, float *v_means2d_abs,
+    float *v_means2d, float *v_conics, float *v_features, float *v_opacities, float *v_pix_vels,
+    float *v_depth_compensations, void *stream) {
+    SPL_REQUIRE(channels >= 1 && channels <= SPLATAD_MAX_CHANNELS, SPLATAD_ERR_CHANNELS,
+                "rasterize_to_points_bwd: unsupported channel count %u (1..%d)", channels,
+                SPLATAD_MAX_CHANNELS);
+    SPL_REQUIRE(depth_channel_idx < channels, SPLATAD_ERR_BAD_ARG,
+                "rasterize_to_points_bwd: depth channel out of range");
+    SPL_REQUIRE(tile_width >= 1 && tile_height >= 1 && tile_width * tile_height <= 1024,
+                SPLATAD_ERR_BAD_ARG, "rasterize_to_points_bwd: tile must have <= 1024 points");
+    const uint32_t blocks = C * tile_grid_width * tile_grid_height;
+    if (blocks == 0 || n_isects == 0 || image_width == 0 || image_height == 0) return SPLATAD_OK;
+    SPL_REQUIRE(means2d && conics && lidar_features && opacities && pix_vels &&
+                    depth_compensations && flatten_ids && tile_offsets && raster_pts &&
+                    render_alphas && last_ids && v_render_features && v_render_alphas &&
+                    v_means2d && v_conics && v_features && v_opacities && v_pix_vels &&
+                    v_depth_compensations,
+                SPLATAD_ERR_BAD_ARG, "rasterize_to_points_bwd: null argument");
+    const uint32_t bs = ((tile_width * tile_height + 31) / 32) * 32;   // whole warps
+    const size_t smem = (size_t)bs * (3 * sizeof(float4) + sizeof(int32_t) + channels * sizeof(float));
+#define CALL(D)                                                                                   \
+    {                                                                                             \
+        int rc = set_smem(rasterize_to_points_bwd_kernel<D>, smem, "rasterize_to_points_bwd");    \
+        if (rc != SPLATAD_OK) return rc;                                                          \
+        rasterize_to_points_bwd_kernel<D><<<blocks, bs, smem, (cudaStream_t)stream>>>(            \
+            C, n_isects, (const float2 *)means2d, conics, lidar_features, channels, opacities,    \
+            pix_vels, (const float2 *)depth_compensations, backgrounds,                           \
+            (const float4 *)raster_pts, image_width, image_height, tile_width, tile_height,       \
+            tile_grid_width, tile_grid_height, compute_alpha_sum_until_points,                    \
+            alpha_sum_threshold, tile_offsets, flatten_ids, depth_channel_idx, render_alphas,     \
+            last_ids, v_render_features, v_render_alphas, v_alpha_sum_until_points,               \
+            v_means2d_abs, v_means2d, v_conics, v_features, v_opacities, v_pix_vels,              \
+            v_depth_compensations);                                                               \
+    }
+    SPL_DISPATCH_CDIM(channels, CALL);
+#undef CALL
+    return check_launch("rasterize_to_points_bwd");
+}

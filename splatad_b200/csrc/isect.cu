@@ -1,0 +1,919 @@
+// Tile intersection: per-Gaussian tile rectangles, intersection counts, and the depth-ordered
+// per-tile Gaussian lists (isect_ids / flatten_ids / isect_offsets).
+//
+// What the reference does (gsplat/cuda/csrc/rasterization.cu:15-216 camera, 287-529 lidar,
+// 218-285 offsets): count tiles per Gaussian, cumsum, emit one 64-bit key
+// (sensor | tile | depth bits) per intersection in flatten-index order, then a stable LSD
+// radix sort of 12-byte pairs over 43-46 key bits, then a boundary scan for the offsets.
+//
+// What this file does instead, with bit-identical results: because a stable sort of the
+// emitted keys orders each tile's list by (depth bits, flatten index), the same lists are
+// obtained by
+//   1. a stable radix sort of the *visible Gaussians* by their 32 depth bits (4 passes over
+//      at most C*N 8-byte pairs - small, L2 resident),
+//   2. emitting (sensor*n_tiles + tile, flatten index) pairs in that depth order, and
+//   3. a stable radix split of those 8-byte pairs by the compact tile key only
+//      (ceil(bits/8) passes: 2 for every configuration up to 65536 sensor-tiles),
+// the last pass writing the 64-bit isect_ids and int32 flatten_ids directly. Offsets are a
+// binary search per tile.
+//
+// All kernels run on a fixed grid (a multiple of the 148 SMs) and read problem sizes from
+// device memory, so the whole sequence can be enqueued without a host round trip; the only
+// device->host traffic is the (n_isects, n_visible, status) triple.
+#include "common.cuh"
+
+namespace splatad {
+
+constexpr int kSortThreads = 256;
+constexpr int kSortWarps = kSortThreads / 32;
+constexpr int kItemsPerLane = 16;
+constexpr int kWarpItems = 32 * kItemsPerLane;           // 512
+constexpr int kTileItems = kSortWarps * kWarpItems;      // 4096
+constexpr int kSortGrid = 4 * kNumSMs;                   // 592 persistent blocks
+constexpr int kRadixBins = 256;
+static_assert(kSortThreads == kRadixBins, "one thread per radix bin");
+static_assert(kSortGrid <= 1024, "row scan and emit scan use one thread per sort block");
+
+// counters[] slots (int64 each)
+enum { CNT_NISECT = 0, CNT_NVIS = 1, CNT_STATUS = 2, CNT_SLOTS = 4 };
+enum { ST_OVERFLOW_CAPACITY = 1, ST_OVERFLOW_INT32 = 2 };
+
+// ---------------------------------------------------------------------------------------
+// Block-wide exclusive scan for any blockDim.x that is a multiple of 32 (<= 1024).
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t block_excl_scan(uint32_t v, uint32_t *warp_tot /*[33]*/,
+                                                    uint32_t &total) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t nwarps = blockDim.x >> 5;
+    uint32_t inc = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        uint32_t o = __shfl_up_sync(0xffffffffu, inc, off);
+        if (lane >= (uint32_t)off) inc += o;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        uint32_t w = (lane < nwarps) ? warp_tot[lane] : 0u;
+        uint32_t winc = w;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            uint32_t o = __shfl_up_sync(0xffffffffu, winc, off);
+            if (lane >= (uint32_t)off) winc += o;
+        }
+        warp_tot[lane] = winc - w;   // exclusive warp offsets
+        if (lane == 31) warp_tot[32] = winc;
+    }
+    __syncthreads();
+    const uint32_t res = warp_tot[warp] + inc - v;
+    total = warp_tot[32];
+    __syncthreads();
+    return res;
+}
+
+// ---------------------------------------------------------------------------------------
+// Tile rectangles
+// ---------------------------------------------------------------------------------------
+struct Rect { int32_t x0, x1, y0, y1; };   // x: [x0, x1), y: [y0, y1)
+
+struct CamGrid { uint32_t tile_size, tile_width, tile_height; };
+
+__device__ __forceinline__ uint32_t clamp_tile(float v, uint32_t hi) {
+    // float -> uint32 conversion that saturates negatives (and NaN) to 0, then min(hi)
+    if (!(v > 0.f)) return 0u;
+    if (v >= (float)hi) return hi;
+    return (uint32_t)v;
+}
+
+__device__ __forceinline__ Rect cam_rect(float2 mean, int2 radius, CamGrid g) {
+    const float ts = (float)g.tile_size;
+    const float ex = (float)radius.x / ts, ey = (float)radius.y / ts;
+    const float tx = mean.x / ts, ty = mean.y / ts;
+    Rect r;
+    r.x0 = (int32_t)clamp_tile(floorf(tx - ex), g.tile_width);
+    r.y0 = (int32_t)clamp_tile(floorf(ty - ey), g.tile_height);
+    r.x1 = (int32_t)clamp_tile(ceilf(tx + ex), g.tile_width);
+    r.y1 = (int32_t)clamp_tile(ceilf(ty + ey), g.tile_height);
+    return r;
+}
+
+struct LidarGrid {
+    const float *elev_boundaries;   // [n_tiles_elev + 1], global or shared
+    float tile_azim_res, min_azim;
+    uint32_t n_tiles_azim, n_tiles_elev;
+};
+
+__device__ __forceinline__ Rect lidar_rect(float2 mean, float2 radius, const LidarGrid &g) {
+    const float el_lo = mean.y - radius.y, el_hi = mean.y + radius.y;
+    const float azim = mean.x - g.min_azim;
+    const float az_lo = azim - radius.x, az_hi = azim + radius.x;
+    const float azim_max = (float)g.n_tiles_azim * g.tile_azim_res;
+    float t_lo, t_hi;
+    if (az_lo >= 0.f) t_lo = az_lo / g.tile_azim_res;
+    else t_lo = (fmodf(az_lo + 360.f, 360.f) - azim_max) / g.tile_azim_res;
+    if (az_hi <= 360.f) t_hi = az_hi / g.tile_azim_res;
+    else t_hi = (float)g.n_tiles_azim + fmodf(az_hi + 360.f, 360.f) / g.tile_azim_res;
+    Rect r;
+    r.x0 = (int32_t)floorf(t_lo);
+    r.x1 = (int32_t)ceilf(t_hi);
+    const int32_t ne = (int32_t)g.n_tiles_elev;
+    int32_t i = 0;
+    while (i <= ne && g.elev_boundaries[i] < el_lo) ++i;
+    r.y0 = max(i - 1, 0);
+    while (i <= ne && g.elev_boundaries[i] < el_hi) ++i;
+    r.y1 = min(i, ne);
+    return r;
+}
+
+__device__ __forceinline__ int32_t rect_count(const Rect &r) {
+    return (r.y1 - r.y0) * (r.x1 - r.x0);
+}
+
+constexpr int kMaxElevSmem = 1024;
+
+template <bool kLidar>
+struct GridArgs {
+    CamGrid cam;
+    LidarGrid lidar;
+    const void *radii;      // int2 (camera) or float2 (lidar)
+    const float2 *means2d;
+};
+
+template <bool kLidar>
+__device__ __forceinline__ bool elem_rect(const GridArgs<kLidar> &a, uint32_t idx, Rect &r) {
+    if (kLidar) {
+        const float2 rad = reinterpret_cast<const float2 *>(a.radii)[idx];
+        if (!(rad.x > 0.f)) return false;
+        r = lidar_rect(a.means2d[idx], rad, a.lidar);
+    } else {
+        const int2 rad = reinterpret_cast<const int2 *>(a.radii)[idx];
+        if (rad.x <= 0) return false;
+        r = cam_rect(a.means2d[idx], rad, a.cam);
+    }
+    return true;
+}
+
+// Copies the elevation boundaries to shared memory when they fit and repoints the grid.
+template <bool kLidar>
+__device__ __forceinline__ void stage_boundaries(GridArgs<kLidar> &a, float *sb) {
+    if (kLidar) {
+        const uint32_t nb = a.lidar.n_tiles_elev + 1;
+        if (nb <= kMaxElevSmem) {
+            for (uint32_t i = threadIdx.x; i < nb; i += blockDim.x) sb[i] = a.lidar.elev_boundaries[i];
+            __syncthreads();
+            a.lidar.elev_boundaries = sb;
+        }
+    }
+}
+
+// tiles_per_gauss[idx] for every (sensor, Gaussian) / packed row.
+template <bool kLidar>
+__global__ void __launch_bounds__(kThreads)
+isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ tiles_per_gauss) {
+    __shared__ float sb[kLidar ? kMaxElevSmem : 1];
+    stage_boundaries<kLidar>(a, sb);
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += gridDim.x * blockDim.x) {
+        Rect r;
+        int32_t cnt = 0;
+        if (elem_rect<kLidar>(a, idx, r)) cnt = rect_count(r);
+        tiles_per_gauss[idx] = cnt;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Radix sort passes (stable LSD, up to 8 bits per pass) on (uint32 key, uint32 value) pairs.
+// Each of the kSortGrid blocks owns a contiguous run of 4096-item tiles.
+//   upsweep:   per-block digit histogram            -> hist[digit][block]
+//   rowscan:   exclusive scan of each digit's row   -> hist (in place), digit_totals
+//   downsweep: stable rank + scatter (through shared memory so global writes are runs)
+// Source of a pass is either a pair buffer with a device-side count, or (kGen) the implicit
+// list idx = 0..total-1 with key = depth bits, value = idx, restricted to tiles_per_gauss>0.
+// ---------------------------------------------------------------------------------------
+struct PassSrc {
+    const uint32_t *keys;            // pair source
+    const uint32_t *vals;
+    const int64_t *n_ptr;            // device count (pair source)
+    const uint32_t *depth_bits;      // gen source
+    const int32_t *tiles_per_gauss;  // gen source
+    uint32_t total;                  // gen source length
+    uint32_t n_cap;                  // pair source: upper bound on the count (buffer size); 0 = none
+};
+
+template <bool kGen>
+__device__ __forceinline__ uint32_t src_count(const PassSrc &s) {
+    if (kGen) return s.total;
+    int64_t n = *s.n_ptr;
+    if (s.n_cap != 0 && n > (int64_t)s.n_cap) n = (int64_t)s.n_cap;
+    return (uint32_t)n;
+}
+
+__device__ __forceinline__ void block_range(uint32_t n, uint32_t &lo, uint32_t &hi) {
+    const uint32_t tiles = (n + kTileItems - 1) / kTileItems;
+    const uint32_t per = (tiles + gridDim.x - 1) / gridDim.x;
+    const uint64_t l = (uint64_t)blockIdx.x * per * kTileItems;
+    const uint64_t h = l + (uint64_t)per * kTileItems;
+    lo = (uint32_t)(l < n ? l : n);
+    hi = (uint32_t)(h < n ? h : n);
+}
+
+template <bool kGen>
+__global__ void __launch_bounds__(kSortThreads)
+radix_upsweep_kernel(PassSrc s, int shift, uint32_t mask, uint32_t *__restrict__ hist) {
+    __shared__ uint32_t wh[kSortWarps][kRadixBins];
+    for (uint32_t i = threadIdx.x; i < kSortWarps * kRadixBins; i += blockDim.x) (&wh[0][0])[i] = 0u;
+    __syncthreads();
+    const uint32_t n = src_count<kGen>(s);
+    uint32_t lo, hi;
+    block_range(n, lo, hi);
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint32_t base = lo; base < hi; base += kSortThreads) {
+        const uint32_t i = base + threadIdx.x;
+        bool valid = i < hi;
+        uint32_t key = 0;
+        if (valid) {
+            if (kGen) {
+                valid = s.tiles_per_gauss[i] > 0;
+                if (valid) key = s.depth_bits[i];
+            } else {
+                key = s.keys[i];
+            }
+        }
+        const uint32_t digit = valid ? ((key >> shift) & mask) : kRadixBins;
+        const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+        if (valid && lane == (uint32_t)(__ffs(peers) - 1)) atomicAdd(&wh[warp][digit], __popc(peers));
+    }
+    __syncthreads();
+    for (uint32_t d = threadIdx.x; d < kRadixBins; d += blockDim.x) {
+        uint32_t sum = 0;
+#pragma unroll
+        for (int w = 0; w < kSortWarps; ++w) sum += wh[w][d];
+        hist[(size_t)d * gridDim.x + blockIdx.x] = sum;
+    }
+}
+
+// One block per digit; blockDim.x >= grid size of the sort kernels (multiple of 32).
+__global__ void radix_rowscan_kernel(uint32_t *__restrict__ hist, uint32_t nblocks,
+                                     uint32_t *__restrict__ digit_totals) {
+    __shared__ uint32_t wt[33];
+    const uint32_t d = blockIdx.x;
+    const uint32_t b = threadIdx.x;
+    uint32_t v = (b < nblocks) ? hist[(size_t)d * nblocks + b] : 0u;
+    uint32_t total;
+    const uint32_t ex = block_excl_scan(v, wt, total);
+    if (b < nblocks) hist[(size_t)d * nblocks + b] = ex;
+    if (b == 0) digit_totals[d] = total;
+}
+
+struct FinalOut {
+    int64_t *isect_ids;          // [capacity]
+    int32_t *flatten_ids;        // [capacity]
+    const uint32_t *depth_bits;  // [total elems]
+    uint32_t n_tiles;            // tiles per sensor
+    uint32_t tile_n_bits;
+    int64_t capacity;
+};
+
+template <bool kGen, bool kFinal>
+__global__ void __launch_bounds__(kSortThreads)
+radix_downsweep_kernel(PassSrc s, int shift, uint32_t mask, const uint32_t *__restrict__ hist,
+                       const uint32_t *__restrict__ digit_totals, uint32_t *__restrict__ keys_out,
+                       uint32_t *__restrict__ vals_out, FinalOut fin,
+                       int64_t *__restrict__ n_out /* optional: total valid count */) {
+    __shared__ uint32_t wh[kSortWarps][kRadixBins];
+    __shared__ uint32_t digit_base[kRadixBins];
+    __shared__ uint32_t tile_excl[kRadixBins];
+    __shared__ uint32_t tile_cnt[kRadixBins];
+    __shared__ uint32_t wt[33];
+    __shared__ uint32_t st_keys[kTileItems];
+    __shared__ uint32_t st_vals[kTileItems];
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    {
+        uint32_t tot;
+        const uint32_t dt = digit_totals[tid];
+        const uint32_t ex = block_excl_scan(dt, wt, tot);
+        digit_base[tid] = ex + hist[(size_t)tid * gridDim.x + blockIdx.x];
+        if (n_out != nullptr && blockIdx.x == 0 && tid == 0) *n_out = (int64_t)tot;
+    }
+    __syncthreads();
+
+    const uint32_t n = src_count<kGen>(s);
+    uint32_t lo, hi;
+    block_range(n, lo, hi);
+
+    for (uint32_t tile_lo = lo; tile_lo < hi; tile_lo += kTileItems) {
+        for (uint32_t i = tid; i < kSortWarps * kRadixBins; i += kSortThreads) (&wh[0][0])[i] = 0u;
+        __syncthreads();
+
+        uint32_t keys[kItemsPerLane], vals[kItemsPerLane];
+        uint16_t ranks[kItemsPerLane];
+        uint32_t validmask = 0;
+        const uint32_t wbase = tile_lo + warp * kWarpItems + lane;
+#pragma unroll
+        for (int r = 0; r < kItemsPerLane; ++r) {
+            const uint32_t i = wbase + r * 32;
+            bool valid = i < hi;
+            uint32_t key = 0, val = 0;
+            if (valid) {
+                if (kGen) {
+                    valid = s.tiles_per_gauss[i] > 0;
+                    if (valid) { key = s.depth_bits[i]; val = i; }
+                } else {
+                    key = s.keys[i];
+                    val = s.vals[i];
+                }
+            }
+            keys[r] = key; vals[r] = val;
+            if (valid) validmask |= (1u << r);
+        }
+#pragma unroll
+        for (int r = 0; r < kItemsPerLane; ++r) {
+            const bool valid = (validmask >> r) & 1u;
+            const uint32_t digit = valid ? ((keys[r] >> shift) & mask) : kRadixBins;
+            const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+            const uint32_t leader = (uint32_t)(__ffs(peers) - 1);
+            uint32_t old = 0;
+            if (valid && lane == leader) {
+                old = wh[warp][digit];
+                wh[warp][digit] = old + __popc(peers);
+            }
+            old = __shfl_sync(0xffffffffu, old, leader);
+            ranks[r] = (uint16_t)(old + __popc(peers & ((1u << lane) - 1u)));
+            __syncwarp();
+        }
+        __syncthreads();
+        // per digit: exclusive offsets of the warps, tile count, then exclusive scan over digits
+        {
+            uint32_t run = 0;
+#pragma unroll
+            for (int w = 0; w < kSortWarps; ++w) {
+                const uint32_t c = wh[w][tid];
+                wh[w][tid] = run;
+                run += c;
+            }
+            tile_cnt[tid] = run;
+            uint32_t tot;
+            tile_excl[tid] = block_excl_scan(run, wt, tot);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < kItemsPerLane; ++r) {
+            if ((validmask >> r) & 1u) {
+                const uint32_t digit = (keys[r] >> shift) & mask;
+                const uint32_t pos = tile_excl[digit] + wh[warp][digit] + ranks[r];
+                st_keys[pos] = keys[r];
+                st_vals[pos] = vals[r];
+            }
+        }
+        __syncthreads();
+        const uint32_t tile_n = tile_excl[kRadixBins - 1] + tile_cnt[kRadixBins - 1];
+        for (uint32_t j = tid; j < tile_n; j += kSortThreads) {
+            const uint32_t k = st_keys[j];
+            const uint32_t v = st_vals[j];
+            const uint32_t digit = (k >> shift) & mask;
+            const uint32_t gpos = digit_base[digit] + (j - tile_excl[digit]);
+            if (kFinal) {
+                if ((int64_t)gpos < fin.capacity) {
+                    const uint32_t cid = k / fin.n_tiles;
+                    const uint32_t tile = k - cid * fin.n_tiles;
+                    const int64_t id = ((int64_t)cid << (32 + fin.tile_n_bits)) |
+                                       ((int64_t)tile << 32) | (int64_t)fin.depth_bits[v];
+                    fin.isect_ids[gpos] = id;
+                    fin.flatten_ids[gpos] = (int32_t)v;
+                }
+            } else {
+                keys_out[gpos] = k;
+                vals_out[gpos] = v;
+            }
+        }
+        __syncthreads();
+        digit_base[tid] += tile_cnt[tid];
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Emission of (compact tile key, flatten index) pairs in depth order.
+// ---------------------------------------------------------------------------------------
+struct EmitArgs {
+    const uint32_t *order;           // [n_vis] flatten indices in depth order, or nullptr = identity
+    const int64_t *n_order_ptr;      // device count of `order` (ignored for identity)
+    uint32_t total;                  // identity length
+    const int32_t *tiles_per_gauss;  // [total]
+    const int64_t *camera_ids;       // packed: sensor of each row, else nullptr
+    uint32_t N;                      // Gaussians per sensor ([C, N] layout)
+    uint32_t n_tiles;                // tiles per sensor
+    uint32_t tile_n_bits;
+    const uint32_t *depth_bits;
+    int64_t capacity;
+};
+
+__device__ __forceinline__ void emit_range(const EmitArgs &e, uint32_t &lo, uint32_t &hi) {
+    const uint32_t n = e.order ? (uint32_t)(*e.n_order_ptr) : e.total;
+    const uint32_t chunks = (n + kThreads - 1) / kThreads;
+    const uint32_t per = (chunks + gridDim.x - 1) / gridDim.x;
+    const uint64_t l = (uint64_t)blockIdx.x * per * kThreads;
+    const uint64_t h = l + (uint64_t)per * kThreads;
+    lo = (uint32_t)(l < n ? l : n);
+    hi = (uint32_t)(h < n ? h : n);
+}
+
+__global__ void __launch_bounds__(kThreads)
+emit_blocksum_kernel(EmitArgs e, unsigned long long *__restrict__ block_sums) {
+    __shared__ unsigned long long ws[kThreads / 32];
+    uint32_t lo, hi;
+    emit_range(e, lo, hi);
+    unsigned long long sum = 0;
+    for (uint32_t p = lo + threadIdx.x; p < hi; p += kThreads) {
+        const uint32_t idx = e.order ? e.order[p] : p;
+        const int32_t c = e.tiles_per_gauss[idx];
+        sum += (unsigned long long)(c > 0 ? c : 0);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long t = 0;
+        for (int w = 0; w < kThreads / 32; ++w) t += ws[w];
+        block_sums[blockIdx.x] = t;
+    }
+}
+
+// Single block (1024 threads): exclusive scan of the per-block sums; writes n_isects and the
+// status word.
+__global__ void __launch_bounds__(1024)
+emit_scan_kernel(const unsigned long long *__restrict__ block_sums, uint32_t nblocks,
+                 unsigned long long *__restrict__ block_offs, int64_t *__restrict__ counters) {
+    __shared__ unsigned long long part[1024];
+    const uint32_t t = threadIdx.x;
+    const unsigned long long v = (t < nblocks) ? block_sums[t] : 0ull;
+    part[t] = v;
+    __syncthreads();
+    for (uint32_t off = 1; off < 1024; off <<= 1) {
+        const unsigned long long o = (t >= off) ? part[t - off] : 0ull;
+        __syncthreads();
+        part[t] += o;
+        __syncthreads();
+    }
+    if (t < nblocks) block_offs[t] = part[t] - v;
+    if (t == 1023) {
+        const unsigned long long run = part[1023];
+        counters[CNT_NISECT] = (int64_t)run;
+        if (run > 0x7fffffffull) counters[CNT_STATUS] |= ST_OVERFLOW_INT32;
+    }
+}
+
+template <bool kLidar, bool kDirect64>
+__global__ void __launch_bounds__(kThreads)
+emit_kernel(GridArgs<kLidar> a, EmitArgs e, const unsigned long long *__restrict__ block_offs,
+            uint32_t *__restrict__ keys_out, uint32_t *__restrict__ vals_out,
+            int64_t *__restrict__ ids64_out, int32_t *__restrict__ flat_out,
+            int64_t *__restrict__ counters) {
+    __shared__ float sb[kLidar ? kMaxElevSmem : 1];
+    __shared__ uint32_t loc[kThreads + 1];
+    __shared__ Rect rects[kThreads];
+    __shared__ uint32_t sidx[kThreads];
+    __shared__ uint32_t scid[kThreads];
+    __shared__ uint32_t wt[33];
+    stage_boundaries<kLidar>(a, sb);
+    uint32_t lo, hi;
+    emit_range(e, lo, hi);
+    unsigned long long running = block_offs[blockIdx.x];
+    bool overflow = false;
+    for (uint32_t base = lo; base < hi; base += kThreads) {
+        const uint32_t p = base + threadIdx.x;
+        uint32_t cnt = 0;
+        if (p < hi) {
+            const uint32_t idx = e.order ? e.order[p] : p;
+            Rect r;
+            if (elem_rect<kLidar>(a, idx, r)) {
+                cnt = (uint32_t)max(rect_count(r), 0);
+                rects[threadIdx.x] = r;
+            }
+            sidx[threadIdx.x] = idx;
+            scid[threadIdx.x] = e.camera_ids ? (uint32_t)e.camera_ids[idx] : idx / e.N;
+        }
+        uint32_t chunk_total;
+        const uint32_t ex = block_excl_scan(cnt, wt, chunk_total);
+        loc[threadIdx.x] = ex;
+        if (threadIdx.x == 0) loc[kThreads] = chunk_total;
+        __syncthreads();
+        for (uint32_t j = threadIdx.x; j < chunk_total; j += kThreads) {
+            // last s with loc[s] <= j
+            uint32_t l = 0, h = kThreads;
+            while (h - l > 1) {
+                const uint32_t m = (l + h) >> 1;
+                if (loc[m] <= j) l = m; else h = m;
+            }
+            const Rect r = rects[l];
+            const uint32_t k = j - loc[l];
+            const uint32_t w = (uint32_t)(r.x1 - r.x0);
+            const uint32_t dy = k / w;
+            const uint32_t dx = k - dy * w;
+            const int32_t ty = r.y0 + (int32_t)dy;
+            int32_t tx = r.x0 + (int32_t)dx;
+            uint32_t tile;
+            if (kLidar) {
+                const int32_t na = (int32_t)a.lidar.n_tiles_azim;
+                tx %= na;
+                if (tx < 0) tx += na;
+                tile = (uint32_t)ty * a.lidar.n_tiles_azim + (uint32_t)tx;
+            } else {
+                tile = (uint32_t)ty * a.cam.tile_width + (uint32_t)tx;
+            }
+            const unsigned long long q = running + j;
+            if ((int64_t)q >= e.capacity) { overflow = true; continue; }
+            const uint32_t idx = sidx[l];
+            if (kDirect64) {
+                ids64_out[q] = ((int64_t)scid[l] << (32 + e.tile_n_bits)) | ((int64_t)tile << 32) |
+                               (int64_t)e.depth_bits[idx];
+                flat_out[q] = (int32_t)idx;
+            } else {
+                keys_out[q] = scid[l] * e.n_tiles + tile;
+                vals_out[q] = idx;
+            }
+        }
+        running += chunk_total;
+        __syncthreads();
+    }
+    if (overflow) atomicOr((unsigned long long *)&counters[CNT_STATUS], (unsigned long long)ST_OVERFLOW_CAPACITY);
+}
+
+// ---------------------------------------------------------------------------------------
+// Offsets: offsets[c, tile] = first position whose (sensor, tile) >= (c, tile).
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+offset_encode_kernel(const int64_t *__restrict__ isect_ids, const int64_t *n_ptr, int64_t n_imm,
+                     uint32_t C, uint32_t n_tiles, uint32_t tile_n_bits,
+                     int32_t *__restrict__ offsets) {
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= C * n_tiles) return;
+    const int64_t n = n_ptr ? *n_ptr : n_imm;
+    const int64_t cid = t / n_tiles, tile = t - (uint32_t)cid * n_tiles;
+    const int64_t target = (cid << tile_n_bits) | tile;
+    int64_t l = 0, h = n;   // first position with (id >> 32) >= target
+    while (l < h) {
+        const int64_t m = (l + h) >> 1;
+        if ((isect_ids[m] >> 32) < target) l = m + 1; else h = m;
+    }
+    offsets[t] = (int32_t)l;
+}
+
+__global__ void init_counters_kernel(int64_t *counters) {
+    if (threadIdx.x < CNT_SLOTS) counters[threadIdx.x] = 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Host orchestration
+// ---------------------------------------------------------------------------------------
+static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct PlanWs {
+    int64_t *counters;
+    uint32_t *hist;
+    uint32_t *digit_totals;
+    unsigned long long *block_sums;
+    unsigned long long *block_offs;
+    uint32_t *keyA, *valA, *keyB, *valB;
+    size_t bytes;
+};
+
+static PlanWs carve_plan(void *ws, uint64_t total) {
+    PlanWs p;
+    char *c = (char *)ws;
+    size_t off = 0;
+    auto take = [&](size_t b) { char *r = c ? c + off : nullptr; off += align256(b); return r; };
+    p.counters = (int64_t *)take(sizeof(int64_t) * CNT_SLOTS);
+    p.hist = (uint32_t *)take(sizeof(uint32_t) * kRadixBins * kSortGrid);
+    p.digit_totals = (uint32_t *)take(sizeof(uint32_t) * kRadixBins);
+    p.block_sums = (unsigned long long *)take(sizeof(unsigned long long) * kSortGrid);
+    p.block_offs = (unsigned long long *)take(sizeof(unsigned long long) * kSortGrid);
+    p.keyA = (uint32_t *)take(sizeof(uint32_t) * total);
+    p.valA = (uint32_t *)take(sizeof(uint32_t) * total);
+    p.keyB = (uint32_t *)take(sizeof(uint32_t) * total);
+    p.valB = (uint32_t *)take(sizeof(uint32_t) * total);
+    p.bytes = off;
+    return p;
+}
+
+struct FillWs {
+    uint32_t *keyA, *valA, *keyB, *valB;
+    size_t bytes;
+};
+
+static FillWs carve_fill(void *ws, uint64_t cap) {
+    FillWs f;
+    char *c = (char *)ws;
+    size_t off = 0;
+    auto take = [&](size_t b) { char *r = c ? c + off : nullptr; off += align256(b); return r; };
+    f.keyA = (uint32_t *)take(sizeof(uint32_t) * cap);
+    f.valA = (uint32_t *)take(sizeof(uint32_t) * cap);
+    f.keyB = (uint32_t *)take(sizeof(uint32_t) * cap);
+    f.valB = (uint32_t *)take(sizeof(uint32_t) * cap);
+    f.bytes = off;
+    return f;
+}
+
+static uint32_t bit_length(uint64_t v) {
+    uint32_t b = 0;
+    while (v) { ++b; v >>= 1; }
+    return b;
+}
+
+struct IsectGeom {
+    bool lidar;
+    GridArgs<false> cam;
+    GridArgs<true> lid;
+    uint32_t C, N, total, n_tiles, tile_n_bits;
+    const int64_t *camera_ids;
+    const uint32_t *depth_bits;
+};
+
+// plan: counts, depth order of visible Gaussians, n_isects.
+static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, void *workspace,
+                      size_t workspace_bytes, int64_t *host_counts, cudaStream_t st) {
+    PlanWs p = carve_plan(workspace, g.total);
+    SPL_REQUIRE(workspace != nullptr && workspace_bytes >= p.bytes, SPLATAD_ERR_WORKSPACE,
+                "isect plan: workspace too small (%zu < %zu)", workspace_bytes, p.bytes);
+    const uint32_t cam_n_bits = bit_length(g.C);   // floor(log2(C)) + 1
+    SPL_REQUIRE(g.tile_n_bits + cam_n_bits <= 32, SPLATAD_ERR_KEY_BITS,
+                "isect: tile bits (%u) + sensor bits (%u) exceed 32", g.tile_n_bits, cam_n_bits);
+    SPL_REQUIRE((uint64_t)g.C * g.n_tiles <= 0xffffffffull, SPLATAD_ERR_KEY_BITS,
+                "isect: sensors * tiles does not fit 32 bits");
+    init_counters_kernel<<<1, 32, 0, st>>>(p.counters);
+    const uint32_t cgrid = min(div_up(g.total, kThreads), (uint32_t)(8 * kNumSMs));
+    if (g.lidar)
+        isect_count_kernel<true><<<cgrid, kThreads, 0, st>>>(g.lid, g.total, tiles_per_gauss);
+    else
+        isect_count_kernel<false><<<cgrid, kThreads, 0, st>>>(g.cam, g.total, tiles_per_gauss);
+
+    EmitArgs e{};
+    e.total = g.total;
+    e.tiles_per_gauss = tiles_per_gauss;
+    if (sort) {
+        // stable sort of the visible (count > 0) elements by depth bits: 4 passes of 8 bits
+        uint32_t *ka = p.keyA, *va = p.valA, *kb = p.keyB, *vb = p.valB;
+        FinalOut nofin{};
+        for (int pass = 0; pass < 4; ++pass) {
+            PassSrc s{};
+            if (pass == 0) {
+                s.depth_bits = g.depth_bits;
+                s.tiles_per_gauss = tiles_per_gauss;
+                s.total = g.total;
+                radix_upsweep_kernel<true><<<kSortGrid, kSortThreads, 0, st>>>(s, 0, 0xffu, p.hist);
+                radix_rowscan_kernel<<<kRadixBins, ((kSortGrid + 31) / 32) * 32, 0, st>>>(
+                    p.hist, kSortGrid, p.digit_totals);
+                radix_downsweep_kernel<true, false><<<kSortGrid, kSortThreads, 0, st>>>(
+                    s, 0, 0xffu, p.hist, p.digit_totals, ka, va, nofin, p.counters + CNT_NVIS);
+            } else {
+                s.keys = ka; s.vals = va; s.n_ptr = p.counters + CNT_NVIS;
+                radix_upsweep_kernel<false><<<kSortGrid, kSortThreads, 0, st>>>(s, 8 * pass, 0xffu, p.hist);
+                radix_rowscan_kernel<<<kRadixBins, ((kSortGrid + 31) / 32) * 32, 0, st>>>(
+                    p.hist, kSortGrid, p.digit_totals);
+                radix_downsweep_kernel<false, false><<<kSortGrid, kSortThreads, 0, st>>>(
+                    s, 8 * pass, 0xffu, p.hist, p.digit_totals, kb, vb, nofin, nullptr);
+                uint32_t *t;
+                t = ka; ka = kb; kb = t;
+                t = va; va = vb; vb = t;
+            }
+        }
+        // 4 passes: A -> (pass0 writes A) ... after pass 3 the result sits in `va`
+        // pass0: gen->A ; pass1: A->B ; pass2: B->A ; pass3: A->B  => sorted order in valB
+        e.order = va;
+        e.n_order_ptr = p.counters + CNT_NVIS;
+    }
+    emit_blocksum_kernel<<<kSortGrid, kThreads, 0, st>>>(e, p.block_sums);
+    emit_scan_kernel<<<1, 1024, 0, st>>>(p.block_sums, kSortGrid, p.block_offs, p.counters);
+    if (host_counts != nullptr)
+        cudaMemcpyAsync(host_counts, p.counters, sizeof(int64_t) * CNT_SLOTS, cudaMemcpyDeviceToHost, st);
+    return check_launch("isect plan");
+}
+
+static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int sort,
+                      void *plan_workspace, void *fill_workspace, size_t fill_workspace_bytes,
+                      int64_t capacity, int64_t *isect_ids, int32_t *flatten_ids,
+                      int64_t *host_counts, cudaStream_t st) {
+    PlanWs p = carve_plan(plan_workspace, g.total);
+    SPL_REQUIRE(plan_workspace != nullptr, SPLATAD_ERR_WORKSPACE, "isect fill: null plan workspace");
+    if (capacity <= 0) return SPLATAD_OK;
+    SPL_REQUIRE(isect_ids && flatten_ids, SPLATAD_ERR_BAD_ARG, "isect fill: null output");
+
+    EmitArgs e{};
+    e.total = g.total;
+    e.tiles_per_gauss = tiles_per_gauss;
+    e.camera_ids = g.camera_ids;
+    e.N = g.N;
+    e.n_tiles = g.n_tiles;
+    e.tile_n_bits = g.tile_n_bits;
+    e.depth_bits = g.depth_bits;
+    e.capacity = capacity;
+
+    if (!sort) {
+        if (g.lidar)
+            emit_kernel<true, true><<<kSortGrid, kThreads, 0, st>>>(
+                g.lid, e, p.block_offs, nullptr, nullptr, isect_ids, flatten_ids, p.counters);
+        else
+            emit_kernel<false, true><<<kSortGrid, kThreads, 0, st>>>(
+                g.cam, e, p.block_offs, nullptr, nullptr, isect_ids, flatten_ids, p.counters);
+    } else {
+        FillWs f = carve_fill(fill_workspace, (uint64_t)capacity);
+        SPL_REQUIRE(fill_workspace != nullptr && fill_workspace_bytes >= f.bytes,
+                    SPLATAD_ERR_WORKSPACE, "isect fill: workspace too small (%zu < %zu)",
+                    fill_workspace_bytes, f.bytes);
+        // depth order left by the plan in valB (see isect_plan)
+        e.order = p.valB;
+        e.n_order_ptr = p.counters + CNT_NVIS;
+        if (g.lidar)
+            emit_kernel<true, false><<<kSortGrid, kThreads, 0, st>>>(
+                g.lid, e, p.block_offs, f.keyA, f.valA, nullptr, nullptr, p.counters);
+        else
+            emit_kernel<false, false><<<kSortGrid, kThreads, 0, st>>>(
+                g.cam, e, p.block_offs, f.keyA, f.valA, nullptr, nullptr, p.counters);
+
+        const uint64_t span = (uint64_t)g.C * g.n_tiles;
+        const uint32_t key_bits = max(1u, bit_length(span - 1));
+        const uint32_t npass = (key_bits + 7) / 8;
+        const uint32_t bits_per = (key_bits + npass - 1) / npass;
+        FinalOut fin{};
+        fin.isect_ids = isect_ids;
+        fin.flatten_ids = flatten_ids;
+        fin.depth_bits = g.depth_bits;
+        fin.n_tiles = g.n_tiles;
+        fin.tile_n_bits = g.tile_n_bits;
+        fin.capacity = capacity;
+        uint32_t *ka = f.keyA, *va = f.valA, *kb = f.keyB, *vb = f.valB;
+        for (uint32_t pass = 0; pass < npass; ++pass) {
+            PassSrc s{};
+            s.keys = ka; s.vals = va; s.n_ptr = p.counters + CNT_NISECT;
+            s.n_cap = (uint32_t)(capacity < 0x7fffffffll ? capacity : 0x7fffffffll);
+            const int shift = (int)(pass * bits_per);
+            const uint32_t mask = (1u << bits_per) - 1u;
+            radix_upsweep_kernel<false><<<kSortGrid, kSortThreads, 0, st>>>(s, shift, mask, p.hist);
+            radix_rowscan_kernel<<<kRadixBins, ((kSortGrid + 31) / 32) * 32, 0, st>>>(
+                p.hist, kSortGrid, p.digit_totals);
+            if (pass + 1 == npass) {
+                radix_downsweep_kernel<false, true><<<kSortGrid, kSortThreads, 0, st>>>(
+                    s, shift, mask, p.hist, p.digit_totals, nullptr, nullptr, fin, nullptr);
+            } else {
+                FinalOut nofin{};
+                radix_downsweep_kernel<false, false><<<kSortGrid, kSortThreads, 0, st>>>(
+                    s, shift, mask, p.hist, p.digit_totals, kb, vb, nofin, nullptr);
+                uint32_t *t;
+                t = ka; ka = kb; kb = t;
+                t = va; va = vb; vb = t;
+            }
+        }
+    }
+    if (host_counts != nullptr)
+        cudaMemcpyAsync(host_counts, p.counters, sizeof(int64_t) * CNT_SLOTS, cudaMemcpyDeviceToHost, st);
+    return check_launch("isect fill");
+}
+
+} // namespace splatad
+
+using namespace splatad;
+
+// =======================================================================================
+// C-ABI
+// =======================================================================================
+extern "C" size_t splatad_isect_plan_workspace_bytes(uint64_t total_elems) {
+    return carve_plan(nullptr, total_elems).bytes;
+}
+
+extern "C" size_t splatad_isect_fill_workspace_bytes(uint64_t capacity) {
+    return carve_fill(nullptr, capacity).bytes;
+}
+
+static int make_cam_geom(IsectGeom &g, uint32_t C, uint32_t N, uint64_t total,
+                         const float *means2d, const int32_t *radii, const float *depths,
+                         const int64_t *camera_ids, uint32_t tile_size, uint32_t tile_width,
+                         uint32_t tile_height) {
+    SPL_REQUIRE(means2d && radii && depths, SPLATAD_ERR_BAD_ARG, "isect_tiles: null input");
+    SPL_REQUIRE(C > 0 && tile_size > 0 && tile_width > 0 && tile_height > 0, SPLATAD_ERR_BAD_ARG,
+                "isect_tiles: bad geometry");
+    SPL_REQUIRE(total <= 0x7fffffffull, SPLATAD_ERR_BAD_ARG, "isect_tiles: too many elements");
+    g = IsectGeom{};
+    g.lidar = false;
+    g.cam.cam = CamGrid{tile_size, tile_width, tile_height};
+    g.cam.radii = radii;
+    g.cam.means2d = (const float2 *)means2d;
+    g.C = C; g.N = N ? N : 1; g.total = (uint32_t)total;
+    g.n_tiles = tile_width * tile_height;
+    g.tile_n_bits = bit_length(g.n_tiles);
+    g.camera_ids = camera_ids;
+    g.depth_bits = (const uint32_t *)depths;
+    return SPLATAD_OK;
+}
+
+static int make_lidar_geom(IsectGeom &g, uint32_t C, uint32_t N, uint64_t total,
+                           const float *means2d, const float *radii, const float *depths,
+                           const int64_t *camera_ids, const float *elev_boundaries,
+                           uint32_t n_boundaries, float tile_azim_resolution, float min_azim) {
+    SPL_REQUIRE(means2d && radii && depths && elev_boundaries, SPLATAD_ERR_BAD_ARG,
+                "isect_lidar_tiles: null input");
+    SPL_REQUIRE(C > 0 && n_boundaries >= 2 && tile_azim_resolution > 0.f, SPLATAD_ERR_BAD_ARG,
+                "isect_lidar_tiles: bad geometry");
+    SPL_REQUIRE(total <= 0x7fffffffull, SPLATAD_ERR_BAD_ARG, "isect_lidar_tiles: too many elements");
+    g = IsectGeom{};
+    g.lidar = true;
+    g.lid.lidar.elev_boundaries = elev_boundaries;
+    g.lid.lidar.tile_azim_res = tile_azim_resolution;
+    g.lid.lidar.min_azim = min_azim;
+    g.lid.lidar.n_tiles_azim = (uint32_t)ceilf(360.f / tile_azim_resolution);
+    g.lid.lidar.n_tiles_elev = n_boundaries - 1;
+    g.lid.radii = radii;
+    g.lid.means2d = (const float2 *)means2d;
+    g.C = C; g.N = N ? N : 1; g.total = (uint32_t)total;
+    g.n_tiles = g.lid.lidar.n_tiles_azim * g.lid.lidar.n_tiles_elev;
+    g.tile_n_bits = bit_length(g.n_tiles);
+    g.camera_ids = camera_ids;
+    g.depth_bits = (const uint32_t *)depths;
+    return SPLATAD_OK;
+}
+
+extern "C" int splatad_isect_tiles_plan(
+    uint32_t C, uint32_t N, uint64_t total_elems, const float *means2d, const int32_t *radii,
+    const float *depths, const int64_t *camera_ids, uint32_t tile_size, uint32_t tile_width,
+    uint32_t tile_height, int32_t sort, int32_t *tiles_per_gauss, void *workspace,
+    size_t workspace_bytes, int64_t *host_counts, void *stream) {
+    if (total_elems == 0) {
+        if (host_counts) for (int i = 0; i < CNT_SLOTS; ++i) host_counts[i] = 0;
+        return SPLATAD_OK;
+    }
+    IsectGeom g;
+    int rc = make_cam_geom(g, C, N, total_elems, means2d, radii, depths, camera_ids, tile_size,
+                           tile_width, tile_height);
+    if (rc != SPLATAD_OK) return rc;
+    SPL_REQUIRE(tiles_per_gauss, SPLATAD_ERR_BAD_ARG, "isect_tiles_plan: null tiles_per_gauss");
+    return isect_plan(g, tiles_per_gauss, sort, workspace, workspace_bytes, host_counts,
+                      (cudaStream_t)stream);
+}
+
+extern "C" int splatad_isect_tiles_fill(
+    uint32_t C, uint32_t N, uint64_t total_elems, const float *means2d, const int32_t *radii,
+    const float *depths, const int64_t *camera_ids, uint32_t tile_size, uint32_t tile_width,
+    uint32_t tile_height, int32_t sort, const int32_t *tiles_per_gauss, void *plan_workspace,
+    void *fill_workspace, size_t fill_workspace_bytes, int64_t capacity, int64_t *isect_ids,
+    int32_t *flatten_ids, int64_t *host_counts, void *stream) {
+    if (total_elems == 0 || capacity <= 0) return SPLATAD_OK;
+    IsectGeom g;
+    int rc = make_cam_geom(g, C, N, total_elems, means2d, radii, depths, camera_ids, tile_size,
+                           tile_width, tile_height);
+    if (rc != SPLATAD_OK) return rc;
+    return isect_fill(g, tiles_per_gauss, sort, plan_workspace, fill_workspace,
+                      fill_workspace_bytes, capacity, isect_ids, flatten_ids, host_counts,
+                      (cudaStream_t)stream);
+}
+
+extern "C" int splatad_isect_lidar_tiles_plan(
+    uint32_t C, uint32_t N, uint64_t total_elems, const float *means2d, const float *radii,
+    const float *depths, const int64_t *camera_ids, const float *elev_boundaries,
+    uint32_t n_boundaries, float tile_azim_resolution, float min_azim, int32_t sort,
+    int32_t *tiles_per_gauss, void *workspace, size_t workspace_bytes, int64_t *host_counts,
+    void *stream) {
+    if (total_elems == 0) {
+        if (host_counts) for (int i = 0; i < CNT_SLOTS; ++i) host_counts[i] = 0;
+        return SPLATAD_OK;
+    }
+    IsectGeom g;
+    int rc = make_lidar_geom(g, C, N, total_elems, means2d, radii, depths, camera_ids,
+                             elev_boundaries, n_boundaries, tile_azim_resolution, min_azim);
+    if (rc != SPLATAD_OK) return rc;
+    SPL_REQUIRE(tiles_per_gauss, SPLATAD_ERR_BAD_ARG, "isect_lidar_tiles_plan: null tiles_per_gauss");
+    return isect_plan(g, tiles_per_gauss, sort, workspace, workspace_bytes, host_counts,
+                      (cudaStream_t)stream);
+}
+
+extern "C" int splatad_isect_lidar_tiles_fill(
+    uint32_t C, uint32_t N, uint64_t total_elems, const float *means2d, const float *radii,
+    const float *depths, const int64_t *camera_ids, const float *elev_boundaries,
+    uint32_t n_boundaries, float tile_azim_resolution, float min_azim, int32_t sort,
+    const int32_t *tiles_per_gauss, void *plan_workspace, void *fill_workspace,
+    size_t fill_workspace_bytes, int64_t capacity, int64_t *isect_ids, int32_t *flatten_ids,
+    int64_t *host_counts, void *stream) {
+    if (total_elems == 0 || capacity <= 0) return SPLATAD_OK;
+    IsectGeom g;
+    int rc = make_lidar_geom(g, C, N, total_elems, means2d, radii, depths, camera_ids,
+                             elev_boundaries, n_boundaries, tile_azim_resolution, min_azim);
+    if (rc != SPLATAD_OK) return rc;
+    return isect_fill(g, tiles_per_gauss, sort, plan_workspace, fill_workspace,
+                      fill_workspace_bytes, capacity, isect_ids, flatten_ids, host_counts,
+                      (cudaStream_t)stream);
+}
+
+extern "C" int splatad_isect_offset_encode(const int64_t *isect_ids, int64_t n_isects, uint32_t C,
+                                           uint32_t tile_width, uint32_t tile_height,
+                                           int32_t *offsets, void *stream) {
+    SPL_REQUIRE(offsets, SPLATAD_ERR_BAD_ARG, "isect_offset_encode: null output");
+    const uint64_t n_tiles = (uint64_t)tile_width * tile_height;
+    SPL_REQUIRE(C > 0 && n_tiles > 0 && (uint64_t)C * n_tiles <= 0x7fffffffull, SPLATAD_ERR_BAD_ARG,
+                "isect_offset_encode: bad geometry");
+    SPL_REQUIRE(n_isects == 0 || isect_ids, SPLATAD_ERR_BAD_ARG, "isect_offset_encode: null input");
+    const uint32_t tile_n_bits = bit_length(n_tiles);
+    const uint32_t total = (uint32_t)(C * n_tiles);
+    offset_encode_kernel<<<div_up(total, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+        isect_ids, nullptr, n_isects, C, (uint32_t)n_tiles, tile_n_bits, offsets);
+    return check_launch("isect_offset_encode");
+}

@@ -1,0 +1,945 @@
+// Projection of 3-D Gaussians to a pinhole camera image or a spherical lidar range image,
+// both with rolling-shutter velocities, forward and backward.
+//
+// Layout and parallelisation (B200): one thread per Gaussian, looping over the C sensors of
+// the call, so the Gaussian's parameters are read from HBM once for all sensors and the
+// parameter gradients of the backward pass are accumulated in registers and written with
+// plain stores (no atomics for means / quats / scales / covars in the [C, N] layout). The
+// 3-wide AoS arrays (means, scales, velocities, conics, lidar velocities) move through
+// shared memory so that global traffic is 128-bit.
+//
+// Behaviour follows the reference kernels
+//   camera fwd/bwd   gsplat/cuda/csrc/projection.cu:605-751 / 753-964
+//   packed fwd/bwd   gsplat/cuda/csrc/projection.cu:1157-1353 / 1466-1716
+//   lidar fwd/bwd    gsplat/cuda/csrc/projection.cu:2268-2417 / 2419-2629
+// except that entries of culled (sensor, Gaussian) pairs are written as zeros instead of
+// being left uninitialised.
+#include "common.cuh"
+#include "splat_math.cuh"
+
+namespace splatad {
+
+struct SensorCam {
+    Pose pose;
+    Intrin K;
+    V3 lin, ang;
+    float rs_time;
+};
+
+struct SensorLidar {
+    Pose pose;
+    V3 lin, ang;
+    float rs_time;
+};
+
+__device__ __forceinline__ V3 ld3(const float *p) { return v3(p[0], p[1], p[2]); }
+
+__device__ __forceinline__ SensorCam load_cam(const float *viewmats, const float *Ks,
+                                              const float *lin, const float *ang,
+                                              const float *rs, uint32_t c) {
+    SensorCam s;
+    s.pose = load_pose(viewmats + 16 * c);
+    const float *K = Ks + 9 * c;
+    s.K.fx = K[0]; s.K.fy = K[4]; s.K.cx = K[2]; s.K.cy = K[5];
+    s.lin = ld3(lin + 3 * c);
+    s.ang = ld3(ang + 3 * c);
+    s.rs_time = rs[c];
+    return s;
+}
+
+__device__ __forceinline__ SensorLidar load_lidar(const float *viewmats, const float *lin,
+                                                  const float *ang, const float *rs, uint32_t c) {
+    SensorLidar s;
+    s.pose = load_pose(viewmats + 16 * c);
+    s.lin = ld3(lin + 3 * c);
+    s.ang = ld3(ang + 3 * c);
+    s.rs_time = rs[c];
+    return s;
+}
+
+struct CamProj {
+    bool valid;
+    float ex, ey;   // extents (float, before int truncation)
+    V2 mean2d;
+    float depth;
+    float conic[3];
+    float comp;
+    V2 pix_vel;
+};
+
+__device__ __forceinline__ CamProj project_cam(const SensorCam &s, V3 mean, const M3 &covar,
+                                               bool has_vel, V3 vel_w, int width, int height,
+                                               float eps2d, float near_plane, float far_plane,
+                                               float radius_clip) {
+    CamProj o;
+    o.valid = false;
+    o.ex = o.ey = 0.f; o.mean2d = v2(0.f, 0.f); o.depth = 0.f;
+    o.conic[0] = o.conic[1] = o.conic[2] = 0.f; o.comp = 0.f; o.pix_vel = v2(0.f, 0.f);
+
+    V3 p = mul(s.pose.R, mean) + s.pose.t;
+    if (p.z < near_plane || p.z > far_plane) return o;
+    M3 covar_c = covar_world_to_cam(s.pose.R, covar);
+    M2 cov2d; V2 m2d; PerspJ J;
+    persp_proj(p, covar_c, s.K, width, height, cov2d, m2d, J);
+    float comp;
+    float det = add_blur(eps2d, cov2d, comp);
+    if (!(det > 0.f)) return o;
+    float ex = 3.f * sqrtf(cov2d.m[0][0]);
+    float ey = 3.f * sqrtf(cov2d.m[1][1]);
+    if (ex <= radius_clip && ey <= radius_clip) return o;
+    V2 pv = v2(0.f, 0.f);
+    if (s.rs_time > 0.f) {
+        V3 vel_c = has_vel ? mul(s.pose.R, vel_w) : v3(0.f, 0.f, 0.f);
+        pv = compute_pix_velocity(p, s.lin, s.ang, vel_c, J);
+        ex += fabsf(pv.x) * 0.5f * s.rs_time;
+        ey += fabsf(pv.y) * 0.5f * s.rs_time;
+    }
+    if (m2d.x + ex <= 0.f || m2d.x - ex >= (float)width || m2d.y + ey <= 0.f ||
+        m2d.y - ey >= (float)height)
+        return o;
+    M2 inv;
+    inverse2(cov2d, det, inv);
+    o.valid = true;
+    o.ex = ex; o.ey = ey; o.mean2d = m2d; o.depth = p.z;
+    o.conic[0] = inv.m[0][0]; o.conic[1] = inv.m[0][1]; o.conic[2] = inv.m[1][1];
+    o.comp = comp; o.pix_vel = pv;
+    return o;
+}
+
+struct LidarProj {
+    bool valid;
+    float ex, ey;
+    V2 mean2d;
+    float depth;
+    float conic[3];
+    float comp;
+    V3 pix_vel;
+    V2 depth_comp;
+};
+
+__device__ __forceinline__ LidarProj project_lidar(const SensorLidar &s, V3 mean, const M3 &covar,
+                                                   bool has_vel, V3 vel_w, float min_el,
+                                                   float max_el, float min_az, float max_az,
+                                                   float eps2d, float near_plane, float far_plane,
+                                                   float radius_clip) {
+    LidarProj o;
+    o.valid = false;
+    o.ex = o.ey = 0.f; o.mean2d = v2(0.f, 0.f); o.depth = 0.f;
+    o.conic[0] = o.conic[1] = o.conic[2] = 0.f; o.comp = 0.f;
+    o.pix_vel = v3(0.f, 0.f, 0.f); o.depth_comp = v2(0.f, 0.f);
+
+    V3 p = mul(s.pose.R, mean) + s.pose.t;
+    float dist = spl_norm3(p.x, p.y, p.z);
+    if (dist < near_plane || dist > far_plane) return o;
+    M3 covar_c = covar_world_to_cam(s.pose.R, covar);
+    M2 cov2d; V2 m2d; V2 dc; M3 J;
+    lidar_proj(p, covar_c, eps2d, m2d, cov2d, dc, J);
+    float comp;
+    float det = add_blur(eps2d, cov2d, comp);
+    if (!(det > 0.f)) return o;
+    float ex = 3.f * sqrtf(fmaxf(0.f, cov2d.m[0][0]));
+    float ey = 3.f * sqrtf(fmaxf(0.f, cov2d.m[1][1]));
+    if (ex <= radius_clip && ey <= radius_clip) return o;
+    V3 pv = v3(0.f, 0.f, 0.f);
+    if (s.rs_time > 0.f) {
+        V3 vel_c = has_vel ? mul(s.pose.R, vel_w) : v3(0.f, 0.f, 0.f);
+        pv = compute_lidar_velocity(p, s.lin, s.ang, vel_c, J);
+        ex += fabsf(pv.x) * 0.5f * s.rs_time;
+        ey += fabsf(pv.y) * 0.5f * s.rs_time;
+    }
+    if (m2d.y + ey <= min_el || m2d.y - ey >= max_el || m2d.x + ex <= min_az || m2d.x - ex >= max_az)
+        return o;
+    M2 inv;
+    inverse2(cov2d, det, inv);
+    o.valid = true;
+    o.ex = ex; o.ey = ey; o.mean2d = m2d; o.depth = dist;
+    o.conic[0] = inv.m[0][0]; o.conic[1] = inv.m[0][1]; o.conic[2] = inv.m[1][1];
+    o.comp = comp; o.pix_vel = pv; o.depth_comp = dc;
+    return o;
+}
+
+// Shared-memory slab loader for this block's Gaussians. Returns through references.
+struct GaussIn {
+    V3 mean;
+    M3 covar;
+    V4 quat;
+    V3 scale;
+    V3 vel;
+};
+
+// smem layout: 3 slabs of kThreads*3 floats (means, scales|covars-part, velocities) + covars 6.
+template <bool kNeedQS>
+__device__ __forceinline__ GaussIn load_gaussian(const float *__restrict__ means,
+                                                 const float *__restrict__ covars,
+                                                 const float *__restrict__ quats,
+                                                 const float *__restrict__ scales,
+                                                 const float *__restrict__ velocities, uint32_t N,
+                                                 uint32_t g0, float *smem /* kThreads*6 floats */) {
+    GaussIn in;
+    const uint32_t n = min((uint32_t)kThreads, N - g0);
+    const uint32_t t = threadIdx.x;
+    const bool live = t < n;
+    in.mean = v3(0.f, 0.f, 1.f); in.scale = v3(1.f, 1.f, 1.f); in.vel = v3(0.f, 0.f, 0.f);
+    in.quat.x = 1.f; in.quat.y = in.quat.z = in.quat.w = 0.f;
+
+    stage_in(means + (size_t)g0 * 3, smem, n * 3);
+    __syncthreads();
+    if (live) in.mean = ld3(smem + 3 * t);
+    __syncthreads();
+    if (velocities != nullptr) {
+        stage_in(velocities + (size_t)g0 * 3, smem, n * 3);
+        __syncthreads();
+        if (live) in.vel = ld3(smem + 3 * t);
+        __syncthreads();
+    }
+    if (covars != nullptr) {
+        stage_in(covars + (size_t)g0 * 6, smem, n * 6);
+        __syncthreads();
+        if (live) in.covar = covar_from_triu(smem + 6 * t);
+        else in.covar = m3_zero();
+        __syncthreads();
+    } else {
+        stage_in(scales + (size_t)g0 * 3, smem, n * 3);
+        __syncthreads();
+        if (live) in.scale = ld3(smem + 3 * t);
+        __syncthreads();
+        if (live) {
+            const float4 q = __ldg(reinterpret_cast<const float4 *>(quats) + g0 + t);
+            in.quat.x = q.x; in.quat.y = q.y; in.quat.z = q.z; in.quat.w = q.w;
+        }
+        in.covar = quat_scale_to_covar(in.quat, in.scale);
+    }
+    return in;
+}
+
+// ---------------------------------------------------------------------------------------
+// Lidar forward
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+lidar_projection_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ means,
+                            const float *__restrict__ covars, const float *__restrict__ quats,
+                            const float *__restrict__ scales, const float *__restrict__ velocities,
+                            const float *__restrict__ viewmats, float min_el, float max_el,
+                            float min_az, float max_az, const float *__restrict__ lin_vel,
+                            const float *__restrict__ ang_vel, const float *__restrict__ rs_time,
+                            float eps2d, float near_plane, float far_plane, float radius_clip,
+                            float *__restrict__ radii, float *__restrict__ means2d,
+                            float *__restrict__ depths, float *__restrict__ conics,
+                            float *__restrict__ compensations, float *__restrict__ pix_vels,
+                            float *__restrict__ depth_comps) {
+    __shared__ __align__(16) float smem[kThreads * 6];
+    const uint32_t g0 = blockIdx.x * kThreads;
+    const uint32_t n = min((uint32_t)kThreads, N - g0);
+    const uint32_t t = threadIdx.x;
+    const bool live = t < n;
+    GaussIn in = load_gaussian<false>(means, covars, quats, scales, velocities, N, g0, smem);
+
+    for (uint32_t c = 0; c < C; ++c) {
+        SensorLidar s = load_lidar(viewmats, lin_vel, ang_vel, rs_time, c);
+        LidarProj o = project_lidar(s, in.mean, in.covar, velocities != nullptr, in.vel, min_el,
+                                    max_el, min_az, max_az, eps2d, near_plane, far_plane,
+                                    radius_clip);
+        const size_t base = (size_t)c * N + g0;
+        if (live) {
+            const size_t i = base + t;
+            reinterpret_cast<float2 *>(radii)[i] = make_float2(o.ex, o.ey);
+            reinterpret_cast<float2 *>(means2d)[i] = make_float2(o.mean2d.x, o.mean2d.y);
+            reinterpret_cast<float2 *>(depth_comps)[i] = make_float2(o.depth_comp.x, o.depth_comp.y);
+            depths[i] = o.depth;
+            if (compensations != nullptr) compensations[i] = o.comp;
+            smem[3 * t + 0] = o.conic[0]; smem[3 * t + 1] = o.conic[1]; smem[3 * t + 2] = o.conic[2];
+            smem[kThreads * 3 + 3 * t + 0] = o.pix_vel.x;
+            smem[kThreads * 3 + 3 * t + 1] = o.pix_vel.y;
+            smem[kThreads * 3 + 3 * t + 2] = o.pix_vel.z;
+        }
+        __syncthreads();
+        stage_out(conics + base * 3, smem, n * 3);
+        stage_out(pix_vels + base * 3, smem + kThreads * 3, n * 3);
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Camera forward, [C, N] layout
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+projection_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ means,
+                      const float *__restrict__ covars, const float *__restrict__ quats,
+                      const float *__restrict__ scales, const float *__restrict__ velocities,
+                      const float *__restrict__ viewmats, const float *__restrict__ Ks, int width,
+                      int height, const float *__restrict__ lin_vel,
+                      const float *__restrict__ ang_vel, const float *__restrict__ rs_time,
+                      float eps2d, float near_plane, float far_plane, float radius_clip,
+                      int32_t *__restrict__ radii, float *__restrict__ means2d,
+                      float *__restrict__ depths, float *__restrict__ conics,
+                      float *__restrict__ compensations, float *__restrict__ pix_vels) {
+    __shared__ __align__(16) float smem[kThreads * 6];
+    const uint32_t g0 = blockIdx.x * kThreads;
+    const uint32_t n = min((uint32_t)kThreads, N - g0);
+    const uint32_t t = threadIdx.x;
+    const bool live = t < n;
+    GaussIn in = load_gaussian<false>(means, covars, quats, scales, velocities, N, g0, smem);
+
+    for (uint32_t c = 0; c < C; ++c) {
+        SensorCam s = load_cam(viewmats, Ks, lin_vel, ang_vel, rs_time, c);
+        CamProj o = project_cam(s, in.mean, in.covar, velocities != nullptr, in.vel, width, height,
+                                eps2d, near_plane, far_plane, radius_clip);
+        const size_t base = (size_t)c * N + g0;
+        if (live) {
+            const size_t i = base + t;
+            int2 r = make_int2((int32_t)o.ex, (int32_t)o.ey);
+            reinterpret_cast<int2 *>(radii)[i] = r;
+            reinterpret_cast<float2 *>(means2d)[i] = make_float2(o.mean2d.x, o.mean2d.y);
+            reinterpret_cast<float2 *>(pix_vels)[i] = make_float2(o.pix_vel.x, o.pix_vel.y);
+            depths[i] = o.depth;
+            if (compensations != nullptr) compensations[i] = o.comp;
+            smem[3 * t + 0] = o.conic[0]; smem[3 * t + 1] = o.conic[1]; smem[3 * t + 2] = o.conic[2];
+        }
+        __syncthreads();
+        stage_out(conics + base * 3, smem, n * 3);
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Camera forward, packed (COO) layout: rows ordered camera-major, Gaussian-minor.
+// Pass 1 (block_counts != nullptr) counts the visible Gaussians of each (camera, block);
+// pass 2 (block_offsets != nullptr) recomputes and writes rows at the scanned offsets.
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+projection_packed_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ means,
+                             const float *__restrict__ covars, const float *__restrict__ quats,
+                             const float *__restrict__ scales, const float *__restrict__ velocities,
+                             const float *__restrict__ viewmats, const float *__restrict__ Ks,
+                             int width, int height, const float *__restrict__ lin_vel,
+                             const float *__restrict__ ang_vel, const float *__restrict__ rs_time,
+                             float eps2d, float near_plane, float far_plane, float radius_clip,
+                             int32_t *__restrict__ block_counts,        // [C, nblocks] pass 1
+                             const int32_t *__restrict__ block_offsets, // [C, nblocks] pass 2 (exclusive)
+                             int64_t *__restrict__ camera_ids, int64_t *__restrict__ gaussian_ids,
+                             int32_t *__restrict__ radii, float *__restrict__ means2d,
+                             float *__restrict__ depths, float *__restrict__ conics,
+                             float *__restrict__ compensations, float *__restrict__ pix_vels) {
+    __shared__ __align__(16) float smem[kThreads * 6];
+    __shared__ int32_t warp_counts[kThreads / 32];
+    const uint32_t g0 = blockIdx.x * kThreads;
+    const uint32_t n = min((uint32_t)kThreads, N - g0);
+    const uint32_t t = threadIdx.x;
+    const bool live = t < n;
+    const uint32_t lane = t & 31, warp = t >> 5;
+    GaussIn in = load_gaussian<false>(means, covars, quats, scales, velocities, N, g0, smem);
+
+    for (uint32_t c = 0; c < C; ++c) {
+        SensorCam s = load_cam(viewmats, Ks, lin_vel, ang_vel, rs_time, c);
+        CamProj o = project_cam(s, in.mean, in.covar, velocities != nullptr, in.vel, width, height,
+                                eps2d, near_plane, far_plane, radius_clip);
+        const bool vis = live && o.valid;
+        const uint32_t ballot = __ballot_sync(0xffffffffu, vis);
+        if (lane == 0) warp_counts[warp] = __popc(ballot);
+        __syncthreads();
+        int32_t before = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) {
+            const int32_t cw = warp_counts[w];
+            if (w < (int)warp) before += cw;
+            total += cw;
+        }
+        __syncthreads();
+        if (block_counts != nullptr) {
+            if (t == 0) block_counts[(size_t)c * gridDim.x + blockIdx.x] = total;
+            continue;
+        }
+        if (vis) {
+            const int64_t row = (int64_t)block_offsets[(size_t)c * gridDim.x + blockIdx.x] + before +
+                                __popc(ballot & ((1u << lane) - 1u));
+            camera_ids[row] = (int64_t)c;
+            gaussian_ids[row] = (int64_t)(g0 + t);
+            radii[2 * row] = (int32_t)o.ex;
+            radii[2 * row + 1] = (int32_t)o.ey;
+            means2d[2 * row] = o.mean2d.x;
+            means2d[2 * row + 1] = o.mean2d.y;
+            depths[row] = o.depth;
+            conics[3 * row] = o.conic[0];
+            conics[3 * row + 1] = o.conic[1];
+            conics[3 * row + 2] = o.conic[2];
+            pix_vels[2 * row] = o.pix_vel.x;
+            pix_vels[2 * row + 1] = o.pix_vel.y;
+            if (compensations != nullptr) compensations[row] = o.comp;
+        }
+    }
+}
+
+// Exclusive scan of the [C * nblocks] block counts (single block), total -> *nnz and
+// indptr[c] = offset of camera c's first row, indptr[C] = nnz.
+__global__ void __launch_bounds__(1024)
+packed_scan_kernel(const int32_t *__restrict__ counts, int32_t *__restrict__ offsets, uint32_t C,
+                   uint32_t nblocks, int32_t *__restrict__ indptr, int64_t *__restrict__ nnz_out) {
+    __shared__ int32_t part[1024];
+    const uint32_t total = C * nblocks;
+    const uint32_t t = threadIdx.x;
+    const uint32_t per = (total + 1023) / 1024;
+    const uint32_t lo = min(t * per, total), hi = min(lo + per, total);
+    int32_t s = 0;
+    for (uint32_t i = lo; i < hi; ++i) s += counts[i];
+    part[t] = s;
+    __syncthreads();
+    // Hillis-Steele inclusive scan over 1024 partials
+    for (uint32_t off = 1; off < 1024; off <<= 1) {
+        int32_t v = (t >= off) ? part[t - off] : 0;
+        __syncthreads();
+        part[t] += v;
+        __syncthreads();
+    }
+    int32_t run = (t == 0) ? 0 : part[t - 1];
+    for (uint32_t i = lo; i < hi; ++i) {
+        offsets[i] = run;
+        if (i % nblocks == 0) indptr[i / nblocks] = run;
+        run += counts[i];
+    }
+    if (t == 1023) {
+        indptr[C] = part[1023];
+        *nnz_out = (int64_t)part[1023];
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Backward helpers
+// ---------------------------------------------------------------------------------------
+struct ParamGrads {
+    V3 v_mean;
+    M3 v_covar;   // full 3x3 gradient of the world covariance
+};
+
+// Block-level reduction of 12 floats (v_R 9 + v_t 3) followed by one atomicAdd set per block.
+__device__ __forceinline__ void block_reduce_viewmat(const M3 &v_R, V3 v_t, float *v_viewmat,
+                                                     float *red /* [kThreads/32][12] */) {
+    float vals[12] = {v_R.m[0][0], v_R.m[0][1], v_R.m[0][2], v_t.x,
+                      v_R.m[1][0], v_R.m[1][1], v_R.m[1][2], v_t.y,
+                      v_R.m[2][0], v_R.m[2][1], v_R.m[2][2], v_t.z};
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < 12; ++k) {
+        float v = vals[k];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (lane == 0) red[warp * 12 + k] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < 12) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) s += red[w * 12 + threadIdx.x];
+        if (s != 0.f) atomicAdd(v_viewmat + threadIdx.x, s);   // rows 0..2 of the 4x4
+    }
+    __syncthreads();
+}
+
+// Camera backward for one (sensor, Gaussian) pair. Returns the world-space mean gradient and
+// covariance gradient, accumulates v_R / v_t.
+__device__ __forceinline__ void cam_pair_bwd(const SensorCam &s, const GaussIn &in, bool has_vel,
+                                             int width, int height, float eps2d,
+                                             const float *conic3, float comp, bool has_comp,
+                                             V2 v_mean2d, float v_depth, const float *v_conic3,
+                                             float v_comp, V2 v_pix_vel, V3 &v_mean, M3 &v_covar,
+                                             M3 &v_R, V3 &v_t, V3 &v_vel_w) {
+    M2 cinv;
+    cinv.m[0][0] = conic3[0]; cinv.m[0][1] = conic3[1]; cinv.m[1][0] = conic3[1]; cinv.m[1][1] = conic3[2];
+    M2 v_cinv;
+    v_cinv.m[0][0] = v_conic3[0]; v_cinv.m[0][1] = v_conic3[1] * 0.5f;
+    v_cinv.m[1][0] = v_conic3[1] * 0.5f; v_cinv.m[1][1] = v_conic3[2];
+    M2 v_cov2d = m2_zero();
+    inverse2_vjp(cinv, v_cinv, v_cov2d);
+    if (has_comp) add_blur_vjp(eps2d, cinv, comp, v_comp, v_cov2d);
+
+    V3 p = mul(s.pose.R, in.mean) + s.pose.t;
+    M3 covar_c = covar_world_to_cam(s.pose.R, in.covar);
+
+    V3 v_p = v3(0.f, 0.f, 0.f);
+    if (s.rs_time > 0.f) {
+        V3 vel_c = has_vel ? mul(s.pose.R, in.vel) : v3(0.f, 0.f, 0.f);
+        V3 v_vel_c = v3(0.f, 0.f, 0.f);
+        pix_velocity_vjp(p, s.lin, s.ang, vel_c, s.K, width, height, v_pix_vel, v_p, v_vel_c);
+        if (has_vel) {
+            v_R = add(v_R, outer(v_vel_c, in.vel));
+            v_vel_w = v_vel_w + mul_t(s.pose.R, v_vel_c);
+        }
+    }
+    M3 v_covar_c = m3_zero();
+    persp_proj_vjp(p, covar_c, s.K, width, height, v_cov2d, v_mean2d, v_p, v_covar_c);
+    v_p.z += v_depth;
+    // p = R mean + t
+    v_R = add(v_R, outer(v_p, in.mean));
+    v_t = v_t + v_p;
+    v_mean = v_mean + mul_t(s.pose.R, v_p);
+    covar_world_to_cam_vjp(s.pose.R, in.covar, v_covar_c, v_R, v_covar);
+}
+
+__device__ __forceinline__ void lidar_pair_bwd(const SensorLidar &s, const GaussIn &in,
+                                               bool has_vel, float eps2d, const float *conic3,
+                                               float comp, bool has_comp, V2 v_mean2d,
+                                               float v_depth, const float *v_conic3, float v_comp,
+                                               V3 v_pix_vel, V2 v_depth_comp, V3 &v_mean,
+                                               M3 &v_covar, M3 &v_R, V3 &v_t, V3 &v_vel_w) {
+    M2 cinv;
+    cinv.m[0][0] = conic3[0]; cinv.m[0][1] = conic3[1]; cinv.m[1][0] = conic3[1]; cinv.m[1][1] = conic3[2];
+    M2 v_cinv;
+    v_cinv.m[0][0] = v_conic3[0]; v_cinv.m[0][1] = v_conic3[1] * 0.5f;
+    v_cinv.m[1][0] = v_conic3[1] * 0.5f; v_cinv.m[1][1] = v_conic3[2];
+    M2 v_cov2d = m2_zero();
+    inverse2_vjp(cinv, v_cinv, v_cov2d);
+    if (has_comp) add_blur_vjp(eps2d, cinv, comp, v_comp, v_cov2d);
+
+    V3 p = mul(s.pose.R, in.mean) + s.pose.t;
+    M3 covar_c = covar_world_to_cam(s.pose.R, in.covar);
+
+    V3 v_p = v3(0.f, 0.f, 0.f);
+    if (s.rs_time > 0.f) {
+        V3 vel_c = has_vel ? mul(s.pose.R, in.vel) : v3(0.f, 0.f, 0.f);
+        V3 v_vel_c = v3(0.f, 0.f, 0.f);
+        lidar_velocity_vjp(p, s.lin, s.ang, vel_c, v_pix_vel, v_p, v_vel_c);
+        if (has_vel) {
+            v_R = add(v_R, outer(v_vel_c, in.vel));
+            v_vel_w = v_vel_w + mul_t(s.pose.R, v_vel_c);
+        }
+    }
+    M3 v_covar_c = m3_zero();
+    lidar_proj_vjp(p, covar_c, eps2d, v_mean2d, v_cov2d, v_depth_comp, v_p, v_covar_c);
+    const float rinv = spl_rnorm3(p.x, p.y, p.z);
+    v_p.x += p.x * rinv * v_depth;
+    v_p.y += p.y * rinv * v_depth;
+    v_p.z += p.z * rinv * v_depth;
+    v_R = add(v_R, outer(v_p, in.mean));
+    v_t = v_t + v_p;
+    v_mean = v_mean + mul_t(s.pose.R, v_p);
+    covar_world_to_cam_vjp(s.pose.R, in.covar, v_covar_c, v_R, v_covar);
+}
+
+__device__ __forceinline__ void covar_grad_to_triu(const M3 &g, float *o) {
+    o[0] = g.m[0][0];
+    o[1] = g.m[0][1] + g.m[1][0];
+    o[2] = g.m[0][2] + g.m[2][0];
+    o[3] = g.m[1][1];
+    o[4] = g.m[1][2] + g.m[2][1];
+    o[5] = g.m[2][2];
+}
+
+// Writes the per-Gaussian parameter gradients of this block (means, and covars or
+// quats+scales, optionally velocities) through shared memory.
+__device__ __forceinline__ void store_param_grads(const GaussIn &in, bool use_covars, V3 v_mean,
+                                                  const M3 &v_covar, V3 v_vel_w, uint32_t g0,
+                                                  uint32_t n, float *smem, float *v_means,
+                                                  float *v_covars, float *v_quats, float *v_scales,
+                                                  float *v_velocities) {
+    const uint32_t t = threadIdx.x;
+    const bool live = t < n;
+    if (v_means != nullptr) {
+        if (live) { smem[3 * t] = v_mean.x; smem[3 * t + 1] = v_mean.y; smem[3 * t + 2] = v_mean.z; }
+        __syncthreads();
+        stage_out(v_means + (size_t)g0 * 3, smem, n * 3);
+        __syncthreads();
+    }
+    if (v_velocities != nullptr) {
+        if (live) { smem[3 * t] = v_vel_w.x; smem[3 * t + 1] = v_vel_w.y; smem[3 * t + 2] = v_vel_w.z; }
+        __syncthreads();
+        stage_out(v_velocities + (size_t)g0 * 3, smem, n * 3);
+        __syncthreads();
+    }
+    if (use_covars) {
+        if (v_covars != nullptr) {
+            if (live) covar_grad_to_triu(v_covar, smem + 6 * t);
+            __syncthreads();
+            stage_out(v_covars + (size_t)g0 * 6, smem, n * 6);
+            __syncthreads();
+        }
+    } else {
+        V4 v_quat; v_quat.x = v_quat.y = v_quat.z = v_quat.w = 0.f;
+        V3 v_scale = v3(0.f, 0.f, 0.f);
+        M3 R = quat_to_rotmat(in.quat);
+        quat_scale_to_covar_vjp(in.quat, in.scale, R, v_covar, v_quat, v_scale);
+        if (v_quats != nullptr && live)
+            reinterpret_cast<float4 *>(v_quats)[g0 + t] = make_float4(v_quat.x, v_quat.y, v_quat.z, v_quat.w);
+        if (v_scales != nullptr) {
+            if (live) { smem[3 * t] = v_scale.x; smem[3 * t + 1] = v_scale.y; smem[3 * t + 2] = v_scale.z; }
+            __syncthreads();
+            stage_out(v_scales + (size_t)g0 * 3, smem, n * 3);
+            __syncthreads();
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Camera backward, [C, N] layout
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+projection_bwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ means,
+                      const float *__restrict__ covars, const float *__restrict__ quats,
+                      const float *__restrict__ scales, const float *__restrict__ velocities,
+                      const float *__restrict__ viewmats, const float *__restrict__ Ks, int width,
+                      int height, const float *__restrict__ lin_vel,
+                      const float *__restrict__ ang_vel, const float *__restrict__ rs_time,
+                      float eps2d, const int32_t *__restrict__ radii,
+                      const float *__restrict__ conics, const float *__restrict__ compensations,
+                      const float *__restrict__ v_means2d, const float *__restrict__ v_depths,
+                      const float *__restrict__ v_conics, const float *__restrict__ v_compensations,
+                      const float *__restrict__ v_pix_vels, float *__restrict__ v_means,
+                      float *__restrict__ v_covars, float *__restrict__ v_quats,
+                      float *__restrict__ v_scales, float *__restrict__ v_viewmats,
+                      float *__restrict__ v_velocities) {
+    __shared__ __align__(16) float smem[kThreads * 6];
+    __shared__ float red[(kThreads / 32) * 12];
+    const uint32_t g0 = blockIdx.x * kThreads;
+    const uint32_t n = min((uint32_t)kThreads, N - g0);
+    const uint32_t t = threadIdx.x;
+    const bool live = t < n;
+    GaussIn in = load_gaussian<true>(means, covars, quats, scales, velocities, N, g0, smem);
+
+    V3 v_mean = v3(0.f, 0.f, 0.f), v_vel_w = v3(0.f, 0.f, 0.f);
+    M3 v_covar = m3_zero();
+    for (uint32_t c = 0; c < C; ++c) {
+        SensorCam s = load_cam(viewmats, Ks, lin_vel, ang_vel, rs_time, c);
+        const size_t i = (size_t)c * N + g0 + t;
+        M3 v_R = m3_zero();
+        V3 v_t = v3(0.f, 0.f, 0.f);
+        if (live && radii[2 * i] > 0) {
+            const float cn[3] = {conics[3 * i], conics[3 * i + 1], conics[3 * i + 2]};
+            const float vcn[3] = {v_conics[3 * i], v_conics[3 * i + 1], v_conics[3 * i + 2]};
+            const bool has_comp = v_compensations != nullptr;
+            cam_pair_bwd(s, in, velocities != nullptr, width, height, eps2d, cn,
+                         has_comp ? compensations[i] : 0.f, has_comp,
+                         v2(v_means2d[2 * i], v_means2d[2 * i + 1]), v_depths[i], vcn,
+                         has_comp ? v_compensations[i] : 0.f,
+                         v2(v_pix_vels[2 * i], v_pix_vels[2 * i + 1]), v_mean, v_covar, v_R, v_t,
+                         v_vel_w);
+        }
+        if (v_viewmats != nullptr) block_reduce_viewmat(v_R, v_t, v_viewmats + 16 * c, red);
+    }
+    store_param_grads(in, covars != nullptr, v_mean, v_covar, v_vel_w, g0, n, smem, v_means,
+                      v_covars, v_quats, v_scales, v_velocities);
+}
+
+// ---------------------------------------------------------------------------------------
+// Lidar backward, [C, N] layout
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+lidar_projection_bwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ means,
+                            const float *__restrict__ covars, const float *__restrict__ quats,
+                            const float *__restrict__ scales, const float *__restrict__ velocities,
+                            const float *__restrict__ viewmats, const float *__restrict__ lin_vel,
+                            const float *__restrict__ ang_vel, const float *__restrict__ rs_time,
+                            float eps2d, const float *__restrict__ radii,
+                            const float *__restrict__ conics,
+                            const float *__restrict__ compensations,
+                            const float *__restrict__ v_means2d, const float *__restrict__ v_depths,
+                            const float *__restrict__ v_conics,
+                            const float *__restrict__ v_compensations,
+                            const float *__restrict__ v_pix_vels,
+                            const float *__restrict__ v_depth_comps, float *__restrict__ v_means,
+                            float *__restrict__ v_covars, float *__restrict__ v_quats,
+                            float *__restrict__ v_scales, float *__restrict__ v_viewmats,
+                            float *__restrict__ v_velocities) {
+    __shared__ __align__(16) float smem[kThreads * 6];
+    __shared__ float red[(kThreads / 32) * 12];
+    const uint32_t g0 = blockIdx.x * kThreads;
+    const uint32_t n = min((uint32_t)kThreads, N - g0);
+    const uint32_t t = threadIdx.x;
+    const bool live = t < n;
+    GaussIn in = load_gaussian<true>(means, covars, quats, scales, velocities, N, g0, smem);
+
+    V3 v_mean = v3(0.f, 0.f, 0.f), v_vel_w = v3(0.f, 0.f, 0.f);
+    M3 v_covar = m3_zero();
+    for (uint32_t c = 0; c < C; ++c) {
+        SensorLidar s = load_lidar(viewmats, lin_vel, ang_vel, rs_time, c);
+        const size_t i = (size_t)c * N + g0 + t;
+        M3 v_R = m3_zero();
+        V3 v_t = v3(0.f, 0.f, 0.f);
+        if (live && radii[2 * i] > 0.f) {
+            const float cn[3] = {conics[3 * i], conics[3 * i + 1], conics[3 * i + 2]};
+            const float vcn[3] = {v_conics[3 * i], v_conics[3 * i + 1], v_conics[3 * i + 2]};
+            const bool has_comp = v_compensations != nullptr;
+            lidar_pair_bwd(s, in, velocities != nullptr, eps2d, cn,
+                           has_comp ? compensations[i] : 0.f, has_comp,
+                           v2(v_means2d[2 * i], v_means2d[2 * i + 1]), v_depths[i], vcn,
+                           has_comp ? v_compensations[i] : 0.f,
+                           v3(v_pix_vels[3 * i], v_pix_vels[3 * i + 1], v_pix_vels[3 * i + 2]),
+                           v2(v_depth_comps[2 * i], v_depth_comps[2 * i + 1]), v_mean, v_covar,
+                           v_R, v_t, v_vel_w);
+        }
+        if (v_viewmats != nullptr) block_reduce_viewmat(v_R, v_t, v_viewmats + 16 * c, red);
+    }
+    store_param_grads(in, covars != nullptr, v_mean, v_covar, v_vel_w, g0, n, smem, v_means,
+                      v_covars, v_quats, v_scales, v_velocities);
+}
+
+// ---------------------------------------------------------------------------------------
+// Camera backward, packed layout: one thread per packed row. Rows of one Gaussian (one per
+// camera that sees it) are far apart, so parameter gradients use atomics (dense outputs) or
+// are written per row (sparse_grad).
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+projection_packed_bwd_kernel(uint32_t C, uint32_t N, uint32_t nnz, const float *__restrict__ means,
+                             const float *__restrict__ covars, const float *__restrict__ quats,
+                             const float *__restrict__ scales, const float *__restrict__ velocities,
+                             const float *__restrict__ viewmats, const float *__restrict__ Ks,
+                             int width, int height, const float *__restrict__ lin_vel,
+                             const float *__restrict__ ang_vel, const float *__restrict__ rs_time,
+                             float eps2d, const int64_t *__restrict__ camera_ids,
+                             const int64_t *__restrict__ gaussian_ids,
+                             const float *__restrict__ conics,
+                             const float *__restrict__ compensations,
+                             const float *__restrict__ v_means2d, const float *__restrict__ v_depths,
+                             const float *__restrict__ v_conics,
+                             const float *__restrict__ v_compensations,
+                             const float *__restrict__ v_pix_vels, int sparse_grad,
+                             float *__restrict__ v_means, float *__restrict__ v_covars,
+                             float *__restrict__ v_quats, float *__restrict__ v_scales,
+                             float *__restrict__ v_viewmats, float *__restrict__ v_velocities) {
+    const uint32_t idx = blockIdx.x * kThreads + threadIdx.x;
+    if (idx >= nnz) return;
+    const uint32_t c = (uint32_t)camera_ids[idx];
+    const uint32_t g = (uint32_t)gaussian_ids[idx];
+    GaussIn in;
+    in.mean = ld3(means + 3 * (size_t)g);
+    in.vel = velocities != nullptr ? ld3(velocities + 3 * (size_t)g) : v3(0.f, 0.f, 0.f);
+    if (covars != nullptr) {
+        in.covar = covar_from_triu(covars + 6 * (size_t)g);
+    } else {
+        const float4 q = __ldg(reinterpret_cast<const float4 *>(quats) + g);
+        in.quat.x = q.x; in.quat.y = q.y; in.quat.z = q.z; in.quat.w = q.w;
+        in.scale = ld3(scales + 3 * (size_t)g);
+        in.covar = quat_scale_to_covar(in.quat, in.scale);
+    }
+    SensorCam s = load_cam(viewmats, Ks, lin_vel, ang_vel, rs_time, c);
+    const size_t i = idx;
+    const float cn[3] = {conics[3 * i], conics[3 * i + 1], conics[3 * i + 2]};
+    const float vcn[3] = {v_conics[3 * i], v_conics[3 * i + 1], v_conics[3 * i + 2]};
+    const bool has_comp = v_compensations != nullptr;
+    V3 v_mean = v3(0.f, 0.f, 0.f), v_vel_w = v3(0.f, 0.f, 0.f), v_t = v3(0.f, 0.f, 0.f);
+    M3 v_covar = m3_zero(), v_R = m3_zero();
+    cam_pair_bwd(s, in, velocities != nullptr, width, height, eps2d, cn,
+                 has_comp ? compensations[i] : 0.f, has_comp,
+                 v2(v_means2d[2 * i], v_means2d[2 * i + 1]), v_depths[i], vcn,
+                 has_comp ? v_compensations[i] : 0.f, v2(v_pix_vels[2 * i], v_pix_vels[2 * i + 1]),
+                 v_mean, v_covar, v_R, v_t, v_vel_w);
+
+    const size_t row = sparse_grad ? (size_t)idx : (size_t)g;
+    auto put = [&](float *base, size_t off, float v) {
+        if (sparse_grad) base[off] = v; else atomicAdd(base + off, v);
+    };
+    if (v_means != nullptr) {
+        put(v_means, 3 * row, v_mean.x); put(v_means, 3 * row + 1, v_mean.y); put(v_means, 3 * row + 2, v_mean.z);
+    }
+    if (v_velocities != nullptr) {
+        put(v_velocities, 3 * row, v_vel_w.x); put(v_velocities, 3 * row + 1, v_vel_w.y);
+        put(v_velocities, 3 * row + 2, v_vel_w.z);
+    }
+    if (covars != nullptr) {
+        if (v_covars != nullptr) {
+            float o[6];
+            covar_grad_to_triu(v_covar, o);
+            for (int k = 0; k < 6; ++k) put(v_covars, 6 * row + k, o[k]);
+        }
+    } else {
+        V4 v_quat; v_quat.x = v_quat.y = v_quat.z = v_quat.w = 0.f;
+        V3 v_scale = v3(0.f, 0.f, 0.f);
+        M3 R = quat_to_rotmat(in.quat);
+        quat_scale_to_covar_vjp(in.quat, in.scale, R, v_covar, v_quat, v_scale);
+        if (v_quats != nullptr) {
+            put(v_quats, 4 * row, v_quat.x); put(v_quats, 4 * row + 1, v_quat.y);
+            put(v_quats, 4 * row + 2, v_quat.z); put(v_quats, 4 * row + 3, v_quat.w);
+        }
+        if (v_scales != nullptr) {
+            put(v_scales, 3 * row, v_scale.x); put(v_scales, 3 * row + 1, v_scale.y);
+            put(v_scales, 3 * row + 2, v_scale.z);
+        }
+    }
+    if (v_viewmats != nullptr) {
+        float *vm = v_viewmats + 16 * (size_t)c;
+        for (int r = 0; r < 3; ++r) {
+            for (int k = 0; k < 3; ++k) atomicAdd(vm + 4 * r + k, v_R.m[r][k]);
+        }
+        atomicAdd(vm + 3, v_t.x); atomicAdd(vm + 7, v_t.y); atomicAdd(vm + 11, v_t.z);
+    }
+}
+
+} // namespace splatad
+
+using namespace splatad;
+
+// =======================================================================================
+// C-ABI
+// =======================================================================================
+extern "C" int splatad_lidar_projection_fwd(
+    uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
+    const float *scales, const float *velocities, const float *viewmats, float min_elevation,
+    float max_elevation, float min_azimuth, float max_azimuth, const float *linear_velocity,
+    const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
+    float near_plane, float far_plane, float radius_clip, float *radii, float *means2d,
+    float *depths, float *conics, float *compensations, float *pix_vels,
+    float *depth_compensations, void *stream) {
+    SPL_REQUIRE(means && viewmats && linear_velocity && angular_velocity && rolling_shutter_time,
+                SPLATAD_ERR_BAD_ARG, "lidar_projection_fwd: null input");
+    SPL_REQUIRE(covars || (quats && scales), SPLATAD_ERR_BAD_ARG,
+                "lidar_projection_fwd: covars or (quats, scales) required");
+    SPL_REQUIRE(radii && means2d && depths && conics && pix_vels && depth_compensations,
+                SPLATAD_ERR_BAD_ARG, "lidar_projection_fwd: null output");
+    if (C == 0 || N == 0) return SPLATAD_OK;
+    lidar_projection_fwd_kernel<<<div_up(N, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+        C, N, means, covars, quats, scales, velocities, viewmats, min_elevation, max_elevation,
+        min_azimuth, max_azimuth, linear_velocity, angular_velocity, rolling_shutter_time, eps2d,
+        near_plane, far_plane, radius_clip, radii, means2d, depths, conics, compensations,
+        pix_vels, depth_compensations);
+    return check_launch("lidar_projection_fwd");
+}
+
+extern "C" int splatad_lidar_projection_bwd(
+    uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
+    const float *scales, const float *velocities, const float *viewmats,
+    const float *linear_velocity, const float *angular_velocity,
+    const float *rolling_shutter_time, float eps2d, const float *radii, const float *conics,
+    const float *compensations, const float *v_means2d, const float *v_depths,
+    const float *v_conics, const float *v_compensations, const float *v_pix_vels,
+    const float *v_depth_compensations, float *v_means, float *v_covars, float *v_quats,
+    float *v_scales, float *v_viewmats, float *v_velocities, void *stream) {
+    SPL_REQUIRE(means && viewmats && radii && conics && v_means2d && v_depths && v_conics &&
+                    v_pix_vels && v_depth_compensations,
+                SPLATAD_ERR_BAD_ARG, "lidar_projection_bwd: null input");
+    SPL_REQUIRE(covars || (quats && scales), SPLATAD_ERR_BAD_ARG,
+                "lidar_projection_bwd: covars or (quats, scales) required");
+    SPL_REQUIRE(!v_compensations || compensations, SPLATAD_ERR_BAD_ARG,
+                "lidar_projection_bwd: v_compensations given without compensations");
+    if (C == 0 || N == 0) return SPLATAD_OK;
+    lidar_projection_bwd_kernel<<<div_up(N, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+        C, N, means, covars, quats, scales, velocities, viewmats, linear_velocity,
+        angular_velocity, rolling_shutter_time, eps2d, radii, conics, compensations, v_means2d,
+        v_depths, v_conics, v_compensations, v_pix_vels, v_depth_compensations, v_means, v_covars,
+        v_quats, v_scales, v_viewmats, v_velocities);
+    return check_launch("lidar_projection_bwd");
+}
+
+extern "C" int splatad_projection_fwd(
+    uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
+    const float *scales, const float *velocities, const float *viewmats, const float *Ks,
+    int32_t image_width, int32_t image_height, const float *linear_velocity,
+    const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
+    float near_plane, float far_plane, float radius_clip, int32_t *radii, float *means2d,
+    float *depths, float *conics, float *compensations, float *pix_vels, void *stream) {
+    SPL_REQUIRE(means && viewmats && Ks && linear_velocity && angular_velocity &&
+                    rolling_shutter_time,
+                SPLATAD_ERR_BAD_ARG, "projection_fwd: null input");
+    SPL_REQUIRE(covars || (quats && scales), SPLATAD_ERR_BAD_ARG,
+                "projection_fwd: covars or (quats, scales) required");
+    SPL_REQUIRE(radii && means2d && depths && conics && pix_vels, SPLATAD_ERR_BAD_ARG,
+                "projection_fwd: null output");
+    if (C == 0 || N == 0) return SPLATAD_OK;
+    projection_fwd_kernel<<<div_up(N, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+        C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
+        linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
+        radius_clip, radii, means2d, depths, conics, compensations, pix_vels);
+    return check_launch("projection_fwd");
+}
+
+extern "C" int splatad_projection_bwd(
+    uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
+    const float *scales, const float *velocities, const float *viewmats, const float *Ks,
+    int32_t image_width, int32_t image_height, const float *linear_velocity,
+    const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
+    const int32_t *radii, const float *conics, const float *compensations,
+    const float *v_means2d, const float *v_depths, const float *v_conics,
+    const float *v_compensations, const float *v_pix_vels, float *v_means, float *v_covars,
+    float *v_quats, float *v_scales, float *v_viewmats, float *v_velocities, void *stream) {
+    SPL_REQUIRE(means && viewmats && Ks && radii && conics && v_means2d && v_depths && v_conics &&
+                    v_pix_vels,
+                SPLATAD_ERR_BAD_ARG, "projection_bwd: null input");
+    SPL_REQUIRE(covars || (quats && scales), SPLATAD_ERR_BAD_ARG,
+                "projection_bwd: covars or (quats, scales) required");
+    SPL_REQUIRE(!v_compensations || compensations, SPLATAD_ERR_BAD_ARG,
+                "projection_bwd: v_compensations given without compensations");
+    if (C == 0 || N == 0) return SPLATAD_OK;
+    projection_bwd_kernel<<<div_up(N, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+        C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
+        linear_velocity, angular_velocity, rolling_shutter_time, eps2d, radii, conics,
+        compensations, v_means2d, v_depths, v_conics, v_compensations, v_pix_vels, v_means,
+        v_covars, v_quats, v_scales, v_viewmats, v_velocities);
+    return check_launch("projection_bwd");
+}
+
+extern "C" size_t splatad_projection_packed_workspace_bytes(uint32_t C, uint32_t N) {
+    // block counts + block offsets
+    return 2 * sizeof(int32_t) * (size_t)C * div_up(N, kThreads) + 256;
+}
+
+extern "C" int splatad_projection_packed_count(
+    uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
+    const float *scales, const float *velocities, const float *viewmats, const float *Ks,
+    int32_t image_width, int32_t image_height, const float *linear_velocity,
+    const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
+    float near_plane, float far_plane, float radius_clip, void *workspace,
+    size_t workspace_bytes, int32_t *indptr, int64_t *nnz_device, void *stream) {
+    SPL_REQUIRE(means && viewmats && Ks && indptr && nnz_device && workspace, SPLATAD_ERR_BAD_ARG,
+                "projection_packed_count: null argument");
+    SPL_REQUIRE(covars || (quats && scales), SPLATAD_ERR_BAD_ARG,
+                "projection_packed_count: covars or (quats, scales) required");
+    SPL_REQUIRE(workspace_bytes >= splatad_projection_packed_workspace_bytes(C, N),
+                SPLATAD_ERR_WORKSPACE, "projection_packed_count: workspace too small");
+    SPL_REQUIRE(C > 0 && N > 0, SPLATAD_ERR_BAD_ARG, "projection_packed_count: empty input");
+    const uint32_t nblocks = div_up(N, kThreads);
+    int32_t *counts = (int32_t *)workspace;
+    int32_t *offsets = counts + (size_t)C * nblocks;
+    cudaStream_t st = (cudaStream_t)stream;
+    projection_packed_fwd_kernel<<<nblocks, kThreads, 0, st>>>(
+        C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
+        linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
+        radius_clip, counts, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+        nullptr, nullptr);
+    packed_scan_kernel<<<1, 1024, 0, st>>>(counts, offsets, C, nblocks, indptr, nnz_device);
+    return check_launch("projection_packed_count");
+}
+
+extern "C" int splatad_projection_packed_fill(
+    uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
+    const float *scales, const float *velocities, const float *viewmats, const float *Ks,
+    int32_t image_width, int32_t image_height, const float *linear_velocity,
+    const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
+    float near_plane, float far_plane, float radius_clip, const void *workspace,
+    int64_t *camera_ids, int64_t *gaussian_ids, int32_t *radii, float *means2d, float *depths,
+    float *conics, float *compensations, float *pix_vels, void *stream) {
+    SPL_REQUIRE(means && viewmats && Ks && workspace && camera_ids && gaussian_ids && radii &&
+                    means2d && depths && conics && pix_vels,
+                SPLATAD_ERR_BAD_ARG, "projection_packed_fill: null argument");
+    SPL_REQUIRE(C > 0 && N > 0, SPLATAD_ERR_BAD_ARG, "projection_packed_fill: empty input");
+    const uint32_t nblocks = div_up(N, kThreads);
+    const int32_t *offsets = (const int32_t *)workspace + (size_t)C * nblocks;
+    projection_packed_fwd_kernel<<<nblocks, kThreads, 0, (cudaStream_t)stream>>>(
+        C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
+        linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
+        radius_clip, nullptr, offsets, camera_ids, gaussian_ids, radii, means2d, depths, conics,
+        compensations, pix_vels);
+    return check_launch("projection_packed_fill");
+}
+
+extern "C" int splatad_projection_packed_bwd(
+    uint32_t C, uint32_t N, uint32_t nnz, const float *means, const float *covars,
+    const float *quats, const float *scales, const float *velocities, const float *viewmats,
+    const float *Ks, int32_t image_width, int32_t image_height, const float *linear_velocity,
+    const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
+    const int64_t *camera_ids, const int64_t *gaussian_ids, const float *conics,
+    const float *compensations, const float *v_means2d, const float *v_depths,
+    const float *v_conics, const float *v_compensations, const float *v_pix_vels,
+    int32_t sparse_grad, float *v_means, float *v_covars, float *v_quats, float *v_scales,
+    float *v_viewmats, float *v_velocities, void *stream) {
+    SPL_REQUIRE(means && viewmats && Ks, SPLATAD_ERR_BAD_ARG, "projection_packed_bwd: null input");
+    SPL_REQUIRE(covars || (quats && scales), SPLATAD_ERR_BAD_ARG,
+                "projection_packed_bwd: covars or (quats, scales) required");
+    SPL_REQUIRE(!v_compensations || compensations, SPLATAD_ERR_BAD_ARG,
+                "projection_packed_bwd: v_compensations given without compensations");
+    if (nnz == 0) return SPLATAD_OK;
+    SPL_REQUIRE(camera_ids && gaussian_ids && conics && v_means2d && v_depths && v_conics &&
+                    v_pix_vels,
+                SPLATAD_ERR_BAD_ARG, "projection_packed_bwd: null input");
+    projection_packed_bwd_kernel<<<div_up(nnz, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+        C, N, nnz, means, covars, quats, scales, velocities, viewmats, Ks, image_width,
+        image_height, linear_velocity, angular_velocity, rolling_shutter_time, eps2d, camera_ids,
+        gaussian_ids, conics, compensations, v_means2d, v_depths, v_conics, v_compensations,
+        v_pix_vels, sparse_grad, v_means, v_covars, v_quats, v_scales, v_viewmats, v_velocities);
+    return check_launch("projection_packed_bwd");
+}

@@ -1,0 +1,878 @@
+"""Op-level API of the render hot path: same function names, argument order, defaults, return
+tuples and gradient slots as ``gsplat/cuda/_wrapper.py`` of the reference, implemented on top
+of the C-ABI CUDA library (``include/splatad_b200.h``).
+
+Reference functions mirrored here (file:line in carlinds/splatad):
+  spherical_harmonics            gsplat/cuda/_wrapper.py:17-43    (_SphericalHarmonics 2321-2351)
+  fully_fused_projection         gsplat/cuda/_wrapper.py:230-387  (_FullyFusedProjection 1495-1640,
+                                                                   _FullyFusedProjectionPacked 2107-2319)
+  fully_fused_lidar_projection   gsplat/cuda/_wrapper.py:390-530  (_FullyFusedLidarProjection 1642-1794)
+  isect_tiles                    gsplat/cuda/_wrapper.py:532-603
+  isect_lidar_tiles              gsplat/cuda/_wrapper.py:605-676
+  isect_offset_encode            gsplat/cuda/_wrapper.py:679-696
+  rasterize_to_pixels            gsplat/cuda/_wrapper.py:811-949  (_RasterizeToPixels 1796-1930)
+  rasterize_to_points            gsplat/cuda/_wrapper.py:951-1111 (_RasterizeToPoints 1932-2105)
+
+Differences that are visible to a caller:
+  * entries of culled (sensor, Gaussian) pairs are zero instead of uninitialised memory;
+  * the fused projection backward can return the gradient of ``velocities`` (the reference
+    computes it and throws it away); off by default, see ``velocity_grads``.
+"""
+
+from __future__ import annotations
+
+import contextlib
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _lib
+
+_RETURN_VELOCITY_GRADS = False
+
+
+@contextlib.contextmanager
+def velocity_grads(enabled: bool = True):
+    """Within this context the fused projections also return d(loss)/d(velocities).
+
+    The reference's fused backward kernels compute this gradient into a local variable and drop
+    it (gsplat/cuda/csrc/projection.cu:874-877, 2538-2541), and its autograd functions return
+    ``None`` for ``velocities``; that stays the default here.
+    """
+    global _RETURN_VELOCITY_GRADS
+    prev = _RETURN_VELOCITY_GRADS
+    _RETURN_VELOCITY_GRADS = enabled
+    try:
+        yield
+    finally:
+        _RETURN_VELOCITY_GRADS = prev
+
+
+def _f(t: Optional[Tensor]) -> Optional[Tensor]:
+    if t is None:
+        return None
+    if t.dtype != torch.float32:
+        t = t.float()
+    return t.contiguous()
+
+
+def _call(name: str, *args) -> None:
+    _lib.check(getattr(_lib.load(), name)(*args))
+
+
+# =============================================================================================
+# Spherical harmonics
+# =============================================================================================
+def spherical_harmonics(
+    degrees_to_use: int,
+    dirs: Tensor,  # [..., 3]
+    coeffs: Tensor,  # [..., K, 3]
+    masks: Optional[Tensor] = None,
+) -> Tensor:
+    """Computes spherical harmonics colours. Returns [..., 3]."""
+    assert (degrees_to_use + 1) ** 2 <= coeffs.shape[-2], coeffs.shape
+    assert dirs.shape[:-1] == coeffs.shape[:-2], (dirs.shape, coeffs.shape)
+    assert dirs.shape[-1] == 3, dirs.shape
+    assert coeffs.shape[-1] == 3, coeffs.shape
+    if masks is not None:
+        assert masks.shape == dirs.shape[:-1], masks.shape
+        masks = masks.contiguous()
+    return _SphericalHarmonics.apply(degrees_to_use, dirs.contiguous(), coeffs.contiguous(), masks)
+
+
+class _SphericalHarmonics(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, sh_degree: int, dirs: Tensor, coeffs: Tensor, masks: Optional[Tensor]) -> Tensor:
+        dirs = _f(dirs)
+        coeffs = _f(coeffs)
+        if masks is not None:
+            masks = masks.to(torch.bool).contiguous()
+        n = dirs.numel() // 3
+        K = coeffs.shape[-2]
+        colors = torch.empty_like(dirs)
+        _call(
+            "splatad_sh_fwd", n, K, sh_degree, _lib.ptr(dirs), _lib.ptr(coeffs), _lib.ptr(masks),
+            _lib.ptr(colors), _lib.stream_ptr(dirs.device),
+        )
+        ctx.save_for_backward(dirs, coeffs, masks)
+        ctx.sh_degree = sh_degree
+        return colors
+
+    @staticmethod
+    def backward(ctx, v_colors: Tensor):
+        dirs, coeffs, masks = ctx.saved_tensors
+        n = dirs.numel() // 3
+        K = coeffs.shape[-2]
+        compute_v_dirs = ctx.needs_input_grad[1]
+        v_coeffs = torch.empty_like(coeffs)
+        v_dirs = torch.empty_like(dirs) if compute_v_dirs else None
+        _call(
+            "splatad_sh_bwd", n, K, ctx.sh_degree, _lib.ptr(dirs), _lib.ptr(coeffs), _lib.ptr(masks),
+            _lib.ptr(_f(v_colors)), _lib.ptr(v_coeffs), _lib.ptr(v_dirs), _lib.stream_ptr(dirs.device),
+        )
+        return None, v_dirs, v_coeffs, None
+
+
+# =============================================================================================
+# Projection
+# =============================================================================================
+def fully_fused_projection(
+    means: Tensor,  # [N, 3]
+    covars: Optional[Tensor],  # [N, 6] or None
+    quats: Optional[Tensor],  # [N, 4] or None
+    scales: Optional[Tensor],  # [N, 3] or None
+    velocities: Optional[Tensor],  # [N, 3] or None
+    viewmats: Tensor,  # [C, 4, 4]
+    Ks: Tensor,  # [C, 3, 3]
+    width: int,
+    height: int,
+    linear_velocity: Tensor,  # [C, 3]
+    angular_velocity: Tensor,  # [C, 3]
+    rolling_shutter_time: Tensor,  # [C]
+    eps2d: float = 0.3,
+    near_plane: float = 0.01,
+    far_plane: float = 1e10,
+    radius_clip: float = 0.0,
+    packed: bool = False,
+    sparse_grad: bool = False,
+    calc_compensations: bool = False,
+):
+    """Projects Gaussians to a batch of pinhole cameras (with rolling-shutter velocities).
+
+    packed=False returns (radii [C,N,2] int32, means2d, depths, conics, compensations, pix_vels);
+    packed=True returns (camera_ids, gaussian_ids, radii [nnz,2], means2d, depths, conics,
+    compensations, pix_vels) with rows ordered camera-major, Gaussian-minor.
+    """
+    C = viewmats.size(0)
+    N = means.size(0)
+    assert means.size() == (N, 3), means.size()
+    assert viewmats.size() == (C, 4, 4), viewmats.size()
+    assert Ks.size() == (C, 3, 3), Ks.size()
+    assert linear_velocity.size() == (C, 3), linear_velocity.size()
+    assert angular_velocity.size() == (C, 3), angular_velocity.size()
+    assert rolling_shutter_time.size() == (C,), rolling_shutter_time.size()
+    means = means.contiguous()
+    if covars is not None:
+        assert covars.size() == (N, 6), covars.size()
+        covars = covars.contiguous()
+    else:
+        assert quats is not None, "covars or quats is required"
+        assert scales is not None, "covars or scales is required"
+        assert quats.size() == (N, 4), quats.size()
+        assert scales.size() == (N, 3), scales.size()
+        quats = quats.contiguous()
+        scales = scales.contiguous()
+    if velocities is not None:
+        assert velocities.size() == (N, 3), velocities.size()
+        velocities = velocities.contiguous()
+    if sparse_grad:
+        assert packed, "sparse_grad is only supported when packed is True"
+    viewmats = viewmats.contiguous()
+    Ks = Ks.contiguous()
+    if packed:
+        return _FullyFusedProjectionPacked.apply(
+            means, covars, quats, scales, velocities, viewmats, Ks, width, height, linear_velocity,
+            angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane, radius_clip,
+            sparse_grad, calc_compensations,
+        )
+    return _FullyFusedProjection.apply(
+        means, covars, quats, scales, velocities, viewmats, Ks, width, height, linear_velocity,
+        angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane, radius_clip,
+        calc_compensations,
+    )
+
+
+def fully_fused_lidar_projection(
+    means: Tensor,  # [N, 3]
+    covars: Optional[Tensor],  # [N, 6] or None
+    quats: Optional[Tensor],  # [N, 4] or None
+    scales: Optional[Tensor],  # [N, 3] or None
+    velocities: Optional[Tensor],  # [N, 3] or None
+    viewmats: Tensor,  # [C, 4, 4]
+    linear_velocity: Tensor,  # [C, 3]
+    angular_velocity: Tensor,  # [C, 3]
+    rolling_shutter_time: Tensor,  # [C]
+    min_elevation: float = -45,
+    max_elevation: float = 45,
+    min_azimuth: float = -180,
+    max_azimuth: float = 180,
+    eps2d: float = 0.01,
+    near_plane: float = 0.01,
+    far_plane: float = 1e10,
+    radius_clip: float = 0.0,
+    packed: bool = False,
+    sparse_grad: bool = False,
+    calc_compensations: bool = False,
+):
+    """Projects Gaussians to a batch of spherical lidars (azimuth / elevation in degrees, range).
+
+    Returns (radii [C,N,2] float degrees, means2d, depths (range), conics, compensations,
+    pix_vels [C,N,3], depth_compensations [C,N,2]).
+    """
+    C = viewmats.size(0)
+    N = means.size(0)
+    assert means.size() == (N, 3), means.size()
+    assert viewmats.size() == (C, 4, 4), viewmats.size()
+    means = means.contiguous()
+    if covars is not None:
+        assert covars.size() == (N, 6), covars.size()
+        covars = covars.contiguous()
+    else:
+        assert quats is not None, "covars or quats is required"
+        assert scales is not None, "covars or scales is required"
+        assert quats.size() == (N, 4), quats.size()
+        assert scales.size() == (N, 3), scales.size()
+        quats = quats.contiguous()
+        scales = scales.contiguous()
+    if velocities is not None:
+        assert velocities.size() == (N, 3), velocities.size()
+        velocities = velocities.contiguous()
+    if sparse_grad:
+        assert packed, "sparse_grad is only supported when packed is True"
+    viewmats = viewmats.contiguous()
+    if packed:
+        raise NotImplementedError("FullyFusedLidarProjectionPacked is not implemented yet")
+    return _FullyFusedLidarProjection.apply(
+        means, covars, quats, scales, velocities, viewmats, min_elevation, max_elevation,
+        min_azimuth, max_azimuth, linear_velocity, angular_velocity, rolling_shutter_time, eps2d,
+        near_plane, far_plane, radius_clip, calc_compensations,
+    )
+
+
+def _proj_inputs(means, covars, quats, scales, velocities, viewmats, lin, ang, rs):
+    return (_f(means), _f(covars), _f(quats), _f(scales), _f(velocities), _f(viewmats), _f(lin),
+            _f(ang), _f(rs))
+
+
+class _FullyFusedProjection(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, means, covars, quats, scales, velocities, viewmats, Ks, width, height,
+                linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane,
+                far_plane, radius_clip, calc_compensations):
+        means, covars, quats, scales, velocities, viewmats, lin, ang, rs = _proj_inputs(
+            means, covars, quats, scales, velocities, viewmats, linear_velocity, angular_velocity,
+            rolling_shutter_time)
+        Ks = _f(Ks)
+        C, N = viewmats.shape[0], means.shape[0]
+        dev = means.device
+        radii = torch.empty((C, N, 2), dtype=torch.int32, device=dev)
+        means2d = torch.empty((C, N, 2), dtype=torch.float32, device=dev)
+        depths = torch.empty((C, N), dtype=torch.float32, device=dev)
+        conics = torch.empty((C, N, 3), dtype=torch.float32, device=dev)
+        pix_vels = torch.empty((C, N, 2), dtype=torch.float32, device=dev)
+        compensations = torch.empty((C, N), dtype=torch.float32, device=dev) if calc_compensations else None
+        _call(
+            "splatad_projection_fwd", C, N, _lib.ptr(means), _lib.ptr(covars), _lib.ptr(quats),
+            _lib.ptr(scales), _lib.ptr(velocities), _lib.ptr(viewmats), _lib.ptr(Ks), width, height,
+            _lib.ptr(lin), _lib.ptr(ang), _lib.ptr(rs), eps2d, near_plane, far_plane, radius_clip,
+            _lib.ptr(radii), _lib.ptr(means2d), _lib.ptr(depths), _lib.ptr(conics),
+            _lib.ptr(compensations), _lib.ptr(pix_vels), _lib.stream_ptr(dev),
+        )
+        ctx.save_for_backward(means, covars, quats, scales, velocities, viewmats, Ks, lin, ang, rs,
+                              radii, conics, compensations)
+        ctx.width, ctx.height, ctx.eps2d = width, height, eps2d
+        ctx.want_vel = _RETURN_VELOCITY_GRADS
+        ctx.mark_non_differentiable(radii)
+        return radii, means2d, depths, conics, compensations, pix_vels
+
+    @staticmethod
+    def backward(ctx, v_radii, v_means2d, v_depths, v_conics, v_compensations, v_pix_vels):
+        (means, covars, quats, scales, velocities, viewmats, Ks, lin, ang, rs, radii, conics,
+         compensations) = ctx.saved_tensors
+        C, N = viewmats.shape[0], means.shape[0]
+        dev = means.device
+        v_means = torch.empty_like(means)
+        v_covars = torch.empty_like(covars) if covars is not None else None
+        v_quats = torch.empty_like(quats) if covars is None else None
+        v_scales = torch.empty_like(scales) if covars is None else None
+        v_viewmats = torch.zeros_like(viewmats) if ctx.needs_input_grad[5] else None
+        want_vel = ctx.want_vel and velocities is not None and ctx.needs_input_grad[4]
+        v_vel = torch.empty_like(velocities) if want_vel else None
+        _call(
+            "splatad_projection_bwd", C, N, _lib.ptr(means), _lib.ptr(covars), _lib.ptr(quats),
+            _lib.ptr(scales), _lib.ptr(velocities), _lib.ptr(viewmats), _lib.ptr(Ks), ctx.width,
+            ctx.height, _lib.ptr(lin), _lib.ptr(ang), _lib.ptr(rs), ctx.eps2d, _lib.ptr(radii),
+            _lib.ptr(conics), _lib.ptr(compensations), _lib.ptr(_f(v_means2d)), _lib.ptr(_f(v_depths)),
+            _lib.ptr(_f(v_conics)),
+            _lib.ptr(_f(v_compensations)) if compensations is not None else None,
+            _lib.ptr(_f(v_pix_vels)), _lib.ptr(v_means), _lib.ptr(v_covars), _lib.ptr(v_quats),
+            _lib.ptr(v_scales), _lib.ptr(v_viewmats), _lib.ptr(v_vel), _lib.stream_ptr(dev),
+        )
+        if not ctx.needs_input_grad[0]:
+            v_means = None
+        if not ctx.needs_input_grad[1]:
+            v_covars = None
+        if not ctx.needs_input_grad[2]:
+            v_quats = None
+        if not ctx.needs_input_grad[3]:
+            v_scales = None
+        return (v_means, v_covars, v_quats, v_scales, v_vel, v_viewmats) + (None,) * 11
+
+
+class _FullyFusedLidarProjection(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, means, covars, quats, scales, velocities, viewmats, min_elevation,
+                max_elevation, min_azimuth, max_azimuth, linear_velocity, angular_velocity,
+                rolling_shutter_time, eps2d, near_plane, far_plane, radius_clip, calc_compensations):
+        means, covars, quats, scales, velocities, viewmats, lin, ang, rs = _proj_inputs(
+            means, covars, quats, scales, velocities, viewmats, linear_velocity, angular_velocity,
+            rolling_shutter_time)
+        C, N = viewmats.shape[0], means.shape[0]
+        dev = means.device
+        f32 = dict(dtype=torch.float32, device=dev)
+        radii = torch.empty((C, N, 2), **f32)
+        means2d = torch.empty((C, N, 2), **f32)
+        depths = torch.empty((C, N), **f32)
+        conics = torch.empty((C, N, 3), **f32)
+        pix_vels = torch.empty((C, N, 3), **f32)
+        depth_comps = torch.empty((C, N, 2), **f32)
+        compensations = torch.empty((C, N), **f32) if calc_compensations else None
+        _call(
+            "splatad_lidar_projection_fwd", C, N, _lib.ptr(means), _lib.ptr(covars), _lib.ptr(quats),
+            _lib.ptr(scales), _lib.ptr(velocities), _lib.ptr(viewmats), min_elevation, max_elevation,
+            min_azimuth, max_azimuth, _lib.ptr(lin), _lib.ptr(ang), _lib.ptr(rs), eps2d, near_plane,
+            far_plane, radius_clip, _lib.ptr(radii), _lib.ptr(means2d), _lib.ptr(depths),
+            _lib.ptr(conics), _lib.ptr(compensations), _lib.ptr(pix_vels), _lib.ptr(depth_comps),
+            _lib.stream_ptr(dev),
+        )
+        ctx.save_for_backward(means, covars, quats, scales, velocities, viewmats, lin, ang, rs, radii,
+                              conics, compensations)
+        ctx.eps2d = eps2d
+        ctx.want_vel = _RETURN_VELOCITY_GRADS
+        ctx.mark_non_differentiable(radii)
+        return radii, means2d, depths, conics, compensations, pix_vels, depth_comps
+
+    @staticmethod
+    def backward(ctx, v_radii, v_means2d, v_depths, v_conics, v_compensations, v_pix_vels,
+                 v_depth_comps):
+        (means, covars, quats, scales, velocities, viewmats, lin, ang, rs, radii, conics,
+         compensations) = ctx.saved_tensors
+        C, N = viewmats.shape[0], means.shape[0]
+        dev = means.device
+        v_means = torch.empty_like(means)
+        v_covars = torch.empty_like(covars) if covars is not None else None
+        v_quats = torch.empty_like(quats) if covars is None else None
+        v_scales = torch.empty_like(scales) if covars is None else None
+        v_viewmats = torch.zeros_like(viewmats) if ctx.needs_input_grad[5] else None
+        want_vel = ctx.want_vel and velocities is not None and ctx.needs_input_grad[4]
+        v_vel = torch.empty_like(velocities) if want_vel else None
+        _call(
+            "splatad_lidar_projection_bwd", C, N, _lib.ptr(means), _lib.ptr(covars), _lib.ptr(quats),
+            _lib.ptr(scales), _lib.ptr(velocities), _lib.ptr(viewmats), _lib.ptr(lin), _lib.ptr(ang),
+            _lib.ptr(rs), ctx.eps2d, _lib.ptr(radii), _lib.ptr(conics), _lib.ptr(compensations),
+            _lib.ptr(_f(v_means2d)), _lib.ptr(_f(v_depths)), _lib.ptr(_f(v_conics)),
+            _lib.ptr(_f(v_compensations)) if compensations is not None else None,
+            _lib.ptr(_f(v_pix_vels)), _lib.ptr(_f(v_depth_comps)), _lib.ptr(v_means),
+            _lib.ptr(v_covars), _lib.ptr(v_quats), _lib.ptr(v_scales), _lib.ptr(v_viewmats),
+            _lib.ptr(v_vel), _lib.stream_ptr(dev),
+        )
+        if not ctx.needs_input_grad[0]:
+            v_means = None
+        if not ctx.needs_input_grad[1]:
+            v_covars = None
+        if not ctx.needs_input_grad[2]:
+            v_quats = None
+        if not ctx.needs_input_grad[3]:
+            v_scales = None
+        return (v_means, v_covars, v_quats, v_scales, v_vel, v_viewmats) + (None,) * 12
+
+
+class _FullyFusedProjectionPacked(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, means, covars, quats, scales, velocities, viewmats, Ks, width, height,
+                linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane,
+                far_plane, radius_clip, sparse_grad, calc_compensations):
+        means, covars, quats, scales, velocities, viewmats, lin, ang, rs = _proj_inputs(
+            means, covars, quats, scales, velocities, viewmats, linear_velocity, angular_velocity,
+            rolling_shutter_time)
+        Ks = _f(Ks)
+        C, N = viewmats.shape[0], means.shape[0]
+        dev = means.device
+        lib = _lib.load()
+        indptr = torch.zeros(C + 1, dtype=torch.int32, device=dev)
+        nnz = 0
+        ws = None
+        if C > 0 and N > 0:
+            ws_bytes = lib.splatad_projection_packed_workspace_bytes(C, N)
+            ws = _lib.workspace("packed", ws_bytes, dev)
+            nnz_dev = torch.zeros(1, dtype=torch.int64, device=dev)
+            common = (
+                C, N, _lib.ptr(means), _lib.ptr(covars), _lib.ptr(quats), _lib.ptr(scales),
+                _lib.ptr(velocities), _lib.ptr(viewmats), _lib.ptr(Ks), width, height, _lib.ptr(lin),
+                _lib.ptr(ang), _lib.ptr(rs), eps2d, near_plane, far_plane, radius_clip,
+            )
+            _call("splatad_projection_packed_count", *common, _lib.ptr(ws), ws.numel(),
+                  _lib.ptr(indptr), _lib.ptr(nnz_dev), _lib.stream_ptr(dev))
+            nnz = int(nnz_dev.item())
+        camera_ids = torch.empty(nnz, dtype=torch.int64, device=dev)
+        gaussian_ids = torch.empty(nnz, dtype=torch.int64, device=dev)
+        radii = torch.empty((nnz, 2), dtype=torch.int32, device=dev)
+        means2d = torch.empty((nnz, 2), dtype=torch.float32, device=dev)
+        depths = torch.empty(nnz, dtype=torch.float32, device=dev)
+        conics = torch.empty((nnz, 3), dtype=torch.float32, device=dev)
+        pix_vels = torch.empty((nnz, 2), dtype=torch.float32, device=dev)
+        compensations = torch.empty(nnz, dtype=torch.float32, device=dev) if calc_compensations else None
+        if nnz > 0:
+            _call("splatad_projection_packed_fill", *common, _lib.ptr(ws), _lib.ptr(camera_ids),
+                  _lib.ptr(gaussian_ids), _lib.ptr(radii), _lib.ptr(means2d), _lib.ptr(depths),
+                  _lib.ptr(conics), _lib.ptr(compensations), _lib.ptr(pix_vels), _lib.stream_ptr(dev))
+        ctx.save_for_backward(camera_ids, gaussian_ids, means, covars, quats, scales, velocities,
+                              viewmats, Ks, lin, ang, rs, conics, compensations)
+        ctx.width, ctx.height, ctx.eps2d, ctx.sparse_grad = width, height, eps2d, sparse_grad
+        ctx.want_vel = _RETURN_VELOCITY_GRADS
+        ctx.mark_non_differentiable(camera_ids, gaussian_ids, radii)
+        return camera_ids, gaussian_ids, radii, means2d, depths, conics, compensations, pix_vels
+
+    @staticmethod
+    def backward(ctx, v_camera_ids, v_gaussian_ids, v_radii, v_means2d, v_depths, v_conics,
+                 v_compensations, v_pix_vels):
+        (camera_ids, gaussian_ids, means, covars, quats, scales, velocities, viewmats, Ks, lin, ang,
+         rs, conics, compensations) = ctx.saved_tensors
+        C, N, nnz = viewmats.shape[0], means.shape[0], camera_ids.shape[0]
+        dev = means.device
+        sparse = ctx.sparse_grad
+        rows = nnz if sparse else N
+
+        def grad_like(t):
+            if t is None:
+                return None
+            shape = (rows,) + tuple(t.shape[1:])
+            return torch.zeros(shape, dtype=torch.float32, device=dev)
+
+        v_means = grad_like(means)
+        v_covars = grad_like(covars)
+        v_quats = grad_like(quats) if covars is None else None
+        v_scales = grad_like(scales) if covars is None else None
+        v_viewmats = torch.zeros_like(viewmats) if ctx.needs_input_grad[5] else None
+        want_vel = ctx.want_vel and velocities is not None and ctx.needs_input_grad[4] and not sparse
+        v_vel = torch.zeros_like(velocities) if want_vel else None
+        _call(
+            "splatad_projection_packed_bwd", C, N, nnz, _lib.ptr(means), _lib.ptr(covars),
+            _lib.ptr(quats), _lib.ptr(scales), _lib.ptr(velocities), _lib.ptr(viewmats), _lib.ptr(Ks),
+            ctx.width, ctx.height, _lib.ptr(lin), _lib.ptr(ang), _lib.ptr(rs), ctx.eps2d,
+            _lib.ptr(camera_ids), _lib.ptr(gaussian_ids), _lib.ptr(conics), _lib.ptr(compensations),
+            _lib.ptr(_f(v_means2d)), _lib.ptr(_f(v_depths)), _lib.ptr(_f(v_conics)),
+            _lib.ptr(_f(v_compensations)) if compensations is not None else None,
+            _lib.ptr(_f(v_pix_vels)), int(sparse), _lib.ptr(v_means), _lib.ptr(v_covars),
+            _lib.ptr(v_quats), _lib.ptr(v_scales), _lib.ptr(v_viewmats), _lib.ptr(v_vel),
+            _lib.stream_ptr(dev),
+        )
+
+        def finish(v, ref, needed):
+            if not needed or v is None:
+                return None
+            if sparse:
+                return torch.sparse_coo_tensor(indices=gaussian_ids[None], values=v, size=ref.size())
+            return v
+
+        v_means = finish(v_means, means, ctx.needs_input_grad[0])
+        v_covars = finish(v_covars, covars, ctx.needs_input_grad[1]) if covars is not None else None
+        v_quats = finish(v_quats, quats, ctx.needs_input_grad[2]) if covars is None else None
+        v_scales = finish(v_scales, scales, ctx.needs_input_grad[3]) if covars is None else None
+        return (v_means, v_covars, v_quats, v_scales, v_vel, v_viewmats) + (None,) * 12
+
+
+# =============================================================================================
+# Tile intersection
+# =============================================================================================
+def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, gaussian_ids, sort,
+                  geom_args):
+    """Shared two-phase driver of both isect ops: plan -> read n_isects on the host -> fill.
+
+    ``kind`` ("tiles" or "lidar_tiles") is spliced into the C symbol name.
+    """
+    if packed:
+        nnz = means2d.size(0)
+        assert means2d.shape == (nnz, 2), means2d.size()
+        assert radii.shape == (nnz, 2), radii.size()
+        assert depths.shape == (nnz,), depths.size()
+        assert camera_ids is not None, "camera_ids is required if packed is True"
+        assert gaussian_ids is not None, "gaussian_ids is required if packed is True"
+        assert n_cameras is not None, "n_cameras is required if packed is True"
+        camera_ids = camera_ids.to(torch.int64).contiguous()
+        C, N, total = n_cameras, 0, nnz
+    else:
+        C, N, _ = means2d.shape
+        assert means2d.shape == (C, N, 2), means2d.size()
+        assert radii.shape == (C, N, 2), radii.size()
+        assert depths.shape == (C, N), depths.size()
+        camera_ids = None
+        total = C * N
+    dev = means2d.device
+    means2d = _f(means2d)
+    depths = _f(depths)
+    if kind == "tiles":
+        radii = radii.to(torch.int32).contiguous()
+    else:
+        radii = _f(radii)
+    lib = _lib.load()
+    tiles_per_gauss = torch.empty(depths.shape, dtype=torch.int32, device=dev)
+    if total == 0:
+        return (tiles_per_gauss, torch.empty(0, dtype=torch.int64, device=dev),
+                torch.empty(0, dtype=torch.int32, device=dev))
+    plan_bytes = lib.splatad_isect_plan_workspace_bytes(total)
+    plan_ws = _lib.workspace("isect_plan", plan_bytes, dev)
+    host = _lib.pinned_counts("isect", dev)
+    stream = _lib.stream_ptr(dev)
+    head = (C, N, total, _lib.ptr(means2d), _lib.ptr(radii), _lib.ptr(depths), _lib.ptr(camera_ids))
+    _call(f"splatad_isect_{kind}_plan", *head, *geom_args, int(bool(sort)), _lib.ptr(tiles_per_gauss),
+          _lib.ptr(plan_ws), plan_ws.numel(), host.data_ptr(), stream)
+    torch.cuda.current_stream(dev).synchronize()
+    n_isects, status = int(host[0]), int(host[2])
+    if status & 2:
+        raise RuntimeError(f"isect: {n_isects} intersections do not fit int32 flatten ids / offsets")
+    isect_ids = torch.empty(n_isects, dtype=torch.int64, device=dev)
+    flatten_ids = torch.empty(n_isects, dtype=torch.int32, device=dev)
+    if n_isects > 0:
+        fill_ws = None
+        fill_bytes = 0
+        if sort:
+            fill_bytes = lib.splatad_isect_fill_workspace_bytes(n_isects)
+            fill_ws = _lib.workspace("isect_fill", fill_bytes, dev)
+        _call(f"splatad_isect_{kind}_fill", *head, *geom_args, int(bool(sort)),
+              _lib.ptr(tiles_per_gauss), _lib.ptr(plan_ws), _lib.ptr(fill_ws),
+              fill_ws.numel() if fill_ws is not None else 0, n_isects, _lib.ptr(isect_ids),
+              _lib.ptr(flatten_ids), None, stream)
+    return tiles_per_gauss, isect_ids, flatten_ids
+
+
+@torch.no_grad()
+def isect_tiles(
+    means2d: Tensor,  # [C, N, 2] or [nnz, 2]
+    radii: Tensor,  # [C, N, 2] or [nnz, 2]
+    depths: Tensor,  # [C, N] or [nnz]
+    tile_size: int,
+    tile_width: int,
+    tile_height: int,
+    sort: bool = True,
+    packed: bool = False,
+    n_cameras: Optional[int] = None,
+    camera_ids: Optional[Tensor] = None,
+    gaussian_ids: Optional[Tensor] = None,
+) -> Tuple[Tensor, Tensor, Tensor]:
+    """Maps projected Gaussians to the camera tiles they touch.
+
+    Returns (tiles_per_gauss int32, isect_ids int64 [n_isects] = sensor | tile | depth bits,
+    flatten_ids int32 [n_isects]), sorted by isect id (ties in flatten order) when ``sort``.
+    """
+    return _isect_common("tiles", means2d, radii, depths, packed, n_cameras, camera_ids, gaussian_ids,
+                         sort, (int(tile_size), int(tile_width), int(tile_height)))
+
+
+@torch.no_grad()
+def isect_lidar_tiles(
+    means2d: Tensor,  # [C, N, 2] or [nnz, 2]
+    radii: Tensor,  # [C, N, 2] or [nnz, 2]
+    depths: Tensor,  # [C, N] or [nnz]
+    elev_boundaries: Tensor,
+    tile_azim_resolution: float,
+    min_azim: float,
+    sort: bool = True,
+    packed: bool = False,
+    n_cameras: Optional[int] = None,
+    camera_ids: Optional[Tensor] = None,
+    gaussian_ids: Optional[Tensor] = None,
+) -> Tuple[Tensor, Tensor, Tensor]:
+    """Maps projected Gaussians to lidar tiles (uniform azimuth tiles with wrap-around, elevation
+    tiles given by ``elev_boundaries``). Same returns as :func:`isect_tiles`."""
+    eb = _f(elev_boundaries)
+    return _isect_common("lidar_tiles", means2d, radii, depths, packed, n_cameras, camera_ids,
+                         gaussian_ids, sort,
+                         (_lib.ptr(eb), int(eb.numel()), float(tile_azim_resolution), float(min_azim)))
+
+
+@torch.no_grad()
+def isect_offset_encode(isect_ids: Tensor, n_cameras: int, tile_width: int, tile_height: int) -> Tensor:
+    """Encodes sorted intersection ids to per-tile start offsets [C, tile_height, tile_width]."""
+    isect_ids = isect_ids.contiguous()
+    dev = isect_ids.device
+    offsets = torch.empty((n_cameras, tile_height, tile_width), dtype=torch.int32, device=dev)
+    if offsets.numel() == 0:
+        return offsets
+    _call("splatad_isect_offset_encode", _lib.ptr(isect_ids) if isect_ids.numel() else None,
+          isect_ids.numel(), n_cameras, tile_width, tile_height, _lib.ptr(offsets), _lib.stream_ptr(dev))
+    return offsets
+
+
+# =============================================================================================
+# Compositing
+# =============================================================================================
+def rasterize_to_pixels(
+    means2d: Tensor,  # [C, N, 2] or [nnz, 2]
+    conics: Tensor,  # [C, N, 3] or [nnz, 3]
+    colors: Tensor,  # [C, N, channels] or [nnz, channels]
+    opacities: Tensor,  # [C, N] or [nnz]
+    pix_vels: Tensor,  # [C, N, 2] or [nnz, 2]
+    image_width: int,
+    image_height: int,
+    tile_size: int,
+    isect_offsets: Tensor,  # [C, tile_height, tile_width]
+    flatten_ids: Tensor,  # [n_isects]
+    rolling_shutter_time: Optional[Tensor] = None,  # [C]
+    backgrounds: Optional[Tensor] = None,  # [C, channels]
+    packed: bool = False,
+    absgrad: bool = False,
+) -> Tuple[Tensor, Tensor]:
+    """Rasterizes Gaussians to pixels. Returns (colors [C,H,W,channels], alphas [C,H,W,1])."""
+    C = isect_offsets.size(0)
+    device = means2d.device
+    if packed:
+        nnz = means2d.size(0)
+        assert means2d.shape == (nnz, 2), means2d.shape
+        assert conics.shape == (nnz, 3), conics.shape
+        assert colors.shape[0] == nnz, colors.shape
+        assert opacities.shape == (nnz,), opacities.shape
+        assert pix_vels.shape == (nnz, 2), pix_vels.shape
+    else:
+        N = means2d.size(1)
+        assert means2d.shape == (C, N, 2), means2d.shape
+        assert conics.shape == (C, N, 3), conics.shape
+        assert colors.shape[:2] == (C, N), colors.shape
+        assert opacities.shape == (C, N), opacities.shape
+        assert pix_vels.shape == (C, N, 2), pix_vels.shape
+    if rolling_shutter_time is not None:
+        assert rolling_shutter_time.shape == (C,), rolling_shutter_time.shape
+    else:
+        rolling_shutter_time = torch.zeros(C, device=device)
+    if backgrounds is not None:
+        assert backgrounds.shape == (C, colors.shape[-1]), backgrounds.shape
+        backgrounds = backgrounds.contiguous()
+    channels = colors.shape[-1]
+    if channels > 513 or channels == 0:
+        raise ValueError(f"Unsupported number of color channels: {channels}")
+    tile_height, tile_width = isect_offsets.shape[1:3]
+    assert tile_height * tile_size >= image_height, f"Assert Failed: {tile_height} * {tile_size} >= {image_height}"
+    assert tile_width * tile_size >= image_width, f"Assert Failed: {tile_width} * {tile_size} >= {image_width}"
+
+    means2d_c = means2d.contiguous()
+    args = (conics.contiguous(), opacities.contiguous(), pix_vels.contiguous(),
+            rolling_shutter_time.contiguous())
+    tail = (image_width, image_height, tile_size, isect_offsets.contiguous(), flatten_ids.contiguous(),
+            absgrad)
+    if channels <= _lib.MAX_CHANNELS:
+        return _RasterizeToPixels.apply(means2d_c, args[0], colors.contiguous(), args[1], args[2],
+                                        args[3], backgrounds, *tail)
+    # more channels than one launch renders: chunks share geometry, alphas are identical
+    renders, alphas = [], None
+    for lo in range(0, channels, _lib.MAX_CHANNELS):
+        hi = min(lo + _lib.MAX_CHANNELS, channels)
+        bg = backgrounds[..., lo:hi].contiguous() if backgrounds is not None else None
+        r, a = _RasterizeToPixels.apply(means2d_c, args[0], colors[..., lo:hi].contiguous(), args[1],
+                                        args[2], args[3], bg, *tail)
+        renders.append(r)
+        alphas = a if alphas is None else alphas
+    return torch.cat(renders, dim=-1), alphas
+
+
+class _RasterizeToPixels(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, means2d, conics, colors, opacities, pix_vels, rolling_shutter_time, backgrounds,
+                width, height, tile_size, isect_offsets, flatten_ids, absgrad):
+        dev = means2d.device
+        assert means2d.dtype == torch.float32, means2d.dtype
+        C, tile_h, tile_w = isect_offsets.shape
+        channels = colors.shape[-1]
+        colors_f, conics_f, opac_f, vels_f = _f(colors), _f(conics), _f(opacities), _f(pix_vels)
+        rs = _f(rolling_shutter_time)
+        bg = _f(backgrounds)
+        render_colors = torch.empty((C, height, width, channels), dtype=torch.float32, device=dev)
+        render_alphas = torch.empty((C, height, width, 1), dtype=torch.float32, device=dev)
+        last_ids = torch.empty((C, height, width), dtype=torch.int32, device=dev)
+        n_isects = flatten_ids.numel()
+        _call(
+            "splatad_rasterize_to_pixels_fwd", C, n_isects, _lib.ptr(means2d), _lib.ptr(conics_f),
+            _lib.ptr(colors_f), channels, _lib.ptr(opac_f), _lib.ptr(vels_f), _lib.ptr(rs), _lib.ptr(bg),
+            width, height, tile_size, tile_w, tile_h, _lib.ptr(isect_offsets), _lib.ptr(flatten_ids),
+            _lib.ptr(render_colors), _lib.ptr(render_alphas), _lib.ptr(last_ids), _lib.stream_ptr(dev),
+        )
+        ctx.save_for_backward(means2d, conics_f, colors_f, opac_f, vels_f, rs, bg, isect_offsets,
+                              flatten_ids, render_alphas, last_ids)
+        ctx.width, ctx.height, ctx.tile_size, ctx.absgrad = width, height, tile_size, absgrad
+        return render_colors, render_alphas
+
+    @staticmethod
+    def backward(ctx, v_render_colors, v_render_alphas):
+        (means2d, conics, colors, opacities, pix_vels, rs, bg, isect_offsets, flatten_ids,
+         render_alphas, last_ids) = ctx.saved_tensors
+        dev = means2d.device
+        C, tile_h, tile_w = isect_offsets.shape
+        channels = colors.shape[-1]
+        v_render_colors = _f(v_render_colors)
+        v_render_alphas = _f(v_render_alphas)
+        v_means2d = torch.zeros_like(means2d, dtype=torch.float32)
+        v_conics = torch.zeros_like(conics)
+        v_colors = torch.zeros_like(colors)
+        v_opacities = torch.zeros_like(opacities)
+        v_pix_vels = torch.zeros_like(pix_vels)
+        v_abs = torch.zeros_like(v_means2d) if ctx.absgrad else None
+        _call(
+            "splatad_rasterize_to_pixels_bwd", C, flatten_ids.numel(), _lib.ptr(means2d),
+            _lib.ptr(conics), _lib.ptr(colors), channels, _lib.ptr(opacities), _lib.ptr(pix_vels),
+            _lib.ptr(rs), _lib.ptr(bg), ctx.width, ctx.height, ctx.tile_size, tile_w, tile_h,
+            _lib.ptr(isect_offsets), _lib.ptr(flatten_ids), _lib.ptr(render_alphas), _lib.ptr(last_ids),
+            _lib.ptr(v_render_colors), _lib.ptr(v_render_alphas), _lib.ptr(v_abs), _lib.ptr(v_means2d),
+            _lib.ptr(v_conics), _lib.ptr(v_colors), _lib.ptr(v_opacities), _lib.ptr(v_pix_vels),
+            _lib.stream_ptr(dev),
+        )
+        if ctx.absgrad:
+            means2d.absgrad = v_abs
+        v_backgrounds = None
+        if ctx.needs_input_grad[6]:
+            v_backgrounds = (v_render_colors * (1.0 - render_alphas).float()).sum(dim=(1, 2))
+        return (v_means2d, v_conics, v_colors, v_opacities, v_pix_vels, None, v_backgrounds, None,
+                None, None, None, None, None)
+
+
+def rasterize_to_points(
+    means2d: Tensor,  # [C, N, 2] or [nnz, 2]
+    conics: Tensor,  # [C, N, 3] or [nnz, 3]
+    lidar_features: Tensor,  # [C, N, channels] or [nnz, channels]
+    opacities: Tensor,  # [C, N] or [nnz]
+    pix_vels: Tensor,  # [C, N, 3] or [nnz, 3]
+    depth_compensations: Tensor,  # [C, N, 2] or [nnz, 2]
+    raster_pts: Tensor,  # [C, H, W, 4]
+    image_width: int,
+    image_height: int,
+    tile_width: int,
+    tile_height: int,
+    isect_offsets: Tensor,  # [C, tile_height, tile_width]
+    flatten_ids: Tensor,  # [n_isects]
+    compute_alpha_sum_until_points: bool,
+    compute_alpha_sum_until_points_threshold: float,
+    backgrounds: Optional[Tensor] = None,  # [C, channels]
+    packed: bool = False,
+    absgrad: bool = False,
+) -> Tuple[Tensor, Tensor, Optional[Tensor], Tensor]:
+    """Rasterizes Gaussians to lidar points; the last feature channel is the Gaussian's range.
+
+    Returns (features [C,H,W,channels], alphas [C,H,W,1], alpha_sum_until_points [C,H,W,1] or
+    None, median_depths [C,H,W,1]).
+    """
+    C = isect_offsets.size(0)
+    if packed:
+        nnz = means2d.size(0)
+        assert means2d.shape == (nnz, 2), means2d.shape
+        assert conics.shape == (nnz, 3), conics.shape
+        assert lidar_features.shape[0] == nnz, lidar_features.shape
+        assert opacities.shape == (nnz,), opacities.shape
+        assert pix_vels.shape == (nnz, 3), pix_vels.shape
+        assert depth_compensations.shape == (nnz, 2), depth_compensations.shape
+    else:
+        N = means2d.size(1)
+        assert means2d.shape == (C, N, 2), means2d.shape
+        assert conics.shape == (C, N, 3), conics.shape
+        assert lidar_features.shape[:2] == (C, N), lidar_features.shape
+        assert opacities.shape == (C, N), opacities.shape
+        assert pix_vels.shape == (C, N, 3), pix_vels.shape
+        assert depth_compensations.shape == (C, N, 2), depth_compensations.shape
+    if backgrounds is not None:
+        assert backgrounds.shape == (C, lidar_features.shape[-1]), backgrounds.shape
+        backgrounds = backgrounds.contiguous()
+    channels = lidar_features.shape[-1]
+    depth_channel_idx = channels - 1
+    if channels > 513 or channels == 0:
+        raise ValueError(f"Unsupported number of lidar_features channels: {channels}")
+    tile_grid_height, tile_grid_width = isect_offsets.shape[1:3]
+    assert tile_grid_height * tile_height >= image_height, (
+        f"Assert Failed: {tile_grid_height} * {tile_height} >= {image_height}")
+    assert tile_grid_width * tile_width >= image_width, (
+        f"Assert Failed: {tile_grid_width} * {tile_width} >= {image_width}")
+    assert raster_pts.shape == (C, image_height, image_width, 4), "raster_pts does not have the correct shape"
+
+    fixed = (means2d.contiguous(), conics.contiguous())
+    mid = (opacities.contiguous(), pix_vels.contiguous(), depth_compensations.contiguous())
+    tail = (raster_pts.contiguous(), image_width, image_height, tile_width, tile_height,
+            isect_offsets.contiguous(), flatten_ids.contiguous(), compute_alpha_sum_until_points,
+            compute_alpha_sum_until_points_threshold, absgrad)
+    if channels <= _lib.MAX_CHANNELS:
+        return _RasterizeToPoints.apply(*fixed, lidar_features.contiguous(), *mid, backgrounds, *tail,
+                                        depth_channel_idx)
+    # more channels than one launch renders: every chunk carries the range as its last channel
+    step = _lib.MAX_CHANNELS - 1
+    n_feat = channels - 1
+    depth = lidar_features[..., -1:]
+    outs, first = [], None
+    for lo in range(0, n_feat, step):
+        hi = min(lo + step, n_feat)
+        feats = torch.cat([lidar_features[..., lo:hi], depth], dim=-1).contiguous()
+        bg = None
+        if backgrounds is not None:
+            bg = torch.cat([backgrounds[..., lo:hi], backgrounds[..., -1:]], dim=-1).contiguous()
+        r, a, s, m = _RasterizeToPoints.apply(*fixed, feats, *mid, bg, *tail, feats.shape[-1] - 1)
+        if first is None:
+            first = (a, s, m)
+        outs.append(r if hi == n_feat else r[..., :-1])
+    return torch.cat(outs, dim=-1), first[0], first[1], first[2]
+
+
+class _RasterizeToPoints(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, means2d, conics, colors, opacities, pix_vels, depth_compensations, backgrounds,
+                raster_pts, width, height, tile_width, tile_height, isect_offsets, flatten_ids,
+                compute_alpha_sum_until_points, compute_alpha_sum_until_points_threshold, absgrad,
+                depth_channel_idx):
+        dev = means2d.device
+        assert means2d.dtype == torch.float32, means2d.dtype
+        C, grid_h, grid_w = isect_offsets.shape
+        channels = colors.shape[-1]
+        colors_f, conics_f, opac_f = _f(colors), _f(conics), _f(opacities)
+        vels_f, dc_f, pts_f, bg = _f(pix_vels), _f(depth_compensations), _f(raster_pts), _f(backgrounds)
+        f32 = dict(dtype=torch.float32, device=dev)
+        render_colors = torch.empty((C, height, width, channels), **f32)
+        render_alphas = torch.empty((C, height, width, 1), **f32)
+        median_depths = torch.empty((C, height, width, 1), **f32)
+        alpha_sum = torch.empty((C, height, width, 1), **f32) if compute_alpha_sum_until_points else None
+        last_ids = torch.empty((C, height, width), dtype=torch.int32, device=dev)
+        _call(
+            "splatad_rasterize_to_points_fwd", C, flatten_ids.numel(), _lib.ptr(means2d),
+            _lib.ptr(conics_f), _lib.ptr(colors_f), channels, _lib.ptr(opac_f), _lib.ptr(vels_f),
+            _lib.ptr(dc_f), _lib.ptr(bg), _lib.ptr(pts_f), width, height, tile_width, tile_height,
+            grid_w, grid_h, int(bool(compute_alpha_sum_until_points)),
+            float(compute_alpha_sum_until_points_threshold), _lib.ptr(isect_offsets),
+            _lib.ptr(flatten_ids), depth_channel_idx, _lib.ptr(render_colors), _lib.ptr(render_alphas),
+            _lib.ptr(alpha_sum), _lib.ptr(last_ids), _lib.ptr(median_depths), _lib.stream_ptr(dev),
+        )
+        ctx.save_for_backward(means2d, conics_f, colors_f, opac_f, vels_f, dc_f, bg, pts_f,
+                              isect_offsets, flatten_ids, render_alphas, last_ids)
+        ctx.meta = (width, height, tile_width, tile_height, absgrad,
+                    bool(compute_alpha_sum_until_points),
+                    float(compute_alpha_sum_until_points_threshold), depth_channel_idx)
+        ctx.mark_non_differentiable(median_depths)
+        return render_colors, render_alphas, alpha_sum, median_depths
+
+    @staticmethod
+    def backward(ctx, v_render_colors, v_render_alphas, v_alpha_sum, v_median_depths):
+        (means2d, conics, colors, opacities, pix_vels, depth_comps, bg, raster_pts, isect_offsets,
+         flatten_ids, render_alphas, last_ids) = ctx.saved_tensors
+        width, height, tile_width, tile_height, absgrad, compute_asum, thr, depth_idx = ctx.meta
+        dev = means2d.device
+        C, grid_h, grid_w = isect_offsets.shape
+        channels = colors.shape[-1]
+        v_render_colors = _f(v_render_colors)
+        v_render_alphas = _f(v_render_alphas)
+        v_asum = _f(v_alpha_sum) if (compute_asum and v_alpha_sum is not None) else None
+        v_means2d = torch.zeros_like(means2d, dtype=torch.float32)
+        v_conics = torch.zeros_like(conics)
+        v_colors = torch.zeros_like(colors)
+        v_opacities = torch.zeros_like(opacities)
+        v_pix_vels = torch.zeros_like(pix_vels)
+        v_depth_comps = torch.zeros_like(depth_comps)
+        v_abs = torch.zeros_like(v_means2d) if absgrad else None
+        _call(
+            "splatad_rasterize_to_points_bwd", C, flatten_ids.numel(), _lib.ptr(means2d),
+            _lib.ptr(conics), _lib.ptr(colors), channels, _lib.ptr(opacities), _lib.ptr(pix_vels),
+            _lib.ptr(depth_comps), _lib.ptr(bg), _lib.ptr(raster_pts), width, height, tile_width,
+            tile_height, grid_w, grid_h, int(compute_asum), thr, _lib.ptr(isect_offsets),
+            _lib.ptr(flatten_ids), depth_idx, _lib.ptr(render_alphas), _lib.ptr(last_ids),
+            _lib.ptr(v_render_colors), _lib.ptr(v_render_alphas), _lib.ptr(v_asum), _lib.ptr(v_abs),
+            _lib.ptr(v_means2d), _lib.ptr(v_conics), _lib.ptr(v_colors), _lib.ptr(v_opacities),
+            _lib.ptr(v_pix_vels), _lib.ptr(v_depth_comps), _lib.stream_ptr(dev),
+        )
+        if absgrad:
+            means2d.absgrad = v_abs
+        v_backgrounds = None
+        if ctx.needs_input_grad[6]:
+            v_backgrounds = (v_render_colors * (1.0 - render_alphas).float()).sum(dim=(1, 2))
+        return (v_means2d, v_conics, v_colors, v_opacities, v_pix_vels, v_depth_comps, v_backgrounds) + (
+            None,) * 11

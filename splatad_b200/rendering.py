@@ -1,0 +1,457 @@
+"""``rasterization()`` and ``lidar_rasterization()``: drop-in replacements for the two render
+entry points of the reference (gsplat/rendering.py:22-440 and 443-819) with the same
+signatures, return tuples and ``meta`` keys, running on the B200 CUDA library of this package.
+
+Both are orchestration only: project -> (spherical harmonics) -> tile intersection -> per-tile
+offsets -> compositing, with the channel chunking rules of the reference.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Tuple, Union
+
+import torch
+from torch import Tensor
+
+try:  # Python >= 3.8 has Literal in typing; keep the reference's import order of preference
+    from typing_extensions import Literal
+except ImportError:  # pragma: no cover
+    from typing import Literal
+
+from .ops import (
+    fully_fused_lidar_projection,
+    fully_fused_projection,
+    isect_lidar_tiles,
+    isect_offset_encode,
+    isect_tiles,
+    rasterize_to_pixels,
+    rasterize_to_points,
+    spherical_harmonics,
+)
+
+
+def rasterization(
+    means: Tensor,  # [N, 3]
+    quats: Tensor,  # [N, 4]
+    scales: Tensor,  # [N, 3]
+    opacities: Tensor,  # [N]
+    colors: Tensor,  # [(C,) N, D] or [(C,) N, K, 3]
+    velocities: Optional[Tensor],  # [N, 3]
+    viewmats: Tensor,  # [C, 4, 4]
+    Ks: Tensor,  # [C, 3, 3]
+    width: int,
+    height: int,
+    linear_velocity: Optional[Tensor] = None,  # [C, 3]
+    angular_velocity: Optional[Tensor] = None,  # [C, 3]
+    rolling_shutter_time: Optional[Tensor] = None,  # [C]
+    near_plane: float = 0.01,
+    far_plane: float = 1e10,
+    radius_clip: float = 0.0,
+    eps2d: float = 0.3,
+    sh_degree: Optional[int] = None,
+    packed: bool = True,
+    tile_size: int = 16,
+    backgrounds: Optional[Tensor] = None,
+    render_mode: Literal["RGB", "D", "ED", "RGB+D", "RGB+ED"] = "RGB",
+    sparse_grad: bool = False,
+    absgrad: bool = False,
+    rasterize_mode: Literal["classic", "antialiased"] = "classic",
+    channel_chunk: int = 32,
+) -> Tuple[Tensor, Tensor, Dict]:
+    """Rasterizes N 3-D Gaussians to C rolling-shutter pinhole cameras.
+
+    Arguments, defaults and behaviour are those of the reference function of the same name
+    (gsplat/rendering.py:22-440): ``colors`` is [(C,) N, D] post-activation values, or
+    [(C,) N, K, 3] SH coefficients when ``sh_degree`` is given; ``render_mode`` selects colour
+    and / or (expected) depth as the last channel; ``packed`` selects COO intermediates;
+    ``rasterize_mode="antialiased"`` multiplies opacities by the blur compensation;
+    ``absgrad`` stores |d loss / d means2d| in ``meta["means2d"].absgrad`` during backward.
+
+    Returns (render_colors [C,H,W,X], render_alphas [C,H,W,1], meta).
+    """
+    N = means.shape[0]
+    C = viewmats.shape[0]
+    assert means.shape == (N, 3), means.shape
+    assert quats.shape == (N, 4), quats.shape
+    assert scales.shape == (N, 3), scales.shape
+    assert opacities.shape == (N,), opacities.shape
+    if velocities is not None:
+        assert velocities.shape == (N, 3), velocities.shape
+    assert viewmats.shape == (C, 4, 4), viewmats.shape
+    assert Ks.shape == (C, 3, 3), Ks.shape
+    if linear_velocity is not None:
+        assert linear_velocity.shape == (C, 3), linear_velocity.shape
+    else:
+        linear_velocity = torch.zeros(C, 3, device=means.device)
+    if angular_velocity is not None:
+        assert angular_velocity.shape == (C, 3), angular_velocity.shape
+    else:
+        angular_velocity = torch.zeros(C, 3, device=means.device)
+    if rolling_shutter_time is not None:
+        assert rolling_shutter_time.shape == (C,), rolling_shutter_time.shape
+    else:
+        rolling_shutter_time = torch.zeros(C, device=means.device)
+    assert render_mode in ["RGB", "D", "ED", "RGB+D", "RGB+ED"], render_mode
+
+    if sh_degree is None:
+        assert (colors.dim() == 2 and colors.shape[0] == N) or (
+            colors.dim() == 3 and colors.shape[:2] == (C, N)
+        ), colors.shape
+    else:
+        assert (colors.dim() == 3 and colors.shape[0] == N and colors.shape[2] == 3) or (
+            colors.dim() == 4 and colors.shape[:2] == (C, N) and colors.shape[3] == 3
+        ), colors.shape
+        assert (sh_degree + 1) ** 2 <= colors.shape[-2], colors.shape
+
+    proj_results = fully_fused_projection(
+        means,
+        None,  # covars
+        quats,
+        scales,
+        velocities,
+        viewmats,
+        Ks,
+        width,
+        height,
+        linear_velocity,
+        angular_velocity,
+        rolling_shutter_time,
+        eps2d=eps2d,
+        packed=packed,
+        near_plane=near_plane,
+        far_plane=far_plane,
+        radius_clip=radius_clip,
+        sparse_grad=sparse_grad,
+        calc_compensations=(rasterize_mode == "antialiased"),
+    )
+
+    if packed:
+        (camera_ids, gaussian_ids, radii, means2d, depths, conics, compensations, pix_vels) = proj_results
+        opacities = opacities[gaussian_ids]  # [nnz]
+    else:
+        radii, means2d, depths, conics, compensations, pix_vels = proj_results
+        opacities = opacities.repeat(C, 1)  # [C, N]
+        camera_ids, gaussian_ids = None, None
+
+    if compensations is not None:
+        opacities = opacities * compensations
+
+    tile_width = math.ceil(width / float(tile_size))
+    tile_height = math.ceil(height / float(tile_size))
+    tiles_per_gauss, isect_ids, flatten_ids = isect_tiles(
+        means2d,
+        radii,
+        depths,
+        tile_size,
+        tile_width,
+        tile_height,
+        packed=packed,
+        n_cameras=C,
+        camera_ids=camera_ids,
+        gaussian_ids=gaussian_ids,
+    )
+    isect_offsets = isect_offset_encode(isect_ids, C, tile_width, tile_height)
+
+    if sh_degree is None:
+        if packed:
+            if colors.dim() == 2:
+                colors = colors[gaussian_ids]
+            else:
+                colors = colors[camera_ids, gaussian_ids]
+        else:
+            if colors.dim() == 2:
+                colors = colors.expand(C, -1, -1)
+    else:
+        camtoworlds = torch.inverse(viewmats)  # [C, 4, 4]
+        if packed:
+            dirs = means[gaussian_ids, :] - camtoworlds[camera_ids, :3, 3]  # [nnz, 3]
+            masks = radii[..., 0] > 0  # [nnz]
+            if colors.dim() == 3:
+                shs = colors[gaussian_ids, :, :]  # [nnz, K, 3]
+            else:
+                shs = colors[camera_ids, gaussian_ids, :, :]  # [nnz, K, 3]
+            colors = spherical_harmonics(sh_degree, dirs, shs, masks=masks)  # [nnz, 3]
+        else:
+            dirs = means[None, :, :] - camtoworlds[:, None, :3, 3]  # [C, N, 3]
+            masks = radii[..., 0] > 0  # [C, N]
+            if colors.dim() == 3:
+                shs = colors.expand(C, -1, -1, -1)  # [C, N, K, 3]
+            else:
+                shs = colors
+            colors = spherical_harmonics(sh_degree, dirs, shs, masks=masks)  # [C, N, 3]
+        colors = torch.clamp_min(colors + 0.5, 0.0)
+
+    if render_mode in ["RGB+D", "RGB+ED"]:
+        colors = torch.cat((colors, depths[..., None]), dim=-1)
+        if backgrounds is not None:
+            backgrounds = torch.cat([backgrounds, torch.zeros(C, 1, device=backgrounds.device)], dim=-1)
+    elif render_mode in ["D", "ED"]:
+        colors = depths[..., None]
+        if backgrounds is not None:
+            backgrounds = torch.zeros(C, 1, device=backgrounds.device)
+
+    if colors.shape[-1] > channel_chunk:
+        n_chunks = (colors.shape[-1] + channel_chunk - 1) // channel_chunk
+        render_colors, render_alphas = [], []
+        for i in range(n_chunks):
+            colors_chunk = colors[..., i * channel_chunk : (i + 1) * channel_chunk]
+            backgrounds_chunk = (
+                backgrounds[..., i * channel_chunk : (i + 1) * channel_chunk]
+                if backgrounds is not None
+                else None
+            )
+            render_colors_, render_alphas_ = rasterize_to_pixels(
+                means2d, conics, colors_chunk, opacities, pix_vels, width, height, tile_size,
+                isect_offsets, flatten_ids, rolling_shutter_time, backgrounds=backgrounds_chunk,
+                packed=packed, absgrad=absgrad,
+            )
+            render_colors.append(render_colors_)
+            render_alphas.append(render_alphas_)
+        render_colors = torch.cat(render_colors, dim=-1)
+        render_alphas = render_alphas[0]  # discard the rest
+    else:
+        render_colors, render_alphas = rasterize_to_pixels(
+            means2d, conics, colors, opacities, pix_vels, width, height, tile_size, isect_offsets,
+            flatten_ids, rolling_shutter_time, backgrounds=backgrounds, packed=packed, absgrad=absgrad,
+        )
+    if render_mode in ["ED", "RGB+ED"]:
+        render_colors = torch.cat(
+            [render_colors[..., :-1], render_colors[..., -1:] / render_alphas.clamp(min=1e-10)],
+            dim=-1,
+        )
+
+    meta = {
+        "camera_ids": camera_ids,
+        "gaussian_ids": gaussian_ids,
+        "radii": radii,
+        "means2d": means2d,
+        "depths": depths,
+        "conics": conics,
+        "opacities": opacities,
+        "pix_vels": pix_vels,
+        "tile_width": tile_width,
+        "tile_height": tile_height,
+        "tiles_per_gauss": tiles_per_gauss,
+        "isect_ids": isect_ids,
+        "flatten_ids": flatten_ids,
+        "isect_offsets": isect_offsets,
+        "width": width,
+        "height": height,
+        "tile_size": tile_size,
+        "n_cameras": C,
+    }
+    return render_colors, render_alphas, meta
+
+
+def lidar_rasterization(
+    means: Tensor,  # [N, 3]
+    quats: Tensor,  # [N, 4]
+    scales: Tensor,  # [N, 3]
+    opacities: Tensor,  # [N]
+    lidar_features: Tensor,  # [C, N, D]
+    velocities: Optional[Tensor],  # [N, 3]
+    viewmats: Tensor,  # [C, 4, 4]
+    raster_pts: Tensor,  # [C, H, W, 4]
+    tile_elevation_boundaries: Tensor,  # [ceil(n_elevation_channels / tile_height) + 1]
+    linear_velocity: Optional[Tensor] = None,  # [C, 3]
+    angular_velocity: Optional[Tensor] = None,  # [C, 3]
+    rolling_shutter_time: Optional[Tensor] = None,  # [C]
+    min_azimuth: float = -180,
+    max_azimuth: float = 180,
+    min_elevation: float = -80,
+    max_elevation: float = 80,
+    n_elevation_channels: int = 32,
+    azimuth_resolution: float = 0.1,
+    tile_width: int = 32,
+    tile_height: int = 8,
+    near_plane: float = 0.01,
+    far_plane: float = 1e10,
+    radius_clip: float = 0.0,
+    eps2d: float = 0.017,
+    compute_alpha_sum_until_points: bool = True,
+    compute_alpha_sum_until_points_threshold: float = 0.2,
+    packed: bool = False,  # packed mode is not supported (as in the reference)
+    sparse_grad: bool = False,
+    absgrad: bool = False,
+    rasterize_mode: Literal["classic", "antialiased"] = "classic",
+    channel_chunk: int = 32,
+    use_depth_compensation: bool = True,
+) -> Tuple[Tensor, Tensor, Union[Tensor, None], Dict]:
+    """Rasterizes N 3-D Gaussians to C spinning-lidar range images given as ``raster_pts``
+    [C, H, W, 4] = (azimuth deg, elevation deg, range m, time offset s).
+
+    Arguments, defaults and behaviour are those of the reference function of the same name
+    (gsplat/rendering.py:443-819). Returns (features with the expected range appended as last
+    channel [C,H,W,D+1], alphas [C,H,W,1], alpha_sum_until_points [C,H,W,1] or None, meta);
+    ``meta["median_depths"]`` holds the median range.
+    """
+    N = means.shape[0]
+    C = viewmats.shape[0]
+    D = lidar_features.shape[-1]
+    assert means.shape == (N, 3), means.shape
+    assert quats.shape == (N, 4), quats.shape
+    assert scales.shape == (N, 3), scales.shape
+    assert opacities.shape == (N,), opacities.shape
+    if velocities is not None:
+        assert velocities.shape == (N, 3), velocities.shape
+    assert viewmats.shape == (C, 4, 4), viewmats.shape
+    assert lidar_features.shape == (C, N, D), lidar_features.shape
+    assert min_azimuth < max_azimuth, (min_azimuth, max_azimuth)
+    assert min_elevation < max_elevation, (min_elevation, max_elevation)
+    assert min_azimuth >= -180.0 and max_azimuth <= 180.0, (min_azimuth, max_azimuth)
+    assert min_elevation >= -85.0 and max_elevation <= 85.0, (min_elevation, max_elevation)
+    assert tile_width * tile_height <= 256, (tile_width, tile_height)
+    assert n_elevation_channels > 0, n_elevation_channels
+    assert tile_elevation_boundaries.shape == (
+        math.ceil(n_elevation_channels / tile_height) + 1,
+    ), tile_elevation_boundaries.shape
+    assert azimuth_resolution > 0.0, azimuth_resolution
+    if linear_velocity is not None:
+        assert linear_velocity.shape == (C, 3), linear_velocity.shape
+    else:
+        linear_velocity = torch.zeros(C, 3, device=means.device)
+    if angular_velocity is not None:
+        assert angular_velocity.shape == (C, 3), angular_velocity.shape
+    else:
+        angular_velocity = torch.zeros(C, 3, device=means.device)
+    if rolling_shutter_time is not None:
+        assert rolling_shutter_time.shape == (C,), rolling_shutter_time.shape
+    else:
+        rolling_shutter_time = torch.zeros(C, device=means.device)
+    assert raster_pts.shape == (C, *raster_pts.shape[1:]), raster_pts.shape
+    assert raster_pts.shape[-1] == 4, raster_pts.shape
+
+    proj_results = fully_fused_lidar_projection(
+        means,
+        None,  # covars
+        quats,
+        scales,
+        velocities,
+        viewmats,
+        linear_velocity,
+        angular_velocity,
+        rolling_shutter_time,
+        min_elevation=min_elevation,
+        max_elevation=max_elevation,
+        min_azimuth=min_azimuth,
+        max_azimuth=max_azimuth,
+        eps2d=eps2d,
+        packed=packed,
+        near_plane=near_plane,
+        far_plane=far_plane,
+        radius_clip=radius_clip,
+        sparse_grad=sparse_grad,
+        calc_compensations=(rasterize_mode == "antialiased"),
+    )
+    if packed:
+        raise NotImplementedError("Packed mode is not supported for lidar_rasterization")
+    radii, means2d, depths, conics, compensations, pix_vels, depth_compensations = proj_results
+    opacities = opacities.repeat(C, 1)  # [C, N]
+    camera_ids, gaussian_ids = None, None
+
+    if not use_depth_compensation:
+        depth_compensations = depth_compensations * 0
+
+    if compensations is not None:
+        opacities = opacities * compensations
+
+    n_elevation_tiles = math.ceil(n_elevation_channels / tile_height)
+    tile_azimuth_resolution = azimuth_resolution * tile_width
+    n_azimuth_tiles = math.ceil((max_azimuth - min_azimuth) / tile_azimuth_resolution)
+    tiles_per_gauss, isect_ids, flatten_ids = isect_lidar_tiles(
+        means2d,
+        radii,
+        depths,
+        elev_boundaries=tile_elevation_boundaries,
+        tile_azim_resolution=tile_azimuth_resolution,
+        min_azim=min_azimuth,
+        packed=packed,
+        n_cameras=C,
+        camera_ids=camera_ids,
+        gaussian_ids=gaussian_ids,
+    )
+    isect_offsets = isect_offset_encode(isect_ids, C, n_azimuth_tiles, n_elevation_tiles)
+
+    image_width = raster_pts.shape[-2]
+    image_height = raster_pts.shape[-3]
+
+    if (lidar_features.shape[-1] + 1) > channel_chunk:
+        n_chunks = (lidar_features.shape[-1] + channel_chunk) // channel_chunk
+        render_lidar_features, render_alphas, alpha_sum_until_points, median_depths = [], [], [], []
+        for i in range(n_chunks):
+            lidar_features_chunk = lidar_features[..., i * (channel_chunk - 1) : (i + 1) * (channel_chunk - 1)]
+            (render_lidar_features_, render_alphas_, alpha_sum_until_points_, median_depths_) = rasterize_to_points(
+                means2d,
+                conics,
+                torch.cat([lidar_features_chunk, depths[..., None]], dim=-1),
+                opacities,
+                pix_vels,
+                depth_compensations,
+                raster_pts,
+                image_width,
+                image_height,
+                tile_width,
+                tile_height,
+                isect_offsets,
+                flatten_ids,
+                compute_alpha_sum_until_points=compute_alpha_sum_until_points,
+                compute_alpha_sum_until_points_threshold=compute_alpha_sum_until_points_threshold,
+                packed=packed,
+                absgrad=absgrad,
+            )
+            if i == (n_chunks - 1):
+                render_lidar_features.append(render_lidar_features_)
+            else:
+                render_lidar_features.append(render_lidar_features_[..., :-1])
+            render_alphas.append(render_alphas_)
+            alpha_sum_until_points.append(alpha_sum_until_points_)
+            median_depths.append(median_depths_)
+        render_lidar_features = torch.cat(render_lidar_features, dim=-1)
+        median_depths = torch.cat(median_depths, dim=-1)
+        render_alphas = render_alphas[0]  # discard the rest
+        alpha_sum_until_points = alpha_sum_until_points[0]  # same alphas for all chunks
+    else:
+        render_lidar_features, render_alphas, alpha_sum_until_points, median_depths = rasterize_to_points(
+            means2d,
+            conics,
+            torch.cat([lidar_features, depths[..., None]], dim=-1),
+            opacities,
+            pix_vels,
+            depth_compensations,
+            raster_pts,
+            image_width,
+            image_height,
+            tile_width,
+            tile_height,
+            isect_offsets,
+            flatten_ids,
+            compute_alpha_sum_until_points=compute_alpha_sum_until_points,
+            compute_alpha_sum_until_points_threshold=compute_alpha_sum_until_points_threshold,
+            packed=packed,
+            absgrad=absgrad,
+        )
+
+    meta = {
+        "camera_ids": camera_ids,
+        "gaussian_ids": gaussian_ids,
+        "radii": radii,
+        "means2d": means2d,
+        "depths": depths,
+        "conics": conics,
+        "opacities": opacities,
+        "pix_vels": pix_vels,
+        "tile_grid_width": n_azimuth_tiles,
+        "tile_grid_height": n_elevation_tiles,
+        "tiles_per_gauss": tiles_per_gauss,
+        "isect_ids": isect_ids,
+        "flatten_ids": flatten_ids,
+        "isect_offsets": isect_offsets,
+        "width": image_width,
+        "height": image_height,
+        "tile_width": tile_width,
+        "tile_height": tile_height,
+        "n_cameras": C,
+        "median_depths": median_depths,
+    }
+    return render_lidar_features, render_alphas, alpha_sum_until_points, meta

@@ -1,0 +1,423 @@
+#!/usr/bin/env python
+"""Benchmark of the SplatAD render hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one forward render of the headline workload: the 128-beam x 1800-column
+rolling-shutter lidar frame over 1 000 000 Gaussians (config 2), synthetic and seeded. Rank 0
+prints ONE JSON line. Keys beyond the base contract:
+
+  value / ms_per_step   lidar points per second with the frame's inputs resident in HBM, timed
+                        per step with CUDA events (L2 flushed between steps), max over ranks.
+  e2e                   the same metric through the public API with HOST inputs: every step
+                        copies the Gaussians and the sensor from pinned host memory, renders, and
+                        copies the rendered frame back.
+  kernels               per-kernel launches and milliseconds of one step (CUDA events inside the
+                        library, measured in a separate, untimed step).
+  roofline              the dominant kernel of the step against the measured HBM copy peak.
+  fp32_probe            measured FP32 FMA throughput of the device (the compositing roofline).
+  camera                config 1 (1920x1080 rolling-shutter camera, 500k Gaussians) in Mpix/s.
+  cpu_baseline          the CPU oracle restatement of the same frame on the host cores (rank 0).
+
+With --gpus N > 1 (launched through torch.distributed.run) every rank renders its own lidar
+sensor over replicated Gaussians: the path shards by sensor with no data-path collective, so
+scaling is "weak" and value is the sum over ranks divided by the slowest rank's time.
+
+--impl reference times the reference's CPU implementation of the path. The reference has no CPU
+backend for its two render functions (its torch compositing calls CUDA kernels), so this arm
+runs the CPU oracle port (reference torch maths for projection, numpy tile intersection, C
+compositing) on a bounded sample of the workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np
+import torch
+
+POINTS_PER_FRAME = 128 * 1800
+WORKLOAD = ("config2: 1,000,000 Gaussians (seed 2), one 128-beam x 1800-column rolling-shutter lidar "
+            "(230,400 points), 16 features + range, alpha, alpha-sum, median range")
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d.get("hbm_gbs", 6650.0)), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons in the background during the timed region."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smmax, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smmax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for nme, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(nme)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(np.max(smmax)) if smmax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def kernel_profile(fn):
+    """Runs fn() once with the library's per-kernel event timing on; returns {name: (launches, ms)}."""
+    from splatad_b200 import _lib
+    lib = _lib.load()
+    torch.cuda.synchronize()
+    lib.splatad_profile_enable(1)
+    try:
+        fn()
+        torch.cuda.synchronize()
+        buf = ctypes.create_string_buffer(1 << 16)
+        lib.splatad_profile_report(buf, len(buf))
+    finally:
+        lib.splatad_profile_enable(0)
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, cnt, ms = line.split()
+        out[name] = (int(cnt), float(ms))
+    return out
+
+
+def fp32_probe(dev):
+    """Measured FP32 FMA rate (TFLOP/s): 148*16 blocks x 256 threads x iters x 128 FMAs."""
+    from splatad_b200 import _lib
+    lib = _lib.load()
+    grid, iters = 148 * 16, 4096
+    out = torch.empty(grid * 256, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    best = None
+    for _ in range(4):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        lib.splatad_fma_probe(out.data_ptr(), grid, iters, stream)
+        b.record()
+        b.synchronize()
+        ms = a.elapsed_time(b)
+        best = ms if best is None else min(best, ms)
+    flops = grid * 256 * iters * 128 * 2
+    return flops / (best * 1e-3) / 1e12
+
+
+def to_device(cfg, dev):
+    return {k: (v.to(dev, non_blocking=True) if isinstance(v, torch.Tensor) else v) for k, v in cfg.items()}
+
+
+def sensor_pose_for_rank(cfg, rank):
+    """Rank r renders the same lidar yawed by r * 45 degrees (a different sensor of the rig)."""
+    if rank == 0:
+        return cfg
+    import math
+    yaw = math.radians(45.0 * rank)
+    c, s = math.cos(yaw), math.sin(yaw)
+    vm = cfg["viewmats"].clone()
+    vm[0, :3, :3] = torch.tensor([[c, s, 0.0], [-s, c, 0.0], [0.0, 0.0, 1.0]])
+    return dict(cfg, viewmats=vm)
+
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    import splatad_b200
+    from splatad_b200 import scenes
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+
+    cfg_host = sensor_pose_for_rank(scenes.config2(), rank)
+    cfg = to_device(cfg_host, dev)
+    flush = torch.empty(256 * 1024 * 1024 // 4, device=dev)  # 256 MB > 126 MB of L2
+
+    def step(c=cfg):
+        return splatad_b200.lidar_rasterization(**c)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        out = step()
+    torch.cuda.synchronize()
+    n_isects = int(out[3]["flatten_ids"].numel())
+
+    # ---- device-resident timing: per-step CUDA events, L2 flushed between steps ----------------
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    t_wall = time.perf_counter()
+    evs = []
+    for _ in range(args.steps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        out = step()
+        b.record()
+        evs.append((a, b))
+    barrier()
+    wall = time.perf_counter() - t_wall
+    clocks = sampler.stop()
+    ms_steps = [a.elapsed_time(b) for a, b in evs]
+    ms_total = float(np.sum(ms_steps))
+    if world > 1:
+        tt = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms_total = float(tt.item())
+    ms_per_step = ms_total / args.steps
+    value = world * POINTS_PER_FRAME / (ms_per_step * 1e-3)
+
+    # ---- end to end: host inputs in pinned memory, H2D + render + D2H every step ---------------
+    pinned = {k: (v.pin_memory() if isinstance(v, torch.Tensor) else v) for k, v in cfg_host.items()}
+    h2d_bytes = sum(v.numel() * v.element_size() for v in pinned.values() if isinstance(v, torch.Tensor))
+    host_out = None
+
+    def e2e_step():
+        nonlocal host_out
+        c = to_device(pinned, dev)
+        feats, alphas, asum, meta = splatad_b200.lidar_rasterization(**c)
+        outs = (feats, alphas, asum, meta["median_depths"])
+        if host_out is None:
+            host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+        for h, o in zip(host_out, outs):
+            h.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return outs
+
+    for _ in range(3):
+        e2e_step()
+    d2h_bytes = sum(h.numel() * h.element_size() for h in host_out)
+    barrier()
+    t0 = time.perf_counter()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        e2e_step()
+    b.record()
+    barrier()
+    e2e_ms = a.elapsed_time(b)
+    if world > 1:
+        tt = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tt.item())
+    e2e_value = world * POINTS_PER_FRAME * args.steps / (e2e_ms * 1e-3)
+
+    result = None
+    if rank == 0:
+        # ---- per-kernel breakdown and roofline of the dominant kernel (untimed extra step) -----
+        prof = kernel_profile(step)
+        launches = int(sum(c for c, _ in prof.values()))
+        kernels = {k: {"launches": c, "ms": round(ms, 4)} for k, (c, ms) in prof.items()}
+        peak, peak_src = load_peaks()
+        dom = max(prof.items(), key=lambda kv: kv[1][1])
+        dom_name, (dom_cnt, dom_ms) = dom
+        # algorithmic bytes per launch of the sort / emit kernels: 8-byte (key, id) pairs
+        n_vis = int((out[3]["radii"][..., 0] > 0).sum())
+        bytes_per_launch = {
+            "tilesort_downsweep": n_isects * (8 + 8 + 2),       # read pair, write pair (last pass 12 B)
+            "tilesort_upsweep": n_isects * 4,
+            "emit_kernel": n_isects * 8 + n_vis * 20,
+            "depthsort_downsweep": n_vis * 16,
+            "depthsort_upsweep": n_vis * 4,
+            "lidar_projection_fwd_kernel": 1_000_000 * 40 + n_vis * 52 + (1_000_000 - n_vis) * 52,
+            "rasterize_to_points_fwd_kernel": POINTS_PER_FRAME * (16 + 4 * 21),
+            "isect_count_kernel": 1_000_000 * 20,
+        }.get(dom_name, None)
+        roofline = None
+        if bytes_per_launch is not None:
+            achieved = bytes_per_launch / (dom_ms / dom_cnt * 1e-3) / 1e9
+            roofline = {"kernel": dom_name, "bound": "hbm", "achieved": round(achieved, 1), "peak": peak,
+                        "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
+                        "peak_source": f"of {peak_src}", "launches_per_step": dom_cnt,
+                        "ms_per_launch": round(dom_ms / dom_cnt, 4),
+                        "algorithmic_bytes_per_launch": int(bytes_per_launch)}
+        tfl = fp32_probe(dev)
+
+        # ---- camera config 1 ---------------------------------------------------------------
+        cam_cfg = to_device(scenes.config1(), dev)
+        for _ in range(3):
+            cam_out = splatad_b200.rasterization(**cam_cfg)
+        torch.cuda.synchronize()
+        cam_ms = []
+        for _ in range(max(3, min(args.steps, 10))):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            cam_out = splatad_b200.rasterization(**cam_cfg)
+            b.record()
+            b.synchronize()
+            cam_ms.append(a.elapsed_time(b))
+        cam_prof = kernel_profile(lambda: splatad_b200.rasterization(**cam_cfg))
+        camera = {"workload": "config1: 500,000 Gaussians, 1920x1080 rolling-shutter camera, SH deg 3, RGB+D, packed",
+                  "mpix_per_s": round(1920 * 1080 * 1e-6 / (np.mean(cam_ms) * 1e-3), 1),
+                  "ms_per_frame": round(float(np.mean(cam_ms)), 4),
+                  "n_isects": int(cam_out[2]["flatten_ids"].numel()),
+                  "kernels": {k: {"launches": c, "ms": round(ms, 4)} for k, (c, ms) in cam_prof.items()}}
+
+        cpu = cpu_baseline_sample()
+        result = {
+            "metric": "lidar_points_per_s", "value": round(value, 1), "unit": "points/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
+            "frames_per_s": round(1e3 / ms_per_step * world, 1),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "impl": "ours",
+            "config": {"workload": WORKLOAD, "n_isects": n_isects, "n_visible": n_vis,
+                       "l2": "flushed between steps (256 MB write)",
+                       "sharding": "one lidar sensor per rank, Gaussians replicated, no collective"},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e_value, 1), "unit": "points/s", "h2d_bytes_per_step": int(h2d_bytes),
+                    "d2h_bytes_per_step": int(d2h_bytes), "ms_per_step": round(e2e_ms / args.steps, 4)},
+            "gpu_launches": launches * args.steps,
+            "launches_per_step": launches,
+            "kernels": kernels,
+            "roofline": roofline,
+            "fp32_probe": {"tflops": round(tfl, 2), "how": "FMA chains, 148*16 blocks x 256 threads"},
+            "camera": camera,
+            "cpu_baseline": cpu,
+            "wall_s_timed_region": round(wall, 3),
+        }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if result is not None:
+        print(json.dumps(result))
+
+
+def cpu_frame(n_gauss):
+    """One config-2 frame through the CPU oracle port with n_gauss Gaussians; returns seconds and stage times."""
+    from oracle import pipeline
+    from splatad_b200 import scenes
+    cfg = scenes.config2(N=n_gauss)
+    timings = {}
+    t0 = time.perf_counter()
+    pipeline.lidar_rasterization(**cfg, timings=timings)
+    return time.perf_counter() - t0, timings
+
+
+def cpu_baseline_sample(fraction=0.1):
+    """The CPU port on a bounded sample: the full sensor over every 1/fraction-th of the Gaussians;
+    cost is linear in the Gaussian count (projection and tile sorting dominate), so the frame rate is
+    extrapolated linearly and labelled as such."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    n = int(1_000_000 * fraction)
+    cpu_frame(n // 4)  # warm-up (imports, C oracle build)
+    best, stages = None, None
+    for _ in range(2):
+        t, tm = cpu_frame(n)
+        if best is None or t < best:
+            best, stages = t, tm
+    value = POINTS_PER_FRAME / (best / fraction)
+    return {"value": round(value, 1), "unit": "points/s", "cores": cores, "kind": "port",
+            "sample": f"full 128x1800 sensor over {n} of 1,000,000 Gaussians (best of 2, {best:.2f} s), "
+                      f"frame time extrapolated linearly in the Gaussian count",
+            "stage_seconds_sample": {k: round(v, 3) for k, v in stages.items()}}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    fraction = 0.05
+    n = int(1_000_000 * fraction)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_frame(n)
+    times = []
+    for _ in range(args.steps):
+        t, _ = cpu_frame(n)
+        times.append(t)
+    per_step = float(np.mean(times)) / fraction  # seconds per full frame (linear in Gaussian count)
+    value = POINTS_PER_FRAME / per_step
+    sample = (f"each step: full 128x1800 sensor over {n} of 1,000,000 Gaussians, frame time extrapolated "
+              f"linearly in the Gaussian count")
+    print(json.dumps({
+        "metric": "lidar_points_per_s", "value": round(value, 1), "unit": "points/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(per_step * 1e3, 2), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
+        "config": {"workload": WORKLOAD},
+        "cpu_baseline": {"value": round(value, 1), "unit": "points/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(value, 1), "unit": "points/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

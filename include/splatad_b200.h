@@ -46,6 +46,13 @@ int splatad_version(void);
  * No counterpart in the reference. */
 int splatad_fma_probe(float *out, int32_t grid, int32_t iters, void *stream);
 
+/* Per-kernel timing for benchmarks (no counterpart in the reference). While enabled, every
+ * kernel launch of the library is bracketed by a CUDA event pair on its stream (this creates
+ * events: a measurement mode only). _report waits for them and writes "name launches total_ms"
+ * lines, one per kernel name in first-launch order, then clears the records. */
+int splatad_profile_enable(int32_t enable);
+int splatad_profile_report(char *buf, size_t cap);
+
 /* ------------------------------------------------------------------------------------------
  * Projection
  * ---------------------------------------------------------------------------------------- */

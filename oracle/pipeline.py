@@ -1,0 +1,156 @@
+"""End-to-end CPU restatement of ``lidar_rasterization`` and ``rasterization`` assembled from the
+oracle pieces. TEST INFRASTRUCTURE ONLY - see ``oracle/__init__.py``. Also the CPU baseline
+timed by ``bench.py`` (the reference has no CPU backend for these two functions: its torch
+compositing calls CUDA kernels, so the compositing leg is this restatement).
+
+Orchestration follows gsplat/rendering.py:205-440 (camera) and 616-819 (lidar).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+
+from . import composite, isect, projection
+
+
+def _np(t):
+    return None if t is None else t.detach().cpu().numpy()
+
+
+def _zeros(C, n, ref):
+    return torch.zeros(C, n, dtype=ref.dtype)
+
+
+def lidar_rasterization(
+    means, quats, scales, opacities, lidar_features, velocities, viewmats, raster_pts,
+    tile_elevation_boundaries, linear_velocity=None, angular_velocity=None, rolling_shutter_time=None,
+    min_azimuth=-180, max_azimuth=180, min_elevation=-80, max_elevation=80, n_elevation_channels=32,
+    azimuth_resolution=0.1, tile_width=32, tile_height=8, near_plane=0.01, far_plane=1e10,
+    radius_clip=0.0, eps2d=0.017, compute_alpha_sum_until_points=True,
+    compute_alpha_sum_until_points_threshold=0.2, rasterize_mode="classic", use_depth_compensation=True,
+    dtype=np.float32, timings: Optional[Dict] = None,
+):
+    """CPU lidar render. Returns (features+range [C,H,W,D+1], alphas, alpha_sum, meta) as numpy;
+    ``meta`` additionally carries ``ambiguous`` (see oracle/composite_impl.h), ``tested`` and
+    ``contributing`` pair counts."""
+    import time
+
+    tdt = torch.float32 if dtype == np.float32 else torch.float64
+    cast = lambda x: None if x is None else torch.as_tensor(x).to(tdt)  # noqa: E731
+    C = viewmats.shape[0]
+    lin = cast(linear_velocity) if linear_velocity is not None else torch.zeros(C, 3, dtype=tdt)
+    ang = cast(angular_velocity) if angular_velocity is not None else torch.zeros(C, 3, dtype=tdt)
+    rs = cast(rolling_shutter_time) if rolling_shutter_time is not None else torch.zeros(C, dtype=tdt)
+    t0 = time.perf_counter()
+    with torch.no_grad():
+        radii, means2d, depths, conics, comps, pix_vels, dcomp = projection.fully_fused_lidar_projection(
+            cast(means), None, cast(quats), cast(scales), cast(velocities), cast(viewmats), lin, ang, rs,
+            min_elevation, max_elevation, min_azimuth, max_azimuth, eps2d, near_plane, far_plane,
+            radius_clip, rasterize_mode == "antialiased")
+    opac = cast(opacities)[None].repeat(C, 1)
+    if comps is not None:
+        opac = opac * comps
+    if not use_depth_compensation:
+        dcomp = dcomp * 0
+    t1 = time.perf_counter()
+    n_el = math.ceil(n_elevation_channels / tile_height)
+    tile_az = azimuth_resolution * tile_width
+    n_az = math.ceil((max_azimuth - min_azimuth) / tile_az)
+    r32 = _np(radii).astype(np.float32)
+    m32 = _np(means2d).astype(np.float32)
+    d32 = _np(depths).astype(np.float32)
+    tpg, ids, flat = isect.isect_lidar_tiles(m32, r32, d32, _np(torch.as_tensor(tile_elevation_boundaries)),
+                                             tile_az, min_azimuth)
+    offsets = isect.isect_offset_encode(ids, C, n_az, n_el)
+    t2 = time.perf_counter()
+    H, W = raster_pts.shape[1:3]
+    feats = torch.cat([cast(lidar_features), depths[..., None]], dim=-1)
+    out = composite.rasterize_to_points_fwd(
+        _np(means2d), _np(conics), _np(feats), _np(opac), _np(pix_vels), _np(dcomp), None,
+        _np(torch.as_tensor(raster_pts)), W, H, tile_width, tile_height, offsets, flat,
+        compute_alpha_sum_until_points, compute_alpha_sum_until_points_threshold, dtype=dtype)
+    t3 = time.perf_counter()
+    if timings is not None:
+        timings.update(projection=t1 - t0, isect=t2 - t1, composite=t3 - t2, total=t3 - t0)
+    meta = dict(radii=_np(radii), means2d=_np(means2d), depths=_np(depths), conics=_np(conics),
+                opacities=_np(opac), pix_vels=_np(pix_vels), depth_compensations=_np(dcomp),
+                tiles_per_gauss=tpg, isect_ids=ids, flatten_ids=flat, isect_offsets=offsets,
+                tile_grid_width=n_az, tile_grid_height=n_el, median_depths=out["median_depths"],
+                last_ids=out["last_ids"], ambiguous=out["ambiguous"], tested=out["tested"],
+                contributing=out["contributing"])
+    return out["render_colors"], out["render_alphas"], out["alpha_sum"], meta
+
+
+def rasterization(
+    means, quats, scales, opacities, colors, velocities, viewmats, Ks, width, height,
+    linear_velocity=None, angular_velocity=None, rolling_shutter_time=None, near_plane=0.01,
+    far_plane=1e10, radius_clip=0.0, eps2d=0.3, sh_degree=None, packed=True, tile_size=16,
+    backgrounds=None, render_mode="RGB", rasterize_mode="classic", dtype=np.float32,
+    timings: Optional[Dict] = None,
+):
+    """CPU camera render (always in the [C, N] layout; ``packed`` only changes intermediate
+    layouts in the product, not the image). Returns (colors [C,H,W,X], alphas [C,H,W,1], meta)."""
+    import time
+
+    tdt = torch.float32 if dtype == np.float32 else torch.float64
+    cast = lambda x: None if x is None else torch.as_tensor(x).to(tdt)  # noqa: E731
+    C = viewmats.shape[0]
+    N = means.shape[0]
+    lin = cast(linear_velocity) if linear_velocity is not None else torch.zeros(C, 3, dtype=tdt)
+    ang = cast(angular_velocity) if angular_velocity is not None else torch.zeros(C, 3, dtype=tdt)
+    rs = cast(rolling_shutter_time) if rolling_shutter_time is not None else torch.zeros(C, dtype=tdt)
+    t0 = time.perf_counter()
+    with torch.no_grad():
+        radii, means2d, depths, conics, comps, pix_vels = projection.fully_fused_projection(
+            cast(means), None, cast(quats), cast(scales), cast(velocities), cast(viewmats), cast(Ks),
+            width, height, lin, ang, rs, eps2d, near_plane, far_plane, radius_clip,
+            rasterize_mode == "antialiased")
+        opac = cast(opacities)[None].repeat(C, 1)
+        if comps is not None:
+            opac = opac * comps
+        col = cast(colors)
+        if sh_degree is not None:
+            camtoworlds = torch.inverse(cast(viewmats))
+            dirs = cast(means)[None] - camtoworlds[:, None, :3, 3]
+            shs = col[None].expand(C, -1, -1, -1) if col.dim() == 3 else col
+            col = projection.spherical_harmonics(sh_degree, dirs, shs, masks=radii[..., 0] > 0)
+            col = torch.clamp_min(col + 0.5, 0.0)
+        elif col.dim() == 2:
+            col = col[None].expand(C, -1, -1)
+        if render_mode in ("RGB+D", "RGB+ED"):
+            col = torch.cat([col, depths[..., None]], dim=-1)
+        elif render_mode in ("D", "ED"):
+            col = depths[..., None]
+    t1 = time.perf_counter()
+    tw = math.ceil(width / float(tile_size))
+    th = math.ceil(height / float(tile_size))
+    tpg, ids, flat = isect.isect_tiles(_np(means2d).astype(np.float32), _np(radii), _np(depths).astype(np.float32),
+                                       tile_size, tw, th)
+    offsets = isect.isect_offset_encode(ids, C, tw, th)
+    t2 = time.perf_counter()
+    bg = None
+    if backgrounds is not None:
+        bg = _np(cast(backgrounds))
+        if render_mode in ("RGB+D", "RGB+ED"):
+            bg = np.concatenate([bg, np.zeros((C, 1), bg.dtype)], axis=-1)
+        elif render_mode in ("D", "ED"):
+            bg = np.zeros((C, 1), bg.dtype)
+    out = composite.rasterize_to_pixels_fwd(_np(means2d), _np(conics), _np(col.contiguous()), _np(opac),
+                                            _np(pix_vels), _np(rs), bg, width, height, tile_size, offsets,
+                                            flat, dtype=dtype)
+    t3 = time.perf_counter()
+    render = out["render_colors"]
+    if render_mode in ("ED", "RGB+ED"):
+        render = np.concatenate([render[..., :-1], render[..., -1:] / np.maximum(out["render_alphas"], 1e-10)], axis=-1)
+    if timings is not None:
+        timings.update(projection=t1 - t0, isect=t2 - t1, composite=t3 - t2, total=t3 - t0)
+    meta = dict(radii=_np(radii), means2d=_np(means2d), depths=_np(depths), conics=_np(conics),
+                opacities=_np(opac), pix_vels=_np(pix_vels), colors=_np(col), tiles_per_gauss=tpg,
+                isect_ids=ids, flatten_ids=flat, isect_offsets=offsets, tile_width=tw, tile_height=th,
+                last_ids=out["last_ids"], ambiguous=out["ambiguous"], tested=out["tested"],
+                contributing=out["contributing"])
+    return render, out["render_alphas"], meta

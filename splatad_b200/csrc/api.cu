@@ -2,6 +2,10 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <map>
+#include <string>
+#include <vector>
+
 #include "common.cuh"
 
 namespace splatad {
@@ -14,6 +18,24 @@ void set_last_error(const char *fmt, ...) {
     vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
     va_end(ap);
 }
+
+// ---- optional per-kernel timing ---------------------------------------------------------
+struct ProfRec { const char *name; cudaEvent_t a, b; };
+static std::vector<ProfRec> g_prof;
+static bool g_prof_on = false;
+
+bool prof_enabled() { return g_prof_on; }
+
+void prof_begin(const char *name, cudaStream_t st) {
+    ProfRec r;
+    r.name = name;
+    cudaEventCreate(&r.a);
+    cudaEventCreate(&r.b);
+    cudaEventRecord(r.a, st);
+    g_prof.push_back(r);
+}
+
+void prof_end(cudaStream_t st) { cudaEventRecord(g_prof.back().b, st); }
 
 // FP32 FMA throughput probe: every thread runs `iters` rounds of 8 independent FMA chains.
 __global__ void __launch_bounds__(256) fma_probe_kernel(float *out, int iters, float a, float b) {
@@ -43,4 +65,41 @@ extern "C" int splatad_fma_probe(float *out, int32_t grid, int32_t iters, void *
     SPL_REQUIRE(out && grid > 0 && iters > 0, SPLATAD_ERR_BAD_ARG, "fma_probe: bad argument");
     fma_probe_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(out, iters, 0.999999f, 1e-7f);
     return check_launch("fma_probe");
+}
+
+// Turns per-kernel CUDA-event timing on or off (off by default). While on, every kernel launch
+// of the library is bracketed by an event pair on its stream; this creates CUDA events, so it is
+// a measurement mode, not for production frames.
+extern "C" int splatad_profile_enable(int32_t enable) {
+    g_prof_on = enable != 0;
+    return SPLATAD_OK;
+}
+
+// Waits for the recorded events, writes one line per kernel name, "name launches total_ms\n",
+// into buf (NUL terminated, truncated to cap) and clears the records.
+extern "C" int splatad_profile_report(char *buf, size_t cap) {
+    SPL_REQUIRE(buf && cap > 0, SPLATAD_ERR_BAD_ARG, "profile_report: bad buffer");
+    std::map<std::string, std::pair<int, double>> agg;
+    std::vector<std::string> order;
+    for (auto &r : g_prof) {
+        cudaEventSynchronize(r.b);
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, r.a, r.b);
+        if (!agg.count(r.name)) order.push_back(r.name);
+        auto &e = agg[r.name];
+        e.first += 1;
+        e.second += ms;
+        cudaEventDestroy(r.a);
+        cudaEventDestroy(r.b);
+    }
+    g_prof.clear();
+    std::string out;
+    char line[256];
+    for (auto &nme : order) {
+        snprintf(line, sizeof(line), "%s %d %.6f\n", nme.c_str(), agg[nme].first, agg[nme].second);
+        out += line;
+    }
+    strncpy(buf, out.c_str(), cap - 1);
+    buf[cap - 1] = 0;
+    return SPLATAD_OK;
 }

@@ -34,6 +34,25 @@ inline int check_launch(const char *what) {
 
 inline uint32_t div_up(uint64_t a, uint64_t b) { return (uint32_t)((a + b - 1) / b); }
 
+// Optional per-kernel timing (off by default, see splatad_profile_enable): while enabled every
+// launch site wrapped in SPL_PROF records a CUDA event pair on the launching stream.
+bool prof_enabled();
+void prof_begin(const char *name, cudaStream_t st);
+void prof_end(cudaStream_t st);
+struct ProfScope {
+    cudaStream_t st;
+    bool on;
+    ProfScope(const char *name, cudaStream_t s) : st(s), on(prof_enabled()) {
+        if (on) prof_begin(name, st);
+    }
+    ~ProfScope() {
+        if (on) prof_end(st);
+    }
+};
+#define SPL_PROF_CAT2(a, b) a##b
+#define SPL_PROF_CAT(a, b) SPL_PROF_CAT2(a, b)
+#define SPL_PROF(name, st) ::splatad::ProfScope SPL_PROF_CAT(_prof_, __LINE__)(name, st)
+
 // Cooperative copy of `nfl` contiguous floats global -> shared with 128-bit loads when the
 // source is 16-byte aligned (it is whenever the tensor base is, because block slabs start at
 // multiples of 256 rows).

@@ -685,7 +685,10 @@ extern "C" int splatad_rasterize_to_pixels_fwd(
             image_height, tile_size, tile_width, tile_height, tile_offsets, flatten_ids,          \
             render_colors, render_alphas, last_ids);                                              \
     }
-    SPL_DISPATCH_CDIM(channels, CALL);
+    {
+        SPL_PROF("rasterize_to_pixels_fwd_kernel", (cudaStream_t)stream);
+        SPL_DISPATCH_CDIM(channels, CALL);
+    }
 #undef CALL
     return check_launch("rasterize_to_pixels_fwd");
 }
@@ -724,7 +727,10 @@ extern "C" int splatad_rasterize_to_pixels_bwd(
             render_alphas, last_ids, v_render_colors, v_render_alphas, v_means2d_abs, v_means2d,  \
             v_conics, v_colors, v_opacities, v_pix_vels);                                         \
     }
-    SPL_DISPATCH_CDIM(channels, CALL);
+    {
+        SPL_PROF("rasterize_to_pixels_bwd_kernel", (cudaStream_t)stream);
+        SPL_DISPATCH_CDIM(channels, CALL);
+    }
 #undef CALL
     return check_launch("rasterize_to_pixels_bwd");
 }
@@ -770,7 +776,10 @@ extern "C" int splatad_rasterize_to_points_fwd(
             alpha_sum_threshold, tile_offsets, flatten_ids, depth_channel_idx, render_features,   \
             render_alphas, alpha_sum_until_points, last_ids, median_depths);                      \
     }
-    SPL_DISPATCH_CDIM(channels, CALL);
+    {
+        SPL_PROF("rasterize_to_points_fwd_kernel", (cudaStream_t)stream);
+        SPL_DISPATCH_CDIM(channels, CALL);
+    }
 #undef CALL
     return check_launch("rasterize_to_points_fwd");
 }
@@ -818,7 +827,10 @@ extern "C" int splatad_rasterize_to_points_bwd(
             v_means2d_abs, v_means2d, v_conics, v_features, v_opacities, v_pix_vels,              \
             v_depth_compensations);                                                               \
     }
-    SPL_DISPATCH_CDIM(channels, CALL);
+    {
+        SPL_PROF("rasterize_to_points_bwd_kernel", (cudaStream_t)stream);
+        SPL_DISPATCH_CDIM(channels, CALL);
+    }
 #undef CALL
     return check_launch("rasterize_to_points_bwd");
 }

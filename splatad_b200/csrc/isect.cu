@@ -642,12 +642,22 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
                 "isect: tile bits (%u) + sensor bits (%u) exceed 32", g.tile_n_bits, cam_n_bits);
     SPL_REQUIRE((uint64_t)g.C * g.n_tiles <= 0xffffffffull, SPLATAD_ERR_KEY_BITS,
                 "isect: sensors * tiles does not fit 32 bits");
-    init_counters_kernel<<<1, 32, 0, st>>>(p.counters);
+    {
+        SPL_PROF("init_counters_kernel", st);
+        init_counters_kernel<<<1, 32, 0, st>>>(p.counters);
+    }
     const uint32_t cgrid = min(div_up(g.total, kThreads), (uint32_t)(8 * kNumSMs));
-    if (g.lidar)
-        isect_count_kernel<true><<<cgrid, kThreads, 0, st>>>(g.lid, g.total, tiles_per_gauss);
-    else
-        isect_count_kernel<false><<<cgrid, kThreads, 0, st>>>(g.cam, g.total, tiles_per_gauss);
+    if (g.lidar) {
+        {
+            SPL_PROF("isect_count_kernel", st);
+            isect_count_kernel<true><<<cgrid, kThreads, 0, st>>>(g.lid, g.total, tiles_per_gauss);
+        }
+    } else {
+        {
+            SPL_PROF("isect_count_kernel", st);
+            isect_count_kernel<false><<<cgrid, kThreads, 0, st>>>(g.cam, g.total, tiles_per_gauss);
+        }
+    }
 
     EmitArgs e{};
     e.total = g.total;
@@ -662,18 +672,36 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
                 s.depth_bits = g.depth_bits;
                 s.tiles_per_gauss = tiles_per_gauss;
                 s.total = g.total;
-                radix_upsweep_kernel<true><<<kSortGrid, kSortThreads, 0, st>>>(s, 0, 0xffu, p.hist);
-                radix_rowscan_kernel<<<kRadixBins, ((kSortGrid + 31) / 32) * 32, 0, st>>>(
-                    p.hist, kSortGrid, p.digit_totals);
-                radix_downsweep_kernel<true, false><<<kSortGrid, kSortThreads, 0, st>>>(
-                    s, 0, 0xffu, p.hist, p.digit_totals, ka, va, nofin, p.counters + CNT_NVIS);
+                {
+                    SPL_PROF("depthsort_upsweep", st);
+                    radix_upsweep_kernel<true><<<kSortGrid, kSortThreads, 0, st>>>(s, 0, 0xffu, p.hist);
+                }
+                {
+                    SPL_PROF("depthsort_rowscan", st);
+                    radix_rowscan_kernel<<<kRadixBins, ((kSortGrid + 31) / 32) * 32, 0, st>>>(
+                        p.hist, kSortGrid, p.digit_totals);
+                }
+                {
+                    SPL_PROF("depthsort_downsweep", st);
+                    radix_downsweep_kernel<true, false><<<kSortGrid, kSortThreads, 0, st>>>(
+                        s, 0, 0xffu, p.hist, p.digit_totals, ka, va, nofin, p.counters + CNT_NVIS);
+                }
             } else {
                 s.keys = ka; s.vals = va; s.n_ptr = p.counters + CNT_NVIS;
-                radix_upsweep_kernel<false><<<kSortGrid, kSortThreads, 0, st>>>(s, 8 * pass, 0xffu, p.hist);
-                radix_rowscan_kernel<<<kRadixBins, ((kSortGrid + 31) / 32) * 32, 0, st>>>(
-                    p.hist, kSortGrid, p.digit_totals);
-                radix_downsweep_kernel<false, false><<<kSortGrid, kSortThreads, 0, st>>>(
-                    s, 8 * pass, 0xffu, p.hist, p.digit_totals, kb, vb, nofin, nullptr);
+                {
+                    SPL_PROF("depthsort_upsweep", st);
+                    radix_upsweep_kernel<false><<<kSortGrid, kSortThreads, 0, st>>>(s, 8 * pass, 0xffu, p.hist);
+                }
+                {
+                    SPL_PROF("depthsort_rowscan", st);
+                    radix_rowscan_kernel<<<kRadixBins, ((kSortGrid + 31) / 32) * 32, 0, st>>>(
+                        p.hist, kSortGrid, p.digit_totals);
+                }
+                {
+                    SPL_PROF("depthsort_downsweep", st);
+                    radix_downsweep_kernel<false, false><<<kSortGrid, kSortThreads, 0, st>>>(
+                        s, 8 * pass, 0xffu, p.hist, p.digit_totals, kb, vb, nofin, nullptr);
+                }
                 uint32_t *t;
                 t = ka; ka = kb; kb = t;
                 t = va; va = vb; vb = t;
@@ -684,8 +712,14 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
         e.order = va;
         e.n_order_ptr = p.counters + CNT_NVIS;
     }
-    emit_blocksum_kernel<<<kSortGrid, kThreads, 0, st>>>(e, p.block_sums);
-    emit_scan_kernel<<<1, 1024, 0, st>>>(p.block_sums, kSortGrid, p.block_offs, p.counters);
+    {
+        SPL_PROF("emit_blocksum_kernel", st);
+        emit_blocksum_kernel<<<kSortGrid, kThreads, 0, st>>>(e, p.block_sums);
+    }
+    {
+        SPL_PROF("emit_scan_kernel", st);
+        emit_scan_kernel<<<1, 1024, 0, st>>>(p.block_sums, kSortGrid, p.block_offs, p.counters);
+    }
     if (host_counts != nullptr)
         cudaMemcpyAsync(host_counts, p.counters, sizeof(int64_t) * CNT_SLOTS, cudaMemcpyDeviceToHost, st);
     return check_launch("isect plan");
@@ -711,12 +745,19 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
     e.capacity = capacity;
 
     if (!sort) {
-        if (g.lidar)
-            emit_kernel<true, true><<<kSortGrid, kThreads, 0, st>>>(
-                g.lid, e, p.block_offs, nullptr, nullptr, isect_ids, flatten_ids, p.counters);
-        else
-            emit_kernel<false, true><<<kSortGrid, kThreads, 0, st>>>(
-                g.cam, e, p.block_offs, nullptr, nullptr, isect_ids, flatten_ids, p.counters);
+        if (g.lidar) {
+            {
+                SPL_PROF("emit_kernel", st);
+                emit_kernel<true, true><<<kSortGrid, kThreads, 0, st>>>(
+                    g.lid, e, p.block_offs, nullptr, nullptr, isect_ids, flatten_ids, p.counters);
+            }
+        } else {
+            {
+                SPL_PROF("emit_kernel", st);
+                emit_kernel<false, true><<<kSortGrid, kThreads, 0, st>>>(
+                    g.cam, e, p.block_offs, nullptr, nullptr, isect_ids, flatten_ids, p.counters);
+            }
+        }
     } else {
         FillWs f = carve_fill(fill_workspace, (uint64_t)capacity);
         SPL_REQUIRE(fill_workspace != nullptr && fill_workspace_bytes >= f.bytes,
@@ -725,12 +766,19 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
         // depth order left by the plan in valB (see isect_plan)
         e.order = p.valB;
         e.n_order_ptr = p.counters + CNT_NVIS;
-        if (g.lidar)
-            emit_kernel<true, false><<<kSortGrid, kThreads, 0, st>>>(
-                g.lid, e, p.block_offs, f.keyA, f.valA, nullptr, nullptr, p.counters);
-        else
-            emit_kernel<false, false><<<kSortGrid, kThreads, 0, st>>>(
-                g.cam, e, p.block_offs, f.keyA, f.valA, nullptr, nullptr, p.counters);
+        if (g.lidar) {
+            {
+                SPL_PROF("emit_kernel", st);
+                emit_kernel<true, false><<<kSortGrid, kThreads, 0, st>>>(
+                    g.lid, e, p.block_offs, f.keyA, f.valA, nullptr, nullptr, p.counters);
+            }
+        } else {
+            {
+                SPL_PROF("emit_kernel", st);
+                emit_kernel<false, false><<<kSortGrid, kThreads, 0, st>>>(
+                    g.cam, e, p.block_offs, f.keyA, f.valA, nullptr, nullptr, p.counters);
+            }
+        }
 
         const uint64_t span = (uint64_t)g.C * g.n_tiles;
         const uint32_t key_bits = max(1u, bit_length(span - 1));
@@ -750,16 +798,28 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
             s.n_cap = (uint32_t)(capacity < 0x7fffffffll ? capacity : 0x7fffffffll);
             const int shift = (int)(pass * bits_per);
             const uint32_t mask = (1u << bits_per) - 1u;
-            radix_upsweep_kernel<false><<<kSortGrid, kSortThreads, 0, st>>>(s, shift, mask, p.hist);
-            radix_rowscan_kernel<<<kRadixBins, ((kSortGrid + 31) / 32) * 32, 0, st>>>(
-                p.hist, kSortGrid, p.digit_totals);
+            {
+                SPL_PROF("tilesort_upsweep", st);
+                radix_upsweep_kernel<false><<<kSortGrid, kSortThreads, 0, st>>>(s, shift, mask, p.hist);
+            }
+            {
+                SPL_PROF("tilesort_rowscan", st);
+                radix_rowscan_kernel<<<kRadixBins, ((kSortGrid + 31) / 32) * 32, 0, st>>>(
+                    p.hist, kSortGrid, p.digit_totals);
+            }
             if (pass + 1 == npass) {
-                radix_downsweep_kernel<false, true><<<kSortGrid, kSortThreads, 0, st>>>(
-                    s, shift, mask, p.hist, p.digit_totals, nullptr, nullptr, fin, nullptr);
+                {
+                    SPL_PROF("tilesort_downsweep", st);
+                    radix_downsweep_kernel<false, true><<<kSortGrid, kSortThreads, 0, st>>>(
+                        s, shift, mask, p.hist, p.digit_totals, nullptr, nullptr, fin, nullptr);
+                }
             } else {
                 FinalOut nofin{};
-                radix_downsweep_kernel<false, false><<<kSortGrid, kSortThreads, 0, st>>>(
-                    s, shift, mask, p.hist, p.digit_totals, kb, vb, nofin, nullptr);
+                {
+                    SPL_PROF("tilesort_downsweep", st);
+                    radix_downsweep_kernel<false, false><<<kSortGrid, kSortThreads, 0, st>>>(
+                        s, shift, mask, p.hist, p.digit_totals, kb, vb, nofin, nullptr);
+                }
                 uint32_t *t;
                 t = ka; ka = kb; kb = t;
                 t = va; va = vb; vb = t;
@@ -913,7 +973,10 @@ extern "C" int splatad_isect_offset_encode(const int64_t *isect_ids, int64_t n_i
     SPL_REQUIRE(n_isects == 0 || isect_ids, SPLATAD_ERR_BAD_ARG, "isect_offset_encode: null input");
     const uint32_t tile_n_bits = bit_length(n_tiles);
     const uint32_t total = (uint32_t)(C * n_tiles);
-    offset_encode_kernel<<<div_up(total, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
-        isect_ids, nullptr, n_isects, C, (uint32_t)n_tiles, tile_n_bits, offsets);
+    {
+        SPL_PROF("offset_encode_kernel", (cudaStream_t)stream);
+        offset_encode_kernel<<<div_up(total, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+            isect_ids, nullptr, n_isects, C, (uint32_t)n_tiles, tile_n_bits, offsets);
+    }
     return check_launch("isect_offset_encode");
 }

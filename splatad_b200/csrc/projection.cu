@@ -783,11 +783,14 @@ extern "C" int splatad_lidar_projection_fwd(
     SPL_REQUIRE(radii && means2d && depths && conics && pix_vels && depth_compensations,
                 SPLATAD_ERR_BAD_ARG, "lidar_projection_fwd: null output");
     if (C == 0 || N == 0) return SPLATAD_OK;
-    lidar_projection_fwd_kernel<<<div_up(N, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
-        C, N, means, covars, quats, scales, velocities, viewmats, min_elevation, max_elevation,
-        min_azimuth, max_azimuth, linear_velocity, angular_velocity, rolling_shutter_time, eps2d,
-        near_plane, far_plane, radius_clip, radii, means2d, depths, conics, compensations,
-        pix_vels, depth_compensations);
+    {
+        SPL_PROF("lidar_projection_fwd_kernel", (cudaStream_t)stream);
+        lidar_projection_fwd_kernel<<<div_up(N, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+            C, N, means, covars, quats, scales, velocities, viewmats, min_elevation, max_elevation,
+            min_azimuth, max_azimuth, linear_velocity, angular_velocity, rolling_shutter_time, eps2d,
+            near_plane, far_plane, radius_clip, radii, means2d, depths, conics, compensations,
+            pix_vels, depth_compensations);
+    }
     return check_launch("lidar_projection_fwd");
 }
 
@@ -808,11 +811,14 @@ extern "C" int splatad_lidar_projection_bwd(
     SPL_REQUIRE(!v_compensations || compensations, SPLATAD_ERR_BAD_ARG,
                 "lidar_projection_bwd: v_compensations given without compensations");
     if (C == 0 || N == 0) return SPLATAD_OK;
-    lidar_projection_bwd_kernel<<<div_up(N, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
-        C, N, means, covars, quats, scales, velocities, viewmats, linear_velocity,
-        angular_velocity, rolling_shutter_time, eps2d, radii, conics, compensations, v_means2d,
-        v_depths, v_conics, v_compensations, v_pix_vels, v_depth_compensations, v_means, v_covars,
-        v_quats, v_scales, v_viewmats, v_velocities);
+    {
+        SPL_PROF("lidar_projection_bwd_kernel", (cudaStream_t)stream);
+        lidar_projection_bwd_kernel<<<div_up(N, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+            C, N, means, covars, quats, scales, velocities, viewmats, linear_velocity,
+            angular_velocity, rolling_shutter_time, eps2d, radii, conics, compensations, v_means2d,
+            v_depths, v_conics, v_compensations, v_pix_vels, v_depth_compensations, v_means, v_covars,
+            v_quats, v_scales, v_viewmats, v_velocities);
+    }
     return check_launch("lidar_projection_bwd");
 }
 
@@ -831,10 +837,13 @@ extern "C" int splatad_projection_fwd(
     SPL_REQUIRE(radii && means2d && depths && conics && pix_vels, SPLATAD_ERR_BAD_ARG,
                 "projection_fwd: null output");
     if (C == 0 || N == 0) return SPLATAD_OK;
-    projection_fwd_kernel<<<div_up(N, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
-        C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
-        linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
-        radius_clip, radii, means2d, depths, conics, compensations, pix_vels);
+    {
+        SPL_PROF("projection_fwd_kernel", (cudaStream_t)stream);
+        projection_fwd_kernel<<<div_up(N, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+            C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
+            linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
+            radius_clip, radii, means2d, depths, conics, compensations, pix_vels);
+    }
     return check_launch("projection_fwd");
 }
 
@@ -855,11 +864,14 @@ extern "C" int splatad_projection_bwd(
     SPL_REQUIRE(!v_compensations || compensations, SPLATAD_ERR_BAD_ARG,
                 "projection_bwd: v_compensations given without compensations");
     if (C == 0 || N == 0) return SPLATAD_OK;
-    projection_bwd_kernel<<<div_up(N, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
-        C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
-        linear_velocity, angular_velocity, rolling_shutter_time, eps2d, radii, conics,
-        compensations, v_means2d, v_depths, v_conics, v_compensations, v_pix_vels, v_means,
-        v_covars, v_quats, v_scales, v_viewmats, v_velocities);
+    {
+        SPL_PROF("projection_bwd_kernel", (cudaStream_t)stream);
+        projection_bwd_kernel<<<div_up(N, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+            C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
+            linear_velocity, angular_velocity, rolling_shutter_time, eps2d, radii, conics,
+            compensations, v_means2d, v_depths, v_conics, v_compensations, v_pix_vels, v_means,
+            v_covars, v_quats, v_scales, v_viewmats, v_velocities);
+    }
     return check_launch("projection_bwd");
 }
 
@@ -886,12 +898,18 @@ extern "C" int splatad_projection_packed_count(
     int32_t *counts = (int32_t *)workspace;
     int32_t *offsets = counts + (size_t)C * nblocks;
     cudaStream_t st = (cudaStream_t)stream;
-    projection_packed_fwd_kernel<<<nblocks, kThreads, 0, st>>>(
-        C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
-        linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
-        radius_clip, counts, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
-        nullptr, nullptr);
-    packed_scan_kernel<<<1, 1024, 0, st>>>(counts, offsets, C, nblocks, indptr, nnz_device);
+    {
+        SPL_PROF("projection_packed_fwd_kernel", st);
+        projection_packed_fwd_kernel<<<nblocks, kThreads, 0, st>>>(
+            C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
+            linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
+            radius_clip, counts, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+            nullptr, nullptr);
+    }
+    {
+        SPL_PROF("packed_scan_kernel", st);
+        packed_scan_kernel<<<1, 1024, 0, st>>>(counts, offsets, C, nblocks, indptr, nnz_device);
+    }
     return check_launch("projection_packed_count");
 }
 
@@ -909,11 +927,14 @@ extern "C" int splatad_projection_packed_fill(
     SPL_REQUIRE(C > 0 && N > 0, SPLATAD_ERR_BAD_ARG, "projection_packed_fill: empty input");
     const uint32_t nblocks = div_up(N, kThreads);
     const int32_t *offsets = (const int32_t *)workspace + (size_t)C * nblocks;
-    projection_packed_fwd_kernel<<<nblocks, kThreads, 0, (cudaStream_t)stream>>>(
-        C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
-        linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
-        radius_clip, nullptr, offsets, camera_ids, gaussian_ids, radii, means2d, depths, conics,
-        compensations, pix_vels);
+    {
+        SPL_PROF("projection_packed_fwd_kernel", (cudaStream_t)stream);
+        projection_packed_fwd_kernel<<<nblocks, kThreads, 0, (cudaStream_t)stream>>>(
+            C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
+            linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
+            radius_clip, nullptr, offsets, camera_ids, gaussian_ids, radii, means2d, depths, conics,
+            compensations, pix_vels);
+    }
     return check_launch("projection_packed_fill");
 }
 
@@ -936,10 +957,13 @@ extern "C" int splatad_projection_packed_bwd(
     SPL_REQUIRE(camera_ids && gaussian_ids && conics && v_means2d && v_depths && v_conics &&
                     v_pix_vels,
                 SPLATAD_ERR_BAD_ARG, "projection_packed_bwd: null input");
-    projection_packed_bwd_kernel<<<div_up(nnz, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
-        C, N, nnz, means, covars, quats, scales, velocities, viewmats, Ks, image_width,
-        image_height, linear_velocity, angular_velocity, rolling_shutter_time, eps2d, camera_ids,
-        gaussian_ids, conics, compensations, v_means2d, v_depths, v_conics, v_compensations,
-        v_pix_vels, sparse_grad, v_means, v_covars, v_quats, v_scales, v_viewmats, v_velocities);
+    {
+        SPL_PROF("projection_packed_bwd_kernel", (cudaStream_t)stream);
+        projection_packed_bwd_kernel<<<div_up(nnz, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+            C, N, nnz, means, covars, quats, scales, velocities, viewmats, Ks, image_width,
+            image_height, linear_velocity, angular_velocity, rolling_shutter_time, eps2d, camera_ids,
+            gaussian_ids, conics, compensations, v_means2d, v_depths, v_conics, v_compensations,
+            v_pix_vels, sparse_grad, v_means, v_covars, v_quats, v_scales, v_viewmats, v_velocities);
+    }
     return check_launch("projection_packed_bwd");
 }

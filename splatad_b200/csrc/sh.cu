@@ -283,8 +283,11 @@ extern "C" int splatad_sh_fwd(uint32_t n_elems, uint32_t K, uint32_t degrees_to_
     SPL_REQUIRE(smem <= 200 * 1024, SPLATAD_ERR_BAD_ARG, "sh_fwd: K too large");
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(sh_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sh_fwd_kernel<<<div_up(n_elems, kShThreads), kShThreads, smem, (cudaStream_t)stream>>>(
-        n_elems, K, (int)degrees_to_use, dirs, coeffs, masks, colors);
+    {
+        SPL_PROF("sh_fwd_kernel", (cudaStream_t)stream);
+        sh_fwd_kernel<<<div_up(n_elems, kShThreads), kShThreads, smem, (cudaStream_t)stream>>>(
+            n_elems, K, (int)degrees_to_use, dirs, coeffs, masks, colors);
+    }
     return check_launch("sh_fwd");
 }
 
@@ -301,7 +304,10 @@ extern "C" int splatad_sh_bwd(uint32_t n_elems, uint32_t K, uint32_t degrees_to_
     SPL_REQUIRE(smem <= 200 * 1024, SPLATAD_ERR_BAD_ARG, "sh_bwd: K too large");
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(sh_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sh_bwd_kernel<<<div_up(n_elems, kShThreads), kShThreads, smem, (cudaStream_t)stream>>>(
-        n_elems, K, (int)degrees_to_use, dirs, coeffs, masks, v_colors, v_coeffs, v_dirs);
+    {
+        SPL_PROF("sh_bwd_kernel", (cudaStream_t)stream);
+        sh_bwd_kernel<<<div_up(n_elems, kShThreads), kShThreads, smem, (cudaStream_t)stream>>>(
+            n_elems, K, (int)degrees_to_use, dirs, coeffs, masks, v_colors, v_coeffs, v_dirs);
+    }
     return check_launch("sh_bwd");
 }

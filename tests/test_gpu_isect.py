@@ -1,0 +1,136 @@
+"""Bit-exact parity of tile intersection (tiles per Gaussian, sorted isect ids, flatten ids,
+offsets) between the CUDA library and the CPU oracle / the reference's golden vectors."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import DEV, n, t
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(got, want, label):
+    for name, a, b in zip(("tiles_per_gauss", "isect_ids", "flatten_ids", "isect_offsets"), got, want):
+        a = n(a)
+        assert a.shape == b.shape, f"{label} {name}: shape {a.shape} vs {b.shape}"
+        if not np.array_equal(a, b):
+            bad = np.nonzero(a.reshape(-1) != b.reshape(-1))[0]
+            raise AssertionError(f"{label} {name}: {bad.size} of {a.size} entries differ, first at {bad[0]}: "
+                                 f"got {a.reshape(-1)[bad[0]]} want {b.reshape(-1)[bad[0]]}")
+
+
+def _run_cam(means2d, radii, depths, ts, tw, th, **kw):
+    from splatad_b200 import ops
+    C = kw.get("n_cameras") or means2d.shape[0]
+    tpg, ids, flat = ops.isect_tiles(t(means2d), t(radii, torch.int32), t(depths), ts, tw, th, **kw)
+    offs = ops.isect_offset_encode(ids, C, tw, th)
+    return tpg, ids, flat, offs
+
+
+def _run_lidar(means2d, radii, depths, eb, res, min_az, **kw):
+    from splatad_b200 import ops
+    C = kw.get("n_cameras") or means2d.shape[0]
+    tpg, ids, flat = ops.isect_lidar_tiles(t(means2d), t(radii), t(depths), t(eb), res, min_az, **kw)
+    n_az = math.ceil(360 / res)
+    offs = ops.isect_offset_encode(ids, C, n_az, len(eb) - 1)
+    return tpg, ids, flat, offs
+
+
+def test_isect_tiles_golden(golden):
+    g = golden("isect_tiles")
+    got = _run_cam(g["means2d"], g["radii"], g["depths"], int(g["tile_size"]), int(g["tile_width"]), int(g["tile_height"]))
+    _check(got, [g[k] for k in ("tiles_per_gauss", "isect_ids", "flatten_ids", "isect_offsets")], "golden camera")
+
+
+@pytest.mark.parametrize("name", ["isect_lidar_tiles", "isect_lidar_tiles_wrap"])
+def test_isect_lidar_tiles_golden(golden, name):
+    g = golden(name)
+    got = _run_lidar(g["means2d"], g["radii"], g["depths"], g["elev_boundaries"], float(g["tile_azim_resolution"]),
+                     float(g["min_azimuth"]))
+    _check(got, [g[k] for k in ("tiles_per_gauss", "isect_ids", "flatten_ids", "isect_offsets")], name)
+
+
+@pytest.mark.parametrize("C,N,W,H,ts", [(1, 1, 64, 64, 16), (2, 5000, 640, 480, 16), (3, 70000, 1920, 1080, 16),
+                                         (1, 3000, 100, 60, 7)])
+def test_isect_tiles_vs_oracle(C, N, W, H, ts):
+    from oracle import isect
+    g = torch.Generator().manual_seed(C * 1000 + N)
+    means2d = (torch.rand(C, N, 2, generator=g) * 1.4 - 0.2) * torch.tensor([W, H])
+    radii = torch.randint(0, 60, (C, N, 2), generator=g, dtype=torch.int32)
+    radii[:, ::9, 0] = 0
+    depths = torch.rand(C, N, generator=g) * 50
+    depths[:, 1::4] = depths[:, 0::4][:, : depths[:, 1::4].shape[1]]  # equal depths: ties keep flatten order
+    tw, th = math.ceil(W / ts), math.ceil(H / ts)
+    want = list(isect.isect_tiles(n(means2d), n(radii), n(depths), ts, tw, th))
+    want.append(isect.isect_offset_encode(want[1], C, tw, th))
+    got = _run_cam(means2d, radii, depths, ts, tw, th)
+    _check(got, want, f"camera C={C} N={N}")
+    # unsorted variant: emission in flatten order
+    from splatad_b200 import ops
+    tpg, ids, flat = ops.isect_tiles(t(means2d), t(radii, torch.int32), t(depths), ts, tw, th, sort=False)
+    w = isect.isect_tiles(n(means2d), n(radii), n(depths), ts, tw, th, sort=False)
+    _check((tpg, ids, flat), w, f"camera unsorted C={C} N={N}")
+
+
+def test_isect_tiles_packed():
+    from oracle import isect
+    C, N, W, H, ts = 3, 20000, 640, 480, 16
+    g = torch.Generator().manual_seed(77)
+    nnz = 30000
+    cam = torch.sort(torch.randint(0, C, (nnz,), generator=g)).values
+    gau = torch.randint(0, N, (nnz,), generator=g)
+    means2d = (torch.rand(nnz, 2, generator=g) * 1.2 - 0.1) * torch.tensor([W, H])
+    radii = torch.randint(1, 40, (nnz, 2), generator=g, dtype=torch.int32)
+    depths = torch.rand(nnz, generator=g) * 50
+    tw, th = math.ceil(W / ts), math.ceil(H / ts)
+    want = list(isect.isect_tiles(n(means2d), n(radii), n(depths), ts, tw, th, n_cameras=C, camera_ids=n(cam)))
+    want.append(isect.isect_offset_encode(want[1], C, tw, th))
+    got = _run_cam(means2d, radii, depths, ts, tw, th, packed=True, n_cameras=C, camera_ids=cam.to(DEV),
+                   gaussian_ids=gau.to(DEV))
+    _check(got, want, "camera packed")
+
+
+@pytest.mark.parametrize("C,N", [(1, 1), (1, 4000), (2, 60000)])
+def test_isect_lidar_tiles_vs_oracle(C, N):
+    from oracle import isect
+    from splatad_b200 import scenes
+    g = torch.Generator().manual_seed(C * 100 + N)
+    elev = scenes.beams_128()
+    eb = scenes.elevation_boundaries(elev, 8)
+    means2d = torch.stack([torch.rand(C, N, generator=g) * 360 - 180, torch.rand(C, N, generator=g) * 44 - 27], -1)
+    radii = torch.rand(C, N, 2, generator=g) * torch.tensor([12.0, 4.0])
+    radii[:, ::50, 0] = 200.0 + torch.rand(C, len(range(0, N, 50)), generator=g) * 300  # more than a full turn
+    radii[:, ::11, 0] = 0
+    depths = torch.rand(C, N, generator=g) * 80
+    depths[:, 1::4] = depths[:, 0::4][:, : depths[:, 1::4].shape[1]]
+    res = 0.2 * 32
+    want = list(isect.isect_lidar_tiles(n(means2d), n(radii), n(depths), n(eb), res, -180.0))
+    n_az = math.ceil(360 / res)
+    want.append(isect.isect_offset_encode(want[1], C, n_az, len(eb) - 1))
+    got = _run_lidar(means2d, radii, depths, eb, res, -180.0)
+    _check(got, want, f"lidar C={C} N={N}")
+
+
+def test_isect_empty_and_invisible():
+    from splatad_b200 import ops
+    z2 = torch.zeros(2, 0, 2, device=DEV)
+    tpg, ids, flat = ops.isect_tiles(z2, z2.int(), torch.zeros(2, 0, device=DEV), 16, 4, 4)
+    assert tpg.shape == (2, 0) and ids.numel() == 0 and flat.numel() == 0
+    offs = ops.isect_offset_encode(ids, 2, 4, 4)
+    assert offs.shape == (2, 4, 4) and int(offs.abs().sum()) == 0
+    # all Gaussians culled
+    m = torch.rand(1, 100, 2, device=DEV) * 64
+    tpg, ids, flat = ops.isect_tiles(m, torch.zeros(1, 100, 2, dtype=torch.int32, device=DEV),
+                                     torch.rand(1, 100, device=DEV), 16, 4, 4)
+    assert int(tpg.sum()) == 0 and ids.numel() == 0
+
+
+def test_isect_key_bits_error():
+    from splatad_b200 import ops
+    m = torch.rand(1, 10, 2, device=DEV)
+    with pytest.raises(RuntimeError):
+        ops.isect_tiles(m, torch.ones(1, 10, 2, dtype=torch.int32, device=DEV), torch.rand(1, 10, device=DEV),
+                        1, 1 << 16, 1 << 16)

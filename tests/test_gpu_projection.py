@@ -1,0 +1,343 @@
+"""Parity of the CUDA projections and SH kernels (called through the C ABI via splatad_b200.ops)
+against the CPU oracle and against the golden vectors of the reference's PyTorch code.
+
+Tolerances: forward 1e-4 relative + 1e-5 absolute (angles / pixels: + 1e-4 absolute because
+they are O(100) numbers in float32); gradients 1e-3 relative, judged against a float64 oracle.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import DEV, assert_close, n, rel_l2, t
+
+pytestmark = pytest.mark.gpu
+
+
+def _scene(N, seed, box="lidar"):
+    g = torch.Generator().manual_seed(seed)
+    means = torch.empty(N, 3)
+    if box == "lidar":
+        means[:, 0] = torch.rand(N, generator=g) * 60 - 30
+        means[:, 1] = torch.rand(N, generator=g) * 60 - 30
+        means[:, 2] = torch.rand(N, generator=g) * 8 - 3
+        ls = (-1.0, 0.5)
+    else:
+        means[:, 0] = torch.rand(N, generator=g) * 40 - 20
+        means[:, 1] = torch.rand(N, generator=g) * 10 - 5
+        means[:, 2] = torch.rand(N, generator=g) * 60 - 10
+        ls = (-1.5, 0.7)
+    quats = torch.randn(N, 4, generator=g)
+    scales = torch.exp(torch.randn(N, 3, generator=g) * ls[1] + ls[0])
+    vel = torch.randn(N, 3, generator=g) * 2
+    return means, quats, scales, vel, g
+
+
+def _lidar_sensors(C, g):
+    import math
+    vm = torch.eye(4)[None].repeat(C, 1, 1)
+    for c in range(C):
+        yaw = float(torch.rand(1, generator=g)) * 2 * math.pi
+        cy, sy = math.cos(yaw), math.sin(yaw)
+        vm[c, :3, :3] = torch.tensor([[cy, sy, 0.0], [-sy, cy, 0.0], [0.0, 0.0, 1.0]])
+        vm[c, :3, 3] = torch.randn(3, generator=g)
+    lin = torch.randn(C, 3, generator=g) * 5
+    ang = torch.randn(C, 3, generator=g) * 0.2
+    rs = torch.tensor([0.1, 0.0, 0.05][:C])
+    return vm, lin, ang, rs
+
+
+LIDAR_KW = dict(min_elevation=-30.0, max_elevation=25.0, min_azimuth=-180.0, max_azimuth=180.0, eps2d=0.017,
+                near_plane=0.5, far_plane=60.0)
+
+
+def _check_lidar_fwd(got, want, label):
+    radii, means2d, depths, conics, comps, pix_vels, dcomp = [n(x) for x in got]
+    o_radii, o_means2d, o_depths, o_conics, o_comps, o_pix_vels, o_dcomp = [n(x) for x in want]
+    vis, o_vis = radii[..., 0] > 0, o_radii[..., 0] > 0
+    assert (vis == o_vis).mean() > 0.9995, f"{label}: visibility differs on {(vis != o_vis).sum()} pairs"
+    m = vis & o_vis
+    assert vis.size < 1000 or m.sum() > 0
+    assert_close(label + " radii", radii[m], o_radii[m], 1e-4, 1e-5)
+    assert_close(label + " means2d", means2d[m], o_means2d[m], 1e-4, 1e-4)
+    assert_close(label + " depths", depths[m], o_depths[m], 1e-4, 1e-5)
+    assert_close(label + " conics", conics[m], o_conics[m], 1e-3, 1e-5)
+    assert_close(label + " pix_vels", pix_vels[m], o_pix_vels[m], 1e-3, 1e-3)
+    assert_close(label + " depth_comp", dcomp[m], o_dcomp[m], 2e-3, 1e-4)
+    if comps is not None:
+        assert_close(label + " compensations", comps[m], o_comps[m], 1e-3, 1e-5)
+    # culled entries are zero in the product
+    assert np.all(means2d[~vis] == 0) and np.all(conics[~vis] == 0) and np.all(depths[~vis] == 0)
+
+
+@pytest.mark.parametrize("use_covars", [False, True])
+@pytest.mark.parametrize("N", [1, 255, 5000])
+def test_lidar_projection_fwd(N, use_covars):
+    from oracle import projection as op
+    from splatad_b200 import ops
+
+    means, quats, scales, vel, g = _scene(N, 7 + N)
+    vm, lin, ang, rs = _lidar_sensors(3, g)
+    covars = None
+    if use_covars:
+        cov = op.quat_scale_to_covar(quats, scales)
+        covars = torch.stack([cov[:, 0, 0], cov[:, 0, 1], cov[:, 0, 2], cov[:, 1, 1], cov[:, 1, 2], cov[:, 2, 2]], -1)
+    want = op.fully_fused_lidar_projection(means, covars, quats, scales, vel, vm, lin, ang, rs,
+                                           radius_clip=0.05, calc_compensations=True, **LIDAR_KW)
+    got = ops.fully_fused_lidar_projection(
+        t(means), t(covars), None if use_covars else t(quats), None if use_covars else t(scales), t(vel),
+        t(vm), t(lin), t(ang), t(rs), radius_clip=0.05, calc_compensations=True, **LIDAR_KW)
+    _check_lidar_fwd(got, want, f"lidar N={N} covars={use_covars}")
+
+
+def test_lidar_projection_golden(golden):
+    from splatad_b200 import ops
+
+    g = golden("lidar_projection")
+    got = ops.fully_fused_lidar_projection(
+        t(g["means"]), None, t(g["quats"]), t(g["scales"]), t(g["velocities"]), t(g["viewmats"]),
+        t(g["lin"]), t(g["ang"]), t(g["rs"]), float(g["min_elevation"]), float(g["max_elevation"]),
+        float(g["min_azimuth"]), float(g["max_azimuth"]), float(g["eps2d"]), float(g["near_plane"]),
+        float(g["far_plane"]), 0.0, calc_compensations=True)
+    want = [torch.from_numpy(g[k]) for k in ("radii", "means2d", "depths", "conics", "compensations",
+                                             "pix_vels", "depth_compensations")]
+    # the reference leaves culled entries unset: zero them like the product does
+    vis = want[0][..., 0] > 0
+    want = [w * (vis[..., None] if w.dim() == 3 else vis) for w in want]
+    _check_lidar_fwd(got, want, "lidar golden")
+
+
+def _camera_sensors(g):
+    import math
+    C = 2
+    vm = torch.eye(4)[None].repeat(C, 1, 1)
+    vm[1, :3, 3] = torch.tensor([0.5, -0.2, 1.0])
+    c1, s1 = math.cos(0.2), math.sin(0.2)
+    vm[1, :3, :3] = torch.tensor([[c1, 0.0, s1], [0.0, 1.0, 0.0], [-s1, 0.0, c1]])
+    Ks = torch.tensor([[[300.0, 0.0, 160.0], [0.0, 310.0, 120.0], [0.0, 0.0, 1.0]]]).repeat(C, 1, 1)
+    lin = torch.tensor([[10.0, 0.0, 0.0], [0.0, 0.0, 3.0]])
+    ang = torch.tensor([[0.0, 0.1, 0.0], [0.05, 0.0, -0.1]])
+    rs = torch.tensor([0.03, 0.0])
+    return vm, Ks, lin, ang, rs
+
+
+CAM_KW = dict(eps2d=0.3, near_plane=0.2, far_plane=45.0)
+
+
+def _check_cam_fwd(got, want, label):
+    radii, means2d, depths, conics, comps, pix_vels = [n(x) for x in got]
+    o_radii, o_means2d, o_depths, o_conics, o_comps, o_pix_vels = [n(x) for x in want]
+    vis, o_vis = radii[..., 0] > 0, o_radii[..., 0] > 0
+    assert (vis == o_vis).mean() > 0.999, f"{label}: visibility differs on {(vis != o_vis).sum()} pairs"
+    m = vis & o_vis
+    assert vis.size < 1000 or m.sum() > 0
+    if m.sum() == 0:
+        return
+    # integer truncation of 3 sigma: a one-ulp difference can move a radius by one pixel
+    assert np.abs(radii[m].astype(np.int64) - o_radii[m]).max() <= 1
+    assert (radii[m] == o_radii[m]).mean() > 0.998
+    assert_close(label + " means2d", means2d[m], o_means2d[m], 1e-4, 1e-3)
+    assert_close(label + " depths", depths[m], o_depths[m], 1e-4, 1e-5)
+    assert_close(label + " conics", conics[m], o_conics[m], 1e-3, 1e-6)
+    assert_close(label + " pix_vels", pix_vels[m], o_pix_vels[m], 1e-3, 1e-2)
+    if comps is not None:
+        assert_close(label + " compensations", comps[m], o_comps[m], 1e-3, 1e-5)
+
+
+@pytest.mark.parametrize("N", [1, 300, 5000])
+def test_camera_projection_fwd(N):
+    from oracle import projection as op
+    from splatad_b200 import ops
+
+    means, quats, scales, vel, g = _scene(N, 11 + N, "cam")
+    vm, Ks, lin, ang, rs = _camera_sensors(g)
+    want = op.fully_fused_projection(means, None, quats, scales, vel, vm, Ks, 320, 240, lin, ang, rs,
+                                     calc_compensations=True, **CAM_KW)
+    got = ops.fully_fused_projection(t(means), None, t(quats), t(scales), t(vel), t(vm), t(Ks), 320, 240,
+                                     t(lin), t(ang), t(rs), calc_compensations=True, **CAM_KW)
+    _check_cam_fwd(got, want, f"camera N={N}")
+
+
+def test_camera_projection_golden(golden):
+    from splatad_b200 import ops
+
+    g = golden("camera_projection")
+    got = ops.fully_fused_projection(
+        t(g["means"]), None, t(g["quats"]), t(g["scales"]), t(g["velocities"]), t(g["viewmats"]), t(g["Ks"]),
+        int(g["width"]), int(g["height"]), t(g["lin"]), t(g["ang"]), t(g["rs"]), float(g["eps2d"]),
+        float(g["near_plane"]), float(g["far_plane"]), calc_compensations=True)
+    want = [torch.from_numpy(g[k]) for k in ("radii", "means2d", "depths", "conics", "compensations", "pix_vels")]
+    _check_cam_fwd(got, want, "camera golden")
+
+
+def test_camera_projection_packed_matches_unpacked():
+    from splatad_b200 import ops
+
+    means, quats, scales, vel, g = _scene(5000, 21, "cam")
+    vm, Ks, lin, ang, rs = _camera_sensors(g)
+    args = (t(means), None, t(quats), t(scales), t(vel), t(vm), t(Ks), 320, 240, t(lin), t(ang), t(rs))
+    radii, means2d, depths, conics, comps, pix_vels = ops.fully_fused_projection(
+        *args, calc_compensations=True, **CAM_KW)
+    cam, gau, p_radii, p_means2d, p_depths, p_conics, p_comps, p_pix_vels = ops.fully_fused_projection(
+        *args, packed=True, calc_compensations=True, **CAM_KW)
+    vis = conics.abs().sum(-1) > 0  # survived every cull (the integer radius may still be 0)
+    c_ref, g_ref = torch.nonzero(vis, as_tuple=True)
+    assert torch.equal(cam, c_ref) and torch.equal(gau, g_ref)
+    assert torch.equal(p_radii, radii[c_ref, g_ref])
+    assert torch.equal(p_means2d, means2d[c_ref, g_ref])
+    assert torch.equal(p_depths, depths[c_ref, g_ref])
+    assert torch.equal(p_conics, conics[c_ref, g_ref])
+    assert torch.equal(p_comps, comps[c_ref, g_ref])
+    assert torch.equal(p_pix_vels, pix_vels[c_ref, g_ref])
+
+
+def _grad_check(label, got, want, rel=1e-3):
+    got, want = n(got), n(want)
+    rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+    assert rel_l2(got, want) < rel, f"{label}: relative L2 error {rel_l2(got, want):.3e}"
+    # elementwise: 1e-3 relative, with an absolute floor of 1e-3 of the gradient's RMS
+    assert_close(label, got, want, rel, rel * rms, max_bad_frac=1e-3)
+
+
+@pytest.mark.parametrize("use_covars", [False, True])
+def test_lidar_projection_bwd(use_covars):
+    from oracle import projection as op
+    from splatad_b200 import ops
+
+    N = 3000
+    means, quats, scales, vel, g = _scene(N, 31)
+    vm, lin, ang, rs = _lidar_sensors(3, g)
+    cov6 = None
+    if use_covars:
+        cov = op.quat_scale_to_covar(quats, scales)
+        cov6 = torch.stack([cov[:, 0, 0], cov[:, 0, 1], cov[:, 0, 2], cov[:, 1, 1], cov[:, 1, 2], cov[:, 2, 2]], -1)
+
+    def leaves(dtype, device):
+        out = {}
+        for k, v in dict(means=means, quats=quats, scales=scales, covars=cov6, vel=vel, vm=vm).items():
+            out[k] = None if v is None else v.to(dtype).to(device).requires_grad_(True)
+        return out
+
+    L = leaves(torch.float32, DEV)
+    with ops.velocity_grads(True):
+        got = ops.fully_fused_lidar_projection(
+            L["means"], L["covars"], None if use_covars else L["quats"], None if use_covars else L["scales"],
+            L["vel"], L["vm"], t(lin), t(ang), t(rs), calc_compensations=True, **LIDAR_KW)
+    O = leaves(torch.float64, "cpu")
+    want = op.fully_fused_lidar_projection(
+        O["means"], O["covars"], O["quats"], O["scales"], O["vel"], O["vm"], lin.double(), ang.double(),
+        rs.double(), calc_compensations=True, **LIDAR_KW)
+    both = (got[0][..., 0] > 0).cpu() & (want[0][..., 0] > 0)
+    gen = torch.Generator().manual_seed(5)
+    loss_g, loss_o = 0.0, 0.0
+    for a, b in zip(got[1:], want[1:]):
+        cot = torch.randn(b.shape, generator=gen, dtype=torch.float64)
+        cot = cot * (both[..., None] if b.dim() == 3 else both)
+        loss_g = loss_g + (a * cot.float().to(DEV)).sum()
+        loss_o = loss_o + (b * cot).sum()
+    names = ["means", "covars"] if use_covars else ["means", "quats", "scales"]
+    names += ["vel", "vm"]
+    g_got = torch.autograd.grad(loss_g, [L[k] for k in names])
+    g_want = torch.autograd.grad(loss_o, [O[k] for k in names])
+    for k, a, b in zip(names, g_got, g_want):
+        if k == "vm":
+            a, b = a[:, :3, :], b[:, :3, :]
+        _grad_check(f"lidar bwd d/d{k}", a, b)
+
+
+@pytest.mark.parametrize("packed,sparse", [(False, False), (True, False), (True, True)])
+def test_camera_projection_bwd(packed, sparse):
+    from oracle import projection as op
+    from splatad_b200 import ops
+
+    N = 3000
+    means, quats, scales, vel, g = _scene(N, 41, "cam")
+    vm, Ks, lin, ang, rs = _camera_sensors(g)
+
+    def leaves(dtype, device):
+        return {k: v.to(dtype).to(device).requires_grad_(True)
+                for k, v in dict(means=means, quats=quats, scales=scales, vel=vel, vm=vm).items()}
+
+    O = leaves(torch.float64, "cpu")
+    want = op.fully_fused_projection(O["means"], None, O["quats"], O["scales"], O["vel"], O["vm"], Ks.double(),
+                                     320, 240, lin.double(), ang.double(), rs.double(),
+                                     calc_compensations=True, **CAM_KW)
+    L = leaves(torch.float32, DEV)
+    with ops.velocity_grads(not sparse):
+        got = ops.fully_fused_projection(L["means"], None, L["quats"], L["scales"], L["vel"], L["vm"], t(Ks), 320,
+                                         240, t(lin), t(ang), t(rs), packed=packed, sparse_grad=sparse,
+                                         calc_compensations=True, **CAM_KW)
+    gen = torch.Generator().manual_seed(6)
+    loss_g, loss_o = 0.0, 0.0
+    if packed:
+        cam, gau = got[0].cpu(), got[1].cpu()
+        got_vals = got[3:]
+        vis_o = want[3].abs().sum(-1) > 0
+        keep = vis_o[cam, gau]
+        for a, b in zip(got_vals, want[1:]):
+            cot = torch.randn(b.shape, generator=gen, dtype=torch.float64)
+            cot_rows = cot[cam, gau] * (keep[..., None] if b.dim() == 3 else keep)
+            loss_g = loss_g + (a * cot_rows.float().to(DEV)).sum()
+            dense = torch.zeros_like(cot)
+            dense[cam, gau] = cot_rows
+            loss_o = loss_o + (b * dense).sum()
+    else:
+        both = (got[3].abs().sum(-1) > 0).cpu() & (want[3].abs().sum(-1) > 0)
+        for a, b in zip(got[1:], want[1:]):
+            cot = torch.randn(b.shape, generator=gen, dtype=torch.float64)
+            cot = cot * (both[..., None] if b.dim() == 3 else both)
+            loss_g = loss_g + (a * cot.float().to(DEV)).sum()
+            loss_o = loss_o + (b * cot).sum()
+    names = ["means", "quats", "scales", "vm"] + ([] if sparse else ["vel"])
+    g_got = torch.autograd.grad(loss_g, [L[k] for k in names])
+    g_want = torch.autograd.grad(loss_o, [O[k] for k in names])
+    for k, a, b in zip(names, g_got, g_want):
+        if a.is_sparse:
+            a = a.to_dense()
+        if k == "vm":
+            a, b = a[:, :3, :], b[:, :3, :]
+        _grad_check(f"camera bwd packed={packed} sparse={sparse} d/d{k}", a, b)
+
+
+def test_velocity_gradient_default_is_none():
+    """The reference's fused projections return no gradient for ``velocities``; so does the default here."""
+    from splatad_b200 import ops
+
+    means, quats, scales, vel, g = _scene(500, 51)
+    vm, lin, ang, rs = _lidar_sensors(3, g)
+    v = t(vel).requires_grad_(True)
+    m = t(means).requires_grad_(True)
+    out = ops.fully_fused_lidar_projection(m, None, t(quats), t(scales), v, t(vm), t(lin), t(ang), t(rs), **LIDAR_KW)
+    out[1].sum().backward()
+    assert v.grad is None and m.grad is not None
+
+
+@pytest.mark.parametrize("degree", [0, 1, 2, 3, 4])
+def test_spherical_harmonics(degree, golden):
+    from oracle import projection as op
+    from splatad_b200 import ops
+
+    g = golden("spherical_harmonics")
+    dirs, coeffs = torch.from_numpy(g["dirs"]), torch.from_numpy(g["coeffs"])
+    got = ops.spherical_harmonics(degree, t(dirs), t(coeffs))
+    assert_close(f"sh golden deg {degree}", n(got), g[f"colors_deg{degree}"], 1e-4, 1e-5)
+
+    gen = torch.Generator().manual_seed(8)
+    M = 1000
+    d = torch.randn(M, 3, generator=gen)
+    c = torch.randn(M, 16 if degree <= 3 else 25, 3, generator=gen)
+    masks = torch.rand(M, generator=gen) > 0.2
+    cot = torch.randn(M, 3, generator=gen, dtype=torch.float64)
+    dg, cg = t(d).requires_grad_(True), t(c).requires_grad_(True)
+    out = ops.spherical_harmonics(degree, dg, cg, masks=masks.to(DEV))
+    do, co = d.double().requires_grad_(True), c.double().requires_grad_(True)
+    ref = op.spherical_harmonics(degree, do, co, masks=masks)
+    assert_close(f"sh fwd deg {degree}", n(out), n(ref), 1e-4, 1e-5)
+    assert np.all(n(out)[~masks.numpy()] == 0)
+    (out * cot.float().to(DEV)).sum().backward()
+    (ref * cot).sum().backward()
+    _grad_check(f"sh d/dcoeffs deg {degree}", cg.grad, co.grad)
+    if degree > 0:
+        _grad_check(f"sh d/ddirs deg {degree}", dg.grad, do.grad)
+    else:
+        assert float(dg.grad.abs().max()) == 0.0

@@ -1,0 +1,82 @@
+"""CPU-only checks of the host side: the C-ABI library loads and exports every declared symbol,
+the Python ops refuse CPU tensors (no fallback), scene generators and sharding helpers."""
+
+import ctypes
+import os
+
+import pytest
+import torch
+
+
+def test_header_symbols_are_exported():
+    from splatad_b200 import _lib
+    if not os.path.exists(_lib.LIB_PATH):
+        _lib.build()
+    decls = _lib.parse_header()
+    assert len(decls) >= 24
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for name in decls:
+        assert hasattr(lib, name), f"{name} is declared in include/splatad_b200.h but not exported"
+    loaded = _lib.load()
+    assert loaded.splatad_version() == 100
+    # workspace queries are pure host functions
+    assert loaded.splatad_isect_plan_workspace_bytes(1000) > 4 * 4 * 1000
+    assert loaded.splatad_isect_fill_workspace_bytes(1000) >= 4 * 4 * 1000
+
+
+def test_error_mapping():
+    from splatad_b200 import _lib
+    lib = _lib.load()
+    # null output pointer is rejected before any CUDA call
+    rc = lib.splatad_isect_offset_encode(None, 0, 1, 4, 4, None, None)
+    assert rc == _lib.ERR_BAD_ARG
+    with pytest.raises(ValueError):
+        _lib.check(rc)
+    assert "isect_offset_encode" in _lib.last_error()
+    rc = lib.splatad_rasterize_to_pixels_fwd(1, 0, None, None, None, 100, None, None, None, None, 8, 8, 16, 1, 1,
+                                             None, None, None, None, None, None)
+    assert rc == _lib.ERR_CHANNELS
+
+
+def test_ops_refuse_cpu_tensors():
+    import splatad_b200
+    N = 8
+    with pytest.raises(RuntimeError, match="CUDA"):
+        splatad_b200.fully_fused_lidar_projection(
+            torch.rand(N, 3), None, torch.rand(N, 4), torch.rand(N, 3), None, torch.eye(4)[None],
+            torch.zeros(1, 3), torch.zeros(1, 3), torch.zeros(1))
+
+
+def test_api_signatures_match_reference_names():
+    import inspect
+
+    import splatad_b200
+    sig = inspect.signature(splatad_b200.lidar_rasterization)
+    assert list(sig.parameters)[:9] == ["means", "quats", "scales", "opacities", "lidar_features", "velocities",
+                                        "viewmats", "raster_pts", "tile_elevation_boundaries"]
+    assert sig.parameters["eps2d"].default == 0.017 and sig.parameters["tile_width"].default == 32
+    sig = inspect.signature(splatad_b200.rasterization)
+    assert list(sig.parameters)[:10] == ["means", "quats", "scales", "opacities", "colors", "velocities",
+                                         "viewmats", "Ks", "width", "height"]
+    assert sig.parameters["packed"].default is True and sig.parameters["eps2d"].default == 0.3
+
+
+def test_scene_generators_are_seeded_and_shaped():
+    from splatad_b200 import scenes
+    a, b = scenes.config0(), scenes.config0()
+    assert torch.equal(a["means"], b["means"]) and torch.equal(a["raster_pts"], b["raster_pts"])
+    assert a["raster_pts"].shape == (1, 32, 512, 4) and a["lidar_features"].shape == (1, 20000, 4)
+    assert a["tile_elevation_boundaries"].shape == (5,)
+    e = scenes.beams_128()
+    assert e.numel() == 128 and float(e[0]) == -25.0 and abs(float(e[-1]) - 15.0) < 1e-5
+    assert abs(float(e[60] - e[59]) - 0.1) < 1e-4
+    c2 = scenes.config2(N=1000)
+    assert c2["raster_pts"].shape == (1, 128, 1800, 4) and c2["tile_elevation_boundaries"].shape == (17,)
+    assert float(c2["raster_pts"][0, 0, 0, 3]) == pytest.approx(-0.05) and c2["azimuth_resolution"] == pytest.approx(0.2)
+    c1 = scenes.config1(N=1000)
+    assert c1["colors"].shape == (1000, 16, 3) and c1["width"] == 1920
+    moving = (c1["velocities"].abs().sum(-1) > 0).float().mean()
+    assert 0.05 < float(moving) < 0.16
+    vm = scenes.yawed_camera_viewmats([0, 60, 120])
+    for R in vm[:, :3, :3]:
+        assert torch.allclose(R @ R.T, torch.eye(3), atol=1e-6) and float(torch.det(R)) == pytest.approx(1.0)

@@ -85,6 +85,32 @@ def lidar_rasterization(
     return out["render_colors"], out["render_alphas"], out["alpha_sum"], meta
 
 
+def lidar_from_projection(radii, means2d, depths, conics, opacities, pix_vels, depth_compensations,
+                          lidar_features, raster_pts, tile_elevation_boundaries, min_azimuth=-180,
+                          max_azimuth=180, n_elevation_channels=32, azimuth_resolution=0.1, tile_width=32,
+                          tile_height=8, compute_alpha_sum_until_points=True,
+                          compute_alpha_sum_until_points_threshold=0.2, dtype=np.float32):
+    """Tile intersection + compositing of the oracle on GIVEN projection outputs ([C,N,..] numpy
+    arrays, e.g. the product's own), so that the list stages are compared on identical inputs.
+    Returns dict(tiles_per_gauss, isect_ids, flatten_ids, isect_offsets, out=<composite dict>)."""
+    C = means2d.shape[0]
+    n_el = math.ceil(n_elevation_channels / tile_height)
+    tile_az = azimuth_resolution * tile_width
+    n_az = math.ceil((max_azimuth - min_azimuth) / tile_az)
+    tpg, ids, flat = isect.isect_lidar_tiles(np.asarray(means2d, np.float32), np.asarray(radii, np.float32),
+                                             np.asarray(depths, np.float32),
+                                             np.asarray(tile_elevation_boundaries, np.float32), tile_az,
+                                             min_azimuth)
+    offsets = isect.isect_offset_encode(ids, C, n_az, n_el)
+    H, W = raster_pts.shape[1:3]
+    feats = np.concatenate([np.asarray(lidar_features), np.asarray(depths)[..., None]], axis=-1)
+    out = composite.rasterize_to_points_fwd(means2d, conics, feats, opacities, pix_vels, depth_compensations,
+                                            None, np.asarray(raster_pts), W, H, tile_width, tile_height, offsets,
+                                            flat, compute_alpha_sum_until_points,
+                                            compute_alpha_sum_until_points_threshold, dtype=dtype)
+    return dict(tiles_per_gauss=tpg, isect_ids=ids, flatten_ids=flat, isect_offsets=offsets, out=out)
+
+
 def rasterization(
     means, quats, scales, opacities, colors, velocities, viewmats, Ks, width, height,
     linear_velocity=None, angular_velocity=None, rolling_shutter_time=None, near_plane=0.01,

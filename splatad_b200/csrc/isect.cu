@@ -217,6 +217,16 @@ __device__ __forceinline__ void block_range(uint32_t n, uint32_t &lo, uint32_t &
     hi = (uint32_t)(h < n ? h : n);
 }
 
+// Adds one key to the warp-private digit histogram; lanes holding the same digit are merged
+// into one shared-memory add.
+__device__ __forceinline__ void hist_add(uint32_t *wh_row, bool valid, uint32_t key, int shift,
+                                         uint32_t mask, uint32_t lane) {
+    const uint32_t digit = valid ? ((key >> shift) & mask) : kRadixBins;
+    const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+    if (valid && lane == (uint32_t)(__ffs(peers) - 1)) wh_row[digit] += __popc(peers);
+    __syncwarp();
+}
+
 template <bool kGen>
 __global__ void __launch_bounds__(kSortThreads)
 radix_upsweep_kernel(PassSrc s, int shift, uint32_t mask, uint32_t *__restrict__ hist) {
@@ -225,23 +235,43 @@ radix_upsweep_kernel(PassSrc s, int shift, uint32_t mask, uint32_t *__restrict__
     __syncthreads();
     const uint32_t n = src_count<kGen>(s);
     uint32_t lo, hi;
-    block_range(n, lo, hi);
+    block_range(n, lo, hi);   // lo is a multiple of 4096
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (uint32_t base = lo; base < hi; base += kSortThreads) {
+    uint32_t *row = wh[warp];
+    const uint32_t *kp = kGen ? s.depth_bits : s.keys;
+    const bool aligned = (reinterpret_cast<uintptr_t>(kp) & 15u) == 0 &&
+                         (!kGen || (reinterpret_cast<uintptr_t>(s.tiles_per_gauss) & 15u) == 0);
+    constexpr uint32_t kStep = kSortThreads * 8;   // two 128-bit loads per thread and iteration
+    uint32_t base = lo;
+    if (aligned) {
+        for (; base + kStep <= hi; base += kStep) {
+            const uint32_t i0 = base + threadIdx.x * 4, i1 = i0 + kSortThreads * 4;
+            const uint4 k0 = __ldg(reinterpret_cast<const uint4 *>(kp + i0));
+            const uint4 k1 = __ldg(reinterpret_cast<const uint4 *>(kp + i1));
+            int4 c0 = make_int4(1, 1, 1, 1), c1 = c0;
+            if (kGen) {
+                c0 = __ldg(reinterpret_cast<const int4 *>(s.tiles_per_gauss + i0));
+                c1 = __ldg(reinterpret_cast<const int4 *>(s.tiles_per_gauss + i1));
+            }
+            hist_add(row, c0.x > 0, k0.x, shift, mask, lane);
+            hist_add(row, c0.y > 0, k0.y, shift, mask, lane);
+            hist_add(row, c0.z > 0, k0.z, shift, mask, lane);
+            hist_add(row, c0.w > 0, k0.w, shift, mask, lane);
+            hist_add(row, c1.x > 0, k1.x, shift, mask, lane);
+            hist_add(row, c1.y > 0, k1.y, shift, mask, lane);
+            hist_add(row, c1.z > 0, k1.z, shift, mask, lane);
+            hist_add(row, c1.w > 0, k1.w, shift, mask, lane);
+        }
+    }
+    for (; base < hi; base += kSortThreads) {
         const uint32_t i = base + threadIdx.x;
         bool valid = i < hi;
         uint32_t key = 0;
         if (valid) {
-            if (kGen) {
-                valid = s.tiles_per_gauss[i] > 0;
-                if (valid) key = s.depth_bits[i];
-            } else {
-                key = s.keys[i];
-            }
+            if (kGen) valid = s.tiles_per_gauss[i] > 0;
+            if (valid) key = kp[i];
         }
-        const uint32_t digit = valid ? ((key >> shift) & mask) : kRadixBins;
-        const uint32_t peers = __match_any_sync(0xffffffffu, digit);
-        if (valid && lane == (uint32_t)(__ffs(peers) - 1)) atomicAdd(&wh[warp][digit], __popc(peers));
+        hist_add(row, valid, key, shift, mask, lane);
     }
     __syncthreads();
     for (uint32_t d = threadIdx.x; d < kRadixBins; d += blockDim.x) {
@@ -465,50 +495,78 @@ emit_scan_kernel(const unsigned long long *__restrict__ block_sums, uint32_t nbl
     }
 }
 
-template <bool kLidar, bool kDirect64>
+// Exclusive offset of every entry of the emission order: eoff[p] = number of intersections
+// emitted before entry p. Same block ranges as emit_blocksum_kernel.
 __global__ void __launch_bounds__(kThreads)
-emit_kernel(GridArgs<kLidar> a, EmitArgs e, const unsigned long long *__restrict__ block_offs,
-            uint32_t *__restrict__ keys_out, uint32_t *__restrict__ vals_out,
-            int64_t *__restrict__ ids64_out, int32_t *__restrict__ flat_out,
-            int64_t *__restrict__ counters) {
-    __shared__ float sb[kLidar ? kMaxElevSmem : 1];
-    __shared__ uint32_t loc[kThreads + 1];
-    __shared__ Rect rects[kThreads];
-    __shared__ uint32_t sidx[kThreads];
-    __shared__ uint32_t scid[kThreads];
+emit_offsets_kernel(EmitArgs e, const unsigned long long *__restrict__ block_offs,
+                    uint32_t *__restrict__ eoff) {
     __shared__ uint32_t wt[33];
-    stage_boundaries<kLidar>(a, sb);
     uint32_t lo, hi;
     emit_range(e, lo, hi);
-    unsigned long long running = block_offs[blockIdx.x];
-    bool overflow = false;
+    uint32_t running = (uint32_t)block_offs[blockIdx.x];
     for (uint32_t base = lo; base < hi; base += kThreads) {
         const uint32_t p = base + threadIdx.x;
         uint32_t cnt = 0;
         if (p < hi) {
             const uint32_t idx = e.order ? e.order[p] : p;
-            Rect r;
-            if (elem_rect<kLidar>(a, idx, r)) {
-                cnt = (uint32_t)max(rect_count(r), 0);
-                rects[threadIdx.x] = r;
-            }
-            sidx[threadIdx.x] = idx;
-            scid[threadIdx.x] = e.camera_ids ? (uint32_t)e.camera_ids[idx] : idx / e.N;
+            const int32_t c = e.tiles_per_gauss[idx];
+            cnt = (uint32_t)(c > 0 ? c : 0);
         }
         uint32_t chunk_total;
         const uint32_t ex = block_excl_scan(cnt, wt, chunk_total);
-        loc[threadIdx.x] = ex;
-        if (threadIdx.x == 0) loc[kThreads] = chunk_total;
+        if (p < hi) eoff[p] = running + ex;
+        running += chunk_total;
+    }
+}
+
+constexpr uint32_t kEmitUnit = 4096;   // intersections per work unit of the emit kernel
+
+// last p in [lo, hi] with eoff[p] <= q (eoff is non-decreasing, eoff[lo] <= q)
+__device__ __forceinline__ uint32_t find_entry(const uint32_t *__restrict__ eoff, uint32_t lo,
+                                               uint32_t hi, uint32_t q) {
+    while (lo < hi) {
+        const uint32_t m = (lo + hi + 1) >> 1;
+        if (__ldg(eoff + m) <= q) lo = m; else hi = m - 1;
+    }
+    return lo;
+}
+
+// Writes the intersections in emission order, balanced by OUTPUT position: depth-sorted
+// Gaussians have wildly different tile counts (the nearest ones cover thousands of tiles), so
+// work is split into units of kEmitUnit consecutive outputs and each output finds its source
+// entry by binary search in the offsets of the entries that overlap its unit.
+template <bool kLidar, bool kDirect64>
+__global__ void __launch_bounds__(kThreads)
+emit_kernel(GridArgs<kLidar> a, EmitArgs e, const uint32_t *__restrict__ eoff,
+            const int64_t *__restrict__ counters_in, uint32_t *__restrict__ keys_out,
+            uint32_t *__restrict__ vals_out, int64_t *__restrict__ ids64_out,
+            int32_t *__restrict__ flat_out, int64_t *__restrict__ counters) {
+    __shared__ float sb[kLidar ? kMaxElevSmem : 1];
+    __shared__ uint32_t window[2];
+    stage_boundaries<kLidar>(a, sb);
+    const uint32_t n_entries = e.order ? (uint32_t)(*e.n_order_ptr) : e.total;
+    int64_t m64 = counters_in[CNT_NISECT];
+    bool overflow = false;
+    if (m64 > e.capacity) { m64 = e.capacity; overflow = true; }
+    const uint32_t M = (uint32_t)m64;
+    if (n_entries == 0) return;
+    const uint32_t n_units = (M + kEmitUnit - 1) / kEmitUnit;
+    for (uint32_t u = blockIdx.x; u < n_units; u += gridDim.x) {
+        const uint32_t q_lo = u * kEmitUnit;
+        const uint32_t q_hi = min(M, q_lo + kEmitUnit);   // exclusive
         __syncthreads();
-        for (uint32_t j = threadIdx.x; j < chunk_total; j += kThreads) {
-            // last s with loc[s] <= j
-            uint32_t l = 0, h = kThreads;
-            while (h - l > 1) {
-                const uint32_t m = (l + h) >> 1;
-                if (loc[m] <= j) l = m; else h = m;
-            }
-            const Rect r = rects[l];
-            const uint32_t k = j - loc[l];
+        if (threadIdx.x < 2) {
+            const uint32_t q = threadIdx.x == 0 ? q_lo : q_hi - 1;
+            window[threadIdx.x] = find_entry(eoff, 0, n_entries - 1, q);
+        }
+        __syncthreads();
+        const uint32_t p_lo = window[0], p_hi = window[1];
+        for (uint32_t q = q_lo + threadIdx.x; q < q_hi; q += kThreads) {
+            const uint32_t p = find_entry(eoff, p_lo, p_hi, q);
+            const uint32_t idx = e.order ? __ldg(e.order + p) : p;
+            Rect r;
+            if (!elem_rect<kLidar>(a, idx, r)) continue;   // cannot happen: entry has a positive count
+            const uint32_t k = q - __ldg(eoff + p);
             const uint32_t w = (uint32_t)(r.x1 - r.x0);
             const uint32_t dy = k / w;
             const uint32_t dx = k - dy * w;
@@ -523,22 +581,19 @@ emit_kernel(GridArgs<kLidar> a, EmitArgs e, const unsigned long long *__restrict
             } else {
                 tile = (uint32_t)ty * a.cam.tile_width + (uint32_t)tx;
             }
-            const unsigned long long q = running + j;
-            if ((int64_t)q >= e.capacity) { overflow = true; continue; }
-            const uint32_t idx = sidx[l];
+            const uint32_t cid = e.camera_ids ? (uint32_t)e.camera_ids[idx] : idx / e.N;
             if (kDirect64) {
-                ids64_out[q] = ((int64_t)scid[l] << (32 + e.tile_n_bits)) | ((int64_t)tile << 32) |
+                ids64_out[q] = ((int64_t)cid << (32 + e.tile_n_bits)) | ((int64_t)tile << 32) |
                                (int64_t)e.depth_bits[idx];
                 flat_out[q] = (int32_t)idx;
             } else {
-                keys_out[q] = scid[l] * e.n_tiles + tile;
+                keys_out[q] = cid * e.n_tiles + tile;
                 vals_out[q] = idx;
             }
         }
-        running += chunk_total;
-        __syncthreads();
     }
-    if (overflow) atomicOr((unsigned long long *)&counters[CNT_STATUS], (unsigned long long)ST_OVERFLOW_CAPACITY);
+    if (overflow && blockIdx.x == 0 && threadIdx.x == 0)
+        atomicOr((unsigned long long *)&counters[CNT_STATUS], (unsigned long long)ST_OVERFLOW_CAPACITY);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -577,6 +632,7 @@ struct PlanWs {
     unsigned long long *block_sums;
     unsigned long long *block_offs;
     uint32_t *keyA, *valA, *keyB, *valB;
+    uint32_t *eoff;
     size_t bytes;
 };
 
@@ -594,6 +650,7 @@ static PlanWs carve_plan(void *ws, uint64_t total) {
     p.valA = (uint32_t *)take(sizeof(uint32_t) * total);
     p.keyB = (uint32_t *)take(sizeof(uint32_t) * total);
     p.valB = (uint32_t *)take(sizeof(uint32_t) * total);
+    p.eoff = (uint32_t *)take(sizeof(uint32_t) * total);
     p.bytes = off;
     return p;
 }
@@ -720,6 +777,10 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
         SPL_PROF("emit_scan_kernel", st);
         emit_scan_kernel<<<1, 1024, 0, st>>>(p.block_sums, kSortGrid, p.block_offs, p.counters);
     }
+    {
+        SPL_PROF("emit_offsets_kernel", st);
+        emit_offsets_kernel<<<kSortGrid, kThreads, 0, st>>>(e, p.block_offs, p.eoff);
+    }
     if (host_counts != nullptr)
         cudaMemcpyAsync(host_counts, p.counters, sizeof(int64_t) * CNT_SLOTS, cudaMemcpyDeviceToHost, st);
     return check_launch("isect plan");
@@ -749,13 +810,13 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
             {
                 SPL_PROF("emit_kernel", st);
                 emit_kernel<true, true><<<kSortGrid, kThreads, 0, st>>>(
-                    g.lid, e, p.block_offs, nullptr, nullptr, isect_ids, flatten_ids, p.counters);
+                    g.lid, e, p.eoff, p.counters, nullptr, nullptr, isect_ids, flatten_ids, p.counters);
             }
         } else {
             {
                 SPL_PROF("emit_kernel", st);
                 emit_kernel<false, true><<<kSortGrid, kThreads, 0, st>>>(
-                    g.cam, e, p.block_offs, nullptr, nullptr, isect_ids, flatten_ids, p.counters);
+                    g.cam, e, p.eoff, p.counters, nullptr, nullptr, isect_ids, flatten_ids, p.counters);
             }
         }
     } else {
@@ -770,13 +831,13 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
             {
                 SPL_PROF("emit_kernel", st);
                 emit_kernel<true, false><<<kSortGrid, kThreads, 0, st>>>(
-                    g.lid, e, p.block_offs, f.keyA, f.valA, nullptr, nullptr, p.counters);
+                    g.lid, e, p.eoff, p.counters, f.keyA, f.valA, nullptr, nullptr, p.counters);
             }
         } else {
             {
                 SPL_PROF("emit_kernel", st);
                 emit_kernel<false, false><<<kSortGrid, kThreads, 0, st>>>(
-                    g.cam, e, p.block_offs, f.keyA, f.valA, nullptr, nullptr, p.counters);
+                    g.cam, e, p.eoff, p.counters, f.keyA, f.valA, nullptr, nullptr, p.counters);
             }
         }
 
@@ -854,6 +915,8 @@ static int make_cam_geom(IsectGeom &g, uint32_t C, uint32_t N, uint64_t total,
     SPL_REQUIRE(C > 0 && tile_size > 0 && tile_width > 0 && tile_height > 0, SPLATAD_ERR_BAD_ARG,
                 "isect_tiles: bad geometry");
     SPL_REQUIRE(total <= 0x7fffffffull, SPLATAD_ERR_BAD_ARG, "isect_tiles: too many elements");
+    SPL_REQUIRE((uint64_t)tile_width * tile_height * C <= 0xffffffffull, SPLATAD_ERR_KEY_BITS,
+                "isect_tiles: sensors * tiles does not fit 32 bits");
     g = IsectGeom{};
     g.lidar = false;
     g.cam.cam = CamGrid{tile_size, tile_width, tile_height};

@@ -167,48 +167,47 @@ struct GaussIn {
     V3 vel;
 };
 
-// smem layout: 3 slabs of kThreads*3 floats (means, scales|covars-part, velocities) + covars 6.
+// Shared-memory staging buffer of the projection kernels: means [256*3] | velocities [256*3] |
+// scales [256*3] or covars [256*6]; the same memory is reused for the 3-wide outputs.
+constexpr int kStageFloats = kThreads * 12;
+
+// Issues every global->shared copy of this block's slab first and synchronises once, so the
+// loads of all arrays are in flight together.
 template <bool kNeedQS>
 __device__ __forceinline__ GaussIn load_gaussian(const float *__restrict__ means,
                                                  const float *__restrict__ covars,
                                                  const float *__restrict__ quats,
                                                  const float *__restrict__ scales,
                                                  const float *__restrict__ velocities, uint32_t N,
-                                                 uint32_t g0, float *smem /* kThreads*6 floats */) {
+                                                 uint32_t g0, float *smem /* kStageFloats */) {
     GaussIn in;
     const uint32_t n = min((uint32_t)kThreads, N - g0);
     const uint32_t t = threadIdx.x;
     const bool live = t < n;
     in.mean = v3(0.f, 0.f, 1.f); in.scale = v3(1.f, 1.f, 1.f); in.vel = v3(0.f, 0.f, 0.f);
     in.quat.x = 1.f; in.quat.y = in.quat.z = in.quat.w = 0.f;
+    float *s_mean = smem, *s_vel = smem + kThreads * 3, *s_cov = smem + kThreads * 6;
 
-    stage_in(means + (size_t)g0 * 3, smem, n * 3);
+    float4 q = make_float4(1.f, 0.f, 0.f, 0.f);
+    if (covars == nullptr && live) q = __ldg(reinterpret_cast<const float4 *>(quats) + g0 + t);
+    stage_in(means + (size_t)g0 * 3, s_mean, n * 3);
+    if (velocities != nullptr) stage_in(velocities + (size_t)g0 * 3, s_vel, n * 3);
+    if (covars != nullptr) stage_in(covars + (size_t)g0 * 6, s_cov, n * 6);
+    else stage_in(scales + (size_t)g0 * 3, s_cov, n * 3);
     __syncthreads();
-    if (live) in.mean = ld3(smem + 3 * t);
-    __syncthreads();
-    if (velocities != nullptr) {
-        stage_in(velocities + (size_t)g0 * 3, smem, n * 3);
-        __syncthreads();
-        if (live) in.vel = ld3(smem + 3 * t);
-        __syncthreads();
+    if (live) {
+        in.mean = ld3(s_mean + 3 * t);
+        if (velocities != nullptr) in.vel = ld3(s_vel + 3 * t);
+        if (covars != nullptr) in.covar = covar_from_triu(s_cov + 6 * t);
+        else in.scale = ld3(s_cov + 3 * t);
     }
-    if (covars != nullptr) {
-        stage_in(covars + (size_t)g0 * 6, smem, n * 6);
-        __syncthreads();
-        if (live) in.covar = covar_from_triu(smem + 6 * t);
-        else in.covar = m3_zero();
-        __syncthreads();
-    } else {
-        stage_in(scales + (size_t)g0 * 3, smem, n * 3);
-        __syncthreads();
-        if (live) in.scale = ld3(smem + 3 * t);
-        __syncthreads();
-        if (live) {
-            const float4 q = __ldg(reinterpret_cast<const float4 *>(quats) + g0 + t);
-            in.quat.x = q.x; in.quat.y = q.y; in.quat.z = q.z; in.quat.w = q.w;
-        }
+    if (covars == nullptr) {
+        in.quat.x = q.x; in.quat.y = q.y; in.quat.z = q.z; in.quat.w = q.w;
         in.covar = quat_scale_to_covar(in.quat, in.scale);
+    } else if (!live) {
+        in.covar = m3_zero();
     }
+    __syncthreads();   // the staging buffer is reused for outputs
     return in;
 }
 
@@ -227,7 +226,7 @@ lidar_projection_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ me
                             float *__restrict__ depths, float *__restrict__ conics,
                             float *__restrict__ compensations, float *__restrict__ pix_vels,
                             float *__restrict__ depth_comps) {
-    __shared__ __align__(16) float smem[kThreads * 6];
+    __shared__ __align__(16) float smem[kStageFloats];
     const uint32_t g0 = blockIdx.x * kThreads;
     const uint32_t n = min((uint32_t)kThreads, N - g0);
     const uint32_t t = threadIdx.x;
@@ -273,7 +272,7 @@ projection_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ means,
                       int32_t *__restrict__ radii, float *__restrict__ means2d,
                       float *__restrict__ depths, float *__restrict__ conics,
                       float *__restrict__ compensations, float *__restrict__ pix_vels) {
-    __shared__ __align__(16) float smem[kThreads * 6];
+    __shared__ __align__(16) float smem[kStageFloats];
     const uint32_t g0 = blockIdx.x * kThreads;
     const uint32_t n = min((uint32_t)kThreads, N - g0);
     const uint32_t t = threadIdx.x;
@@ -320,7 +319,7 @@ projection_packed_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ m
                              int32_t *__restrict__ radii, float *__restrict__ means2d,
                              float *__restrict__ depths, float *__restrict__ conics,
                              float *__restrict__ compensations, float *__restrict__ pix_vels) {
-    __shared__ __align__(16) float smem[kThreads * 6];
+    __shared__ __align__(16) float smem[kStageFloats];
     __shared__ int32_t warp_counts[kThreads / 32];
     const uint32_t g0 = blockIdx.x * kThreads;
     const uint32_t n = min((uint32_t)kThreads, N - g0);
@@ -585,7 +584,7 @@ projection_bwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ means,
                       float *__restrict__ v_covars, float *__restrict__ v_quats,
                       float *__restrict__ v_scales, float *__restrict__ v_viewmats,
                       float *__restrict__ v_velocities) {
-    __shared__ __align__(16) float smem[kThreads * 6];
+    __shared__ __align__(16) float smem[kStageFloats];
     __shared__ float red[(kThreads / 32) * 12];
     const uint32_t g0 = blockIdx.x * kThreads;
     const uint32_t n = min((uint32_t)kThreads, N - g0);
@@ -637,7 +636,7 @@ lidar_projection_bwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ me
                             float *__restrict__ v_covars, float *__restrict__ v_quats,
                             float *__restrict__ v_scales, float *__restrict__ v_viewmats,
                             float *__restrict__ v_velocities) {
-    __shared__ __align__(16) float smem[kThreads * 6];
+    __shared__ __align__(16) float smem[kStageFloats];
     __shared__ float red[(kThreads / 32) * 12];
     const uint32_t g0 = blockIdx.x * kThreads;
     const uint32_t n = min((uint32_t)kThreads, N - g0);

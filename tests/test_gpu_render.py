@@ -25,8 +25,7 @@ def _lidar_stagewise_reference(cfg, m, **kw):
     """Oracle isect + compositing run on the PRODUCT's projection outputs (identical stage
     inputs), plus the number of Gaussians whose tile count differs from the one obtained with
     the oracle's own projection."""
-    import math
-    from oracle import composite, isect, pipeline
+    from oracle import pipeline
     from splatad_b200 import ops
     C = cfg["viewmats"].shape[0]
     g = _to_gpu(cfg)
@@ -42,24 +41,19 @@ def _lidar_stagewise_reference(cfg, m, **kw):
     assert torch.equal(radii, m["radii"]) and torch.equal(means2d, m["means2d"])
     if not kw.get("use_depth_compensation", True):
         dcomp = dcomp * 0
-    th, tw = cfg["tile_height"], cfg["tile_width"]
-    res = cfg["azimuth_resolution"] * tw
-    tpg, ids, flat = isect.isect_lidar_tiles(n(means2d), n(radii), n(depths), n(cfg["tile_elevation_boundaries"]),
-                                             res, cfg["min_azimuth"])
-    n_az = math.ceil((cfg["max_azimuth"] - cfg["min_azimuth"]) / res)
-    n_el = math.ceil(cfg["n_elevation_channels"] / th)
-    offs = isect.isect_offset_encode(ids, C, n_az, n_el)
-    feats = torch.cat([g["lidar_features"], depths[..., None]], -1)
-    H, W = cfg["raster_pts"].shape[1:3]
     asum = kw.get("compute_alpha_sum_until_points", True)
-    out = composite.rasterize_to_points_fwd(n(means2d), n(conics), n(feats), n(m["opacities"]), n(pix_vels),
-                                            n(dcomp), None, n(cfg["raster_pts"]), W, H, tw, th, offs, flat, asum,
-                                            0.2)
+    ref = pipeline.lidar_from_projection(
+        n(radii), n(means2d), n(depths), n(conics), n(m["opacities"]), n(pix_vels), n(dcomp),
+        n(cfg["lidar_features"]), n(cfg["raster_pts"]), n(cfg["tile_elevation_boundaries"]),
+        min_azimuth=cfg["min_azimuth"], max_azimuth=cfg["max_azimuth"],
+        n_elevation_channels=cfg["n_elevation_channels"], azimuth_resolution=cfg["azimuth_resolution"],
+        tile_width=cfg["tile_width"], tile_height=cfg["tile_height"], compute_alpha_sum_until_points=asum)
+    tpg = ref["tiles_per_gauss"]
     # rectangles from the oracle's own projection of the same Gaussians
     _, _, _, ometa = pipeline.lidar_rasterization(**cfg, **kw)
     rect_diff = int((ometa["tiles_per_gauss"] != tpg).sum())
-    return dict(tiles_per_gauss=tpg, isect_ids=ids, flatten_ids=flat, isect_offsets=offs, out=out,
-                rect_diff=rect_diff, oracle_meta=ometa)
+    ref.update(rect_diff=rect_diff, oracle_meta=ometa)
+    return ref
 
 
 def _check_lists(m, ref, label):

@@ -217,14 +217,19 @@ __device__ __forceinline__ void block_range(uint32_t n, uint32_t &lo, uint32_t &
     hi = (uint32_t)(h < n ? h : n);
 }
 
-// Adds one key to the warp-private digit histogram; lanes holding the same digit are merged
-// into one shared-memory add.
+// Adds one key to the warp-private digit histogram (order is irrelevant for a histogram, so
+// plain shared-memory atomics are used; a warp whose 32 keys share one digit - typical for the
+// high tile-key digit - does a single add instead of a 32-way serialised atomic).
 __device__ __forceinline__ void hist_add(uint32_t *wh_row, bool valid, uint32_t key, int shift,
                                          uint32_t mask, uint32_t lane) {
-    const uint32_t digit = valid ? ((key >> shift) & mask) : kRadixBins;
-    const uint32_t peers = __match_any_sync(0xffffffffu, digit);
-    if (valid && lane == (uint32_t)(__ffs(peers) - 1)) wh_row[digit] += __popc(peers);
-    __syncwarp();
+    const uint32_t digit = valid ? ((key >> shift) & mask) : 0xffffffffu;
+    const uint32_t d0 = __shfl_sync(0xffffffffu, digit, 0);
+    if (__all_sync(0xffffffffu, digit == d0)) {
+        if (lane == 0 && valid) wh_row[d0] += 32u;
+        __syncwarp();
+    } else if (valid) {
+        atomicAdd(&wh_row[digit], 1u);
+    }
 }
 
 template <bool kGen>
@@ -306,7 +311,7 @@ struct FinalOut {
 
 template <bool kGen, bool kFinal>
 __global__ void __launch_bounds__(kSortThreads)
-radix_downsweep_kernel(PassSrc s, int shift, uint32_t mask, const uint32_t *__restrict__ hist,
+radix_downsweep_kernel(PassSrc s, int shift, int nbits, uint32_t mask, const uint32_t *__restrict__ hist,
                        const uint32_t *__restrict__ digit_totals, uint32_t *__restrict__ keys_out,
                        uint32_t *__restrict__ vals_out, FinalOut fin,
                        int64_t *__restrict__ n_out /* optional: total valid count */) {
@@ -361,7 +366,14 @@ radix_downsweep_kernel(PassSrc s, int shift, uint32_t mask, const uint32_t *__re
         for (int r = 0; r < kItemsPerLane; ++r) {
             const bool valid = (validmask >> r) & 1u;
             const uint32_t digit = valid ? ((keys[r] >> shift) & mask) : kRadixBins;
-            const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+            // lanes with the same digit: one ballot per digit bit (cheaper than match.any when
+            // a warp holds many distinct digits)
+            uint32_t peers = __ballot_sync(0xffffffffu, valid);
+            for (int b = 0; b < nbits; ++b) {
+                const uint32_t bal = __ballot_sync(0xffffffffu, (digit >> b) & 1u);
+                peers &= ((digit >> b) & 1u) ? bal : ~bal;
+            }
+            if (!valid) peers = 1u << lane;
             const uint32_t leader = (uint32_t)(__ffs(peers) - 1);
             uint32_t old = 0;
             if (valid && lane == leader) {
@@ -519,7 +531,10 @@ emit_offsets_kernel(EmitArgs e, const unsigned long long *__restrict__ block_off
     }
 }
 
-constexpr uint32_t kEmitUnit = 4096;   // intersections per work unit of the emit kernel
+constexpr uint32_t kEmitPerThread = 16;
+constexpr uint32_t kEmitUnit = kThreads * kEmitPerThread;   // 4096 intersections per work unit
+constexpr uint32_t kEmitEntries = 1024;                     // entries staged per sub-chunk
+constexpr uint32_t kEmitUnitsPerBatch = 64;                 // unit windows searched at once
 
 // last p in [lo, hi] with eoff[p] <= q (eoff is non-decreasing, eoff[lo] <= q)
 __device__ __forceinline__ uint32_t find_entry(const uint32_t *__restrict__ eoff, uint32_t lo,
@@ -533,8 +548,9 @@ __device__ __forceinline__ uint32_t find_entry(const uint32_t *__restrict__ eoff
 
 // Writes the intersections in emission order, balanced by OUTPUT position: depth-sorted
 // Gaussians have wildly different tile counts (the nearest ones cover thousands of tiles), so
-// work is split into units of kEmitUnit consecutive outputs and each output finds its source
-// entry by binary search in the offsets of the entries that overlap its unit.
+// work is split into units of kEmitUnit consecutive outputs. The entries overlapping a unit are
+// staged in shared memory (rectangle computed once per entry), every entry marks the first output
+// it owns, and a prefix-max over the unit tells each output which entry it belongs to.
 template <bool kLidar, bool kDirect64>
 __global__ void __launch_bounds__(kThreads)
 emit_kernel(GridArgs<kLidar> a, EmitArgs e, const uint32_t *__restrict__ eoff,
@@ -542,53 +558,131 @@ emit_kernel(GridArgs<kLidar> a, EmitArgs e, const uint32_t *__restrict__ eoff,
             uint32_t *__restrict__ vals_out, int64_t *__restrict__ ids64_out,
             int32_t *__restrict__ flat_out, int64_t *__restrict__ counters) {
     __shared__ float sb[kLidar ? kMaxElevSmem : 1];
-    __shared__ uint32_t window[2];
+    __shared__ uint32_t s_off[kEmitEntries + 1];
+    __shared__ int4 s_rect[kEmitEntries];           // x0, width, y0, sensor
+    __shared__ uint32_t s_idx[kEmitEntries];
+    __shared__ uint32_t owner[kThreads * (kEmitPerThread + 1)];   // padded: 17 words per thread
+    __shared__ uint32_t s_win[2 * kEmitUnitsPerBatch];
+    __shared__ uint32_t wmax[kThreads / 32];
     stage_boundaries<kLidar>(a, sb);
     const uint32_t n_entries = e.order ? (uint32_t)(*e.n_order_ptr) : e.total;
-    int64_t m64 = counters_in[CNT_NISECT];
+    const int64_t m_total = counters_in[CNT_NISECT];
+    int64_t m64 = m_total;
     bool overflow = false;
     if (m64 > e.capacity) { m64 = e.capacity; overflow = true; }
     const uint32_t M = (uint32_t)m64;
-    if (n_entries == 0) return;
+    if (n_entries == 0 || M == 0) return;
     const uint32_t n_units = (M + kEmitUnit - 1) / kEmitUnit;
-    for (uint32_t u = blockIdx.x; u < n_units; u += gridDim.x) {
-        const uint32_t q_lo = u * kEmitUnit;
-        const uint32_t q_hi = min(M, q_lo + kEmitUnit);   // exclusive
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    for (uint32_t u0 = blockIdx.x; u0 < n_units; u0 += gridDim.x * kEmitUnitsPerBatch) {
+        // entry windows of this block's next units, searched in parallel
         __syncthreads();
-        if (threadIdx.x < 2) {
-            const uint32_t q = threadIdx.x == 0 ? q_lo : q_hi - 1;
-            window[threadIdx.x] = find_entry(eoff, 0, n_entries - 1, q);
+        if (tid < 2 * kEmitUnitsPerBatch) {
+            const uint32_t u = u0 + (tid >> 1) * gridDim.x;
+            if (u < n_units) {
+                const uint32_t q_lo = u * kEmitUnit;
+                const uint32_t q_last = min(M, q_lo + kEmitUnit) - 1;
+                s_win[tid] = find_entry(eoff, 0, n_entries - 1, (tid & 1) ? q_last : q_lo);
+            }
         }
         __syncthreads();
-        const uint32_t p_lo = window[0], p_hi = window[1];
-        for (uint32_t q = q_lo + threadIdx.x; q < q_hi; q += kThreads) {
-            const uint32_t p = find_entry(eoff, p_lo, p_hi, q);
-            const uint32_t idx = e.order ? __ldg(e.order + p) : p;
-            Rect r;
-            if (!elem_rect<kLidar>(a, idx, r)) continue;   // cannot happen: entry has a positive count
-            const uint32_t k = q - __ldg(eoff + p);
-            const uint32_t w = (uint32_t)(r.x1 - r.x0);
-            const uint32_t dy = k / w;
-            const uint32_t dx = k - dy * w;
-            const int32_t ty = r.y0 + (int32_t)dy;
-            int32_t tx = r.x0 + (int32_t)dx;
-            uint32_t tile;
-            if (kLidar) {
-                const int32_t na = (int32_t)a.lidar.n_tiles_azim;
-                tx %= na;
-                if (tx < 0) tx += na;
-                tile = (uint32_t)ty * a.lidar.n_tiles_azim + (uint32_t)tx;
-            } else {
-                tile = (uint32_t)ty * a.cam.tile_width + (uint32_t)tx;
-            }
-            const uint32_t cid = e.camera_ids ? (uint32_t)e.camera_ids[idx] : idx / e.N;
-            if (kDirect64) {
-                ids64_out[q] = ((int64_t)cid << (32 + e.tile_n_bits)) | ((int64_t)tile << 32) |
-                               (int64_t)e.depth_bits[idx];
-                flat_out[q] = (int32_t)idx;
-            } else {
-                keys_out[q] = cid * e.n_tiles + tile;
-                vals_out[q] = idx;
+        for (uint32_t b = 0; b < kEmitUnitsPerBatch; ++b) {
+            const uint32_t u = u0 + b * gridDim.x;
+            if (u >= n_units) break;
+            const uint32_t q_lo = u * kEmitUnit;
+            const uint32_t q_hi = min(M, q_lo + kEmitUnit);   // exclusive
+            const uint32_t p_lo = s_win[2 * b], p_hi = s_win[2 * b + 1];
+            for (uint32_t c_lo = p_lo; c_lo <= p_hi; c_lo += kEmitEntries) {
+                const uint32_t c_hi = min(p_hi, c_lo + kEmitEntries - 1);
+                const uint32_t n_e = c_hi - c_lo + 1;
+                __syncthreads();
+                for (uint32_t i = tid; i < n_e; i += kThreads) {
+                    const uint32_t p = c_lo + i;
+                    const uint32_t idx = e.order ? __ldg(e.order + p) : p;
+                    Rect r;
+                    int4 packed = make_int4(0, 0, 0, 0);
+                    if (elem_rect<kLidar>(a, idx, r)) {
+                        packed.x = r.x0;
+                        packed.y = r.x1 - r.x0;
+                        packed.z = r.y0;
+                        packed.w = (int32_t)(e.camera_ids ? (uint32_t)e.camera_ids[idx] : idx / e.N);
+                    }
+                    s_off[i] = __ldg(eoff + p);
+                    s_rect[i] = packed;
+                    s_idx[i] = idx;
+                }
+                if (tid == 0)
+                    s_off[n_e] = (c_hi + 1 < n_entries) ? __ldg(eoff + c_hi + 1)
+                                                        : (uint32_t)min(m_total, (int64_t)0xffffffffll);
+                for (uint32_t i = tid; i < kThreads * (kEmitPerThread + 1); i += kThreads) owner[i] = 0u;
+                __syncthreads();
+                // outputs of this unit covered by the staged entries
+                const uint32_t o_lo = max(q_lo, s_off[0]);
+                const uint32_t o_hi = min(q_hi, s_off[n_e]);
+                for (uint32_t i = tid; i < n_e; i += kThreads) {
+                    const uint32_t s0 = s_off[i], s1 = s_off[i + 1];
+                    if (s1 > s0 && s1 > o_lo && s0 < o_hi) {
+                        const uint32_t j = max(s0, o_lo) - o_lo;
+                        owner[j + j / kEmitPerThread] = i + 1;
+                    }
+                }
+                __syncthreads();
+                // inclusive prefix-max over owner: per-thread segment, then across threads
+                uint32_t run = 0;
+                uint32_t *seg = owner + tid * (kEmitPerThread + 1);
+#pragma unroll
+                for (uint32_t k = 0; k < kEmitPerThread; ++k) {
+                    run = max(run, seg[k]);
+                    seg[k] = run;
+                }
+                uint32_t inc = run;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const uint32_t o = __shfl_up_sync(0xffffffffu, inc, off);
+                    if (lane >= (uint32_t)off) inc = max(inc, o);
+                }
+                if (lane == 31) wmax[warp] = inc;
+                __syncthreads();
+                uint32_t prefix = __shfl_up_sync(0xffffffffu, inc, 1);
+                if (lane == 0) prefix = 0;
+                for (uint32_t w = 0; w < warp; ++w) prefix = max(prefix, wmax[w]);
+#pragma unroll
+                for (uint32_t k = 0; k < kEmitPerThread; ++k) seg[k] = max(seg[k], prefix);
+                __syncthreads();
+                // coalesced emission
+                const uint32_t n_out = o_hi > o_lo ? o_hi - o_lo : 0u;
+                for (uint32_t j = tid; j < n_out; j += kThreads) {
+                    const uint32_t own = owner[j + j / kEmitPerThread];
+                    if (own == 0) continue;   // cannot happen: every output has an owner
+                    const uint32_t i = own - 1;
+                    const int4 r = s_rect[i];
+                    const uint32_t q = o_lo + j;
+                    const uint32_t k = q - s_off[i];
+                    const uint32_t w = (uint32_t)r.y;
+                    const uint32_t dy = k / w;
+                    const uint32_t dx = k - dy * w;
+                    const int32_t ty = r.z + (int32_t)dy;
+                    int32_t tx = r.x + (int32_t)dx;
+                    uint32_t tile;
+                    if (kLidar) {
+                        const int32_t na = (int32_t)a.lidar.n_tiles_azim;
+                        tx %= na;
+                        if (tx < 0) tx += na;
+                        tile = (uint32_t)ty * a.lidar.n_tiles_azim + (uint32_t)tx;
+                    } else {
+                        tile = (uint32_t)ty * a.cam.tile_width + (uint32_t)tx;
+                    }
+                    const uint32_t idx = s_idx[i];
+                    if (kDirect64) {
+                        ids64_out[q] = ((int64_t)(uint32_t)r.w << (32 + e.tile_n_bits)) |
+                                       ((int64_t)tile << 32) | (int64_t)e.depth_bits[idx];
+                        flat_out[q] = (int32_t)idx;
+                    } else {
+                        keys_out[q] = (uint32_t)r.w * e.n_tiles + tile;
+                        vals_out[q] = idx;
+                    }
+                }
             }
         }
     }
@@ -741,7 +835,7 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
                 {
                     SPL_PROF("depthsort_downsweep", st);
                     radix_downsweep_kernel<true, false><<<kSortGrid, kSortThreads, 0, st>>>(
-                        s, 0, 0xffu, p.hist, p.digit_totals, ka, va, nofin, p.counters + CNT_NVIS);
+                        s, 0, 8, 0xffu, p.hist, p.digit_totals, ka, va, nofin, p.counters + CNT_NVIS);
                 }
             } else {
                 s.keys = ka; s.vals = va; s.n_ptr = p.counters + CNT_NVIS;
@@ -757,7 +851,7 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
                 {
                     SPL_PROF("depthsort_downsweep", st);
                     radix_downsweep_kernel<false, false><<<kSortGrid, kSortThreads, 0, st>>>(
-                        s, 8 * pass, 0xffu, p.hist, p.digit_totals, kb, vb, nofin, nullptr);
+                        s, 8 * pass, 8, 0xffu, p.hist, p.digit_totals, kb, vb, nofin, nullptr);
                 }
                 uint32_t *t;
                 t = ka; ka = kb; kb = t;
@@ -872,14 +966,14 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
                 {
                     SPL_PROF("tilesort_downsweep", st);
                     radix_downsweep_kernel<false, true><<<kSortGrid, kSortThreads, 0, st>>>(
-                        s, shift, mask, p.hist, p.digit_totals, nullptr, nullptr, fin, nullptr);
+                        s, shift, (int)bits_per, mask, p.hist, p.digit_totals, nullptr, nullptr, fin, nullptr);
                 }
             } else {
                 FinalOut nofin{};
                 {
                     SPL_PROF("tilesort_downsweep", st);
                     radix_downsweep_kernel<false, false><<<kSortGrid, kSortThreads, 0, st>>>(
-                        s, shift, mask, p.hist, p.digit_totals, kb, vb, nofin, nullptr);
+                        s, shift, (int)bits_per, mask, p.hist, p.digit_totals, kb, vb, nofin, nullptr);
                 }
                 uint32_t *t;
                 t = ka; ka = kb; kb = t;

@@ -343,6 +343,24 @@ def run_ours(args):
         print(json.dumps(result))
 
 
+def run_frames(args):
+    """Renders a few frames of the chosen workload and exits: the command profiled under ncu."""
+    import splatad_b200
+    from splatad_b200 import scenes
+    dev = torch.device("cuda:0")
+    if args.workload == "lidar":
+        cfg = to_device(scenes.config2(), dev)
+        fn = lambda: splatad_b200.lidar_rasterization(**cfg)  # noqa: E731
+    else:
+        cfg = to_device(scenes.config1(), dev)
+        fn = lambda: splatad_b200.rasterization(**cfg)  # noqa: E731
+    for _ in range(args.frames):
+        out = fn()
+    torch.cuda.synchronize()
+    print(json.dumps({"frames": args.frames, "workload": args.workload,
+                      "n_isects": int(out[-1]["flatten_ids"].numel())}))
+
+
 def cpu_frame(n_gauss):
     """One config-2 frame through the CPU oracle port with n_gauss Gaussians; returns seconds and stage times."""
     from oracle import pipeline
@@ -410,7 +428,14 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--frames", type=int, default=0,
+                    help="only render this many frames of the workload and exit (for use under ncu)")
+    ap.add_argument("--workload", default="lidar", choices=["lidar", "camera"],
+                    help="with --frames: config 2 lidar (default) or config 1 camera")
     args = ap.parse_args()
+    if args.frames > 0:
+        run_frames(args)
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

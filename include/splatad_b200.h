@@ -133,6 +133,31 @@ int splatad_projection_packed_fill(
     int64_t *camera_ids, int64_t *gaussian_ids, int32_t *radii, float *means2d, float *depths,
     float *conics, float *compensations, float *pix_vels, void *stream);
 
+/* No counterpart in the reference. Same result as splatad_projection_packed_count (indptr [C+1]
+ * and *nnz_device), but for hosts that must not allocate device memory at all: a plugin living
+ * inside an engine that has already handed the whole GPU to its own arena, a control loop whose
+ * certification forbids allocator calls after start-up, a process whose memory budget is fixed by
+ * an outer scheduler. Such a caller has no workspace to pass, so the per-(camera, block) counters
+ * live in a 512 KiB array compiled into the library (every GPU that loads the library keeps it
+ * until the process exits). Limit: C * ceil(N / 256) <= 65536 (e.g. one camera and 16.7 M
+ * Gaussians, or 8 cameras and 2 M); beyond it the call fails with SPLATAD_ERR_WORKSPACE and a
+ * message, and touches nothing. The call makes no cudaMalloc / cudaFree and uses no allocating
+ * library routine; inputs and outputs are still the caller's.
+ * The first call on each device looks the array's device address up (cudaGetSymbolAddress, with
+ * that device current); make that first call outside any stream capture.
+ * All calls on a device share the one array: nothing in it has to be cleared between calls
+ * (every slot a call reads it has written first), but two calls that overlap on the GPU - on
+ * different streams, or from different threads - race on it and corrupt each other's counts.
+ * It answers "how many packed rows, and where does each camera start"; it does not feed
+ * splatad_projection_packed_fill, which reads its offsets from a caller workspace. */
+int splatad_projection_packed_count_noalloc(
+    uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
+    const float *scales, const float *velocities, const float *viewmats, const float *Ks,
+    int32_t image_width, int32_t image_height, const float *linear_velocity,
+    const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
+    float near_plane, float far_plane, float radius_clip, int32_t *indptr, int64_t *nnz_device,
+    void *stream);
+
 /* fully_fused_projection_packed_bwd_tensor - gsplat/cuda/csrc/projection.cu:1718-1838, kernel
  * 1466-1716. sparse_grad != 0: parameter gradients are [nnz,..] rows (plain stores);
  * otherwise [N,..] accumulated with atomics, so the caller zero-initialises them.

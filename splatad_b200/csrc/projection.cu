@@ -966,3 +966,80 @@ extern "C" int splatad_projection_packed_bwd(
     }
     return check_launch("projection_packed_bwd");
 }
+
+// =======================================================================================
+// Allocation-free variant of the packed count
+// =======================================================================================
+namespace splatad {
+
+// Scratch of splatad_projection_packed_count_noalloc: per-(camera, block) visible counts followed
+// by their exclusive offsets. 2 x 65536 int32 = 512 KiB, resident on every GPU that loads the
+// library until the process exits.
+constexpr uint32_t kNoAllocMaxBlockRows = 65536;
+static __device__ __align__(256) int32_t g_packed_count_scratch[2 * kNoAllocMaxBlockRows];
+
+// Device address of the scratch array on the CURRENT device, looked up once per device. In host
+// code the array's name is only a handle for the runtime, not a device address, so the address
+// must come from cudaGetSymbolAddress.
+static int packed_count_scratch(int32_t **out) {
+    constexpr int kMaxDevices = 64;
+    static int32_t *cached[kMaxDevices] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_last_error("projection_packed_count_noalloc: cudaGetDevice failed or device index %d unsupported", dev);
+        return SPLATAD_ERR_CUDA;
+    }
+    int32_t *p = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+    if (p == nullptr) {
+        void *addr = nullptr;
+        e = cudaGetSymbolAddress(&addr, g_packed_count_scratch);
+        if (e != cudaSuccess || addr == nullptr) {
+            set_last_error("projection_packed_count_noalloc: cudaGetSymbolAddress failed: %s",
+                           cudaGetErrorString(e));
+            return SPLATAD_ERR_CUDA;
+        }
+        p = (int32_t *)addr;
+        __atomic_store_n(&cached[dev], p, __ATOMIC_RELEASE);
+    }
+    *out = p;
+    return SPLATAD_OK;
+}
+
+} // namespace splatad
+
+extern "C" int splatad_projection_packed_count_noalloc(
+    uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
+    const float *scales, const float *velocities, const float *viewmats, const float *Ks,
+    int32_t image_width, int32_t image_height, const float *linear_velocity,
+    const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
+    float near_plane, float far_plane, float radius_clip, int32_t *indptr, int64_t *nnz_device,
+    void *stream) {
+    SPL_REQUIRE(means && viewmats && Ks && indptr && nnz_device && linear_velocity &&
+                    angular_velocity && rolling_shutter_time,
+                SPLATAD_ERR_BAD_ARG, "projection_packed_count_noalloc: null argument");
+    SPL_REQUIRE(covars || (quats && scales), SPLATAD_ERR_BAD_ARG,
+                "projection_packed_count_noalloc: covars or (quats, scales) required");
+    SPL_REQUIRE(C > 0 && N > 0, SPLATAD_ERR_BAD_ARG, "projection_packed_count_noalloc: empty input");
+    const uint64_t nblocks = div_up(N, kThreads);
+    const uint64_t rows = (uint64_t)C * nblocks;
+    SPL_REQUIRE(rows <= kNoAllocMaxBlockRows, SPLATAD_ERR_WORKSPACE,
+                "projection_packed_count_noalloc: C * ceil(N / 256) = %llu exceeds the built-in scratch of "
+                "%u rows; use splatad_projection_packed_count with a caller workspace",
+                (unsigned long long)rows, kNoAllocMaxBlockRows);
+    int32_t *scratch = nullptr;
+    const int rc = packed_count_scratch(&scratch);
+    if (rc != SPLATAD_OK) return rc;
+    int32_t *counts = scratch;
+    int32_t *offsets = scratch + rows;
+    cudaStream_t st = (cudaStream_t)stream;
+    // every slot the scan reads is written by the count pass of this same call: nothing in the
+    // scratch needs clearing, and what earlier (larger) calls left behind is never read
+    projection_packed_fwd_kernel<<<(uint32_t)nblocks, kThreads, 0, st>>>(
+        C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
+        linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
+        radius_clip, counts, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+        nullptr, nullptr);
+    packed_scan_kernel<<<1, 1024, 0, st>>>(counts, offsets, C, (uint32_t)nblocks, indptr, nnz_device);
+    return check_launch("projection_packed_count_noalloc");
+}

@@ -277,10 +277,15 @@ int splatad_rasterize_to_pixels_bwd(
  * 2021-2219. raster_pts [C,H,W,4] = (azimuth deg, elevation deg, range m, time offset s);
  * points with range <= 0 are not rendered and produce zeros. pix_vels [.,3],
  * depth_compensations [.,2]. depth_channel_idx names the channel that holds the Gaussian's
- * range. alpha_sum_until_points may be NULL when compute_alpha_sum_until_points == 0. */
+ * range. alpha_sum_until_points may be NULL when compute_alpha_sum_until_points == 0.
+ * gaussian_ranges (optional): when given, lidar_features holds channels - 1 columns and the
+ * last rendered channel (depth_channel_idx == channels - 1) is read from this [C,N] / [nnz]
+ * array instead - this spares the caller the concatenation of features and range that
+ * gsplat/rendering.py:746, 779 performs for every frame. */
 int splatad_rasterize_to_points_fwd(
     uint32_t C, int64_t n_isects, const float *means2d, const float *conics,
-    const float *lidar_features, uint32_t channels, const float *opacities,
+    const float *lidar_features, const float *gaussian_ranges, uint32_t channels,
+    const float *opacities,
     const float *pix_vels, const float *depth_compensations, const float *backgrounds,
     const float *raster_pts, uint32_t image_width, uint32_t image_height, uint32_t tile_width,
     uint32_t tile_height, uint32_t tile_grid_width, uint32_t tile_grid_height,
@@ -291,10 +296,12 @@ int splatad_rasterize_to_points_fwd(
 
 /* rasterize_to_points_bwd_tensor - gsplat/cuda/csrc/rasterization.cu:4056-4851, kernel
  * 3728-4054. v_alpha_sum_until_points may be NULL (treated as zero). Gradient outputs are
- * accumulated with atomics: zero-initialise them. */
+ * accumulated with atomics: zero-initialise them. With gaussian_ranges, v_features has
+ * channels - 1 columns and the range gradient goes to v_gaussian_ranges. */
 int splatad_rasterize_to_points_bwd(
     uint32_t C, int64_t n_isects, const float *means2d, const float *conics,
-    const float *lidar_features, uint32_t channels, const float *opacities,
+    const float *lidar_features, const float *gaussian_ranges, uint32_t channels,
+    const float *opacities,
     const float *pix_vels, const float *depth_compensations, const float *backgrounds,
     const float *raster_pts, uint32_t image_width, uint32_t image_height, uint32_t tile_width,
     uint32_t tile_height, uint32_t tile_grid_width, uint32_t tile_grid_height,
@@ -303,7 +310,7 @@ int splatad_rasterize_to_points_bwd(
     const float *render_alphas, const int32_t *last_ids, const float *v_render_features,
     const float *v_render_alphas, const float *v_alpha_sum_until_points, float *v_means2d_abs,
     float *v_means2d, float *v_conics, float *v_features, float *v_opacities, float *v_pix_vels,
-    float *v_depth_compensations, void *stream);
+    float *v_depth_compensations, float *v_gaussian_ranges, void *stream);
 
 #ifdef __cplusplus
 }

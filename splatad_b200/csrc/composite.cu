@@ -138,7 +138,8 @@ __global__ void rasterize_to_pixels_fwd_kernel(
 template <int CDIM>
 __global__ void rasterize_to_points_fwd_kernel(
     uint32_t C, int64_t n_isects, const float2 *__restrict__ means2d,
-    const float *__restrict__ conics, const float *__restrict__ colors, uint32_t channels,
+    const float *__restrict__ conics, const float *__restrict__ colors,
+    const float *__restrict__ ranges /* optional: last channel comes from here */, uint32_t channels,
     const float *__restrict__ opacities, const float *__restrict__ pix_vels /* [.,3] */,
     const float2 *__restrict__ depth_comps, const float *__restrict__ backgrounds,
     const float4 *__restrict__ raster_pts, uint32_t W, uint32_t H, uint32_t tile_width,
@@ -175,6 +176,8 @@ __global__ void rasterize_to_points_fwd_kernel(
     const TileRange range = tile_range(offsets, blockIdx.x, C * tiles_per_cam, n_isects);
     const uint32_t num_batches = (uint32_t)(range.end - range.start + bs - 1) / bs;
 
+    // with a separate range array the feature rows hold channels - 1 columns
+    const uint32_t fstride = ranges ? channels - 1 : channels;
     bool done = !inside;
     float T = 1.f;
     uint32_t cur_idx = 0;
@@ -195,7 +198,8 @@ __global__ void rasterize_to_points_fwd_kernel(
             sA[tr] = make_float4(xy.x, xy.y, v[0], v[1]);
             sB[tr] = make_float4(conics[3 * (size_t)g], conics[3 * (size_t)g + 1],
                                  conics[3 * (size_t)g + 2], opacities[g]);
-            sC[tr] = make_float4(v[2], dc.x, dc.y, colors[(size_t)g * channels + depth_idx]);
+            sC[tr] = make_float4(v[2], dc.x, dc.y,
+                                 ranges ? ranges[g] : colors[(size_t)g * channels + depth_idx]);
             sId[tr] = g;
         }
         __syncthreads();
@@ -213,10 +217,12 @@ __global__ void rasterize_to_points_fwd_kernel(
             if (next_T <= kTStop) { done = true; break; }
             const float vis = alpha * T;
             const float4 Cc = sC[t];
-            const float *c_ptr = colors + (size_t)sId[t] * channels;
+            const float *c_ptr = colors + (size_t)sId[t] * fstride;
 #pragma unroll
-            for (int k = 0; k < CDIM; ++k)
-                if ((uint32_t)k < channels) pix_out[k] += __ldg(c_ptr + k) * vis;
+            for (int k = 0; k < CDIM; ++k) {
+                if ((uint32_t)k < fstride) pix_out[k] += __ldg(c_ptr + k) * vis;
+                else if ((uint32_t)k < channels) pix_out[k] += Cc.w * vis;
+            }
             const float dterm = Cc.y * dx + Cc.z * dy + Cc.x * roll;
             depth_extra += dterm * vis;
             if (T > 0.5f && next_T <= 0.5f) median = Cc.w + dterm;
@@ -430,7 +436,8 @@ __global__ void rasterize_to_pixels_bwd_kernel(
 template <int CDIM>
 __global__ void rasterize_to_points_bwd_kernel(
     uint32_t C, int64_t n_isects, const float2 *__restrict__ means2d,
-    const float *__restrict__ conics, const float *__restrict__ colors, uint32_t channels,
+    const float *__restrict__ conics, const float *__restrict__ colors,
+    const float *__restrict__ ranges, uint32_t channels,
     const float *__restrict__ opacities, const float *__restrict__ pix_vels,
     const float2 *__restrict__ depth_comps, const float *__restrict__ backgrounds,
     const float4 *__restrict__ raster_pts, uint32_t W, uint32_t H, uint32_t tile_width,
@@ -442,7 +449,7 @@ __global__ void rasterize_to_points_bwd_kernel(
     const float *__restrict__ v_alpha_sum, float *__restrict__ v_means2d_abs,
     float *__restrict__ v_means2d, float *__restrict__ v_conics, float *__restrict__ v_colors,
     float *__restrict__ v_opacities, float *__restrict__ v_pix_vels,
-    float *__restrict__ v_depth_comps) {
+    float *__restrict__ v_depth_comps, float *__restrict__ v_ranges) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int red[32];
     const uint32_t bs = blockDim.x;
@@ -470,6 +477,7 @@ __global__ void rasterize_to_points_bwd_kernel(
 
     const TileRange range = tile_range(offsets, blockIdx.x, C * tiles_per_cam, n_isects);
 
+    const uint32_t fstride = ranges ? channels - 1 : channels;
     const float T_final = 1.f - render_alphas[pix];
     float T = T_final;
     const int32_t bin_final = inside ? last_ids[pix] : 0;
@@ -512,7 +520,8 @@ __global__ void rasterize_to_points_bwd_kernel(
                                  conics[3 * (size_t)g + 2], opacities[g]);
             sC[tr] = make_float4(v[2], dc.x, dc.y, 0.f);
             sId[tr] = g;
-            for (uint32_t k = 0; k < channels; ++k) sRgb[tr * channels + k] = colors[(size_t)g * channels + k];
+            for (uint32_t k = 0; k < fstride; ++k) sRgb[tr * channels + k] = colors[(size_t)g * fstride + k];
+            if (ranges) sRgb[tr * channels + channels - 1] = ranges[g];
         }
         __syncthreads();
         for (int32_t t = max(0, batch_end - warp_bin_final); t < batch_size; ++t) {
@@ -604,8 +613,10 @@ __global__ void rasterize_to_points_bwd_kernel(
             if (lane == 0) {
                 const size_t g = (size_t)sId[t];
 #pragma unroll
-                for (int k = 0; k < CDIM; ++k)
-                    if ((uint32_t)k < channels) atomicAdd(v_colors + g * channels + k, v_rgb[k]);
+                for (int k = 0; k < CDIM; ++k) {
+                    if ((uint32_t)k < fstride) atomicAdd(v_colors + g * fstride + k, v_rgb[k]);
+                    else if ((uint32_t)k < channels) atomicAdd(v_ranges + g, v_rgb[k]);
+                }
                 atomicAdd(v_conics + 3 * g, v_conic_x);
                 atomicAdd(v_conics + 3 * g + 1, v_conic_y);
                 atomicAdd(v_conics + 3 * g + 2, v_conic_z);
@@ -737,7 +748,8 @@ extern "C" int splatad_rasterize_to_pixels_bwd(
 
 extern "C" int splatad_rasterize_to_points_fwd(
     uint32_t C, int64_t n_isects, const float *means2d, const float *conics,
-    const float *lidar_features, uint32_t channels, const float *opacities,
+    const float *lidar_features, const float *gaussian_ranges, uint32_t channels,
+    const float *opacities,
     const float *pix_vels, const float *depth_compensations, const float *backgrounds,
     const float *raster_pts, uint32_t image_width, uint32_t image_height, uint32_t tile_width,
     uint32_t tile_height, uint32_t tile_grid_width, uint32_t tile_grid_height,
@@ -750,6 +762,8 @@ extern "C" int splatad_rasterize_to_points_fwd(
                 SPLATAD_MAX_CHANNELS);
     SPL_REQUIRE(depth_channel_idx < channels, SPLATAD_ERR_BAD_ARG,
                 "rasterize_to_points_fwd: depth channel out of range");
+    SPL_REQUIRE(!gaussian_ranges || depth_channel_idx == channels - 1, SPLATAD_ERR_BAD_ARG,
+                "rasterize_to_points_fwd: a separate range array is the last channel");
     SPL_REQUIRE(tile_width >= 1 && tile_height >= 1 && tile_width * tile_height <= 1024,
                 SPLATAD_ERR_BAD_ARG, "rasterize_to_points_fwd: tile must have <= 1024 points");
     SPL_REQUIRE(render_features && render_alphas && last_ids && median_depths && tile_offsets &&
@@ -757,8 +771,9 @@ extern "C" int splatad_rasterize_to_points_fwd(
                 SPLATAD_ERR_BAD_ARG, "rasterize_to_points_fwd: null argument");
     SPL_REQUIRE(!compute_alpha_sum_until_points || alpha_sum_until_points, SPLATAD_ERR_BAD_ARG,
                 "rasterize_to_points_fwd: alpha-sum output missing");
-    SPL_REQUIRE(n_isects == 0 || (means2d && conics && lidar_features && opacities && pix_vels &&
-                                  depth_compensations && flatten_ids),
+    SPL_REQUIRE(n_isects == 0 || (means2d && conics && opacities && pix_vels &&
+                                  depth_compensations && flatten_ids &&
+                                  (lidar_features || (gaussian_ranges && channels == 1))),
                 SPLATAD_ERR_BAD_ARG, "rasterize_to_points_fwd: null input");
     const uint32_t blocks = C * tile_grid_width * tile_grid_height;
     if (blocks == 0 || image_width == 0 || image_height == 0) return SPLATAD_OK;
@@ -769,7 +784,8 @@ extern "C" int splatad_rasterize_to_points_fwd(
         int rc = set_smem(rasterize_to_points_fwd_kernel<D>, smem, "rasterize_to_points_fwd");    \
         if (rc != SPLATAD_OK) return rc;                                                          \
         rasterize_to_points_fwd_kernel<D><<<blocks, bs, smem, (cudaStream_t)stream>>>(            \
-            C, n_isects, (const float2 *)means2d, conics, lidar_features, channels, opacities,    \
+            C, n_isects, (const float2 *)means2d, conics, lidar_features, gaussian_ranges,        \
+            channels, opacities,                                                                  \
             pix_vels, (const float2 *)depth_compensations, backgrounds,                           \
             (const float4 *)raster_pts, image_width, image_height, tile_width, tile_height,       \
             tile_grid_width, tile_grid_height, compute_alpha_sum_until_points,                    \
@@ -786,7 +802,8 @@ extern "C" int splatad_rasterize_to_points_fwd(
 
 extern "C" int splatad_rasterize_to_points_bwd(
     uint32_t C, int64_t n_isects, const float *means2d, const float *conics,
-    const float *lidar_features, uint32_t channels, const float *opacities,
+    const float *lidar_features, const float *gaussian_ranges, uint32_t channels,
+    const float *opacities,
     const float *pix_vels, const float *depth_compensations, const float *backgrounds,
     const float *raster_pts, uint32_t image_width, uint32_t image_height, uint32_t tile_width,
     uint32_t tile_height, uint32_t tile_grid_width, uint32_t tile_grid_height,
@@ -795,7 +812,7 @@ extern "C" int splatad_rasterize_to_points_bwd(
     const float *render_alphas, const int32_t *last_ids, const float *v_render_features,
     const float *v_render_alphas, const float *v_alpha_sum_until_points, float *v_means2d_abs,
     float *v_means2d, float *v_conics, float *v_features, float *v_opacities, float *v_pix_vels,
-    float *v_depth_compensations, void *stream) {
+    float *v_depth_compensations, float *v_gaussian_ranges, void *stream) {
     SPL_REQUIRE(channels >= 1 && channels <= SPLATAD_MAX_CHANNELS, SPLATAD_ERR_CHANNELS,
                 "rasterize_to_points_bwd: unsupported channel count %u (1..%d)", channels,
                 SPLATAD_MAX_CHANNELS);
@@ -805,12 +822,15 @@ extern "C" int splatad_rasterize_to_points_bwd(
                 SPLATAD_ERR_BAD_ARG, "rasterize_to_points_bwd: tile must have <= 1024 points");
     const uint32_t blocks = C * tile_grid_width * tile_grid_height;
     if (blocks == 0 || n_isects == 0 || image_width == 0 || image_height == 0) return SPLATAD_OK;
-    SPL_REQUIRE(means2d && conics && lidar_features && opacities && pix_vels &&
+    SPL_REQUIRE(means2d && conics && opacities && pix_vels &&
                     depth_compensations && flatten_ids && tile_offsets && raster_pts &&
                     render_alphas && last_ids && v_render_features && v_render_alphas &&
-                    v_means2d && v_conics && v_features && v_opacities && v_pix_vels &&
-                    v_depth_compensations,
+                    v_means2d && v_conics && v_opacities && v_pix_vels && v_depth_compensations,
                 SPLATAD_ERR_BAD_ARG, "rasterize_to_points_bwd: null argument");
+    SPL_REQUIRE((lidar_features && v_features) || (gaussian_ranges && channels == 1), SPLATAD_ERR_BAD_ARG,
+                "rasterize_to_points_bwd: features / v_features missing");
+    SPL_REQUIRE(!gaussian_ranges || (v_gaussian_ranges && depth_channel_idx == channels - 1),
+                SPLATAD_ERR_BAD_ARG, "rasterize_to_points_bwd: range array needs v_gaussian_ranges");
     const uint32_t bs = ((tile_width * tile_height + 31) / 32) * 32;   // whole warps
     const size_t smem = (size_t)bs * (3 * sizeof(float4) + sizeof(int32_t) + channels * sizeof(float));
 #define CALL(D)                                                                                   \
@@ -818,14 +838,15 @@ extern "C" int splatad_rasterize_to_points_bwd(
         int rc = set_smem(rasterize_to_points_bwd_kernel<D>, smem, "rasterize_to_points_bwd");    \
         if (rc != SPLATAD_OK) return rc;                                                          \
         rasterize_to_points_bwd_kernel<D><<<blocks, bs, smem, (cudaStream_t)stream>>>(            \
-            C, n_isects, (const float2 *)means2d, conics, lidar_features, channels, opacities,    \
+            C, n_isects, (const float2 *)means2d, conics, lidar_features, gaussian_ranges,        \
+            channels, opacities,                                                                  \
             pix_vels, (const float2 *)depth_compensations, backgrounds,                           \
             (const float4 *)raster_pts, image_width, image_height, tile_width, tile_height,       \
             tile_grid_width, tile_grid_height, compute_alpha_sum_until_points,                    \
             alpha_sum_threshold, tile_offsets, flatten_ids, depth_channel_idx, render_alphas,     \
             last_ids, v_render_features, v_render_alphas, v_alpha_sum_until_points,               \
             v_means2d_abs, v_means2d, v_conics, v_features, v_opacities, v_pix_vels,              \
-            v_depth_compensations);                                                               \
+            v_depth_compensations, v_gaussian_ranges);                                            \
     }
     {
         SPL_PROF("rasterize_to_points_bwd_kernel", (cudaStream_t)stream);

@@ -786,7 +786,7 @@ def rasterize_to_points(
             isect_offsets.contiguous(), flatten_ids.contiguous(), compute_alpha_sum_until_points,
             compute_alpha_sum_until_points_threshold, absgrad)
     if channels <= _lib.MAX_CHANNELS:
-        return _RasterizeToPoints.apply(*fixed, lidar_features.contiguous(), *mid, backgrounds, *tail,
+        return _RasterizeToPoints.apply(*fixed, lidar_features.contiguous(), None, *mid, backgrounds, *tail,
                                         depth_channel_idx)
     # more channels than one launch renders: every chunk carries the range as its last channel
     step = _lib.MAX_CHANNELS - 1
@@ -799,23 +799,47 @@ def rasterize_to_points(
         bg = None
         if backgrounds is not None:
             bg = torch.cat([backgrounds[..., lo:hi], backgrounds[..., -1:]], dim=-1).contiguous()
-        r, a, s, m = _RasterizeToPoints.apply(*fixed, feats, *mid, bg, *tail, feats.shape[-1] - 1)
+        r, a, s, m = _RasterizeToPoints.apply(*fixed, feats, None, *mid, bg, *tail, feats.shape[-1] - 1)
         if first is None:
             first = (a, s, m)
         outs.append(r if hi == n_feat else r[..., :-1])
     return torch.cat(outs, dim=-1), first[0], first[1], first[2]
 
 
+def rasterize_to_points_split(
+    means2d: Tensor, conics: Tensor, lidar_features: Tensor, ranges: Tensor, opacities: Tensor,
+    pix_vels: Tensor, depth_compensations: Tensor, raster_pts: Tensor, image_width: int, image_height: int,
+    tile_width: int, tile_height: int, isect_offsets: Tensor, flatten_ids: Tensor,
+    compute_alpha_sum_until_points: bool, compute_alpha_sum_until_points_threshold: float,
+    absgrad: bool = False,
+) -> Tuple[Tensor, Tensor, Optional[Tensor], Tensor]:
+    """:func:`rasterize_to_points` with the Gaussians' ranges given as their own [C,N] tensor instead
+    of being concatenated to the features as last channel (what ``lidar_rasterization`` of the
+    reference does per frame, gsplat/rendering.py:746, 779): same outputs, D + 1 <= 32 channels, no
+    [C,N,D+1] copy. Not part of the reference's API; used by ``splatad_b200.lidar_rasterization``."""
+    assert lidar_features.shape[-1] + 1 <= _lib.MAX_CHANNELS
+    assert ranges.shape == lidar_features.shape[:-1], (ranges.shape, lidar_features.shape)
+    return _RasterizeToPoints.apply(
+        means2d.contiguous(), conics.contiguous(), lidar_features.contiguous(), ranges.contiguous(),
+        opacities.contiguous(), pix_vels.contiguous(), depth_compensations.contiguous(), None,
+        raster_pts.contiguous(), image_width, image_height, tile_width, tile_height,
+        isect_offsets.contiguous(), flatten_ids.contiguous(), compute_alpha_sum_until_points,
+        compute_alpha_sum_until_points_threshold, absgrad, lidar_features.shape[-1])
+
+
 class _RasterizeToPoints(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, means2d, conics, colors, opacities, pix_vels, depth_compensations, backgrounds,
+    def forward(ctx, means2d, conics, colors, ranges, opacities, pix_vels, depth_compensations, backgrounds,
                 raster_pts, width, height, tile_width, tile_height, isect_offsets, flatten_ids,
                 compute_alpha_sum_until_points, compute_alpha_sum_until_points_threshold, absgrad,
                 depth_channel_idx):
+        # ``ranges`` (optional, [C,N] / [nnz]): the Gaussians' ranges as a separate array; the rendered
+        # channel count is then colors.shape[-1] + 1 with the range as last channel.
         dev = means2d.device
         assert means2d.dtype == torch.float32, means2d.dtype
         C, grid_h, grid_w = isect_offsets.shape
-        channels = colors.shape[-1]
+        channels = colors.shape[-1] + (1 if ranges is not None else 0)
+        ranges_f = _f(ranges)
         colors_f, conics_f, opac_f = _f(colors), _f(conics), _f(opacities)
         vels_f, dc_f, pts_f, bg = _f(pix_vels), _f(depth_compensations), _f(raster_pts), _f(backgrounds)
         f32 = dict(dtype=torch.float32, device=dev)
@@ -826,14 +850,15 @@ class _RasterizeToPoints(torch.autograd.Function):
         last_ids = torch.empty((C, height, width), dtype=torch.int32, device=dev)
         _call(
             "splatad_rasterize_to_points_fwd", C, flatten_ids.numel(), _lib.ptr(means2d),
-            _lib.ptr(conics_f), _lib.ptr(colors_f), channels, _lib.ptr(opac_f), _lib.ptr(vels_f),
+            _lib.ptr(conics_f), _lib.ptr(colors_f) if colors_f.numel() else None, _lib.ptr(ranges_f), channels,
+            _lib.ptr(opac_f), _lib.ptr(vels_f),
             _lib.ptr(dc_f), _lib.ptr(bg), _lib.ptr(pts_f), width, height, tile_width, tile_height,
             grid_w, grid_h, int(bool(compute_alpha_sum_until_points)),
             float(compute_alpha_sum_until_points_threshold), _lib.ptr(isect_offsets),
             _lib.ptr(flatten_ids), depth_channel_idx, _lib.ptr(render_colors), _lib.ptr(render_alphas),
             _lib.ptr(alpha_sum), _lib.ptr(last_ids), _lib.ptr(median_depths), _lib.stream_ptr(dev),
         )
-        ctx.save_for_backward(means2d, conics_f, colors_f, opac_f, vels_f, dc_f, bg, pts_f,
+        ctx.save_for_backward(means2d, conics_f, colors_f, ranges_f, opac_f, vels_f, dc_f, bg, pts_f,
                               isect_offsets, flatten_ids, render_alphas, last_ids)
         ctx.meta = (width, height, tile_width, tile_height, absgrad,
                     bool(compute_alpha_sum_until_points),
@@ -843,12 +868,13 @@ class _RasterizeToPoints(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, v_render_colors, v_render_alphas, v_alpha_sum, v_median_depths):
-        (means2d, conics, colors, opacities, pix_vels, depth_comps, bg, raster_pts, isect_offsets,
+        (means2d, conics, colors, ranges, opacities, pix_vels, depth_comps, bg, raster_pts, isect_offsets,
          flatten_ids, render_alphas, last_ids) = ctx.saved_tensors
         width, height, tile_width, tile_height, absgrad, compute_asum, thr, depth_idx = ctx.meta
         dev = means2d.device
         C, grid_h, grid_w = isect_offsets.shape
-        channels = colors.shape[-1]
+        channels = colors.shape[-1] + (1 if ranges is not None else 0)
+        v_ranges = torch.zeros_like(ranges) if ranges is not None else None
         v_render_colors = _f(v_render_colors)
         v_render_alphas = _f(v_render_alphas)
         v_asum = _f(v_alpha_sum) if (compute_asum and v_alpha_sum is not None) else None
@@ -861,18 +887,20 @@ class _RasterizeToPoints(torch.autograd.Function):
         v_abs = torch.zeros_like(v_means2d) if absgrad else None
         _call(
             "splatad_rasterize_to_points_bwd", C, flatten_ids.numel(), _lib.ptr(means2d),
-            _lib.ptr(conics), _lib.ptr(colors), channels, _lib.ptr(opacities), _lib.ptr(pix_vels),
+            _lib.ptr(conics), _lib.ptr(colors) if colors.numel() else None, _lib.ptr(ranges), channels,
+            _lib.ptr(opacities), _lib.ptr(pix_vels),
             _lib.ptr(depth_comps), _lib.ptr(bg), _lib.ptr(raster_pts), width, height, tile_width,
             tile_height, grid_w, grid_h, int(compute_asum), thr, _lib.ptr(isect_offsets),
             _lib.ptr(flatten_ids), depth_idx, _lib.ptr(render_alphas), _lib.ptr(last_ids),
             _lib.ptr(v_render_colors), _lib.ptr(v_render_alphas), _lib.ptr(v_asum), _lib.ptr(v_abs),
-            _lib.ptr(v_means2d), _lib.ptr(v_conics), _lib.ptr(v_colors), _lib.ptr(v_opacities),
-            _lib.ptr(v_pix_vels), _lib.ptr(v_depth_comps), _lib.stream_ptr(dev),
+            _lib.ptr(v_means2d), _lib.ptr(v_conics), _lib.ptr(v_colors) if v_colors.numel() else None,
+            _lib.ptr(v_opacities), _lib.ptr(v_pix_vels), _lib.ptr(v_depth_comps), _lib.ptr(v_ranges),
+            _lib.stream_ptr(dev),
         )
         if absgrad:
             means2d.absgrad = v_abs
         v_backgrounds = None
-        if ctx.needs_input_grad[6]:
+        if ctx.needs_input_grad[7]:
             v_backgrounds = (v_render_colors * (1.0 - render_alphas).float()).sum(dim=(1, 2))
-        return (v_means2d, v_conics, v_colors, v_opacities, v_pix_vels, v_depth_comps, v_backgrounds) + (
-            None,) * 11
+        return (v_means2d, v_conics, v_colors, v_ranges, v_opacities, v_pix_vels, v_depth_comps,
+                v_backgrounds) + (None,) * 11

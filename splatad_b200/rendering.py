@@ -27,6 +27,7 @@ from .ops import (
     isect_tiles,
     rasterize_to_pixels,
     rasterize_to_points,
+    rasterize_to_points_split,
     spherical_harmonics,
 )
 
@@ -412,10 +413,12 @@ def lidar_rasterization(
         render_alphas = render_alphas[0]  # discard the rest
         alpha_sum_until_points = alpha_sum_until_points[0]  # same alphas for all chunks
     else:
-        render_lidar_features, render_alphas, alpha_sum_until_points, median_depths = rasterize_to_points(
+        # one launch: the range channel is read from `depths` directly (no [C,N,D+1] concatenation)
+        render_lidar_features, render_alphas, alpha_sum_until_points, median_depths = rasterize_to_points_split(
             means2d,
             conics,
-            torch.cat([lidar_features, depths[..., None]], dim=-1),
+            lidar_features,
+            depths,
             opacities,
             pix_vels,
             depth_compensations,
@@ -428,7 +431,6 @@ def lidar_rasterization(
             flatten_ids,
             compute_alpha_sum_until_points=compute_alpha_sum_until_points,
             compute_alpha_sum_until_points_threshold=compute_alpha_sum_until_points_threshold,
-            packed=packed,
             absgrad=absgrad,
         )
 

@@ -295,3 +295,34 @@ def test_accumulate_until_points_known_answer():
     others = np.ones((H, W), bool)
     others[pi, pj] = False
     assert np.all(n(out_a)[0, others] == 0) and np.all(n(out_c)[0, others] == 0)
+
+
+@pytest.mark.parametrize("channels", [1, 5, 32])
+def test_rasterize_to_points_split_ranges(channels):
+    """Ranges passed as their own array give the same render and the same gradients as ranges
+    concatenated to the features as last channel (the reference's layout, gsplat/rendering.py:779)."""
+    from splatad_b200 import ops
+    c = _lidar_case(2, 3000, 32, 256, 32, 8, channels, 500 + channels)
+    g = torch.Generator().manual_seed(5)
+    C, H, W = 2, c["H"], c["W"]
+    v = [t(torch.randn(C, H, W, k, generator=g)) for k in (channels, 1, 1)]
+    common = lambda L: (L["opacities"], L["pix_vels"], L["dcomp"], t(c["pts"]), W, H, c["tw"], c["th"],
+                        t(c["offsets"], torch.int32), t(c["flatten_ids"], torch.int32), True, 0.5)
+    keys = ("means2d", "conics", "feats", "opacities", "pix_vels", "dcomp")
+    A = {k: t(c[k]).requires_grad_(True) for k in keys}
+    outs_a = ops.rasterize_to_points(A["means2d"], A["conics"], A["feats"], *common(A))
+    B = {k: t(c[k]).requires_grad_(True) for k in keys if k != "feats"}
+    B["f"] = t(c["feats"][..., :-1].contiguous()).requires_grad_(True)
+    B["r"] = t(c["feats"][..., -1].contiguous()).requires_grad_(True)
+    outs_b = ops.rasterize_to_points_split(B["means2d"], B["conics"], B["f"], B["r"], *common(B))
+    # same decisions, same arithmetic; the compiler may contract the range accumulation differently
+    assert_close("split render", n(outs_b[0]), n(outs_a[0]), 1e-6, 1e-7)
+    for a, b in zip(outs_a[1:], outs_b[1:]):
+        assert torch.equal(a, b)
+    for outs in (outs_a, outs_b):
+        (outs[0] * v[0]).sum().add((outs[1] * v[1]).sum()).add((outs[2] * v[2]).sum()).backward()
+    for k in ("means2d", "conics", "opacities", "pix_vels", "dcomp"):
+        _grad_check(f"split {k}", B[k].grad, n(A[k].grad), rel=1e-5)
+    if channels > 1:
+        _grad_check("split features", B["f"].grad, n(A["feats"].grad[..., :-1]), rel=1e-5)
+    _grad_check("split ranges", B["r"].grad, n(A["feats"].grad[..., -1]), rel=1e-5)

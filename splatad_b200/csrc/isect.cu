@@ -508,11 +508,18 @@ emit_scan_kernel(const unsigned long long *__restrict__ block_sums, uint32_t nbl
 }
 
 // Exclusive offset of every entry of the emission order: eoff[p] = number of intersections
-// emitted before entry p. Same block ranges as emit_blocksum_kernel.
+// emitted before entry p. Same block ranges as emit_blocksum_kernel. With kRec the entry's tile
+// rectangle is also stored, packed into two words (x0 | width << 16, first grid row |
+// height << 16 with grid row = sensor * tile rows + y; 16-bit fields, used only when
+// sensors * tiles <= 1024), for the row / column split below.
+template <bool kLidar, bool kRec>
 __global__ void __launch_bounds__(kThreads)
-emit_offsets_kernel(EmitArgs e, const unsigned long long *__restrict__ block_offs,
-                    uint32_t *__restrict__ eoff) {
+emit_offsets_kernel(GridArgs<kLidar> a, EmitArgs e, const unsigned long long *__restrict__ block_offs,
+                    uint32_t *__restrict__ eoff, uint32_t *__restrict__ rec_xw,
+                    uint32_t *__restrict__ rec_ys) {
     __shared__ uint32_t wt[33];
+    __shared__ float sb[(kLidar && kRec) ? kMaxElevSmem : 1];
+    if (kRec) stage_boundaries<kLidar>(a, sb);
     uint32_t lo, hi;
     emit_range(e, lo, hi);
     uint32_t running = (uint32_t)block_offs[blockIdx.x];
@@ -523,6 +530,18 @@ emit_offsets_kernel(EmitArgs e, const unsigned long long *__restrict__ block_off
             const uint32_t idx = e.order ? e.order[p] : p;
             const int32_t c = e.tiles_per_gauss[idx];
             cnt = (uint32_t)(c > 0 ? c : 0);
+            if (kRec) {
+                Rect r;
+                uint32_t xw = 0, ys = 0;
+                if (elem_rect<kLidar>(a, idx, r)) {
+                    const uint32_t sensor = e.camera_ids ? (uint32_t)e.camera_ids[idx] : idx / e.N;
+                    const uint32_t tile_rows = kLidar ? a.lidar.n_tiles_elev : a.cam.tile_height;
+                    xw = ((uint32_t)r.x0 & 0xffffu) | ((uint32_t)(r.x1 - r.x0) << 16);
+                    ys = (sensor * tile_rows + (uint32_t)r.y0) | ((uint32_t)(r.y1 - r.y0) << 16);
+                }
+                rec_xw[p] = xw;
+                rec_ys[p] = ys;
+            }
         }
         uint32_t chunk_total;
         const uint32_t ex = block_excl_scan(cnt, wt, chunk_total);
@@ -691,6 +710,626 @@ emit_kernel(GridArgs<kLidar> a, EmitArgs e, const uint32_t *__restrict__ eoff,
 }
 
 // ---------------------------------------------------------------------------------------
+// Row / column split (sensors * tile rows <= 32 and sensors * tiles <= 1024, e.g. one lidar
+// with 57 x 16 tiles): builds the per-tile lists without ever writing the emission out.
+//
+// A rectangle is a stack of `h` row runs, each `w` tiles wide. The tile lists of grid row r are
+// made of the row runs of the rectangles that cover r, in depth order, so the split is done in
+// two stable steps that both write long contiguous runs:
+//   A. rows:    every depth-ordered entry appends one record (run start, width, flatten index,
+//               depth bits, running output offset) to the bucket of each grid row it covers.
+//               Ranks inside a bucket come from one ballot per (32 entries, row); the offsets
+//               from a warp prefix sum of the widths. ~0.4 records per intersection.
+//   B. columns: the records of a row, expanded to their `w` outputs, are cut into units of
+//               2048 consecutive outputs (one block each, 256 per warp). The number of outputs
+//               per column of a piece comes from +1 / -1 updates of a difference row; inside a
+//               piece the warp walks 32 outputs at a time: the records that start inside the
+//               32 outputs set one bit each, which tells every lane its record, and lanes that
+//               hit the same column are ranked in lane order (few records: they take turns,
+//               the columns of one run being distinct; many: one ballot per column bit). The
+//               2048 outputs are put in tile order in shared memory and leave as ~36-entry
+//               runs per tile.
+// Positions are exclusive sums over (earlier tiles, earlier units, earlier warps), all of
+// them plain scans: the result is the same for any scheduling.
+// ---------------------------------------------------------------------------------------
+constexpr uint32_t kSplitMaxRows = 32;                     // one lane per grid row
+constexpr uint32_t kSplitMaxTiles = 1024;
+constexpr uint32_t kSplitMaxSlots = 2048;                  // rows * (row_width + 1)
+constexpr uint32_t kSplitWarps = 8;
+constexpr uint32_t kSplitEntries = kSplitWarps * 256;      // entries per block in step A
+constexpr uint32_t kSplitSub = 256;                        // outputs per warp in step B
+constexpr uint32_t kSplitUnit = kSplitWarps * kSplitSub;   // outputs per block in step B
+constexpr uint32_t kSplitTurns = 8;                        // records per chunk ranked by turns
+constexpr uint32_t kSplitColBits = 11;
+
+struct SplitArgs {
+    // depth-ordered entries
+    const uint32_t *ent_xw;      // x0 | width << 16
+    const uint32_t *ent_yh;      // first grid row | height << 16
+    const uint32_t *order;       // flatten index
+    const uint32_t *depth_key;   // depth bits
+    const int64_t *n_entries_ptr;
+    const int64_t *counters;     // CNT_NISECT
+    int64_t capacity;
+    uint32_t rows;               // grid rows over all sensors
+    uint32_t tile_rows;          // rows per sensor
+    uint32_t row_width, stride;  // tiles per row, row_width + 1
+    uint32_t tile_n_bits, col_bits, wrap;
+    // workspace
+    uint32_t *ha_cnt, *ha_out;   // [units_a][rows]: records / outputs per (entry block, row)
+    uint32_t *row_rec, *row_out, *row_unit;   // [rows + 1] exclusive starts
+    uint32_t *r_xw, *r_off, *r_idx, *r_depth; // records, row bucket after row bucket
+    uint32_t *hb;                // [units_b][stride] outputs per (unit, column)
+    uint32_t *slot_tot, *slot_base;           // [rows * stride]
+};
+
+// Warp-cooperative search: last p in [lo, hi] with off[p] <= q (off non-decreasing,
+// off[lo] <= q). 32 probes per round.
+__device__ __forceinline__ uint32_t warp_find_entry(const uint32_t *__restrict__ off, uint32_t lo,
+                                                    uint32_t hi, uint32_t q, uint32_t lane) {
+    while (lo < hi) {
+        const uint32_t step = (hi - lo + 31) / 32;
+        const uint64_t pp = (uint64_t)lo + (uint64_t)(lane + 1) * step;
+        const bool le = (pp <= hi) && (__ldg(off + pp) <= q);
+        const uint32_t c = __popc(__ballot_sync(0xffffffffu, le));
+        lo += c * step;
+        hi = min(hi, lo + step - 1);
+    }
+    return lo;
+}
+
+// ---- step A: rows -----------------------------------------------------------------------
+struct SplitEntry {
+    uint32_t xw, row0, h;
+    bool valid;
+};
+
+__device__ __forceinline__ SplitEntry split_load_entry(const SplitArgs &a, uint32_t p, uint32_t n_entries) {
+    SplitEntry e{0u, 0u, 0u, p < n_entries};
+    if (e.valid) {
+        e.xw = __ldg(a.ent_xw + p);
+        const uint32_t yh = __ldg(a.ent_yh + p);
+        e.row0 = yh & 0xffffu;
+        e.h = yh >> 16;
+    }
+    return e;
+}
+
+// Records and outputs per grid row of the 256 entries starting at `first`; lane r holds row r.
+__device__ __forceinline__ void split_rows_of_warp(const SplitArgs &a, uint32_t first, uint32_t n_entries,
+                                                   uint32_t lane, uint32_t &cnt, uint32_t &out) {
+    cnt = 0;
+    out = 0;
+    for (uint32_t win = 0; win < 8; ++win) {
+        const uint32_t base = first + win * 32;
+        if (base >= n_entries) break;
+        const SplitEntry e = split_load_entry(a, base + lane, n_entries);
+        const uint32_t w = e.xw >> 16;
+        for (uint32_t r = 0; r < a.rows; ++r) {
+            const bool hit = e.valid && (r - e.row0) < e.h;
+            const uint32_t bal = __ballot_sync(0xffffffffu, hit);
+            if (bal == 0u) continue;
+            const uint32_t s = __reduce_add_sync(0xffffffffu, hit ? w : 0u);
+            if (lane == r) {
+                cnt += __popc(bal);
+                out += s;
+            }
+        }
+    }
+}
+
+// More intersections than output slots: the split is skipped altogether (the record arrays are
+// sized by the capacity) and only the status bit is raised.
+__device__ __forceinline__ bool split_overflow(const SplitArgs &a) {
+    return a.counters[CNT_NISECT] > a.capacity;
+}
+
+__global__ void __launch_bounds__(kSplitWarps * 32)
+rowsplit_count_kernel(SplitArgs a) {
+    __shared__ uint32_t s_cnt[kSplitMaxRows], s_out[kSplitMaxRows];
+    if (split_overflow(a)) return;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t n_entries = (uint32_t)(*a.n_entries_ptr);
+    const uint32_t first = blockIdx.x * kSplitEntries;
+    if (first >= n_entries) return;
+    if (threadIdx.x < kSplitMaxRows) {
+        s_cnt[threadIdx.x] = 0;
+        s_out[threadIdx.x] = 0;
+    }
+    __syncthreads();
+    uint32_t cnt, out;
+    split_rows_of_warp(a, first + warp * 256, n_entries, lane, cnt, out);
+    if (lane < a.rows && cnt) {
+        atomicAdd(&s_cnt[lane], cnt);
+        atomicAdd(&s_out[lane], out);
+    }
+    __syncthreads();
+    if (threadIdx.x < a.rows) {
+        a.ha_cnt[blockIdx.x * a.rows + threadIdx.x] = s_cnt[threadIdx.x];
+        a.ha_out[blockIdx.x * a.rows + threadIdx.x] = s_out[threadIdx.x];
+    }
+}
+
+// One block, 32 rows x 32 segments of entry blocks: exclusive scan over the entry blocks of
+// every row (in place), then the row starts of records, outputs and step-B units.
+__global__ void __launch_bounds__(1024)
+rowsplit_scan_kernel(SplitArgs a) {
+    __shared__ uint32_t seg_c[32][33], seg_o[32][33];
+    __shared__ uint32_t tot_c[32], tot_o[32];
+    const uint32_t r = threadIdx.x & 31, seg = threadIdx.x >> 5;
+    if (split_overflow(a)) return;
+    const uint32_t n_entries = (uint32_t)(*a.n_entries_ptr);
+    const uint32_t n_units = (n_entries + kSplitEntries - 1) / kSplitEntries;
+    const uint32_t per = (n_units + 31) / 32;
+    const uint32_t u_lo = min(n_units, seg * per), u_hi = min(n_units, u_lo + per);
+    const bool live = r < a.rows;
+    uint32_t sc = 0, so = 0;
+    if (live)
+        for (uint32_t u = u_lo; u < u_hi; ++u) {
+            sc += a.ha_cnt[u * a.rows + r];
+            so += a.ha_out[u * a.rows + r];
+        }
+    seg_c[seg][r] = sc;
+    seg_o[seg][r] = so;
+    __syncthreads();
+    uint32_t pc = 0, po = 0, tc = 0, to = 0;
+    for (uint32_t s2 = 0; s2 < 32; ++s2) {
+        const uint32_t vc = seg_c[s2][r], vo = seg_o[s2][r];
+        if (s2 < seg) { pc += vc; po += vo; }
+        tc += vc;
+        to += vo;
+    }
+    if (live)
+        for (uint32_t u = u_lo; u < u_hi; ++u) {
+            const uint32_t vc = a.ha_cnt[u * a.rows + r], vo = a.ha_out[u * a.rows + r];
+            a.ha_cnt[u * a.rows + r] = pc;
+            a.ha_out[u * a.rows + r] = po;
+            pc += vc;
+            po += vo;
+        }
+    if (seg == 0) {
+        tot_c[r] = live ? tc : 0u;
+        tot_o[r] = live ? to : 0u;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        // exclusive scans over the rows (one warp)
+        const uint32_t vc = tot_c[r], vo = tot_o[r];
+        const uint32_t vu = (vo + kSplitUnit - 1) / kSplitUnit;
+        uint32_t ic = vc, io = vo, iu = vu;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t oc = __shfl_up_sync(0xffffffffu, ic, off);
+            const uint32_t oo = __shfl_up_sync(0xffffffffu, io, off);
+            const uint32_t ou = __shfl_up_sync(0xffffffffu, iu, off);
+            if (r >= (uint32_t)off) { ic += oc; io += oo; iu += ou; }
+        }
+        if (r < a.rows) {
+            a.row_rec[r] = ic - vc;
+            a.row_out[r] = io - vo;
+            a.row_unit[r] = iu - vu;
+        }
+        if (r == 31) {
+            a.row_rec[a.rows] = ic;
+            a.row_out[a.rows] = io;
+            a.row_unit[a.rows] = iu;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kSplitWarps * 32)
+rowsplit_scatter_kernel(SplitArgs a) {
+    __shared__ uint32_t w_cnt[kSplitWarps][kSplitMaxRows], w_out[kSplitWarps][kSplitMaxRows];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t lt = (1u << lane) - 1u;
+    if (split_overflow(a)) return;
+    const uint32_t n_entries = (uint32_t)(*a.n_entries_ptr);
+    const uint32_t first = blockIdx.x * kSplitEntries;
+    if (first >= n_entries) return;
+    const uint32_t cap = (uint32_t)(a.capacity < 0x7fffffffll ? a.capacity : 0x7fffffffll);
+    uint32_t cnt, out;
+    split_rows_of_warp(a, first + warp * 256, n_entries, lane, cnt, out);
+    w_cnt[warp][lane] = cnt;
+    w_out[warp][lane] = out;
+    __syncthreads();
+    // lane r: where this warp's records / outputs of row r start
+    uint32_t rec_at = 0, out_at = 0;
+    if (lane < a.rows) {
+        rec_at = a.row_rec[lane] + a.ha_cnt[blockIdx.x * a.rows + lane];
+        out_at = a.row_out[lane] + a.ha_out[blockIdx.x * a.rows + lane];
+        for (uint32_t w2 = 0; w2 < warp; ++w2) {
+            rec_at += w_cnt[w2][lane];
+            out_at += w_out[w2][lane];
+        }
+    }
+    for (uint32_t win = 0; win < 8; ++win) {
+        const uint32_t base = first + warp * 256 + win * 32;
+        if (base >= n_entries) break;
+        const uint32_t p = base + lane;
+        const SplitEntry e = split_load_entry(a, p, n_entries);
+        const uint32_t w = e.xw >> 16;
+        uint32_t xs = 0, idx = 0, depth = 0;
+        if (e.valid) {
+            int32_t x0 = (int32_t)(int16_t)(e.xw & 0xffffu);
+            if (a.wrap) {
+                x0 %= (int32_t)a.row_width;
+                if (x0 < 0) x0 += (int32_t)a.row_width;
+            }
+            xs = (uint32_t)x0;
+            idx = __ldg(a.order + p);
+            depth = __ldg(a.depth_key + p);
+        }
+        for (uint32_t r = 0; r < a.rows; ++r) {
+            const bool hit = e.valid && (r - e.row0) < e.h;
+            const uint32_t bal = __ballot_sync(0xffffffffu, hit);
+            if (bal == 0u) continue;
+            // exclusive prefix of the widths of the hit lanes
+            const uint32_t v = hit ? w : 0u;
+            uint32_t inc = v;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const uint32_t o = __shfl_up_sync(0xffffffffu, inc, off);
+                if (lane >= (uint32_t)off) inc += o;
+            }
+            const uint32_t total = __shfl_sync(0xffffffffu, inc, 31);
+            const uint32_t rbase = __shfl_sync(0xffffffffu, rec_at, r);
+            const uint32_t obase = __shfl_sync(0xffffffffu, out_at, r);
+            if (hit) {
+                const uint32_t pos = rbase + __popc(bal & lt);
+                if (pos < cap) {
+                    a.r_xw[pos] = xs | (w << 16);
+                    a.r_off[pos] = obase + inc - v;
+                    a.r_idx[pos] = idx;
+                    a.r_depth[pos] = depth;
+                }
+            }
+            if (lane == r) {
+                rec_at += __popc(bal);
+                out_at += total;
+            }
+        }
+    }
+}
+
+// ---- step B: columns --------------------------------------------------------------------
+struct SplitUnit {
+    uint32_t row, q_lo, q_hi;   // grid row and output range
+    uint32_t n_rec, n_out;      // records / outputs in all rows
+    bool live;
+};
+
+__device__ __forceinline__ SplitUnit split_unit(const SplitArgs &a, uint32_t u, uint32_t lane) {
+    SplitUnit s{};
+    const uint32_t n_units = a.row_unit[a.rows];
+    s.n_rec = a.row_rec[a.rows];
+    s.n_out = a.row_out[a.rows];
+    s.live = u < n_units;
+    if (!s.live) return s;
+    const bool le = lane < a.rows && a.row_unit[lane] <= u;
+    // rows without outputs own no unit: the last row whose first unit is <= u that has units
+    const uint32_t m = __ballot_sync(0xffffffffu, le);
+    s.row = 31u - __clz(m);
+    const uint32_t k = u - a.row_unit[s.row];
+    const uint32_t row_end = a.row_out[s.row + 1];
+    s.q_lo = min(row_end, a.row_out[s.row] + k * kSplitUnit);
+    s.q_hi = min(row_end, s.q_lo + kSplitUnit);
+    return s;
+}
+
+// Adds the outputs [q_lo, q_hi) to a difference row (one record per lane).
+__device__ __forceinline__ void split_count_cols(int32_t *d, const SplitArgs &a, uint32_t q_lo,
+                                                 uint32_t q_hi, uint32_t n_rec, uint32_t n_out,
+                                                 uint32_t lane) {
+    if (q_lo >= q_hi || n_rec == 0) return;
+    const uint32_t rw = a.row_width;
+    uint32_t base = warp_find_entry(a.r_off, 0, n_rec - 1, q_lo, lane);
+    while (true) {
+        const uint32_t p = base + lane;
+        uint32_t s1 = 0u;
+        if (p < n_rec) {
+            const uint32_t s0 = __ldg(a.r_off + p);
+            s1 = (p + 1 < n_rec) ? __ldg(a.r_off + p + 1) : n_out;
+            if (s0 < q_hi && s1 > q_lo) {
+                const uint32_t xw = __ldg(a.r_xw + p);
+                const uint32_t k_lo = max(s0, q_lo) - s0, k_hi = min(s1, q_hi) - s0;
+                uint32_t start = (xw & 0xffffu) + k_lo;
+                uint32_t len = k_hi - k_lo;
+                if (a.wrap) {
+                    if (len >= rw) {   // the run covers every tile of the row `full` times
+                        const int32_t full = (int32_t)(len / rw);
+                        atomicAdd(d, full);
+                        atomicAdd(d + rw, -full);
+                        len -= (uint32_t)full * rw;
+                    }
+                    if (len) {
+                        if (start >= rw) start %= rw;
+                        const uint32_t end = start + len;
+                        atomicAdd(d + start, 1);
+                        if (end <= rw) {
+                            atomicAdd(d + end, -1);
+                        } else {
+                            atomicAdd(d + rw, -1);
+                            atomicAdd(d, 1);
+                            atomicAdd(d + (end - rw), -1);
+                        }
+                    }
+                } else if (start + len <= rw) {
+                    atomicAdd(d + start, 1);
+                    atomicAdd(d + start + len, -1);
+                }
+            }
+        }
+        const uint32_t last_s1 = __shfl_sync(0xffffffffu, s1, 31);
+        if (base + 32 >= n_rec || last_s1 >= q_hi) break;
+        base += 32;
+    }
+}
+
+// In-place inclusive prefix sum of d[0 .. n) by one warp.
+__device__ __forceinline__ void warp_prefix_inplace(int32_t *d, uint32_t n, uint32_t lane) {
+    int32_t carry = 0;
+    for (uint32_t i0 = 0; i0 < n; i0 += 32) {
+        const uint32_t i = i0 + lane;
+        int32_t v = i < n ? d[i] : 0;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int32_t o = __shfl_up_sync(0xffffffffu, v, off);
+            if (lane >= (uint32_t)off) v += o;
+        }
+        v += carry;
+        if (i < n) d[i] = v;
+        carry = __shfl_sync(0xffffffffu, v, 31);
+    }
+}
+
+__global__ void __launch_bounds__(kSplitWarps * 32)
+colsplit_count_kernel(SplitArgs a) {
+    extern __shared__ int32_t s_d[];   // [stride]
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (split_overflow(a)) return;
+    const SplitUnit u = split_unit(a, blockIdx.x, lane);
+    if (!u.live) return;
+    for (uint32_t i = tid; i < a.stride; i += blockDim.x) s_d[i] = 0;
+    __syncthreads();
+    const uint32_t q_lo = min(u.q_hi, u.q_lo + warp * kSplitSub);
+    split_count_cols(s_d, a, q_lo, min(u.q_hi, q_lo + kSplitSub), u.n_rec, u.n_out, lane);
+    __syncthreads();
+    if (warp == 0) warp_prefix_inplace(s_d, a.stride, lane);
+    __syncthreads();
+    uint32_t *row = a.hb + (size_t)blockIdx.x * a.stride;
+    for (uint32_t i = tid; i < a.stride; i += blockDim.x) row[i] = (uint32_t)s_d[i];
+}
+
+// Block r: exclusive scan over the units of grid row r for every column (in place); the
+// column totals go to slot_tot[r][col].
+__global__ void __launch_bounds__(1024)
+colsplit_scan_kernel(SplitArgs a) {
+    __shared__ uint32_t seg_sum[32][33];
+    const uint32_t lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
+    const uint32_t r = blockIdx.x;
+    if (split_overflow(a)) return;
+    const uint32_t ub0 = a.row_unit[r], n_units = a.row_unit[r + 1] - ub0;
+    const uint32_t per = (n_units + 31) / 32;
+    const uint32_t u_lo = min(n_units, seg * per), u_hi = min(n_units, u_lo + per);
+    const size_t S = a.stride;
+    for (uint32_t c0 = 0; c0 < a.stride; c0 += 32) {
+        const uint32_t c = c0 + lane;
+        const bool live = c < a.stride;
+        uint32_t *col = a.hb + (size_t)ub0 * S + c;
+        uint32_t sum = 0;
+        if (live) {
+            uint32_t u = u_lo;
+            for (; u + 4 <= u_hi; u += 4) {
+                const uint32_t *h = col + (size_t)u * S;
+                const uint32_t v0 = h[0], v1 = h[S], v2 = h[2 * S], v3 = h[3 * S];
+                sum += v0 + v1 + v2 + v3;
+            }
+            for (; u < u_hi; ++u) sum += col[(size_t)u * S];
+        }
+        __syncthreads();
+        seg_sum[seg][lane] = sum;
+        __syncthreads();
+        uint32_t prefix = 0, total = 0;
+        for (uint32_t s2 = 0; s2 < 32; ++s2) {
+            const uint32_t v = seg_sum[s2][lane];
+            if (s2 < seg) prefix += v;
+            total += v;
+        }
+        if (live) {
+            uint32_t run = prefix;
+            for (uint32_t u = u_lo; u < u_hi; ++u) {
+                uint32_t *h = col + (size_t)u * S;
+                const uint32_t v = *h;
+                *h = run;
+                run += v;
+            }
+            if (seg == 0) a.slot_tot[r * a.stride + c] = total;
+        }
+    }
+}
+
+// One block of 1024 threads, two slots each: slot_base = exclusive scan of slot_tot.
+__global__ void __launch_bounds__(1024)
+split_base_kernel(const uint32_t *__restrict__ slot_tot, uint32_t n_slots, uint32_t *__restrict__ slot_base) {
+    __shared__ uint32_t wt[33];
+    const uint32_t i0 = 2 * threadIdx.x, i1 = i0 + 1;
+    const uint32_t v0 = i0 < n_slots ? slot_tot[i0] : 0u;
+    const uint32_t v1 = i1 < n_slots ? slot_tot[i1] : 0u;
+    uint32_t total;
+    const uint32_t ex = block_excl_scan(v0 + v1, wt, total);
+    if (i0 < n_slots) slot_base[i0] = ex;
+    if (i1 < n_slots) slot_base[i1] = ex + v0;
+}
+
+struct SplitWindow {
+    uint32_t xw, s0, s1, idx, depth;
+};
+
+__device__ __forceinline__ SplitWindow split_load_window(const SplitArgs &a, uint32_t base, uint32_t lane,
+                                                         uint32_t n_rec, uint32_t n_out) {
+    SplitWindow win{0u, 0u, 0u, 0u, 0u};
+    const uint32_t p = base + lane;
+    if (p < n_rec) {
+        win.xw = __ldg(a.r_xw + p);
+        win.s0 = __ldg(a.r_off + p);
+        win.s1 = (p + 1 < n_rec) ? __ldg(a.r_off + p + 1) : n_out;
+        win.idx = __ldg(a.r_idx + p);
+        win.depth = __ldg(a.r_depth + p);
+    }
+    return win;
+}
+
+__global__ void __launch_bounds__(kSplitWarps * 32)
+colsplit_scatter_kernel(SplitArgs a, int64_t *__restrict__ isect_ids, int32_t *__restrict__ flatten_ids,
+                        int64_t *__restrict__ counters) {
+    extern __shared__ int32_t s_dyn[];
+    // [kSplitWarps][stride] column tables, [stride] global - local start, staged outputs
+    int32_t *s_tab = s_dyn;
+    int32_t *s_shift = s_tab + kSplitWarps * a.stride;
+    uint32_t *st_hi = reinterpret_cast<uint32_t *>(s_shift + a.stride);
+    uint32_t *st_depth = st_hi + kSplitUnit;
+    uint32_t *st_idx = st_depth + kSplitUnit;
+    __shared__ uint32_t wt[33];
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t lt = (1u << lane) - 1u, le = 0xffffffffu >> (31 - lane);
+    if (split_overflow(a)) {
+        if (blockIdx.x == 0 && tid == 0)
+            atomicOr((unsigned long long *)&counters[CNT_STATUS], (unsigned long long)ST_OVERFLOW_CAPACITY);
+        return;
+    }
+    const SplitUnit u = split_unit(a, blockIdx.x, lane);
+    if (!u.live) return;
+    const uint32_t cap = (uint32_t)(a.capacity < 0x7fffffffll ? a.capacity : 0x7fffffffll);
+    const uint32_t q_lo = min(u.q_hi, u.q_lo + warp * kSplitSub);
+    const uint32_t q_hi = min(u.q_hi, q_lo + kSplitSub);
+    int32_t *wd = s_tab + warp * a.stride;
+    uint32_t *hist = reinterpret_cast<uint32_t *>(wd);
+
+    // outputs per column of this warp's piece
+    for (uint32_t i = lane; i < a.stride; i += 32) wd[i] = 0;
+    __syncwarp();
+    split_count_cols(wd, a, q_lo, q_hi, u.n_rec, u.n_out, lane);
+    __syncwarp();
+    warp_prefix_inplace(wd, a.stride, lane);
+    __syncthreads();
+    // local start of every (warp, column) inside the unit, and the shift to global positions
+    const uint32_t *hrow = a.hb + (size_t)blockIdx.x * a.stride;
+    const uint32_t *sbase = a.slot_base + u.row * a.stride;
+    uint32_t carry = 0;
+    for (uint32_t c0 = 0; c0 < a.stride; c0 += blockDim.x) {
+        const uint32_t c = c0 + tid;
+        uint32_t tot = 0;
+        if (c < a.stride)
+#pragma unroll
+            for (uint32_t w2 = 0; w2 < kSplitWarps; ++w2) tot += (uint32_t)s_tab[w2 * a.stride + c];
+        uint32_t chunk_total;
+        const uint32_t ex = block_excl_scan(tot, wt, chunk_total);
+        if (c < a.stride) {
+            uint32_t run = carry + ex;
+            s_shift[c] = (int32_t)(hrow[c] + sbase[c] - run);
+#pragma unroll
+            for (uint32_t w2 = 0; w2 < kSplitWarps; ++w2) {
+                const uint32_t v = (uint32_t)s_tab[w2 * a.stride + c];
+                s_tab[w2 * a.stride + c] = (int32_t)run;
+                run += v;
+            }
+        }
+        carry += chunk_total;
+    }
+    __syncthreads();
+
+    // walk the piece, 32 outputs at a time
+    const uint32_t sensor = u.row / a.tile_rows, y = u.row - sensor * a.tile_rows;
+    const uint32_t hi_row = (sensor << a.tile_n_bits) | (y * a.row_width);
+    if (q_lo < q_hi && u.n_rec > 0) {
+        uint32_t base = warp_find_entry(a.r_off, 0, u.n_rec - 1, q_lo, lane);
+        uint32_t q = q_lo;
+        SplitWindow win = split_load_window(a, base, lane, u.n_rec, u.n_out);
+        while (q < q_hi && base < u.n_rec) {
+            const SplitWindow nxt = split_load_window(a, base + 32, lane, u.n_rec, u.n_out);
+            const uint32_t n_in = min(32u, u.n_rec - base);
+            const uint32_t w_end = min(__shfl_sync(0xffffffffu, win.s1, n_in - 1), q_hi);
+            uint32_t cur = 0;   // window lane of the record owning output q
+            while (q < w_end) {
+                // records after `cur` that start inside this chunk (one may start exactly at q)
+                const bool starts = lane > cur && lane < n_in && win.s0 >= q && (win.s0 - q) < 32u;
+                const uint32_t B = __reduce_or_sync(0xffffffffu, starts ? (1u << (win.s0 - q)) : 0u);
+                const uint32_t o = q + lane;
+                const uint32_t rel = __popc(B & le);
+                const uint32_t own = (cur + rel) & 31u;
+                const uint32_t jxw = __shfl_sync(0xffffffffu, win.xw, own);
+                const uint32_t e0 = __shfl_sync(0xffffffffu, win.s0, own);
+                const uint32_t idx = __shfl_sync(0xffffffffu, win.idx, own);
+                const uint32_t depth = __shfl_sync(0xffffffffu, win.depth, own);
+                const uint32_t w = jxw >> 16;
+                uint32_t col = (jxw & 0xffffu) + (o - e0);
+                if (a.wrap && col >= a.row_width) {
+                    col -= a.row_width;
+                    if (col >= a.row_width) col %= a.row_width;
+                }
+                // a column outside the row cannot come from a consistent record
+                const bool active = o < w_end && col < a.row_width;
+                if (!active) col = 0;
+                // Rank among the outputs of this chunk in the same column. The columns of one run
+                // are distinct (unless it is wider than a full turn), so with few records in the
+                // chunk they take turns; otherwise lanes with equal columns are matched with one
+                // ballot per column bit and ranked in lane order.
+                const uint32_t n_own = __popc(B) + 1u;
+                const bool twins = a.wrap && __any_sync(0xffffffffu, active && w > a.row_width);
+                uint32_t lpos = 0;
+                if (!twins && n_own <= kSplitTurns) {
+                    for (uint32_t turn = 0; turn < n_own; ++turn) {
+                        if (active && rel == turn) {
+                            lpos = hist[col];
+                            hist[col] = lpos + 1u;
+                        }
+                        __syncwarp();
+                    }
+                } else {
+                    uint32_t peers = __ballot_sync(0xffffffffu, active);
+#pragma unroll
+                    for (uint32_t bit = 0; bit < kSplitColBits; ++bit) {
+                        if (bit >= a.col_bits) break;
+                        const bool one = (col >> bit) & 1u;
+                        const uint32_t bal = __ballot_sync(0xffffffffu, one);
+                        peers &= one ? bal : ~bal;
+                    }
+                    const uint32_t rank = __popc(peers & lt), cnt = __popc(peers);
+                    uint32_t v = 0;
+                    if (active) v = hist[col];
+                    __syncwarp();
+                    if (active && rank + 1 == cnt) hist[col] = v + cnt;   // one lane per column
+                    __syncwarp();
+                    lpos = v + rank;
+                }
+                if (active && lpos < kSplitUnit) {
+                    st_hi[lpos] = hi_row + col;
+                    st_depth[lpos] = depth;
+                    st_idx[lpos] = idx;
+                }
+                cur += __popc(B);
+                q = min(q + 32u, w_end);
+            }
+            base += 32;
+            win = nxt;
+        }
+    }
+    __syncthreads();
+    // the unit's outputs now sit in tile order: consecutive threads write consecutive entries
+    const uint32_t n_unit = u.q_hi - u.q_lo;
+    const uint32_t tile_mask = (1u << a.tile_n_bits) - 1u;
+    for (uint32_t i = tid; i < n_unit; i += blockDim.x) {
+        const uint32_t hi = st_hi[i];
+        const uint32_t col = (hi & tile_mask) - y * a.row_width;
+        const uint32_t pos = i + (uint32_t)s_shift[col < a.stride ? col : 0];
+        if (pos < cap) {
+            isect_ids[pos] = ((int64_t)hi << 32) | (int64_t)st_depth[i];
+            flatten_ids[pos] = (int32_t)st_idx[i];
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // Offsets: offsets[c, tile] = first position whose (sensor, tile) >= (c, tile).
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
@@ -727,6 +1366,7 @@ struct PlanWs {
     unsigned long long *block_offs;
     uint32_t *keyA, *valA, *keyB, *valB;
     uint32_t *eoff;
+    uint32_t *ha_cnt, *ha_out;   // row split: per (block of entries, grid row)
     size_t bytes;
 };
 
@@ -745,6 +1385,9 @@ static PlanWs carve_plan(void *ws, uint64_t total) {
     p.keyB = (uint32_t *)take(sizeof(uint32_t) * total);
     p.valB = (uint32_t *)take(sizeof(uint32_t) * total);
     p.eoff = (uint32_t *)take(sizeof(uint32_t) * total);
+    const size_t n_ha = (size_t)((total + 2047) / 2048) * 32;
+    p.ha_cnt = (uint32_t *)take(sizeof(uint32_t) * n_ha);
+    p.ha_out = (uint32_t *)take(sizeof(uint32_t) * n_ha);
     p.bytes = off;
     return p;
 }
@@ -767,6 +1410,35 @@ static FillWs carve_fill(void *ws, uint64_t cap) {
     return f;
 }
 
+struct SplitWs {
+    uint32_t *row_rec, *row_out, *row_unit;
+    uint32_t *r_xw, *r_off, *r_idx, *r_depth;
+    uint32_t *hb, *slot_tot, *slot_base;
+    uint32_t units_b_cap;
+    size_t bytes;
+};
+
+static SplitWs carve_split(void *ws, uint64_t cap, uint32_t rows, uint32_t stride) {
+    SplitWs w;
+    char *c = (char *)ws;
+    size_t off = 0;
+    auto take = [&](size_t n) { char *r = c ? c + off : nullptr; off += align256(n); return r; };
+    w.row_rec = (uint32_t *)take(sizeof(uint32_t) * (kSplitMaxRows + 1));
+    w.row_out = (uint32_t *)take(sizeof(uint32_t) * (kSplitMaxRows + 1));
+    w.row_unit = (uint32_t *)take(sizeof(uint32_t) * (kSplitMaxRows + 1));
+    w.r_xw = (uint32_t *)take(sizeof(uint32_t) * cap);
+    w.r_off = (uint32_t *)take(sizeof(uint32_t) * cap);
+    w.r_idx = (uint32_t *)take(sizeof(uint32_t) * cap);
+    w.r_depth = (uint32_t *)take(sizeof(uint32_t) * cap);
+    // every grid row rounds its outputs up to whole units
+    w.units_b_cap = (uint32_t)((cap + kSplitUnit - 1) / kSplitUnit) + rows;
+    w.hb = (uint32_t *)take(sizeof(uint32_t) * (size_t)w.units_b_cap * stride);
+    w.slot_tot = (uint32_t *)take(sizeof(uint32_t) * kSplitMaxSlots);
+    w.slot_base = (uint32_t *)take(sizeof(uint32_t) * kSplitMaxSlots);
+    w.bytes = off;
+    return w;
+}
+
 static uint32_t bit_length(uint64_t v) {
     uint32_t b = 0;
     while (v) { ++b; v >>= 1; }
@@ -781,6 +1453,15 @@ struct IsectGeom {
     const int64_t *camera_ids;
     const uint32_t *depth_bits;
 };
+
+// The row / column split applies to sorted output with at most 32 grid rows and 1024 tiles over
+// all sensors (every field of the packed rectangle record then fits 16 bits).
+static bool use_split(const IsectGeom &g, int sort) {
+    if (!sort || (uint64_t)g.C * g.n_tiles > kSplitMaxTiles) return false;
+    const uint64_t rw = g.lidar ? g.lid.lidar.n_tiles_azim : g.cam.cam.tile_width;
+    const uint64_t rows = (uint64_t)g.C * (g.n_tiles / rw);
+    return rows <= kSplitMaxRows && rows * (rw + 1) <= kSplitMaxSlots;
+}
 
 // plan: counts, depth order of visible Gaussians, n_isects.
 static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, void *workspace,
@@ -813,6 +1494,8 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
     EmitArgs e{};
     e.total = g.total;
     e.tiles_per_gauss = tiles_per_gauss;
+    e.camera_ids = g.camera_ids;
+    e.N = g.N;
     if (sort) {
         // stable sort of the visible (count > 0) elements by depth bits: 4 passes of 8 bits
         uint32_t *ka = p.keyA, *va = p.valA, *kb = p.keyB, *vb = p.valB;
@@ -871,9 +1554,22 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
         SPL_PROF("emit_scan_kernel", st);
         emit_scan_kernel<<<1, 1024, 0, st>>>(p.block_sums, kSortGrid, p.block_offs, p.counters);
     }
+    // with few enough sensor-tiles the fill uses the row / column split and wants the rectangles
+    // of the sorted entries; keyA / valA are free once the depth order sits in keyB / valB
+    const bool rec = use_split(g, sort);
     {
         SPL_PROF("emit_offsets_kernel", st);
-        emit_offsets_kernel<<<kSortGrid, kThreads, 0, st>>>(e, p.block_offs, p.eoff);
+        if (g.lidar) {
+            if (rec) emit_offsets_kernel<true, true><<<kSortGrid, kThreads, 0, st>>>(
+                g.lid, e, p.block_offs, p.eoff, p.keyA, p.valA);
+            else emit_offsets_kernel<true, false><<<kSortGrid, kThreads, 0, st>>>(
+                g.lid, e, p.block_offs, p.eoff, nullptr, nullptr);
+        } else {
+            if (rec) emit_offsets_kernel<false, true><<<kSortGrid, kThreads, 0, st>>>(
+                g.cam, e, p.block_offs, p.eoff, p.keyA, p.valA);
+            else emit_offsets_kernel<false, false><<<kSortGrid, kThreads, 0, st>>>(
+                g.cam, e, p.block_offs, p.eoff, nullptr, nullptr);
+        }
     }
     if (host_counts != nullptr)
         cudaMemcpyAsync(host_counts, p.counters, sizeof(int64_t) * CNT_SLOTS, cudaMemcpyDeviceToHost, st);
@@ -912,6 +1608,66 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
                 emit_kernel<false, true><<<kSortGrid, kThreads, 0, st>>>(
                     g.cam, e, p.eoff, p.counters, nullptr, nullptr, isect_ids, flatten_ids, p.counters);
             }
+        }
+    } else if (use_split(g, sort)) {
+        SplitArgs a{};
+        a.ent_xw = p.keyA;
+        a.ent_yh = p.valA;
+        a.order = p.valB;
+        a.depth_key = p.keyB;
+        a.n_entries_ptr = p.counters + CNT_NVIS;
+        a.counters = p.counters;
+        a.capacity = capacity;
+        a.row_width = g.lidar ? g.lid.lidar.n_tiles_azim : g.cam.cam.tile_width;
+        a.stride = a.row_width + 1;
+        a.tile_rows = g.n_tiles / a.row_width;
+        a.rows = g.C * a.tile_rows;
+        a.tile_n_bits = g.tile_n_bits;
+        a.col_bits = max(1u, bit_length((uint64_t)a.row_width - 1));
+        a.wrap = g.lidar ? 1u : 0u;
+        SplitWs w = carve_split(fill_workspace, (uint64_t)capacity, a.rows, a.stride);
+        SPL_REQUIRE(fill_workspace != nullptr && fill_workspace_bytes >= w.bytes,
+                    SPLATAD_ERR_WORKSPACE, "isect fill: workspace too small (%zu < %zu)",
+                    fill_workspace_bytes, w.bytes);
+        a.ha_cnt = p.ha_cnt;
+        a.ha_out = p.ha_out;
+        a.row_rec = w.row_rec; a.row_out = w.row_out; a.row_unit = w.row_unit;
+        a.r_xw = w.r_xw; a.r_off = w.r_off; a.r_idx = w.r_idx; a.r_depth = w.r_depth;
+        a.hb = w.hb; a.slot_tot = w.slot_tot; a.slot_base = w.slot_base;
+        const uint32_t units_a = div_up(g.total, kSplitEntries);
+        const size_t smem_count = sizeof(int32_t) * a.stride;
+        const size_t smem_scatter = sizeof(int32_t) * ((kSplitWarps + 1) * a.stride + 3 * kSplitUnit);
+        if (smem_scatter > 48 * 1024)   // above the default dynamic shared memory limit
+            cudaFuncSetAttribute(colsplit_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem_scatter);
+        {
+            SPL_PROF("rowsplit_count_kernel", st);
+            rowsplit_count_kernel<<<units_a, kSplitWarps * 32, 0, st>>>(a);
+        }
+        {
+            SPL_PROF("rowsplit_scan_kernel", st);
+            rowsplit_scan_kernel<<<1, 1024, 0, st>>>(a);
+        }
+        {
+            SPL_PROF("rowsplit_scatter_kernel", st);
+            rowsplit_scatter_kernel<<<units_a, kSplitWarps * 32, 0, st>>>(a);
+        }
+        {
+            SPL_PROF("colsplit_count_kernel", st);
+            colsplit_count_kernel<<<w.units_b_cap, kSplitWarps * 32, smem_count, st>>>(a);
+        }
+        {
+            SPL_PROF("colsplit_scan_kernel", st);
+            colsplit_scan_kernel<<<a.rows, 1024, 0, st>>>(a);
+        }
+        {
+            SPL_PROF("split_base_kernel", st);
+            split_base_kernel<<<1, 1024, 0, st>>>(w.slot_tot, a.rows * a.stride, w.slot_base);
+        }
+        {
+            SPL_PROF("colsplit_scatter_kernel", st);
+            colsplit_scatter_kernel<<<w.units_b_cap, kSplitWarps * 32, smem_scatter, st>>>(
+                a, isect_ids, flatten_ids, p.counters);
         }
     } else {
         FillWs f = carve_fill(fill_workspace, (uint64_t)capacity);
@@ -998,7 +1754,11 @@ extern "C" size_t splatad_isect_plan_workspace_bytes(uint64_t total_elems) {
 }
 
 extern "C" size_t splatad_isect_fill_workspace_bytes(uint64_t capacity) {
-    return carve_fill(nullptr, capacity).bytes;
+    // the larger of the radix buffers and the split's records + tables; (units + rows) * stride
+    // <= (capacity / 2048 + 3) * 1025 for every geometry the split accepts
+    const size_t a = carve_fill(nullptr, capacity).bytes;
+    const size_t b = carve_split(nullptr, capacity, 2, kSplitMaxTiles + 1).bytes;
+    return a > b ? a : b;
 }
 
 static int make_cam_geom(IsectGeom &g, uint32_t C, uint32_t N, uint64_t total,

@@ -201,6 +201,9 @@ int splatad_sh_bwd(uint32_t n_elems, uint32_t K, uint32_t degrees_to_use, const 
  *          (sensor, tile, depth bits, flatten index) when sort != 0, in flatten-index order
  *          otherwise. capacity >= n_isects; if it is smaller, status bit 1 is set in
  *          host_counts[2] (copied again by _fill) and the outputs are incomplete.
+ *          tile_offsets (optional, [C * tiles] int32, sort != 0 only) receives what
+ *          splatad_isect_offset_encode would compute from isect_ids - the fill knows every
+ *          tile's start already, so asking for it here saves that pass.
  * `total_elems` is C*N for the [C,N] layout (camera_ids NULL) or nnz for the packed layout
  * (camera_ids [nnz] int64 gives the sensor of each row, N is ignored).
  * Depths must be non-negative: their bit patterns are ordered as unsigned integers.
@@ -218,11 +221,13 @@ int splatad_isect_tiles_fill(
     const float *depths, const int64_t *camera_ids, uint32_t tile_size, uint32_t tile_width,
     uint32_t tile_height, int32_t sort, const int32_t *tiles_per_gauss, void *plan_workspace,
     void *fill_workspace, size_t fill_workspace_bytes, int64_t capacity, int64_t *isect_ids,
-    int32_t *flatten_ids, int64_t *host_counts, void *stream);
+    int32_t *flatten_ids, int32_t *tile_offsets, int64_t *host_counts, void *stream);
 
 /* elev_boundaries [n_boundaries] = tile boundaries in elevation (n_boundaries - 1 tile rows);
- * the number of azimuth tiles is ceil(360 / tile_azim_resolution) as in
- * gsplat/cuda/csrc/rasterization.cu:435. */
+ * the number of azimuth tiles is ceil(360 / tile_azim_resolution) in float32 as in
+ * gsplat/cuda/csrc/rasterization.cu:435; splatad_lidar_azimuth_tiles returns that number (to
+ * size tile_offsets). */
+uint32_t splatad_lidar_azimuth_tiles(float tile_azim_resolution);
 int splatad_isect_lidar_tiles_plan(
     uint32_t C, uint32_t N, uint64_t total_elems, const float *means2d, const float *radii,
     const float *depths, const int64_t *camera_ids, const float *elev_boundaries,
@@ -235,7 +240,7 @@ int splatad_isect_lidar_tiles_fill(
     uint32_t n_boundaries, float tile_azim_resolution, float min_azim, int32_t sort,
     const int32_t *tiles_per_gauss, void *plan_workspace, void *fill_workspace,
     size_t fill_workspace_bytes, int64_t capacity, int64_t *isect_ids, int32_t *flatten_ids,
-    int64_t *host_counts, void *stream);
+    int32_t *tile_offsets, int64_t *host_counts, void *stream);
 
 /* isect_offset_encode_tensor - gsplat/cuda/csrc/rasterization.cu:264-285.
  * offsets [C, tile_height, tile_width] int32. */

@@ -721,13 +721,13 @@ emit_kernel(GridArgs<kLidar> a, EmitArgs e, const uint32_t *__restrict__ eoff,
 //               Ranks inside a bucket come from one ballot per (32 entries, row); the offsets
 //               from a warp prefix sum of the widths. ~0.4 records per intersection.
 //   B. columns: the records of a row, expanded to their `w` outputs, are cut into units of
-//               2048 consecutive outputs (one block each, 256 per warp). The number of outputs
+//               4096 consecutive outputs (one block each, 512 per warp). The number of outputs
 //               per column of a piece comes from +1 / -1 updates of a difference row; inside a
 //               piece the warp walks 32 outputs at a time: the records that start inside the
 //               32 outputs set one bit each, which tells every lane its record, and lanes that
 //               hit the same column are ranked in lane order (few records: they take turns,
 //               the columns of one run being distinct; many: one ballot per column bit). The
-//               2048 outputs are put in tile order in shared memory and leave as ~36-entry
+//               4096 outputs are put in tile order in shared memory and leave as ~70-entry
 //               runs per tile.
 // Positions are exclusive sums over (earlier tiles, earlier units, earlier warps), all of
 // them plain scans: the result is the same for any scheduling.
@@ -736,8 +736,9 @@ constexpr uint32_t kSplitMaxRows = 32;                     // one lane per grid 
 constexpr uint32_t kSplitMaxTiles = 1024;
 constexpr uint32_t kSplitMaxSlots = 2048;                  // rows * (row_width + 1)
 constexpr uint32_t kSplitWarps = 8;
-constexpr uint32_t kSplitEntries = kSplitWarps * 256;      // entries per block in step A
-constexpr uint32_t kSplitSub = 256;                        // outputs per warp in step B
+constexpr uint32_t kSplitWarpEntries = 128;                // entries per warp in step A
+constexpr uint32_t kSplitEntries = kSplitWarps * kSplitWarpEntries;   // entries per block
+constexpr uint32_t kSplitSub = 512;                        // outputs per warp in step B
 constexpr uint32_t kSplitUnit = kSplitWarps * kSplitSub;   // outputs per block in step B
 constexpr uint32_t kSplitTurns = 8;                        // records per chunk ranked by turns
 constexpr uint32_t kSplitColBits = 11;
@@ -795,12 +796,13 @@ __device__ __forceinline__ SplitEntry split_load_entry(const SplitArgs &a, uint3
     return e;
 }
 
-// Records and outputs per grid row of the 256 entries starting at `first`; lane r holds row r.
+// Records and outputs per grid row of the kSplitWarpEntries entries starting at `first`; lane r
+// holds row r.
 __device__ __forceinline__ void split_rows_of_warp(const SplitArgs &a, uint32_t first, uint32_t n_entries,
                                                    uint32_t lane, uint32_t &cnt, uint32_t &out) {
     cnt = 0;
     out = 0;
-    for (uint32_t win = 0; win < 8; ++win) {
+    for (uint32_t win = 0; win < kSplitWarpEntries / 32; ++win) {
         const uint32_t base = first + win * 32;
         if (base >= n_entries) break;
         const SplitEntry e = split_load_entry(a, base + lane, n_entries);
@@ -838,7 +840,7 @@ rowsplit_count_kernel(SplitArgs a) {
     }
     __syncthreads();
     uint32_t cnt, out;
-    split_rows_of_warp(a, first + warp * 256, n_entries, lane, cnt, out);
+    split_rows_of_warp(a, first + warp * kSplitWarpEntries, n_entries, lane, cnt, out);
     if (lane < a.rows && cnt) {
         atomicAdd(&s_cnt[lane], cnt);
         atomicAdd(&s_out[lane], out);
@@ -928,7 +930,7 @@ rowsplit_scatter_kernel(SplitArgs a) {
     if (first >= n_entries) return;
     const uint32_t cap = (uint32_t)(a.capacity < 0x7fffffffll ? a.capacity : 0x7fffffffll);
     uint32_t cnt, out;
-    split_rows_of_warp(a, first + warp * 256, n_entries, lane, cnt, out);
+    split_rows_of_warp(a, first + warp * kSplitWarpEntries, n_entries, lane, cnt, out);
     w_cnt[warp][lane] = cnt;
     w_out[warp][lane] = out;
     __syncthreads();
@@ -942,8 +944,8 @@ rowsplit_scatter_kernel(SplitArgs a) {
             out_at += w_out[w2][lane];
         }
     }
-    for (uint32_t win = 0; win < 8; ++win) {
-        const uint32_t base = first + warp * 256 + win * 32;
+    for (uint32_t win = 0; win < kSplitWarpEntries / 32; ++win) {
+        const uint32_t base = first + warp * kSplitWarpEntries + win * 32;
         if (base >= n_entries) break;
         const uint32_t p = base + lane;
         const SplitEntry e = split_load_entry(a, p, n_entries);
@@ -1017,12 +1019,14 @@ __device__ __forceinline__ SplitUnit split_unit(const SplitArgs &a, uint32_t u, 
 }
 
 // Adds the outputs [q_lo, q_hi) to a difference row (one record per lane).
-__device__ __forceinline__ void split_count_cols(int32_t *d, const SplitArgs &a, uint32_t q_lo,
-                                                 uint32_t q_hi, uint32_t n_rec, uint32_t n_out,
-                                                 uint32_t lane) {
-    if (q_lo >= q_hi || n_rec == 0) return;
+// Returns the record that owns output q_lo.
+__device__ __forceinline__ uint32_t split_count_cols(int32_t *d, const SplitArgs &a, uint32_t q_lo,
+                                                     uint32_t q_hi, uint32_t n_rec, uint32_t n_out,
+                                                     uint32_t lane) {
+    if (q_lo >= q_hi || n_rec == 0) return 0u;
     const uint32_t rw = a.row_width;
-    uint32_t base = warp_find_entry(a.r_off, 0, n_rec - 1, q_lo, lane);
+    const uint32_t first = warp_find_entry(a.r_off, 0, n_rec - 1, q_lo, lane);
+    uint32_t base = first;
     while (true) {
         const uint32_t p = base + lane;
         uint32_t s1 = 0u;
@@ -1063,6 +1067,7 @@ __device__ __forceinline__ void split_count_cols(int32_t *d, const SplitArgs &a,
         if (base + 32 >= n_rec || last_s1 >= q_hi) break;
         base += 32;
     }
+    return first;
 }
 
 // In-place inclusive prefix sum of d[0 .. n) by one warp.
@@ -1161,6 +1166,15 @@ split_base_kernel(const uint32_t *__restrict__ slot_tot, uint32_t n_slots, uint3
     if (i1 < n_slots) slot_base[i1] = ex + v0;
 }
 
+// Tile offsets straight from the slot starts (drops the closing column of every row).
+__global__ void split_offsets_kernel(const uint32_t *__restrict__ slot_base, uint32_t rows, uint32_t stride,
+                                     uint32_t row_width, int32_t *__restrict__ offsets) {
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= rows * row_width) return;
+    const uint32_t r = t / row_width, c = t - r * row_width;
+    offsets[t] = (int32_t)slot_base[r * stride + c];
+}
+
 struct SplitWindow {
     uint32_t xw, s0, s1, idx, depth;
 };
@@ -1208,7 +1222,7 @@ colsplit_scatter_kernel(SplitArgs a, int64_t *__restrict__ isect_ids, int32_t *_
     // outputs per column of this warp's piece
     for (uint32_t i = lane; i < a.stride; i += 32) wd[i] = 0;
     __syncwarp();
-    split_count_cols(wd, a, q_lo, q_hi, u.n_rec, u.n_out, lane);
+    const uint32_t first_rec = split_count_cols(wd, a, q_lo, q_hi, u.n_rec, u.n_out, lane);
     __syncwarp();
     warp_prefix_inplace(wd, a.stride, lane);
     __syncthreads();
@@ -1242,7 +1256,7 @@ colsplit_scatter_kernel(SplitArgs a, int64_t *__restrict__ isect_ids, int32_t *_
     const uint32_t sensor = u.row / a.tile_rows, y = u.row - sensor * a.tile_rows;
     const uint32_t hi_row = (sensor << a.tile_n_bits) | (y * a.row_width);
     if (q_lo < q_hi && u.n_rec > 0) {
-        uint32_t base = warp_find_entry(a.r_off, 0, u.n_rec - 1, q_lo, lane);
+        uint32_t base = first_rec;
         uint32_t q = q_lo;
         SplitWindow win = split_load_window(a, base, lane, u.n_rec, u.n_out);
         while (q < q_hi && base < u.n_rec) {
@@ -1338,7 +1352,7 @@ offset_encode_kernel(const int64_t *__restrict__ isect_ids, const int64_t *n_ptr
                      int32_t *__restrict__ offsets) {
     const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= C * n_tiles) return;
-    const int64_t n = n_ptr ? *n_ptr : n_imm;
+    const int64_t n = n_ptr ? (*n_ptr < n_imm ? *n_ptr : n_imm) : n_imm;
     const int64_t cid = t / n_tiles, tile = t - (uint32_t)cid * n_tiles;
     const int64_t target = (cid << tile_n_bits) | tile;
     int64_t l = 0, h = n;   // first position with (id >> 32) >= target
@@ -1385,7 +1399,7 @@ static PlanWs carve_plan(void *ws, uint64_t total) {
     p.keyB = (uint32_t *)take(sizeof(uint32_t) * total);
     p.valB = (uint32_t *)take(sizeof(uint32_t) * total);
     p.eoff = (uint32_t *)take(sizeof(uint32_t) * total);
-    const size_t n_ha = (size_t)((total + 2047) / 2048) * 32;
+    const size_t n_ha = (size_t)((total + 1023) / 1024) * 32;   // kSplitEntries, kSplitMaxRows
     p.ha_cnt = (uint32_t *)take(sizeof(uint32_t) * n_ha);
     p.ha_out = (uint32_t *)take(sizeof(uint32_t) * n_ha);
     p.bytes = off;
@@ -1579,7 +1593,7 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
 static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int sort,
                       void *plan_workspace, void *fill_workspace, size_t fill_workspace_bytes,
                       int64_t capacity, int64_t *isect_ids, int32_t *flatten_ids,
-                      int64_t *host_counts, cudaStream_t st) {
+                      int32_t *tile_offsets, int64_t *host_counts, cudaStream_t st) {
     PlanWs p = carve_plan(plan_workspace, g.total);
     SPL_REQUIRE(plan_workspace != nullptr, SPLATAD_ERR_WORKSPACE, "isect fill: null plan workspace");
     if (capacity <= 0) return SPLATAD_OK;
@@ -1669,6 +1683,12 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
             colsplit_scatter_kernel<<<w.units_b_cap, kSplitWarps * 32, smem_scatter, st>>>(
                 a, isect_ids, flatten_ids, p.counters);
         }
+        if (tile_offsets != nullptr) {
+            SPL_PROF("split_offsets_kernel", st);
+            split_offsets_kernel<<<div_up(a.rows * a.row_width, kThreads), kThreads, 0, st>>>(
+                w.slot_base, a.rows, a.stride, a.row_width, tile_offsets);
+            tile_offsets = nullptr;   // done
+        }
     } else {
         FillWs f = carve_fill(fill_workspace, (uint64_t)capacity);
         SPL_REQUIRE(fill_workspace != nullptr && fill_workspace_bytes >= f.bytes,
@@ -1737,6 +1757,12 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
             }
         }
     }
+    if (sort && tile_offsets != nullptr) {
+        SPL_PROF("offset_encode_kernel", st);
+        const uint32_t n_ct = g.C * g.n_tiles;
+        offset_encode_kernel<<<div_up(n_ct, kThreads), kThreads, 0, st>>>(
+            isect_ids, p.counters + CNT_NISECT, capacity, g.C, g.n_tiles, g.tile_n_bits, tile_offsets);
+    }
     if (host_counts != nullptr)
         cudaMemcpyAsync(host_counts, p.counters, sizeof(int64_t) * CNT_SLOTS, cudaMemcpyDeviceToHost, st);
     return check_launch("isect fill");
@@ -1755,7 +1781,7 @@ extern "C" size_t splatad_isect_plan_workspace_bytes(uint64_t total_elems) {
 
 extern "C" size_t splatad_isect_fill_workspace_bytes(uint64_t capacity) {
     // the larger of the radix buffers and the split's records + tables; (units + rows) * stride
-    // <= (capacity / 2048 + 3) * 1025 for every geometry the split accepts
+    // <= (capacity / kSplitUnit + 3) * 1025 for every geometry the split accepts
     const size_t a = carve_fill(nullptr, capacity).bytes;
     const size_t b = carve_split(nullptr, capacity, 2, kSplitMaxTiles + 1).bytes;
     return a > b ? a : b;
@@ -1798,7 +1824,7 @@ static int make_lidar_geom(IsectGeom &g, uint32_t C, uint32_t N, uint64_t total,
     g.lid.lidar.elev_boundaries = elev_boundaries;
     g.lid.lidar.tile_azim_res = tile_azim_resolution;
     g.lid.lidar.min_azim = min_azim;
-    g.lid.lidar.n_tiles_azim = (uint32_t)ceilf(360.f / tile_azim_resolution);
+    g.lid.lidar.n_tiles_azim = splatad_lidar_azimuth_tiles(tile_azim_resolution);
     g.lid.lidar.n_tiles_elev = n_boundaries - 1;
     g.lid.radii = radii;
     g.lid.means2d = (const float2 *)means2d;
@@ -1833,15 +1859,19 @@ extern "C" int splatad_isect_tiles_fill(
     const float *depths, const int64_t *camera_ids, uint32_t tile_size, uint32_t tile_width,
     uint32_t tile_height, int32_t sort, const int32_t *tiles_per_gauss, void *plan_workspace,
     void *fill_workspace, size_t fill_workspace_bytes, int64_t capacity, int64_t *isect_ids,
-    int32_t *flatten_ids, int64_t *host_counts, void *stream) {
+    int32_t *flatten_ids, int32_t *tile_offsets, int64_t *host_counts, void *stream) {
     if (total_elems == 0 || capacity <= 0) return SPLATAD_OK;
     IsectGeom g;
     int rc = make_cam_geom(g, C, N, total_elems, means2d, radii, depths, camera_ids, tile_size,
                            tile_width, tile_height);
     if (rc != SPLATAD_OK) return rc;
     return isect_fill(g, tiles_per_gauss, sort, plan_workspace, fill_workspace,
-                      fill_workspace_bytes, capacity, isect_ids, flatten_ids, host_counts,
+                      fill_workspace_bytes, capacity, isect_ids, flatten_ids, tile_offsets, host_counts,
                       (cudaStream_t)stream);
+}
+
+extern "C" uint32_t splatad_lidar_azimuth_tiles(float tile_azim_resolution) {
+    return tile_azim_resolution > 0.f ? (uint32_t)ceilf(360.f / tile_azim_resolution) : 0u;
 }
 
 extern "C" int splatad_isect_lidar_tiles_plan(
@@ -1869,14 +1899,14 @@ extern "C" int splatad_isect_lidar_tiles_fill(
     uint32_t n_boundaries, float tile_azim_resolution, float min_azim, int32_t sort,
     const int32_t *tiles_per_gauss, void *plan_workspace, void *fill_workspace,
     size_t fill_workspace_bytes, int64_t capacity, int64_t *isect_ids, int32_t *flatten_ids,
-    int64_t *host_counts, void *stream) {
+    int32_t *tile_offsets, int64_t *host_counts, void *stream) {
     if (total_elems == 0 || capacity <= 0) return SPLATAD_OK;
     IsectGeom g;
     int rc = make_lidar_geom(g, C, N, total_elems, means2d, radii, depths, camera_ids,
                              elev_boundaries, n_boundaries, tile_azim_resolution, min_azim);
     if (rc != SPLATAD_OK) return rc;
     return isect_fill(g, tiles_per_gauss, sort, plan_workspace, fill_workspace,
-                      fill_workspace_bytes, capacity, isect_ids, flatten_ids, host_counts,
+                      fill_workspace_bytes, capacity, isect_ids, flatten_ids, tile_offsets, host_counts,
                       (cudaStream_t)stream);
 }
 

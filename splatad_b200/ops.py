@@ -477,10 +477,11 @@ class _FullyFusedProjectionPacked(torch.autograd.Function):
 # Tile intersection
 # =============================================================================================
 def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, gaussian_ids, sort,
-                  geom_args):
+                  geom_args, n_tiles):
     """Shared two-phase driver of both isect ops: plan -> read n_isects on the host -> fill.
 
-    ``kind`` ("tiles" or "lidar_tiles") is spliced into the C symbol name.
+    ``kind`` ("tiles" or "lidar_tiles") is spliced into the C symbol name; ``n_tiles`` is the number
+    of tiles per sensor.
     """
     if packed:
         nnz = means2d.size(0)
@@ -500,6 +501,7 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
         camera_ids = None
         total = C * N
     dev = means2d.device
+    n_tiles_total = C * n_tiles
     means2d = _f(means2d)
     depths = _f(depths)
     if kind == "tiles":
@@ -527,13 +529,18 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
     if n_isects > 0:
         fill_ws = None
         fill_bytes = 0
+        offsets = None
         if sort:
             fill_bytes = lib.splatad_isect_fill_workspace_bytes(n_isects)
             fill_ws = _lib.workspace("isect_fill", fill_bytes, dev)
+            # the fill knows where every tile starts; kept for isect_offset_encode on this tensor
+            offsets = torch.empty(n_tiles_total, dtype=torch.int32, device=dev)
         _call(f"splatad_isect_{kind}_fill", *head, *geom_args, int(bool(sort)),
               _lib.ptr(tiles_per_gauss), _lib.ptr(plan_ws), _lib.ptr(fill_ws),
               fill_ws.numel() if fill_ws is not None else 0, n_isects, _lib.ptr(isect_ids),
-              _lib.ptr(flatten_ids), None, stream)
+              _lib.ptr(flatten_ids), _lib.ptr(offsets), None, stream)
+        if offsets is not None:
+            isect_ids._splatad_tile_offsets = (C, offsets)
     return tiles_per_gauss, isect_ids, flatten_ids
 
 
@@ -557,7 +564,8 @@ def isect_tiles(
     flatten_ids int32 [n_isects]), sorted by isect id (ties in flatten order) when ``sort``.
     """
     return _isect_common("tiles", means2d, radii, depths, packed, n_cameras, camera_ids, gaussian_ids,
-                         sort, (int(tile_size), int(tile_width), int(tile_height)))
+                         sort, (int(tile_size), int(tile_width), int(tile_height)),
+                         int(tile_width) * int(tile_height))
 
 
 @torch.no_grad()
@@ -579,12 +587,17 @@ def isect_lidar_tiles(
     eb = _f(elev_boundaries)
     return _isect_common("lidar_tiles", means2d, radii, depths, packed, n_cameras, camera_ids,
                          gaussian_ids, sort,
-                         (_lib.ptr(eb), int(eb.numel()), float(tile_azim_resolution), float(min_azim)))
+                         (_lib.ptr(eb), int(eb.numel()), float(tile_azim_resolution), float(min_azim)),
+                         int(_lib.load().splatad_lidar_azimuth_tiles(float(tile_azim_resolution)))
+                         * (int(eb.numel()) - 1))
 
 
 @torch.no_grad()
 def isect_offset_encode(isect_ids: Tensor, n_cameras: int, tile_width: int, tile_height: int) -> Tensor:
     """Encodes sorted intersection ids to per-tile start offsets [C, tile_height, tile_width]."""
+    cached = getattr(isect_ids, "_splatad_tile_offsets", None)
+    if cached is not None and cached[0] == n_cameras and cached[1].numel() == n_cameras * tile_height * tile_width:
+        return cached[1].view(n_cameras, tile_height, tile_width)
     isect_ids = isect_ids.contiguous()
     dev = isect_ids.device
     offsets = torch.empty((n_cameras, tile_height, tile_width), dtype=torch.int32, device=dev)

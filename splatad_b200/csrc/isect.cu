@@ -166,19 +166,55 @@ __device__ __forceinline__ void stage_boundaries(GridArgs<kLidar> &a, float *sb)
     }
 }
 
-// tiles_per_gauss[idx] for every (sensor, Gaussian) / packed row.
+// tiles_per_gauss[idx] for every (sensor, Gaussian) / packed row. With rect_xw / rect_yh the
+// rectangle is also stored, packed into two words per element (x0 | width << 16, first grid row |
+// height << 16 with grid row = sensor * tile rows + y; 16-bit fields, used only when
+// sensors * tiles <= 1024) for the row / column split, and the total is added to *n_isects.
 template <bool kLidar>
 __global__ void __launch_bounds__(kThreads)
-isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ tiles_per_gauss) {
+isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ tiles_per_gauss,
+                   const int64_t *__restrict__ camera_ids, uint32_t N, uint32_t *__restrict__ rect_xw,
+                   uint32_t *__restrict__ rect_yh, int64_t *__restrict__ n_isects) {
     __shared__ float sb[kLidar ? kMaxElevSmem : 1];
+    __shared__ unsigned long long wsum[kThreads / 32];
     stage_boundaries<kLidar>(a, sb);
+    const uint32_t tile_rows = kLidar ? a.lidar.n_tiles_elev : a.cam.tile_height;
+    unsigned long long sum = 0;
     for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += gridDim.x * blockDim.x) {
         Rect r;
         int32_t cnt = 0;
-        if (elem_rect<kLidar>(a, idx, r)) cnt = rect_count(r);
+        uint32_t xw = 0, yh = 0;
+        if (elem_rect<kLidar>(a, idx, r)) {
+            cnt = rect_count(r);
+            if (rect_xw != nullptr && cnt > 0) {
+                const uint32_t sensor = camera_ids ? (uint32_t)camera_ids[idx] : idx / N;
+                xw = ((uint32_t)r.x0 & 0xffffu) | ((uint32_t)(r.x1 - r.x0) << 16);
+                yh = (sensor * tile_rows + (uint32_t)r.y0) | ((uint32_t)(r.y1 - r.y0) << 16);
+            }
+        }
         tiles_per_gauss[idx] = cnt;
+        if (rect_xw != nullptr) {
+            rect_xw[idx] = xw;
+            rect_yh[idx] = yh;
+        }
+        sum += (unsigned long long)(cnt > 0 ? cnt : 0);
     }
+    if (n_isects == nullptr) return;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long t = 0;
+        for (int w = 0; w < kThreads / 32; ++w) t += wsum[w];
+        if (t) atomicAdd((unsigned long long *)n_isects, t);
+    }
+}
+
+// Raises the status bit when the total does not fit the int32 outputs.
+__global__ void check_total_kernel(int64_t *counters) {
+    if (threadIdx.x == 0 && counters[CNT_NISECT] > 0x7fffffffll) counters[CNT_STATUS] |= ST_OVERFLOW_INT32;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -508,18 +544,11 @@ emit_scan_kernel(const unsigned long long *__restrict__ block_sums, uint32_t nbl
 }
 
 // Exclusive offset of every entry of the emission order: eoff[p] = number of intersections
-// emitted before entry p. Same block ranges as emit_blocksum_kernel. With kRec the entry's tile
-// rectangle is also stored, packed into two words (x0 | width << 16, first grid row |
-// height << 16 with grid row = sensor * tile rows + y; 16-bit fields, used only when
-// sensors * tiles <= 1024), for the row / column split below.
-template <bool kLidar, bool kRec>
+// emitted before entry p. Same block ranges as emit_blocksum_kernel.
 __global__ void __launch_bounds__(kThreads)
-emit_offsets_kernel(GridArgs<kLidar> a, EmitArgs e, const unsigned long long *__restrict__ block_offs,
-                    uint32_t *__restrict__ eoff, uint32_t *__restrict__ rec_xw,
-                    uint32_t *__restrict__ rec_ys) {
+emit_offsets_kernel(EmitArgs e, const unsigned long long *__restrict__ block_offs,
+                    uint32_t *__restrict__ eoff) {
     __shared__ uint32_t wt[33];
-    __shared__ float sb[(kLidar && kRec) ? kMaxElevSmem : 1];
-    if (kRec) stage_boundaries<kLidar>(a, sb);
     uint32_t lo, hi;
     emit_range(e, lo, hi);
     uint32_t running = (uint32_t)block_offs[blockIdx.x];
@@ -530,18 +559,6 @@ emit_offsets_kernel(GridArgs<kLidar> a, EmitArgs e, const unsigned long long *__
             const uint32_t idx = e.order ? e.order[p] : p;
             const int32_t c = e.tiles_per_gauss[idx];
             cnt = (uint32_t)(c > 0 ? c : 0);
-            if (kRec) {
-                Rect r;
-                uint32_t xw = 0, ys = 0;
-                if (elem_rect<kLidar>(a, idx, r)) {
-                    const uint32_t sensor = e.camera_ids ? (uint32_t)e.camera_ids[idx] : idx / e.N;
-                    const uint32_t tile_rows = kLidar ? a.lidar.n_tiles_elev : a.cam.tile_height;
-                    xw = ((uint32_t)r.x0 & 0xffffu) | ((uint32_t)(r.x1 - r.x0) << 16);
-                    ys = (sensor * tile_rows + (uint32_t)r.y0) | ((uint32_t)(r.y1 - r.y0) << 16);
-                }
-                rec_xw[p] = xw;
-                rec_ys[p] = ys;
-            }
         }
         uint32_t chunk_total;
         const uint32_t ex = block_excl_scan(cnt, wt, chunk_total);
@@ -744,11 +761,11 @@ constexpr uint32_t kSplitTurns = 8;                        // records per chunk 
 constexpr uint32_t kSplitColBits = 11;
 
 struct SplitArgs {
-    // depth-ordered entries
-    const uint32_t *ent_xw;      // x0 | width << 16
-    const uint32_t *ent_yh;      // first grid row | height << 16
-    const uint32_t *order;       // flatten index
-    const uint32_t *depth_key;   // depth bits
+    // entries: rectangles by flatten index, visited in depth order
+    const uint32_t *rect_xw;     // [total] x0 | width << 16
+    const uint32_t *rect_yh;     // [total] first grid row | height << 16
+    const uint32_t *order;       // [n_entries] flatten index, depth order
+    const uint32_t *depth_key;   // [n_entries] depth bits
     const int64_t *n_entries_ptr;
     const int64_t *counters;     // CNT_NISECT
     int64_t capacity;
@@ -781,15 +798,16 @@ __device__ __forceinline__ uint32_t warp_find_entry(const uint32_t *__restrict__
 
 // ---- step A: rows -----------------------------------------------------------------------
 struct SplitEntry {
-    uint32_t xw, row0, h;
+    uint32_t xw, row0, h, idx;
     bool valid;
 };
 
 __device__ __forceinline__ SplitEntry split_load_entry(const SplitArgs &a, uint32_t p, uint32_t n_entries) {
-    SplitEntry e{0u, 0u, 0u, p < n_entries};
+    SplitEntry e{0u, 0u, 0u, 0u, p < n_entries};
     if (e.valid) {
-        e.xw = __ldg(a.ent_xw + p);
-        const uint32_t yh = __ldg(a.ent_yh + p);
+        e.idx = __ldg(a.order + p);
+        e.xw = __ldg(a.rect_xw + e.idx);
+        const uint32_t yh = __ldg(a.rect_yh + e.idx);
         e.row0 = yh & 0xffffu;
         e.h = yh >> 16;
     }
@@ -958,7 +976,7 @@ rowsplit_scatter_kernel(SplitArgs a) {
                 if (x0 < 0) x0 += (int32_t)a.row_width;
             }
             xs = (uint32_t)x0;
-            idx = __ldg(a.order + p);
+            idx = e.idx;
             depth = __ldg(a.depth_key + p);
         }
         for (uint32_t r = 0; r < a.rows; ++r) {
@@ -1343,6 +1361,182 @@ colsplit_scatter_kernel(SplitArgs a, int64_t *__restrict__ isect_ids, int32_t *_
     }
 }
 
+// Step B for rows of at most kLaneMaxCols tiles (the lidar grid: 57): instead of ranking 32
+// outputs against each other, every THREAD walks 16 consecutive outputs of the unit one after the
+// other with private per-column counters, so no two updates ever compete. One pass counts, an
+// exclusive scan over the 256 threads of each column turns the counts into local positions, and a
+// second pass places the outputs in shared memory in tile order; they leave as contiguous runs.
+constexpr uint32_t kLaneOutputs = kSplitUnit / (kSplitWarps * 32);   // 16
+constexpr uint32_t kLaneMaxCols = 64;
+
+struct LaneCursor {
+    uint32_t rec, j, w, col;
+};
+
+// Advances the cursor by one output; loads the next record's run when the current one ends.
+__device__ __forceinline__ bool lane_advance(LaneCursor &c, const SplitArgs &a, uint32_t rw,
+                                             uint32_t n_rec, bool more) {
+    ++c.j;
+    ++c.col;
+    if (c.col >= rw) c.col = 0;
+    if (c.j == c.w && more && c.rec + 1 < n_rec) {
+        ++c.rec;
+        const uint32_t xw = __ldg(a.r_xw + c.rec);
+        const uint32_t xs = xw & 0xffffu;
+        c.j = 0;
+        c.w = xw >> 16;
+        c.col = xs < rw ? xs : 0u;   // run starts are stored wrapped
+        return true;
+    }
+    return false;
+}
+
+__global__ void __launch_bounds__(kSplitWarps * 32)
+colsplit_scatter_lanes_kernel(SplitArgs a, int64_t *__restrict__ isect_ids,
+                              int32_t *__restrict__ flatten_ids, int64_t *__restrict__ counters) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    constexpr uint32_t T = kSplitWarps * 32;
+    const uint32_t rw = a.row_width;
+    uint16_t *cnt = reinterpret_cast<uint16_t *>(s_raw);                  // [rw][T]
+    uint32_t *st_depth = reinterpret_cast<uint32_t *>(cnt + rw * T);      // [kSplitUnit]
+    uint32_t *st_idx = st_depth + kSplitUnit;                             // [kSplitUnit]
+    uint16_t *st_col = reinterpret_cast<uint16_t *>(st_idx + kSplitUnit); // [kSplitUnit]
+    __shared__ uint32_t col_tot[kLaneMaxCols], col_start[kLaneMaxCols];
+    __shared__ int32_t shift[kLaneMaxCols];
+    __shared__ uint32_t s_rec[2];
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (split_overflow(a)) {
+        if (blockIdx.x == 0 && tid == 0)
+            atomicOr((unsigned long long *)&counters[CNT_STATUS], (unsigned long long)ST_OVERFLOW_CAPACITY);
+        return;
+    }
+    const SplitUnit u = split_unit(a, blockIdx.x, lane);
+    if (!u.live || u.q_lo >= u.q_hi || u.n_rec == 0) return;
+    const uint32_t cap = (uint32_t)(a.capacity < 0x7fffffffll ? a.capacity : 0x7fffffffll);
+
+    // records of the unit; zero the counters
+    if (warp == 0) {
+        const uint32_t lo = warp_find_entry(a.r_off, 0, u.n_rec - 1, u.q_lo, lane);
+        const uint32_t hi = warp_find_entry(a.r_off, lo, u.n_rec - 1, u.q_hi - 1, lane);
+        if (lane == 0) {
+            s_rec[0] = lo;
+            s_rec[1] = hi;
+        }
+    }
+    for (uint32_t i = tid; i < rw * T / 2; i += T) reinterpret_cast<uint32_t *>(cnt)[i] = 0u;
+    __syncthreads();
+
+    // this thread's outputs [q_t, q_t + n_t) and the record owning the first of them
+    const uint32_t q_t = u.q_lo + tid * kLaneOutputs;
+    const uint32_t n_t = q_t < u.q_hi ? min(kLaneOutputs, u.q_hi - q_t) : 0u;
+    LaneCursor c0{0u, 0u, 1u, 0u};
+    if (n_t) {
+        uint32_t lo = s_rec[0], hi = s_rec[1];
+        while (lo < hi) {   // last record with r_off <= q_t
+            const uint32_t m = (lo + hi + 1) >> 1;
+            if (__ldg(a.r_off + m) <= q_t) lo = m; else hi = m - 1;
+        }
+        const uint32_t xw = __ldg(a.r_xw + lo);
+        c0.rec = lo;
+        c0.j = q_t - __ldg(a.r_off + lo);
+        c0.w = xw >> 16;
+        c0.col = ((xw & 0xffffu) + c0.j) % rw;
+        if (c0.j >= c0.w) c0.j = c0.w - 1;   // cannot happen with consistent offsets
+    }
+
+    // pass 1: outputs per column of this thread
+    {
+        LaneCursor c = c0;
+        for (uint32_t k = 0; k < n_t; ++k) {
+            cnt[c.col * T + tid] += 1;
+            lane_advance(c, a, rw, u.n_rec, k + 1 < n_t);
+        }
+    }
+    __syncthreads();
+    // exclusive scan over the threads of every column (thread order is output order)
+    for (uint32_t col = warp; col < rw; col += kSplitWarps) {
+        uint4 *p4 = reinterpret_cast<uint4 *>(cnt + col * T + 8 * lane);
+        const uint4 v = *p4;
+        uint32_t e[8] = {v.x & 0xffffu, v.x >> 16, v.y & 0xffffu, v.y >> 16,
+                         v.z & 0xffffu, v.z >> 16, v.w & 0xffffu, v.w >> 16};
+        uint32_t sum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t t = e[i];
+            e[i] = sum;
+            sum += t;
+        }
+        uint32_t inc = sum;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t o = __shfl_up_sync(0xffffffffu, inc, off);
+            if (lane >= (uint32_t)off) inc += o;
+        }
+        const uint32_t ex = inc - sum;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) e[i] += ex;
+        *p4 = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+        if (lane == 31) col_tot[col] = inc;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // where every column starts inside the unit, and the shift to its global position
+        const uint32_t c_a = 2 * lane, c_b = c_a + 1;
+        const uint32_t t_a = c_a < rw ? col_tot[c_a] : 0u, t_b = c_b < rw ? col_tot[c_b] : 0u;
+        uint32_t inc = t_a + t_b;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t o = __shfl_up_sync(0xffffffffu, inc, off);
+            if (lane >= (uint32_t)off) inc += o;
+        }
+        const uint32_t ex = inc - t_a - t_b;
+        const uint32_t *hrow = a.hb + (size_t)blockIdx.x * a.stride;
+        const uint32_t *sbase = a.slot_base + u.row * a.stride;
+        if (c_a < rw) {
+            col_start[c_a] = ex;
+            shift[c_a] = (int32_t)(hrow[c_a] + sbase[c_a] - ex);
+        }
+        if (c_b < rw) {
+            col_start[c_b] = ex + t_a;
+            shift[c_b] = (int32_t)(hrow[c_b] + sbase[c_b] - (ex + t_a));
+        }
+    }
+    __syncthreads();
+    // pass 2: place the outputs in tile order
+    if (n_t) {
+        LaneCursor c = c0;
+        uint32_t idx = __ldg(a.r_idx + c.rec), depth = __ldg(a.r_depth + c.rec);
+        for (uint32_t k = 0; k < n_t; ++k) {
+            const uint32_t at = c.col * T + tid;
+            const uint32_t r = cnt[at];
+            cnt[at] = (uint16_t)(r + 1);
+            const uint32_t lpos = col_start[c.col] + r;
+            if (lpos < kSplitUnit) {
+                st_col[lpos] = (uint16_t)c.col;
+                st_depth[lpos] = depth;
+                st_idx[lpos] = idx;
+            }
+            if (lane_advance(c, a, rw, u.n_rec, k + 1 < n_t)) {
+                idx = __ldg(a.r_idx + c.rec);
+                depth = __ldg(a.r_depth + c.rec);
+            }
+        }
+    }
+    __syncthreads();
+    // consecutive threads write consecutive entries of a tile's run
+    const uint32_t sensor = u.row / a.tile_rows, y = u.row - sensor * a.tile_rows;
+    const uint32_t hi_row = (sensor << a.tile_n_bits) | (y * rw);
+    const uint32_t n_unit = u.q_hi - u.q_lo;
+    for (uint32_t i = tid; i < n_unit; i += T) {
+        const uint32_t col = st_col[i];
+        const uint32_t pos = i + (uint32_t)shift[col < rw ? col : 0];
+        if (pos < cap) {
+            isect_ids[pos] = ((int64_t)(hi_row + col) << 32) | (int64_t)st_depth[i];
+            flatten_ids[pos] = (int32_t)st_idx[i];
+        }
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // Offsets: offsets[c, tile] = first position whose (sensor, tile) >= (c, tile).
 // ---------------------------------------------------------------------------------------
@@ -1381,6 +1575,7 @@ struct PlanWs {
     uint32_t *keyA, *valA, *keyB, *valB;
     uint32_t *eoff;
     uint32_t *ha_cnt, *ha_out;   // row split: per (block of entries, grid row)
+    uint32_t *rect_xw, *rect_yh; // row split: packed rectangles by flatten index
     size_t bytes;
 };
 
@@ -1402,6 +1597,8 @@ static PlanWs carve_plan(void *ws, uint64_t total) {
     const size_t n_ha = (size_t)((total + 1023) / 1024) * 32;   // kSplitEntries, kSplitMaxRows
     p.ha_cnt = (uint32_t *)take(sizeof(uint32_t) * n_ha);
     p.ha_out = (uint32_t *)take(sizeof(uint32_t) * n_ha);
+    p.rect_xw = (uint32_t *)take(sizeof(uint32_t) * total);
+    p.rect_yh = (uint32_t *)take(sizeof(uint32_t) * total);
     p.bytes = off;
     return p;
 }
@@ -1492,17 +1689,20 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
         SPL_PROF("init_counters_kernel", st);
         init_counters_kernel<<<1, 32, 0, st>>>(p.counters);
     }
+    // with few enough sensor-tiles the fill uses the row / column split: it wants the packed
+    // rectangles and needs neither the emission offsets nor their block sums
+    const bool split = use_split(g, sort);
     const uint32_t cgrid = min(div_up(g.total, kThreads), (uint32_t)(8 * kNumSMs));
-    if (g.lidar) {
-        {
-            SPL_PROF("isect_count_kernel", st);
-            isect_count_kernel<true><<<cgrid, kThreads, 0, st>>>(g.lid, g.total, tiles_per_gauss);
-        }
-    } else {
-        {
-            SPL_PROF("isect_count_kernel", st);
-            isect_count_kernel<false><<<cgrid, kThreads, 0, st>>>(g.cam, g.total, tiles_per_gauss);
-        }
+    {
+        SPL_PROF("isect_count_kernel", st);
+        uint32_t *rx = split ? p.rect_xw : nullptr, *ry = split ? p.rect_yh : nullptr;
+        int64_t *tot = split ? p.counters + CNT_NISECT : nullptr;
+        if (g.lidar)
+            isect_count_kernel<true><<<cgrid, kThreads, 0, st>>>(g.lid, g.total, tiles_per_gauss,
+                                                                 g.camera_ids, g.N, rx, ry, tot);
+        else
+            isect_count_kernel<false><<<cgrid, kThreads, 0, st>>>(g.cam, g.total, tiles_per_gauss,
+                                                                  g.camera_ids, g.N, rx, ry, tot);
     }
 
     EmitArgs e{};
@@ -1560,29 +1760,21 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
         e.order = va;
         e.n_order_ptr = p.counters + CNT_NVIS;
     }
-    {
-        SPL_PROF("emit_blocksum_kernel", st);
-        emit_blocksum_kernel<<<kSortGrid, kThreads, 0, st>>>(e, p.block_sums);
-    }
-    {
-        SPL_PROF("emit_scan_kernel", st);
-        emit_scan_kernel<<<1, 1024, 0, st>>>(p.block_sums, kSortGrid, p.block_offs, p.counters);
-    }
-    // with few enough sensor-tiles the fill uses the row / column split and wants the rectangles
-    // of the sorted entries; keyA / valA are free once the depth order sits in keyB / valB
-    const bool rec = use_split(g, sort);
-    {
-        SPL_PROF("emit_offsets_kernel", st);
-        if (g.lidar) {
-            if (rec) emit_offsets_kernel<true, true><<<kSortGrid, kThreads, 0, st>>>(
-                g.lid, e, p.block_offs, p.eoff, p.keyA, p.valA);
-            else emit_offsets_kernel<true, false><<<kSortGrid, kThreads, 0, st>>>(
-                g.lid, e, p.block_offs, p.eoff, nullptr, nullptr);
-        } else {
-            if (rec) emit_offsets_kernel<false, true><<<kSortGrid, kThreads, 0, st>>>(
-                g.cam, e, p.block_offs, p.eoff, p.keyA, p.valA);
-            else emit_offsets_kernel<false, false><<<kSortGrid, kThreads, 0, st>>>(
-                g.cam, e, p.block_offs, p.eoff, nullptr, nullptr);
+    if (split) {
+        SPL_PROF("check_total_kernel", st);
+        check_total_kernel<<<1, 32, 0, st>>>(p.counters);
+    } else {
+        {
+            SPL_PROF("emit_blocksum_kernel", st);
+            emit_blocksum_kernel<<<kSortGrid, kThreads, 0, st>>>(e, p.block_sums);
+        }
+        {
+            SPL_PROF("emit_scan_kernel", st);
+            emit_scan_kernel<<<1, 1024, 0, st>>>(p.block_sums, kSortGrid, p.block_offs, p.counters);
+        }
+        {
+            SPL_PROF("emit_offsets_kernel", st);
+            emit_offsets_kernel<<<kSortGrid, kThreads, 0, st>>>(e, p.block_offs, p.eoff);
         }
     }
     if (host_counts != nullptr)
@@ -1625,8 +1817,8 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
         }
     } else if (use_split(g, sort)) {
         SplitArgs a{};
-        a.ent_xw = p.keyA;
-        a.ent_yh = p.valA;
+        a.rect_xw = p.rect_xw;
+        a.rect_yh = p.rect_yh;
         a.order = p.valB;
         a.depth_key = p.keyB;
         a.n_entries_ptr = p.counters + CNT_NVIS;
@@ -1678,7 +1870,15 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
             SPL_PROF("split_base_kernel", st);
             split_base_kernel<<<1, 1024, 0, st>>>(w.slot_tot, a.rows * a.stride, w.slot_base);
         }
-        {
+        if (a.row_width <= kLaneMaxCols - 1) {
+            const size_t smem_lanes = (size_t)a.row_width * kSplitWarps * 32 * sizeof(uint16_t) +
+                                      kSplitUnit * (2 * sizeof(uint32_t) + sizeof(uint16_t));
+            cudaFuncSetAttribute(colsplit_scatter_lanes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem_lanes);
+            SPL_PROF("colsplit_scatter_lanes_kernel", st);
+            colsplit_scatter_lanes_kernel<<<w.units_b_cap, kSplitWarps * 32, smem_lanes, st>>>(
+                a, isect_ids, flatten_ids, p.counters);
+        } else {
             SPL_PROF("colsplit_scatter_kernel", st);
             colsplit_scatter_kernel<<<w.units_b_cap, kSplitWarps * 32, smem_scatter, st>>>(
                 a, isect_ids, flatten_ids, p.counters);

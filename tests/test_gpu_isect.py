@@ -27,6 +27,8 @@ def _run_cam(means2d, radii, depths, ts, tw, th, **kw):
     C = kw.get("n_cameras") or means2d.shape[0]
     tpg, ids, flat = ops.isect_tiles(t(means2d), t(radii, torch.int32), t(depths), ts, tw, th, **kw)
     offs = ops.isect_offset_encode(ids, C, tw, th)
+    # the offsets handed over by the fill equal the ones recomputed from the ids alone
+    assert torch.equal(offs, ops.isect_offset_encode(ids.clone(), C, tw, th))
     return tpg, ids, flat, offs
 
 
@@ -36,6 +38,7 @@ def _run_lidar(means2d, radii, depths, eb, res, min_az, **kw):
     tpg, ids, flat = ops.isect_lidar_tiles(t(means2d), t(radii), t(depths), t(eb), res, min_az, **kw)
     n_az = math.ceil(360 / res)
     offs = ops.isect_offset_encode(ids, C, n_az, len(eb) - 1)
+    assert torch.equal(offs, ops.isect_offset_encode(ids.clone(), C, n_az, len(eb) - 1))
     return tpg, ids, flat, offs
 
 
@@ -54,7 +57,7 @@ def test_isect_lidar_tiles_golden(golden, name):
 
 
 @pytest.mark.parametrize("C,N,W,H,ts", [(1, 1, 64, 64, 16), (2, 5000, 640, 480, 16), (3, 70000, 1920, 1080, 16),
-                                         (1, 3000, 100, 60, 7)])
+                                         (1, 3000, 100, 60, 7), (1, 6000, 1100, 200, 16), (2, 9000, 300, 250, 16)])
 def test_isect_tiles_vs_oracle(C, N, W, H, ts):
     from oracle import isect
     g = torch.Generator().manual_seed(C * 1000 + N)

@@ -776,19 +776,24 @@ struct SplitArgs {
     // workspace
     uint32_t *ha_cnt, *ha_out;   // [units_a][rows]: records / outputs per (entry block, row)
     uint32_t *row_rec, *row_out, *row_unit;   // [rows + 1] exclusive starts
-    uint32_t *r_xw, *r_off, *r_idx, *r_depth; // records, row bucket after row bucket
+    uint4 *rec;                  // records {run start | width << 16, output offset, flatten index,
+                                 // depth bits}, row bucket after row bucket
     uint32_t *hb;                // [units_b][stride] outputs per (unit, column)
     uint32_t *slot_tot, *slot_base;           // [rows * stride]
 };
 
-// Warp-cooperative search: last p in [lo, hi] with off[p] <= q (off non-decreasing,
-// off[lo] <= q). 32 probes per round.
-__device__ __forceinline__ uint32_t warp_find_entry(const uint32_t *__restrict__ off, uint32_t lo,
-                                                    uint32_t hi, uint32_t q, uint32_t lane) {
+// Warp-cooperative search: last record p in [lo, hi] whose output offset is <= q (offsets are
+// non-decreasing, that of lo is <= q). 32 probes per round.
+__device__ __forceinline__ uint32_t rec_off(const SplitArgs &a, uint32_t p) {
+    return __ldg(reinterpret_cast<const uint32_t *>(a.rec + p) + 1);
+}
+
+__device__ __forceinline__ uint32_t warp_find_entry(const SplitArgs &a, uint32_t lo, uint32_t hi,
+                                                    uint32_t q, uint32_t lane) {
     while (lo < hi) {
         const uint32_t step = (hi - lo + 31) / 32;
         const uint64_t pp = (uint64_t)lo + (uint64_t)(lane + 1) * step;
-        const bool le = (pp <= hi) && (__ldg(off + pp) <= q);
+        const bool le = (pp <= hi) && (rec_off(a, (uint32_t)pp) <= q);
         const uint32_t c = __popc(__ballot_sync(0xffffffffu, le));
         lo += c * step;
         hi = min(hi, lo + step - 1);
@@ -996,12 +1001,7 @@ rowsplit_scatter_kernel(SplitArgs a) {
             const uint32_t obase = __shfl_sync(0xffffffffu, out_at, r);
             if (hit) {
                 const uint32_t pos = rbase + __popc(bal & lt);
-                if (pos < cap) {
-                    a.r_xw[pos] = xs | (w << 16);
-                    a.r_off[pos] = obase + inc - v;
-                    a.r_idx[pos] = idx;
-                    a.r_depth[pos] = depth;
-                }
+                if (pos < cap) a.rec[pos] = make_uint4(xs | (w << 16), obase + inc - v, idx, depth);
             }
             if (lane == r) {
                 rec_at += __popc(bal);
@@ -1043,16 +1043,17 @@ __device__ __forceinline__ uint32_t split_count_cols(int32_t *d, const SplitArgs
                                                      uint32_t lane) {
     if (q_lo >= q_hi || n_rec == 0) return 0u;
     const uint32_t rw = a.row_width;
-    const uint32_t first = warp_find_entry(a.r_off, 0, n_rec - 1, q_lo, lane);
+    const uint32_t first = warp_find_entry(a, 0, n_rec - 1, q_lo, lane);
     uint32_t base = first;
     while (true) {
         const uint32_t p = base + lane;
         uint32_t s1 = 0u;
         if (p < n_rec) {
-            const uint32_t s0 = __ldg(a.r_off + p);
-            s1 = (p + 1 < n_rec) ? __ldg(a.r_off + p + 1) : n_out;
+            const uint2 xo = __ldg(reinterpret_cast<const uint2 *>(a.rec + p));
+            const uint32_t s0 = xo.y;
+            s1 = (p + 1 < n_rec) ? rec_off(a, p + 1) : n_out;
             if (s0 < q_hi && s1 > q_lo) {
-                const uint32_t xw = __ldg(a.r_xw + p);
+                const uint32_t xw = xo.x;
                 const uint32_t k_lo = max(s0, q_lo) - s0, k_hi = min(s1, q_hi) - s0;
                 uint32_t start = (xw & 0xffffu) + k_lo;
                 uint32_t len = k_hi - k_lo;
@@ -1202,11 +1203,12 @@ __device__ __forceinline__ SplitWindow split_load_window(const SplitArgs &a, uin
     SplitWindow win{0u, 0u, 0u, 0u, 0u};
     const uint32_t p = base + lane;
     if (p < n_rec) {
-        win.xw = __ldg(a.r_xw + p);
-        win.s0 = __ldg(a.r_off + p);
-        win.s1 = (p + 1 < n_rec) ? __ldg(a.r_off + p + 1) : n_out;
-        win.idx = __ldg(a.r_idx + p);
-        win.depth = __ldg(a.r_depth + p);
+        const uint4 r = __ldg(a.rec + p);
+        win.xw = r.x;
+        win.s0 = r.y;
+        win.s1 = (p + 1 < n_rec) ? rec_off(a, p + 1) : n_out;
+        win.idx = r.z;
+        win.depth = r.w;
     }
     return win;
 }
@@ -1218,9 +1220,9 @@ colsplit_scatter_kernel(SplitArgs a, int64_t *__restrict__ isect_ids, int32_t *_
     // [kSplitWarps][stride] column tables, [stride] global - local start, staged outputs
     int32_t *s_tab = s_dyn;
     int32_t *s_shift = s_tab + kSplitWarps * a.stride;
-    uint32_t *st_hi = reinterpret_cast<uint32_t *>(s_shift + a.stride);
-    uint32_t *st_depth = st_hi + kSplitUnit;
+    uint32_t *st_depth = reinterpret_cast<uint32_t *>(s_shift + a.stride);
     uint32_t *st_idx = st_depth + kSplitUnit;
+    uint16_t *st_col = reinterpret_cast<uint16_t *>(st_idx + kSplitUnit);
     __shared__ uint32_t wt[33];
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t lt = (1u << lane) - 1u, le = 0xffffffffu >> (31 - lane);
@@ -1335,7 +1337,7 @@ colsplit_scatter_kernel(SplitArgs a, int64_t *__restrict__ isect_ids, int32_t *_
                     lpos = v + rank;
                 }
                 if (active && lpos < kSplitUnit) {
-                    st_hi[lpos] = hi_row + col;
+                    st_col[lpos] = (uint16_t)col;
                     st_depth[lpos] = depth;
                     st_idx[lpos] = idx;
                 }
@@ -1349,187 +1351,9 @@ colsplit_scatter_kernel(SplitArgs a, int64_t *__restrict__ isect_ids, int32_t *_
     __syncthreads();
     // the unit's outputs now sit in tile order: consecutive threads write consecutive entries
     const uint32_t n_unit = u.q_hi - u.q_lo;
-    const uint32_t tile_mask = (1u << a.tile_n_bits) - 1u;
     for (uint32_t i = tid; i < n_unit; i += blockDim.x) {
-        const uint32_t hi = st_hi[i];
-        const uint32_t col = (hi & tile_mask) - y * a.row_width;
-        const uint32_t pos = i + (uint32_t)s_shift[col < a.stride ? col : 0];
-        if (pos < cap) {
-            isect_ids[pos] = ((int64_t)hi << 32) | (int64_t)st_depth[i];
-            flatten_ids[pos] = (int32_t)st_idx[i];
-        }
-    }
-}
-
-// Step B for rows of at most kLaneMaxCols tiles (the lidar grid: 57): instead of ranking 32
-// outputs against each other, every THREAD walks 16 consecutive outputs of the unit one after the
-// other with private per-column counters, so no two updates ever compete. One pass counts, an
-// exclusive scan over the 256 threads of each column turns the counts into local positions, and a
-// second pass places the outputs in shared memory in tile order; they leave as contiguous runs.
-constexpr uint32_t kLaneOutputs = kSplitUnit / (kSplitWarps * 32);   // 16
-constexpr uint32_t kLaneMaxCols = 64;
-
-struct LaneCursor {
-    uint32_t rec, j, w, col;
-};
-
-// Advances the cursor by one output; loads the next record's run when the current one ends.
-__device__ __forceinline__ bool lane_advance(LaneCursor &c, const SplitArgs &a, uint32_t rw,
-                                             uint32_t n_rec, bool more) {
-    ++c.j;
-    ++c.col;
-    if (c.col >= rw) c.col = 0;
-    if (c.j == c.w && more && c.rec + 1 < n_rec) {
-        ++c.rec;
-        const uint32_t xw = __ldg(a.r_xw + c.rec);
-        const uint32_t xs = xw & 0xffffu;
-        c.j = 0;
-        c.w = xw >> 16;
-        c.col = xs < rw ? xs : 0u;   // run starts are stored wrapped
-        return true;
-    }
-    return false;
-}
-
-__global__ void __launch_bounds__(kSplitWarps * 32)
-colsplit_scatter_lanes_kernel(SplitArgs a, int64_t *__restrict__ isect_ids,
-                              int32_t *__restrict__ flatten_ids, int64_t *__restrict__ counters) {
-    extern __shared__ __align__(16) unsigned char s_raw[];
-    constexpr uint32_t T = kSplitWarps * 32;
-    const uint32_t rw = a.row_width;
-    uint16_t *cnt = reinterpret_cast<uint16_t *>(s_raw);                  // [rw][T]
-    uint32_t *st_depth = reinterpret_cast<uint32_t *>(cnt + rw * T);      // [kSplitUnit]
-    uint32_t *st_idx = st_depth + kSplitUnit;                             // [kSplitUnit]
-    uint16_t *st_col = reinterpret_cast<uint16_t *>(st_idx + kSplitUnit); // [kSplitUnit]
-    __shared__ uint32_t col_tot[kLaneMaxCols], col_start[kLaneMaxCols];
-    __shared__ int32_t shift[kLaneMaxCols];
-    __shared__ uint32_t s_rec[2];
-    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (split_overflow(a)) {
-        if (blockIdx.x == 0 && tid == 0)
-            atomicOr((unsigned long long *)&counters[CNT_STATUS], (unsigned long long)ST_OVERFLOW_CAPACITY);
-        return;
-    }
-    const SplitUnit u = split_unit(a, blockIdx.x, lane);
-    if (!u.live || u.q_lo >= u.q_hi || u.n_rec == 0) return;
-    const uint32_t cap = (uint32_t)(a.capacity < 0x7fffffffll ? a.capacity : 0x7fffffffll);
-
-    // records of the unit; zero the counters
-    if (warp == 0) {
-        const uint32_t lo = warp_find_entry(a.r_off, 0, u.n_rec - 1, u.q_lo, lane);
-        const uint32_t hi = warp_find_entry(a.r_off, lo, u.n_rec - 1, u.q_hi - 1, lane);
-        if (lane == 0) {
-            s_rec[0] = lo;
-            s_rec[1] = hi;
-        }
-    }
-    for (uint32_t i = tid; i < rw * T / 2; i += T) reinterpret_cast<uint32_t *>(cnt)[i] = 0u;
-    __syncthreads();
-
-    // this thread's outputs [q_t, q_t + n_t) and the record owning the first of them
-    const uint32_t q_t = u.q_lo + tid * kLaneOutputs;
-    const uint32_t n_t = q_t < u.q_hi ? min(kLaneOutputs, u.q_hi - q_t) : 0u;
-    LaneCursor c0{0u, 0u, 1u, 0u};
-    if (n_t) {
-        uint32_t lo = s_rec[0], hi = s_rec[1];
-        while (lo < hi) {   // last record with r_off <= q_t
-            const uint32_t m = (lo + hi + 1) >> 1;
-            if (__ldg(a.r_off + m) <= q_t) lo = m; else hi = m - 1;
-        }
-        const uint32_t xw = __ldg(a.r_xw + lo);
-        c0.rec = lo;
-        c0.j = q_t - __ldg(a.r_off + lo);
-        c0.w = xw >> 16;
-        c0.col = ((xw & 0xffffu) + c0.j) % rw;
-        if (c0.j >= c0.w) c0.j = c0.w - 1;   // cannot happen with consistent offsets
-    }
-
-    // pass 1: outputs per column of this thread
-    {
-        LaneCursor c = c0;
-        for (uint32_t k = 0; k < n_t; ++k) {
-            cnt[c.col * T + tid] += 1;
-            lane_advance(c, a, rw, u.n_rec, k + 1 < n_t);
-        }
-    }
-    __syncthreads();
-    // exclusive scan over the threads of every column (thread order is output order)
-    for (uint32_t col = warp; col < rw; col += kSplitWarps) {
-        uint4 *p4 = reinterpret_cast<uint4 *>(cnt + col * T + 8 * lane);
-        const uint4 v = *p4;
-        uint32_t e[8] = {v.x & 0xffffu, v.x >> 16, v.y & 0xffffu, v.y >> 16,
-                         v.z & 0xffffu, v.z >> 16, v.w & 0xffffu, v.w >> 16};
-        uint32_t sum = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t t = e[i];
-            e[i] = sum;
-            sum += t;
-        }
-        uint32_t inc = sum;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            const uint32_t o = __shfl_up_sync(0xffffffffu, inc, off);
-            if (lane >= (uint32_t)off) inc += o;
-        }
-        const uint32_t ex = inc - sum;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) e[i] += ex;
-        *p4 = make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
-        if (lane == 31) col_tot[col] = inc;
-    }
-    __syncthreads();
-    if (warp == 0) {
-        // where every column starts inside the unit, and the shift to its global position
-        const uint32_t c_a = 2 * lane, c_b = c_a + 1;
-        const uint32_t t_a = c_a < rw ? col_tot[c_a] : 0u, t_b = c_b < rw ? col_tot[c_b] : 0u;
-        uint32_t inc = t_a + t_b;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            const uint32_t o = __shfl_up_sync(0xffffffffu, inc, off);
-            if (lane >= (uint32_t)off) inc += o;
-        }
-        const uint32_t ex = inc - t_a - t_b;
-        const uint32_t *hrow = a.hb + (size_t)blockIdx.x * a.stride;
-        const uint32_t *sbase = a.slot_base + u.row * a.stride;
-        if (c_a < rw) {
-            col_start[c_a] = ex;
-            shift[c_a] = (int32_t)(hrow[c_a] + sbase[c_a] - ex);
-        }
-        if (c_b < rw) {
-            col_start[c_b] = ex + t_a;
-            shift[c_b] = (int32_t)(hrow[c_b] + sbase[c_b] - (ex + t_a));
-        }
-    }
-    __syncthreads();
-    // pass 2: place the outputs in tile order
-    if (n_t) {
-        LaneCursor c = c0;
-        uint32_t idx = __ldg(a.r_idx + c.rec), depth = __ldg(a.r_depth + c.rec);
-        for (uint32_t k = 0; k < n_t; ++k) {
-            const uint32_t at = c.col * T + tid;
-            const uint32_t r = cnt[at];
-            cnt[at] = (uint16_t)(r + 1);
-            const uint32_t lpos = col_start[c.col] + r;
-            if (lpos < kSplitUnit) {
-                st_col[lpos] = (uint16_t)c.col;
-                st_depth[lpos] = depth;
-                st_idx[lpos] = idx;
-            }
-            if (lane_advance(c, a, rw, u.n_rec, k + 1 < n_t)) {
-                idx = __ldg(a.r_idx + c.rec);
-                depth = __ldg(a.r_depth + c.rec);
-            }
-        }
-    }
-    __syncthreads();
-    // consecutive threads write consecutive entries of a tile's run
-    const uint32_t sensor = u.row / a.tile_rows, y = u.row - sensor * a.tile_rows;
-    const uint32_t hi_row = (sensor << a.tile_n_bits) | (y * rw);
-    const uint32_t n_unit = u.q_hi - u.q_lo;
-    for (uint32_t i = tid; i < n_unit; i += T) {
         const uint32_t col = st_col[i];
-        const uint32_t pos = i + (uint32_t)shift[col < rw ? col : 0];
+        const uint32_t pos = i + (uint32_t)s_shift[col < a.stride ? col : 0];
         if (pos < cap) {
             isect_ids[pos] = ((int64_t)(hi_row + col) << 32) | (int64_t)st_depth[i];
             flatten_ids[pos] = (int32_t)st_idx[i];
@@ -1623,7 +1447,7 @@ static FillWs carve_fill(void *ws, uint64_t cap) {
 
 struct SplitWs {
     uint32_t *row_rec, *row_out, *row_unit;
-    uint32_t *r_xw, *r_off, *r_idx, *r_depth;
+    uint4 *rec;
     uint32_t *hb, *slot_tot, *slot_base;
     uint32_t units_b_cap;
     size_t bytes;
@@ -1637,10 +1461,7 @@ static SplitWs carve_split(void *ws, uint64_t cap, uint32_t rows, uint32_t strid
     w.row_rec = (uint32_t *)take(sizeof(uint32_t) * (kSplitMaxRows + 1));
     w.row_out = (uint32_t *)take(sizeof(uint32_t) * (kSplitMaxRows + 1));
     w.row_unit = (uint32_t *)take(sizeof(uint32_t) * (kSplitMaxRows + 1));
-    w.r_xw = (uint32_t *)take(sizeof(uint32_t) * cap);
-    w.r_off = (uint32_t *)take(sizeof(uint32_t) * cap);
-    w.r_idx = (uint32_t *)take(sizeof(uint32_t) * cap);
-    w.r_depth = (uint32_t *)take(sizeof(uint32_t) * cap);
+    w.rec = (uint4 *)take(sizeof(uint4) * cap);
     // every grid row rounds its outputs up to whole units
     w.units_b_cap = (uint32_t)((cap + kSplitUnit - 1) / kSplitUnit) + rows;
     w.hb = (uint32_t *)take(sizeof(uint32_t) * (size_t)w.units_b_cap * stride);
@@ -1838,11 +1659,12 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
         a.ha_cnt = p.ha_cnt;
         a.ha_out = p.ha_out;
         a.row_rec = w.row_rec; a.row_out = w.row_out; a.row_unit = w.row_unit;
-        a.r_xw = w.r_xw; a.r_off = w.r_off; a.r_idx = w.r_idx; a.r_depth = w.r_depth;
+        a.rec = w.rec;
         a.hb = w.hb; a.slot_tot = w.slot_tot; a.slot_base = w.slot_base;
         const uint32_t units_a = div_up(g.total, kSplitEntries);
         const size_t smem_count = sizeof(int32_t) * a.stride;
-        const size_t smem_scatter = sizeof(int32_t) * ((kSplitWarps + 1) * a.stride + 3 * kSplitUnit);
+        const size_t smem_scatter = sizeof(int32_t) * ((kSplitWarps + 1) * a.stride + 2 * kSplitUnit) +
+                                    sizeof(uint16_t) * kSplitUnit;
         if (smem_scatter > 48 * 1024)   // above the default dynamic shared memory limit
             cudaFuncSetAttribute(colsplit_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem_scatter);
@@ -1870,15 +1692,7 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
             SPL_PROF("split_base_kernel", st);
             split_base_kernel<<<1, 1024, 0, st>>>(w.slot_tot, a.rows * a.stride, w.slot_base);
         }
-        if (a.row_width <= kLaneMaxCols - 1) {
-            const size_t smem_lanes = (size_t)a.row_width * kSplitWarps * 32 * sizeof(uint16_t) +
-                                      kSplitUnit * (2 * sizeof(uint32_t) + sizeof(uint16_t));
-            cudaFuncSetAttribute(colsplit_scatter_lanes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem_lanes);
-            SPL_PROF("colsplit_scatter_lanes_kernel", st);
-            colsplit_scatter_lanes_kernel<<<w.units_b_cap, kSplitWarps * 32, smem_lanes, st>>>(
-                a, isect_ids, flatten_ids, p.counters);
-        } else {
+        {
             SPL_PROF("colsplit_scatter_kernel", st);
             colsplit_scatter_kernel<<<w.units_b_cap, kSplitWarps * 32, smem_scatter, st>>>(
                 a, isect_ids, flatten_ids, p.counters);

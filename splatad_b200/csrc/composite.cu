@@ -35,6 +35,19 @@ __device__ __forceinline__ float angle_difference(float a, float b) {
     return d < -180.f ? d + 360.f : d;
 }
 
+// Copies row g of a [*, n] float table to dst (one thread per row): 16-byte loads when the rows
+// are 16-byte aligned.
+__device__ __forceinline__ void stage_row(float *__restrict__ dst, const float *__restrict__ table,
+                                          size_t g, uint32_t n, bool vec) {
+    const float *src = table + g * n;
+    if (vec) {
+        for (uint32_t k = 0; k < n; k += 4)
+            *reinterpret_cast<float4 *>(dst + k) = __ldg(reinterpret_cast<const float4 *>(src + k));
+    } else {
+        for (uint32_t k = 0; k < n; ++k) dst[k] = __ldg(src + k);
+    }
+}
+
 struct TileRange { int32_t start, end; };
 
 __device__ __forceinline__ TileRange tile_range(const int32_t *__restrict__ offsets, uint32_t tile,
@@ -57,12 +70,16 @@ __global__ void rasterize_to_pixels_fwd_kernel(
     uint32_t H, uint32_t tile_size, uint32_t tile_w, uint32_t tile_h,
     const int32_t *__restrict__ offsets, const int32_t *__restrict__ flatten_ids,
     float *__restrict__ render_colors, float *__restrict__ render_alphas,
-    int32_t *__restrict__ last_ids) {
+    int32_t *__restrict__ last_ids, uint32_t stage_colors) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const uint32_t bs = blockDim.x;
     float4 *sA = reinterpret_cast<float4 *>(smem_raw);   // x, y, vx, vy
     float4 *sB = sA + bs;                                // conic a, b, c, opacity
     int32_t *sId = reinterpret_cast<int32_t *>(sB + bs);
+    // colour rows of the batch (when they fit): the inner loop then never waits on global memory
+    float *sCol = reinterpret_cast<float *>(sId + bs);
+    const uint32_t cpad = (channels + 3u) & ~3u;
+    const bool vec = (channels % 4u == 0u) && ((reinterpret_cast<uintptr_t>(colors) & 15u) == 0u);
 
     const uint32_t tiles_per_cam = tile_w * tile_h;
     const uint32_t cam = blockIdx.x / tiles_per_cam;
@@ -97,6 +114,7 @@ __global__ void rasterize_to_pixels_fwd_kernel(
             sB[tr] = make_float4(conics[3 * (size_t)g], conics[3 * (size_t)g + 1],
                                  conics[3 * (size_t)g + 2], opacities[g]);
             sId[tr] = g;
+            if (stage_colors) stage_row(sCol + tr * cpad, colors, (size_t)g, channels, vec);
         }
         __syncthreads();
         if (__all_sync(0xffffffffu, done)) continue;
@@ -112,10 +130,10 @@ __global__ void rasterize_to_pixels_fwd_kernel(
             const float next_T = T * (1.f - alpha);
             if (next_T <= kTStop) { done = true; break; }
             const float vis = alpha * T;
-            const float *c_ptr = colors + (size_t)sId[t] * channels;
+            const float *c_ptr = stage_colors ? sCol + t * cpad : colors + (size_t)sId[t] * channels;
 #pragma unroll
             for (int k = 0; k < CDIM; ++k)
-                if ((uint32_t)k < channels) pix_out[k] += __ldg(c_ptr + k) * vis;
+                if ((uint32_t)k < channels) pix_out[k] += c_ptr[k] * vis;
             cur_idx = batch_start + t;
             T = next_T;
         }
@@ -148,13 +166,15 @@ __global__ void rasterize_to_points_fwd_kernel(
     const int32_t *__restrict__ flatten_ids, uint32_t depth_idx,
     float *__restrict__ render_colors, float *__restrict__ render_alphas,
     float *__restrict__ alpha_sum_out, int32_t *__restrict__ last_ids,
-    float *__restrict__ median_depths) {
+    float *__restrict__ median_depths, uint32_t stage_features) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const uint32_t bs = blockDim.x;
     float4 *sA = reinterpret_cast<float4 *>(smem_raw);   // az, el, v_az, v_el
     float4 *sB = sA + bs;                                // conic a, b, c, opacity
     float4 *sC = sB + bs;                                // v_range, dc.x, dc.y, range (depth channel)
     int32_t *sId = reinterpret_cast<int32_t *>(sC + bs);
+    // feature rows of the batch (when they fit): the inner loop then never waits on global memory
+    float *sFeat = reinterpret_cast<float *>(sId + bs);
 
     const uint32_t tiles_per_cam = grid_w * grid_h;
     const uint32_t cam = blockIdx.x / tiles_per_cam;
@@ -178,6 +198,8 @@ __global__ void rasterize_to_points_fwd_kernel(
 
     // with a separate range array the feature rows hold channels - 1 columns
     const uint32_t fstride = ranges ? channels - 1 : channels;
+    const uint32_t fpad = (fstride + 3u) & ~3u;
+    const bool vec = (fstride % 4u == 0u) && ((reinterpret_cast<uintptr_t>(colors) & 15u) == 0u);
     bool done = !inside;
     float T = 1.f;
     uint32_t cur_idx = 0;
@@ -201,6 +223,7 @@ __global__ void rasterize_to_points_fwd_kernel(
             sC[tr] = make_float4(v[2], dc.x, dc.y,
                                  ranges ? ranges[g] : colors[(size_t)g * channels + depth_idx]);
             sId[tr] = g;
+            if (stage_features && fstride) stage_row(sFeat + tr * fpad, colors, (size_t)g, fstride, vec);
         }
         __syncthreads();
         if (__all_sync(0xffffffffu, done)) continue;
@@ -217,10 +240,10 @@ __global__ void rasterize_to_points_fwd_kernel(
             if (next_T <= kTStop) { done = true; break; }
             const float vis = alpha * T;
             const float4 Cc = sC[t];
-            const float *c_ptr = colors + (size_t)sId[t] * fstride;
+            const float *c_ptr = stage_features ? sFeat + t * fpad : colors + (size_t)sId[t] * fstride;
 #pragma unroll
             for (int k = 0; k < CDIM; ++k) {
-                if ((uint32_t)k < fstride) pix_out[k] += __ldg(c_ptr + k) * vis;
+                if ((uint32_t)k < fstride) pix_out[k] += c_ptr[k] * vis;
                 else if ((uint32_t)k < channels) pix_out[k] += Cc.w * vis;
             }
             const float dterm = Cc.y * dx + Cc.z * dy + Cc.x * roll;
@@ -685,7 +708,11 @@ extern "C" int splatad_rasterize_to_pixels_fwd(
     const uint32_t blocks = C * tile_width * tile_height;
     if (blocks == 0 || image_width == 0 || image_height == 0) return SPLATAD_OK;
     const uint32_t bs = ((tile_size * tile_size + 31) / 32) * 32;   // whole warps
-    const size_t smem = (size_t)bs * (2 * sizeof(float4) + sizeof(int32_t));
+    size_t smem = (size_t)bs * (2 * sizeof(float4) + sizeof(int32_t));
+    // the batch's colour rows ride along in shared memory while a block stays under 64 KB
+    const size_t smem_colors = (size_t)bs * ((channels + 3u) & ~3u) * sizeof(float);
+    const uint32_t stage_colors = (smem + smem_colors <= 64 * 1024) ? 1u : 0u;
+    if (stage_colors) smem += smem_colors;
 #define CALL(D)                                                                                   \
     {                                                                                             \
         int rc = set_smem(rasterize_to_pixels_fwd_kernel<D>, smem, "rasterize_to_pixels_fwd");    \
@@ -694,7 +721,7 @@ extern "C" int splatad_rasterize_to_pixels_fwd(
             C, n_isects, (const float2 *)means2d, conics, colors, channels, opacities,            \
             (const float2 *)pix_vels, rolling_shutter_time, backgrounds, image_width,             \
             image_height, tile_size, tile_width, tile_height, tile_offsets, flatten_ids,          \
-            render_colors, render_alphas, last_ids);                                              \
+            render_colors, render_alphas, last_ids, stage_colors);                                \
     }
     {
         SPL_PROF("rasterize_to_pixels_fwd_kernel", (cudaStream_t)stream);
@@ -778,7 +805,12 @@ extern "C" int splatad_rasterize_to_points_fwd(
     const uint32_t blocks = C * tile_grid_width * tile_grid_height;
     if (blocks == 0 || image_width == 0 || image_height == 0) return SPLATAD_OK;
     const uint32_t bs = ((tile_width * tile_height + 31) / 32) * 32;   // whole warps
-    const size_t smem = (size_t)bs * (3 * sizeof(float4) + sizeof(int32_t));
+    size_t smem = (size_t)bs * (3 * sizeof(float4) + sizeof(int32_t));
+    // the batch's feature rows ride along in shared memory while a block stays under 64 KB
+    const uint32_t fcols = gaussian_ranges ? channels - 1 : channels;
+    const size_t smem_feat = (size_t)bs * ((fcols + 3u) & ~3u) * sizeof(float);
+    const uint32_t stage_features = (smem + smem_feat <= 64 * 1024) ? 1u : 0u;
+    if (stage_features) smem += smem_feat;
 #define CALL(D)                                                                                   \
     {                                                                                             \
         int rc = set_smem(rasterize_to_points_fwd_kernel<D>, smem, "rasterize_to_points_fwd");    \
@@ -790,7 +822,7 @@ extern "C" int splatad_rasterize_to_points_fwd(
             (const float4 *)raster_pts, image_width, image_height, tile_width, tile_height,       \
             tile_grid_width, tile_grid_height, compute_alpha_sum_until_points,                    \
             alpha_sum_threshold, tile_offsets, flatten_ids, depth_channel_idx, render_features,   \
-            render_alphas, alpha_sum_until_points, last_ids, median_depths);                      \
+            render_alphas, alpha_sum_until_points, last_ids, median_depths, stage_features);      \
     }
     {
         SPL_PROF("rasterize_to_points_fwd_kernel", (cudaStream_t)stream);

@@ -35,7 +35,7 @@ static_assert(kSortThreads == kRadixBins, "one thread per radix bin");
 static_assert(kSortGrid <= 1024, "row scan and emit scan use one thread per sort block");
 
 // counters[] slots (int64 each)
-enum { CNT_NISECT = 0, CNT_NVIS = 1, CNT_STATUS = 2, CNT_SLOTS = 4 };
+enum { CNT_NISECT = 0, CNT_NVIS = 1, CNT_STATUS = 2, CNT_TICKET = 3, CNT_SLOTS = 4 };
 enum { ST_OVERFLOW_CAPACITY = 1, ST_OVERFLOW_INT32 = 2 };
 
 // ---------------------------------------------------------------------------------------
@@ -875,70 +875,63 @@ rowsplit_count_kernel(SplitArgs a) {
     }
 }
 
-// One block, 32 rows x 32 segments of entry blocks: exclusive scan over the entry blocks of
-// every row (in place), then the row starts of records, outputs and step-B units.
+// Block r: exclusive scan over the entry blocks of grid row r (in place). The block that
+// finishes last turns the row totals into the row starts of records, outputs and step-B units.
 __global__ void __launch_bounds__(1024)
-rowsplit_scan_kernel(SplitArgs a) {
-    __shared__ uint32_t seg_c[32][33], seg_o[32][33];
-    __shared__ uint32_t tot_c[32], tot_o[32];
-    const uint32_t r = threadIdx.x & 31, seg = threadIdx.x >> 5;
+rowsplit_scan_kernel(SplitArgs a, unsigned long long *__restrict__ ticket) {
+    __shared__ uint32_t wt[33];
+    __shared__ bool s_last;
+    const uint32_t r = blockIdx.x, tid = threadIdx.x;
     if (split_overflow(a)) return;
     const uint32_t n_entries = (uint32_t)(*a.n_entries_ptr);
     const uint32_t n_units = (n_entries + kSplitEntries - 1) / kSplitEntries;
-    const uint32_t per = (n_units + 31) / 32;
-    const uint32_t u_lo = min(n_units, seg * per), u_hi = min(n_units, u_lo + per);
-    const bool live = r < a.rows;
-    uint32_t sc = 0, so = 0;
-    if (live)
-        for (uint32_t u = u_lo; u < u_hi; ++u) {
-            sc += a.ha_cnt[u * a.rows + r];
-            so += a.ha_out[u * a.rows + r];
+    uint32_t carry_c = 0, carry_o = 0;
+    for (uint32_t u0 = 0; u0 < n_units; u0 += 1024) {
+        const uint32_t u = u0 + tid;
+        const bool live = u < n_units;
+        const uint32_t vc = live ? a.ha_cnt[u * a.rows + r] : 0u;
+        const uint32_t vo = live ? a.ha_out[u * a.rows + r] : 0u;
+        uint32_t tc, to;
+        const uint32_t ec = block_excl_scan(vc, wt, tc);
+        const uint32_t eo = block_excl_scan(vo, wt, to);
+        if (live) {
+            a.ha_cnt[u * a.rows + r] = carry_c + ec;
+            a.ha_out[u * a.rows + r] = carry_o + eo;
         }
-    seg_c[seg][r] = sc;
-    seg_o[seg][r] = so;
-    __syncthreads();
-    uint32_t pc = 0, po = 0, tc = 0, to = 0;
-    for (uint32_t s2 = 0; s2 < 32; ++s2) {
-        const uint32_t vc = seg_c[s2][r], vo = seg_o[s2][r];
-        if (s2 < seg) { pc += vc; po += vo; }
-        tc += vc;
-        to += vo;
+        carry_c += tc;
+        carry_o += to;
     }
-    if (live)
-        for (uint32_t u = u_lo; u < u_hi; ++u) {
-            const uint32_t vc = a.ha_cnt[u * a.rows + r], vo = a.ha_out[u * a.rows + r];
-            a.ha_cnt[u * a.rows + r] = pc;
-            a.ha_out[u * a.rows + r] = po;
-            pc += vc;
-            po += vo;
-        }
-    if (seg == 0) {
-        tot_c[r] = live ? tc : 0u;
-        tot_o[r] = live ? to : 0u;
+    // row totals, parked in the upper half of the row tables until the last block arrives
+    if (tid == 0) {
+        a.row_rec[kSplitMaxRows + 1 + r] = carry_c;
+        a.row_out[kSplitMaxRows + 1 + r] = carry_o;
+        __threadfence();
+        s_last = atomicAdd(ticket, 1ull) + 1ull == (unsigned long long)gridDim.x;
     }
     __syncthreads();
-    if (threadIdx.x < 32) {
-        // exclusive scans over the rows (one warp)
-        const uint32_t vc = tot_c[r], vo = tot_o[r];
-        const uint32_t vu = (vo + kSplitUnit - 1) / kSplitUnit;
-        uint32_t ic = vc, io = vo, iu = vu;
+    if (!s_last || tid >= 32) return;
+    __threadfence();
+    const uint32_t vc = tid < a.rows ? a.row_rec[kSplitMaxRows + 1 + tid] : 0u;
+    const uint32_t vo = tid < a.rows ? a.row_out[kSplitMaxRows + 1 + tid] : 0u;
+    const uint32_t vu = (vo + kSplitUnit - 1) / kSplitUnit;
+    uint32_t ic = vc, io = vo, iu = vu;
 #pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            const uint32_t oc = __shfl_up_sync(0xffffffffu, ic, off);
-            const uint32_t oo = __shfl_up_sync(0xffffffffu, io, off);
-            const uint32_t ou = __shfl_up_sync(0xffffffffu, iu, off);
-            if (r >= (uint32_t)off) { ic += oc; io += oo; iu += ou; }
-        }
-        if (r < a.rows) {
-            a.row_rec[r] = ic - vc;
-            a.row_out[r] = io - vo;
-            a.row_unit[r] = iu - vu;
-        }
-        if (r == 31) {
-            a.row_rec[a.rows] = ic;
-            a.row_out[a.rows] = io;
-            a.row_unit[a.rows] = iu;
-        }
+    for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t oc = __shfl_up_sync(0xffffffffu, ic, off);
+        const uint32_t oo = __shfl_up_sync(0xffffffffu, io, off);
+        const uint32_t ou = __shfl_up_sync(0xffffffffu, iu, off);
+        if (tid >= (uint32_t)off) { ic += oc; io += oo; iu += ou; }
+    }
+    if (tid < a.rows) {
+        a.row_rec[tid] = ic - vc;
+        a.row_out[tid] = io - vo;
+        a.row_unit[tid] = iu - vu;
+    }
+    if (tid == 31) {
+        a.row_rec[a.rows] = ic;
+        a.row_out[a.rows] = io;
+        a.row_unit[a.rows] = iu;
+        *ticket = 0ull;
     }
 }
 
@@ -1458,8 +1451,9 @@ static SplitWs carve_split(void *ws, uint64_t cap, uint32_t rows, uint32_t strid
     char *c = (char *)ws;
     size_t off = 0;
     auto take = [&](size_t n) { char *r = c ? c + off : nullptr; off += align256(n); return r; };
-    w.row_rec = (uint32_t *)take(sizeof(uint32_t) * (kSplitMaxRows + 1));
-    w.row_out = (uint32_t *)take(sizeof(uint32_t) * (kSplitMaxRows + 1));
+    // [0 .. rows] exclusive starts; the second half parks the row totals during the scan
+    w.row_rec = (uint32_t *)take(sizeof(uint32_t) * 2 * (kSplitMaxRows + 1));
+    w.row_out = (uint32_t *)take(sizeof(uint32_t) * 2 * (kSplitMaxRows + 1));
     w.row_unit = (uint32_t *)take(sizeof(uint32_t) * (kSplitMaxRows + 1));
     w.rec = (uint4 *)take(sizeof(uint4) * cap);
     // every grid row rounds its outputs up to whole units
@@ -1674,7 +1668,8 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
         }
         {
             SPL_PROF("rowsplit_scan_kernel", st);
-            rowsplit_scan_kernel<<<1, 1024, 0, st>>>(a);
+            rowsplit_scan_kernel<<<a.rows, 1024, 0, st>>>(
+                a, (unsigned long long *)(p.counters + CNT_TICKET));
         }
         {
             SPL_PROF("rowsplit_scatter_kernel", st);

@@ -155,6 +155,23 @@ def fp32_probe(dev):
     return flops / (best * 1e-3) / 1e12
 
 
+def count_row_records(meta, cfg):
+    """Number of (Gaussian, elevation tile row) pairs of a lidar frame: the records step A of the
+    tile ordering writes. Same row range as the library's rectangle (first boundary not below the
+    lower edge minus one, up to the first boundary not below the upper edge)."""
+    radii, means2d = meta["radii"], meta["means2d"]
+    vis = radii[..., 0] > 0
+    eb = torch.as_tensor(cfg["tile_elevation_boundaries"], dtype=torch.float32, device=radii.device).contiguous()
+    ne = eb.numel() - 1
+    el = means2d[..., 1][vis].contiguous()
+    rad = radii[..., 1][vis].contiguous()
+    i_lo = torch.searchsorted(eb, el - rad, right=False)
+    i_hi = torch.maximum(i_lo, torch.searchsorted(eb, el + rad, right=False))
+    y0 = torch.clamp(i_lo - 1, min=0)
+    y1 = torch.clamp(i_hi, max=ne)
+    return int(torch.clamp(y1 - y0, min=0).sum())
+
+
 def to_device(cfg, dev):
     return {k: (v.to(dev, non_blocking=True) if isinstance(v, torch.Tensor) else v) for k, v in cfg.items()}
 
@@ -300,9 +317,16 @@ def run_ours(args):
         peak, peak_src = load_peaks()
         dom = max(prof.items(), key=lambda kv: kv[1][1])
         dom_name, (dom_cnt, dom_ms) = dom
-        # algorithmic bytes per launch of the sort / emit kernels: 8-byte (key, id) pairs
+        # algorithmic bytes per launch. Tile ordering of config 2 is a row / column split: step A
+        # writes one 16-byte record per (Gaussian, tile row), step B reads the records once and
+        # writes 8 + 4 bytes per intersection.
         n_vis = int((out[3]["radii"][..., 0] > 0).sum())
+        n_rec = count_row_records(out[3], cfg)
         bytes_per_launch = {
+            "colsplit_scatter_kernel": n_rec * 16 + n_isects * 12,
+            "colsplit_count_kernel": n_rec * 8,
+            "rowsplit_scatter_kernel": n_vis * 16 + n_rec * 16,
+            "rowsplit_count_kernel": n_vis * 12,
             "tilesort_downsweep": n_isects * (8 + 8 + 2),       # read pair, write pair (last pass 12 B)
             "tilesort_upsweep": n_isects * 4,
             "emit_kernel": n_isects * 8 + n_vis * 20,

@@ -201,9 +201,13 @@ int splatad_sh_bwd(uint32_t n_elems, uint32_t K, uint32_t degrees_to_use, const 
  *          (sensor, tile, depth bits, flatten index) when sort != 0, in flatten-index order
  *          otherwise. capacity >= n_isects; if it is smaller, status bit 1 is set in
  *          host_counts[2] (copied again by _fill) and the outputs are incomplete.
- *          tile_offsets (optional, [C * tiles] int32, sort != 0 only) receives what
+ *          tile_offsets (optional, [C * tiles + 1] int32, sort != 0 only) receives what
  *          splatad_isect_offset_encode would compute from isect_ids - the fill knows every
- *          tile's start already, so asking for it here saves that pass.
+ *          tile's start already, so asking for it here saves that pass - followed by one more
+ *          entry, the number of intersections written. With that entry in place the four
+ *          compositing calls accept n_isects = -1 ("read the end of the last tile from
+ *          tile_offsets[C * tiles]"), so a caller that passes a generous capacity can enqueue
+ *          plan, fill and compositing without waiting for the count.
  * `total_elems` is C*N for the [C,N] layout (camera_ids NULL) or nnz for the packed layout
  * (camera_ids [nnz] int64 gives the sensor of each row, N is ignored).
  * Depths must be non-negative: their bit patterns are ordered as unsigned integers.

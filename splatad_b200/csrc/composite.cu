@@ -54,7 +54,8 @@ __device__ __forceinline__ TileRange tile_range(const int32_t *__restrict__ offs
                                                 uint32_t n_tiles_total, int64_t n_isects) {
     TileRange r;
     r.start = offsets[tile];
-    r.end = (tile + 1 == n_tiles_total) ? (int32_t)n_isects : offsets[tile + 1];
+    // n_isects < 0: the caller's offsets carry one more entry, the total, written on the device
+    r.end = (tile + 1 == n_tiles_total && n_isects >= 0) ? (int32_t)n_isects : offsets[tile + 1];
     return r;
 }
 

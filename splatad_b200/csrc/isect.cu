@@ -1178,13 +1178,19 @@ split_base_kernel(const uint32_t *__restrict__ slot_tot, uint32_t n_slots, uint3
     if (i1 < n_slots) slot_base[i1] = ex + v0;
 }
 
-// Tile offsets straight from the slot starts (drops the closing column of every row).
+// Tile offsets straight from the slot starts (drops the closing column of every row), followed by
+// the total. When the split was skipped for lack of room every entry is 0, so that compositing
+// enqueued behind it finds empty tiles instead of stale numbers.
 __global__ void split_offsets_kernel(const uint32_t *__restrict__ slot_base, uint32_t rows, uint32_t stride,
-                                     uint32_t row_width, int32_t *__restrict__ offsets) {
+                                     uint32_t row_width, const uint32_t *__restrict__ row_out,
+                                     const int64_t *__restrict__ counters, int64_t capacity,
+                                     int32_t *__restrict__ offsets) {
     const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool skipped = counters[CNT_NISECT] > capacity;
+    if (t == rows * row_width) offsets[t] = skipped ? 0 : (int32_t)row_out[rows];
     if (t >= rows * row_width) return;
     const uint32_t r = t / row_width, c = t - r * row_width;
-    offsets[t] = (int32_t)slot_base[r * stride + c];
+    offsets[t] = skipped ? 0 : (int32_t)slot_base[r * stride + c];
 }
 
 struct SplitWindow {
@@ -1362,8 +1368,9 @@ offset_encode_kernel(const int64_t *__restrict__ isect_ids, const int64_t *n_ptr
                      uint32_t C, uint32_t n_tiles, uint32_t tile_n_bits,
                      int32_t *__restrict__ offsets) {
     const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= C * n_tiles) return;
     const int64_t n = n_ptr ? (*n_ptr < n_imm ? *n_ptr : n_imm) : n_imm;
+    if (t == C * n_tiles && n_ptr != nullptr) offsets[t] = (int32_t)n;   // fill only: the total
+    if (t >= C * n_tiles) return;
     const int64_t cid = t / n_tiles, tile = t - (uint32_t)cid * n_tiles;
     const int64_t target = (cid << tile_n_bits) | tile;
     int64_t l = 0, h = n;   // first position with (id >> 32) >= target
@@ -1694,8 +1701,8 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
         }
         if (tile_offsets != nullptr) {
             SPL_PROF("split_offsets_kernel", st);
-            split_offsets_kernel<<<div_up(a.rows * a.row_width, kThreads), kThreads, 0, st>>>(
-                w.slot_base, a.rows, a.stride, a.row_width, tile_offsets);
+            split_offsets_kernel<<<div_up(a.rows * a.row_width + 1, kThreads), kThreads, 0, st>>>(
+                w.slot_base, a.rows, a.stride, a.row_width, w.row_out, p.counters, capacity, tile_offsets);
             tile_offsets = nullptr;   // done
         }
     } else {
@@ -1769,7 +1776,7 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
     if (sort && tile_offsets != nullptr) {
         SPL_PROF("offset_encode_kernel", st);
         const uint32_t n_ct = g.C * g.n_tiles;
-        offset_encode_kernel<<<div_up(n_ct, kThreads), kThreads, 0, st>>>(
+        offset_encode_kernel<<<div_up(n_ct + 1, kThreads), kThreads, 0, st>>>(
             isect_ids, p.counters + CNT_NISECT, capacity, g.C, g.n_tiles, g.tile_n_bits, tile_offsets);
     }
     if (host_counts != nullptr)

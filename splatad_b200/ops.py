@@ -477,11 +477,12 @@ class _FullyFusedProjectionPacked(torch.autograd.Function):
 # Tile intersection
 # =============================================================================================
 def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, gaussian_ids, sort,
-                  geom_args, n_tiles):
+                  geom_args, n_tiles, deferred=False):
     """Shared two-phase driver of both isect ops: plan -> read n_isects on the host -> fill.
 
     ``kind`` ("tiles" or "lidar_tiles") is spliced into the C symbol name; ``n_tiles`` is the number
-    of tiles per sensor.
+    of tiles per sensor. With ``deferred`` a :class:`DeferredIsect` is returned instead: when a call
+    of the same shape has been seen before, plan and fill are enqueued without the host round trip.
     """
     if packed:
         nnz = means2d.size(0)
@@ -511,37 +512,131 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
     lib = _lib.load()
     tiles_per_gauss = torch.empty(depths.shape, dtype=torch.int32, device=dev)
     if total == 0:
-        return (tiles_per_gauss, torch.empty(0, dtype=torch.int64, device=dev),
-                torch.empty(0, dtype=torch.int32, device=dev))
+        out = (tiles_per_gauss, torch.empty(0, dtype=torch.int64, device=dev),
+               torch.empty(0, dtype=torch.int32, device=dev))
+        return DeferredIsect.done(*out, C, n_tiles_total) if deferred else out
     plan_bytes = lib.splatad_isect_plan_workspace_bytes(total)
     plan_ws = _lib.workspace("isect_plan", plan_bytes, dev)
     host = _lib.pinned_counts("isect", dev)
     stream = _lib.stream_ptr(dev)
     head = (C, N, total, _lib.ptr(means2d), _lib.ptr(radii), _lib.ptr(depths), _lib.ptr(camera_ids))
-    _call(f"splatad_isect_{kind}_plan", *head, *geom_args, int(bool(sort)), _lib.ptr(tiles_per_gauss),
-          _lib.ptr(plan_ws), plan_ws.numel(), host.data_ptr(), stream)
-    torch.cuda.current_stream(dev).synchronize()
-    n_isects, status = int(host[0]), int(host[2])
-    if status & 2:
-        raise RuntimeError(f"isect: {n_isects} intersections do not fit int32 flatten ids / offsets")
-    isect_ids = torch.empty(n_isects, dtype=torch.int64, device=dev)
-    flatten_ids = torch.empty(n_isects, dtype=torch.int32, device=dev)
-    if n_isects > 0:
-        fill_ws = None
-        fill_bytes = 0
+    key = (kind, C, N, total, n_tiles_total, dev.index)
+    hint = _isect_count_hint.get(key) if (deferred and sort) else None
+
+    def plan():
+        _call(f"splatad_isect_{kind}_plan", *head, *geom_args, int(bool(sort)), _lib.ptr(tiles_per_gauss),
+              _lib.ptr(plan_ws), plan_ws.numel(), host.data_ptr(), stream)
+
+    def fill(capacity):
+        isect_ids = torch.empty(capacity, dtype=torch.int64, device=dev)
+        flatten_ids = torch.empty(capacity, dtype=torch.int32, device=dev)
         offsets = None
-        if sort:
-            fill_bytes = lib.splatad_isect_fill_workspace_bytes(n_isects)
-            fill_ws = _lib.workspace("isect_fill", fill_bytes, dev)
-            # the fill knows where every tile starts; kept for isect_offset_encode on this tensor
-            offsets = torch.empty(n_tiles_total, dtype=torch.int32, device=dev)
-        _call(f"splatad_isect_{kind}_fill", *head, *geom_args, int(bool(sort)),
-              _lib.ptr(tiles_per_gauss), _lib.ptr(plan_ws), _lib.ptr(fill_ws),
-              fill_ws.numel() if fill_ws is not None else 0, n_isects, _lib.ptr(isect_ids),
-              _lib.ptr(flatten_ids), _lib.ptr(offsets), None, stream)
+        if capacity > 0:
+            fill_ws = None
+            if sort:
+                fill_bytes = lib.splatad_isect_fill_workspace_bytes(capacity)
+                fill_ws = _lib.workspace("isect_fill", fill_bytes, dev)
+                # the fill knows where every tile starts (and appends the total); kept for
+                # isect_offset_encode on this tensor
+                offsets = torch.empty(n_tiles_total + 1, dtype=torch.int32, device=dev)
+            _call(f"splatad_isect_{kind}_fill", *head, *geom_args, int(bool(sort)),
+                  _lib.ptr(tiles_per_gauss), _lib.ptr(plan_ws), _lib.ptr(fill_ws),
+                  fill_ws.numel() if fill_ws is not None else 0, capacity, _lib.ptr(isect_ids),
+                  _lib.ptr(flatten_ids), _lib.ptr(offsets), None, stream)
+        return isect_ids, flatten_ids, offsets
+
+    def read_count():
+        n_isects, status = int(host[0]), int(host[2])
+        if status & 2:
+            raise RuntimeError(f"isect: {n_isects} intersections do not fit int32 flatten ids / offsets")
+        _isect_count_hint[key] = n_isects
+        return n_isects
+
+    def exact():
+        plan()
+        torch.cuda.current_stream(dev).synchronize()
+        n_isects = read_count()
+        isect_ids, flatten_ids, offsets = fill(n_isects)
         if offsets is not None:
-            isect_ids._splatad_tile_offsets = (C, offsets)
-    return tiles_per_gauss, isect_ids, flatten_ids
+            isect_ids._splatad_tile_offsets = (C, offsets[:n_tiles_total])
+        return tiles_per_gauss, isect_ids, flatten_ids
+
+    if not deferred:
+        return exact()
+    if hint is None:
+        return DeferredIsect.done(*exact(), C, n_tiles_total)
+    # Enqueue plan and fill back to back with room for somewhat more intersections than last time;
+    # the count is read when the caller asks for the exact tensors.
+    capacity = hint + hint // 8 + 65536
+    plan()
+    counted = torch.cuda.Event()
+    counted.record(torch.cuda.current_stream(dev))
+    isect_buf, flat_buf, offsets = fill(capacity)
+    return DeferredIsect(tiles_per_gauss, isect_buf, flat_buf, offsets, C, n_tiles_total, capacity,
+                         counted, read_count, exact)
+
+
+_isect_count_hint: dict = {}
+
+
+class DeferredIsect:
+    """Tile intersection whose count may still be on the device.
+
+    ``flatten_ids`` (at least as long as the count) and ``offsets`` ([C * tiles] tile starts followed
+    by the total) can be handed to the compositing ops at once; ``resolve()`` waits for the count
+    and returns (isect_ids, flatten_ids) of the exact length - or None when the count outgrew the
+    room given to it, in which case ``redo()`` runs the two-step protocol and everything composited
+    from this object has to be repeated.
+    """
+
+    def __init__(self, tiles_per_gauss, isect_buf, flat_buf, offsets, C, n_tiles_total, capacity, counted,
+                 read_count, exact):
+        self.tiles_per_gauss = tiles_per_gauss
+        self.flatten_ids = flat_buf
+        self._isect_buf = isect_buf
+        self._offsets = offsets
+        self._C, self._n_tiles_total = C, n_tiles_total
+        self._capacity, self._counted, self._read_count, self._exact = capacity, counted, read_count, exact
+        self._resolved = None
+
+    @classmethod
+    def done(cls, tiles_per_gauss, isect_ids, flatten_ids, C, n_tiles_total):
+        d = cls(tiles_per_gauss, isect_ids, flatten_ids, None, C, n_tiles_total, isect_ids.numel(), None,
+                None, None)
+        d._resolved = (isect_ids, flatten_ids)
+        return d
+
+    def offsets(self, tile_height: int, tile_width: int) -> Tensor:
+        """[C, tile_height, tile_width] tile starts for the compositing ops."""
+        if self._offsets is None or self._C * tile_height * tile_width != self._n_tiles_total:
+            resolved = self.resolve()
+            if resolved is None:
+                raise RuntimeError("isect: count outgrew its room and the tile grid does not match")
+            return isect_offset_encode(resolved[0], self._C, tile_width, tile_height)
+        view = self._offsets[: self._n_tiles_total].view(self._C, tile_height, tile_width)
+        view._splatad_total_follows = True   # the compositing ops may read the total behind it
+        return view
+
+    def resolve(self):
+        if self._resolved is None:
+            self._counted.synchronize()
+            n_isects = self._read_count()
+            if n_isects > self._capacity:
+                return None
+            isect_ids = self._isect_buf[:n_isects]
+            isect_ids._splatad_tile_offsets = (self._C, self._offsets[: self._n_tiles_total])
+            self._resolved = (isect_ids, self.flatten_ids[:n_isects])
+        return self._resolved
+
+    def redo(self):
+        tiles_per_gauss, isect_ids, flatten_ids = self._exact()
+        return DeferredIsect.done(tiles_per_gauss, isect_ids, flatten_ids, self._C, self._n_tiles_total)
+
+
+def _n_isects_arg(isect_offsets: Tensor, flatten_ids: Tensor) -> int:
+    """What the compositing entry points get as n_isects: the length of flatten_ids, or -1 when the
+    total sits behind the tile starts on the device (see DeferredIsect)."""
+    return -1 if getattr(isect_offsets, "_splatad_total_follows", False) else flatten_ids.numel()
 
 
 @torch.no_grad()
@@ -590,6 +685,30 @@ def isect_lidar_tiles(
                          (_lib.ptr(eb), int(eb.numel()), float(tile_azim_resolution), float(min_azim)),
                          int(_lib.load().splatad_lidar_azimuth_tiles(float(tile_azim_resolution)))
                          * (int(eb.numel()) - 1))
+
+
+@torch.no_grad()
+def isect_tiles_deferred(means2d, radii, depths, tile_size, tile_width, tile_height, packed=False,
+                         n_cameras=None, camera_ids=None, gaussian_ids=None) -> "DeferredIsect":
+    """:func:`isect_tiles` (sorted) without the wait for the intersection count in the middle; see
+    :class:`DeferredIsect`. Used by ``splatad_b200.rasterization``."""
+    return _isect_common("tiles", means2d, radii, depths, packed, n_cameras, camera_ids, gaussian_ids,
+                         True, (int(tile_size), int(tile_width), int(tile_height)),
+                         int(tile_width) * int(tile_height), deferred=True)
+
+
+@torch.no_grad()
+def isect_lidar_tiles_deferred(means2d, radii, depths, elev_boundaries, tile_azim_resolution, min_azim,
+                               packed=False, n_cameras=None, camera_ids=None,
+                               gaussian_ids=None) -> "DeferredIsect":
+    """:func:`isect_lidar_tiles` (sorted) without the wait for the intersection count in the middle;
+    see :class:`DeferredIsect`. Used by ``splatad_b200.lidar_rasterization``."""
+    eb = _f(elev_boundaries)
+    n_tiles = int(_lib.load().splatad_lidar_azimuth_tiles(float(tile_azim_resolution))) * (int(eb.numel()) - 1)
+    return _isect_common("lidar_tiles", means2d, radii, depths, packed, n_cameras, camera_ids,
+                         gaussian_ids, True,
+                         (_lib.ptr(eb), int(eb.numel()), float(tile_azim_resolution), float(min_azim)),
+                         n_tiles, deferred=True)
 
 
 @torch.no_grad()
@@ -692,7 +811,8 @@ class _RasterizeToPixels(torch.autograd.Function):
         render_colors = torch.empty((C, height, width, channels), dtype=torch.float32, device=dev)
         render_alphas = torch.empty((C, height, width, 1), dtype=torch.float32, device=dev)
         last_ids = torch.empty((C, height, width), dtype=torch.int32, device=dev)
-        n_isects = flatten_ids.numel()
+        n_isects = _n_isects_arg(isect_offsets, flatten_ids)
+        ctx.n_isects_arg = n_isects
         _call(
             "splatad_rasterize_to_pixels_fwd", C, n_isects, _lib.ptr(means2d), _lib.ptr(conics_f),
             _lib.ptr(colors_f), channels, _lib.ptr(opac_f), _lib.ptr(vels_f), _lib.ptr(rs), _lib.ptr(bg),
@@ -720,7 +840,7 @@ class _RasterizeToPixels(torch.autograd.Function):
         v_pix_vels = torch.zeros_like(pix_vels)
         v_abs = torch.zeros_like(v_means2d) if ctx.absgrad else None
         _call(
-            "splatad_rasterize_to_pixels_bwd", C, flatten_ids.numel(), _lib.ptr(means2d),
+            "splatad_rasterize_to_pixels_bwd", C, ctx.n_isects_arg, _lib.ptr(means2d),
             _lib.ptr(conics), _lib.ptr(colors), channels, _lib.ptr(opacities), _lib.ptr(pix_vels),
             _lib.ptr(rs), _lib.ptr(bg), ctx.width, ctx.height, ctx.tile_size, tile_w, tile_h,
             _lib.ptr(isect_offsets), _lib.ptr(flatten_ids), _lib.ptr(render_alphas), _lib.ptr(last_ids),
@@ -861,8 +981,9 @@ class _RasterizeToPoints(torch.autograd.Function):
         median_depths = torch.empty((C, height, width, 1), **f32)
         alpha_sum = torch.empty((C, height, width, 1), **f32) if compute_alpha_sum_until_points else None
         last_ids = torch.empty((C, height, width), dtype=torch.int32, device=dev)
+        ctx.n_isects_arg = _n_isects_arg(isect_offsets, flatten_ids)
         _call(
-            "splatad_rasterize_to_points_fwd", C, flatten_ids.numel(), _lib.ptr(means2d),
+            "splatad_rasterize_to_points_fwd", C, ctx.n_isects_arg, _lib.ptr(means2d),
             _lib.ptr(conics_f), _lib.ptr(colors_f) if colors_f.numel() else None, _lib.ptr(ranges_f), channels,
             _lib.ptr(opac_f), _lib.ptr(vels_f),
             _lib.ptr(dc_f), _lib.ptr(bg), _lib.ptr(pts_f), width, height, tile_width, tile_height,
@@ -899,7 +1020,7 @@ class _RasterizeToPoints(torch.autograd.Function):
         v_depth_comps = torch.zeros_like(depth_comps)
         v_abs = torch.zeros_like(v_means2d) if absgrad else None
         _call(
-            "splatad_rasterize_to_points_bwd", C, flatten_ids.numel(), _lib.ptr(means2d),
+            "splatad_rasterize_to_points_bwd", C, ctx.n_isects_arg, _lib.ptr(means2d),
             _lib.ptr(conics), _lib.ptr(colors) if colors.numel() else None, _lib.ptr(ranges), channels,
             _lib.ptr(opacities), _lib.ptr(pix_vels),
             _lib.ptr(depth_comps), _lib.ptr(bg), _lib.ptr(raster_pts), width, height, tile_width,

@@ -22,9 +22,8 @@ except ImportError:  # pragma: no cover
 from .ops import (
     fully_fused_lidar_projection,
     fully_fused_projection,
-    isect_lidar_tiles,
-    isect_offset_encode,
-    isect_tiles,
+    isect_lidar_tiles_deferred,
+    isect_tiles_deferred,
     rasterize_to_pixels,
     rasterize_to_points,
     rasterize_to_points_split,
@@ -140,7 +139,9 @@ def rasterization(
 
     tile_width = math.ceil(width / float(tile_size))
     tile_height = math.ceil(height / float(tile_size))
-    tiles_per_gauss, isect_ids, flatten_ids = isect_tiles(
+    # plan + fill are enqueued without waiting for the intersection count (once a frame of this
+    # shape has been seen); the exact-length isect_ids / flatten_ids are cut out after compositing
+    isect = isect_tiles_deferred(
         means2d,
         radii,
         depths,
@@ -152,7 +153,6 @@ def rasterization(
         camera_ids=camera_ids,
         gaussian_ids=gaussian_ids,
     )
-    isect_offsets = isect_offset_encode(isect_ids, C, tile_width, tile_height)
 
     if sh_degree is None:
         if packed:
@@ -192,30 +192,39 @@ def rasterization(
         if backgrounds is not None:
             backgrounds = torch.zeros(C, 1, device=backgrounds.device)
 
-    if colors.shape[-1] > channel_chunk:
-        n_chunks = (colors.shape[-1] + channel_chunk - 1) // channel_chunk
-        render_colors, render_alphas = [], []
-        for i in range(n_chunks):
-            colors_chunk = colors[..., i * channel_chunk : (i + 1) * channel_chunk]
-            backgrounds_chunk = (
-                backgrounds[..., i * channel_chunk : (i + 1) * channel_chunk]
-                if backgrounds is not None
-                else None
-            )
-            render_colors_, render_alphas_ = rasterize_to_pixels(
-                means2d, conics, colors_chunk, opacities, pix_vels, width, height, tile_size,
-                isect_offsets, flatten_ids, rolling_shutter_time, backgrounds=backgrounds_chunk,
-                packed=packed, absgrad=absgrad,
-            )
-            render_colors.append(render_colors_)
-            render_alphas.append(render_alphas_)
-        render_colors = torch.cat(render_colors, dim=-1)
-        render_alphas = render_alphas[0]  # discard the rest
-    else:
-        render_colors, render_alphas = rasterize_to_pixels(
+    def composite(isect_offsets, flatten_ids):
+        if colors.shape[-1] > channel_chunk:
+            n_chunks = (colors.shape[-1] + channel_chunk - 1) // channel_chunk
+            chunk_colors, chunk_alphas = [], []
+            for i in range(n_chunks):
+                colors_chunk = colors[..., i * channel_chunk : (i + 1) * channel_chunk]
+                backgrounds_chunk = (
+                    backgrounds[..., i * channel_chunk : (i + 1) * channel_chunk]
+                    if backgrounds is not None
+                    else None
+                )
+                render_colors_, render_alphas_ = rasterize_to_pixels(
+                    means2d, conics, colors_chunk, opacities, pix_vels, width, height, tile_size,
+                    isect_offsets, flatten_ids, rolling_shutter_time, backgrounds=backgrounds_chunk,
+                    packed=packed, absgrad=absgrad,
+                )
+                chunk_colors.append(render_colors_)
+                chunk_alphas.append(render_alphas_)
+            return torch.cat(chunk_colors, dim=-1), chunk_alphas[0]  # alphas are the same for every chunk
+        return rasterize_to_pixels(
             means2d, conics, colors, opacities, pix_vels, width, height, tile_size, isect_offsets,
             flatten_ids, rolling_shutter_time, backgrounds=backgrounds, packed=packed, absgrad=absgrad,
         )
+
+    render_colors, render_alphas = composite(isect.offsets(tile_height, tile_width), isect.flatten_ids)
+    resolved = isect.resolve()
+    if resolved is None:  # more intersections than there was room for: the two-step way, again
+        isect = isect.redo()
+        render_colors, render_alphas = composite(isect.offsets(tile_height, tile_width), isect.flatten_ids)
+        resolved = isect.resolve()
+    isect_ids, flatten_ids = resolved
+    isect_offsets = isect.offsets(tile_height, tile_width)
+    tiles_per_gauss = isect.tiles_per_gauss
     if render_mode in ["ED", "RGB+ED"]:
         render_colors = torch.cat(
             [render_colors[..., :-1], render_colors[..., -1:] / render_alphas.clamp(min=1e-10)],
@@ -360,7 +369,9 @@ def lidar_rasterization(
     n_elevation_tiles = math.ceil(n_elevation_channels / tile_height)
     tile_azimuth_resolution = azimuth_resolution * tile_width
     n_azimuth_tiles = math.ceil((max_azimuth - min_azimuth) / tile_azimuth_resolution)
-    tiles_per_gauss, isect_ids, flatten_ids = isect_lidar_tiles(
+    # plan + fill are enqueued without waiting for the intersection count (once a frame of this
+    # shape has been seen); the exact-length isect_ids / flatten_ids are cut out after compositing
+    isect = isect_lidar_tiles_deferred(
         means2d,
         radii,
         depths,
@@ -372,67 +383,49 @@ def lidar_rasterization(
         camera_ids=camera_ids,
         gaussian_ids=gaussian_ids,
     )
-    isect_offsets = isect_offset_encode(isect_ids, C, n_azimuth_tiles, n_elevation_tiles)
 
     image_width = raster_pts.shape[-2]
     image_height = raster_pts.shape[-3]
 
-    if (lidar_features.shape[-1] + 1) > channel_chunk:
-        n_chunks = (lidar_features.shape[-1] + channel_chunk) // channel_chunk
-        render_lidar_features, render_alphas, alpha_sum_until_points, median_depths = [], [], [], []
-        for i in range(n_chunks):
-            lidar_features_chunk = lidar_features[..., i * (channel_chunk - 1) : (i + 1) * (channel_chunk - 1)]
-            (render_lidar_features_, render_alphas_, alpha_sum_until_points_, median_depths_) = rasterize_to_points(
-                means2d,
-                conics,
-                torch.cat([lidar_features_chunk, depths[..., None]], dim=-1),
-                opacities,
-                pix_vels,
-                depth_compensations,
-                raster_pts,
-                image_width,
-                image_height,
-                tile_width,
-                tile_height,
-                isect_offsets,
-                flatten_ids,
-                compute_alpha_sum_until_points=compute_alpha_sum_until_points,
-                compute_alpha_sum_until_points_threshold=compute_alpha_sum_until_points_threshold,
-                packed=packed,
-                absgrad=absgrad,
-            )
-            if i == (n_chunks - 1):
-                render_lidar_features.append(render_lidar_features_)
-            else:
-                render_lidar_features.append(render_lidar_features_[..., :-1])
-            render_alphas.append(render_alphas_)
-            alpha_sum_until_points.append(alpha_sum_until_points_)
-            median_depths.append(median_depths_)
-        render_lidar_features = torch.cat(render_lidar_features, dim=-1)
-        median_depths = torch.cat(median_depths, dim=-1)
-        render_alphas = render_alphas[0]  # discard the rest
-        alpha_sum_until_points = alpha_sum_until_points[0]  # same alphas for all chunks
-    else:
-        # one launch: the range channel is read from `depths` directly (no [C,N,D+1] concatenation)
-        render_lidar_features, render_alphas, alpha_sum_until_points, median_depths = rasterize_to_points_split(
-            means2d,
-            conics,
-            lidar_features,
-            depths,
-            opacities,
-            pix_vels,
-            depth_compensations,
-            raster_pts,
-            image_width,
-            image_height,
-            tile_width,
-            tile_height,
-            isect_offsets,
-            flatten_ids,
+    def composite(isect_offsets, flatten_ids):
+        common = dict(
             compute_alpha_sum_until_points=compute_alpha_sum_until_points,
             compute_alpha_sum_until_points_threshold=compute_alpha_sum_until_points_threshold,
             absgrad=absgrad,
         )
+        geometry = (raster_pts, image_width, image_height, tile_width, tile_height, isect_offsets, flatten_ids)
+        if (lidar_features.shape[-1] + 1) <= channel_chunk:
+            # one launch: the range channel is read from `depths` directly (no [C,N,D+1] concatenation)
+            return rasterize_to_points_split(
+                means2d, conics, lidar_features, depths, opacities, pix_vels, depth_compensations,
+                *geometry, **common,
+            )
+        # every chunk carries channel_chunk - 1 features and the range as its last channel
+        n_chunks = (lidar_features.shape[-1] + channel_chunk) // channel_chunk
+        chunks, medians, first = [], [], None
+        for i in range(n_chunks):
+            lidar_features_chunk = lidar_features[..., i * (channel_chunk - 1) : (i + 1) * (channel_chunk - 1)]
+            features_, alphas_, alpha_sum_, median_ = rasterize_to_points(
+                means2d, conics, torch.cat([lidar_features_chunk, depths[..., None]], dim=-1), opacities,
+                pix_vels, depth_compensations, *geometry, packed=packed, **common,
+            )
+            chunks.append(features_ if i == n_chunks - 1 else features_[..., :-1])
+            medians.append(median_)
+            if first is None:
+                first = (alphas_, alpha_sum_)  # the same for every chunk
+        return torch.cat(chunks, dim=-1), first[0], first[1], torch.cat(medians, dim=-1)
+
+    grid = (n_elevation_tiles, n_azimuth_tiles)
+    outputs = composite(isect.offsets(*grid), isect.flatten_ids)
+    resolved = isect.resolve()
+    if resolved is None:  # more intersections than there was room for: the two-step way, again
+        isect = isect.redo()
+        outputs = composite(isect.offsets(*grid), isect.flatten_ids)
+        resolved = isect.resolve()
+    render_lidar_features, render_alphas, alpha_sum_until_points, median_depths = outputs
+    isect_ids, flatten_ids = resolved
+    isect_offsets = isect.offsets(*grid)
+    tiles_per_gauss = isect.tiles_per_gauss
 
     meta = {
         "camera_ids": camera_ids,

@@ -228,3 +228,56 @@ def test_lidar_training_step_gradients_flow():
         assert float(cfg[k].grad.abs().sum()) > 0, k
     assert m["means2d"].grad is not None and hasattr(m["means2d"], "absgrad")
     assert torch.all(m["means2d"].absgrad + 1e-6 >= m["means2d"].grad.abs())
+
+
+def test_repeated_frames_skip_the_count_round_trip():
+    """From the second frame of a shape on, plan and fill are enqueued with a capacity guessed from
+    the previous count. Results must not depend on that: same lists, same render, same gradients;
+    and a frame whose count outgrows the guess is redone the two-step way."""
+    import splatad_b200
+    from splatad_b200 import ops, scenes
+    cfg = scenes.config2(N=40_000)
+    g = _to_gpu(cfg)
+    ops._isect_count_hint.clear()
+    first = splatad_b200.lidar_rasterization(**g)            # no hint yet: two-step protocol
+    assert len(ops._isect_count_hint) == 1
+    second = splatad_b200.lidar_rasterization(**g)           # hinted
+    for a, b in zip(first[:3], second[:3]):
+        assert torch.equal(a, b)
+    for key in ("tiles_per_gauss", "isect_ids", "flatten_ids", "isect_offsets", "median_depths"):
+        assert torch.equal(first[3][key], second[3][key]), key
+    assert second[3]["isect_ids"].numel() == first[3]["isect_ids"].numel()
+    # three times the scale -> far more intersections than the hint allows for
+    big = dict(g, scales=g["scales"] * 3.0)
+    key = next(iter(ops._isect_count_hint))
+    hinted = ops._isect_count_hint[key]
+    third = splatad_b200.lidar_rasterization(**big)
+    assert third[3]["isect_ids"].numel() > hinted + hinted // 8 + 65536
+    ops._isect_count_hint.clear()
+    want = splatad_b200.lidar_rasterization(**big)           # two-step protocol again
+    for a, b in zip(third[:3], want[:3]):
+        assert torch.equal(a, b)
+    assert torch.equal(third[3]["isect_ids"], want[3]["isect_ids"])
+    assert torch.equal(third[3]["flatten_ids"], want[3]["flatten_ids"])
+    # gradients through a hinted frame equal those of a two-step frame
+    grads = []
+    for _ in range(2):
+        leaves = {k: g[k].clone().requires_grad_(True) for k in ("means", "quats", "scales", "opacities")}
+        out = splatad_b200.lidar_rasterization(**dict(big, **leaves))
+        (out[0].square().mean() + out[1].mean()).backward()
+        grads.append({k: v.grad.clone() for k, v in leaves.items()})
+    for k in grads[0]:
+        assert_close(f"hinted grad {k}", n(grads[1][k]), n(grads[0][k]), 1e-4, 1e-7, max_bad_frac=1e-3)
+
+
+def test_repeated_camera_frames():
+    import splatad_b200
+    from splatad_b200 import ops, scenes
+    cfg = scenes.config1(N=30_000)
+    g = _to_gpu(cfg)
+    ops._isect_count_hint.clear()
+    first = splatad_b200.rasterization(**g)
+    second = splatad_b200.rasterization(**g)
+    assert torch.equal(first[0], second[0]) and torch.equal(first[1], second[1])
+    for key in ("isect_ids", "flatten_ids", "isect_offsets", "tiles_per_gauss"):
+        assert torch.equal(first[2][key], second[2][key]), key

@@ -196,7 +196,8 @@ int splatad_sh_bwd(uint32_t n_elems, uint32_t K, uint32_t degrees_to_use, const 
  * Here each is a two-call protocol on one stream:
  *   _plan  writes tiles_per_gauss, orders the visible Gaussians by depth, and copies
  *          host_counts[0..3] = {n_isects, n_visible, status bits, 0} to the host (pinned memory
- *          recommended; valid once the stream has reached that point).
+ *          recommended; valid once the stream has reached that point). n_isects must fit
+ *          int32 (flatten ids and offsets are int32): check it before calling _fill.
  *   _fill  writes isect_ids [capacity] int64 and flatten_ids [capacity] int32, sorted by
  *          (sensor, tile, depth bits, flatten index) when sort != 0, in flatten-index order
  *          otherwise. capacity >= n_isects; if it is smaller, status bit 1 is set in

@@ -212,11 +212,6 @@ isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ til
     }
 }
 
-// Raises the status bit when the total does not fit the int32 outputs.
-__global__ void check_total_kernel(int64_t *counters) {
-    if (threadIdx.x == 0 && counters[CNT_NISECT] > 0x7fffffffll) counters[CNT_STATUS] |= ST_OVERFLOW_INT32;
-}
-
 // ---------------------------------------------------------------------------------------
 // Radix sort passes (stable LSD, up to 8 bits per pass) on (uint32 key, uint32 value) pairs.
 // Each of the kSortGrid blocks owns a contiguous run of 4096-item tiles.
@@ -742,8 +737,7 @@ emit_kernel(GridArgs<kLidar> a, EmitArgs e, const uint32_t *__restrict__ eoff,
 //               per column of a piece comes from +1 / -1 updates of a difference row; inside a
 //               piece the warp walks 32 outputs at a time: the records that start inside the
 //               32 outputs set one bit each, which tells every lane its record, and lanes that
-//               hit the same column are ranked in lane order (few records: they take turns,
-//               the columns of one run being distinct; many: one ballot per column bit). The
+//               hit the same column are ranked in lane order (one ballot per column bit). The
 //               4096 outputs are put in tile order in shared memory and leave as ~70-entry
 //               runs per tile.
 // Positions are exclusive sums over (earlier tiles, earlier units, earlier warps), all of
@@ -757,7 +751,6 @@ constexpr uint32_t kSplitWarpEntries = 128;                // entries per warp i
 constexpr uint32_t kSplitEntries = kSplitWarps * kSplitWarpEntries;   // entries per block
 constexpr uint32_t kSplitSub = 512;                        // outputs per warp in step B
 constexpr uint32_t kSplitUnit = kSplitWarps * kSplitSub;   // outputs per block in step B
-constexpr uint32_t kSplitTurns = 8;                        // records per chunk ranked by turns
 constexpr uint32_t kSplitColBits = 11;
 
 struct SplitArgs {
@@ -1117,14 +1110,25 @@ colsplit_count_kernel(SplitArgs a) {
     for (uint32_t i = tid; i < a.stride; i += blockDim.x) row[i] = (uint32_t)s_d[i];
 }
 
-// Block r: exclusive scan over the units of grid row r for every column (in place); the
-// column totals go to slot_tot[r][col].
+// Block r: exclusive scan over the units of grid row r for every column (in place); the column
+// totals go to slot_tot[r][col]. The block that finishes last (an atomic ticket, nobody waits)
+// scans the totals into slot_base and, when asked, writes the tile offsets - the slot starts
+// without the closing column of every row - followed by the total.
 __global__ void __launch_bounds__(1024)
-colsplit_scan_kernel(SplitArgs a) {
+colsplit_scan_kernel(SplitArgs a, unsigned long long *__restrict__ ticket, int32_t *__restrict__ offsets) {
     __shared__ uint32_t seg_sum[32][33];
+    __shared__ uint32_t wt[33];
+    __shared__ bool s_last;
     const uint32_t lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
     const uint32_t r = blockIdx.x;
-    if (split_overflow(a)) return;
+    const uint32_t n_tiles = a.rows * a.row_width;
+    if (split_overflow(a)) {
+        // the split is skipped for lack of room: every offset 0, so that compositing enqueued
+        // behind it finds empty tiles instead of stale numbers
+        if (offsets != nullptr)
+            for (uint32_t t = r * 1024 + threadIdx.x; t <= n_tiles; t += gridDim.x * 1024) offsets[t] = 0;
+        return;
+    }
     const uint32_t ub0 = a.row_unit[r], n_units = a.row_unit[r + 1] - ub0;
     const uint32_t per = (n_units + 31) / 32;
     const uint32_t u_lo = min(n_units, seg * per), u_hi = min(n_units, u_lo + per);
@@ -1163,34 +1167,30 @@ colsplit_scan_kernel(SplitArgs a) {
             if (seg == 0) a.slot_tot[r * a.stride + c] = total;
         }
     }
-}
-
-// One block of 1024 threads, two slots each: slot_base = exclusive scan of slot_tot.
-__global__ void __launch_bounds__(1024)
-split_base_kernel(const uint32_t *__restrict__ slot_tot, uint32_t n_slots, uint32_t *__restrict__ slot_base) {
-    __shared__ uint32_t wt[33];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        s_last = atomicAdd(ticket, 1ull) + 1ull == (unsigned long long)gridDim.x;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // two slots per thread: slot_base = exclusive scan of slot_tot
+    const uint32_t n_slots = a.rows * a.stride;
     const uint32_t i0 = 2 * threadIdx.x, i1 = i0 + 1;
-    const uint32_t v0 = i0 < n_slots ? slot_tot[i0] : 0u;
-    const uint32_t v1 = i1 < n_slots ? slot_tot[i1] : 0u;
+    const uint32_t v0 = i0 < n_slots ? a.slot_tot[i0] : 0u;
+    const uint32_t v1 = i1 < n_slots ? a.slot_tot[i1] : 0u;
     uint32_t total;
     const uint32_t ex = block_excl_scan(v0 + v1, wt, total);
-    if (i0 < n_slots) slot_base[i0] = ex;
-    if (i1 < n_slots) slot_base[i1] = ex + v0;
-}
-
-// Tile offsets straight from the slot starts (drops the closing column of every row), followed by
-// the total. When the split was skipped for lack of room every entry is 0, so that compositing
-// enqueued behind it finds empty tiles instead of stale numbers.
-__global__ void split_offsets_kernel(const uint32_t *__restrict__ slot_base, uint32_t rows, uint32_t stride,
-                                     uint32_t row_width, const uint32_t *__restrict__ row_out,
-                                     const int64_t *__restrict__ counters, int64_t capacity,
-                                     int32_t *__restrict__ offsets) {
-    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
-    const bool skipped = counters[CNT_NISECT] > capacity;
-    if (t == rows * row_width) offsets[t] = skipped ? 0 : (int32_t)row_out[rows];
-    if (t >= rows * row_width) return;
-    const uint32_t r = t / row_width, c = t - r * row_width;
-    offsets[t] = skipped ? 0 : (int32_t)slot_base[r * stride + c];
+    if (i0 < n_slots) a.slot_base[i0] = ex;
+    if (i1 < n_slots) a.slot_base[i1] = ex + v0;
+    if (threadIdx.x == 0) *ticket = 0ull;
+    if (offsets == nullptr) return;
+    __syncthreads();
+    for (uint32_t t = threadIdx.x; t <= n_tiles; t += 1024) {
+        const uint32_t rr = t / a.row_width, c = t - rr * a.row_width;
+        offsets[t] = (t == n_tiles) ? (int32_t)total : (int32_t)a.slot_base[rr * a.stride + c];
+    }
 }
 
 struct SplitWindow {
@@ -1294,7 +1294,6 @@ colsplit_scatter_kernel(SplitArgs a, int64_t *__restrict__ isect_ids, int32_t *_
                 const uint32_t e0 = __shfl_sync(0xffffffffu, win.s0, own);
                 const uint32_t idx = __shfl_sync(0xffffffffu, win.idx, own);
                 const uint32_t depth = __shfl_sync(0xffffffffu, win.depth, own);
-                const uint32_t w = jxw >> 16;
                 uint32_t col = (jxw & 0xffffu) + (o - e0);
                 if (a.wrap && col >= a.row_width) {
                     col -= a.row_width;
@@ -1303,38 +1302,25 @@ colsplit_scatter_kernel(SplitArgs a, int64_t *__restrict__ isect_ids, int32_t *_
                 // a column outside the row cannot come from a consistent record
                 const bool active = o < w_end && col < a.row_width;
                 if (!active) col = 0;
-                // Rank among the outputs of this chunk in the same column. The columns of one run
-                // are distinct (unless it is wider than a full turn), so with few records in the
-                // chunk they take turns; otherwise lanes with equal columns are matched with one
-                // ballot per column bit and ranked in lane order.
-                const uint32_t n_own = __popc(B) + 1u;
-                const bool twins = a.wrap && __any_sync(0xffffffffu, active && w > a.row_width);
-                uint32_t lpos = 0;
-                if (!twins && n_own <= kSplitTurns) {
-                    for (uint32_t turn = 0; turn < n_own; ++turn) {
-                        if (active && rel == turn) {
-                            lpos = hist[col];
-                            hist[col] = lpos + 1u;
-                        }
-                        __syncwarp();
-                    }
-                } else {
-                    uint32_t peers = __ballot_sync(0xffffffffu, active);
+                // Rank among the outputs of this chunk in the same column: lanes with equal
+                // columns are matched with one ballot per column bit and ranked in lane order.
+                // (Letting the records of a chunk take turns instead - the columns of one run are
+                // distinct - measured the same.)
+                uint32_t peers = __ballot_sync(0xffffffffu, active);
 #pragma unroll
-                    for (uint32_t bit = 0; bit < kSplitColBits; ++bit) {
-                        if (bit >= a.col_bits) break;
-                        const bool one = (col >> bit) & 1u;
-                        const uint32_t bal = __ballot_sync(0xffffffffu, one);
-                        peers &= one ? bal : ~bal;
-                    }
-                    const uint32_t rank = __popc(peers & lt), cnt = __popc(peers);
-                    uint32_t v = 0;
-                    if (active) v = hist[col];
-                    __syncwarp();
-                    if (active && rank + 1 == cnt) hist[col] = v + cnt;   // one lane per column
-                    __syncwarp();
-                    lpos = v + rank;
+                for (uint32_t bit = 0; bit < kSplitColBits; ++bit) {
+                    if (bit >= a.col_bits) break;
+                    const bool one = (col >> bit) & 1u;
+                    const uint32_t bal = __ballot_sync(0xffffffffu, one);
+                    peers &= one ? bal : ~bal;
                 }
+                const uint32_t rank = __popc(peers & lt), cnt = __popc(peers);
+                uint32_t v = 0;
+                if (active) v = hist[col];
+                __syncwarp();
+                if (active && rank + 1 == cnt) hist[col] = v + cnt;   // one lane per column
+                __syncwarp();
+                const uint32_t lpos = v + rank;
                 if (active && lpos < kSplitUnit) {
                     st_col[lpos] = (uint16_t)col;
                     st_depth[lpos] = depth;
@@ -1582,10 +1568,7 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
         e.order = va;
         e.n_order_ptr = p.counters + CNT_NVIS;
     }
-    if (split) {
-        SPL_PROF("check_total_kernel", st);
-        check_total_kernel<<<1, 32, 0, st>>>(p.counters);
-    } else {
+    if (!split) {
         {
             SPL_PROF("emit_blocksum_kernel", st);
             emit_blocksum_kernel<<<kSortGrid, kThreads, 0, st>>>(e, p.block_sums);
@@ -1688,22 +1671,14 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
         }
         {
             SPL_PROF("colsplit_scan_kernel", st);
-            colsplit_scan_kernel<<<a.rows, 1024, 0, st>>>(a);
-        }
-        {
-            SPL_PROF("split_base_kernel", st);
-            split_base_kernel<<<1, 1024, 0, st>>>(w.slot_tot, a.rows * a.stride, w.slot_base);
+            colsplit_scan_kernel<<<a.rows, 1024, 0, st>>>(
+                a, (unsigned long long *)(p.counters + CNT_TICKET), tile_offsets);
+            tile_offsets = nullptr;   // done
         }
         {
             SPL_PROF("colsplit_scatter_kernel", st);
             colsplit_scatter_kernel<<<w.units_b_cap, kSplitWarps * 32, smem_scatter, st>>>(
                 a, isect_ids, flatten_ids, p.counters);
-        }
-        if (tile_offsets != nullptr) {
-            SPL_PROF("split_offsets_kernel", st);
-            split_offsets_kernel<<<div_up(a.rows * a.row_width + 1, kThreads), kThreads, 0, st>>>(
-                w.slot_base, a.rows, a.stride, a.row_width, w.row_out, p.counters, capacity, tile_offsets);
-            tile_offsets = nullptr;   // done
         }
     } else {
         FillWs f = carve_fill(fill_workspace, (uint64_t)capacity);

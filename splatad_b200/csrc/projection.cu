@@ -214,7 +214,7 @@ __device__ __forceinline__ GaussIn load_gaussian(const float *__restrict__ means
 // ---------------------------------------------------------------------------------------
 // Lidar forward
 // ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 3)
 lidar_projection_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ means,
                             const float *__restrict__ covars, const float *__restrict__ quats,
                             const float *__restrict__ scales, const float *__restrict__ velocities,

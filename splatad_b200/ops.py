@@ -547,7 +547,7 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
 
     def read_count():
         n_isects, status = int(host[0]), int(host[2])
-        if status & 2:
+        if status & 2 or n_isects > 0x7FFFFFFF:
             raise RuntimeError(f"isect: {n_isects} intersections do not fit int32 flatten ids / offsets")
         _isect_count_hint[key] = n_isects
         return n_isects

@@ -35,8 +35,8 @@ __device__ __forceinline__ float angle_difference(float a, float b) {
     return d < -180.f ? d + 360.f : d;
 }
 
-// Copies row g of a [*, n] float table to dst (one thread per row): 16-byte loads when the rows
-// are 16-byte aligned.
+// Copies row g of a [*, n] float table to dst (one thread per row), zero-padded to a multiple of
+// four floats: 16-byte loads when the rows are 16-byte aligned.
 __device__ __forceinline__ void stage_row(float *__restrict__ dst, const float *__restrict__ table,
                                           size_t g, uint32_t n, bool vec) {
     const float *src = table + g * n;
@@ -44,7 +44,26 @@ __device__ __forceinline__ void stage_row(float *__restrict__ dst, const float *
         for (uint32_t k = 0; k < n; k += 4)
             *reinterpret_cast<float4 *>(dst + k) = __ldg(reinterpret_cast<const float4 *>(src + k));
     } else {
-        for (uint32_t k = 0; k < n; ++k) dst[k] = __ldg(src + k);
+        const uint32_t npad = (n + 3u) & ~3u;
+        for (uint32_t k = 0; k < npad; ++k) dst[k] = k < n ? __ldg(src + k) : 0.f;
+    }
+}
+
+// acc[0 .. 4 * ceil(n / 4)) += row * w for a staged (zero-padded, 16-byte aligned) row: one
+// 16-byte shared-memory load and one uniform test per four channels.
+template <int CDIM>
+__device__ __forceinline__ void axpy_staged(float (&acc)[CDIM], const float *__restrict__ row, uint32_t n,
+                                            float w) {
+    const float4 *r4 = reinterpret_cast<const float4 *>(row);
+#pragma unroll
+    for (int k4 = 0; k4 < CDIM / 4; ++k4) {
+        if ((uint32_t)(4 * k4) < n) {
+            const float4 v = r4[k4];
+            acc[4 * k4 + 0] += v.x * w;
+            acc[4 * k4 + 1] += v.y * w;
+            acc[4 * k4 + 2] += v.z * w;
+            acc[4 * k4 + 3] += v.w * w;
+        }
     }
 }
 
@@ -131,10 +150,14 @@ __global__ void rasterize_to_pixels_fwd_kernel(
             const float next_T = T * (1.f - alpha);
             if (next_T <= kTStop) { done = true; break; }
             const float vis = alpha * T;
-            const float *c_ptr = stage_colors ? sCol + t * cpad : colors + (size_t)sId[t] * channels;
+            if (stage_colors) {
+                axpy_staged<CDIM>(pix_out, sCol + t * cpad, channels, vis);
+            } else {
+                const float *c_ptr = colors + (size_t)sId[t] * channels;
 #pragma unroll
-            for (int k = 0; k < CDIM; ++k)
-                if ((uint32_t)k < channels) pix_out[k] += c_ptr[k] * vis;
+                for (int k = 0; k < CDIM; ++k)
+                    if ((uint32_t)k < channels) pix_out[k] += __ldg(c_ptr + k) * vis;
+            }
             cur_idx = batch_start + t;
             T = next_T;
         }
@@ -241,11 +264,21 @@ __global__ void rasterize_to_points_fwd_kernel(
             if (next_T <= kTStop) { done = true; break; }
             const float vis = alpha * T;
             const float4 Cc = sC[t];
-            const float *c_ptr = stage_features ? sFeat + t * fpad : colors + (size_t)sId[t] * fstride;
+            if (stage_features) {
+                // the zero padding of a staged row adds nothing to the channels behind it
+                axpy_staged<CDIM>(pix_out, sFeat + t * fpad, fstride, vis);
+                if (ranges) {
 #pragma unroll
-            for (int k = 0; k < CDIM; ++k) {
-                if ((uint32_t)k < fstride) pix_out[k] += c_ptr[k] * vis;
-                else if ((uint32_t)k < channels) pix_out[k] += Cc.w * vis;
+                    for (int k = 0; k < CDIM; ++k)
+                        if ((uint32_t)k == fstride) pix_out[k] += Cc.w * vis;
+                }
+            } else {
+                const float *c_ptr = colors + (size_t)sId[t] * fstride;
+#pragma unroll
+                for (int k = 0; k < CDIM; ++k) {
+                    if ((uint32_t)k < fstride) pix_out[k] += __ldg(c_ptr + k) * vis;
+                    else if ((uint32_t)k < channels) pix_out[k] += Cc.w * vis;
+                }
             }
             const float dterm = Cc.y * dx + Cc.z * dy + Cc.x * roll;
             depth_extra += dterm * vis;

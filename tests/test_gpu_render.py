@@ -141,8 +141,10 @@ def test_lidar_channel_chunking_and_options():
     # chunks agree with each other: the range channel of a one-chunk render of the first 31 features
     cfg31 = dict(cfg, lidar_features=cfg["lidar_features"][..., :31].contiguous())
     c31, a31, _, _ = splatad_b200.lidar_rasterization(**_to_gpu(cfg31), **kw)
-    assert torch.equal(c31[..., :31], out_c[..., :31]) and torch.equal(c31[..., -1], out_c[..., -1])
-    assert torch.equal(a31, out_a)
+    # (same decisions and products; the range is accumulated from its own array in one case and as
+    # the last feature column in the other, which the compiler may contract differently)
+    assert torch.equal(c31[..., :31], out_c[..., :31]) and torch.equal(a31, out_a)
+    assert_close("range of chunked vs single render", n(c31[..., -1]), n(out_c[..., -1]), 1e-6, 1e-7)
 
 
 @pytest.mark.parametrize("packed", [True, False])

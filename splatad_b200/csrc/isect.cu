@@ -26,9 +26,9 @@ namespace splatad {
 
 constexpr int kSortThreads = 256;
 constexpr int kSortWarps = kSortThreads / 32;
-constexpr int kItemsPerLane = 16;
-constexpr int kWarpItems = 32 * kItemsPerLane;           // 512
-constexpr int kTileItems = kSortWarps * kWarpItems;      // 4096
+constexpr int kItemsPerLane = 8;
+constexpr int kWarpItems = 32 * kItemsPerLane;           // 256
+constexpr int kTileItems = kSortWarps * kWarpItems;      // 2048
 constexpr int kSortGrid = 4 * kNumSMs;                   // 592 persistent blocks
 constexpr int kRadixBins = 256;
 static_assert(kSortThreads == kRadixBins, "one thread per radix bin");
@@ -214,7 +214,7 @@ isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ til
 
 // ---------------------------------------------------------------------------------------
 // Radix sort passes (stable LSD, up to 8 bits per pass) on (uint32 key, uint32 value) pairs.
-// Each of the kSortGrid blocks owns a contiguous run of 4096-item tiles.
+// Each of the kSortGrid blocks owns a contiguous run of 2048-item tiles.
 //   upsweep:   per-block digit histogram            -> hist[digit][block]
 //   rowscan:   exclusive scan of each digit's row   -> hist (in place), digit_totals
 //   downsweep: stable rank + scatter (through shared memory so global writes are runs)

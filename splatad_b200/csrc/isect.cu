@@ -103,6 +103,16 @@ struct LidarGrid {
     uint32_t n_tiles_azim, n_tiles_elev;
 };
 
+// Number of leading entries of the ascending array b[0 .. n) that are < v.
+__device__ __forceinline__ int32_t lower_bound_f(const float *__restrict__ b, int32_t n, float v) {
+    int32_t lo = 0, hi = n;
+    while (lo < hi) {
+        const int32_t m = (lo + hi) >> 1;
+        if (b[m] < v) lo = m + 1; else hi = m;
+    }
+    return lo;
+}
+
 __device__ __forceinline__ Rect lidar_rect(float2 mean, float2 radius, const LidarGrid &g) {
     const float el_lo = mean.y - radius.y, el_hi = mean.y + radius.y;
     const float azim = mean.x - g.min_azim;
@@ -116,12 +126,13 @@ __device__ __forceinline__ Rect lidar_rect(float2 mean, float2 radius, const Lid
     Rect r;
     r.x0 = (int32_t)floorf(t_lo);
     r.x1 = (int32_t)ceilf(t_hi);
+    // first boundary not below the lower edge (minus one), first boundary not below the upper
+    // edge: the reference walks the ascending boundaries one by one, a bisection finds the same
+    // indices (a NaN edge compares false everywhere and leaves both at 0, as there)
     const int32_t ne = (int32_t)g.n_tiles_elev;
-    int32_t i = 0;
-    while (i <= ne && g.elev_boundaries[i] < el_lo) ++i;
+    const int32_t i = lower_bound_f(g.elev_boundaries, ne + 1, el_lo);
     r.y0 = max(i - 1, 0);
-    while (i <= ne && g.elev_boundaries[i] < el_hi) ++i;
-    r.y1 = min(i, ne);
+    r.y1 = min(max(i, lower_bound_f(g.elev_boundaries, ne + 1, el_hi)), ne);
     return r;
 }
 

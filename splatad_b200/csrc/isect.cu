@@ -778,11 +778,15 @@ struct SplitArgs {
     uint32_t row_width, stride;  // tiles per row, row_width + 1
     uint32_t tile_n_bits, col_bits, wrap;
     // workspace
-    uint32_t *ha_cnt, *ha_out;   // [units_a][rows]: records / outputs per (entry block, row)
+    uint32_t *ha_cnt, *ha_out;   // [blocks][rows]: records / outputs per (1024 entries, row); scanned
+    uint32_t *hw_cnt, *hw_out;   // [blocks][warps][rows]: the same per warp (128 entries), as counted
     uint32_t *row_rec, *row_out, *row_unit;   // [rows + 1] exclusive starts
     uint4 *rec;                  // records {run start | width << 16, output offset, flatten index,
                                  // depth bits}, row bucket after row bucket
-    uint32_t *hb;                // [units_b][stride] outputs per (unit, column)
+    uint32_t *hb;                // [units_b][stride] outputs per (unit, column); after the scan:
+                                 // outputs of the column in earlier units of the row
+    uint32_t *hw;                // [units_b][warps][stride] outputs per (unit, warp, column)
+    uint32_t *hb_first;          // [units_b][warps] record owning the first output of the warp
     uint32_t *slot_tot, *slot_base;           // [rows * stride]
 };
 
@@ -868,9 +872,15 @@ rowsplit_count_kernel(SplitArgs a) {
     __syncthreads();
     uint32_t cnt, out;
     split_rows_of_warp(a, first + warp * kSplitWarpEntries, n_entries, lane, cnt, out);
-    if (lane < a.rows && cnt) {
-        atomicAdd(&s_cnt[lane], cnt);
-        atomicAdd(&s_out[lane], out);
+    if (lane < a.rows) {
+        // kept per warp too, so that the scatter does not have to count again
+        const uint32_t wu = blockIdx.x * kSplitWarps + warp;
+        a.hw_cnt[wu * a.rows + lane] = cnt;
+        a.hw_out[wu * a.rows + lane] = out;
+        if (cnt) {
+            atomicAdd(&s_cnt[lane], cnt);
+            atomicAdd(&s_out[lane], out);
+        }
     }
     __syncthreads();
     if (threadIdx.x < a.rows) {
@@ -941,31 +951,27 @@ rowsplit_scan_kernel(SplitArgs a, unsigned long long *__restrict__ ticket) {
 
 __global__ void __launch_bounds__(kSplitWarps * 32)
 rowsplit_scatter_kernel(SplitArgs a) {
-    __shared__ uint32_t w_cnt[kSplitWarps][kSplitMaxRows], w_out[kSplitWarps][kSplitMaxRows];
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t lt = (1u << lane) - 1u;
     if (split_overflow(a)) return;
     const uint32_t n_entries = (uint32_t)(*a.n_entries_ptr);
-    const uint32_t first = blockIdx.x * kSplitEntries;
+    const uint32_t wu = blockIdx.x * kSplitWarps + warp;
+    const uint32_t first = wu * kSplitWarpEntries;
     if (first >= n_entries) return;
     const uint32_t cap = (uint32_t)(a.capacity < 0x7fffffffll ? a.capacity : 0x7fffffffll);
-    uint32_t cnt, out;
-    split_rows_of_warp(a, first + warp * kSplitWarpEntries, n_entries, lane, cnt, out);
-    w_cnt[warp][lane] = cnt;
-    w_out[warp][lane] = out;
-    __syncthreads();
-    // lane r: where this warp's records / outputs of row r start
+    // lane r: where this warp's records / outputs of row r start: row start, earlier blocks
+    // (scanned), earlier warps of this block (as counted)
     uint32_t rec_at = 0, out_at = 0;
     if (lane < a.rows) {
         rec_at = a.row_rec[lane] + a.ha_cnt[blockIdx.x * a.rows + lane];
         out_at = a.row_out[lane] + a.ha_out[blockIdx.x * a.rows + lane];
-        for (uint32_t w2 = 0; w2 < warp; ++w2) {
-            rec_at += w_cnt[w2][lane];
-            out_at += w_out[w2][lane];
+        for (uint32_t w2 = blockIdx.x * kSplitWarps; w2 < wu; ++w2) {
+            rec_at += a.hw_cnt[w2 * a.rows + lane];
+            out_at += a.hw_out[w2 * a.rows + lane];
         }
     }
     for (uint32_t win = 0; win < kSplitWarpEntries / 32; ++win) {
-        const uint32_t base = first + warp * kSplitWarpEntries + win * 32;
+        const uint32_t base = first + win * 32;
         if (base >= n_entries) break;
         const uint32_t p = base + lane;
         const SplitEntry e = split_load_entry(a, p, n_entries);
@@ -1105,20 +1111,31 @@ __device__ __forceinline__ void warp_prefix_inplace(int32_t *d, uint32_t n, uint
 
 __global__ void __launch_bounds__(kSplitWarps * 32)
 colsplit_count_kernel(SplitArgs a) {
-    extern __shared__ int32_t s_d[];   // [stride]
+    extern __shared__ int32_t s_d[];   // [kSplitWarps][stride]
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (split_overflow(a)) return;
     const SplitUnit u = split_unit(a, blockIdx.x, lane);
     if (!u.live) return;
-    for (uint32_t i = tid; i < a.stride; i += blockDim.x) s_d[i] = 0;
-    __syncthreads();
+    int32_t *wd = s_d + warp * a.stride;
+    for (uint32_t i = lane; i < a.stride; i += 32) wd[i] = 0;
+    __syncwarp();
     const uint32_t q_lo = min(u.q_hi, u.q_lo + warp * kSplitSub);
-    split_count_cols(s_d, a, q_lo, min(u.q_hi, q_lo + kSplitSub), u.n_rec, u.n_out, lane);
+    const uint32_t first = split_count_cols(wd, a, q_lo, min(u.q_hi, q_lo + kSplitSub), u.n_rec, u.n_out, lane);
+    __syncwarp();
+    warp_prefix_inplace(wd, a.stride, lane);
     __syncthreads();
-    if (warp == 0) warp_prefix_inplace(s_d, a.stride, lane);
-    __syncthreads();
+    // per warp (so that the scatter does not have to count again) and per unit (to be scanned)
+    const size_t piece = (size_t)blockIdx.x * kSplitWarps + warp;
+    uint32_t *prow = a.hw + piece * a.stride;
+    for (uint32_t i = lane; i < a.stride; i += 32) prow[i] = (uint32_t)wd[i];
+    if (lane == 0) a.hb_first[piece] = first;
     uint32_t *row = a.hb + (size_t)blockIdx.x * a.stride;
-    for (uint32_t i = tid; i < a.stride; i += blockDim.x) row[i] = (uint32_t)s_d[i];
+    for (uint32_t i = tid; i < a.stride; i += blockDim.x) {
+        uint32_t tot = 0;
+#pragma unroll
+        for (uint32_t w2 = 0; w2 < kSplitWarps; ++w2) tot += (uint32_t)s_d[w2 * a.stride + i];
+        row[i] = tot;
+    }
 }
 
 // Block r: exclusive scan over the units of grid row r for every column (in place); the column
@@ -1249,23 +1266,20 @@ colsplit_scatter_kernel(SplitArgs a, int64_t *__restrict__ isect_ids, int32_t *_
     int32_t *wd = s_tab + warp * a.stride;
     uint32_t *hist = reinterpret_cast<uint32_t *>(wd);
 
-    // outputs per column of this warp's piece
-    for (uint32_t i = lane; i < a.stride; i += 32) wd[i] = 0;
-    __syncwarp();
-    const uint32_t first_rec = split_count_cols(wd, a, q_lo, q_hi, u.n_rec, u.n_out, lane);
-    __syncwarp();
-    warp_prefix_inplace(wd, a.stride, lane);
-    __syncthreads();
-    // local start of every (warp, column) inside the unit, and the shift to global positions
+    // Local start of every (warp, column) inside the unit, and the shift to global positions: the
+    // per-warp counts come from the count kernel, the unit's global starts from the scans.
+    const size_t piece0 = (size_t)blockIdx.x * kSplitWarps;
     const uint32_t *hrow = a.hb + (size_t)blockIdx.x * a.stride;
     const uint32_t *sbase = a.slot_base + u.row * a.stride;
     uint32_t carry = 0;
     for (uint32_t c0 = 0; c0 < a.stride; c0 += blockDim.x) {
         const uint32_t c = c0 + tid;
-        uint32_t tot = 0;
-        if (c < a.stride)
+        uint32_t cnt[kSplitWarps], tot = 0;
 #pragma unroll
-            for (uint32_t w2 = 0; w2 < kSplitWarps; ++w2) tot += (uint32_t)s_tab[w2 * a.stride + c];
+        for (uint32_t w2 = 0; w2 < kSplitWarps; ++w2) {
+            cnt[w2] = c < a.stride ? a.hw[(piece0 + w2) * a.stride + c] : 0u;
+            tot += cnt[w2];
+        }
         uint32_t chunk_total;
         const uint32_t ex = block_excl_scan(tot, wt, chunk_total);
         if (c < a.stride) {
@@ -1273,13 +1287,13 @@ colsplit_scatter_kernel(SplitArgs a, int64_t *__restrict__ isect_ids, int32_t *_
             s_shift[c] = (int32_t)(hrow[c] + sbase[c] - run);
 #pragma unroll
             for (uint32_t w2 = 0; w2 < kSplitWarps; ++w2) {
-                const uint32_t v = (uint32_t)s_tab[w2 * a.stride + c];
                 s_tab[w2 * a.stride + c] = (int32_t)run;
-                run += v;
+                run += cnt[w2];
             }
         }
         carry += chunk_total;
     }
+    const uint32_t first_rec = a.hb_first[piece0 + warp];
     __syncthreads();
 
     // walk the piece, 32 outputs at a time
@@ -1396,6 +1410,7 @@ struct PlanWs {
     uint32_t *keyA, *valA, *keyB, *valB;
     uint32_t *eoff;
     uint32_t *ha_cnt, *ha_out;   // row split: per (block of entries, grid row)
+    uint32_t *hw_cnt, *hw_out;   // row split: per (warp of a block, grid row)
     uint32_t *rect_xw, *rect_yh; // row split: packed rectangles by flatten index
     size_t bytes;
 };
@@ -1418,6 +1433,8 @@ static PlanWs carve_plan(void *ws, uint64_t total) {
     const size_t n_ha = (size_t)((total + 1023) / 1024) * 32;   // kSplitEntries, kSplitMaxRows
     p.ha_cnt = (uint32_t *)take(sizeof(uint32_t) * n_ha);
     p.ha_out = (uint32_t *)take(sizeof(uint32_t) * n_ha);
+    p.hw_cnt = (uint32_t *)take(sizeof(uint32_t) * n_ha * 8);    // kSplitWarps
+    p.hw_out = (uint32_t *)take(sizeof(uint32_t) * n_ha * 8);
     p.rect_xw = (uint32_t *)take(sizeof(uint32_t) * total);
     p.rect_yh = (uint32_t *)take(sizeof(uint32_t) * total);
     p.bytes = off;
@@ -1445,7 +1462,7 @@ static FillWs carve_fill(void *ws, uint64_t cap) {
 struct SplitWs {
     uint32_t *row_rec, *row_out, *row_unit;
     uint4 *rec;
-    uint32_t *hb, *slot_tot, *slot_base;
+    uint32_t *hb, *hw, *hb_first, *slot_tot, *slot_base;
     uint32_t units_b_cap;
     size_t bytes;
 };
@@ -1463,6 +1480,8 @@ static SplitWs carve_split(void *ws, uint64_t cap, uint32_t rows, uint32_t strid
     // every grid row rounds its outputs up to whole units
     w.units_b_cap = (uint32_t)((cap + kSplitUnit - 1) / kSplitUnit) + rows;
     w.hb = (uint32_t *)take(sizeof(uint32_t) * (size_t)w.units_b_cap * stride);
+    w.hw = (uint32_t *)take(sizeof(uint32_t) * (size_t)w.units_b_cap * kSplitWarps * stride);
+    w.hb_first = (uint32_t *)take(sizeof(uint32_t) * (size_t)w.units_b_cap * kSplitWarps);
     w.slot_tot = (uint32_t *)take(sizeof(uint32_t) * kSplitMaxSlots);
     w.slot_base = (uint32_t *)take(sizeof(uint32_t) * kSplitMaxSlots);
     w.bytes = off;
@@ -1653,11 +1672,13 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
                     fill_workspace_bytes, w.bytes);
         a.ha_cnt = p.ha_cnt;
         a.ha_out = p.ha_out;
+        a.hw_cnt = p.hw_cnt;
+        a.hw_out = p.hw_out;
         a.row_rec = w.row_rec; a.row_out = w.row_out; a.row_unit = w.row_unit;
         a.rec = w.rec;
-        a.hb = w.hb; a.slot_tot = w.slot_tot; a.slot_base = w.slot_base;
+        a.hb = w.hb; a.hw = w.hw; a.hb_first = w.hb_first; a.slot_tot = w.slot_tot; a.slot_base = w.slot_base;
         const uint32_t units_a = div_up(g.total, kSplitEntries);
-        const size_t smem_count = sizeof(int32_t) * a.stride;
+        const size_t smem_count = sizeof(int32_t) * kSplitWarps * a.stride;
         const size_t smem_scatter = sizeof(int32_t) * ((kSplitWarps + 1) * a.stride + 2 * kSplitUnit) +
                                     sizeof(uint16_t) * kSplitUnit;
         if (smem_scatter > 48 * 1024)   // above the default dynamic shared memory limit

@@ -283,3 +283,41 @@ def test_repeated_camera_frames():
     assert torch.equal(first[0], second[0]) and torch.equal(first[1], second[1])
     for key in ("isect_ids", "flatten_ids", "isect_offsets", "tiles_per_gauss"):
         assert torch.equal(first[2][key], second[2][key]), key
+
+
+def test_config2_full_size_properties():
+    """The headline frame (1 M Gaussians, 15.3 M intersections) is too large for the CPU oracle, so it
+    is checked through properties that do not depend on size - and by building its tile lists twice,
+    with the two independent implementations the library has (row / column split for small tile
+    grids, radix split otherwise), which must agree bit for bit."""
+    import splatad_b200
+    from splatad_b200 import ops, scenes
+    cfg = scenes.config2()
+    g = _to_gpu(cfg)
+    feats, alphas, asum, m = splatad_b200.lidar_rasterization(**g)
+    ids, flat, tpg, offs = m["isect_ids"], m["flatten_ids"], m["tiles_per_gauss"], m["isect_offsets"]
+    n_isects = ids.numel()
+    assert n_isects > 15_000_000 and flat.numel() == n_isects
+    # counts, order, offsets
+    assert int(tpg.sum()) == n_isects
+    assert bool((ids[1:] >= ids[:-1]).all()), "isect ids are not sorted"
+    assert torch.equal(offs, ops.isect_offset_encode(ids.clone(), 1, m["tile_grid_width"], m["tile_grid_height"]))
+    # every Gaussian appears once per tile it touches
+    assert torch.equal(torch.bincount(flat.long(), minlength=tpg.numel()), tpg.reshape(-1).long())
+    # depth bits of the ids are the Gaussians' depths; the tile of an id is the tile whose range holds it
+    assert torch.equal((ids & 0xFFFFFFFF).to(torch.int32), m["depths"].reshape(-1)[flat.long()].view(torch.int32))
+    tile_of = torch.bucketize(torch.arange(n_isects, device=DEV), offs.reshape(-1).long(), right=True) - 1
+    assert torch.equal(ids >> 32, tile_of)
+    # the same lists from the radix split: the packed layout with 64 (empty but one) sensors is
+    # outside the row / column split's reach, and sensor 0 leaves the ids unchanged
+    N = cfg["means"].shape[0]
+    zeros = torch.zeros(N, dtype=torch.int64, device=DEV)
+    _, ids2, flat2 = ops.isect_lidar_tiles(
+        m["means2d"][0], m["radii"][0], m["depths"][0], g["tile_elevation_boundaries"],
+        cfg["azimuth_resolution"] * cfg["tile_width"], cfg["min_azimuth"], packed=True, n_cameras=64,
+        camera_ids=zeros, gaussian_ids=torch.arange(N, device=DEV))
+    assert torch.equal(ids2, ids) and torch.equal(flat2, flat)
+    # render: repeatable, alphas in range
+    again = splatad_b200.lidar_rasterization(**g)
+    assert torch.equal(again[0], feats) and torch.equal(again[1], alphas) and torch.equal(again[2], asum)
+    assert float(alphas.min()) >= 0.0 and float(alphas.max()) <= 1.0 and bool(torch.isfinite(feats).all())

@@ -336,11 +336,14 @@ def run_ours(args):
             "rasterize_to_points_fwd_kernel": POINTS_PER_FRAME * (16 + 4 * 21),
             "isect_count_kernel": 1_000_000 * 20,
         }.get(dom_name, None)
+        # DRAM bytes (read + written) per launch of the same kernel on this workload from the ncu
+        # capture summarised under profiles/
+        traffic = {"colsplit_scatter_kernel": 229_227_008}.get(dom_name)
         roofline = None
         if bytes_per_launch is not None:
             achieved = bytes_per_launch / (dom_ms / dom_cnt * 1e-3) / 1e9
             roofline = {"kernel": dom_name, "bound": "hbm", "achieved": round(achieved, 1), "peak": peak,
-                        "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": None,
+                        "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": traffic,
                         "peak_source": f"of {peak_src}", "launches_per_step": dom_cnt,
                         "ms_per_launch": round(dom_ms / dom_cnt, 4),
                         "algorithmic_bytes_per_launch": int(bytes_per_launch)}

@@ -180,7 +180,7 @@ __device__ __forceinline__ void stage_boundaries(GridArgs<kLidar> &a, float *sb)
 // tiles_per_gauss[idx] for every (sensor, Gaussian) / packed row. With rect_xw / rect_yh the
 // rectangle is also stored, packed into two words per element (x0 | width << 16, first grid row |
 // height << 16 with grid row = sensor * tile rows + y; 16-bit fields, used only when
-// sensors * tiles <= 1024) for the row / column split, and the total is added to *n_isects.
+// the geometry is within its limits) for the row / column split, and the total is added to *n_isects.
 template <bool kLidar>
 __global__ void __launch_bounds__(kThreads)
 isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ tiles_per_gauss,
@@ -733,8 +733,9 @@ emit_kernel(GridArgs<kLidar> a, EmitArgs e, const uint32_t *__restrict__ eoff,
 }
 
 // ---------------------------------------------------------------------------------------
-// Row / column split (sensors * tile rows <= 32 and sensors * tiles <= 1024, e.g. one lidar
-// with 57 x 16 tiles): builds the per-tile lists without ever writing the emission out.
+// Row / column split (at most 128 tile rows and 16384 tiles over all sensors, rows of at most
+// 1024 tiles: a lidar with 57 x 16 tiles, a 1920 x 1080 camera with 120 x 68): builds the
+// per-tile lists without ever writing the emission out.
 //
 // A rectangle is a stack of `h` row runs, each `w` tiles wide. The tile lists of grid row r are
 // made of the row runs of the rectangles that cover r, in depth order, so the split is done in
@@ -754,9 +755,10 @@ emit_kernel(GridArgs<kLidar> a, EmitArgs e, const uint32_t *__restrict__ eoff,
 // Positions are exclusive sums over (earlier tiles, earlier units, earlier warps), all of
 // them plain scans: the result is the same for any scheduling.
 // ---------------------------------------------------------------------------------------
-constexpr uint32_t kSplitMaxRows = 32;                     // one lane per grid row
-constexpr uint32_t kSplitMaxTiles = 1024;
-constexpr uint32_t kSplitMaxSlots = 2048;                  // rows * (row_width + 1)
+constexpr uint32_t kSplitMaxRows = 128;                    // grid rows over all sensors
+constexpr uint32_t kSplitMaxWidth = 1024;                  // tiles per row
+constexpr uint32_t kSplitMaxTiles = 16384;
+constexpr uint32_t kSplitMaxSlots = kSplitMaxTiles + kSplitMaxRows;   // rows * (row_width + 1)
 constexpr uint32_t kSplitWarps = 8;
 constexpr uint32_t kSplitWarpEntries = 128;                // entries per warp in step A
 constexpr uint32_t kSplitEntries = kSplitWarps * kSplitWarpEntries;   // entries per block
@@ -827,23 +829,25 @@ __device__ __forceinline__ SplitEntry split_load_entry(const SplitArgs &a, uint3
     return e;
 }
 
-// Records and outputs per grid row of the kSplitWarpEntries entries starting at `first`; lane r
-// holds row r.
+// Records and outputs per grid row of the kSplitWarpEntries entries starting at `first`, for the
+// 32 rows starting at `row_lo`; lane l holds row row_lo + l.
 __device__ __forceinline__ void split_rows_of_warp(const SplitArgs &a, uint32_t first, uint32_t n_entries,
-                                                   uint32_t lane, uint32_t &cnt, uint32_t &out) {
+                                                   uint32_t lane, uint32_t row_lo, uint32_t &cnt,
+                                                   uint32_t &out) {
     cnt = 0;
     out = 0;
+    const uint32_t row_hi = min(a.rows, row_lo + 32u);
     for (uint32_t win = 0; win < kSplitWarpEntries / 32; ++win) {
         const uint32_t base = first + win * 32;
         if (base >= n_entries) break;
         const SplitEntry e = split_load_entry(a, base + lane, n_entries);
         const uint32_t w = e.xw >> 16;
-        for (uint32_t r = 0; r < a.rows; ++r) {
+        for (uint32_t r = row_lo; r < row_hi; ++r) {
             const bool hit = e.valid && (r - e.row0) < e.h;
             const uint32_t bal = __ballot_sync(0xffffffffu, hit);
             if (bal == 0u) continue;
             const uint32_t s = __reduce_add_sync(0xffffffffu, hit ? w : 0u);
-            if (lane == r) {
+            if (row_lo + lane == r) {
                 cnt += __popc(bal);
                 out += s;
             }
@@ -870,16 +874,19 @@ rowsplit_count_kernel(SplitArgs a) {
         s_out[threadIdx.x] = 0;
     }
     __syncthreads();
-    uint32_t cnt, out;
-    split_rows_of_warp(a, first + warp * kSplitWarpEntries, n_entries, lane, cnt, out);
-    if (lane < a.rows) {
-        // kept per warp too, so that the scatter does not have to count again
-        const uint32_t wu = blockIdx.x * kSplitWarps + warp;
-        a.hw_cnt[wu * a.rows + lane] = cnt;
-        a.hw_out[wu * a.rows + lane] = out;
-        if (cnt) {
-            atomicAdd(&s_cnt[lane], cnt);
-            atomicAdd(&s_out[lane], out);
+    const uint32_t wu = blockIdx.x * kSplitWarps + warp;
+    for (uint32_t row_lo = 0; row_lo < a.rows; row_lo += 32) {
+        uint32_t cnt, out;
+        split_rows_of_warp(a, first + warp * kSplitWarpEntries, n_entries, lane, row_lo, cnt, out);
+        const uint32_t r = row_lo + lane;
+        if (r < a.rows) {
+            // kept per warp too, so that the scatter does not have to count again
+            a.hw_cnt[wu * a.rows + r] = cnt;
+            a.hw_out[wu * a.rows + r] = out;
+            if (cnt) {
+                atomicAdd(&s_cnt[r], cnt);
+                atomicAdd(&s_out[r], out);
+            }
         }
     }
     __syncthreads();
@@ -923,32 +930,31 @@ rowsplit_scan_kernel(SplitArgs a, unsigned long long *__restrict__ ticket) {
         s_last = atomicAdd(ticket, 1ull) + 1ull == (unsigned long long)gridDim.x;
     }
     __syncthreads();
-    if (!s_last || tid >= 32) return;
+    if (!s_last) return;
     __threadfence();
+    // exclusive scans over the rows (rows <= 128 <= blockDim)
     const uint32_t vc = tid < a.rows ? a.row_rec[kSplitMaxRows + 1 + tid] : 0u;
     const uint32_t vo = tid < a.rows ? a.row_out[kSplitMaxRows + 1 + tid] : 0u;
     const uint32_t vu = (vo + kSplitUnit - 1) / kSplitUnit;
-    uint32_t ic = vc, io = vo, iu = vu;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-        const uint32_t oc = __shfl_up_sync(0xffffffffu, ic, off);
-        const uint32_t oo = __shfl_up_sync(0xffffffffu, io, off);
-        const uint32_t ou = __shfl_up_sync(0xffffffffu, iu, off);
-        if (tid >= (uint32_t)off) { ic += oc; io += oo; iu += ou; }
-    }
+    uint32_t tc, to, tu;
+    const uint32_t ec = block_excl_scan(vc, wt, tc);
+    const uint32_t eo = block_excl_scan(vo, wt, to);
+    const uint32_t eu = block_excl_scan(vu, wt, tu);
     if (tid < a.rows) {
-        a.row_rec[tid] = ic - vc;
-        a.row_out[tid] = io - vo;
-        a.row_unit[tid] = iu - vu;
+        a.row_rec[tid] = ec;
+        a.row_out[tid] = eo;
+        a.row_unit[tid] = eu;
     }
-    if (tid == 31) {
-        a.row_rec[a.rows] = ic;
-        a.row_out[a.rows] = io;
-        a.row_unit[a.rows] = iu;
+    if (tid == 0) {
+        a.row_rec[a.rows] = tc;
+        a.row_out[a.rows] = to;
+        a.row_unit[a.rows] = tu;
         *ticket = 0ull;
     }
 }
 
+// kOneGroup: at most 32 grid rows, so the loop over groups of 32 rows runs once from row 0.
+template <bool kOneGroup>
 __global__ void __launch_bounds__(kSplitWarps * 32)
 rowsplit_scatter_kernel(SplitArgs a) {
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -959,56 +965,60 @@ rowsplit_scatter_kernel(SplitArgs a) {
     const uint32_t first = wu * kSplitWarpEntries;
     if (first >= n_entries) return;
     const uint32_t cap = (uint32_t)(a.capacity < 0x7fffffffll ? a.capacity : 0x7fffffffll);
-    // lane r: where this warp's records / outputs of row r start: row start, earlier blocks
-    // (scanned), earlier warps of this block (as counted)
-    uint32_t rec_at = 0, out_at = 0;
-    if (lane < a.rows) {
-        rec_at = a.row_rec[lane] + a.ha_cnt[blockIdx.x * a.rows + lane];
-        out_at = a.row_out[lane] + a.ha_out[blockIdx.x * a.rows + lane];
-        for (uint32_t w2 = blockIdx.x * kSplitWarps; w2 < wu; ++w2) {
-            rec_at += a.hw_cnt[w2 * a.rows + lane];
-            out_at += a.hw_out[w2 * a.rows + lane];
-        }
-    }
-    for (uint32_t win = 0; win < kSplitWarpEntries / 32; ++win) {
-        const uint32_t base = first + win * 32;
-        if (base >= n_entries) break;
-        const uint32_t p = base + lane;
-        const SplitEntry e = split_load_entry(a, p, n_entries);
-        const uint32_t w = e.xw >> 16;
-        uint32_t xs = 0, idx = 0, depth = 0;
-        if (e.valid) {
-            int32_t x0 = (int32_t)(int16_t)(e.xw & 0xffffu);
-            if (a.wrap) {
-                x0 %= (int32_t)a.row_width;
-                if (x0 < 0) x0 += (int32_t)a.row_width;
+    for (uint32_t row_lo = 0; row_lo < (kOneGroup ? 1u : a.rows); row_lo += 32) {
+        // lane l: where this warp's records / outputs of row row_lo + l start: row start, earlier
+        // blocks (scanned), earlier warps of this block (as counted)
+        const uint32_t row_hi = min(a.rows, row_lo + 32u);
+        const uint32_t my_row = row_lo + lane;
+        uint32_t rec_at = 0, out_at = 0;
+        if (my_row < a.rows) {
+            rec_at = a.row_rec[my_row] + a.ha_cnt[blockIdx.x * a.rows + my_row];
+            out_at = a.row_out[my_row] + a.ha_out[blockIdx.x * a.rows + my_row];
+            for (uint32_t w2 = blockIdx.x * kSplitWarps; w2 < wu; ++w2) {
+                rec_at += a.hw_cnt[w2 * a.rows + my_row];
+                out_at += a.hw_out[w2 * a.rows + my_row];
             }
-            xs = (uint32_t)x0;
-            idx = e.idx;
-            depth = __ldg(a.depth_key + p);
         }
-        for (uint32_t r = 0; r < a.rows; ++r) {
-            const bool hit = e.valid && (r - e.row0) < e.h;
-            const uint32_t bal = __ballot_sync(0xffffffffu, hit);
-            if (bal == 0u) continue;
-            // exclusive prefix of the widths of the hit lanes
-            const uint32_t v = hit ? w : 0u;
-            uint32_t inc = v;
+        for (uint32_t win = 0; win < kSplitWarpEntries / 32; ++win) {
+            const uint32_t base = first + win * 32;
+            if (base >= n_entries) break;
+            const uint32_t p = base + lane;
+            const SplitEntry e = split_load_entry(a, p, n_entries);
+            const uint32_t w = e.xw >> 16;
+            uint32_t xs = 0, idx = 0, depth = 0;
+            if (e.valid) {
+                int32_t x0 = (int32_t)(int16_t)(e.xw & 0xffffu);
+                if (a.wrap) {
+                    x0 %= (int32_t)a.row_width;
+                    if (x0 < 0) x0 += (int32_t)a.row_width;
+                }
+                xs = (uint32_t)x0;
+                idx = e.idx;
+                depth = __ldg(a.depth_key + p);
+            }
+            for (uint32_t r = row_lo; r < row_hi; ++r) {
+                const bool hit = e.valid && (r - e.row0) < e.h;
+                const uint32_t bal = __ballot_sync(0xffffffffu, hit);
+                if (bal == 0u) continue;
+                // exclusive prefix of the widths of the hit lanes
+                const uint32_t v = hit ? w : 0u;
+                uint32_t inc = v;
 #pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const uint32_t o = __shfl_up_sync(0xffffffffu, inc, off);
-                if (lane >= (uint32_t)off) inc += o;
-            }
-            const uint32_t total = __shfl_sync(0xffffffffu, inc, 31);
-            const uint32_t rbase = __shfl_sync(0xffffffffu, rec_at, r);
-            const uint32_t obase = __shfl_sync(0xffffffffu, out_at, r);
-            if (hit) {
-                const uint32_t pos = rbase + __popc(bal & lt);
-                if (pos < cap) a.rec[pos] = make_uint4(xs | (w << 16), obase + inc - v, idx, depth);
-            }
-            if (lane == r) {
-                rec_at += __popc(bal);
-                out_at += total;
+                for (int off = 1; off < 32; off <<= 1) {
+                    const uint32_t o = __shfl_up_sync(0xffffffffu, inc, off);
+                    if (lane >= (uint32_t)off) inc += o;
+                }
+                const uint32_t total = __shfl_sync(0xffffffffu, inc, 31);
+                const uint32_t rbase = __shfl_sync(0xffffffffu, rec_at, r - row_lo);
+                const uint32_t obase = __shfl_sync(0xffffffffu, out_at, r - row_lo);
+                if (hit) {
+                    const uint32_t pos = rbase + __popc(bal & lt);
+                    if (pos < cap) a.rec[pos] = make_uint4(xs | (w << 16), obase + inc - v, idx, depth);
+                }
+                if (my_row == r) {
+                    rec_at += __popc(bal);
+                    out_at += total;
+                }
             }
         }
     }
@@ -1028,10 +1038,18 @@ __device__ __forceinline__ SplitUnit split_unit(const SplitArgs &a, uint32_t u, 
     s.n_out = a.row_out[a.rows];
     s.live = u < n_units;
     if (!s.live) return s;
-    const bool le = lane < a.rows && a.row_unit[lane] <= u;
-    // rows without outputs own no unit: the last row whose first unit is <= u that has units
-    const uint32_t m = __ballot_sync(0xffffffffu, le);
-    s.row = 31u - __clz(m);
+    // last row whose first unit is <= u (rows without outputs own no unit and are passed over)
+    if (a.rows <= 32) {   // one probe per lane
+        const uint32_t m = __ballot_sync(0xffffffffu, lane < a.rows && a.row_unit[lane] <= u);
+        s.row = 31u - __clz(m);
+    } else {
+        uint32_t lo = 0, hi = a.rows - 1;
+        while (lo < hi) {
+            const uint32_t m = (lo + hi + 1) >> 1;
+            if (a.row_unit[m] <= u) lo = m; else hi = m - 1;
+        }
+        s.row = lo;
+    }
     const uint32_t k = u - a.row_unit[s.row];
     const uint32_t row_end = a.row_out[s.row + 1];
     s.q_lo = min(row_end, a.row_out[s.row] + k * kSplitUnit);
@@ -1203,15 +1221,19 @@ colsplit_scan_kernel(SplitArgs a, unsigned long long *__restrict__ ticket, int32
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // two slots per thread: slot_base = exclusive scan of slot_tot
+    // slot_base = exclusive scan of slot_tot, two slots per thread and 2048 per round
     const uint32_t n_slots = a.rows * a.stride;
-    const uint32_t i0 = 2 * threadIdx.x, i1 = i0 + 1;
-    const uint32_t v0 = i0 < n_slots ? a.slot_tot[i0] : 0u;
-    const uint32_t v1 = i1 < n_slots ? a.slot_tot[i1] : 0u;
-    uint32_t total;
-    const uint32_t ex = block_excl_scan(v0 + v1, wt, total);
-    if (i0 < n_slots) a.slot_base[i0] = ex;
-    if (i1 < n_slots) a.slot_base[i1] = ex + v0;
+    uint32_t total = 0;
+    for (uint32_t s0 = 0; s0 < n_slots; s0 += 2048) {
+        const uint32_t i0 = s0 + 2 * threadIdx.x, i1 = i0 + 1;
+        const uint32_t v0 = i0 < n_slots ? a.slot_tot[i0] : 0u;
+        const uint32_t v1 = i1 < n_slots ? a.slot_tot[i1] : 0u;
+        uint32_t round_total;
+        const uint32_t ex = block_excl_scan(v0 + v1, wt, round_total);
+        if (i0 < n_slots) a.slot_base[i0] = total + ex;
+        if (i1 < n_slots) a.slot_base[i1] = total + ex + v0;
+        total += round_total;
+    }
     if (threadIdx.x == 0) *ticket = 0ull;
     if (offsets == nullptr) return;
     __syncthreads();
@@ -1430,7 +1452,7 @@ static PlanWs carve_plan(void *ws, uint64_t total) {
     p.keyB = (uint32_t *)take(sizeof(uint32_t) * total);
     p.valB = (uint32_t *)take(sizeof(uint32_t) * total);
     p.eoff = (uint32_t *)take(sizeof(uint32_t) * total);
-    const size_t n_ha = (size_t)((total + 1023) / 1024) * 32;   // kSplitEntries, kSplitMaxRows
+    const size_t n_ha = (size_t)((total + 1023) / 1024) * 128;   // kSplitEntries, kSplitMaxRows
     p.ha_cnt = (uint32_t *)take(sizeof(uint32_t) * n_ha);
     p.ha_out = (uint32_t *)take(sizeof(uint32_t) * n_ha);
     p.hw_cnt = (uint32_t *)take(sizeof(uint32_t) * n_ha * 8);    // kSplitWarps
@@ -1503,13 +1525,14 @@ struct IsectGeom {
     const uint32_t *depth_bits;
 };
 
-// The row / column split applies to sorted output with at most 32 grid rows and 1024 tiles over
-// all sensors (every field of the packed rectangle record then fits 16 bits).
+// The row / column split applies to sorted output with at most 128 grid rows and 16384 tiles over
+// all sensors and rows of at most 1024 tiles (every field of the packed rectangle record then fits
+// 16 bits, the column tables fit shared memory).
 static bool use_split(const IsectGeom &g, int sort) {
     if (!sort || (uint64_t)g.C * g.n_tiles > kSplitMaxTiles) return false;
     const uint64_t rw = g.lidar ? g.lid.lidar.n_tiles_azim : g.cam.cam.tile_width;
     const uint64_t rows = (uint64_t)g.C * (g.n_tiles / rw);
-    return rows <= kSplitMaxRows && rows * (rw + 1) <= kSplitMaxSlots;
+    return rows <= kSplitMaxRows && rw <= kSplitMaxWidth;
 }
 
 // plan: counts, depth order of visible Gaussians, n_isects.
@@ -1695,7 +1718,8 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
         }
         {
             SPL_PROF("rowsplit_scatter_kernel", st);
-            rowsplit_scatter_kernel<<<units_a, kSplitWarps * 32, 0, st>>>(a);
+            if (a.rows <= 32) rowsplit_scatter_kernel<true><<<units_a, kSplitWarps * 32, 0, st>>>(a);
+            else rowsplit_scatter_kernel<false><<<units_a, kSplitWarps * 32, 0, st>>>(a);
         }
         {
             SPL_PROF("colsplit_count_kernel", st);
@@ -1803,10 +1827,10 @@ extern "C" size_t splatad_isect_plan_workspace_bytes(uint64_t total_elems) {
 }
 
 extern "C" size_t splatad_isect_fill_workspace_bytes(uint64_t capacity) {
-    // the larger of the radix buffers and the split's records + tables; (units + rows) * stride
-    // <= (capacity / kSplitUnit + 3) * 1025 for every geometry the split accepts
+    // the larger of the radix buffers and the split's records + tables; the widest rows and the
+    // most rows together bound (units + rows) * stride of every geometry the split accepts
     const size_t a = carve_fill(nullptr, capacity).bytes;
-    const size_t b = carve_split(nullptr, capacity, 2, kSplitMaxTiles + 1).bytes;
+    const size_t b = carve_split(nullptr, capacity, kSplitMaxRows, kSplitMaxWidth + 1).bytes;
     return a > b ? a : b;
 }
 

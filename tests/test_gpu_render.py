@@ -321,3 +321,79 @@ def test_config2_full_size_properties():
     again = splatad_b200.lidar_rasterization(**g)
     assert torch.equal(again[0], feats) and torch.equal(again[1], alphas) and torch.equal(again[2], asum)
     assert float(alphas.min()) >= 0.0 and float(alphas.max()) <= 1.0 and bool(torch.isfinite(feats).all())
+
+
+def _camera_lists_match_oracle(m, C, label):
+    """Tile lists of a (packed) camera render against the oracle's isect on the same projection."""
+    import math
+    from oracle import isect
+    tw, th = math.ceil(m["width"] / m["tile_size"]), math.ceil(m["height"] / m["tile_size"])
+    cam_ids = n(m["camera_ids"]) if m["camera_ids"] is not None else None
+    tpg, ids, flat = isect.isect_tiles(n(m["means2d"]), n(m["radii"]), n(m["depths"]), m["tile_size"], tw, th,
+                                       n_cameras=C, camera_ids=cam_ids)
+    assert np.array_equal(n(m["tiles_per_gauss"]), tpg), f"{label}: tile counts differ"
+    assert np.array_equal(n(m["isect_ids"]), ids), f"{label}: isect ids differ"
+    assert np.array_equal(n(m["flatten_ids"]), flat), f"{label}: sorted Gaussian id lists differ"
+    assert np.array_equal(n(m["isect_offsets"]), isect.isect_offset_encode(ids, C, tw, th)), f"{label}: offsets"
+
+
+def test_config3_six_cameras_and_lidar_reduced():
+    """Config 3's rig (six 1920 x 1080 cameras yawed 60 degrees apart + the 128-beam lidar) on 20k
+    Gaussians: 48960 camera tiles go through the radix split, the lidar through the row / column
+    split; both against the oracle."""
+    import splatad_b200
+    from oracle import pipeline
+    from splatad_b200 import scenes
+    cfg = scenes.config3(N=20_000)
+    cam, lid = cfg["camera"], cfg["lidar"]
+    out_c, out_a, m = splatad_b200.rasterization(**_to_gpu(cam))
+    assert out_c.shape == (6, 1080, 1920, 4)
+    _camera_lists_match_oracle(m, 6, "config3 cameras")
+    ref_c, ref_a, meta = pipeline.rasterization(**cam)
+    ok = ~meta["ambiguous"][..., None]
+    assert meta["ambiguous"].mean() < 0.01
+    assert_close("config3 RGB+D", n(out_c), ref_c, 5e-4, 5e-4, mask=ok, max_bad_frac=2e-3)
+    assert_close("config3 alpha", n(out_a), ref_a, 5e-4, 1e-4, mask=ok, max_bad_frac=2e-3)
+    lo_c, lo_a, lo_s, lm = splatad_b200.lidar_rasterization(**_to_gpu(lid))
+    ref = _lidar_stagewise_reference(lid, lm)
+    _check_lists(lm, ref, "config3 lidar")
+    _check_lidar_render("config3 lidar", lo_c, lo_a, lo_s, lm, ref)
+
+
+def test_config4_training_step_reduced():
+    """Config 4's rig (eight cameras, two lidars) on 20k Gaussians, forward + backward with fixed
+    seeded cotangents: forward against the oracle, gradients of the packed and the [C, N] camera
+    layouts (two different backward code paths) against each other, all parameters reached."""
+    import splatad_b200
+    from splatad_b200 import scenes
+    cfg = scenes.config4(N=20_000)
+    cam, lid = _to_gpu(cfg["camera"]), _to_gpu(cfg["lidar"])
+    names = ("means", "quats", "scales", "opacities")
+    g = torch.Generator().manual_seed(44)
+    # two lidars
+    leaves = {k: lid[k].clone().requires_grad_(True) for k in names + ("lidar_features",)}
+    lo_c, lo_a, lo_s, lm = splatad_b200.lidar_rasterization(**dict(lid, **leaves))
+    assert lo_c.shape == (2, 128, 1800, 17)
+    ref = _lidar_stagewise_reference(cfg["lidar"], lm)
+    _check_lists(lm, ref, "config4 lidars")
+    _check_lidar_render("config4 lidars", lo_c, lo_a, lo_s, lm, ref)
+    w_c = torch.randn(lo_c.shape, generator=g).to(DEV)
+    w_a = torch.randn(lo_a.shape, generator=g).to(DEV)
+    ((lo_c * w_c).sum() + (lo_a * w_a).sum()).backward()
+    for k, v in leaves.items():
+        assert v.grad is not None and bool(torch.isfinite(v.grad).all()) and float(v.grad.abs().sum()) > 0, k
+    # eight cameras, packed and unpacked
+    w_img = torch.randn(8, 1080, 1920, 4, generator=g).to(DEV)
+    grads = {}
+    for packed in (True, False):
+        leaves = {k: cam[k].clone().requires_grad_(True) for k in names + ("colors",)}
+        out_c, out_a, m = splatad_b200.rasterization(**dict(cam, packed=packed, **leaves))
+        if packed:
+            _camera_lists_match_oracle(m, 8, "config4 cameras")
+        ((out_c * w_img).sum() + out_a.sum()).backward()
+        grads[packed] = {k: v.grad.clone() for k, v in leaves.items()}
+    for k in grads[True]:
+        a, b = grads[True][k], grads[False][k]
+        assert float(b.abs().sum()) > 0, k
+        err = float((a - b).norm() / b.norm())
+        assert err < 1e-4, f"config4 camera grad {k}: packed vs [C,N] relative L2 {err:.2e}"

@@ -254,6 +254,37 @@ int splatad_isect_offset_encode(const int64_t *isect_ids, int64_t n_isects, uint
                                 void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Lidar points -> tiles -> raster image: prepares `raster_pts` from a point cloud, the step
+ * before a lidar render (examples/lidar_rendering.ipynb cell 8).
+ *
+ * map_points_to_lidar_tiles_tensor - gsplat/cuda/csrc/rasterization.cu:596-747: tile of every
+ * point (zero radius), tile_ids [total] int64 = sensor << 32 | tile, flatten_ids [total] int32 =
+ * point index; with sort != 0 both are ordered by tile id, ties in point order (a stable sort, as
+ * the reference's radix sort is). points2d [C,N,2] (camera_ids NULL) or [nnz,2] with camera_ids
+ * [nnz] int64. The workspace (splatad_map_points_workspace_bytes) is only needed when sorting.
+ * points_mapping_offset_encode_tensor - rasterization.cu:531-594. offsets [C, tile_height,
+ * tile_width] int32 (zeros when there are no points).
+ * populate_image_from_points_tensor - rasterization.cu:749-833. image [C, H, W, 5] is cleared
+ * and then, per tile, the k-th point of the tile's list is written at the tile's k-th pixel
+ * (row-major inside the tile; points beyond tile_width * tile_height per tile are dropped, as are
+ * those whose pixel lies outside the image).
+ * ---------------------------------------------------------------------------------------- */
+size_t splatad_map_points_workspace_bytes(uint64_t total_elems);
+int splatad_map_points_to_lidar_tiles(
+    uint32_t C, uint32_t N, uint64_t total_elems, const float *points2d, const int64_t *camera_ids,
+    const float *elev_boundaries, uint32_t n_boundaries, float tile_azim_resolution, float min_azim,
+    int32_t sort, void *workspace, size_t workspace_bytes, int64_t *tile_ids, int32_t *flatten_ids,
+    void *stream);
+int splatad_points_mapping_offset_encode(const int64_t *point_ids, int64_t n_points, uint32_t C,
+                                         uint32_t tile_width, uint32_t tile_height, int32_t *offsets,
+                                         void *stream);
+int splatad_populate_image_from_points(
+    uint32_t C, int64_t n_points, const float *points, uint32_t image_width, uint32_t image_height,
+    uint32_t tile_width, uint32_t tile_height, uint32_t tile_grid_width, uint32_t tile_grid_height,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, float *image, void *stream);
+
+
+/* ------------------------------------------------------------------------------------------
  * Compositing. `channels` is the true channel count (1..SPLATAD_MAX_CHANNELS): no padding to
  * a supported size is needed, unlike gsplat/cuda/_wrapper.py:876-921.
  * ---------------------------------------------------------------------------------------- */

@@ -151,3 +151,79 @@ def isect_offset_encode(isect_ids: np.ndarray, n_cameras: int, tile_width: int, 
     targets = np.arange(n_cameras * n_tiles, dtype=np.int64)
     offsets = np.searchsorted(flat, targets, side="left")
     return offsets.astype(np.int32).reshape(n_cameras, tile_height, tile_width)
+
+
+# ---------------------------------------------------------------------------------------------
+# Lidar points -> tiles -> raster image (gsplat/cuda/csrc/rasterization.cu:531-833; the reference has
+# no torch twin of these three, so this follows the CUDA kernels and is pinned by the properties the
+# reference's own tests assert, tests/test_basic.py:787-890).
+# ---------------------------------------------------------------------------------------------
+def map_points_to_lidar_tiles(points2d, elev_boundaries, tile_azim_resolution, min_azim, sort=True,
+                              n_cameras: Optional[int] = None, camera_ids=None):
+    """points2d [C,N,2] or [nnz,2] float32 -> (tile_ids int64 = sensor << 32 | tile, flatten_ids int32).
+
+    Kernel rasterization.cu:596-651: azimuth tile = int(azim / res) with azim = x - min_azim wrapped
+    by fmodf(azim + 360, 360) outside [0, 360); elevation tile = (number of the first n_tiles_elev
+    boundaries that are < y) - 1, at least 0. Sorted by tile id with a stable sort (the reference
+    radix-sorts the 64-bit ids, rasterization.cu:705-742)."""
+    p = np.asarray(points2d, dtype=np.float32)
+    packed = p.ndim == 2
+    pts = p.reshape(-1, 2)
+    if packed:
+        cids = np.asarray(camera_ids, dtype=np.int64)
+    else:
+        C, N = p.shape[:2]
+        cids = np.repeat(np.arange(C, dtype=np.int64), N)
+    eb = np.asarray(elev_boundaries, dtype=np.float32)
+    res = np.float32(tile_azim_resolution)
+    n_az = int(np.ceil(np.float32(360.0) / res))
+    n_el = eb.shape[0] - 1
+    azim = pts[:, 0] - np.float32(min_azim)
+    inside = (azim >= 0) & (azim < np.float32(360.0))
+    wrapped = np.fmod(azim + np.float32(360.0), np.float32(360.0))
+    tile_azim = np.where(inside, azim, wrapped) / res
+    tx = np.where(np.isnan(tile_azim), 0, np.trunc(tile_azim)).astype(np.int64)
+    tx = np.clip(tx, 0, n_az - 1)
+    below = (eb[None, :n_el] < pts[:, 1:2])          # NaN compares false, like the kernel's loop
+    i = np.where(below.all(axis=1), n_el, np.argmin(below, axis=1))   # leading run of "below"
+    ty = np.maximum(i - 1, 0).astype(np.int64)
+    ids = (cids << 32) | (ty * n_az + tx)
+    flat = np.arange(pts.shape[0], dtype=np.int32)
+    if sort:
+        order = np.argsort(ids, kind="stable")
+        ids, flat = ids[order], flat[order]
+    return ids, flat
+
+
+def points_mapping_offset_encode(point_ids: np.ndarray, n_lidars: int, tile_width: int, tile_height: int):
+    """Sorted point tile ids -> offsets [C, tile_height, tile_width] int32 (rasterization.cu:531-594)."""
+    n_tiles = tile_width * tile_height
+    ids = np.asarray(point_ids, dtype=np.int64)
+    flat = (ids >> 32) * n_tiles + (ids & 0xFFFFFFFF)
+    targets = np.arange(n_lidars * n_tiles, dtype=np.int64)
+    return np.searchsorted(flat, targets, side="left").astype(np.int32).reshape(n_lidars, tile_height, tile_width)
+
+
+def populate_image_from_points(points, image_width, image_height, tile_width, tile_height, tile_offsets,
+                               flatten_ids):
+    """[C,N,5] or [nnz,5] points -> image [C,H,W,5]: per tile, the k-th listed point lands on the
+    tile's k-th pixel (row-major in the tile), at most tile_width * tile_height points per tile,
+    pixels outside the image skipped (rasterization.cu:749-796)."""
+    pts = np.asarray(points, dtype=np.float32).reshape(-1, 5)
+    offs = np.asarray(tile_offsets)
+    C, gh, gw = offs.shape
+    flat_offs = offs.reshape(-1)
+    n_points = len(flatten_ids)
+    img = np.zeros((C, image_height, image_width, 5), np.float32)
+    for b in range(C * gh * gw):
+        cam, tile = divmod(b, gh * gw)
+        by, bx = divmod(tile, gw)
+        start = int(flat_offs[b])
+        end = n_points if b + 1 == C * gh * gw else int(flat_offs[b + 1])
+        end = min(end, start + tile_width * tile_height)
+        for k in range(start, end):
+            tr = k - start
+            i, j = by * tile_height + tr // tile_width, bx * tile_width + tr % tile_width
+            if i < image_height and j < image_width:
+                img[cam, i, j] = pts[flatten_ids[k]]
+    return img

@@ -11,6 +11,9 @@ from .ops import (
     isect_lidar_tiles,
     isect_offset_encode,
     isect_tiles,
+    map_points_to_lidar_tiles,
+    points_mapping_offset_encode,
+    populate_image_from_points,
     rasterize_to_pixels,
     rasterize_to_points,
     spherical_harmonics,
@@ -26,6 +29,9 @@ __all__ = [
     "isect_tiles",
     "isect_lidar_tiles",
     "isect_offset_encode",
+    "map_points_to_lidar_tiles",
+    "points_mapping_offset_encode",
+    "populate_image_from_points",
     "rasterize_to_pixels",
     "rasterize_to_points",
     "spherical_harmonics",

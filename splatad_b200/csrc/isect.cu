@@ -1815,6 +1815,121 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
     return check_launch("isect fill");
 }
 
+// ---------------------------------------------------------------------------------------
+// Lidar points -> tiles (what prepares `raster_pts` from a point cloud before a lidar render;
+// reference: gsplat/cuda/csrc/rasterization.cu:531-833). Same sort machinery as above on
+// (sensor * n_tiles + tile, point index) pairs.
+// ---------------------------------------------------------------------------------------
+struct PointsWs {
+    int64_t *count;
+    uint32_t *hist, *digit_totals;
+    uint32_t *keyA, *valA, *keyB, *valB;
+    size_t bytes;
+};
+
+static PointsWs carve_points(void *ws, uint64_t total) {
+    PointsWs p;
+    char *c = (char *)ws;
+    size_t off = 0;
+    auto take = [&](size_t b) { char *r = c ? c + off : nullptr; off += align256(b); return r; };
+    p.count = (int64_t *)take(sizeof(int64_t));
+    p.hist = (uint32_t *)take(sizeof(uint32_t) * kRadixBins * kSortGrid);
+    p.digit_totals = (uint32_t *)take(sizeof(uint32_t) * kRadixBins);
+    p.keyA = (uint32_t *)take(sizeof(uint32_t) * total);
+    p.valA = (uint32_t *)take(sizeof(uint32_t) * total);
+    p.keyB = (uint32_t *)take(sizeof(uint32_t) * total);
+    p.valB = (uint32_t *)take(sizeof(uint32_t) * total);
+    p.bytes = off;
+    return p;
+}
+
+// Tile of every point: azimuth tile by truncation (angles outside [0, 360) wrapped with fmodf),
+// elevation tile = number of the first n_tiles_elev boundaries below the point, minus one.
+__global__ void __launch_bounds__(kThreads)
+points_tile_kernel(uint32_t total, uint32_t N, const int64_t *__restrict__ camera_ids,
+                   const float2 *__restrict__ points2d, const float *__restrict__ elev_boundaries,
+                   float tile_azim_resolution, float min_azim, uint32_t n_tiles_azim, uint32_t n_tiles_elev,
+                   uint32_t *__restrict__ keys, uint32_t *__restrict__ vals, int64_t *__restrict__ tile_ids,
+                   int32_t *__restrict__ flatten_ids, int64_t *__restrict__ count) {
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx == 0 && count != nullptr) *count = (int64_t)total;
+    if (idx >= total) return;
+    const float2 pt = points2d[idx];
+    const float azim = pt.x - min_azim;
+    float tile_azim;
+    if (azim >= 0.f && azim < 360.f) tile_azim = azim / tile_azim_resolution;
+    else tile_azim = fmodf(azim + 360.f, 360.f) / tile_azim_resolution;
+    // float -> int conversion saturates (NaN -> 0); a point cannot land beyond the last tile of
+    // its row, the clamp only keeps a malformed input inside the key range
+    const uint32_t tx = min((uint32_t)max((int32_t)tile_azim, 0), n_tiles_azim - 1);
+    int32_t i = 0;
+    while (i < (int32_t)n_tiles_elev && elev_boundaries[i] < pt.y) ++i;
+    const uint32_t ty = (uint32_t)max(i - 1, 0);
+    const uint32_t cid = camera_ids ? (uint32_t)camera_ids[idx] : idx / N;
+    const uint32_t tile = ty * n_tiles_azim + tx;
+    if (keys != nullptr) {
+        keys[idx] = cid * (n_tiles_azim * n_tiles_elev) + tile;
+        vals[idx] = idx;
+    } else {
+        tile_ids[idx] = ((int64_t)cid << 32) | (int64_t)tile;
+        flatten_ids[idx] = (int32_t)idx;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+points_ids_kernel(uint32_t total, uint32_t n_tiles, const uint32_t *__restrict__ keys,
+                  const uint32_t *__restrict__ vals, int64_t *__restrict__ tile_ids,
+                  int32_t *__restrict__ flatten_ids) {
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const uint32_t key = keys[idx];
+    const uint32_t cid = key / n_tiles;
+    tile_ids[idx] = ((int64_t)cid << 32) | (int64_t)(key - cid * n_tiles);
+    flatten_ids[idx] = (int32_t)vals[idx];
+}
+
+// offsets[c, tile] = first position whose (sensor, tile) >= (c, tile); ids are sensor << 32 | tile.
+__global__ void __launch_bounds__(kThreads)
+points_offset_encode_kernel(const int64_t *__restrict__ point_ids, int64_t n, uint32_t C, uint32_t n_tiles,
+                            int32_t *__restrict__ offsets) {
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= C * n_tiles) return;
+    int64_t l = 0, h = n;
+    while (l < h) {
+        const int64_t m = (l + h) >> 1;
+        const int64_t id = point_ids[m];
+        const int64_t flat = (id >> 32) * (int64_t)n_tiles + (id & 0xffffffffll);
+        if (flat < (int64_t)t) l = m + 1; else h = m;
+    }
+    offsets[t] = (int32_t)l;
+}
+
+// One block per tile, one thread per pixel of the tile: the thread of rank k takes the tile's
+// k-th point (if there is one) and writes it at its own pixel.
+__global__ void populate_image_kernel(uint32_t C, int64_t n_points, const float *__restrict__ points,
+                                      uint32_t W, uint32_t H, uint32_t tile_width, uint32_t tile_height,
+                                      uint32_t grid_w, uint32_t grid_h, const int32_t *__restrict__ offsets,
+                                      const int32_t *__restrict__ flatten_ids, float *__restrict__ image) {
+    const uint32_t tiles_per_cam = grid_w * grid_h;
+    const uint32_t cam = blockIdx.x / tiles_per_cam;
+    const uint32_t tile = blockIdx.x - cam * tiles_per_cam;
+    const uint32_t by = tile / grid_w, bx = tile - by * grid_w;
+    const uint32_t tr = threadIdx.x;
+    if (tr >= tile_width * tile_height) return;
+    const uint32_t i = by * tile_height + tr / tile_width;
+    const uint32_t j = bx * tile_width + tr % tile_width;
+    if (i >= H || j >= W) return;
+    const int64_t start = offsets[blockIdx.x];
+    int64_t end = (blockIdx.x + 1 == C * tiles_per_cam) ? n_points : (int64_t)offsets[blockIdx.x + 1];
+    end = min(end, start + (int64_t)(tile_width * tile_height));
+    const int64_t k = start + tr;
+    if (k >= end) return;
+    const float *src = points + (size_t)flatten_ids[k] * 5;
+    float *dst = image + (((size_t)cam * H + i) * W + j) * 5;
+#pragma unroll
+    for (int c = 0; c < 5; ++c) dst[c] = src[c];
+}
+
 } // namespace splatad
 
 using namespace splatad;
@@ -1973,4 +2088,124 @@ extern "C" int splatad_isect_offset_encode(const int64_t *isect_ids, int64_t n_i
             isect_ids, nullptr, n_isects, C, (uint32_t)n_tiles, tile_n_bits, offsets);
     }
     return check_launch("isect_offset_encode");
+}
+
+// =======================================================================================
+// Lidar points -> tiles -> raster image
+// =======================================================================================
+extern "C" size_t splatad_map_points_workspace_bytes(uint64_t total_elems) {
+    return carve_points(nullptr, total_elems).bytes;
+}
+
+extern "C" int splatad_map_points_to_lidar_tiles(
+    uint32_t C, uint32_t N, uint64_t total_elems, const float *points2d, const int64_t *camera_ids,
+    const float *elev_boundaries, uint32_t n_boundaries, float tile_azim_resolution, float min_azim,
+    int32_t sort, void *workspace, size_t workspace_bytes, int64_t *tile_ids, int32_t *flatten_ids,
+    void *stream) {
+    if (total_elems == 0) return SPLATAD_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    SPL_REQUIRE(points2d && elev_boundaries && tile_ids && flatten_ids, SPLATAD_ERR_BAD_ARG,
+                "map_points_to_lidar_tiles: null argument");
+    SPL_REQUIRE(C > 0 && n_boundaries >= 2 && tile_azim_resolution > 0.f, SPLATAD_ERR_BAD_ARG,
+                "map_points_to_lidar_tiles: bad geometry");
+    SPL_REQUIRE(total_elems <= 0x7fffffffull, SPLATAD_ERR_BAD_ARG, "map_points_to_lidar_tiles: too many points");
+    const uint32_t total = (uint32_t)total_elems;
+    const uint32_t n_az = splatad_lidar_azimuth_tiles(tile_azim_resolution), n_el = n_boundaries - 1;
+    const uint64_t span = (uint64_t)C * n_az * n_el;
+    SPL_REQUIRE(span <= 0xffffffffull, SPLATAD_ERR_KEY_BITS, "map_points_to_lidar_tiles: sensors * tiles does not fit 32 bits");
+    const uint32_t n_per = N ? N : 1;
+    const uint32_t grid = div_up(total, kThreads);
+    if (!sort) {
+        SPL_PROF("points_tile_kernel", st);
+        points_tile_kernel<<<grid, kThreads, 0, st>>>(total, n_per, camera_ids, (const float2 *)points2d,
+                                                     elev_boundaries, tile_azim_resolution, min_azim, n_az,
+                                                     n_el, nullptr, nullptr, tile_ids, flatten_ids, nullptr);
+        return check_launch("map_points_to_lidar_tiles");
+    }
+    PointsWs p = carve_points(workspace, total);
+    SPL_REQUIRE(workspace != nullptr && workspace_bytes >= p.bytes, SPLATAD_ERR_WORKSPACE,
+                "map_points_to_lidar_tiles: workspace too small (%zu < %zu)", workspace_bytes, p.bytes);
+    {
+        SPL_PROF("points_tile_kernel", st);
+        points_tile_kernel<<<grid, kThreads, 0, st>>>(total, n_per, camera_ids, (const float2 *)points2d,
+                                                     elev_boundaries, tile_azim_resolution, min_azim, n_az,
+                                                     n_el, p.keyA, p.valA, nullptr, nullptr, p.count);
+    }
+    // stable LSD radix sort of the (key, index) pairs over the bits the keys use
+    const uint32_t key_bits = max(1u, bit_length(span - 1));
+    const uint32_t npass = (key_bits + 7) / 8;
+    const uint32_t bits_per = (key_bits + npass - 1) / npass;
+    uint32_t *ka = p.keyA, *va = p.valA, *kb = p.keyB, *vb = p.valB;
+    FinalOut nofin{};
+    for (uint32_t pass = 0; pass < npass; ++pass) {
+        PassSrc s{};
+        s.keys = ka; s.vals = va; s.n_ptr = p.count;
+        s.n_cap = total;
+        const int shift = (int)(pass * bits_per);
+        const uint32_t mask = (1u << bits_per) - 1u;
+        {
+            SPL_PROF("points_sort_upsweep", st);
+            radix_upsweep_kernel<false><<<kSortGrid, kSortThreads, 0, st>>>(s, shift, mask, p.hist);
+        }
+        {
+            SPL_PROF("points_sort_rowscan", st);
+            radix_rowscan_kernel<<<kRadixBins, ((kSortGrid + 31) / 32) * 32, 0, st>>>(p.hist, kSortGrid,
+                                                                                    p.digit_totals);
+        }
+        {
+            SPL_PROF("points_sort_downsweep", st);
+            radix_downsweep_kernel<false, false><<<kSortGrid, kSortThreads, 0, st>>>(
+                s, shift, (int)bits_per, mask, p.hist, p.digit_totals, kb, vb, nofin, nullptr);
+        }
+        uint32_t *t;
+        t = ka; ka = kb; kb = t;
+        t = va; va = vb; vb = t;
+    }
+    {
+        SPL_PROF("points_ids_kernel", st);
+        points_ids_kernel<<<grid, kThreads, 0, st>>>(total, n_az * n_el, ka, va, tile_ids, flatten_ids);
+    }
+    return check_launch("map_points_to_lidar_tiles");
+}
+
+extern "C" int splatad_points_mapping_offset_encode(const int64_t *point_ids, int64_t n_points, uint32_t C,
+                                                    uint32_t tile_width, uint32_t tile_height,
+                                                    int32_t *offsets, void *stream) {
+    SPL_REQUIRE(offsets, SPLATAD_ERR_BAD_ARG, "points_mapping_offset_encode: null output");
+    const uint64_t n_tiles = (uint64_t)tile_width * tile_height;
+    SPL_REQUIRE(C > 0 && n_tiles > 0 && (uint64_t)C * n_tiles <= 0x7fffffffull, SPLATAD_ERR_BAD_ARG,
+                "points_mapping_offset_encode: bad geometry");
+    SPL_REQUIRE(n_points == 0 || point_ids, SPLATAD_ERR_BAD_ARG, "points_mapping_offset_encode: null input");
+    const uint32_t total = (uint32_t)(C * n_tiles);
+    {
+        SPL_PROF("points_offset_encode_kernel", (cudaStream_t)stream);
+        points_offset_encode_kernel<<<div_up(total, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+            point_ids, n_points, C, (uint32_t)n_tiles, offsets);
+    }
+    return check_launch("points_mapping_offset_encode");
+}
+
+extern "C" int splatad_populate_image_from_points(
+    uint32_t C, int64_t n_points, const float *points, uint32_t image_width, uint32_t image_height,
+    uint32_t tile_width, uint32_t tile_height, uint32_t tile_grid_width, uint32_t tile_grid_height,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, float *image, void *stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    SPL_REQUIRE(image && tile_offsets, SPLATAD_ERR_BAD_ARG, "populate_image_from_points: null argument");
+    SPL_REQUIRE(tile_width >= 1 && tile_height >= 1 && tile_width * tile_height <= 1024, SPLATAD_ERR_BAD_ARG,
+                "populate_image_from_points: tile_width * tile_height must be in 1..1024");
+    SPL_REQUIRE(n_points == 0 || (points && flatten_ids), SPLATAD_ERR_BAD_ARG,
+                "populate_image_from_points: null input");
+    const size_t n_pix = (size_t)C * image_height * image_width;
+    if (n_pix == 0) return SPLATAD_OK;
+    cudaMemsetAsync(image, 0, n_pix * 5 * sizeof(float), st);
+    const uint32_t blocks = C * tile_grid_width * tile_grid_height;
+    if (blocks == 0 || n_points == 0) return check_launch("populate_image_from_points");
+    const uint32_t bs = ((tile_width * tile_height + 31) / 32) * 32;
+    {
+        SPL_PROF("populate_image_kernel", st);
+        populate_image_kernel<<<blocks, bs, 0, st>>>(C, n_points, points, image_width, image_height, tile_width,
+                                                    tile_height, tile_grid_width, tile_grid_height, tile_offsets,
+                                                    flatten_ids, image);
+    }
+    return check_launch("populate_image_from_points");
 }

@@ -728,6 +728,91 @@ def isect_offset_encode(isect_ids: Tensor, n_cameras: int, tile_width: int, tile
 
 
 # =============================================================================================
+# Lidar points -> tiles -> raster image
+# =============================================================================================
+@torch.no_grad()
+def map_points_to_lidar_tiles(
+    points2d: Tensor,  # [C, N, 2] or [nnz, 2]
+    elev_boundaries: Tensor,
+    tile_azim_resolution: float,
+    min_azim: float,
+    packed: bool = False,
+    n_cameras: Optional[int] = None,
+    camera_ids: Optional[Tensor] = None,
+    sort: bool = True,
+) -> Tuple[Tensor, Tensor]:
+    """Maps (azimuth, elevation) points to the lidar tile that holds them (zero radius), as
+    ``gsplat.cuda._wrapper.map_points_to_lidar_tiles`` (gsplat/cuda/_wrapper.py:697-758).
+
+    Returns (tile ids int64 [total] = sensor << 32 | tile, flatten ids int32 [total]), ordered by
+    tile id (ties in point order) when ``sort``."""
+    if packed:
+        nnz = points2d.size(0)
+        assert points2d.shape == (nnz, 2), points2d.size()
+        assert camera_ids is not None, "camera_ids is required if packed is True"
+        assert n_cameras is not None, "n_cameras is required if packed is True"
+        camera_ids = camera_ids.to(torch.int64).contiguous()
+        C, N, total = n_cameras, 0, nnz
+    else:
+        C, N, _ = points2d.shape
+        assert points2d.shape == (C, N, 2), points2d.size()
+        camera_ids, total = None, C * N
+    dev = points2d.device
+    pts, eb = _f(points2d), _f(elev_boundaries)
+    tile_ids = torch.empty(total, dtype=torch.int64, device=dev)
+    flatten_ids = torch.empty(total, dtype=torch.int32, device=dev)
+    if total == 0:
+        return tile_ids, flatten_ids
+    lib = _lib.load()
+    ws = _lib.workspace("map_points", lib.splatad_map_points_workspace_bytes(total), dev) if sort else None
+    _call("splatad_map_points_to_lidar_tiles", C, N, total, _lib.ptr(pts), _lib.ptr(camera_ids), _lib.ptr(eb),
+          int(eb.numel()), float(tile_azim_resolution), float(min_azim), int(bool(sort)), _lib.ptr(ws),
+          ws.numel() if ws is not None else 0, _lib.ptr(tile_ids), _lib.ptr(flatten_ids), _lib.stream_ptr(dev))
+    return tile_ids, flatten_ids
+
+
+@torch.no_grad()
+def points_mapping_offset_encode(point_ids: Tensor, n_lidars: int, tile_width: int, tile_height: int) -> Tensor:
+    """Sorted point tile ids -> start of every tile's list, [C, tile_height, tile_width] int32
+    (gsplat/cuda/_wrapper.py:760-776)."""
+    point_ids = point_ids.contiguous()
+    dev = point_ids.device
+    offsets = torch.empty((n_lidars, tile_height, tile_width), dtype=torch.int32, device=dev)
+    if offsets.numel() == 0:
+        return offsets
+    _call("splatad_points_mapping_offset_encode", _lib.ptr(point_ids) if point_ids.numel() else None,
+          point_ids.numel(), n_lidars, tile_width, tile_height, _lib.ptr(offsets), _lib.stream_ptr(dev))
+    return offsets
+
+
+@torch.no_grad()
+def populate_image_from_points(
+    points: Tensor,  # [C, N, 5] or [nnz, 5]
+    image_width: int,
+    image_height: int,
+    tile_width: int,
+    tile_height: int,
+    tile_offsets: Tensor,  # [C, tile grid height, tile grid width]
+    flatten_id: Tensor,  # [n_points]
+) -> Tensor:
+    """Raster image [C, image_height, image_width, 5] whose pixels take the values of the points
+    listed for their tile, in list order (gsplat/cuda/_wrapper.py:778-809)."""
+    assert points.shape[-1] == 5, points.shape
+    pts = _f(points)
+    dev = pts.device
+    C, grid_h, grid_w = tile_offsets.shape
+    offs = tile_offsets.to(torch.int32).contiguous()
+    flat = flatten_id.to(torch.int32).contiguous()
+    image = torch.empty((C, image_height, image_width, 5), dtype=torch.float32, device=dev)
+    if image.numel() == 0:
+        return image
+    _call("splatad_populate_image_from_points", C, flat.numel(), _lib.ptr(pts) if pts.numel() else None,
+          image_width, image_height, tile_width, tile_height, grid_w, grid_h, _lib.ptr(offs),
+          _lib.ptr(flat) if flat.numel() else None, _lib.ptr(image), _lib.stream_ptr(dev))
+    return image
+
+
+# =============================================================================================
 # Compositing
 # =============================================================================================
 def rasterize_to_pixels(

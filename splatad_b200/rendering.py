@@ -31,6 +31,43 @@ from .ops import (
 )
 
 
+def _check_gaussians(means: Tensor, quats: Tensor, scales: Tensor, opacities: Tensor,
+                     velocities: Optional[Tensor], viewmats: Tensor) -> Tuple[int, int]:
+    """Shape checks shared by both entry points; returns (N, C)."""
+    N, C = means.shape[0], viewmats.shape[0]
+    for name, tensor, shape in (("means", means, (N, 3)), ("quats", quats, (N, 4)), ("scales", scales, (N, 3)),
+                                ("opacities", opacities, (N,)), ("viewmats", viewmats, (C, 4, 4))):
+        assert tensor.shape == shape, f"{name}: {tuple(tensor.shape)}"
+    if velocities is not None:
+        assert velocities.shape == (N, 3), velocities.shape
+    return N, C
+
+
+def _sensor_motion(C: int, device, linear_velocity: Optional[Tensor], angular_velocity: Optional[Tensor],
+                   rolling_shutter_time: Optional[Tensor]) -> Tuple[Tensor, Tensor, Tensor]:
+    """Ego motion of the C sensors during read-out; a sensor without one stands still."""
+    out = []
+    for value, shape in ((linear_velocity, (C, 3)), (angular_velocity, (C, 3)), (rolling_shutter_time, (C,))):
+        if value is None:
+            value = torch.zeros(shape, device=device)
+        assert value.shape == shape, value.shape
+        out.append(value)
+    return tuple(out)
+
+
+def _composite_with_count_check(isect, grid: Tuple[int, int], composite):
+    """Runs ``composite(isect_offsets, flatten_ids)`` on a deferred tile intersection and returns
+    (outputs, isect_ids, flatten_ids, isect_offsets): if the intersection count turns out to exceed
+    the room it was given, intersection and compositing are repeated the two-step way."""
+    outputs = composite(isect.offsets(*grid), isect.flatten_ids)
+    resolved = isect.resolve()
+    if resolved is None:
+        isect = isect.redo()
+        outputs = composite(isect.offsets(*grid), isect.flatten_ids)
+        resolved = isect.resolve()
+    return outputs, resolved[0], resolved[1], isect.offsets(*grid), isect.tiles_per_gauss
+
+
 def rasterization(
     means: Tensor,  # [N, 3]
     quats: Tensor,  # [N, 4]
@@ -70,29 +107,11 @@ def rasterization(
 
     Returns (render_colors [C,H,W,X], render_alphas [C,H,W,1], meta).
     """
-    N = means.shape[0]
-    C = viewmats.shape[0]
-    assert means.shape == (N, 3), means.shape
-    assert quats.shape == (N, 4), quats.shape
-    assert scales.shape == (N, 3), scales.shape
-    assert opacities.shape == (N,), opacities.shape
-    if velocities is not None:
-        assert velocities.shape == (N, 3), velocities.shape
-    assert viewmats.shape == (C, 4, 4), viewmats.shape
+    N, C = _check_gaussians(means, quats, scales, opacities, velocities, viewmats)
     assert Ks.shape == (C, 3, 3), Ks.shape
-    if linear_velocity is not None:
-        assert linear_velocity.shape == (C, 3), linear_velocity.shape
-    else:
-        linear_velocity = torch.zeros(C, 3, device=means.device)
-    if angular_velocity is not None:
-        assert angular_velocity.shape == (C, 3), angular_velocity.shape
-    else:
-        angular_velocity = torch.zeros(C, 3, device=means.device)
-    if rolling_shutter_time is not None:
-        assert rolling_shutter_time.shape == (C,), rolling_shutter_time.shape
-    else:
-        rolling_shutter_time = torch.zeros(C, device=means.device)
-    assert render_mode in ["RGB", "D", "ED", "RGB+D", "RGB+ED"], render_mode
+    assert render_mode in ("RGB", "D", "ED", "RGB+D", "RGB+ED"), render_mode
+    linear_velocity, angular_velocity, rolling_shutter_time = _sensor_motion(
+        C, means.device, linear_velocity, angular_velocity, rolling_shutter_time)
 
     if sh_degree is None:
         assert (colors.dim() == 2 and colors.shape[0] == N) or (
@@ -105,27 +124,11 @@ def rasterization(
         assert (sh_degree + 1) ** 2 <= colors.shape[-2], colors.shape
 
     proj_results = fully_fused_projection(
-        means,
-        None,  # covars
-        quats,
-        scales,
-        velocities,
-        viewmats,
-        Ks,
-        width,
-        height,
-        linear_velocity,
-        angular_velocity,
-        rolling_shutter_time,
-        eps2d=eps2d,
-        packed=packed,
-        near_plane=near_plane,
-        far_plane=far_plane,
-        radius_clip=radius_clip,
-        sparse_grad=sparse_grad,
+        means, None, quats, scales, velocities, viewmats, Ks, width, height, linear_velocity,
+        angular_velocity, rolling_shutter_time, eps2d=eps2d, packed=packed, near_plane=near_plane,
+        far_plane=far_plane, radius_clip=radius_clip, sparse_grad=sparse_grad,
         calc_compensations=(rasterize_mode == "antialiased"),
     )
-
     if packed:
         (camera_ids, gaussian_ids, radii, means2d, depths, conics, compensations, pix_vels) = proj_results
         opacities = opacities[gaussian_ids]  # [nnz]
@@ -141,18 +144,8 @@ def rasterization(
     tile_height = math.ceil(height / float(tile_size))
     # plan + fill are enqueued without waiting for the intersection count (once a frame of this
     # shape has been seen); the exact-length isect_ids / flatten_ids are cut out after compositing
-    isect = isect_tiles_deferred(
-        means2d,
-        radii,
-        depths,
-        tile_size,
-        tile_width,
-        tile_height,
-        packed=packed,
-        n_cameras=C,
-        camera_ids=camera_ids,
-        gaussian_ids=gaussian_ids,
-    )
+    isect = isect_tiles_deferred(means2d, radii, depths, tile_size, tile_width, tile_height, packed=packed,
+                                 n_cameras=C, camera_ids=camera_ids, gaussian_ids=gaussian_ids)
 
     if sh_degree is None:
         if packed:
@@ -216,41 +209,20 @@ def rasterization(
             flatten_ids, rolling_shutter_time, backgrounds=backgrounds, packed=packed, absgrad=absgrad,
         )
 
-    render_colors, render_alphas = composite(isect.offsets(tile_height, tile_width), isect.flatten_ids)
-    resolved = isect.resolve()
-    if resolved is None:  # more intersections than there was room for: the two-step way, again
-        isect = isect.redo()
-        render_colors, render_alphas = composite(isect.offsets(tile_height, tile_width), isect.flatten_ids)
-        resolved = isect.resolve()
-    isect_ids, flatten_ids = resolved
-    isect_offsets = isect.offsets(tile_height, tile_width)
-    tiles_per_gauss = isect.tiles_per_gauss
+    (render_colors, render_alphas), isect_ids, flatten_ids, isect_offsets, tiles_per_gauss = (
+        _composite_with_count_check(isect, (tile_height, tile_width), composite))
     if render_mode in ["ED", "RGB+ED"]:
         render_colors = torch.cat(
             [render_colors[..., :-1], render_colors[..., -1:] / render_alphas.clamp(min=1e-10)],
             dim=-1,
         )
 
-    meta = {
-        "camera_ids": camera_ids,
-        "gaussian_ids": gaussian_ids,
-        "radii": radii,
-        "means2d": means2d,
-        "depths": depths,
-        "conics": conics,
-        "opacities": opacities,
-        "pix_vels": pix_vels,
-        "tile_width": tile_width,
-        "tile_height": tile_height,
-        "tiles_per_gauss": tiles_per_gauss,
-        "isect_ids": isect_ids,
-        "flatten_ids": flatten_ids,
-        "isect_offsets": isect_offsets,
-        "width": width,
-        "height": height,
-        "tile_size": tile_size,
-        "n_cameras": C,
-    }
+    meta = dict(
+        camera_ids=camera_ids, gaussian_ids=gaussian_ids, radii=radii, means2d=means2d, depths=depths,
+        conics=conics, opacities=opacities, pix_vels=pix_vels, tile_width=tile_width, tile_height=tile_height,
+        tiles_per_gauss=tiles_per_gauss, isect_ids=isect_ids, flatten_ids=flatten_ids,
+        isect_offsets=isect_offsets, width=width, height=height, tile_size=tile_size, n_cameras=C,
+    )
     return render_colors, render_alphas, meta
 
 
@@ -296,67 +268,27 @@ def lidar_rasterization(
     channel [C,H,W,D+1], alphas [C,H,W,1], alpha_sum_until_points [C,H,W,1] or None, meta);
     ``meta["median_depths"]`` holds the median range.
     """
-    N = means.shape[0]
-    C = viewmats.shape[0]
-    D = lidar_features.shape[-1]
-    assert means.shape == (N, 3), means.shape
-    assert quats.shape == (N, 4), quats.shape
-    assert scales.shape == (N, 3), scales.shape
-    assert opacities.shape == (N,), opacities.shape
-    if velocities is not None:
-        assert velocities.shape == (N, 3), velocities.shape
-    assert viewmats.shape == (C, 4, 4), viewmats.shape
-    assert lidar_features.shape == (C, N, D), lidar_features.shape
-    assert min_azimuth < max_azimuth, (min_azimuth, max_azimuth)
-    assert min_elevation < max_elevation, (min_elevation, max_elevation)
-    assert min_azimuth >= -180.0 and max_azimuth <= 180.0, (min_azimuth, max_azimuth)
-    assert min_elevation >= -85.0 and max_elevation <= 85.0, (min_elevation, max_elevation)
+    N, C = _check_gaussians(means, quats, scales, opacities, velocities, viewmats)
+    assert lidar_features.shape[:2] == (C, N) and lidar_features.dim() == 3, lidar_features.shape
+    assert -180.0 <= min_azimuth < max_azimuth <= 180.0, (min_azimuth, max_azimuth)
+    assert -85.0 <= min_elevation < max_elevation <= 85.0, (min_elevation, max_elevation)
     assert tile_width * tile_height <= 256, (tile_width, tile_height)
-    assert n_elevation_channels > 0, n_elevation_channels
-    assert tile_elevation_boundaries.shape == (
-        math.ceil(n_elevation_channels / tile_height) + 1,
-    ), tile_elevation_boundaries.shape
-    assert azimuth_resolution > 0.0, azimuth_resolution
-    if linear_velocity is not None:
-        assert linear_velocity.shape == (C, 3), linear_velocity.shape
-    else:
-        linear_velocity = torch.zeros(C, 3, device=means.device)
-    if angular_velocity is not None:
-        assert angular_velocity.shape == (C, 3), angular_velocity.shape
-    else:
-        angular_velocity = torch.zeros(C, 3, device=means.device)
-    if rolling_shutter_time is not None:
-        assert rolling_shutter_time.shape == (C,), rolling_shutter_time.shape
-    else:
-        rolling_shutter_time = torch.zeros(C, device=means.device)
-    assert raster_pts.shape == (C, *raster_pts.shape[1:]), raster_pts.shape
-    assert raster_pts.shape[-1] == 4, raster_pts.shape
-
-    proj_results = fully_fused_lidar_projection(
-        means,
-        None,  # covars
-        quats,
-        scales,
-        velocities,
-        viewmats,
-        linear_velocity,
-        angular_velocity,
-        rolling_shutter_time,
-        min_elevation=min_elevation,
-        max_elevation=max_elevation,
-        min_azimuth=min_azimuth,
-        max_azimuth=max_azimuth,
-        eps2d=eps2d,
-        packed=packed,
-        near_plane=near_plane,
-        far_plane=far_plane,
-        radius_clip=radius_clip,
-        sparse_grad=sparse_grad,
-        calc_compensations=(rasterize_mode == "antialiased"),
-    )
+    assert n_elevation_channels > 0 and azimuth_resolution > 0.0, (n_elevation_channels, azimuth_resolution)
+    n_elevation_tiles = math.ceil(n_elevation_channels / tile_height)
+    assert tile_elevation_boundaries.shape == (n_elevation_tiles + 1,), tile_elevation_boundaries.shape
+    assert raster_pts.dim() == 4 and raster_pts.shape[0] == C and raster_pts.shape[-1] == 4, raster_pts.shape
     if packed:
         raise NotImplementedError("Packed mode is not supported for lidar_rasterization")
-    radii, means2d, depths, conics, compensations, pix_vels, depth_compensations = proj_results
+    linear_velocity, angular_velocity, rolling_shutter_time = _sensor_motion(
+        C, means.device, linear_velocity, angular_velocity, rolling_shutter_time)
+
+    radii, means2d, depths, conics, compensations, pix_vels, depth_compensations = fully_fused_lidar_projection(
+        means, None, quats, scales, velocities, viewmats, linear_velocity, angular_velocity,
+        rolling_shutter_time, min_elevation=min_elevation, max_elevation=max_elevation,
+        min_azimuth=min_azimuth, max_azimuth=max_azimuth, eps2d=eps2d, packed=False, near_plane=near_plane,
+        far_plane=far_plane, radius_clip=radius_clip, sparse_grad=sparse_grad,
+        calc_compensations=(rasterize_mode == "antialiased"),
+    )
     opacities = opacities.repeat(C, 1)  # [C, N]
     camera_ids, gaussian_ids = None, None
 
@@ -366,23 +298,13 @@ def lidar_rasterization(
     if compensations is not None:
         opacities = opacities * compensations
 
-    n_elevation_tiles = math.ceil(n_elevation_channels / tile_height)
     tile_azimuth_resolution = azimuth_resolution * tile_width
     n_azimuth_tiles = math.ceil((max_azimuth - min_azimuth) / tile_azimuth_resolution)
     # plan + fill are enqueued without waiting for the intersection count (once a frame of this
     # shape has been seen); the exact-length isect_ids / flatten_ids are cut out after compositing
     isect = isect_lidar_tiles_deferred(
-        means2d,
-        radii,
-        depths,
-        elev_boundaries=tile_elevation_boundaries,
-        tile_azim_resolution=tile_azimuth_resolution,
-        min_azim=min_azimuth,
-        packed=packed,
-        n_cameras=C,
-        camera_ids=camera_ids,
-        gaussian_ids=gaussian_ids,
-    )
+        means2d, radii, depths, elev_boundaries=tile_elevation_boundaries,
+        tile_azim_resolution=tile_azimuth_resolution, min_azim=min_azimuth, packed=False, n_cameras=C)
 
     image_width = raster_pts.shape[-2]
     image_height = raster_pts.shape[-3]
@@ -415,38 +337,15 @@ def lidar_rasterization(
                 first = (alphas_, alpha_sum_)  # the same for every chunk
         return torch.cat(chunks, dim=-1), first[0], first[1], torch.cat(medians, dim=-1)
 
-    grid = (n_elevation_tiles, n_azimuth_tiles)
-    outputs = composite(isect.offsets(*grid), isect.flatten_ids)
-    resolved = isect.resolve()
-    if resolved is None:  # more intersections than there was room for: the two-step way, again
-        isect = isect.redo()
-        outputs = composite(isect.offsets(*grid), isect.flatten_ids)
-        resolved = isect.resolve()
-    render_lidar_features, render_alphas, alpha_sum_until_points, median_depths = outputs
-    isect_ids, flatten_ids = resolved
-    isect_offsets = isect.offsets(*grid)
-    tiles_per_gauss = isect.tiles_per_gauss
+    (render_lidar_features, render_alphas, alpha_sum_until_points, median_depths), isect_ids, flatten_ids, \
+        isect_offsets, tiles_per_gauss = _composite_with_count_check(
+            isect, (n_elevation_tiles, n_azimuth_tiles), composite)
 
-    meta = {
-        "camera_ids": camera_ids,
-        "gaussian_ids": gaussian_ids,
-        "radii": radii,
-        "means2d": means2d,
-        "depths": depths,
-        "conics": conics,
-        "opacities": opacities,
-        "pix_vels": pix_vels,
-        "tile_grid_width": n_azimuth_tiles,
-        "tile_grid_height": n_elevation_tiles,
-        "tiles_per_gauss": tiles_per_gauss,
-        "isect_ids": isect_ids,
-        "flatten_ids": flatten_ids,
-        "isect_offsets": isect_offsets,
-        "width": image_width,
-        "height": image_height,
-        "tile_width": tile_width,
-        "tile_height": tile_height,
-        "n_cameras": C,
-        "median_depths": median_depths,
-    }
+    meta = dict(
+        camera_ids=camera_ids, gaussian_ids=gaussian_ids, radii=radii, means2d=means2d, depths=depths,
+        conics=conics, opacities=opacities, pix_vels=pix_vels, tile_grid_width=n_azimuth_tiles,
+        tile_grid_height=n_elevation_tiles, tiles_per_gauss=tiles_per_gauss, isect_ids=isect_ids,
+        flatten_ids=flatten_ids, isect_offsets=isect_offsets, width=image_width, height=image_height,
+        tile_width=tile_width, tile_height=tile_height, n_cameras=C, median_depths=median_depths,
+    )
     return render_lidar_features, render_alphas, alpha_sum_until_points, meta

@@ -189,6 +189,63 @@ int splatad_sh_bwd(uint32_t n_elems, uint32_t K, uint32_t degrees_to_use, const 
                    float *v_coeffs, float *v_dirs, void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Unfused building blocks of the projection (exported by the reference as separate ops,
+ * gsplat/__init__.py:4-18). All tensors FP32 row-major; gradient outputs are written (not
+ * accumulated) except v_viewmats, which is accumulated and must be zero-initialised.
+ *
+ * quat_scale_to_covar_preci_fwd/_bwd_tensor - gsplat/cuda/csrc/projection.cu:18-260. quats [N,4]
+ *   (w,x,y,z, need not be normalised), scales [N,3]; covars / precis [N,3,3], or [N,6] upper
+ *   triangles when triu != 0; either output (and its gradient) may be NULL.
+ * world_to_cam_fwd/_bwd_tensor - projection.cu:466-599 (kernels in utils.cuh). means [N,3],
+ *   covars [N,3,3], viewmats [C,4,4] -> means_c [C,N,3], covars_c [C,N,3,3]. In the backward any
+ *   of v_means, v_covars, v_viewmats may be NULL.
+ * persp_proj_fwd/_bwd_tensor - projection.cu:262-464. Sensor-frame means [C,N,3], covars
+ *   [C,N,3,3], Ks [C,3,3] -> means2d [C,N,2], covars2d [C,N,2,2] (no blur added).
+ * compute_pix_velocity_fwd/_bwd_tensor - projection.cu:2064-2266. p_view [C,N,3], lin_vel /
+ *   ang_vel [C,3], velocities [C,N,3] (sensor frame) -> pixel velocities [C,N,2].
+ * lidar_proj_fwd/_bwd_tensor - projection.cu:1841-2062. -> means2d [C,N,2] (azimuth, elevation in
+ *   degrees), covars2d [C,N,2,2] (no blur added), depth_compensations [C,N,2].
+ * compute_lidar_velocity_fwd/_bwd_tensor - projection.cu:2064-2266 (lidar variants). -> (azimuth,
+ *   elevation, range) velocities [C,N,3].
+ * ---------------------------------------------------------------------------------------- */
+int splatad_quat_scale_to_covar_preci_fwd(uint32_t N, const float *quats, const float *scales,
+                                          int32_t triu, float *covars, float *precis, void *stream);
+int splatad_quat_scale_to_covar_preci_bwd(uint32_t N, const float *quats, const float *scales,
+                                          const float *v_covars, const float *v_precis, int32_t triu,
+                                          float *v_quats, float *v_scales, void *stream);
+int splatad_world_to_cam_fwd(uint32_t C, uint32_t N, const float *means, const float *covars,
+                             const float *viewmats, float *means_c, float *covars_c, void *stream);
+int splatad_world_to_cam_bwd(uint32_t C, uint32_t N, const float *means, const float *covars,
+                             const float *viewmats, const float *v_means_c, const float *v_covars_c,
+                             float *v_means, float *v_covars, float *v_viewmats, void *stream);
+int splatad_persp_proj_fwd(uint32_t C, uint32_t N, const float *means, const float *covars,
+                           const float *Ks, uint32_t width, uint32_t height, float *means2d,
+                           float *covars2d, void *stream);
+int splatad_persp_proj_bwd(uint32_t C, uint32_t N, const float *means, const float *covars,
+                           const float *Ks, uint32_t width, uint32_t height, const float *v_means2d,
+                           const float *v_covars2d, float *v_means, float *v_covars, void *stream);
+int splatad_compute_pix_velocity_fwd(uint32_t C, uint32_t N, const float *p_view, const float *lin_vel,
+                                     const float *ang_vel, const float *velocities, const float *Ks,
+                                     uint32_t width, uint32_t height, float *pix_vels, void *stream);
+int splatad_compute_pix_velocity_bwd(uint32_t C, uint32_t N, const float *p_view, const float *lin_vel,
+                                     const float *ang_vel, const float *velocities, const float *Ks,
+                                     uint32_t width, uint32_t height, const float *v_pix_vels,
+                                     float *v_p_view, float *v_velocities, void *stream);
+int splatad_lidar_proj_fwd(uint32_t C, uint32_t N, const float *means, const float *covars, float eps2d,
+                           float *means2d, float *covars2d, float *depth_compensations, void *stream);
+int splatad_lidar_proj_bwd(uint32_t C, uint32_t N, const float *means, const float *covars, float eps2d,
+                           const float *v_means2d, const float *v_covars2d,
+                           const float *v_depth_compensations, float *v_means, float *v_covars,
+                           void *stream);
+int splatad_compute_lidar_velocity_fwd(uint32_t C, uint32_t N, const float *p_view, const float *lin_vel,
+                                       const float *ang_vel, const float *velocities, float *lidar_vels,
+                                       void *stream);
+int splatad_compute_lidar_velocity_bwd(uint32_t C, uint32_t N, const float *p_view, const float *lin_vel,
+                                       const float *ang_vel, const float *velocities,
+                                       const float *v_lidar_vels, float *v_p_view, float *v_velocities,
+                                       void *stream);
+
+/* ------------------------------------------------------------------------------------------
  * Tile intersection
  *
  * isect_tiles_tensor (gsplat/cuda/csrc/rasterization.cu:92-216) and isect_lidar_tiles_tensor

@@ -296,3 +296,67 @@ def spherical_harmonics(degree: int, dirs: Tensor, coeffs: Tensor, masks: Option
     if masks is not None:
         out = out * masks[..., None]
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# The unfused ops (torch twins in gsplat/cuda/_torch_impl.py:10-262), differentiable.
+# ---------------------------------------------------------------------------------------------
+def _triu(m: Tensor) -> Tensor:
+    return torch.stack([m[..., 0, 0], m[..., 0, 1], m[..., 0, 2], m[..., 1, 1], m[..., 1, 2], m[..., 2, 2]], dim=-1)
+
+
+def quat_scale_to_covar_preci(quats: Tensor, scales: Tensor, compute_covar: bool = True,
+                              compute_preci: bool = True, triu: bool = False):
+    """gsplat/cuda/_torch_impl.py:10-51: covariance (R S)(R S)^T and precision (R / S)(R / S)^T."""
+    covars = quat_scale_to_covar(quats, scales) if compute_covar else None
+    precis = quat_scale_to_covar(quats, 1.0 / scales) if compute_preci else None
+    if triu:
+        covars = _triu(covars) if covars is not None else None
+        precis = _triu(precis) if precis is not None else None
+    return covars, precis
+
+
+def world_to_cam(means: Tensor, covars: Tensor, viewmats: Tensor) -> Tuple[Tensor, Tensor]:
+    """gsplat/cuda/_torch_impl.py:168-190."""
+    p, cov, _ = _world_to_sensor(means, covars, viewmats)
+    return p, cov
+
+
+def persp_proj(means: Tensor, covars: Tensor, Ks: Tensor, width: int, height: int) -> Tuple[Tensor, Tensor]:
+    """gsplat/cuda/_torch_impl.py:54-101: sensor-frame Gaussians -> pixel means and 2x2 covariances."""
+    J = persp_jacobian(means, Ks, width, height)
+    cov2d = J @ covars @ J.transpose(-1, -2)
+    x, y, z = means.unbind(-1)
+    fx, fy, cx, cy = Ks[:, 0, 0, None], Ks[:, 1, 1, None], Ks[:, 0, 2, None], Ks[:, 1, 2, None]
+    return torch.stack([fx * x / z + cx, fy * y / z + cy], dim=-1), cov2d
+
+
+def compute_pix_velocity(p_view: Tensor, lin_vel: Tensor, ang_vel: Tensor, velocities: Tensor, Ks: Tensor,
+                         width: int, height: int) -> Tensor:
+    """gsplat/cuda/_torch_impl.py:193-224: -J (lin + ang x p - v)."""
+    J = persp_jacobian(p_view, Ks, width, height)
+    total = lin_vel[:, None, :] + torch.cross(ang_vel[:, None, :].expand_as(p_view), p_view, dim=-1) - velocities
+    return -(J @ total[..., None])[..., 0]
+
+
+def lidar_proj(means: Tensor, covars: Tensor, eps2d: float) -> Tuple[Tensor, Tensor, Tensor]:
+    """gsplat/cuda/_torch_impl.py:104-165: (azimuth, elevation) in degrees, their 2x2 covariance
+    (no blur added) and the depth compensation."""
+    J = lidar_jacobian(means)
+    cov_s = J @ covars @ J.transpose(-1, -2)
+    x, y, z = means.unbind(-1)
+    rinv = torch.rsqrt(x * x + y * y + z * z)
+    means2d = torch.stack([torch.atan2(y, x), torch.asin(z * rinv)], dim=-1) * RAD_TO_DEG
+    a1, a2 = cov_s[..., 0, 0] + eps2d, cov_s[..., 0, 1]
+    b1, b2 = cov_s[..., 1, 0], cov_s[..., 1, 1] + eps2d
+    c1, c2 = cov_s[..., 2, 0], cov_s[..., 2, 1]
+    invD = 1.0 / (a1 * b2 - a2 * b1)
+    depth_comp = torch.stack([(b1 * c2 - b2 * c1) * invD, (a2 * c1 - a1 * c2) * invD], dim=-1)
+    return means2d, cov_s[..., :2, :2], depth_comp
+
+
+def compute_lidar_velocity(p_view: Tensor, lin_vel: Tensor, ang_vel: Tensor, velocities: Tensor) -> Tensor:
+    """gsplat/cuda/_torch_impl.py:227-262: -J (lin + ang x p - v) with the spherical Jacobian."""
+    J = lidar_jacobian(p_view)
+    total = lin_vel[:, None, :] + torch.cross(ang_vel[:, None, :].expand_as(p_view), p_view, dim=-1) - velocities
+    return -(J @ total[..., None])[..., 0]

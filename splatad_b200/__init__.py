@@ -6,18 +6,24 @@ everything runs in hand-written CUDA behind the C ABI declared in ``include/spla
 """
 
 from .ops import (
+    compute_lidar_velocity,
+    compute_pix_velocity,
     fully_fused_lidar_projection,
     fully_fused_projection,
     isect_lidar_tiles,
     isect_offset_encode,
     isect_tiles,
+    lidar_proj,
     map_points_to_lidar_tiles,
+    persp_proj,
     points_mapping_offset_encode,
     populate_image_from_points,
+    quat_scale_to_covar_preci,
     rasterize_to_pixels,
     rasterize_to_points,
     spherical_harmonics,
     velocity_grads,
+    world_to_cam,
 )
 from .rendering import lidar_rasterization, rasterization
 
@@ -36,6 +42,12 @@ __all__ = [
     "rasterize_to_points",
     "spherical_harmonics",
     "velocity_grads",
+    "quat_scale_to_covar_preci",
+    "world_to_cam",
+    "persp_proj",
+    "compute_pix_velocity",
+    "lidar_proj",
+    "compute_lidar_velocity",
 ]
 
 __version__ = "0.1.0"

@@ -474,6 +474,220 @@ class _FullyFusedProjectionPacked(torch.autograd.Function):
 
 
 # =============================================================================================
+# Unfused building blocks of the projection (gsplat/cuda/_wrapper.py:46-228, 1283-1493)
+# =============================================================================================
+def quat_scale_to_covar_preci(quats: Tensor, scales: Tensor, compute_covar: bool = True,
+                              compute_preci: bool = True, triu: bool = False,
+                              ) -> Tuple[Optional[Tensor], Optional[Tensor]]:
+    """Quaternions (w, x, y, z; need not be normalised) and scales -> covariance and precision
+    matrices, [N,3,3] each or [N,6] upper triangles with ``triu``."""
+    assert quats.dim() == 2 and quats.size(1) == 4, quats.size()
+    assert scales.dim() == 2 and scales.size(1) == 3, scales.size()
+    covars, precis = _QuatScaleToCovarPreci.apply(quats.contiguous(), scales.contiguous(), compute_covar,
+                                                  compute_preci, triu)
+    return covars if compute_covar else None, precis if compute_preci else None
+
+
+class _QuatScaleToCovarPreci(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, quats, scales, compute_covar, compute_preci, triu):
+        N, dev = quats.shape[0], quats.device
+        q, s = _f(quats), _f(scales)
+        shape = (N, 6) if triu else (N, 3, 3)
+        covars = torch.empty(shape, dtype=torch.float32, device=dev) if compute_covar else None
+        precis = torch.empty(shape, dtype=torch.float32, device=dev) if compute_preci else None
+        if compute_covar or compute_preci:
+            _call("splatad_quat_scale_to_covar_preci_fwd", N, _lib.ptr(q), _lib.ptr(s), int(bool(triu)),
+                  _lib.ptr(covars), _lib.ptr(precis), _lib.stream_ptr(dev))
+        ctx.save_for_backward(q, s)
+        ctx.flags = (compute_covar, compute_preci, triu)
+        # autograd wants tensors: an output that was not asked for is an empty placeholder
+        empty = torch.empty(0, device=dev)
+        return (covars if compute_covar else empty), (precis if compute_preci else empty)
+
+    @staticmethod
+    def backward(ctx, v_covars, v_precis):
+        q, s = ctx.saved_tensors
+        compute_covar, compute_preci, triu = ctx.flags
+        dev = q.device
+        vc = _f(v_covars.to_dense() if v_covars.is_sparse else v_covars) if compute_covar else None
+        vp = _f(v_precis.to_dense() if v_precis.is_sparse else v_precis) if compute_preci else None
+        v_quats, v_scales = torch.zeros_like(q), torch.zeros_like(s)
+        if compute_covar or compute_preci:
+            _call("splatad_quat_scale_to_covar_preci_bwd", q.shape[0], _lib.ptr(q), _lib.ptr(s), _lib.ptr(vc),
+                  _lib.ptr(vp), int(bool(triu)), _lib.ptr(v_quats), _lib.ptr(v_scales), _lib.stream_ptr(dev))
+        return v_quats, v_scales, None, None, None
+
+
+def world_to_cam(means: Tensor, covars: Tensor, viewmats: Tensor) -> Tuple[Tensor, Tensor]:
+    """World-frame Gaussians [N,3] / [N,3,3] -> sensor frames [C,N,3] / [C,N,3,3]."""
+    C, N = viewmats.size(0), means.size(0)
+    assert means.size() == (N, 3), means.size()
+    assert covars.size() == (N, 3, 3), covars.size()
+    assert viewmats.size() == (C, 4, 4), viewmats.size()
+    return _WorldToCam.apply(means.contiguous(), covars.contiguous(), viewmats.contiguous())
+
+
+class _WorldToCam(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, means, covars, viewmats):
+        C, N, dev = viewmats.shape[0], means.shape[0], means.device
+        m, c, v = _f(means), _f(covars), _f(viewmats)
+        means_c = torch.empty((C, N, 3), dtype=torch.float32, device=dev)
+        covars_c = torch.empty((C, N, 3, 3), dtype=torch.float32, device=dev)
+        _call("splatad_world_to_cam_fwd", C, N, _lib.ptr(m), _lib.ptr(c), _lib.ptr(v), _lib.ptr(means_c),
+              _lib.ptr(covars_c), _lib.stream_ptr(dev))
+        ctx.save_for_backward(m, c, v)
+        return means_c, covars_c
+
+    @staticmethod
+    def backward(ctx, v_means_c, v_covars_c):
+        m, c, v = ctx.saved_tensors
+        need = ctx.needs_input_grad
+        v_means = torch.zeros_like(m) if need[0] else None
+        v_covars = torch.zeros_like(c) if need[1] else None
+        v_viewmats = torch.zeros_like(v) if need[2] else None
+        _call("splatad_world_to_cam_bwd", v.shape[0], m.shape[0], _lib.ptr(m), _lib.ptr(c), _lib.ptr(v),
+              _lib.ptr(_f(v_means_c)), _lib.ptr(_f(v_covars_c)), _lib.ptr(v_means), _lib.ptr(v_covars),
+              _lib.ptr(v_viewmats), _lib.stream_ptr(m.device))
+        return v_means, v_covars, v_viewmats
+
+
+def persp_proj(means: Tensor, covars: Tensor, Ks: Tensor, width: int, height: int) -> Tuple[Tensor, Tensor]:
+    """Pinhole projection of sensor-frame Gaussians: means2d [C,N,2], covars2d [C,N,2,2]."""
+    C, N, _ = means.shape
+    assert means.shape == (C, N, 3), means.size()
+    assert covars.shape == (C, N, 3, 3), covars.size()
+    assert Ks.shape == (C, 3, 3), Ks.size()
+    return _PerspProj.apply(means.contiguous(), covars.contiguous(), Ks.contiguous(), width, height)
+
+
+class _PerspProj(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, means, covars, Ks, width, height):
+        C, N, dev = means.shape[0], means.shape[1], means.device
+        m, c, k = _f(means), _f(covars), _f(Ks)
+        means2d = torch.empty((C, N, 2), dtype=torch.float32, device=dev)
+        covars2d = torch.empty((C, N, 2, 2), dtype=torch.float32, device=dev)
+        _call("splatad_persp_proj_fwd", C, N, _lib.ptr(m), _lib.ptr(c), _lib.ptr(k), int(width), int(height),
+              _lib.ptr(means2d), _lib.ptr(covars2d), _lib.stream_ptr(dev))
+        ctx.save_for_backward(m, c, k)
+        ctx.size = (int(width), int(height))
+        return means2d, covars2d
+
+    @staticmethod
+    def backward(ctx, v_means2d, v_covars2d):
+        m, c, k = ctx.saved_tensors
+        v_means, v_covars = torch.empty_like(m), torch.empty_like(c)
+        _call("splatad_persp_proj_bwd", m.shape[0], m.shape[1], _lib.ptr(m), _lib.ptr(c), _lib.ptr(k), *ctx.size,
+              _lib.ptr(_f(v_means2d)), _lib.ptr(_f(v_covars2d)), _lib.ptr(v_means), _lib.ptr(v_covars),
+              _lib.stream_ptr(m.device))
+        return v_means, v_covars, None, None, None
+
+
+def _check_velocity_args(p_view, lin_vel, ang_vel, velocities):
+    C, N, _ = p_view.shape
+    assert p_view.shape == (C, N, 3), p_view.size()
+    assert lin_vel.shape == (C, 3), lin_vel.size()
+    assert ang_vel.shape == (C, 3), ang_vel.size()
+    assert velocities.shape == (C, N, 3), velocities.size()
+    return C, N
+
+
+def compute_pix_velocity(p_view: Tensor, lin_vel: Tensor, ang_vel: Tensor, velocities: Tensor, Ks: Tensor,
+                         width: int, height: int) -> Tensor:
+    """Velocity of sensor-frame Gaussians on the image plane, [C,N,2]: -J (lin + ang x p - v)."""
+    C, _ = _check_velocity_args(p_view, lin_vel, ang_vel, velocities)
+    assert Ks.shape == (C, 3, 3), Ks.size()
+    return _ComputePixVelocity.apply(p_view.contiguous(), lin_vel.contiguous(), ang_vel.contiguous(),
+                                     velocities.contiguous(), Ks.contiguous(), width, height)
+
+
+class _ComputePixVelocity(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, p_view, lin_vel, ang_vel, velocities, Ks, width, height):
+        C, N, dev = p_view.shape[0], p_view.shape[1], p_view.device
+        args = tuple(_f(x) for x in (p_view, lin_vel, ang_vel, velocities, Ks))
+        out = torch.empty((C, N, 2), dtype=torch.float32, device=dev)
+        _call("splatad_compute_pix_velocity_fwd", C, N, *(_lib.ptr(x) for x in args), int(width), int(height),
+              _lib.ptr(out), _lib.stream_ptr(dev))
+        ctx.save_for_backward(*args)
+        ctx.size = (int(width), int(height))
+        return out
+
+    @staticmethod
+    def backward(ctx, v_out):
+        args = ctx.saved_tensors
+        p_view, velocities = args[0], args[3]
+        v_p, v_v = torch.empty_like(p_view), torch.empty_like(velocities)
+        _call("splatad_compute_pix_velocity_bwd", p_view.shape[0], p_view.shape[1], *(_lib.ptr(x) for x in args),
+              *ctx.size, _lib.ptr(_f(v_out)), _lib.ptr(v_p), _lib.ptr(v_v), _lib.stream_ptr(p_view.device))
+        return v_p, None, None, v_v, None, None, None
+
+
+def lidar_proj(means: Tensor, covars: Tensor, eps2d: float) -> Tuple[Tensor, Tensor, Tensor]:
+    """Spherical projection of sensor-frame Gaussians: (azimuth, elevation) in degrees [C,N,2], their
+    covariance [C,N,2,2] and the depth compensation [C,N,2]."""
+    C, N, _ = means.shape
+    assert means.shape == (C, N, 3), means.size()
+    assert covars.shape == (C, N, 3, 3), covars.size()
+    return _LidarProj.apply(means.contiguous(), covars.contiguous(), eps2d)
+
+
+class _LidarProj(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, means, covars, eps2d):
+        C, N, dev = means.shape[0], means.shape[1], means.device
+        m, c = _f(means), _f(covars)
+        means2d = torch.empty((C, N, 2), dtype=torch.float32, device=dev)
+        covars2d = torch.empty((C, N, 2, 2), dtype=torch.float32, device=dev)
+        depth_comps = torch.empty((C, N, 2), dtype=torch.float32, device=dev)
+        _call("splatad_lidar_proj_fwd", C, N, _lib.ptr(m), _lib.ptr(c), float(eps2d), _lib.ptr(means2d),
+              _lib.ptr(covars2d), _lib.ptr(depth_comps), _lib.stream_ptr(dev))
+        ctx.save_for_backward(m, c)
+        ctx.eps2d = float(eps2d)
+        return means2d, covars2d, depth_comps
+
+    @staticmethod
+    def backward(ctx, v_means2d, v_covars2d, v_depth_comps):
+        m, c = ctx.saved_tensors
+        v_means, v_covars = torch.empty_like(m), torch.empty_like(c)
+        _call("splatad_lidar_proj_bwd", m.shape[0], m.shape[1], _lib.ptr(m), _lib.ptr(c), ctx.eps2d,
+              _lib.ptr(_f(v_means2d)), _lib.ptr(_f(v_covars2d)), _lib.ptr(_f(v_depth_comps)), _lib.ptr(v_means),
+              _lib.ptr(v_covars), _lib.stream_ptr(m.device))
+        return v_means, v_covars, None
+
+
+def compute_lidar_velocity(p_view: Tensor, lin_vel: Tensor, ang_vel: Tensor, velocities: Tensor) -> Tensor:
+    """Velocity of sensor-frame Gaussians in (azimuth, elevation, range), [C,N,3]."""
+    _check_velocity_args(p_view, lin_vel, ang_vel, velocities)
+    return _ComputeLidarVelocity.apply(p_view.contiguous(), lin_vel.contiguous(), ang_vel.contiguous(),
+                                       velocities.contiguous())
+
+
+class _ComputeLidarVelocity(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, p_view, lin_vel, ang_vel, velocities):
+        C, N, dev = p_view.shape[0], p_view.shape[1], p_view.device
+        args = tuple(_f(x) for x in (p_view, lin_vel, ang_vel, velocities))
+        out = torch.empty((C, N, 3), dtype=torch.float32, device=dev)
+        _call("splatad_compute_lidar_velocity_fwd", C, N, *(_lib.ptr(x) for x in args), _lib.ptr(out),
+              _lib.stream_ptr(dev))
+        ctx.save_for_backward(*args)
+        return out
+
+    @staticmethod
+    def backward(ctx, v_out):
+        args = ctx.saved_tensors
+        p_view, velocities = args[0], args[3]
+        v_p, v_v = torch.empty_like(p_view), torch.empty_like(velocities)
+        _call("splatad_compute_lidar_velocity_bwd", p_view.shape[0], p_view.shape[1],
+              *(_lib.ptr(x) for x in args), _lib.ptr(_f(v_out)), _lib.ptr(v_p), _lib.ptr(v_v),
+              _lib.stream_ptr(p_view.device))
+        return v_p, None, None, v_v
+
+
+# =============================================================================================
 # Tile intersection
 # =============================================================================================
 def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, gaussian_ids, sort,

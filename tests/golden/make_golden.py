@@ -267,6 +267,35 @@ def main():
          depth_compensations=depth_comps, raster_pts=raster_pts, width=W, height=H, threshold=0.5,
          renders=renders, alphas=alphas, alpha_sum=asum)
 
+    # ------------------------------------------------------------------ unfused ops
+    g = torch.Generator().manual_seed(110)
+    N, C = 300, 2
+    quats = torch.randn(N, 4, generator=g)
+    scales = torch.exp(torch.randn(N, 3, generator=g) * 0.5 - 1.0)
+    covars, precis = ref._quat_scale_to_covar_preci(quats, scales, True, True, False)
+    covars_triu, precis_triu = ref._quat_scale_to_covar_preci(quats, scales, True, True, True)
+    means = torch.empty(N, 3)
+    means[:, 0] = torch.rand(N, generator=g) * 30 - 15
+    means[:, 1] = torch.rand(N, generator=g) * 12 - 6
+    means[:, 2] = torch.rand(N, generator=g) * 40 + 1.0
+    viewmats = rand_rigid(g, C, spread=0.3)
+    means_c, covars_c = ref._world_to_cam(means, covars, viewmats)
+    means_c[..., 2] = means_c[..., 2].abs() + 0.5      # in front of the sensor for the pinhole ops
+    Ks = torch.tensor([[[300.0, 0.0, 160.0], [0.0, 310.0, 120.0], [0.0, 0.0, 1.0]]]).repeat(C, 1, 1)
+    W, H = 320, 240
+    lin = torch.randn(C, 3, generator=g) * 5
+    ang = torch.randn(C, 3, generator=g) * 0.2
+    vel_c = torch.randn(C, N, 3, generator=g) * 2
+    means2d, covars2d = ref._persp_proj(means_c, covars_c, Ks, W, H)
+    pix_vel = ref._compute_pix_velocity(means_c, lin, ang, vel_c, Ks, W, H)
+    l_means2d, l_covars2d, _, l_depth_comp = ref._lidar_proj(means_c, covars_c, 0.017)
+    lidar_vel = ref._compute_lidar_velocity(means_c, lin, ang, vel_c)
+    save("unfused_ops", quats=quats, scales=scales, covars=covars, precis=precis, covars_triu=covars_triu,
+         precis_triu=precis_triu, means=means, viewmats=viewmats, means_c=means_c, covars_c=covars_c, Ks=Ks,
+         width=np.int64(W), height=np.int64(H), lin=lin, ang=ang, vel_c=vel_c, means2d=means2d,
+         covars2d=covars2d, pix_vel=pix_vel, lidar_means2d=l_means2d, lidar_covars2d=l_covars2d,
+         lidar_depth_comp=l_depth_comp, lidar_vel=lidar_vel, eps2d=np.float64(0.017))
+
 
 if __name__ == "__main__":
     main()

@@ -410,6 +410,55 @@ int splatad_rasterize_to_points_bwd(
     float *v_means2d, float *v_conics, float *v_features, float *v_opacities, float *v_pix_vels,
     float *v_depth_compensations, float *v_gaussian_ranges, void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Indices of contributing (Gaussian, pixel) pairs within a range of list batches.
+ * rasterize_to_indices_in_range_tensor - gsplat/cuda/csrc/rasterization.cu:992-1090 (kernel
+ * 839-990) and rasterize_to_indices_in_range_lidar_tensor - 1264-1358 (kernel 1092-1262);
+ * Python wrappers gsplat/cuda/_wrapper.py:1115-1281.
+ *
+ * A batch is tile_size^2 (lidar: tile_width * tile_height) consecutive entries of a tile's
+ * list; batches [range_start, range_end) are walked from transmittances [C,H,W]. The
+ * reference's two kernel passes with torch.cumsum in between become two calls:
+ *   _count  counts per pixel, prefix-sums on the device and fills chunk_starts [C*H*W + 1]
+ *           (int64, exclusive, the total in the last entry); if host_total is not NULL the
+ *           total is also copied there and the stream is synchronised;
+ *   _write  fills gaussian_ids / pixel_ids / camera_ids [total] (int64; pixel_ids are row-major
+ *           inside their camera, i.e. already split the way _wrapper.py:1194-1196 does).
+ * Pairs are ordered by camera, then pixel, then list position. workspace: device memory of
+ * splatad_rasterize_to_indices_workspace_bytes(C, W, H) bytes (count pass only).
+ * ---------------------------------------------------------------------------------------- */
+size_t splatad_rasterize_to_indices_workspace_bytes(uint32_t C, uint32_t image_width,
+                                                    uint32_t image_height);
+int splatad_rasterize_to_indices_in_range_count(
+    uint32_t range_start, uint32_t range_end, uint32_t C, uint32_t N, int64_t n_isects,
+    const float *transmittances, const float *means2d, const float *conics, const float *opacities,
+    const float *pix_vels, const float *rolling_shutter_time, uint32_t image_width,
+    uint32_t image_height, uint32_t tile_size, uint32_t tile_width, uint32_t tile_height,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, void *workspace, size_t workspace_bytes,
+    int64_t *chunk_starts, int64_t *host_total, void *stream);
+int splatad_rasterize_to_indices_in_range_write(
+    uint32_t range_start, uint32_t range_end, uint32_t C, uint32_t N, int64_t n_isects,
+    const float *transmittances, const float *means2d, const float *conics, const float *opacities,
+    const float *pix_vels, const float *rolling_shutter_time, uint32_t image_width,
+    uint32_t image_height, uint32_t tile_size, uint32_t tile_width, uint32_t tile_height,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, const int64_t *chunk_starts,
+    int64_t *gaussian_ids, int64_t *pixel_ids, int64_t *camera_ids, void *stream);
+/* Lidar: raster_pts [C,H,W,4], pix_vels [C,N,3]; points with range <= 0 list nothing. */
+int splatad_rasterize_to_indices_in_range_lidar_count(
+    uint32_t range_start, uint32_t range_end, uint32_t C, uint32_t N, int64_t n_isects,
+    const float *transmittances, const float *means2d, const float *conics, const float *opacities,
+    const float *pix_vels, const float *raster_pts, uint32_t image_width, uint32_t image_height,
+    uint32_t tile_width, uint32_t tile_height, uint32_t tile_grid_width, uint32_t tile_grid_height,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, void *workspace, size_t workspace_bytes,
+    int64_t *chunk_starts, int64_t *host_total, void *stream);
+int splatad_rasterize_to_indices_in_range_lidar_write(
+    uint32_t range_start, uint32_t range_end, uint32_t C, uint32_t N, int64_t n_isects,
+    const float *transmittances, const float *means2d, const float *conics, const float *opacities,
+    const float *pix_vels, const float *raster_pts, uint32_t image_width, uint32_t image_height,
+    uint32_t tile_width, uint32_t tile_height, uint32_t tile_grid_width, uint32_t tile_grid_height,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, const int64_t *chunk_starts,
+    int64_t *gaussian_ids, int64_t *pixel_ids, int64_t *camera_ids, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -369,6 +369,87 @@ void FN(rasterize_to_points_bwd)(
     }
 }
 
+/*
+ * Indices of the (Gaussian, pixel) pairs that contribute within batches [range_start, range_end)
+ * of every tile's list, a batch being tile_w * tile_h list entries, starting from the given
+ * per-pixel transmittances. Follows gsplat/cuda/csrc/rasterization.cu:839-990 (camera) and
+ * 1092-1262 (lidar). Called twice like the reference's kernel: with chunk_starts == NULL it
+ * counts per pixel into chunk_cnts, otherwise it writes gaussian_ids (index % N) and pixel_ids
+ * (camera * H * W + row-major pixel) at chunk_starts[pixel] + k in list order.
+ */
+void FN(rasterize_to_indices_in_range)(
+    int lidar, long range_start, long range_end, int C, long N, long n_isects, const REAL *means2d,
+    const REAL *conics, const REAL *opacities, const REAL *pix_vels, const REAL *rs_time,
+    const REAL *raster_pts, int W, int H, int tile_w, int tile_h, int grid_w, int grid_h,
+    const int *offsets, const int *flatten_ids, const REAL *transmittances, const long *chunk_starts,
+    int *chunk_cnts, long *gaussian_ids, long *pixel_ids, unsigned char *ambiguous, REAL amb_tol) {
+    const long n_tiles_total = (long)C * grid_w * grid_h;
+    const long block_size = (long)tile_w * tile_h;
+    const int vstride = lidar ? 3 : 2;
+#pragma omp parallel for schedule(dynamic, 4)
+    for (long tile = 0; tile < n_tiles_total; ++tile) {
+        const int cam = (int)(tile / ((long)grid_w * grid_h));
+        const int t = (int)(tile % ((long)grid_w * grid_h));
+        const int ty = t / grid_w, tx = t % grid_w;
+        const long start = offsets[tile];
+        const long end = (tile + 1 == n_tiles_total) ? n_isects : offsets[tile + 1];
+        const long num_batches = (end - start + block_size - 1) / block_size;
+        if (range_start >= num_batches) continue;
+        const long b_end = range_end < num_batches ? range_end : num_batches;
+        const long lo = start + block_size * range_start;
+        const long hi = (start + block_size * b_end) < end ? (start + block_size * b_end) : end;
+        for (int li = 0; li < tile_h; ++li)
+            for (int lj = 0; lj < tile_w; ++lj) {
+                const int i = ty * tile_h + li, j = tx * tile_w + lj;
+                if (i >= H || j >= W) continue;
+                const long pix = ((long)cam * H + i) * W + j;
+                REAL px, py, roll;
+                if (lidar) {
+                    px = raster_pts[4 * pix];
+                    py = raster_pts[4 * pix + 1];
+                    roll = raster_pts[4 * pix + 3];
+                    if (raster_pts[4 * pix + 2] <= 0) continue;
+                } else {
+                    px = (REAL)j + (REAL)0.5;
+                    py = (REAL)i + (REAL)0.5;
+                    roll = rs_time[cam] * ((py - (REAL)0.5) / (REAL)(H - 1) - (REAL)0.5);
+                }
+                REAL T = transmittances[pix];
+                int cnt = 0;
+                unsigned char amb = 0;
+                for (long idx = lo; idx < hi; ++idx) {
+                    const long g = flatten_ids[idx];
+                    REAL dx = means2d[2 * g] + roll * pix_vels[vstride * g];
+                    REAL dy = means2d[2 * g + 1] + roll * pix_vels[vstride * g + 1];
+                    if (lidar) {
+                        dx = FN(angle_difference)(dx, px);
+                        dy = FN(angle_difference)(dy, py);
+                    } else {
+                        dx -= px;
+                        dy -= py;
+                    }
+                    const REAL ca = conics[3 * g], cb = conics[3 * g + 1], cc = conics[3 * g + 2];
+                    const REAL sigma = (REAL)0.5 * (ca * dx * dx + cc * dy * dy) + cb * dx * dy;
+                    const REAL raw = opacities[g] * EXP(-sigma);
+                    const REAL alpha = raw < ALPHA_MAX ? raw : ALPHA_MAX;
+                    if (FN(near)(raw, ALPHA_MIN, amb_tol)) amb = 1;
+                    if (sigma < 0 || alpha < ALPHA_MIN) continue;
+                    const REAL next_T = T * ((REAL)1 - alpha);
+                    if (FN(near)(next_T, T_STOP, amb_tol)) amb = 1;
+                    if (next_T <= T_STOP) break;
+                    if (chunk_starts) {
+                        gaussian_ids[chunk_starts[pix] + cnt] = g % N;
+                        pixel_ids[chunk_starts[pix] + cnt] = pix;
+                    }
+                    ++cnt;
+                    T = next_T;
+                }
+                if (!chunk_starts) chunk_cnts[pix] = cnt;
+                if (ambiguous) ambiguous[pix] = amb;
+            }
+    }
+}
+
 #undef ALPHA_MAX
 #undef ALPHA_MIN
 #undef T_STOP

@@ -19,6 +19,8 @@ from .ops import (
     points_mapping_offset_encode,
     populate_image_from_points,
     quat_scale_to_covar_preci,
+    rasterize_to_indices_in_range,
+    rasterize_to_indices_in_range_lidar,
     rasterize_to_pixels,
     rasterize_to_points,
     spherical_harmonics,
@@ -40,6 +42,8 @@ __all__ = [
     "populate_image_from_points",
     "rasterize_to_pixels",
     "rasterize_to_points",
+    "rasterize_to_indices_in_range",
+    "rasterize_to_indices_in_range_lidar",
     "spherical_harmonics",
     "velocity_grads",
     "quat_scale_to_covar_preci",

@@ -12,6 +12,7 @@ Reference functions mirrored here (file:line in carlinds/splatad):
   isect_offset_encode            gsplat/cuda/_wrapper.py:679-696
   rasterize_to_pixels            gsplat/cuda/_wrapper.py:811-949  (_RasterizeToPixels 1796-1930)
   rasterize_to_points            gsplat/cuda/_wrapper.py:951-1111 (_RasterizeToPoints 1932-2105)
+  rasterize_to_indices_in_range  gsplat/cuda/_wrapper.py:1115-1196 (lidar twin 1198-1281)
 
 Differences that are visible to a caller:
   * entries of culled (sensor, Gaussian) pairs are zero instead of uninitialised memory;
@@ -22,6 +23,7 @@ Differences that are visible to a caller:
 from __future__ import annotations
 
 import contextlib
+import ctypes
 from typing import Optional, Tuple
 
 import torch
@@ -1337,3 +1339,118 @@ class _RasterizeToPoints(torch.autograd.Function):
             v_backgrounds = (v_render_colors * (1.0 - render_alphas).float()).sum(dim=(1, 2))
         return (v_means2d, v_conics, v_colors, v_ranges, v_opacities, v_pix_vels, v_depth_comps,
                 v_backgrounds) + (None,) * 11
+
+
+# =============================================================================================
+# Indices of contributing (Gaussian, pixel) pairs
+# =============================================================================================
+_RANGE_MAX = 2 ** 32 - 1   # the range arguments are uint32 in the reference's kernels
+
+
+def _indices_in_range(kind, range_start, range_end, transmittances, means2d, conics, opacities, pix_vels,
+                      sensor, image_width, image_height, tile_w, tile_h, isect_offsets, flatten_ids):
+    C, N, _ = means2d.shape
+    dev = means2d.device
+    grid_h, grid_w = isect_offsets.shape[1:3]
+    n_isects = _n_isects_arg(isect_offsets, flatten_ids)
+    offs = isect_offsets if isect_offsets.dtype == torch.int32 and isect_offsets.is_contiguous() \
+        else isect_offsets.to(torch.int32).contiguous()
+    flat = flatten_ids.to(torch.int32).contiguous()
+    tensors = tuple(_f(x) for x in (transmittances, means2d, conics, opacities, pix_vels, sensor))
+    n_pix = C * image_height * image_width
+    empty = torch.empty(0, dtype=torch.int64, device=dev)
+    if n_pix == 0 or flat.numel() == 0:
+        return empty, empty.clone(), empty.clone()
+    lib = _lib.load()
+    ws = _lib.workspace("indices", lib.splatad_rasterize_to_indices_workspace_bytes(C, image_width, image_height), dev)
+    starts = torch.empty(n_pix + 1, dtype=torch.int64, device=dev)
+    total = ctypes.c_int64(0)
+    head = (min(max(int(range_start), 0), _RANGE_MAX), min(max(int(range_end), 0), _RANGE_MAX), C, N, n_isects,
+            *(_lib.ptr(x) for x in tensors), image_width, image_height)
+    grid = (tile_w, grid_w, grid_h) if kind == "camera" else (tile_w, tile_h, grid_w, grid_h)
+    name = "splatad_rasterize_to_indices_in_range" + ("" if kind == "camera" else "_lidar")
+    _call(name + "_count", *head, *grid, _lib.ptr(offs), _lib.ptr(flat), _lib.ptr(ws), ws.numel(),
+          _lib.ptr(starts), ctypes.addressof(total), _lib.stream_ptr(dev))
+    m = int(total.value)
+    gaussian_ids = torch.empty(m, dtype=torch.int64, device=dev)
+    pixel_ids = torch.empty(m, dtype=torch.int64, device=dev)
+    camera_ids = torch.empty(m, dtype=torch.int64, device=dev)
+    if m:
+        _call(name + "_write", *head, *grid, _lib.ptr(offs), _lib.ptr(flat), _lib.ptr(starts),
+              _lib.ptr(gaussian_ids), _lib.ptr(pixel_ids), _lib.ptr(camera_ids), _lib.stream_ptr(dev))
+    return gaussian_ids, pixel_ids, camera_ids
+
+
+@torch.no_grad()
+def rasterize_to_indices_in_range(
+    range_start: int,
+    range_end: int,
+    transmittances: Tensor,  # [C, image_height, image_width]
+    means2d: Tensor,  # [C, N, 2]
+    conics: Tensor,  # [C, N, 3]
+    opacities: Tensor,  # [C, N]
+    pix_vels: Tensor,  # [C, N, 2]
+    image_width: int,
+    image_height: int,
+    tile_size: int,
+    isect_offsets: Tensor,  # [C, tile_height, tile_width]
+    flatten_ids: Tensor,  # [n_isects]
+    rolling_shutter_time: Optional[Tensor] = None,  # [C]
+) -> Tuple[Tensor, Tensor, Tensor]:
+    """Lists the (Gaussian, pixel, camera) triples that contribute to the image within list batches
+    ``[range_start, range_end)`` (a batch is ``tile_size ** 2`` entries of a tile's list), starting
+    from the given transmittances: ``gsplat.cuda._wrapper.rasterize_to_indices_in_range``
+    (gsplat/cuda/_wrapper.py:1115-1196). Returns int64 (gaussian_ids, pixel_ids, camera_ids), each
+    [M], ordered by camera, pixel (row-major) and list position."""
+    C, N, _ = means2d.shape
+    assert conics.shape == (C, N, 3), conics.shape
+    assert opacities.shape == (C, N), opacities.shape
+    assert isect_offsets.shape[0] == C, isect_offsets.shape
+    assert pix_vels.shape == (C, N, 2), pix_vels.shape
+    assert transmittances.shape == (C, image_height, image_width), transmittances.shape
+    if rolling_shutter_time is not None:
+        assert rolling_shutter_time.shape == (C,), rolling_shutter_time.shape
+    else:
+        rolling_shutter_time = torch.zeros(C, device=means2d.device)
+    tile_height, tile_width = isect_offsets.shape[1:3]
+    assert tile_height * tile_size >= image_height, f"Assert Failed: {tile_height} * {tile_size} >= {image_height}"
+    assert tile_width * tile_size >= image_width, f"Assert Failed: {tile_width} * {tile_size} >= {image_width}"
+    return _indices_in_range("camera", range_start, range_end, transmittances, means2d, conics, opacities,
+                             pix_vels, rolling_shutter_time, image_width, image_height, tile_size, tile_size,
+                             isect_offsets, flatten_ids)
+
+
+@torch.no_grad()
+def rasterize_to_indices_in_range_lidar(
+    range_start: int,
+    range_end: int,
+    transmittances: Tensor,  # [C, image_height, image_width]
+    means2d: Tensor,  # [C, N, 2]
+    conics: Tensor,  # [C, N, 3]
+    opacities: Tensor,  # [C, N]
+    pix_vels: Tensor,  # [C, N, 3]
+    raster_pts: Tensor,  # [C, image_height, image_width, 4]
+    image_width: int,
+    image_height: int,
+    tile_width: int,
+    tile_height: int,
+    isect_offsets: Tensor,  # [C, tile grid height, tile grid width]
+    flatten_ids: Tensor,  # [n_isects]
+) -> Tuple[Tensor, Tensor, Tensor]:
+    """Lidar twin of :func:`rasterize_to_indices_in_range` (gsplat/cuda/_wrapper.py:1198-1281): a
+    batch is ``tile_width * tile_height`` entries, points with range <= 0 list nothing."""
+    C, N, _ = means2d.shape
+    assert conics.shape == (C, N, 3), conics.shape
+    assert opacities.shape == (C, N), opacities.shape
+    assert isect_offsets.shape[0] == C, isect_offsets.shape
+    assert pix_vels.shape == (C, N, 3), pix_vels.shape
+    assert transmittances.shape == (C, image_height, image_width), transmittances.shape
+    assert raster_pts.shape == (C, image_height, image_width, 4), raster_pts.shape
+    tile_grid_height, tile_grid_width = isect_offsets.shape[1:3]
+    assert tile_grid_height * tile_height >= image_height, \
+        f"Assert Failed: {tile_grid_height} * {tile_height} >= {image_height}"
+    assert tile_grid_width * tile_width >= image_width, \
+        f"Assert Failed: {tile_grid_width} * {tile_width} >= {image_width}"
+    return _indices_in_range("lidar", range_start, range_end, transmittances, means2d, conics, opacities,
+                             pix_vels, raster_pts, image_width, image_height, tile_width, tile_height,
+                             isect_offsets, flatten_ids)

@@ -459,6 +459,26 @@ int splatad_rasterize_to_indices_in_range_lidar_write(
     const int32_t *tile_offsets, const int32_t *flatten_ids, const int64_t *chunk_starts,
     int64_t *gaussian_ids, int64_t *pixel_ids, int64_t *camera_ids, void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Densification hooks: what the training strategies do with the render path's outputs.
+ * ---------------------------------------------------------------------------------------- */
+
+/* DefaultStrategy._update_state - gsplat/strategy/default.py:203-258, fused. grads [total,2] is
+ * means2d.grad or means2d.absgrad, radii [total,2] int32. gaussian_ids NULL: the [C,N] layout
+ * (total = C * N; entries with radii[.,0] > 0 take part, Gaussian = entry % N); otherwise the
+ * packed layout (int64 [total]). Accumulates into grad2d [N], count [N] and, unless NULL,
+ * radii_state [N] (a true maximum, normalised by max(width, height)). */
+int splatad_densify_update_state(
+    uint64_t total, uint32_t N, const float *grads, const int32_t *radii, const int64_t *gaussian_ids,
+    uint32_t image_width, uint32_t image_height, uint32_t n_cameras, float *grad2d, float *count,
+    float *radii_state, void *stream);
+
+/* compute_relocation_tensor - gsplat/cuda/csrc/relocation.cu:33-53 (kernel 4-31). ratios int32
+ * [N] (clamped to 1..n_max), binoms [n_max,n_max]; outputs new_opacities [N], new_scales [N,3]. */
+int splatad_compute_relocation(uint32_t N, const float *opacities, const float *scales,
+                               const int32_t *ratios, const float *binoms, int32_t n_max,
+                               float *new_opacities, float *new_scales, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -27,6 +27,7 @@ from .ops import (
     velocity_grads,
     world_to_cam,
 )
+from .densify import compute_relocation
 from .rendering import lidar_rasterization, rasterization
 
 __all__ = [
@@ -52,6 +53,7 @@ __all__ = [
     "compute_pix_velocity",
     "lidar_proj",
     "compute_lidar_velocity",
+    "compute_relocation",
 ]
 
 __version__ = "0.1.0"

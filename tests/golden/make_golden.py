@@ -297,5 +297,47 @@ def main():
          lidar_depth_comp=l_depth_comp, lidar_vel=lidar_vel, eps2d=np.float64(0.017))
 
 
+    # ------------------------------------------------------------------ densification statistics
+    # DefaultStrategy._update_state (gsplat/strategy/default.py:203-258) is pure torch: two frames
+    # accumulated in the [C, N] layout (grad and absgrad), and one in the packed layout whose
+    # Gaussian ids are unique, so that the reference's indexed radii assignment is well defined
+    # (it keeps an arbitrary candidate when a Gaussian appears twice).
+    from gsplat.strategy.default import DefaultStrategy
+
+    g = torch.Generator().manual_seed(120)
+    C, N, W, H = 3, 400, 320, 200
+    out = {}
+    for absgrad in (False, True):
+        strat = DefaultStrategy(absgrad=absgrad, refine_scale2d_stop_iter=0)
+        state = strat.initialize_state()
+        params = {"means": torch.zeros(N, 3)}
+        for frame in range(2):
+            radii = torch.randint(0, 40, (C, N, 2), generator=g, dtype=torch.int32)
+            radii[torch.rand(C, N, generator=g) < 0.4] = 0
+            means2d = torch.randn(C, N, 2, generator=g)
+            means2d.grad = torch.randn(C, N, 2, generator=g) * 1e-3
+            means2d.absgrad = means2d.grad.abs() * 1.5
+            info = dict(width=W, height=H, n_cameras=C, radii=radii, gaussian_ids=None, means2d=means2d)
+            strat._update_state(params, state, info, packed=False)
+            tag = f"{'abs' if absgrad else 'grad'}_f{frame}"
+            out.update({f"{tag}_radii": radii, f"{tag}_grads": means2d.absgrad if absgrad else means2d.grad,
+                        f"{tag}_grad2d": state["grad2d"].clone(), f"{tag}_count": state["count"].clone()})
+    strat = DefaultStrategy(absgrad=False, refine_scale2d_stop_iter=1000)
+    state = strat.initialize_state()
+    for frame in range(2):
+        nnz = 250
+        ids = torch.randperm(N, generator=g)[:nnz]
+        radii = torch.randint(1, 60, (nnz, 2), generator=g, dtype=torch.int32)
+        means2d = torch.randn(nnz, 2, generator=g)
+        means2d.grad = torch.randn(nnz, 2, generator=g) * 1e-3
+        info = dict(width=W, height=H, n_cameras=C, radii=radii, gaussian_ids=ids, means2d=means2d)
+        strat._update_state({"means": torch.zeros(N, 3)}, state, info, packed=True)
+        tag = f"packed_f{frame}"
+        out.update({f"{tag}_radii": radii, f"{tag}_grads": means2d.grad, f"{tag}_ids": ids,
+                    f"{tag}_grad2d": state["grad2d"].clone(), f"{tag}_count": state["count"].clone(),
+                    f"{tag}_state_radii": state["radii"].clone()})
+    save("densify_state", C=np.int64(C), N=np.int64(N), width=np.int64(W), height=np.int64(H), **out)
+
+
 if __name__ == "__main__":
     main()

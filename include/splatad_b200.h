@@ -188,6 +188,32 @@ int splatad_sh_bwd(uint32_t n_elems, uint32_t K, uint32_t degrees_to_use, const 
                    const float *coeffs, const uint8_t *masks, const float *v_colors,
                    float *v_coeffs, float *v_dirs, void *stream);
 
+/* Camera centres campos [C,3] = inverse(viewmats)[:, :3, 3] (general 4 x 4 inverse by cofactors,
+ * evaluated in double): what gsplat/rendering.py:345 takes from torch.inverse(viewmats). */
+int splatad_camera_centers(uint32_t C, const float *viewmats, float *campos, void *stream);
+
+/* View-dependent colours of the projected Gaussians in one pass - the torch chain around the SH
+ * kernel in gsplat/rendering.py:345-373 (gathers by the packed ids, directions = means - camera
+ * centres, spherical_harmonics with the radii mask, + 0.5, clamp at 0, depth appended for the
+ * "+D" render modes). Entry e is (camera_ids[e], gaussian_ids[e]) (packed, int64) or
+ * (e / N, e % N) (both NULL, n_elems = C * N). coeffs is [N,K,3], or [C,N,K,3] when
+ * coeffs_per_camera != 0; campos [C,3]; radii [n_elems,2] int32; colors [n_elems,out_channels]
+ * with out_channels 3, or 4 (then depths [n_elems] is the last channel). Entries with
+ * radii[e][0] <= 0 hold 0.5 (the reference: uninitialised memory + 0.5). */
+int splatad_sh_colors_fwd(uint32_t n_elems, uint32_t N, uint32_t K, uint32_t degrees_to_use,
+                          const float *means, const float *campos, const float *coeffs,
+                          uint32_t coeffs_per_camera, const int64_t *camera_ids,
+                          const int64_t *gaussian_ids, const int32_t *radii, const float *depths,
+                          uint32_t out_channels, float *colors, void *stream);
+/* VJP: v_coeffs (shape of coeffs), v_means [N,3] and v_campos [C,3] are accumulated with atomics
+ * (zero-initialise them), v_depths [n_elems] is overwritten; each may be NULL. */
+int splatad_sh_colors_bwd(uint32_t n_elems, uint32_t N, uint32_t K, uint32_t degrees_to_use,
+                          const float *means, const float *campos, const float *coeffs,
+                          uint32_t coeffs_per_camera, const int64_t *camera_ids,
+                          const int64_t *gaussian_ids, const int32_t *radii,
+                          uint32_t out_channels, const float *v_colors, float *v_coeffs,
+                          float *v_means, float *v_campos, float *v_depths, void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * Unfused building blocks of the projection (exported by the reference as separate ops,
  * gsplat/__init__.py:4-18). All tensors FP32 row-major; gradient outputs are written (not

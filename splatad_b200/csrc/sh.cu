@@ -267,9 +267,310 @@ sh_bwd_kernel(uint32_t n_elems, uint32_t K, int degree, const float *__restrict_
     stage_rows_out(v_coeffs + (size_t)e0 * row, sm, n, row);
 }
 
+// ---------------------------------------------------------------------------------------
+// View-dependent colours of the projected Gaussians in one pass: what the reference's
+// rasterization() builds from a chain of torch ops around its SH kernel
+// (gsplat/rendering.py:345-373: gather means / camera centres / coefficients by the packed ids,
+// directions, spherical_harmonics, + 0.5, clamp at 0, concatenation of the depth channel).
+// Entry e is (camera_ids[e], gaussian_ids[e]) in the packed layout and (e / N, e % N) in the
+// dense one; entries with radii[e][0] <= 0 produce zeros and read no coefficients.
+// ---------------------------------------------------------------------------------------
+struct ShColorArgs {
+    uint32_t n_elems, N, K;
+    int degree;
+    const float *means;         // [N, 3]
+    const float *campos;        // [C, 3]
+    const float *coeffs;        // [N, K, 3] or [C, N, K, 3]
+    uint32_t coeffs_per_camera;
+    const int64_t *camera_ids, *gaussian_ids;   // packed layout, else null
+    const int32_t *radii;       // [n_elems, 2]
+    const float *depths;        // [n_elems] or null
+    uint32_t out_channels;      // 3, or 4 with the depth as last channel
+};
+
+__device__ __forceinline__ void sh_entry(const ShColorArgs &a, size_t e, uint32_t &cam, uint32_t &g) {
+    if (a.gaussian_ids) {
+        cam = (uint32_t)a.camera_ids[e];
+        g = (uint32_t)a.gaussian_ids[e];
+    } else {
+        cam = (uint32_t)(e / a.N);
+        g = (uint32_t)(e - (size_t)cam * a.N);
+    }
+}
+
+// Gathers the first nfl floats of the coefficient rows listed in rows[0 .. n) (negative = skip)
+// into shared memory with row stride row + 1.
+__device__ __forceinline__ void stage_rows_gather(const float *__restrict__ coeffs, const int64_t *rows,
+                                                  float *smem, uint32_t n, uint32_t row, uint32_t nfl) {
+    if ((row & 3u) == 0 && (nfl & 3u) == 0 && (reinterpret_cast<uintptr_t>(coeffs) & 15u) == 0) {
+        const uint32_t per_row = nfl >> 2;
+        for (uint32_t i = threadIdx.x; i < n * per_row; i += blockDim.x) {
+            const uint32_t r = i / per_row, q = i - r * per_row;
+            const int64_t src = rows[r];
+            if (src < 0) continue;
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(coeffs + (size_t)src * row) + q);
+            float *d = smem + r * (row + 1) + 4 * q;
+            d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < n * nfl; i += blockDim.x) {
+            const uint32_t r = i / nfl, q = i - r * nfl;
+            const int64_t src = rows[r];
+            if (src < 0) continue;
+            smem[r * (row + 1) + q] = __ldg(coeffs + (size_t)src * row + q);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kShThreads)
+sh_colors_fwd_kernel(const ShColorArgs a, float *__restrict__ colors) {
+    extern __shared__ __align__(16) float sm[];   // [kShThreads][3K+1] floats, then the row indices
+    const uint32_t row = 3 * a.K;
+    int64_t *rows = reinterpret_cast<int64_t *>(sm + ((kShThreads * (row + 1) + 1) & ~1u));
+    const uint32_t e0 = blockIdx.x * kShThreads;
+    const uint32_t n = min((uint32_t)kShThreads, a.n_elems - e0);
+    const uint32_t t = threadIdx.x;
+    const size_t e = (size_t)e0 + t;
+    const int nb = (a.degree + 1) * (a.degree + 1);
+    bool active = false;
+    float dx = 0.f, dy = 0.f, dz = 1.f;
+    if (t < n) {
+        uint32_t cam, g;
+        sh_entry(a, e, cam, g);
+        active = a.radii[2 * e] > 0;
+        rows[t] = active ? (int64_t)(a.coeffs_per_camera ? (size_t)cam * a.N + g : g) : -1;
+        if (active) {
+            dx = a.means[3 * (size_t)g] - a.campos[3 * cam];
+            dy = a.means[3 * (size_t)g + 1] - a.campos[3 * cam + 1];
+            dz = a.means[3 * (size_t)g + 2] - a.campos[3 * cam + 2];
+        }
+    }
+    __syncthreads();
+    stage_rows_gather(a.coeffs, rows, sm, n, row, 3 * nb);
+    __syncthreads();
+    if (t >= n) return;
+    float r = 0.f, gg = 0.f, bl = 0.f;
+    if (active) {
+        const float inorm = rsqrtf(dx * dx + dy * dy + dz * dz);
+        float b[kShMaxBases];
+        sh_bases(a.degree, dx * inorm, dy * inorm, dz * inorm, b);
+        const float *c = sm + t * (row + 1);
+#pragma unroll
+        for (int i = 0; i < kShMaxBases; ++i)
+            if (i < nb) {
+                r += b[i] * c[3 * i];
+                gg += b[i] * c[3 * i + 1];
+                bl += b[i] * c[3 * i + 2];
+            }
+    }
+    // + 0.5 and the clamp at zero apply to every entry, culled ones included (they hold 0 + 0.5)
+    float *o = colors + e * a.out_channels;
+    o[0] = fmaxf(r + 0.5f, 0.f);
+    o[1] = fmaxf(gg + 0.5f, 0.f);
+    o[2] = fmaxf(bl + 0.5f, 0.f);
+    if (a.out_channels == 4) o[3] = a.depths[e];
+}
+
+// VJP of the above. v_coeffs / v_means / v_campos are accumulated with atomics (zero-initialise);
+// v_depths [n_elems] is overwritten. Any of them may be null.
+__global__ void __launch_bounds__(kShThreads)
+sh_colors_bwd_kernel(const ShColorArgs a, const float *__restrict__ v_colors, float *__restrict__ v_coeffs,
+                     float *__restrict__ v_means, float *__restrict__ v_campos, float *__restrict__ v_depths) {
+    extern __shared__ __align__(16) float sm[];
+    const uint32_t row = 3 * a.K;
+    int64_t *rows = reinterpret_cast<int64_t *>(sm + ((kShThreads * (row + 1) + 1) & ~1u));
+    const uint32_t e0 = blockIdx.x * kShThreads;
+    const uint32_t n = min((uint32_t)kShThreads, a.n_elems - e0);
+    const uint32_t t = threadIdx.x;
+    const size_t e = (size_t)e0 + t;
+    const int nb = (a.degree + 1) * (a.degree + 1);
+    bool active = false;
+    uint32_t cam = 0, g = 0;
+    float dx = 0.f, dy = 0.f, dz = 1.f;
+    if (t < n) {
+        sh_entry(a, e, cam, g);
+        active = a.radii[2 * e] > 0;
+        rows[t] = active ? (int64_t)(a.coeffs_per_camera ? (size_t)cam * a.N + g : g) : -1;
+        if (active) {
+            dx = a.means[3 * (size_t)g] - a.campos[3 * cam];
+            dy = a.means[3 * (size_t)g + 1] - a.campos[3 * cam + 1];
+            dz = a.means[3 * (size_t)g + 2] - a.campos[3 * cam + 2];
+        }
+        if (v_depths) v_depths[e] = a.out_channels == 4 ? v_colors[e * a.out_channels + 3] : 0.f;
+    }
+    __syncthreads();
+    stage_rows_gather(a.coeffs, rows, sm, n, row, 3 * nb);
+    __syncthreads();
+    float gx = 0.f, gy = 0.f, gz = 0.f;
+    if (active) {
+        const float inorm = rsqrtf(dx * dx + dy * dy + dz * dz);
+        const float x = dx * inorm, y = dy * inorm, z = dz * inorm;
+        float b[kShMaxBases];
+        sh_bases(a.degree, x, y, z, b);
+        const float *c = sm + t * (row + 1);
+        float r = 0.f, gg = 0.f, bl = 0.f;
+#pragma unroll
+        for (int i = 0; i < kShMaxBases; ++i)
+            if (i < nb) {
+                r += b[i] * c[3 * i];
+                gg += b[i] * c[3 * i + 1];
+                bl += b[i] * c[3 * i + 2];
+            }
+        // the clamp passes the gradient where its input is >= 0, like torch.clamp_min
+        const float *vc = v_colors + e * a.out_channels;
+        const float vr = (r + 0.5f >= 0.f) ? vc[0] : 0.f;
+        const float vg = (gg + 0.5f >= 0.f) ? vc[1] : 0.f;
+        const float vb = (bl + 0.5f >= 0.f) ? vc[2] : 0.f;
+        if (v_means || v_campos) {
+            float bx[kShMaxBases], by[kShMaxBases], bz[kShMaxBases];
+            sh_bases_grad(a.degree, x, y, z, bx, by, bz);
+#pragma unroll
+            for (int i = 0; i < kShMaxBases; ++i)
+                if (i < nb) {
+                    const float w = vr * c[3 * i] + vg * c[3 * i + 1] + vb * c[3 * i + 2];
+                    gx += bx[i] * w; gy += by[i] * w; gz += bz[i] * w;
+                }
+            const float d = gx * x + gy * y + gz * z;
+            gx = (gx - d * x) * inorm;
+            gy = (gy - d * y) * inorm;
+            gz = (gz - d * z) * inorm;
+            if (v_means) {
+                atomicAdd(v_means + 3 * (size_t)g, gx);
+                atomicAdd(v_means + 3 * (size_t)g + 1, gy);
+                atomicAdd(v_means + 3 * (size_t)g + 2, gz);
+            }
+        }
+        if (v_coeffs) {
+            float *vrow = v_coeffs + (size_t)rows[t] * row;
+#pragma unroll
+            for (int i = 0; i < kShMaxBases; ++i)
+                if (i < nb) {
+                    atomicAdd(vrow + 3 * i, b[i] * vr);
+                    atomicAdd(vrow + 3 * i + 1, b[i] * vg);
+                    atomicAdd(vrow + 3 * i + 2, b[i] * vb);
+                }
+        }
+    }
+    if (v_campos) {
+        // d dirs / d campos = -1: one atomic per warp when its lanes share a camera
+        const uint32_t cam0 = __shfl_sync(0xffffffffu, cam, 0);
+        if (__all_sync(0xffffffffu, cam == cam0 || !active)) {
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                gx += __shfl_xor_sync(0xffffffffu, gx, off);
+                gy += __shfl_xor_sync(0xffffffffu, gy, off);
+                gz += __shfl_xor_sync(0xffffffffu, gz, off);
+            }
+            // lane 0 may be inactive with cam = 0: take the camera of any active lane
+            const uint32_t act = __ballot_sync(0xffffffffu, active);
+            if (act) {
+                const uint32_t camw = __shfl_sync(0xffffffffu, cam, __ffs(act) - 1);
+                if ((threadIdx.x & 31) == 0) {
+                    atomicAdd(v_campos + 3 * camw, -gx);
+                    atomicAdd(v_campos + 3 * camw + 1, -gy);
+                    atomicAdd(v_campos + 3 * camw + 2, -gz);
+                }
+            }
+        } else if (active) {
+            atomicAdd(v_campos + 3 * cam, -gx);
+            atomicAdd(v_campos + 3 * cam + 1, -gy);
+            atomicAdd(v_campos + 3 * cam + 2, -gz);
+        }
+    }
+}
+
+// Camera centres in world coordinates, the translation column of inverse(viewmat), by cofactors
+// in double precision (the general 4 x 4 inverse: the last row need not be 0 0 0 1).
+__global__ void camera_centers_kernel(uint32_t C, const float *__restrict__ viewmats, float *__restrict__ campos) {
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    double m[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) m[i][j] = (double)viewmats[16 * (size_t)c + 4 * i + j];
+    // cof[j] = cofactor of m[3][j]: (-1)^(3 + j) times the minor of the first three rows without column j
+    double cof[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int c0 = j == 0 ? 1 : 0, c1 = j <= 1 ? 2 : 1, c2 = j <= 2 ? 3 : 2;
+        const double minor = m[0][c0] * (m[1][c1] * m[2][c2] - m[1][c2] * m[2][c1]) -
+                             m[0][c1] * (m[1][c0] * m[2][c2] - m[1][c2] * m[2][c0]) +
+                             m[0][c2] * (m[1][c0] * m[2][c1] - m[1][c1] * m[2][c0]);
+        cof[j] = ((3 + j) & 1) ? -minor : minor;
+    }
+    const double det = m[3][0] * cof[0] + m[3][1] * cof[1] + m[3][2] * cof[2] + m[3][3] * cof[3];
+    // inverse[i][3] = cofactor(3, i) / det
+#pragma unroll
+    for (int i = 0; i < 3; ++i) campos[3 * (size_t)c + i] = (float)(cof[i] / det);
+}
+
+static size_t sh_colors_smem(uint32_t K) {
+    return sizeof(float) * ((kShThreads * (3 * K + 1) + 1) & ~1u) + sizeof(int64_t) * kShThreads;
+}
+
+static int sh_colors_check(const ShColorArgs &a, const char *what) {
+    SPL_REQUIRE(a.degree >= 0 && a.degree <= 4, SPLATAD_ERR_BAD_ARG, "%s: degree must be <= 4", what);
+    SPL_REQUIRE((uint32_t)((a.degree + 1) * (a.degree + 1)) <= a.K, SPLATAD_ERR_BAD_ARG,
+                "%s: K too small for the degree", what);
+    SPL_REQUIRE(a.out_channels == 3 || (a.out_channels == 4 && a.depths), SPLATAD_ERR_BAD_ARG,
+                "%s: 3 channels, or 4 with depths", what);
+    SPL_REQUIRE(a.means && a.campos && a.coeffs && a.radii && a.N > 0, SPLATAD_ERR_BAD_ARG,
+                "%s: null argument", what);
+    SPL_REQUIRE((a.camera_ids == nullptr) == (a.gaussian_ids == nullptr), SPLATAD_ERR_BAD_ARG,
+                "%s: camera_ids and gaussian_ids go together", what);
+    SPL_REQUIRE(sh_colors_smem(a.K) <= 200 * 1024, SPLATAD_ERR_BAD_ARG, "%s: K too large", what);
+    return SPLATAD_OK;
+}
+
 } // namespace splatad
 
 using namespace splatad;
+extern "C" int splatad_sh_colors_fwd(uint32_t n_elems, uint32_t N, uint32_t K, uint32_t degrees_to_use,
+                                     const float *means, const float *campos, const float *coeffs,
+                                     uint32_t coeffs_per_camera, const int64_t *camera_ids,
+                                     const int64_t *gaussian_ids, const int32_t *radii, const float *depths,
+                                     uint32_t out_channels, float *colors, void *stream) {
+    if (n_elems == 0) return SPLATAD_OK;
+    const ShColorArgs a = {n_elems, N, K, (int)degrees_to_use, means, campos, coeffs, coeffs_per_camera,
+                           camera_ids, gaussian_ids, radii, depths, out_channels};
+    int rc = sh_colors_check(a, "sh_colors_fwd");
+    if (rc != SPLATAD_OK) return rc;
+    SPL_REQUIRE(colors, SPLATAD_ERR_BAD_ARG, "sh_colors_fwd: null output");
+    const size_t smem = sh_colors_smem(K);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(sh_colors_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        SPL_PROF("sh_colors_fwd_kernel", (cudaStream_t)stream);
+        sh_colors_fwd_kernel<<<div_up(n_elems, kShThreads), kShThreads, smem, (cudaStream_t)stream>>>(a, colors);
+    }
+    return check_launch("sh_colors_fwd");
+}
+
+extern "C" int splatad_sh_colors_bwd(uint32_t n_elems, uint32_t N, uint32_t K, uint32_t degrees_to_use,
+                                     const float *means, const float *campos, const float *coeffs,
+                                     uint32_t coeffs_per_camera, const int64_t *camera_ids,
+                                     const int64_t *gaussian_ids, const int32_t *radii,
+                                     uint32_t out_channels, const float *v_colors, float *v_coeffs,
+                                     float *v_means, float *v_campos, float *v_depths, void *stream) {
+    if (n_elems == 0) return SPLATAD_OK;
+    // the depth values are not needed for the VJP: any non-null pointer satisfies the check
+    const ShColorArgs a = {n_elems, N, K, (int)degrees_to_use, means, campos, coeffs, coeffs_per_camera,
+                           camera_ids, gaussian_ids, radii, out_channels == 4 ? means : nullptr, out_channels};
+    int rc = sh_colors_check(a, "sh_colors_bwd");
+    if (rc != SPLATAD_OK) return rc;
+    SPL_REQUIRE(v_colors, SPLATAD_ERR_BAD_ARG, "sh_colors_bwd: null argument");
+    const size_t smem = sh_colors_smem(K);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(sh_colors_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    {
+        SPL_PROF("sh_colors_bwd_kernel", (cudaStream_t)stream);
+        sh_colors_bwd_kernel<<<div_up(n_elems, kShThreads), kShThreads, smem, (cudaStream_t)stream>>>(
+            a, v_colors, v_coeffs, v_means, v_campos, v_depths);
+    }
+    return check_launch("sh_colors_bwd");
+}
+
 
 extern "C" int splatad_sh_fwd(uint32_t n_elems, uint32_t K, uint32_t degrees_to_use,
                               const float *dirs, const float *coeffs, const uint8_t *masks,
@@ -310,4 +611,11 @@ extern "C" int splatad_sh_bwd(uint32_t n_elems, uint32_t K, uint32_t degrees_to_
             n_elems, K, (int)degrees_to_use, dirs, coeffs, masks, v_colors, v_coeffs, v_dirs);
     }
     return check_launch("sh_bwd");
+}
+
+extern "C" int splatad_camera_centers(uint32_t C, const float *viewmats, float *campos, void *stream) {
+    if (C == 0) return SPLATAD_OK;
+    SPL_REQUIRE(viewmats && campos, SPLATAD_ERR_BAD_ARG, "camera_centers: null argument");
+    camera_centers_kernel<<<div_up(C, 64), 64, 0, (cudaStream_t)stream>>>(C, viewmats, campos);
+    return check_launch("camera_centers");
 }

@@ -116,6 +116,104 @@ class _SphericalHarmonics(torch.autograd.Function):
         return None, v_dirs, v_coeffs, None
 
 
+def camera_centers(viewmats: Tensor) -> Tensor:
+    """Camera centres in world coordinates, ``torch.inverse(viewmats)[:, :3, 3]`` ([C, 3]) from one
+    tiny kernel (cofactors in double precision) instead of a batched LU with its error-check round
+    trip to the host; differentiable with respect to ``viewmats``."""
+    assert viewmats.dim() == 3 and viewmats.shape[1:] == (4, 4), viewmats.shape
+    return _CameraCenters.apply(viewmats)
+
+
+class _CameraCenters(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, viewmats):
+        viewmats = _f(viewmats)
+        campos = torch.empty((viewmats.shape[0], 3), dtype=torch.float32, device=viewmats.device)
+        _call("splatad_camera_centers", viewmats.shape[0], _lib.ptr(viewmats), _lib.ptr(campos),
+              _lib.stream_ptr(viewmats.device))
+        ctx.save_for_backward(viewmats)
+        return campos
+
+    @staticmethod
+    def backward(ctx, v_campos):
+        # Y = A^-1: dA = -Y^T dY Y^T with dY zero except for its translation column
+        (viewmats,) = ctx.saved_tensors
+        inv = torch.linalg.inv_ex(viewmats).inverse
+        v_inv = torch.zeros_like(viewmats)
+        v_inv[:, :3, 3] = v_campos
+        return -inv.transpose(1, 2) @ v_inv @ inv.transpose(1, 2)
+
+
+def view_dependent_colors(
+    sh_degree: int,
+    means: Tensor,  # [N, 3]
+    campos: Tensor,  # [C, 3] camera centres in world coordinates
+    coeffs: Tensor,  # [N, K, 3] or [C, N, K, 3]
+    radii: Tensor,  # [C, N, 2] or [nnz, 2]
+    camera_ids: Optional[Tensor] = None,  # [nnz] (packed layout)
+    gaussian_ids: Optional[Tensor] = None,  # [nnz]
+    depths: Optional[Tensor] = None,  # [C, N] or [nnz]: appended as a fourth channel
+) -> Tensor:
+    """Colours of the projected Gaussians seen from their cameras, ``clamp_min(SH(dirs) + 0.5, 0)``
+    with ``dirs = means - camera centre``, in one kernel; with ``depths`` the result carries the
+    depth as last channel. This is the chain of gathers and elementwise torch ops around the SH
+    kernel in the reference's ``rasterization()`` (gsplat/rendering.py:345-373, 383-384) - same
+    values, same gradients (means, campos, coeffs, depths) - without materialising the gathered
+    ``[nnz, K, 3]`` coefficients. Returns [C, N, 3|4] or [nnz, 3|4]."""
+    N = means.shape[0]
+    assert means.shape == (N, 3), means.shape
+    C = campos.shape[0]
+    assert campos.shape == (C, 3), campos.shape
+    assert coeffs.shape[-1] == 3 and (sh_degree + 1) ** 2 <= coeffs.shape[-2], coeffs.shape
+    assert (coeffs.dim() == 3 and coeffs.shape[0] == N) or (coeffs.dim() == 4 and coeffs.shape[:2] == (C, N)), \
+        coeffs.shape
+    packed = gaussian_ids is not None
+    if packed:
+        assert camera_ids is not None and radii.shape == (gaussian_ids.numel(), 2), radii.shape
+    else:
+        assert radii.shape == (C, N, 2), radii.shape
+    if depths is not None:
+        assert depths.shape == radii.shape[:-1], depths.shape
+    return _ViewDependentColors.apply(sh_degree, means, campos, coeffs, depths, radii, camera_ids, gaussian_ids)
+
+
+class _ViewDependentColors(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, sh_degree, means, campos, coeffs, depths, radii, camera_ids, gaussian_ids):
+        means, campos, coeffs = _f(means), _f(campos), _f(coeffs)
+        depths = _f(depths)
+        radii = radii.to(torch.int32).contiguous()
+        if gaussian_ids is not None:
+            camera_ids = camera_ids.to(torch.int64).contiguous()
+            gaussian_ids = gaussian_ids.to(torch.int64).contiguous()
+        N, K = means.shape[0], coeffs.shape[-2]
+        out_ch = 3 if depths is None else 4
+        colors = torch.empty(radii.shape[:-1] + (out_ch,), dtype=torch.float32, device=means.device)
+        n_elems = radii.numel() // 2
+        _call("splatad_sh_colors_fwd", n_elems, N, K, sh_degree, _lib.ptr(means), _lib.ptr(campos),
+              _lib.ptr(coeffs), int(coeffs.dim() == 4), _lib.ptr(camera_ids), _lib.ptr(gaussian_ids),
+              _lib.ptr(radii), _lib.ptr(depths), out_ch, _lib.ptr(colors), _lib.stream_ptr(means.device))
+        ctx.save_for_backward(means, campos, coeffs, radii, camera_ids, gaussian_ids)
+        ctx.sh_degree, ctx.out_ch = sh_degree, out_ch
+        return colors
+
+    @staticmethod
+    def backward(ctx, v_colors):
+        means, campos, coeffs, radii, camera_ids, gaussian_ids = ctx.saved_tensors
+        N, K = means.shape[0], coeffs.shape[-2]
+        need_means, need_campos, need_coeffs, need_depths = ctx.needs_input_grad[1:5]
+        v_means = torch.zeros_like(means) if need_means else None
+        v_campos = torch.zeros_like(campos) if need_campos else None
+        v_coeffs = torch.zeros_like(coeffs) if need_coeffs else None
+        v_depths = (torch.empty(radii.shape[:-1], dtype=torch.float32, device=means.device)
+                    if (need_depths and ctx.out_ch == 4) else None)
+        _call("splatad_sh_colors_bwd", radii.numel() // 2, N, K, ctx.sh_degree, _lib.ptr(means),
+              _lib.ptr(campos), _lib.ptr(coeffs), int(coeffs.dim() == 4), _lib.ptr(camera_ids),
+              _lib.ptr(gaussian_ids), _lib.ptr(radii), ctx.out_ch, _lib.ptr(_f(v_colors)), _lib.ptr(v_coeffs),
+              _lib.ptr(v_means), _lib.ptr(v_campos), _lib.ptr(v_depths), _lib.stream_ptr(means.device))
+        return None, v_means, v_campos, v_coeffs, v_depths, None, None, None
+
+
 # =============================================================================================
 # Projection
 # =============================================================================================

@@ -20,6 +20,7 @@ except ImportError:  # pragma: no cover
     from typing import Literal
 
 from .ops import (
+    camera_centers,
     fully_fused_lidar_projection,
     fully_fused_projection,
     isect_lidar_tiles_deferred,
@@ -27,7 +28,7 @@ from .ops import (
     rasterize_to_pixels,
     rasterize_to_points,
     rasterize_to_points_split,
-    spherical_harmonics,
+    view_dependent_colors,
 )
 
 
@@ -157,27 +158,15 @@ def rasterization(
             if colors.dim() == 2:
                 colors = colors.expand(C, -1, -1)
     else:
-        camtoworlds = torch.inverse(viewmats)  # [C, 4, 4]
-        if packed:
-            dirs = means[gaussian_ids, :] - camtoworlds[camera_ids, :3, 3]  # [nnz, 3]
-            masks = radii[..., 0] > 0  # [nnz]
-            if colors.dim() == 3:
-                shs = colors[gaussian_ids, :, :]  # [nnz, K, 3]
-            else:
-                shs = colors[camera_ids, gaussian_ids, :, :]  # [nnz, K, 3]
-            colors = spherical_harmonics(sh_degree, dirs, shs, masks=masks)  # [nnz, 3]
-        else:
-            dirs = means[None, :, :] - camtoworlds[:, None, :3, 3]  # [C, N, 3]
-            masks = radii[..., 0] > 0  # [C, N]
-            if colors.dim() == 3:
-                shs = colors.expand(C, -1, -1, -1)  # [C, N, K, 3]
-            else:
-                shs = colors
-            colors = spherical_harmonics(sh_degree, dirs, shs, masks=masks)  # [C, N, 3]
-        colors = torch.clamp_min(colors + 0.5, 0.0)
+        # camera centres (the translation of inverse(viewmats)), then gathers, directions, SH, + 0.5,
+        # clamp and the depth channel in one kernel
+        colors = view_dependent_colors(
+            sh_degree, means, camera_centers(viewmats), colors, radii, camera_ids, gaussian_ids,
+            depths=depths if render_mode in ["RGB+D", "RGB+ED"] else None)
 
     if render_mode in ["RGB+D", "RGB+ED"]:
-        colors = torch.cat((colors, depths[..., None]), dim=-1)
+        if sh_degree is None:
+            colors = torch.cat((colors, depths[..., None]), dim=-1)
         if backgrounds is not None:
             backgrounds = torch.cat([backgrounds, torch.zeros(C, 1, device=backgrounds.device)], dim=-1)
     elif render_mode in ["D", "ED"]:

@@ -6,7 +6,11 @@
 // batches of blockDim Gaussians staged into shared memory as two float4 (+ extras for lidar),
 // stops as soon as every pixel of the tile is saturated, and a warp whose 32 pixels are all
 // saturated skips the batch body. The backward pass starts at the last list position any
-// pixel of the tile actually consumed instead of the end of the list.
+// pixel of the tile actually consumed instead of the end of the list. The camera forward kernel
+// stages only Gaussians that can reach alpha >= 1/255 somewhere in the tile (an exact, conservative
+// test of the quadratic form over the tile's box of pixel centres, once per tile and Gaussian): the
+// bounding rectangles behind the tile lists are loose, a quarter to a third of their entries never
+// touch a pixel of the tile. The same test did not pay for lidar tiles and is not used there.
 //
 // Semantics follow the reference kernels
 //   pixels fwd  gsplat/cuda/csrc/rasterization.cu:1360-1518     bwd 2833-3089
@@ -70,8 +74,10 @@ __global__ void rasterize_to_pixels_fwd_kernel(
     float4 *sA = reinterpret_cast<float4 *>(smem_raw);   // x, y, vx, vy
     float4 *sB = sA + bs;                                // conic a, b, c, opacity
     int32_t *sId = reinterpret_cast<int32_t *>(sB + bs);
+    uint32_t *sPos = reinterpret_cast<uint32_t *>(sId + bs);   // list position of the staged entry
     // colour rows of the batch (when they fit): the inner loop then never waits on global memory
-    float *sCol = reinterpret_cast<float *>(sId + bs);
+    float *sCol = reinterpret_cast<float *>(sPos + bs);
+    __shared__ uint32_t s_warp_kept[32];
     const uint32_t cpad = (channels + 3u) & ~3u;
     const bool vec = (channels % 4u == 0u) && ((reinterpret_cast<uintptr_t>(colors) & 15u) == 0u);
 
@@ -84,7 +90,19 @@ __global__ void rasterize_to_pixels_fwd_kernel(
     const uint32_t j = tx * tile_size + tr % tile_size;
     const bool inside = (tr < tile_size * tile_size) && (i < H && j < W);
     const float px = (float)j + 0.5f, py = (float)i + 0.5f;
-    const float roll = rs_time[cam] * ((py - 0.5f) / (float)(H - 1) - 0.5f);
+    const float rs = rs_time[cam];
+    const float roll = rs * ((py - 0.5f) / (float)(H - 1) - 0.5f);
+
+    // pixel centres of this tile and the rolling-shutter offsets of its first and last row: a
+    // Gaussian that cannot be seen anywhere in that box is not staged at all
+    const float box_x0 = (float)(tx * tile_size) + 0.5f;
+    const float box_x1 = (float)min((tx + 1) * tile_size, W) - 0.5f;
+    const float box_y0 = (float)(ty * tile_size) + 0.5f;
+    const float box_y1 = (float)min((ty + 1) * tile_size, H) - 0.5f;
+    const float roll_a = rs * ((box_y0 - 0.5f) / (float)(H - 1) - 0.5f);
+    const float roll_b = rs * ((box_y1 - 0.5f) / (float)(H - 1) - 0.5f);
+    const float roll_lo = fminf(roll_a, roll_b), roll_hi = fmaxf(roll_a, roll_b);
+    const uint32_t lane = tr & 31u, warp = tr >> 5, n_warps = bs >> 5;
 
     const TileRange range = tile_range(offsets, blockIdx.x, C * tiles_per_cam, n_isects);
     const uint32_t num_batches = (uint32_t)(range.end - range.start + bs - 1) / bs;
@@ -100,19 +118,42 @@ __global__ void rasterize_to_pixels_fwd_kernel(
         if (__syncthreads_count(done) >= (int)bs) break;
         const uint32_t batch_start = (uint32_t)range.start + bs * b;
         const uint32_t idx = batch_start + tr;
+        bool keep = false;
+        int32_t g = 0;
+        float4 A, B;
         if (idx < (uint32_t)range.end) {
-            const int32_t g = flatten_ids[idx];
+            g = flatten_ids[idx];
             const float2 xy = means2d[g];
             const float2 v = pix_vels[g];
-            sA[tr] = make_float4(xy.x, xy.y, v.x, v.y);
-            sB[tr] = make_float4(conics[3 * (size_t)g], conics[3 * (size_t)g + 1],
-                                 conics[3 * (size_t)g + 2], opacities[g]);
-            sId[tr] = g;
-            if (stage_colors) stage_row(sCol + tr * cpad, colors, (size_t)g, channels, vec);
+            A = make_float4(xy.x, xy.y, v.x, v.y);
+            B = make_float4(conics[3 * (size_t)g], conics[3 * (size_t)g + 1],
+                            conics[3 * (size_t)g + 2], opacities[g]);
+            // offsets mean - pixel over the tile; the mean moves with the row's shutter time
+            const float mx_a = A.x + roll_lo * A.z, mx_b = A.x + roll_hi * A.z;
+            const float my_a = A.y + roll_lo * A.w, my_b = A.y + roll_hi * A.w;
+            keep = !never_visible_in_box(B.x, B.y, B.z, B.w, fminf(mx_a, mx_b) - box_x1,
+                                         fmaxf(mx_a, mx_b) - box_x0, fminf(my_a, my_b) - box_y1,
+                                         fmaxf(my_a, my_b) - box_y0);
+        }
+        // compact the survivors to the front of the staging arrays, list order kept
+        const uint32_t kept_mask = __ballot_sync(0xffffffffu, keep);
+        if (lane == 0) s_warp_kept[warp] = __popc(kept_mask);
+        __syncthreads();
+        uint32_t pos = __popc(kept_mask & ((1u << lane) - 1u)), batch_size = 0;
+        for (uint32_t w = 0; w < n_warps; ++w) {
+            const uint32_t cnt = s_warp_kept[w];
+            if (w < warp) pos += cnt;
+            batch_size += cnt;
+        }
+        if (keep) {
+            sA[pos] = A;
+            sB[pos] = B;
+            sId[pos] = g;
+            sPos[pos] = idx;
+            if (stage_colors) stage_row(sCol + pos * cpad, colors, (size_t)g, channels, vec);
         }
         __syncthreads();
         if (__all_sync(0xffffffffu, done)) continue;
-        const uint32_t batch_size = min(bs, (uint32_t)range.end - batch_start);
         for (uint32_t t = 0; t < batch_size && !done; ++t) {
             const float4 A = sA[t];
             const float4 B = sB[t];
@@ -132,7 +173,7 @@ __global__ void rasterize_to_pixels_fwd_kernel(
                 for (int k = 0; k < CDIM; ++k)
                     if ((uint32_t)k < channels) pix_out[k] += __ldg(c_ptr + k) * vis;
             }
-            cur_idx = batch_start + t;
+            cur_idx = sPos[t];
             T = next_T;
         }
     }
@@ -716,7 +757,7 @@ extern "C" int splatad_rasterize_to_pixels_fwd(
     const uint32_t blocks = C * tile_width * tile_height;
     if (blocks == 0 || image_width == 0 || image_height == 0) return SPLATAD_OK;
     const uint32_t bs = ((tile_size * tile_size + 31) / 32) * 32;   // whole warps
-    size_t smem = (size_t)bs * (2 * sizeof(float4) + sizeof(int32_t));
+    size_t smem = (size_t)bs * (2 * sizeof(float4) + 2 * sizeof(int32_t));
     // the batch's colour rows ride along in shared memory while a block stays under 64 KB
     const size_t smem_colors = (size_t)bs * ((channels + 3u) & ~3u) * sizeof(float);
     const uint32_t stage_colors = (smem + smem_colors <= 64 * 1024) ? 1u : 0u;

@@ -135,7 +135,7 @@ def rasterization(
         opacities = opacities[gaussian_ids]  # [nnz]
     else:
         radii, means2d, depths, conics, compensations, pix_vels = proj_results
-        opacities = opacities.repeat(C, 1)  # [C, N]
+        opacities = opacities[None] if C == 1 else opacities.repeat(C, 1)  # [C, N], no copy for one sensor
         camera_ids, gaussian_ids = None, None
 
     if compensations is not None:
@@ -278,7 +278,7 @@ def lidar_rasterization(
         far_plane=far_plane, radius_clip=radius_clip, sparse_grad=sparse_grad,
         calc_compensations=(rasterize_mode == "antialiased"),
     )
-    opacities = opacities.repeat(C, 1)  # [C, N]
+    opacities = opacities[None] if C == 1 else opacities.repeat(C, 1)  # [C, N], no copy for one sensor
     camera_ids, gaussian_ids = None, None
 
     if not use_depth_compensation:

@@ -62,33 +62,73 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons in the background during the timed region."""
+    """Samples the SM clock and the throttle reasons of one GPU in the background during the timed
+    regions: through NVML from a thread of this process (the counters nvidia-smi prints, without a
+    second process per rank polling the driver), or an `nvidia-smi -lms` child when the NVML
+    binding is missing. Read-only."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20,
+                   "hw_thermal_slowdown": 0x40}
 
-    def __init__(self, gpu_index: int):
-        self.gpu_index = gpu_index
-        self.proc = None
-        self.lines = []
+    def __init__(self, gpu_index: int, period_s: float = 0.1):
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+        ids = [v.strip() for v in visible.split(",") if v.strip()]
+        if gpu_index < len(ids) and ids[gpu_index].isdigit():
+            gpu_index = int(ids[gpu_index])
+        self.gpu_index, self.period_s = gpu_index, period_s
+        self.proc = self.thread = self.nvml = None
+        self.lines, self.sm, self.smmax, self.reasons = [], [], [], set()
+        self.stop_flag = threading.Event()
 
     def start(self):
         try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+            self.nvml = pynvml
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+            return
+        except Exception:   # no binding, no driver library: fall back to the command line tool
+            self.nvml = None
+        try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", str(int(self.period_s * 1e3))],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
 
+    def _poll_nvml(self):
+        nv = self.nvml
+        reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self.stop_flag.is_set():
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                self.smmax.append(float(nv.nvmlDeviceGetMaxClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                mask = int(reasons_fn(self.handle))
+                self.reasons.update(k for k, bit in self.REASON_BITS.items() if mask & bit)
+            except Exception:
+                pass
+            self.stop_flag.wait(self.period_s)
+
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self.nvml is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            return {"sm_mhz": float(np.median(self.sm)) if self.sm else None,
+                    "sm_max_mhz": float(np.max(self.smmax)) if self.smmax else None,
+                    "samples": len(self.sm), "reasons": sorted(self.reasons), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -112,7 +152,7 @@ class ClockSampler:
                     reasons.add(nme)
         return {"sm_mhz": float(np.median(sm)) if sm else None,
                 "sm_max_mhz": float(np.max(smmax)) if smmax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi"}
 
 
 def kernel_profile(fn):

@@ -53,6 +53,32 @@ struct ProfScope {
 #define SPL_PROF_CAT(a, b) SPL_PROF_CAT2(a, b)
 #define SPL_PROF(name, st) ::splatad::ProfScope SPL_PROF_CAT(_prof_, __LINE__)(name, st)
 
+// Programmatic dependent launch for chains of short kernels on one stream. A kernel started with
+// launch_chained() may have its blocks placed on the SMs while the kernel before it is still
+// draining; it must call chain_enter() before it touches anything, which waits (in hardware) until
+// the whole preceding kernel has finished and its writes are visible, and then lets the kernel
+// behind it start the same way. Started with <<<>>> instead, chain_enter() does nothing.
+__device__ __forceinline__ void chain_enter() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KP, typename... A>
+inline void launch_chained(void (*kernel)(KP...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                           A &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KP>(args)...);   // errors surface in check_launch()
+}
+
 // Cooperative copy of `nfl` contiguous floats global -> shared with 128-bit loads when the
 // source is 16-byte aligned (it is whenever the tensor base is, because block slabs start at
 // multiples of 256 rows).

@@ -69,6 +69,7 @@ __global__ void rasterize_to_pixels_fwd_kernel(
     const int32_t *__restrict__ offsets, const int32_t *__restrict__ flatten_ids,
     float *__restrict__ render_colors, float *__restrict__ render_alphas,
     int32_t *__restrict__ last_ids, uint32_t stage_colors) {
+    chain_enter();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const uint32_t bs = blockDim.x;
     float4 *sA = reinterpret_cast<float4 *>(smem_raw);   // x, y, vx, vy
@@ -206,6 +207,7 @@ __global__ void rasterize_to_points_fwd_kernel(
     float *__restrict__ render_colors, float *__restrict__ render_alphas,
     float *__restrict__ alpha_sum_out, int32_t *__restrict__ last_ids,
     float *__restrict__ median_depths, uint32_t stage_features) {
+    chain_enter();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const uint32_t bs = blockDim.x;
     float4 *sA = reinterpret_cast<float4 *>(smem_raw);   // az, el, v_az, v_el
@@ -766,7 +768,7 @@ extern "C" int splatad_rasterize_to_pixels_fwd(
     {                                                                                             \
         int rc = set_smem(rasterize_to_pixels_fwd_kernel<D>, smem, "rasterize_to_pixels_fwd");    \
         if (rc != SPLATAD_OK) return rc;                                                          \
-        rasterize_to_pixels_fwd_kernel<D><<<blocks, bs, smem, (cudaStream_t)stream>>>(            \
+        launch_chained(rasterize_to_pixels_fwd_kernel<D>, blocks, bs, smem, (cudaStream_t)stream, \
             C, n_isects, (const float2 *)means2d, conics, colors, channels, opacities,            \
             (const float2 *)pix_vels, rolling_shutter_time, backgrounds, image_width,             \
             image_height, tile_size, tile_width, tile_height, tile_offsets, flatten_ids,          \
@@ -864,7 +866,7 @@ extern "C" int splatad_rasterize_to_points_fwd(
     {                                                                                             \
         int rc = set_smem(rasterize_to_points_fwd_kernel<D>, smem, "rasterize_to_points_fwd");    \
         if (rc != SPLATAD_OK) return rc;                                                          \
-        rasterize_to_points_fwd_kernel<D><<<blocks, bs, smem, (cudaStream_t)stream>>>(            \
+        launch_chained(rasterize_to_points_fwd_kernel<D>, blocks, bs, smem, (cudaStream_t)stream, \
             C, n_isects, (const float2 *)means2d, conics, lidar_features, gaussian_ranges,        \
             channels, opacities,                                                                  \
             pix_vels, (const float2 *)depth_compensations, backgrounds,                           \

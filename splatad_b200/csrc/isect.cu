@@ -186,6 +186,7 @@ __global__ void __launch_bounds__(kThreads)
 isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ tiles_per_gauss,
                    const int64_t *__restrict__ camera_ids, uint32_t N, uint32_t *__restrict__ rect_xw,
                    uint32_t *__restrict__ rect_yh, int64_t *__restrict__ n_isects) {
+    chain_enter();
     __shared__ float sb[kLidar ? kMaxElevSmem : 1];
     __shared__ unsigned long long wsum[kThreads / 32];
     stage_boundaries<kLidar>(a, sb);
@@ -277,6 +278,7 @@ __device__ __forceinline__ void hist_add(uint32_t *wh_row, bool valid, uint32_t 
 template <bool kGen>
 __global__ void __launch_bounds__(kSortThreads)
 radix_upsweep_kernel(PassSrc s, int shift, uint32_t mask, uint32_t *__restrict__ hist) {
+    chain_enter();
     __shared__ uint32_t wh[kSortWarps][kRadixBins];
     for (uint32_t i = threadIdx.x; i < kSortWarps * kRadixBins; i += blockDim.x) (&wh[0][0])[i] = 0u;
     __syncthreads();
@@ -332,6 +334,7 @@ radix_upsweep_kernel(PassSrc s, int shift, uint32_t mask, uint32_t *__restrict__
 // One block per digit; blockDim.x >= grid size of the sort kernels (multiple of 32).
 __global__ void radix_rowscan_kernel(uint32_t *__restrict__ hist, uint32_t nblocks,
                                      uint32_t *__restrict__ digit_totals) {
+    chain_enter();
     __shared__ uint32_t wt[33];
     const uint32_t d = blockIdx.x;
     const uint32_t b = threadIdx.x;
@@ -357,6 +360,7 @@ radix_downsweep_kernel(PassSrc s, int shift, int nbits, uint32_t mask, const uin
                        const uint32_t *__restrict__ digit_totals, uint32_t *__restrict__ keys_out,
                        uint32_t *__restrict__ vals_out, FinalOut fin,
                        int64_t *__restrict__ n_out /* optional: total valid count */) {
+    chain_enter();
     __shared__ uint32_t wh[kSortWarps][kRadixBins];
     __shared__ uint32_t digit_base[kRadixBins];
     __shared__ uint32_t tile_excl[kRadixBins];
@@ -863,6 +867,7 @@ __device__ __forceinline__ bool split_overflow(const SplitArgs &a) {
 
 __global__ void __launch_bounds__(kSplitWarps * 32)
 rowsplit_count_kernel(SplitArgs a) {
+    chain_enter();
     __shared__ uint32_t s_cnt[kSplitMaxRows], s_out[kSplitMaxRows];
     if (split_overflow(a)) return;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -900,6 +905,7 @@ rowsplit_count_kernel(SplitArgs a) {
 // finishes last turns the row totals into the row starts of records, outputs and step-B units.
 __global__ void __launch_bounds__(1024)
 rowsplit_scan_kernel(SplitArgs a, unsigned long long *__restrict__ ticket) {
+    chain_enter();
     __shared__ uint32_t wt[33];
     __shared__ bool s_last;
     const uint32_t r = blockIdx.x, tid = threadIdx.x;
@@ -957,6 +963,7 @@ rowsplit_scan_kernel(SplitArgs a, unsigned long long *__restrict__ ticket) {
 template <bool kOneGroup>
 __global__ void __launch_bounds__(kSplitWarps * 32)
 rowsplit_scatter_kernel(SplitArgs a) {
+    chain_enter();
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t lt = (1u << lane) - 1u;
     if (split_overflow(a)) return;
@@ -1129,6 +1136,7 @@ __device__ __forceinline__ void warp_prefix_inplace(int32_t *d, uint32_t n, uint
 
 __global__ void __launch_bounds__(kSplitWarps * 32)
 colsplit_count_kernel(SplitArgs a) {
+    chain_enter();
     extern __shared__ int32_t s_d[];   // [kSplitWarps][stride]
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (split_overflow(a)) return;
@@ -1162,6 +1170,7 @@ colsplit_count_kernel(SplitArgs a) {
 // without the closing column of every row - followed by the total.
 __global__ void __launch_bounds__(1024)
 colsplit_scan_kernel(SplitArgs a, unsigned long long *__restrict__ ticket, int32_t *__restrict__ offsets) {
+    chain_enter();
     __shared__ uint32_t seg_sum[32][33];
     __shared__ uint32_t wt[33];
     __shared__ bool s_last;
@@ -1265,6 +1274,7 @@ __device__ __forceinline__ SplitWindow split_load_window(const SplitArgs &a, uin
 __global__ void __launch_bounds__(kSplitWarps * 32)
 colsplit_scatter_kernel(SplitArgs a, int64_t *__restrict__ isect_ids, int32_t *__restrict__ flatten_ids,
                         int64_t *__restrict__ counters) {
+    chain_enter();
     extern __shared__ int32_t s_dyn[];
     // [kSplitWarps][stride] column tables, [stride] global - local start, staged outputs
     int32_t *s_tab = s_dyn;
@@ -1415,6 +1425,7 @@ offset_encode_kernel(const int64_t *__restrict__ isect_ids, const int64_t *n_ptr
 }
 
 __global__ void init_counters_kernel(int64_t *counters) {
+    chain_enter();
     if (threadIdx.x < CNT_SLOTS) counters[threadIdx.x] = 0;
 }
 
@@ -1548,7 +1559,7 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
                 "isect: sensors * tiles does not fit 32 bits");
     {
         SPL_PROF("init_counters_kernel", st);
-        init_counters_kernel<<<1, 32, 0, st>>>(p.counters);
+        launch_chained(init_counters_kernel, 1, 32, 0, st, p.counters);
     }
     // with few enough sensor-tiles the fill uses the row / column split: it wants the packed
     // rectangles and needs neither the emission offsets nor their block sums
@@ -1559,11 +1570,11 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
         uint32_t *rx = split ? p.rect_xw : nullptr, *ry = split ? p.rect_yh : nullptr;
         int64_t *tot = split ? p.counters + CNT_NISECT : nullptr;
         if (g.lidar)
-            isect_count_kernel<true><<<cgrid, kThreads, 0, st>>>(g.lid, g.total, tiles_per_gauss,
-                                                                 g.camera_ids, g.N, rx, ry, tot);
+            launch_chained(isect_count_kernel<true>, cgrid, kThreads, 0, st, g.lid, g.total, tiles_per_gauss,
+                           g.camera_ids, g.N, rx, ry, tot);
         else
-            isect_count_kernel<false><<<cgrid, kThreads, 0, st>>>(g.cam, g.total, tiles_per_gauss,
-                                                                  g.camera_ids, g.N, rx, ry, tot);
+            launch_chained(isect_count_kernel<false>, cgrid, kThreads, 0, st, g.cam, g.total, tiles_per_gauss,
+                           g.camera_ids, g.N, rx, ry, tot);
     }
 
     EmitArgs e{};
@@ -1583,33 +1594,33 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
                 s.total = g.total;
                 {
                     SPL_PROF("depthsort_upsweep", st);
-                    radix_upsweep_kernel<true><<<kSortGrid, kSortThreads, 0, st>>>(s, 0, 0xffu, p.hist);
+                    launch_chained(radix_upsweep_kernel<true>, kSortGrid, kSortThreads, 0, st, s, 0, 0xffu, p.hist);
                 }
                 {
                     SPL_PROF("depthsort_rowscan", st);
-                    radix_rowscan_kernel<<<kRadixBins, ((kSortGrid + 31) / 32) * 32, 0, st>>>(
-                        p.hist, kSortGrid, p.digit_totals);
+                    launch_chained(radix_rowscan_kernel, kRadixBins, ((kSortGrid + 31) / 32) * 32, 0, st,
+                                   p.hist, (uint32_t)kSortGrid, p.digit_totals);
                 }
                 {
                     SPL_PROF("depthsort_downsweep", st);
-                    radix_downsweep_kernel<true, false><<<kSortGrid, kSortThreads, 0, st>>>(
-                        s, 0, 8, 0xffu, p.hist, p.digit_totals, ka, va, nofin, p.counters + CNT_NVIS);
+                    launch_chained(radix_downsweep_kernel<true, false>, kSortGrid, kSortThreads, 0, st,
+                                   s, 0, 8, 0xffu, p.hist, p.digit_totals, ka, va, nofin, p.counters + CNT_NVIS);
                 }
             } else {
                 s.keys = ka; s.vals = va; s.n_ptr = p.counters + CNT_NVIS;
                 {
                     SPL_PROF("depthsort_upsweep", st);
-                    radix_upsweep_kernel<false><<<kSortGrid, kSortThreads, 0, st>>>(s, 8 * pass, 0xffu, p.hist);
+                    launch_chained(radix_upsweep_kernel<false>, kSortGrid, kSortThreads, 0, st, s, 8 * pass, 0xffu, p.hist);
                 }
                 {
                     SPL_PROF("depthsort_rowscan", st);
-                    radix_rowscan_kernel<<<kRadixBins, ((kSortGrid + 31) / 32) * 32, 0, st>>>(
-                        p.hist, kSortGrid, p.digit_totals);
+                    launch_chained(radix_rowscan_kernel, kRadixBins, ((kSortGrid + 31) / 32) * 32, 0, st,
+                                   p.hist, (uint32_t)kSortGrid, p.digit_totals);
                 }
                 {
                     SPL_PROF("depthsort_downsweep", st);
-                    radix_downsweep_kernel<false, false><<<kSortGrid, kSortThreads, 0, st>>>(
-                        s, 8 * pass, 8, 0xffu, p.hist, p.digit_totals, kb, vb, nofin, nullptr);
+                    launch_chained(radix_downsweep_kernel<false, false>, kSortGrid, kSortThreads, 0, st,
+                                   s, 8 * pass, 8, 0xffu, p.hist, p.digit_totals, kb, vb, nofin, nullptr);
                 }
                 uint32_t *t;
                 t = ka; ka = kb; kb = t;
@@ -1709,32 +1720,32 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
                                  (int)smem_scatter);
         {
             SPL_PROF("rowsplit_count_kernel", st);
-            rowsplit_count_kernel<<<units_a, kSplitWarps * 32, 0, st>>>(a);
+            launch_chained(rowsplit_count_kernel, units_a, kSplitWarps * 32, 0, st, a);
         }
         {
             SPL_PROF("rowsplit_scan_kernel", st);
-            rowsplit_scan_kernel<<<a.rows, 1024, 0, st>>>(
-                a, (unsigned long long *)(p.counters + CNT_TICKET));
+            launch_chained(rowsplit_scan_kernel, a.rows, 1024, 0, st, a,
+                           (unsigned long long *)(p.counters + CNT_TICKET));
         }
         {
             SPL_PROF("rowsplit_scatter_kernel", st);
-            if (a.rows <= 32) rowsplit_scatter_kernel<true><<<units_a, kSplitWarps * 32, 0, st>>>(a);
-            else rowsplit_scatter_kernel<false><<<units_a, kSplitWarps * 32, 0, st>>>(a);
+            if (a.rows <= 32) launch_chained(rowsplit_scatter_kernel<true>, units_a, kSplitWarps * 32, 0, st, a);
+            else launch_chained(rowsplit_scatter_kernel<false>, units_a, kSplitWarps * 32, 0, st, a);
         }
         {
             SPL_PROF("colsplit_count_kernel", st);
-            colsplit_count_kernel<<<w.units_b_cap, kSplitWarps * 32, smem_count, st>>>(a);
+            launch_chained(colsplit_count_kernel, w.units_b_cap, kSplitWarps * 32, smem_count, st, a);
         }
         {
             SPL_PROF("colsplit_scan_kernel", st);
-            colsplit_scan_kernel<<<a.rows, 1024, 0, st>>>(
-                a, (unsigned long long *)(p.counters + CNT_TICKET), tile_offsets);
+            launch_chained(colsplit_scan_kernel, a.rows, 1024, 0, st, a,
+                           (unsigned long long *)(p.counters + CNT_TICKET), tile_offsets);
             tile_offsets = nullptr;   // done
         }
         {
             SPL_PROF("colsplit_scatter_kernel", st);
-            colsplit_scatter_kernel<<<w.units_b_cap, kSplitWarps * 32, smem_scatter, st>>>(
-                a, isect_ids, flatten_ids, p.counters);
+            launch_chained(colsplit_scatter_kernel, w.units_b_cap, kSplitWarps * 32, smem_scatter, st, a,
+                           isect_ids, flatten_ids, p.counters);
         }
     } else {
         FillWs f = carve_fill(fill_workspace, (uint64_t)capacity);

@@ -394,15 +394,16 @@ def run_ours(args):
         for _ in range(3):
             cam_out = splatad_b200.rasterization(**cam_cfg)
         torch.cuda.synchronize()
-        cam_ms = []
-        for _ in range(max(3, min(args.steps, 10))):
+        cam_evs = []
+        for _ in range(max(3, min(args.steps, 20))):   # timed like the lidar steps: per-frame events, one wait
             flush.zero_()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             cam_out = splatad_b200.rasterization(**cam_cfg)
             b.record()
-            b.synchronize()
-            cam_ms.append(a.elapsed_time(b))
+            cam_evs.append((a, b))
+        torch.cuda.synchronize()
+        cam_ms = [a.elapsed_time(b) for a, b in cam_evs]
         cam_prof = kernel_profile(lambda: splatad_b200.rasterization(**cam_cfg))
         camera = {"workload": "config1: 500,000 Gaussians, 1920x1080 rolling-shutter camera, SH deg 3, RGB+D, packed",
                   "mpix_per_s": round(1920 * 1080 * 1e-6 / (np.mean(cam_ms) * 1e-3), 1),

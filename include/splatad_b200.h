@@ -115,7 +115,10 @@ int splatad_projection_bwd(
  * 1157-1353. The reference sizes its outputs after a device->host read of nnz; here that is a
  * two-call protocol: _count writes indptr [C+1] and *nnz_device (int64, device memory; the
  * caller copies it to the host), _fill writes the nnz rows (camera-major, Gaussian-minor).
- * The same workspace must be passed to both calls. */
+ * The same workspace must be passed to both calls. _fill does not need the count on the host:
+ * with outputs of `capacity` rows (from an earlier frame, say) it can be enqueued right behind
+ * _count; rows at or beyond the capacity are dropped, the caller then sees nnz > capacity and
+ * fills again. capacity < 0: the outputs hold nnz rows. */
 size_t splatad_projection_packed_workspace_bytes(uint32_t C, uint32_t N);
 int splatad_projection_packed_count(
     uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
@@ -129,7 +132,7 @@ int splatad_projection_packed_fill(
     const float *scales, const float *velocities, const float *viewmats, const float *Ks,
     int32_t image_width, int32_t image_height, const float *linear_velocity,
     const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
-    float near_plane, float far_plane, float radius_clip, const void *workspace,
+    float near_plane, float far_plane, float radius_clip, const void *workspace, int64_t capacity,
     int64_t *camera_ids, int64_t *gaussian_ids, int32_t *radii, float *means2d, float *depths,
     float *conics, float *compensations, float *pix_vels, void *stream);
 

@@ -315,6 +315,7 @@ projection_packed_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ m
                              float eps2d, float near_plane, float far_plane, float radius_clip,
                              int32_t *__restrict__ block_counts,        // [C, nblocks] pass 1
                              const int32_t *__restrict__ block_offsets, // [C, nblocks] pass 2 (exclusive)
+                             int64_t capacity /* rows the outputs hold; < 0: as many as needed */,
                              int64_t *__restrict__ camera_ids, int64_t *__restrict__ gaussian_ids,
                              int32_t *__restrict__ radii, float *__restrict__ means2d,
                              float *__restrict__ depths, float *__restrict__ conics,
@@ -351,6 +352,7 @@ projection_packed_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ m
         if (vis) {
             const int64_t row = (int64_t)block_offsets[(size_t)c * gridDim.x + blockIdx.x] + before +
                                 __popc(ballot & ((1u << lane) - 1u));
+            if (capacity >= 0 && row >= capacity) continue;   // the caller sees nnz > capacity and refills
             camera_ids[row] = (int64_t)c;
             gaussian_ids[row] = (int64_t)(g0 + t);
             radii[2 * row] = (int32_t)o.ex;
@@ -902,8 +904,8 @@ extern "C" int splatad_projection_packed_count(
         projection_packed_fwd_kernel<<<nblocks, kThreads, 0, st>>>(
             C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
             linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
-            radius_clip, counts, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
-            nullptr, nullptr);
+            radius_clip, counts, nullptr, (int64_t)-1, nullptr, nullptr, nullptr, nullptr, nullptr,
+            nullptr, nullptr, nullptr);
     }
     {
         SPL_PROF("packed_scan_kernel", st);
@@ -917,7 +919,7 @@ extern "C" int splatad_projection_packed_fill(
     const float *scales, const float *velocities, const float *viewmats, const float *Ks,
     int32_t image_width, int32_t image_height, const float *linear_velocity,
     const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
-    float near_plane, float far_plane, float radius_clip, const void *workspace,
+    float near_plane, float far_plane, float radius_clip, const void *workspace, int64_t capacity,
     int64_t *camera_ids, int64_t *gaussian_ids, int32_t *radii, float *means2d, float *depths,
     float *conics, float *compensations, float *pix_vels, void *stream) {
     SPL_REQUIRE(means && viewmats && Ks && workspace && camera_ids && gaussian_ids && radii &&
@@ -931,8 +933,8 @@ extern "C" int splatad_projection_packed_fill(
         projection_packed_fwd_kernel<<<nblocks, kThreads, 0, (cudaStream_t)stream>>>(
             C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
             linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
-            radius_clip, nullptr, offsets, camera_ids, gaussian_ids, radii, means2d, depths, conics,
-            compensations, pix_vels);
+            radius_clip, nullptr, offsets, capacity, camera_ids, gaussian_ids, radii, means2d, depths,
+            conics, compensations, pix_vels);
     }
     return check_launch("projection_packed_fill");
 }
@@ -1038,7 +1040,7 @@ extern "C" int splatad_projection_packed_count_noalloc(
     projection_packed_fwd_kernel<<<(uint32_t)nblocks, kThreads, 0, st>>>(
         C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
         linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
-        radius_clip, counts, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+        radius_clip, counts, nullptr, (int64_t)-1, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
         nullptr, nullptr);
     packed_scan_kernel<<<1, 1024, 0, st>>>(counts, offsets, C, (uint32_t)nblocks, indptr, nnz_device);
     return check_launch("projection_packed_count_noalloc");

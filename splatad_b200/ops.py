@@ -32,6 +32,7 @@ from torch import Tensor
 from . import _lib
 
 _RETURN_VELOCITY_GRADS = False
+_packed_nnz_hint = {}   # (C, N, device) -> packed row count of the last frame of that shape
 
 
 @contextlib.contextmanager
@@ -237,12 +238,16 @@ def fully_fused_projection(
     packed: bool = False,
     sparse_grad: bool = False,
     calc_compensations: bool = False,
+    pending: Optional["PendingPackedCount"] = None,
 ):
     """Projects Gaussians to a batch of pinhole cameras (with rolling-shutter velocities).
 
     packed=False returns (radii [C,N,2] int32, means2d, depths, conics, compensations, pix_vels);
     packed=True returns (camera_ids, gaussian_ids, radii [nnz,2], means2d, depths, conics,
     compensations, pix_vels) with rows ordered camera-major, Gaussian-minor.
+
+    ``pending`` (not in the reference, packed only): a :class:`PendingPackedCount` that lets the call
+    return without waiting for the row count; see there.
     """
     C = viewmats.size(0)
     N = means.size(0)
@@ -274,7 +279,7 @@ def fully_fused_projection(
         return _FullyFusedProjectionPacked.apply(
             means, covars, quats, scales, velocities, viewmats, Ks, width, height, linear_velocity,
             angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane, radius_clip,
-            sparse_grad, calc_compensations,
+            sparse_grad, calc_compensations, pending,
         )
     return _FullyFusedProjection.apply(
         means, covars, quats, scales, velocities, viewmats, Ks, width, height, linear_velocity,
@@ -478,11 +483,41 @@ class _FullyFusedLidarProjection(torch.autograd.Function):
         return (v_means, v_covars, v_quats, v_scales, v_vel, v_viewmats) + (None,) * 12
 
 
+class PendingPackedCount:
+    """Lets ``fully_fused_projection(packed=True, pending=...)`` return before the host knows the
+    number of packed rows. From the second frame of a shape on, the outputs then come back with
+    ``capacity`` rows (the previous count + 12.5 %, rounded up to 64 Ki): the first ``nnz`` rows are
+    the packed rows, the rest are padding with radii 0 and ids 0, which every op of this package
+    skips or leaves unused (no tiles, colour 0.5, never listed). ``resolve()`` waits for the count
+    and returns it, or None when the rows outgrew the capacity and the projection has to be called
+    again; until then ``active`` says whether the outputs are padded at all (a first frame, or an
+    empty input, is returned at its exact length as usual). Tensors handed on to the caller are cut
+    to ``[:nnz]`` views; the backward pass reads the count from here."""
+
+    def __init__(self):
+        self.active = False
+        self.capacity = 0
+        self.nnz: Optional[int] = None
+        self._event = self._host = self._key = None
+
+    def resolve(self) -> Optional[int]:
+        if not self.active:
+            return self.nnz
+        if self.nnz is None:
+            self._event.synchronize()
+            nnz = int(self._host[0])
+            _packed_nnz_hint[self._key] = nnz
+            if nnz > self.capacity:
+                return None
+            self.nnz = nnz
+        return self.nnz
+
+
 class _FullyFusedProjectionPacked(torch.autograd.Function):
     @staticmethod
     def forward(ctx, means, covars, quats, scales, velocities, viewmats, Ks, width, height,
                 linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane,
-                far_plane, radius_clip, sparse_grad, calc_compensations):
+                far_plane, radius_clip, sparse_grad, calc_compensations, pending=None):
         means, covars, quats, scales, velocities, viewmats, lin, ang, rs = _proj_inputs(
             means, covars, quats, scales, velocities, viewmats, linear_velocity, angular_velocity,
             rolling_shutter_time)
@@ -491,8 +526,19 @@ class _FullyFusedProjectionPacked(torch.autograd.Function):
         dev = means.device
         lib = _lib.load()
         indptr = torch.zeros(C + 1, dtype=torch.int32, device=dev)
-        nnz = 0
-        ws = None
+
+        def outputs(rows, padded=False):
+            ids = torch.zeros if padded else torch.empty   # padding rows: ids 0, radii 0
+            return (ids(rows, dtype=torch.int64, device=dev),
+                    ids(rows, dtype=torch.int64, device=dev),
+                    ids((rows, 2), dtype=torch.int32, device=dev),
+                    torch.empty((rows, 2), dtype=torch.float32, device=dev),
+                    torch.empty(rows, dtype=torch.float32, device=dev),
+                    torch.empty((rows, 3), dtype=torch.float32, device=dev),
+                    torch.empty(rows, dtype=torch.float32, device=dev) if calc_compensations else None,
+                    torch.empty((rows, 2), dtype=torch.float32, device=dev))
+
+        nnz, out = 0, None
         if C > 0 and N > 0:
             ws_bytes = lib.splatad_projection_packed_workspace_bytes(C, N)
             ws = _lib.workspace("packed", ws_bytes, dev)
@@ -502,21 +548,46 @@ class _FullyFusedProjectionPacked(torch.autograd.Function):
                 _lib.ptr(velocities), _lib.ptr(viewmats), _lib.ptr(Ks), width, height, _lib.ptr(lin),
                 _lib.ptr(ang), _lib.ptr(rs), eps2d, near_plane, far_plane, radius_clip,
             )
+
+            def fill(capacity, o):
+                _call("splatad_projection_packed_fill", *common, _lib.ptr(ws), capacity, *(_lib.ptr(x) for x in o),
+                      _lib.stream_ptr(dev))
+
             _call("splatad_projection_packed_count", *common, _lib.ptr(ws), ws.numel(),
                   _lib.ptr(indptr), _lib.ptr(nnz_dev), _lib.stream_ptr(dev))
-            nnz = int(nnz_dev.item())
-        camera_ids = torch.empty(nnz, dtype=torch.int64, device=dev)
-        gaussian_ids = torch.empty(nnz, dtype=torch.int64, device=dev)
-        radii = torch.empty((nnz, 2), dtype=torch.int32, device=dev)
-        means2d = torch.empty((nnz, 2), dtype=torch.float32, device=dev)
-        depths = torch.empty(nnz, dtype=torch.float32, device=dev)
-        conics = torch.empty((nnz, 3), dtype=torch.float32, device=dev)
-        pix_vels = torch.empty((nnz, 2), dtype=torch.float32, device=dev)
-        compensations = torch.empty(nnz, dtype=torch.float32, device=dev) if calc_compensations else None
-        if nnz > 0:
-            _call("splatad_projection_packed_fill", *common, _lib.ptr(ws), _lib.ptr(camera_ids),
-                  _lib.ptr(gaussian_ids), _lib.ptr(radii), _lib.ptr(means2d), _lib.ptr(depths),
-                  _lib.ptr(conics), _lib.ptr(compensations), _lib.ptr(pix_vels), _lib.stream_ptr(dev))
+            # From the second frame of a shape on, the rows are written while the host still waits
+            # for the count: into buffers with the previous count + 12.5 % of room, cut to length
+            # afterwards (views). A frame that outgrows its room is filled again at the exact size.
+            key = (C, N, dev.index)
+            hint = _packed_nnz_hint.get(key)
+            capacity = None
+            if hint:
+                capacity = min((hint + hint // 8 + 4096 + 0xFFFF) & ~0xFFFF, C * N)
+                out = outputs(capacity, padded=pending is not None)
+                fill(capacity, out)
+            if pending is not None and capacity is not None:
+                # the caller carries on with padded outputs and asks for the count when it needs it
+                host = torch.empty(1, dtype=torch.int64, pin_memory=True)
+                host.copy_(nnz_dev, non_blocking=True)
+                pending._event = torch.cuda.Event()
+                pending._event.record(torch.cuda.current_stream(dev))
+                pending._host, pending._key = host, key
+                pending.active, pending.capacity = True, capacity
+            else:
+                nnz = int(nnz_dev.item())
+                _packed_nnz_hint[key] = nnz
+                if capacity is not None and nnz <= capacity:
+                    out = tuple(None if x is None else x[:nnz] for x in out)
+                else:
+                    out = outputs(nnz)
+                    if nnz > 0:
+                        fill(-1, out)
+        if out is None:
+            out = outputs(0)
+        if pending is not None and not pending.active:
+            pending.nnz = nnz
+        ctx.pending = pending if (pending is not None and pending.active) else None
+        camera_ids, gaussian_ids, radii, means2d, depths, conics, compensations, pix_vels = out
         ctx.save_for_backward(camera_ids, gaussian_ids, means, covars, quats, scales, velocities,
                               viewmats, Ks, lin, ang, rs, conics, compensations)
         ctx.width, ctx.height, ctx.eps2d, ctx.sparse_grad = width, height, eps2d, sparse_grad
@@ -530,6 +601,11 @@ class _FullyFusedProjectionPacked(torch.autograd.Function):
         (camera_ids, gaussian_ids, means, covars, quats, scales, velocities, viewmats, Ks, lin, ang,
          rs, conics, compensations) = ctx.saved_tensors
         C, N, nnz = viewmats.shape[0], means.shape[0], camera_ids.shape[0]
+        if ctx.pending is not None:
+            # padded outputs: the first nnz rows count (the gradients of the padding are zero)
+            nnz = ctx.pending.resolve()
+            assert nnz is not None, "backward through a packed projection whose rows outgrew their room"
+            gaussian_ids = gaussian_ids[:nnz]
         dev = means.device
         sparse = ctx.sparse_grad
         rows = nnz if sparse else N
@@ -570,7 +646,7 @@ class _FullyFusedProjectionPacked(torch.autograd.Function):
         v_covars = finish(v_covars, covars, ctx.needs_input_grad[1]) if covars is not None else None
         v_quats = finish(v_quats, quats, ctx.needs_input_grad[2]) if covars is None else None
         v_scales = finish(v_scales, scales, ctx.needs_input_grad[3]) if covars is None else None
-        return (v_means, v_covars, v_quats, v_scales, v_vel, v_viewmats) + (None,) * 12
+        return (v_means, v_covars, v_quats, v_scales, v_vel, v_viewmats) + (None,) * 13
 
 
 # =============================================================================================
@@ -834,7 +910,8 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
     host = _lib.pinned_counts("isect", dev)
     stream = _lib.stream_ptr(dev)
     head = (C, N, total, _lib.ptr(means2d), _lib.ptr(radii), _lib.ptr(depths), _lib.ptr(camera_ids))
-    key = (kind, C, N, total, n_tiles_total, dev.index)
+    # packed inputs: the row count changes from frame to frame, the hint only sizes the room
+    key = (kind, C, N, None if packed else total, n_tiles_total, dev.index)
     hint = _isect_count_hint.get(key) if (deferred and sort) else None
 
     def plan():

@@ -20,6 +20,7 @@ except ImportError:  # pragma: no cover
     from typing import Literal
 
 from .ops import (
+    PendingPackedCount,
     camera_centers,
     fully_fused_lidar_projection,
     fully_fused_projection,
@@ -108,6 +109,19 @@ def rasterization(
 
     Returns (render_colors [C,H,W,X], render_alphas [C,H,W,1], meta).
     """
+    args = (means, quats, scales, opacities, colors, velocities, viewmats, Ks, width, height, linear_velocity,
+            angular_velocity, rolling_shutter_time, near_plane, far_plane, radius_clip, eps2d, sh_degree, packed,
+            tile_size, backgrounds, render_mode, sparse_grad, absgrad, rasterize_mode, channel_chunk)
+    # packed: the frame is enqueued without waiting for the number of packed rows (once a frame of
+    # this shape has been seen); if the rows outgrow the room they were given, the frame is redone
+    out = _rasterization(*args, wait_for_packed_count=not packed)
+    return out if out is not None else _rasterization(*args, wait_for_packed_count=True)
+
+
+def _rasterization(means, quats, scales, opacities, colors, velocities, viewmats, Ks, width, height,
+                   linear_velocity, angular_velocity, rolling_shutter_time, near_plane, far_plane, radius_clip,
+                   eps2d, sh_degree, packed, tile_size, backgrounds, render_mode, sparse_grad, absgrad,
+                   rasterize_mode, channel_chunk, wait_for_packed_count):
     N, C = _check_gaussians(means, quats, scales, opacities, velocities, viewmats)
     assert Ks.shape == (C, 3, 3), Ks.shape
     assert render_mode in ("RGB", "D", "ED", "RGB+D", "RGB+ED"), render_mode
@@ -124,11 +138,12 @@ def rasterization(
         ), colors.shape
         assert (sh_degree + 1) ** 2 <= colors.shape[-2], colors.shape
 
+    pending = None if wait_for_packed_count else PendingPackedCount()
     proj_results = fully_fused_projection(
         means, None, quats, scales, velocities, viewmats, Ks, width, height, linear_velocity,
         angular_velocity, rolling_shutter_time, eps2d=eps2d, packed=packed, near_plane=near_plane,
         far_plane=far_plane, radius_clip=radius_clip, sparse_grad=sparse_grad,
-        calc_compensations=(rasterize_mode == "antialiased"),
+        calc_compensations=(rasterize_mode == "antialiased"), pending=pending,
     )
     if packed:
         (camera_ids, gaussian_ids, radii, means2d, depths, conics, compensations, pix_vels) = proj_results
@@ -174,6 +189,17 @@ def rasterization(
         if backgrounds is not None:
             backgrounds = torch.zeros(C, 1, device=backgrounds.device)
 
+    tiles_per_gauss_cut = None
+    if pending is not None and pending.active:
+        # everything up to here ran on padded rows; the count has long arrived by now
+        nnz = pending.resolve()
+        if nnz is None:
+            return None
+        camera_ids, gaussian_ids, radii = camera_ids[:nnz], gaussian_ids[:nnz], radii[:nnz]
+        means2d, depths, conics, pix_vels = means2d[:nnz], depths[:nnz], conics[:nnz], pix_vels[:nnz]
+        opacities, colors = opacities[:nnz], colors[:nnz]
+        tiles_per_gauss_cut = nnz
+
     def composite(isect_offsets, flatten_ids):
         if colors.shape[-1] > channel_chunk:
             n_chunks = (colors.shape[-1] + channel_chunk - 1) // channel_chunk
@@ -200,6 +226,8 @@ def rasterization(
 
     (render_colors, render_alphas), isect_ids, flatten_ids, isect_offsets, tiles_per_gauss = (
         _composite_with_count_check(isect, (tile_height, tile_width), composite))
+    if tiles_per_gauss_cut is not None:
+        tiles_per_gauss = tiles_per_gauss[:tiles_per_gauss_cut]
     if render_mode in ["ED", "RGB+ED"]:
         render_colors = torch.cat(
             [render_colors[..., :-1], render_colors[..., -1:] / render_alphas.clamp(min=1e-10)],

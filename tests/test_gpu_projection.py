@@ -191,6 +191,43 @@ def test_camera_projection_packed_matches_unpacked():
     assert torch.equal(p_pix_vels, pix_vels[c_ref, g_ref])
 
 
+def test_camera_projection_packed_repeated_frames_fill_ahead_of_the_count():
+    """From the second frame of a shape on the packed rows are written before the host has the
+    count (into room sized from the previous frame) and cut to length afterwards; a frame that
+    outgrows the room is filled again. Results must not depend on which way a frame went."""
+    from splatad_b200 import ops
+
+    N = 6001   # a shape no other test uses: the first call below is a first frame
+    means, quats, scales, vel, g = _scene(N, 23, "cam")
+    vm, Ks, lin, ang, rs = _camera_sensors(g)
+    fixed = (None, t(quats), t(scales), t(vel), t(vm), t(Ks), 320, 240, t(lin), t(ang), t(rs))
+
+    def both(m, **kw):
+        dense = ops.fully_fused_projection(t(m), *fixed, calc_compensations=True, **kw)
+        packed = ops.fully_fused_projection(t(m), *fixed, packed=True, calc_compensations=True, **kw)
+        vis = dense[3].abs().sum(-1) > 0
+        c_ref, g_ref = torch.nonzero(vis, as_tuple=True)
+        assert torch.equal(packed[0], c_ref) and torch.equal(packed[1], g_ref)
+        for p_out, d_out in zip(packed[2:], dense):
+            assert torch.equal(p_out, d_out[c_ref, g_ref])
+            assert p_out.is_contiguous()
+        return c_ref.numel()
+
+    far = means.clone()
+    far[1::10, 2] += 1e4                          # nine in ten stay; then only one in ten
+    far[2::10, 2] += 1e4
+    moved = torch.ones(N, dtype=torch.bool)
+    moved[::10] = False
+    far[moved, 2] = far[moved, 2].abs() + 1e4     # beyond the far plane
+    few = both(far, **CAM_KW)
+    assert few > 0
+    first = both(means, **CAM_KW)                 # outgrows the room left by the frame before: refilled
+    again = both(means, **CAM_KW)                 # fits: filled ahead of the count
+    assert few < first // 4 and again == first
+    shrunk = both(means * torch.tensor([3.0, 3.0, 1.0]), **CAM_KW)   # fewer rows than the room
+    assert 0 < shrunk < first
+
+
 def _grad_check(label, got, want, rel=1e-3):
     got, want = n(got), n(want)
     rms = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))

@@ -285,6 +285,54 @@ def test_repeated_camera_frames():
         assert torch.equal(first[2][key], second[2][key]), key
 
 
+def test_repeated_packed_camera_frames_do_not_wait_for_the_row_count():
+    """From the second frame of a shape on, a packed camera frame is enqueued on padded rows and cut
+    to length before compositing; a frame whose rows outgrow the room is redone. Renders, meta and
+    gradients must be those of the first (two-step) frame."""
+    import splatad_b200
+    from splatad_b200 import ops, scenes
+    cfg = scenes.config1(N=200_001)         # a shape of its own: the first call is a first frame
+    cfg.update(absgrad=True, rasterize_mode="antialiased")
+    g = _to_gpu(cfg)
+    leaves = ("means", "quats", "scales", "opacities", "colors")
+
+    def frame(scale=1.0):
+        kw = dict(g)
+        for k in leaves:
+            kw[k] = g[k].clone().requires_grad_(True)
+        m_in = kw["means"]
+        kw["means"] = m_in * torch.tensor([scale, scale, 1.0], device=DEV)
+        colors, alphas, meta = splatad_b200.rasterization(**kw)
+        meta["means2d"].retain_grad()
+        (colors.square().mean() + alphas.mean()).backward()
+        grads = {k: kw[k].grad if k != "means" else m_in.grad for k in leaves}
+        return colors, alphas, meta, grads
+
+    ops._packed_nnz_hint.pop((1, 200_001, torch.device(DEV).index), None)
+    first = frame()
+    second = frame()                         # padded rows, cut to length
+    nnz = first[2]["camera_ids"].numel()
+    assert 100_000 < nnz < 200_001   # more rows than the 64 Ki granule of the room
+    assert torch.equal(first[0], second[0]) and torch.equal(first[1], second[1])
+    for key in ("camera_ids", "gaussian_ids", "radii", "means2d", "depths", "conics", "opacities", "pix_vels",
+                "isect_ids", "flatten_ids", "isect_offsets", "tiles_per_gauss"):
+        a, b = first[2][key], second[2][key]
+        assert a.shape == b.shape and torch.equal(a, b), key
+    for key in ("means2d",):
+        assert second[2][key].grad is not None and second[2][key].absgrad is not None
+        assert_close("packed d/d" + key, n(second[2][key].grad), n(first[2][key].grad), 1e-4, 1e-9)
+        assert_close("packed absgrad", n(second[2][key].absgrad), n(first[2][key].absgrad), 1e-4, 1e-9)
+    for k in leaves:
+        ga, gb = n(first[3][k]), n(second[3][k])
+        assert_close("packed d/d" + k, gb, ga, 1e-3, 1e-3 * float(np.sqrt((ga ** 2).mean())), max_bad_frac=1e-3)
+    # a frame that sees far fewer Gaussians, then the full one again: the second outgrows its room
+    few = frame(scale=40.0)
+    assert few[2]["camera_ids"].numel() < nnz // 2
+    third = frame()
+    assert torch.equal(first[0], third[0])
+    assert torch.equal(first[2]["flatten_ids"], third[2]["flatten_ids"])
+
+
 def test_config2_full_size_properties():
     """The headline frame (1 M Gaussians, 15.3 M intersections) is too large for the CPU oracle, so it
     is checked through properties that do not depend on size - and by building its tile lists twice,

@@ -725,9 +725,24 @@ __global__ void rasterize_to_points_bwd_kernel(
         else { CALL(32); }                                                                       \
     } while (0)
 
+// A tile may have up to 1024 samples, one thread each; the backward kernels with many channels
+// need more registers per thread than a block of that size can have. Said here, with the numbers,
+// rather than by a failed launch.
+template <typename K>
+static int check_block_size(K kernel, uint32_t threads, uint32_t channels, const char *what) {
+    if (threads <= 256) return SPLATAD_OK;
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, kernel) != cudaSuccess) return check_launch(what);
+    SPL_REQUIRE((uint32_t)fa.maxThreadsPerBlock >= threads, SPLATAD_ERR_BAD_ARG,
+                "%s: a tile of %u samples with %u channels needs blocks of %u threads, this kernel runs at "
+                "most %d (%d registers per thread): use a smaller tile or fewer channels per call",
+                what, threads, channels, threads, fa.maxThreadsPerBlock, fa.numRegs);
+    return SPLATAD_OK;
+}
+
 template <typename K>
 static int set_smem(K kernel, size_t bytes, const char *what) {
-    if (bytes > 48 * 1024) {
+    if (bytes > 32 * 1024) {   // the 48 KB default also has to hold the kernels' static shared memory
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
         if (e != cudaSuccess) {
             set_last_error("%s: cannot reserve %zu bytes of shared memory: %s", what, bytes,
@@ -809,7 +824,9 @@ extern "C" int splatad_rasterize_to_pixels_bwd(
     const size_t smem = (size_t)bs * (2 * sizeof(float4) + sizeof(int32_t) + channels * sizeof(float));
 #define CALL(D)                                                                                   \
     {                                                                                             \
-        int rc = set_smem(rasterize_to_pixels_bwd_kernel<D>, smem, "rasterize_to_pixels_bwd");    \
+        int rc = check_block_size(rasterize_to_pixels_bwd_kernel<D>, bs, channels, "rasterize_to_pixels_bwd"); \
+        if (rc != SPLATAD_OK) return rc;                                                          \
+        rc = set_smem(rasterize_to_pixels_bwd_kernel<D>, smem, "rasterize_to_pixels_bwd");    \
         if (rc != SPLATAD_OK) return rc;                                                          \
         rasterize_to_pixels_bwd_kernel<D><<<blocks, bs, smem, (cudaStream_t)stream>>>(            \
             C, n_isects, (const float2 *)means2d, conics, colors, channels, opacities,            \
@@ -920,7 +937,9 @@ extern "C" int splatad_rasterize_to_points_bwd(
     const size_t smem = (size_t)bs * (3 * sizeof(float4) + sizeof(int32_t) + channels * sizeof(float));
 #define CALL(D)                                                                                   \
     {                                                                                             \
-        int rc = set_smem(rasterize_to_points_bwd_kernel<D>, smem, "rasterize_to_points_bwd");    \
+        int rc = check_block_size(rasterize_to_points_bwd_kernel<D>, bs, channels, "rasterize_to_points_bwd"); \
+        if (rc != SPLATAD_OK) return rc;                                                          \
+        rc = set_smem(rasterize_to_points_bwd_kernel<D>, smem, "rasterize_to_points_bwd");    \
         if (rc != SPLATAD_OK) return rc;                                                          \
         rasterize_to_points_bwd_kernel<D><<<blocks, bs, smem, (cudaStream_t)stream>>>(            \
             C, n_isects, (const float2 *)means2d, conics, lidar_features, gaussian_ranges,        \

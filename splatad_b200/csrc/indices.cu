@@ -235,7 +235,7 @@ static IndicesWs carve_indices(void *ws, uint64_t n_pix) {
 
 template <typename K>
 static int reserve_smem(K kernel, size_t bytes, const char *what) {
-    if (bytes > 48 * 1024) {
+    if (bytes > 32 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
         if (e != cudaSuccess) {
             set_last_error("%s: cannot reserve %zu bytes of shared memory: %s", what, bytes,

@@ -1715,7 +1715,7 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
         const size_t smem_count = sizeof(int32_t) * kSplitWarps * a.stride;
         const size_t smem_scatter = sizeof(int32_t) * ((kSplitWarps + 1) * a.stride + 2 * kSplitUnit) +
                                     sizeof(uint16_t) * kSplitUnit;
-        if (smem_scatter > 48 * 1024)   // above the default dynamic shared memory limit
+        if (smem_scatter > 32 * 1024)   // the 48 KB default also has to hold static shared memory
             cudaFuncSetAttribute(colsplit_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem_scatter);
         {

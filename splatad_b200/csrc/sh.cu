@@ -538,7 +538,7 @@ extern "C" int splatad_sh_colors_fwd(uint32_t n_elems, uint32_t N, uint32_t K, u
     if (rc != SPLATAD_OK) return rc;
     SPL_REQUIRE(colors, SPLATAD_ERR_BAD_ARG, "sh_colors_fwd: null output");
     const size_t smem = sh_colors_smem(K);
-    if (smem > 48 * 1024)
+    if (smem > 32 * 1024)
         cudaFuncSetAttribute(sh_colors_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     {
         SPL_PROF("sh_colors_fwd_kernel", (cudaStream_t)stream);
@@ -561,7 +561,7 @@ extern "C" int splatad_sh_colors_bwd(uint32_t n_elems, uint32_t N, uint32_t K, u
     if (rc != SPLATAD_OK) return rc;
     SPL_REQUIRE(v_colors, SPLATAD_ERR_BAD_ARG, "sh_colors_bwd: null argument");
     const size_t smem = sh_colors_smem(K);
-    if (smem > 48 * 1024)
+    if (smem > 32 * 1024)
         cudaFuncSetAttribute(sh_colors_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     {
         SPL_PROF("sh_colors_bwd_kernel", (cudaStream_t)stream);
@@ -582,7 +582,7 @@ extern "C" int splatad_sh_fwd(uint32_t n_elems, uint32_t K, uint32_t degrees_to_
     SPL_REQUIRE(dirs && coeffs && colors, SPLATAD_ERR_BAD_ARG, "sh_fwd: null argument");
     const size_t smem = sizeof(float) * kShThreads * (3 * K + 1);
     SPL_REQUIRE(smem <= 200 * 1024, SPLATAD_ERR_BAD_ARG, "sh_fwd: K too large");
-    if (smem > 48 * 1024)
+    if (smem > 32 * 1024)
         cudaFuncSetAttribute(sh_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     {
         SPL_PROF("sh_fwd_kernel", (cudaStream_t)stream);
@@ -603,7 +603,7 @@ extern "C" int splatad_sh_bwd(uint32_t n_elems, uint32_t K, uint32_t degrees_to_
     SPL_REQUIRE(dirs && coeffs && v_colors && v_coeffs, SPLATAD_ERR_BAD_ARG, "sh_bwd: null argument");
     const size_t smem = sizeof(float) * kShThreads * (3 * K + 1);
     SPL_REQUIRE(smem <= 200 * 1024, SPLATAD_ERR_BAD_ARG, "sh_bwd: K too large");
-    if (smem > 48 * 1024)
+    if (smem > 32 * 1024)
         cudaFuncSetAttribute(sh_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     {
         SPL_PROF("sh_bwd_kernel", (cudaStream_t)stream);

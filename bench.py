@@ -175,6 +175,48 @@ def kernel_profile(fn):
     return out
 
 
+def training_step(render, cfg, leaves, flush, steps=5):
+    """Forward + backward of one frame with a fixed seeded cotangent on every float output (the
+    training configuration's loss = sum(output * cotangent)): mean step time over `steps` steps by
+    CUDA events, L2 flushed between steps, and the library's per-kernel timings of one step."""
+    kw = dict(cfg)
+    for k in leaves:
+        kw[k] = cfg[k].detach().clone().requires_grad_(True)
+    gen = torch.Generator(device=cfg["means"].device).manual_seed(7)
+    cot = {}
+
+    def step():
+        out = render(**kw)
+        loss = 0.0
+        for i, o in enumerate(out[:-1]):
+            if o is None:
+                continue
+            if i not in cot:
+                cot[i] = torch.randn(o.shape, device=o.device, generator=gen)
+            loss = loss + (o * cot[i]).sum()
+        loss.backward()
+        for k in leaves:
+            kw[k].grad = None
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    evs = []
+    for _ in range(steps):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        step()
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    ms = float(np.mean([a.elapsed_time(b) for a, b in evs]))
+    prof = kernel_profile(step)
+    return {"ms_per_step": round(ms, 4), "steps": steps,
+            "what": "forward + backward, loss = sum(output * seeded cotangent), gradients for " + ", ".join(leaves),
+            "kernels": {k: {"launches": c, "ms": round(t, 4)} for k, (c, t) in prof.items()}}
+
+
 def fp32_probe(dev):
     """Measured FP32 FMA rate (TFLOP/s): 148*16 blocks x 256 threads x iters x 128 FMAs."""
     from splatad_b200 import _lib
@@ -411,6 +453,11 @@ def run_ours(args):
                   "n_isects": int(cam_out[2]["flatten_ids"].numel()),
                   "kernels": {k: {"launches": c, "ms": round(ms, 4)} for k, (c, ms) in cam_prof.items()}}
 
+        training = {"lidar": training_step(splatad_b200.lidar_rasterization, cfg,
+                                            ("means", "quats", "scales", "opacities", "lidar_features"), flush),
+                    "camera": training_step(splatad_b200.rasterization, cam_cfg,
+                                            ("means", "quats", "scales", "opacities", "colors"), flush)}
+
         cpu = cpu_baseline_sample()
         result = {
             "metric": "lidar_points_per_s", "value": round(value, 1), "unit": "points/s", "n_gpus": world,
@@ -431,6 +478,7 @@ def run_ours(args):
             "roofline": roofline,
             "fp32_probe": {"tflops": round(tfl, 2), "how": "FMA chains, 148*16 blocks x 256 threads"},
             "camera": camera,
+            "training": training,
             "cpu_baseline": cpu,
             "wall_s_timed_region": round(wall, 3),
         }

@@ -117,6 +117,29 @@ class _SphericalHarmonics(torch.autograd.Function):
         return None, v_dirs, v_coeffs, None
 
 
+def gather_rows(table: Tensor, ids: Tensor) -> Tensor:
+    """``table[ids]`` along the first axis, with a backward pass that adds the gradient rows into a
+    zero tensor with atomics (``index_add_``). torch's own backward of advanced indexing sorts the
+    indices first, which takes 9.7 ms for the 350 k packed rows of a 500 k-Gaussian camera frame -
+    three quarters of that frame's training step."""
+    return _GatherRows.apply(table, ids)
+
+
+class _GatherRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, table, ids):
+        ctx.save_for_backward(ids)
+        ctx.rows = table.shape[0]
+        return table.index_select(0, ids)
+
+    @staticmethod
+    def backward(ctx, v_out):
+        (ids,) = ctx.saved_tensors
+        v_table = torch.zeros((ctx.rows,) + tuple(v_out.shape[1:]), dtype=v_out.dtype, device=v_out.device)
+        v_table.index_add_(0, ids, v_out.contiguous())
+        return v_table, None
+
+
 def camera_centers(viewmats: Tensor) -> Tensor:
     """Camera centres in world coordinates, ``torch.inverse(viewmats)[:, :3, 3]`` ([C, 3]) from one
     tiny kernel (cofactors in double precision) instead of a batched LU with its error-check round

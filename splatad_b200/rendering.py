@@ -24,6 +24,7 @@ from .ops import (
     camera_centers,
     fully_fused_lidar_projection,
     fully_fused_projection,
+    gather_rows,
     isect_lidar_tiles_deferred,
     isect_tiles_deferred,
     rasterize_to_pixels,
@@ -147,7 +148,7 @@ def _rasterization(means, quats, scales, opacities, colors, velocities, viewmats
     )
     if packed:
         (camera_ids, gaussian_ids, radii, means2d, depths, conics, compensations, pix_vels) = proj_results
-        opacities = opacities[gaussian_ids]  # [nnz]
+        opacities = gather_rows(opacities, gaussian_ids)  # [nnz]
     else:
         radii, means2d, depths, conics, compensations, pix_vels = proj_results
         opacities = opacities[None] if C == 1 else opacities.repeat(C, 1)  # [C, N], no copy for one sensor
@@ -166,7 +167,7 @@ def _rasterization(means, quats, scales, opacities, colors, velocities, viewmats
     if sh_degree is None:
         if packed:
             if colors.dim() == 2:
-                colors = colors[gaussian_ids]
+                colors = gather_rows(colors, gaussian_ids)
             else:
                 colors = colors[camera_ids, gaussian_ids]
         else:

@@ -334,6 +334,33 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// Sums kSlots (a power of two <= 32) per-lane values over the warp at once: every step halves the
+// number of values a lane carries and swaps the other half with the partner lane, kSlots - 1
+// shuffles in all (plus one per remaining lane bit) where one butterfly per value takes 5 * kSlots.
+// Returns, on lane l, the warp total of value (l * kSlots) / 32; lanes that share an index return
+// the same total. v is destroyed.
+template <int kSlots>
+__device__ __forceinline__ float warp_sum_slots(float (&v)[kSlots], uint32_t lane) {
+    int off = 16;
+#pragma unroll
+    for (int half = kSlots / 2; half >= 1; half >>= 1) {
+        const bool upper = (lane & (uint32_t)off) != 0u;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+            const float send = upper ? v[i] : v[i + half];
+            const float keep = upper ? v[i + half] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+        off >>= 1;
+    }
+    float r = v[0];
+#pragma unroll
+    for (; off >= 1; off >>= 1) r += __shfl_xor_sync(0xffffffffu, r, off);
+    return r;
+}
+
+constexpr int pow2_at_least(int n) { return n <= 1 ? 1 : 2 * pow2_at_least((n + 1) / 2); }
+
 __device__ __forceinline__ int block_max_int(int v, int *red /* [32] */) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, off));
@@ -476,32 +503,41 @@ __global__ void rasterize_to_pixels_bwd_kernel(
                 for (int k = 0; k < CDIM; ++k)
                     if ((uint32_t)k < channels) buffer[k] += rgb[k] * fac;
             }
+            // warp totals by multi-value butterflies; each total then sits on its own lane, which adds it in
+            const size_t g = (size_t)sId[t];
+            float g_tot;
+            uint32_t gi;   // index of the geometry gradient this lane ends up holding
+            if (CDIM + 10 <= 16) {
+                // up to 6 channels: colours and geometry share one 16-value butterfly
+                float gs[16] = {v_conic_x, v_conic_y, v_conic_z, v_x, v_y, v_vx, v_vy, v_o, v_ax, v_ay,
+                                0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int k = 0; k < CDIM; ++k)
-                if ((uint32_t)k < channels) v_rgb[k] = warp_sum(v_rgb[k]);
-            v_conic_x = warp_sum(v_conic_x); v_conic_y = warp_sum(v_conic_y); v_conic_z = warp_sum(v_conic_z);
-            v_x = warp_sum(v_x); v_y = warp_sum(v_y);
-            v_vx = warp_sum(v_vx); v_vy = warp_sum(v_vy);
-            v_o = warp_sum(v_o);
-            if (v_means2d_abs != nullptr) { v_ax = warp_sum(v_ax); v_ay = warp_sum(v_ay); }
-            if (lane == 0) {
-                const size_t g = (size_t)sId[t];
+                for (int k = 0; k < CDIM && k < 6; ++k) gs[10 + k] = v_rgb[k];
+                g_tot = warp_sum_slots<16>(gs, lane);
+                gi = lane >> 1;
+                if ((lane & 1u) == 0u && gi >= 10u && gi - 10u < channels)
+                    atomicAdd(v_colors + g * channels + (gi - 10u), g_tot);
+            } else {
+                constexpr int kColorSlots = pow2_at_least(CDIM);
+                float cs[kColorSlots];
 #pragma unroll
-                for (int k = 0; k < CDIM; ++k)
-                    if ((uint32_t)k < channels) atomicAdd(v_colors + g * channels + k, v_rgb[k]);
-                atomicAdd(v_conics + 3 * g, v_conic_x);
-                atomicAdd(v_conics + 3 * g + 1, v_conic_y);
-                atomicAdd(v_conics + 3 * g + 2, v_conic_z);
-                atomicAdd(v_means2d + 2 * g, v_x);
-                atomicAdd(v_means2d + 2 * g + 1, v_y);
-                if (v_means2d_abs != nullptr) {
-                    atomicAdd(v_means2d_abs + 2 * g, v_ax);
-                    atomicAdd(v_means2d_abs + 2 * g + 1, v_ay);
-                }
-                atomicAdd(v_pix_vels + 2 * g, v_vx);
-                atomicAdd(v_pix_vels + 2 * g + 1, v_vy);
-                atomicAdd(v_opacities + g, v_o);
+                for (int k = 0; k < kColorSlots; ++k) cs[k] = k < CDIM ? v_rgb[k] : 0.f;
+                float gs[16] = {v_conic_x, v_conic_y, v_conic_z, v_x, v_y, v_vx, v_vy, v_o, v_ax, v_ay,
+                                0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                const float c_tot = warp_sum_slots<kColorSlots>(cs, lane);
+                g_tot = warp_sum_slots<16>(gs, lane);
+                gi = lane >> 1;
+                const uint32_t ci = (lane * (uint32_t)kColorSlots) >> 5;
+                if ((lane & (32u / kColorSlots - 1u)) == 0u && ci < channels)
+                    atomicAdd(v_colors + g * channels + ci, c_tot);
             }
+            float *dst = nullptr;
+            if (gi < 3u) dst = v_conics + 3 * g + gi;
+            else if (gi < 5u) dst = v_means2d + 2 * g + (gi - 3u);
+            else if (gi < 7u) dst = v_pix_vels + 2 * g + (gi - 5u);
+            else if (gi == 7u) dst = v_opacities + g;
+            else if (gi < 10u && v_means2d_abs != nullptr) dst = v_means2d_abs + 2 * g + (gi - 8u);
+            if ((lane & 1u) == 0u && dst != nullptr) atomicAdd(dst, g_tot);
         }
     }
 }
@@ -677,38 +713,31 @@ __global__ void rasterize_to_points_bwd_kernel(
                     v_o += v_asum * vis;
                 }
             }
+            // warp totals: the feature gradients in one multi-value butterfly, the thirteen geometry
+            // gradients in another; each total then sits on its own lane, which adds it in
+            constexpr int kColorSlots = pow2_at_least(CDIM);
+            float cs[kColorSlots];
 #pragma unroll
-            for (int k = 0; k < CDIM; ++k)
-                if ((uint32_t)k < channels) v_rgb[k] = warp_sum(v_rgb[k]);
-            v_conic_x = warp_sum(v_conic_x); v_conic_y = warp_sum(v_conic_y); v_conic_z = warp_sum(v_conic_z);
-            v_x = warp_sum(v_x); v_y = warp_sum(v_y);
-            v_vx = warp_sum(v_vx); v_vy = warp_sum(v_vy); v_vz = warp_sum(v_vz);
-            v_dcx = warp_sum(v_dcx); v_dcy = warp_sum(v_dcy);
-            v_o = warp_sum(v_o);
-            if (v_means2d_abs != nullptr) { v_ax = warp_sum(v_ax); v_ay = warp_sum(v_ay); }
-            if (lane == 0) {
-                const size_t g = (size_t)sId[t];
-#pragma unroll
-                for (int k = 0; k < CDIM; ++k) {
-                    if ((uint32_t)k < fstride) atomicAdd(v_colors + g * fstride + k, v_rgb[k]);
-                    else if ((uint32_t)k < channels) atomicAdd(v_ranges + g, v_rgb[k]);
-                }
-                atomicAdd(v_conics + 3 * g, v_conic_x);
-                atomicAdd(v_conics + 3 * g + 1, v_conic_y);
-                atomicAdd(v_conics + 3 * g + 2, v_conic_z);
-                atomicAdd(v_means2d + 2 * g, v_x);
-                atomicAdd(v_means2d + 2 * g + 1, v_y);
-                if (v_means2d_abs != nullptr) {
-                    atomicAdd(v_means2d_abs + 2 * g, v_ax);
-                    atomicAdd(v_means2d_abs + 2 * g + 1, v_ay);
-                }
-                atomicAdd(v_pix_vels + 3 * g, v_vx);
-                atomicAdd(v_pix_vels + 3 * g + 1, v_vy);
-                atomicAdd(v_pix_vels + 3 * g + 2, v_vz);
-                atomicAdd(v_depth_comps + 2 * g, v_dcx);
-                atomicAdd(v_depth_comps + 2 * g + 1, v_dcy);
-                atomicAdd(v_opacities + g, v_o);
+            for (int k = 0; k < kColorSlots; ++k) cs[k] = k < CDIM ? v_rgb[k] : 0.f;
+            float gs[16] = {v_conic_x, v_conic_y, v_conic_z, v_x, v_y, v_vx, v_vy, v_vz, v_dcx, v_dcy,
+                            v_o, v_ax, v_ay, 0.f, 0.f, 0.f};
+            const float c_tot = warp_sum_slots<kColorSlots>(cs, lane);
+            const float g_tot = warp_sum_slots<16>(gs, lane);
+            const size_t g = (size_t)sId[t];
+            const uint32_t ci = (lane * (uint32_t)kColorSlots) >> 5;
+            if ((lane & (32u / kColorSlots - 1u)) == 0u) {
+                if (ci < fstride) atomicAdd(v_colors + g * fstride + ci, c_tot);
+                else if (ci < channels) atomicAdd(v_ranges + g, c_tot);
             }
+            const uint32_t gi = lane >> 1;
+            float *dst = nullptr;
+            if (gi < 3u) dst = v_conics + 3 * g + gi;
+            else if (gi < 5u) dst = v_means2d + 2 * g + (gi - 3u);
+            else if (gi < 8u) dst = v_pix_vels + 3 * g + (gi - 5u);
+            else if (gi < 10u) dst = v_depth_comps + 2 * g + (gi - 8u);
+            else if (gi == 10u) dst = v_opacities + g;
+            else if (gi < 13u && v_means2d_abs != nullptr) dst = v_means2d_abs + 2 * g + (gi - 11u);
+            if ((lane & 1u) == 0u && dst != nullptr) atomicAdd(dst, g_tot);
         }
     }
 }

@@ -500,10 +500,28 @@ def run_frames(args):
     else:
         cfg = to_device(scenes.config1(), dev)
         fn = lambda: splatad_b200.rasterization(**cfg)  # noqa: E731
+    if args.train:
+        # forward + backward per frame, like training_step(): the command profiled for the backward kernels
+        leaves = ("means", "quats", "scales", "opacities", "lidar_features" if args.workload == "lidar" else "colors")
+        for k in leaves:
+            cfg[k] = cfg[k].detach().clone().requires_grad_(True)
+        gen = torch.Generator(device=dev).manual_seed(7)
+        cot = {}
     for _ in range(args.frames):
         out = fn()
+        if args.train:
+            loss = 0.0
+            for i, o in enumerate(out[:-1]):
+                if o is None:
+                    continue
+                if i not in cot:
+                    cot[i] = torch.randn(o.shape, device=dev, generator=gen)
+                loss = loss + (o * cot[i]).sum()
+            loss.backward()
+            for k in leaves:
+                cfg[k].grad = None
     torch.cuda.synchronize()
-    print(json.dumps({"frames": args.frames, "workload": args.workload,
+    print(json.dumps({"frames": args.frames, "workload": args.workload, "train": bool(args.train),
                       "n_isects": int(out[-1]["flatten_ids"].numel())}))
 
 
@@ -583,6 +601,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--frames", type=int, default=0,
                     help="only render this many frames of the workload and exit (for use under ncu)")
+    ap.add_argument("--train", action="store_true",
+                    help="with --frames: forward + backward per frame (sum(output * seeded cotangent))")
     ap.add_argument("--workload", default="lidar", choices=["lidar", "camera"],
                     help="with --frames: config 2 lidar (default) or config 1 camera")
     args = ap.parse_args()

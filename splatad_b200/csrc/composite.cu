@@ -394,7 +394,9 @@ __global__ void rasterize_to_pixels_bwd_kernel(
     float4 *sA = reinterpret_cast<float4 *>(smem_raw);
     float4 *sB = sA + bs;
     int32_t *sId = reinterpret_cast<int32_t *>(sB + bs);
-    float *sRgb = reinterpret_cast<float *>(sId + bs);   // [bs * channels]
+    int32_t *sPos = sId + bs;                            // list position of the staged entry
+    float *sRgb = reinterpret_cast<float *>(sPos + bs);  // [bs * channels]
+    __shared__ uint32_t s_warp_kept[32];
 
     const uint32_t tiles_per_cam = tile_w * tile_h;
     const uint32_t cam = blockIdx.x / tiles_per_cam;
@@ -405,8 +407,18 @@ __global__ void rasterize_to_pixels_bwd_kernel(
     const uint32_t j = tx * tile_size + tr % tile_size;
     const bool inside = (tr < tile_size * tile_size) && (i < H && j < W);
     const float px = (float)j + 0.5f, py = (float)i + 0.5f;
-    const float roll = rs_time[cam] * ((py - 0.5f) / (float)(H - 1) - 0.5f);
+    const float rs = rs_time[cam];
+    const float roll = rs * ((py - 0.5f) / (float)(H - 1) - 0.5f);
     const size_t pix = ((size_t)cam * H + min(i, H - 1)) * W + min(j, W - 1);
+    // box of the tile's pixel centres and the shutter offsets of its first and last row, as in the
+    // forward kernel: entries that cannot be seen anywhere in the tile are not staged
+    const float box_x0 = (float)(tx * tile_size) + 0.5f;
+    const float box_x1 = (float)min((tx + 1) * tile_size, W) - 0.5f;
+    const float box_y0 = (float)(ty * tile_size) + 0.5f;
+    const float box_y1 = (float)min((ty + 1) * tile_size, H) - 0.5f;
+    const float roll_a = rs * ((box_y0 - 0.5f) / (float)(H - 1) - 0.5f);
+    const float roll_b = rs * ((box_y1 - 0.5f) / (float)(H - 1) - 0.5f);
+    const float roll_lo = fminf(roll_a, roll_b), roll_hi = fmaxf(roll_a, roll_b);
 
     const TileRange range = tile_range(offsets, blockIdx.x, C * tiles_per_cam, n_isects);
 
@@ -433,26 +445,50 @@ __global__ void rasterize_to_pixels_bwd_kernel(
     const int32_t eff_end = min(range.end, tile_last + 1);
     if (eff_end <= range.start) return;
     const uint32_t num_batches = (uint32_t)(eff_end - range.start + bs - 1) / bs;
-    const uint32_t lane = tr & 31;
+    const uint32_t lane = tr & 31, warp = tr >> 5, n_warps = bs >> 5;
 
     for (uint32_t b = 0; b < num_batches; ++b) {
         __syncthreads();
         const int32_t batch_end = eff_end - 1 - (int32_t)(bs * b);
-        const int32_t batch_size = min((int32_t)bs, batch_end + 1 - range.start);
         const int32_t idx = batch_end - (int32_t)tr;
+        bool keep = false;
+        int32_t g = 0;
+        float4 A, B0;
         if (idx >= range.start) {
-            const int32_t g = flatten_ids[idx];
+            g = flatten_ids[idx];
             const float2 xy = means2d[g];
             const float2 v = pix_vels[g];
-            sA[tr] = make_float4(xy.x, xy.y, v.x, v.y);
-            sB[tr] = make_float4(conics[3 * (size_t)g], conics[3 * (size_t)g + 1],
-                                 conics[3 * (size_t)g + 2], opacities[g]);
-            sId[tr] = g;
-            for (uint32_t k = 0; k < channels; ++k) sRgb[tr * channels + k] = colors[(size_t)g * channels + k];
+            A = make_float4(xy.x, xy.y, v.x, v.y);
+            B0 = make_float4(conics[3 * (size_t)g], conics[3 * (size_t)g + 1],
+                             conics[3 * (size_t)g + 2], opacities[g]);
+            const float mx_a = A.x + roll_lo * A.z, mx_b = A.x + roll_hi * A.z;
+            const float my_a = A.y + roll_lo * A.w, my_b = A.y + roll_hi * A.w;
+            keep = !never_visible_in_box(B0.x, B0.y, B0.z, B0.w, fminf(mx_a, mx_b) - box_x1,
+                                         fmaxf(mx_a, mx_b) - box_x0, fminf(my_a, my_b) - box_y1,
+                                         fmaxf(my_a, my_b) - box_y0);
+        }
+        // survivors to the front, still back to front in list order
+        const uint32_t kept_mask = __ballot_sync(0xffffffffu, keep);
+        if (lane == 0) s_warp_kept[warp] = __popc(kept_mask);
+        __syncthreads();
+        uint32_t pos = __popc(kept_mask & ((1u << lane) - 1u)), n_kept = 0;
+        for (uint32_t w = 0; w < n_warps; ++w) {
+            const uint32_t cnt = s_warp_kept[w];
+            if (w < warp) pos += cnt;
+            n_kept += cnt;
+        }
+        if (keep) {
+            sA[pos] = A;
+            sB[pos] = B0;
+            sId[pos] = g;
+            sPos[pos] = idx;
+            for (uint32_t k = 0; k < channels; ++k) sRgb[pos * channels + k] = colors[(size_t)g * channels + k];
         }
         __syncthreads();
-        for (int32_t t = max(0, batch_end - warp_bin_final); t < batch_size; ++t) {
-            bool valid = inside && (batch_end - t <= bin_final);
+        for (uint32_t t = 0; t < n_kept; ++t) {
+            const int32_t entry = sPos[t];
+            if (entry > warp_bin_final) continue;   // behind everything this warp consumed
+            bool valid = inside && (entry <= bin_final);
             float alpha = 0.f, opac = 0.f, vis = 0.f, dx = 0.f, dy = 0.f;
             float4 B = make_float4(0.f, 0.f, 0.f, 0.f);
             if (valid) {
@@ -850,7 +886,7 @@ extern "C" int splatad_rasterize_to_pixels_bwd(
                     v_pix_vels && rolling_shutter_time,
                 SPLATAD_ERR_BAD_ARG, "rasterize_to_pixels_bwd: null argument");
     const uint32_t bs = ((tile_size * tile_size + 31) / 32) * 32;   // whole warps
-    const size_t smem = (size_t)bs * (2 * sizeof(float4) + sizeof(int32_t) + channels * sizeof(float));
+    const size_t smem = (size_t)bs * (2 * sizeof(float4) + 2 * sizeof(int32_t) + channels * sizeof(float));
 #define CALL(D)                                                                                   \
     {                                                                                             \
         int rc = check_block_size(rasterize_to_pixels_bwd_kernel<D>, bs, channels, "rasterize_to_pixels_bwd"); \

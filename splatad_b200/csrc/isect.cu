@@ -764,13 +764,16 @@ constexpr uint32_t kSplitMaxWidth = 1024;                  // tiles per row
 constexpr uint32_t kSplitMaxTiles = 16384;
 constexpr uint32_t kSplitMaxSlots = kSplitMaxTiles + kSplitMaxRows;   // rows * (row_width + 1)
 constexpr uint32_t kSplitWarps = 8;
-constexpr uint32_t kSplitWarpEntries = 128;                // entries per warp in step A
-constexpr uint32_t kSplitEntries = kSplitWarps * kSplitWarpEntries;   // entries per block
+// Entries per warp in step A, chosen per call: 128 for grids of up to 32 rows, 32 above (a warp walks
+// its entries 32 at a time and loops over the rows for each window: with many rows that chain gets
+// long and short pieces keep more warps in flight; config 1, 68 rows: step A 119 -> 71 us).
+constexpr uint32_t kSplitWarpEntriesMin = 32, kSplitWarpEntriesMax = 128;
 constexpr uint32_t kSplitSub = 512;                        // outputs per warp in step B
 constexpr uint32_t kSplitUnit = kSplitWarps * kSplitSub;   // outputs per block in step B
 constexpr uint32_t kSplitColBits = 11;
 
 struct SplitArgs {
+    uint32_t warp_entries;       // step A: entries per warp (a multiple of 32)
     // entries: rectangles by flatten index, visited in depth order
     const uint32_t *rect_xw;     // [total] x0 | width << 16
     const uint32_t *rect_yh;     // [total] first grid row | height << 16
@@ -833,7 +836,7 @@ __device__ __forceinline__ SplitEntry split_load_entry(const SplitArgs &a, uint3
     return e;
 }
 
-// Records and outputs per grid row of the kSplitWarpEntries entries starting at `first`, for the
+// Records and outputs per grid row of the a.warp_entries entries starting at `first`, for the
 // 32 rows starting at `row_lo`; lane l holds row row_lo + l.
 __device__ __forceinline__ void split_rows_of_warp(const SplitArgs &a, uint32_t first, uint32_t n_entries,
                                                    uint32_t lane, uint32_t row_lo, uint32_t &cnt,
@@ -841,7 +844,7 @@ __device__ __forceinline__ void split_rows_of_warp(const SplitArgs &a, uint32_t 
     cnt = 0;
     out = 0;
     const uint32_t row_hi = min(a.rows, row_lo + 32u);
-    for (uint32_t win = 0; win < kSplitWarpEntries / 32; ++win) {
+    for (uint32_t win = 0; win < a.warp_entries / 32; ++win) {
         const uint32_t base = first + win * 32;
         if (base >= n_entries) break;
         const SplitEntry e = split_load_entry(a, base + lane, n_entries);
@@ -872,7 +875,7 @@ rowsplit_count_kernel(SplitArgs a) {
     if (split_overflow(a)) return;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t n_entries = (uint32_t)(*a.n_entries_ptr);
-    const uint32_t first = blockIdx.x * kSplitEntries;
+    const uint32_t first = blockIdx.x * kSplitWarps * a.warp_entries;
     if (first >= n_entries) return;
     if (threadIdx.x < kSplitMaxRows) {
         s_cnt[threadIdx.x] = 0;
@@ -882,7 +885,7 @@ rowsplit_count_kernel(SplitArgs a) {
     const uint32_t wu = blockIdx.x * kSplitWarps + warp;
     for (uint32_t row_lo = 0; row_lo < a.rows; row_lo += 32) {
         uint32_t cnt, out;
-        split_rows_of_warp(a, first + warp * kSplitWarpEntries, n_entries, lane, row_lo, cnt, out);
+        split_rows_of_warp(a, first + warp * a.warp_entries, n_entries, lane, row_lo, cnt, out);
         const uint32_t r = row_lo + lane;
         if (r < a.rows) {
             // kept per warp too, so that the scatter does not have to count again
@@ -911,7 +914,8 @@ rowsplit_scan_kernel(SplitArgs a, unsigned long long *__restrict__ ticket) {
     const uint32_t r = blockIdx.x, tid = threadIdx.x;
     if (split_overflow(a)) return;
     const uint32_t n_entries = (uint32_t)(*a.n_entries_ptr);
-    const uint32_t n_units = (n_entries + kSplitEntries - 1) / kSplitEntries;
+    const uint32_t block_entries = kSplitWarps * a.warp_entries;
+    const uint32_t n_units = (n_entries + block_entries - 1) / block_entries;
     uint32_t carry_c = 0, carry_o = 0;
     for (uint32_t u0 = 0; u0 < n_units; u0 += 1024) {
         const uint32_t u = u0 + tid;
@@ -969,7 +973,7 @@ rowsplit_scatter_kernel(SplitArgs a) {
     if (split_overflow(a)) return;
     const uint32_t n_entries = (uint32_t)(*a.n_entries_ptr);
     const uint32_t wu = blockIdx.x * kSplitWarps + warp;
-    const uint32_t first = wu * kSplitWarpEntries;
+    const uint32_t first = wu * a.warp_entries;
     if (first >= n_entries) return;
     const uint32_t cap = (uint32_t)(a.capacity < 0x7fffffffll ? a.capacity : 0x7fffffffll);
     for (uint32_t row_lo = 0; row_lo < (kOneGroup ? 1u : a.rows); row_lo += 32) {
@@ -986,7 +990,7 @@ rowsplit_scatter_kernel(SplitArgs a) {
                 out_at += a.hw_out[w2 * a.rows + my_row];
             }
         }
-        for (uint32_t win = 0; win < kSplitWarpEntries / 32; ++win) {
+        for (uint32_t win = 0; win < a.warp_entries / 32; ++win) {
             const uint32_t base = first + win * 32;
             if (base >= n_entries) break;
             const uint32_t p = base + lane;
@@ -1463,11 +1467,12 @@ static PlanWs carve_plan(void *ws, uint64_t total) {
     p.keyB = (uint32_t *)take(sizeof(uint32_t) * total);
     p.valB = (uint32_t *)take(sizeof(uint32_t) * total);
     p.eoff = (uint32_t *)take(sizeof(uint32_t) * total);
-    const size_t n_ha = (size_t)((total + 1023) / 1024) * 128;   // kSplitEntries, kSplitMaxRows
+    const uint64_t smallest_block = kSplitWarps * kSplitWarpEntriesMin;
+    const size_t n_ha = (size_t)((total + smallest_block - 1) / smallest_block) * kSplitMaxRows;
     p.ha_cnt = (uint32_t *)take(sizeof(uint32_t) * n_ha);
     p.ha_out = (uint32_t *)take(sizeof(uint32_t) * n_ha);
-    p.hw_cnt = (uint32_t *)take(sizeof(uint32_t) * n_ha * 8);    // kSplitWarps
-    p.hw_out = (uint32_t *)take(sizeof(uint32_t) * n_ha * 8);
+    p.hw_cnt = (uint32_t *)take(sizeof(uint32_t) * n_ha * kSplitWarps);
+    p.hw_out = (uint32_t *)take(sizeof(uint32_t) * n_ha * kSplitWarps);
     p.rect_xw = (uint32_t *)take(sizeof(uint32_t) * total);
     p.rect_yh = (uint32_t *)take(sizeof(uint32_t) * total);
     p.bytes = off;
@@ -1711,7 +1716,8 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
         a.row_rec = w.row_rec; a.row_out = w.row_out; a.row_unit = w.row_unit;
         a.rec = w.rec;
         a.hb = w.hb; a.hw = w.hw; a.hb_first = w.hb_first; a.slot_tot = w.slot_tot; a.slot_base = w.slot_base;
-        const uint32_t units_a = div_up(g.total, kSplitEntries);
+        a.warp_entries = a.rows > 32 ? kSplitWarpEntriesMin : kSplitWarpEntriesMax;
+        const uint32_t units_a = div_up(g.total, kSplitWarps * a.warp_entries);
         const size_t smem_count = sizeof(int32_t) * kSplitWarps * a.stride;
         const size_t smem_scatter = sizeof(int32_t) * ((kSplitWarps + 1) * a.stride + 2 * kSplitUnit) +
                                     sizeof(uint16_t) * kSplitUnit;

@@ -1168,8 +1168,8 @@ colsplit_count_kernel(SplitArgs a) {
     }
 }
 
-// Block r: exclusive scan over the units of grid row r for every column (in place); the column
-// totals go to slot_tot[r][col]. The block that finishes last (an atomic ticket, nobody waits)
+// One block per grid row and group of 32 columns: exclusive scan over the units of the row for
+// those columns (in place); the column totals go to slot_tot[r][col]. The block that finishes last (an atomic ticket, nobody waits)
 // scans the totals into slot_base and, when asked, writes the tile offsets - the slot starts
 // without the closing column of every row - followed by the total.
 __global__ void __launch_bounds__(1024)
@@ -1179,21 +1179,23 @@ colsplit_scan_kernel(SplitArgs a, unsigned long long *__restrict__ ticket, int32
     __shared__ uint32_t wt[33];
     __shared__ bool s_last;
     const uint32_t lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
-    const uint32_t r = blockIdx.x;
+    // one block per (grid row, group of 32 columns)
+    const uint32_t n_groups = (a.stride + 31) / 32;
+    const uint32_t r = blockIdx.x / n_groups, c_first = (blockIdx.x - r * n_groups) * 32;
     const uint32_t n_tiles = a.rows * a.row_width;
     if (split_overflow(a)) {
         // the split is skipped for lack of room: every offset 0, so that compositing enqueued
         // behind it finds empty tiles instead of stale numbers
         if (offsets != nullptr)
-            for (uint32_t t = r * 1024 + threadIdx.x; t <= n_tiles; t += gridDim.x * 1024) offsets[t] = 0;
+            for (uint32_t t = blockIdx.x * 1024 + threadIdx.x; t <= n_tiles; t += gridDim.x * 1024) offsets[t] = 0;
         return;
     }
     const uint32_t ub0 = a.row_unit[r], n_units = a.row_unit[r + 1] - ub0;
     const uint32_t per = (n_units + 31) / 32;
     const uint32_t u_lo = min(n_units, seg * per), u_hi = min(n_units, u_lo + per);
     const size_t S = a.stride;
-    for (uint32_t c0 = 0; c0 < a.stride; c0 += 32) {
-        const uint32_t c = c0 + lane;
+    {
+        const uint32_t c = c_first + lane;
         const bool live = c < a.stride;
         uint32_t *col = a.hb + (size_t)ub0 * S + c;
         uint32_t sum = 0;
@@ -1226,6 +1228,7 @@ colsplit_scan_kernel(SplitArgs a, unsigned long long *__restrict__ ticket, int32
             if (seg == 0) a.slot_tot[r * a.stride + c] = total;
         }
     }
+    __threadfence();   // the writers of slot_tot publish before the ticket is taken
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
@@ -1744,7 +1747,7 @@ static int isect_fill(const IsectGeom &g, const int32_t *tiles_per_gauss, int so
         }
         {
             SPL_PROF("colsplit_scan_kernel", st);
-            launch_chained(colsplit_scan_kernel, a.rows, 1024, 0, st, a,
+            launch_chained(colsplit_scan_kernel, a.rows * ((a.stride + 31) / 32), 1024, 0, st, a,
                            (unsigned long long *)(p.counters + CNT_TICKET), tile_offsets);
             tile_offsets = nullptr;   // done
         }

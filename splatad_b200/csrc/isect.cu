@@ -805,19 +805,6 @@ __device__ __forceinline__ uint32_t rec_off(const SplitArgs &a, uint32_t p) {
     return __ldg(reinterpret_cast<const uint32_t *>(a.rec + p) + 1);
 }
 
-__device__ __forceinline__ uint32_t warp_find_entry(const SplitArgs &a, uint32_t lo, uint32_t hi,
-                                                    uint32_t q, uint32_t lane) {
-    while (lo < hi) {
-        const uint32_t step = (hi - lo + 31) / 32;
-        const uint64_t pp = (uint64_t)lo + (uint64_t)(lane + 1) * step;
-        const bool le = (pp <= hi) && (rec_off(a, (uint32_t)pp) <= q);
-        const uint32_t c = __popc(__ballot_sync(0xffffffffu, le));
-        lo += c * step;
-        hi = min(hi, lo + step - 1);
-    }
-    return lo;
-}
-
 // ---- step A: rows -----------------------------------------------------------------------
 struct SplitEntry {
     uint32_t xw, row0, h, idx;
@@ -981,10 +968,12 @@ rowsplit_scatter_kernel(SplitArgs a) {
         // blocks (scanned), earlier warps of this block (as counted)
         const uint32_t row_hi = min(a.rows, row_lo + 32u);
         const uint32_t my_row = row_lo + lane;
-        uint32_t rec_at = 0, out_at = 0;
+        uint32_t rec_at = 0, out_at = 0, row_start = 0, row_piece0 = 0;
         if (my_row < a.rows) {
+            row_start = a.row_out[my_row];
+            row_piece0 = a.row_unit[my_row] * kSplitWarps;   // first step-B piece of the row
             rec_at = a.row_rec[my_row] + a.ha_cnt[blockIdx.x * a.rows + my_row];
-            out_at = a.row_out[my_row] + a.ha_out[blockIdx.x * a.rows + my_row];
+            out_at = row_start + a.ha_out[blockIdx.x * a.rows + my_row];
             for (uint32_t w2 = blockIdx.x * kSplitWarps; w2 < wu; ++w2) {
                 rec_at += a.hw_cnt[w2 * a.rows + my_row];
                 out_at += a.hw_out[w2 * a.rows + my_row];
@@ -1022,9 +1011,19 @@ rowsplit_scatter_kernel(SplitArgs a) {
                 const uint32_t total = __shfl_sync(0xffffffffu, inc, 31);
                 const uint32_t rbase = __shfl_sync(0xffffffffu, rec_at, r - row_lo);
                 const uint32_t obase = __shfl_sync(0xffffffffu, out_at, r - row_lo);
+                const uint32_t rstart = __shfl_sync(0xffffffffu, row_start, r - row_lo);
+                const uint32_t rpiece0 = __shfl_sync(0xffffffffu, row_piece0, r - row_lo);
                 if (hit) {
                     const uint32_t pos = rbase + __popc(bal & lt);
-                    if (pos < cap) a.rec[pos] = make_uint4(xs | (w << 16), obase + inc - v, idx, depth);
+                    const uint32_t s0 = obase + inc - v;
+                    if (pos < cap) {
+                        a.rec[pos] = make_uint4(xs | (w << 16), s0, idx, depth);
+                        // step B cuts the row's outputs into pieces of kSplitSub: the record that
+                        // holds the first output of a piece is noted for it
+                        const uint32_t rel = s0 - rstart;
+                        for (uint32_t m = (rel + kSplitSub - 1) / kSplitSub; m * kSplitSub < rel + w; ++m)
+                            a.hb_first[rpiece0 + m] = pos;
+                    }
                 }
                 if (my_row == r) {
                     rec_at += __popc(bal);
@@ -1068,14 +1067,13 @@ __device__ __forceinline__ SplitUnit split_unit(const SplitArgs &a, uint32_t u, 
     return s;
 }
 
-// Adds the outputs [q_lo, q_hi) to a difference row (one record per lane).
-// Returns the record that owns output q_lo.
-__device__ __forceinline__ uint32_t split_count_cols(int32_t *d, const SplitArgs &a, uint32_t q_lo,
-                                                     uint32_t q_hi, uint32_t n_rec, uint32_t n_out,
-                                                     uint32_t lane) {
-    if (q_lo >= q_hi || n_rec == 0) return 0u;
+// Adds the outputs [q_lo, q_hi) to a difference row (one record per lane), starting at the record
+// `first` that owns output q_lo (noted by step A's scatter).
+__device__ __forceinline__ void split_count_cols(int32_t *d, const SplitArgs &a, uint32_t q_lo,
+                                                 uint32_t q_hi, uint32_t n_rec, uint32_t n_out,
+                                                 uint32_t first, uint32_t lane) {
+    if (q_lo >= q_hi || n_rec == 0) return;
     const uint32_t rw = a.row_width;
-    const uint32_t first = warp_find_entry(a, 0, n_rec - 1, q_lo, lane);
     uint32_t base = first;
     while (true) {
         const uint32_t p = base + lane;
@@ -1118,7 +1116,6 @@ __device__ __forceinline__ uint32_t split_count_cols(int32_t *d, const SplitArgs
         if (base + 32 >= n_rec || last_s1 >= q_hi) break;
         base += 32;
     }
-    return first;
 }
 
 // In-place inclusive prefix sum of d[0 .. n) by one warp.
@@ -1150,15 +1147,16 @@ colsplit_count_kernel(SplitArgs a) {
     for (uint32_t i = lane; i < a.stride; i += 32) wd[i] = 0;
     __syncwarp();
     const uint32_t q_lo = min(u.q_hi, u.q_lo + warp * kSplitSub);
-    const uint32_t first = split_count_cols(wd, a, q_lo, min(u.q_hi, q_lo + kSplitSub), u.n_rec, u.n_out, lane);
+    const uint32_t q_hi = min(u.q_hi, q_lo + kSplitSub);
+    const size_t piece = (size_t)blockIdx.x * kSplitWarps + warp;
+    const uint32_t first = q_lo < q_hi ? min(a.hb_first[piece], u.n_rec ? u.n_rec - 1 : 0u) : 0u;
+    split_count_cols(wd, a, q_lo, q_hi, u.n_rec, u.n_out, first, lane);
     __syncwarp();
     warp_prefix_inplace(wd, a.stride, lane);
     __syncthreads();
     // per warp (so that the scatter does not have to count again) and per unit (to be scanned)
-    const size_t piece = (size_t)blockIdx.x * kSplitWarps + warp;
     uint32_t *prow = a.hw + piece * a.stride;
     for (uint32_t i = lane; i < a.stride; i += 32) prow[i] = (uint32_t)wd[i];
-    if (lane == 0) a.hb_first[piece] = first;
     uint32_t *row = a.hb + (size_t)blockIdx.x * a.stride;
     for (uint32_t i = tid; i < a.stride; i += blockDim.x) {
         uint32_t tot = 0;

@@ -122,6 +122,14 @@ def isect_tiles(means2d, radii, depths, tile_size, tile_width, tile_height, sort
     return tpg.reshape(shape), ids, flat
 
 
+def camera_tile_counts(means2d, radii, tile_size, tile_width, tile_height) -> np.ndarray:
+    """Tiles per (sensor, Gaussian) of :func:`isect_tiles` without emitting or sorting anything."""
+    r = radii.reshape(-1, 2)
+    x0, x1, y0, y1 = cam_rects(means2d.reshape(-1, 2), r, tile_size, tile_width, tile_height)
+    cnt = np.where(r[:, 0] > 0, (y1 - y0) * (x1 - x0), 0)
+    return cnt.astype(np.int32).reshape(radii.shape[:-1])
+
+
 def isect_lidar_tiles(means2d, radii, depths, elev_boundaries, tile_azim_resolution, min_azim, sort=True,
                       n_cameras: Optional[int] = None, camera_ids=None):
     packed = means2d.ndim == 2

@@ -111,6 +111,26 @@ def lidar_from_projection(radii, means2d, depths, conics, opacities, pix_vels, d
     return dict(tiles_per_gauss=tpg, isect_ids=ids, flatten_ids=flat, isect_offsets=offsets, out=out)
 
 
+def camera_from_projection(radii, means2d, depths, conics, opacities, pix_vels, colors, rolling_shutter_time,
+                           width, height, tile_size, n_cameras, camera_ids=None, backgrounds=None,
+                           dtype=np.float32):
+    """Tile intersection + compositing of the oracle on GIVEN camera projection outputs and colours
+    ([C,N,..] arrays, or [nnz,..] rows with ``camera_ids`` for the packed layout), so that the list
+    stages and the image are compared on identical stage inputs. ``colors`` already carries every
+    rendered channel (e.g. RGB + depth). Returns dict(tiles_per_gauss, isect_ids, flatten_ids,
+    isect_offsets, out=<composite dict>)."""
+    tw = math.ceil(width / float(tile_size))
+    th = math.ceil(height / float(tile_size))
+    tpg, ids, flat = isect.isect_tiles(np.asarray(means2d, np.float32), np.asarray(radii),
+                                       np.asarray(depths, np.float32), tile_size, tw, th,
+                                       n_cameras=n_cameras, camera_ids=camera_ids)
+    offsets = isect.isect_offset_encode(ids, n_cameras, tw, th)
+    out = composite.rasterize_to_pixels_fwd(means2d, conics, np.ascontiguousarray(colors), opacities, pix_vels,
+                                            np.asarray(rolling_shutter_time), backgrounds, width, height,
+                                            tile_size, offsets, flat, dtype=dtype)
+    return dict(tiles_per_gauss=tpg, isect_ids=ids, flatten_ids=flat, isect_offsets=offsets, out=out)
+
+
 def rasterization(
     means, quats, scales, opacities, colors, velocities, viewmats, Ks, width, height,
     linear_velocity=None, angular_velocity=None, rolling_shutter_time=None, near_plane=0.01,
@@ -180,3 +200,120 @@ def rasterization(
                 last_ids=out["last_ids"], ambiguous=out["ambiguous"], tested=out["tested"],
                 contributing=out["contributing"])
     return render, out["render_alphas"], meta
+
+
+# ---------------------------------------------------------------------------------------------
+# Float64 gradient chains: projection (torch autograd) -> [SH colours] -> analytic compositing
+# backward (C), on GIVEN tile lists. What an end-to-end training step is checked against.
+# ---------------------------------------------------------------------------------------------
+def _leaf64(x):
+    return None if x is None else torch.as_tensor(x).detach().to(torch.float64).cpu().clone().requires_grad_(True)
+
+
+def lidar_gradients_f64(cfg, offsets, flatten_ids, cotangents, names, mask_f32=None, amb_tol=1e-4, **kw):
+    """Gradients of ``sum(features * cot[0] * mask) + sum(alphas * cot[1] * mask) + sum(alpha_sum *
+    cot[2] * mask)`` with respect to ``cfg[name]`` for ``name in names``, in float64, through the
+    oracle's differentiable lidar projection and the analytic compositing backward, on the given
+    tile lists ([C, grid_h, grid_w] offsets, flatten ids into the [C, N] layout).
+
+    ``mask`` [C, H, W] keeps the points whose include / skip / stop decisions are the same in
+    float32 (``mask_f32``: oracle compositing dict of a float32 run with the same ``amb_tol``, or
+    None to compute one on the float32 cast of this projection) and float64. Returns (grads dict,
+    mask, float64 forward dict)."""
+    C = cfg["viewmats"].shape[0]
+    L = {k: _leaf64(cfg[k]) for k in names}
+    get = lambda k: L[k] if k in L else (None if cfg.get(k) is None else torch.as_tensor(cfg[k]).double())  # noqa: E731
+    zeros = lambda *s: torch.zeros(*s, dtype=torch.float64)  # noqa: E731
+    lin = get("linear_velocity") if cfg.get("linear_velocity") is not None else zeros(C, 3)
+    ang = get("angular_velocity") if cfg.get("angular_velocity") is not None else zeros(C, 3)
+    rs = get("rolling_shutter_time") if cfg.get("rolling_shutter_time") is not None else zeros(C)
+    radii, means2d, depths, conics, comps, pix_vels, dcomp = projection.fully_fused_lidar_projection(
+        get("means"), None, get("quats"), get("scales"), get("velocities"), get("viewmats"), lin, ang, rs,
+        cfg.get("min_elevation", -80), cfg.get("max_elevation", 80), cfg.get("min_azimuth", -180),
+        cfg.get("max_azimuth", 180), cfg.get("eps2d", 0.017), cfg.get("near_plane", 0.01),
+        cfg.get("far_plane", 1e10), cfg.get("radius_clip", 0.0), kw.get("rasterize_mode") == "antialiased")
+    opac = get("opacities")[None].repeat(C, 1)
+    if comps is not None:
+        opac = opac * comps
+    if not kw.get("use_depth_compensation", True):
+        dcomp = dcomp * 0
+    feats = torch.cat([get("lidar_features"), depths[..., None]], dim=-1)
+    pts = np.asarray(torch.as_tensor(cfg["raster_pts"]).double())
+    H, W = pts.shape[1:3]
+    asum = kw.get("compute_alpha_sum_until_points", True)
+    thr = kw.get("compute_alpha_sum_until_points_threshold", 0.2)
+    stage = [means2d, conics, feats, opac, pix_vels, dcomp]
+    vals = [_np(x) for x in stage]
+    geom = (pts, W, H, cfg["tile_width"], cfg["tile_height"], np.asarray(offsets), np.asarray(flatten_ids), asum, thr)
+    f64 = composite.rasterize_to_points_fwd(*vals, None, *geom, dtype=np.float64)
+    if mask_f32 is None:
+        mask_f32 = composite.rasterize_to_points_fwd(*[v.astype(np.float32) for v in vals], None, *geom,
+                                                     dtype=np.float32, amb_tol=amb_tol)
+    mask = (mask_f32["last_ids"] == f64["last_ids"]) & ~mask_f32["ambiguous"]
+    mk = mask[..., None].astype(np.float64)
+    v_c, v_a = np.asarray(cotangents[0], np.float64) * mk, np.asarray(cotangents[1], np.float64) * mk
+    v_s = np.asarray(cotangents[2], np.float64) * mk if (asum and cotangents[2] is not None) else None
+    g = composite.rasterize_to_points_bwd(*vals, None, *geom, f64["render_alphas"], f64["last_ids"], v_c, v_a, v_s)
+    grads_in = [g["v_means2d"], g["v_conics"], g["v_colors"], g["v_opacities"], g["v_pix_vels"], g["v_depth_comps"]]
+    torch.autograd.backward(stage, [torch.from_numpy(x) for x in grads_in])
+    return {k: L[k].grad for k in names}, mask, f64
+
+
+def camera_gradients_f64(cfg, offsets, flatten_ids, cotangents, names, camera_ids=None, gaussian_ids=None,
+                         mask_f32=None, amb_tol=1e-4):
+    """Camera counterpart of :func:`lidar_gradients_f64`: gradients of ``sum(image * cot[0] * mask)
+    + sum(alphas * cot[1] * mask)`` through the oracle's camera projection, SH colours
+    (``sh_degree``) or plain colours, the render-mode channel rules, and the analytic compositing
+    backward. ``flatten_ids`` index the [C, N] layout, or packed rows when ``camera_ids`` /
+    ``gaussian_ids`` are given."""
+    C, N = cfg["viewmats"].shape[0], cfg["means"].shape[0]
+    L = {k: _leaf64(cfg[k]) for k in names}
+    get = lambda k: L[k] if k in L else (None if cfg.get(k) is None else torch.as_tensor(cfg[k]).double())  # noqa: E731
+    zeros = lambda *s: torch.zeros(*s, dtype=torch.float64)  # noqa: E731
+    lin = get("linear_velocity") if cfg.get("linear_velocity") is not None else zeros(C, 3)
+    ang = get("angular_velocity") if cfg.get("angular_velocity") is not None else zeros(C, 3)
+    rs = get("rolling_shutter_time") if cfg.get("rolling_shutter_time") is not None else zeros(C)
+    mode = cfg.get("render_mode", "RGB")
+    assert mode in ("RGB", "RGB+D", "D"), mode
+    aa = cfg.get("rasterize_mode", "classic") == "antialiased"
+    radii, means2d, depths, conics, comps, pix_vels = projection.fully_fused_projection(
+        get("means"), None, get("quats"), get("scales"), get("velocities"), get("viewmats"), get("Ks"),
+        cfg["width"], cfg["height"], lin, ang, rs, cfg.get("eps2d", 0.3), cfg.get("near_plane", 0.01),
+        cfg.get("far_plane", 1e10), cfg.get("radius_clip", 0.0), aa)
+    opac = get("opacities")[None].repeat(C, 1)
+    if comps is not None:
+        opac = opac * comps
+    col = get("colors")
+    if cfg.get("sh_degree") is not None:
+        dirs = get("means")[None] - torch.inverse(get("viewmats"))[:, None, :3, 3]
+        shs = col[None].expand(C, -1, -1, -1) if col.dim() == 3 else col
+        col = torch.clamp_min(projection.spherical_harmonics(cfg["sh_degree"], dirs, shs, masks=radii[..., 0] > 0)
+                              + 0.5, 0.0)
+    elif col.dim() == 2:
+        col = col[None].expand(C, -1, -1)
+    if mode == "RGB+D":
+        col = torch.cat([col, depths[..., None]], dim=-1)
+    elif mode == "D":
+        col = depths[..., None]
+    col = col.contiguous()
+    flat = np.asarray(flatten_ids).astype(np.int64)
+    if camera_ids is not None:
+        flat = np.asarray(camera_ids).astype(np.int64)[flat] * N + np.asarray(gaussian_ids).astype(np.int64)[flat]
+    stage = [means2d, conics, col, opac, pix_vels]
+    vals = [_np(x) for x in stage]
+    bg = None if cfg.get("backgrounds") is None else np.asarray(torch.as_tensor(cfg["backgrounds"]).double())
+    if bg is not None and mode == "RGB+D":
+        bg = np.concatenate([bg, np.zeros((C, 1))], axis=-1)
+    geom = (cfg["width"], cfg["height"], cfg.get("tile_size", 16), np.asarray(offsets), flat.astype(np.int32))
+    rs_np = _np(rs)
+    f64 = composite.rasterize_to_pixels_fwd(*vals, rs_np, bg, *geom, dtype=np.float64)
+    if mask_f32 is None:
+        mask_f32 = composite.rasterize_to_pixels_fwd(*[v.astype(np.float32) for v in vals], rs_np, bg, *geom,
+                                                     dtype=np.float32, amb_tol=amb_tol)
+    mask = (mask_f32["last_ids"] == f64["last_ids"]) & ~mask_f32["ambiguous"]
+    mk = mask[..., None].astype(np.float64)
+    v_c, v_a = np.asarray(cotangents[0], np.float64) * mk, np.asarray(cotangents[1], np.float64) * mk
+    g = composite.rasterize_to_pixels_bwd(*vals, rs_np, bg, *geom, f64["render_alphas"], f64["last_ids"], v_c, v_a)
+    grads_in = [g["v_means2d"], g["v_conics"], g["v_colors"], g["v_opacities"], g["v_pix_vels"]]
+    torch.autograd.backward(stage, [torch.from_numpy(x) for x in grads_in])
+    return {k: L[k].grad for k in names}, mask, f64

@@ -210,9 +210,10 @@ def test_camera_render_modes_and_backgrounds(mode):
 
 
 def test_lidar_training_step_gradients_flow():
-    """Forward + backward through the whole lidar path: gradients reach every Gaussian parameter
-    and match a float64 finite-difference probe of the product's own forward along a random
-    direction (self-consistency of the full chain through projection and compositing)."""
+    """Forward + backward through the whole lidar path: gradients reach every Gaussian parameter,
+    ``meta["means2d"]`` receives its gradient and, with ``absgrad``, the sum of absolute
+    contributions, which bounds it. The values of the gradients are compared with an independent
+    float64 chain in ``test_gpu_gradients.py``."""
     import splatad_b200
     from splatad_b200 import scenes
     cfg = _to_gpu(scenes.config0(N=3000))
@@ -334,8 +335,9 @@ def test_repeated_packed_camera_frames_do_not_wait_for_the_row_count():
 
 
 def test_config2_full_size_properties():
-    """The headline frame (1 M Gaussians, 15.3 M intersections) is too large for the CPU oracle, so it
-    is checked through properties that do not depend on size - and by building its tile lists twice,
+    """The headline frame (1 M Gaussians, 15.3 M intersections) through properties that do not depend
+    on size (the comparison with the CPU oracle at this size is ``test_gpu_full_size.py``) - and by
+    building its tile lists twice,
     with the two independent implementations the library has (row / column split for small tile
     grids, radix split otherwise), which must agree bit for bit."""
     import splatad_b200

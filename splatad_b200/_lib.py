@@ -116,6 +116,16 @@ def check(status: int) -> None:
     raise RuntimeError(msg)
 
 
+class DevPtr(int):
+    """A device address (or stream handle) that remembers which GPU it belongs to, so that
+    :func:`call` can make that GPU current for the launch and refuse arguments from two GPUs."""
+
+    def __new__(cls, value: int, device_index: int):
+        obj = int.__new__(cls, value)
+        obj.device_index = device_index
+        return obj
+
+
 def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     """Device pointer of a contiguous CUDA tensor (None stays NULL)."""
     if t is None:
@@ -124,22 +134,51 @@ def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
         raise RuntimeError("splatad_b200 ops need CUDA tensors (there is no CPU fallback)")
     if not t.is_contiguous():
         raise RuntimeError("splatad_b200 ops need contiguous tensors")
-    return t.data_ptr()
+    return DevPtr(t.data_ptr(), t.device.index)
 
 
 def stream_ptr(device: torch.device) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    return DevPtr(torch.cuda.current_stream(device).cuda_stream, index)
+
+
+def call(name: str, *args) -> None:
+    """Calls entry point ``name`` with the GPU of its arguments current (the reference wraps every
+    binding in a device guard, gsplat/cuda/csrc/*.cu ``DEVICE_GUARD``): the launch, the stream handle
+    and the library's per-device state all refer to the device the tensors live on, whatever device
+    the calling thread has selected. Arguments from two different GPUs raise ``ValueError`` before
+    anything is launched."""
+    dev = None
+    for a in args:
+        idx = getattr(a, "device_index", None)
+        if idx is None:
+            continue
+        if dev is None:
+            dev = idx
+        elif idx != dev:
+            raise ValueError(f"{name}: arguments live on cuda:{dev} and cuda:{idx}; every tensor of a call "
+                             "must be on the same device")
+    fn = getattr(load(), name)
+    if dev is None or dev == torch.cuda.current_device():
+        check(fn(*args))
+    else:
+        with torch.cuda.device(dev):
+            check(fn(*args))
 
 
 # ---------------------------------------------------------------------------------------------
 # Grow-only per-device workspaces and pinned host slots (the library itself never allocates).
 # ---------------------------------------------------------------------------------------------
-_workspaces: Dict[Tuple[str, int], torch.Tensor] = {}
+_workspaces: Dict[Tuple[str, int, int], torch.Tensor] = {}
 _pinned: Dict[Tuple[str, int], torch.Tensor] = {}
+_free_slots: List[torch.Tensor] = []
 
 
 def workspace(tag: str, nbytes: int, device: torch.device) -> torch.Tensor:
-    key = (tag, device.index if device.index is not None else torch.cuda.current_device())
+    """Scratch buffer for (tag, device, current stream of that device). Work enqueued on one stream
+    is ordered, so consecutive calls may share a buffer; two streams never do."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    key = (tag, index, torch.cuda.current_stream(device).cuda_stream)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         # grow with headroom so slowly growing scenes do not reallocate every frame
@@ -150,6 +189,7 @@ def workspace(tag: str, nbytes: int, device: torch.device) -> torch.Tensor:
 
 
 def pinned_counts(tag: str, device: torch.device, n: int = 4) -> torch.Tensor:
+    """One pinned host slot per (tag, device) for calls that read their count before returning."""
     key = (tag, device.index if device.index is not None else torch.cuda.current_device())
     buf = _pinned.get(key)
     if buf is None or buf.numel() < n:
@@ -158,6 +198,20 @@ def pinned_counts(tag: str, device: torch.device, n: int = 4) -> torch.Tensor:
     return buf
 
 
+def acquire_pinned_slot() -> torch.Tensor:
+    """A pinned 4 x int64 host slot owned by one outstanding call (its count arrives there
+    asynchronously); give it back with :func:`release_pinned_slot` once it has been read."""
+    if _free_slots:
+        return _free_slots.pop()
+    return torch.zeros(4, dtype=torch.int64).pin_memory()
+
+
+def release_pinned_slot(slot: torch.Tensor) -> None:
+    if len(_free_slots) < 64:
+        _free_slots.append(slot)
+
+
 def release_workspaces() -> None:
     _workspaces.clear()
     _pinned.clear()
+    _free_slots.clear()

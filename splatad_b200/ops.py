@@ -32,7 +32,10 @@ from torch import Tensor
 from . import _lib
 
 _RETURN_VELOCITY_GRADS = False
-_packed_nnz_hint = {}   # (C, N, device) -> packed row count of the last frame of that shape
+# (C, N, device, stream) -> packed row count of the last frame of that shape rendered on that stream.
+# A hint only sizes the room a frame is given (too small -> the frame is redone), and a stream's
+# frames are issued by one thread at a time, so streams never share or fight over an entry.
+_packed_nnz_hint = {}
 
 
 @contextlib.contextmanager
@@ -60,8 +63,7 @@ def _f(t: Optional[Tensor]) -> Optional[Tensor]:
     return t.contiguous()
 
 
-def _call(name: str, *args) -> None:
-    _lib.check(getattr(_lib.load(), name)(*args))
+_call = _lib.call   # device-guarded: see _lib.call
 
 
 # =============================================================================================
@@ -581,7 +583,7 @@ class _FullyFusedProjectionPacked(torch.autograd.Function):
             # From the second frame of a shape on, the rows are written while the host still waits
             # for the count: into buffers with the previous count + 12.5 % of room, cut to length
             # afterwards (views). A frame that outgrows its room is filled again at the exact size.
-            key = (C, N, dev.index)
+            key = (C, N, dev.index, int(_lib.stream_ptr(dev)))
             hint = _packed_nnz_hint.get(key)
             capacity = None
             if hint:
@@ -930,16 +932,18 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
         return DeferredIsect.done(*out, C, n_tiles_total) if deferred else out
     plan_bytes = lib.splatad_isect_plan_workspace_bytes(total)
     plan_ws = _lib.workspace("isect_plan", plan_bytes, dev)
+    # where the plan's count arrives: the two-step protocol reads it before returning and can share
+    # one slot per device; a deferred call reads it later and owns its slot until then
     host = _lib.pinned_counts("isect", dev)
     stream = _lib.stream_ptr(dev)
     head = (C, N, total, _lib.ptr(means2d), _lib.ptr(radii), _lib.ptr(depths), _lib.ptr(camera_ids))
     # packed inputs: the row count changes from frame to frame, the hint only sizes the room
-    key = (kind, C, N, None if packed else total, n_tiles_total, dev.index)
+    key = (kind, C, N, None if packed else total, n_tiles_total, dev.index, int(stream))
     hint = _isect_count_hint.get(key) if (deferred and sort) else None
 
-    def plan():
+    def plan(slot=None):
         _call(f"splatad_isect_{kind}_plan", *head, *geom_args, int(bool(sort)), _lib.ptr(tiles_per_gauss),
-              _lib.ptr(plan_ws), plan_ws.numel(), host.data_ptr(), stream)
+              _lib.ptr(plan_ws), plan_ws.numel(), (host if slot is None else slot).data_ptr(), stream)
 
     def fill(capacity):
         isect_ids = torch.empty(capacity, dtype=torch.int64, device=dev)
@@ -959,8 +963,11 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
                   _lib.ptr(flatten_ids), _lib.ptr(offsets), None, stream)
         return isect_ids, flatten_ids, offsets
 
-    def read_count():
-        n_isects, status = int(host[0]), int(host[2])
+    def read_count(slot=None):
+        src = host if slot is None else slot
+        n_isects, status = int(src[0]), int(src[2])
+        if slot is not None:
+            _lib.release_pinned_slot(slot)
         if status & 2 or n_isects > 0x7FFFFFFF:
             raise RuntimeError(f"isect: {n_isects} intersections do not fit int32 flatten ids / offsets")
         _isect_count_hint[key] = n_isects
@@ -982,14 +989,17 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
     # Enqueue plan and fill back to back with room for somewhat more intersections than last time;
     # the count is read when the caller asks for the exact tensors.
     capacity = hint + hint // 8 + 65536
-    plan()
+    slot = _lib.acquire_pinned_slot()
+    plan(slot)
     counted = torch.cuda.Event()
     counted.record(torch.cuda.current_stream(dev))
     isect_buf, flat_buf, offsets = fill(capacity)
     return DeferredIsect(tiles_per_gauss, isect_buf, flat_buf, offsets, C, n_tiles_total, capacity,
-                         counted, read_count, exact)
+                         counted, lambda: read_count(slot), exact)
 
 
+# (kind, shape, tile grid, device, stream) -> intersection count of the last frame of that shape on
+# that stream (see _packed_nnz_hint for why the stream is part of the key)
 _isect_count_hint: dict = {}
 
 
@@ -1027,9 +1037,13 @@ class DeferredIsect:
             if resolved is None:
                 raise RuntimeError("isect: count outgrew its room and the tile grid does not match")
             return isect_offset_encode(resolved[0], self._C, tile_width, tile_height)
-        view = self._offsets[: self._n_tiles_total].view(self._C, tile_height, tile_width)
-        view._splatad_total_follows = True   # the compositing ops may read the total behind it
-        return view
+        return self._offsets[: self._n_tiles_total].view(self._C, tile_height, tile_width)
+
+    def total_follows(self, tile_height: int, tile_width: int) -> bool:
+        """Whether :meth:`offsets` for this grid is a view of a buffer that holds the intersection
+        count right behind the last tile start (pass it on as ``total_follows`` to the compositing
+        ops, which then take the end of the last tile from there instead of ``len(flatten_ids)``)."""
+        return self._offsets is not None and self._C * tile_height * tile_width == self._n_tiles_total
 
     def resolve(self):
         if self._resolved is None:
@@ -1047,10 +1061,16 @@ class DeferredIsect:
         return DeferredIsect.done(tiles_per_gauss, isect_ids, flatten_ids, self._C, self._n_tiles_total)
 
 
-def _n_isects_arg(isect_offsets: Tensor, flatten_ids: Tensor) -> int:
+def _n_isects_arg(isect_offsets: Tensor, flatten_ids: Tensor, total_follows: bool = False) -> int:
     """What the compositing entry points get as n_isects: the length of flatten_ids, or -1 when the
-    total sits behind the tile starts on the device (see DeferredIsect)."""
-    return -1 if getattr(isect_offsets, "_splatad_total_follows", False) else flatten_ids.numel()
+    caller states that the total sits behind the tile starts on the device (see DeferredIsect)."""
+    if not total_follows:
+        return flatten_ids.numel()
+    room = isect_offsets.untyped_storage().nbytes() // isect_offsets.element_size()
+    if not (isect_offsets.is_contiguous() and isect_offsets.dtype == torch.int32
+            and room >= isect_offsets.storage_offset() + isect_offsets.numel() + 1):
+        raise ValueError("total_follows: isect_offsets is not a contiguous int32 view with one more entry behind it")
+    return -1
 
 
 @torch.no_grad()
@@ -1244,8 +1264,14 @@ def rasterize_to_pixels(
     backgrounds: Optional[Tensor] = None,  # [C, channels]
     packed: bool = False,
     absgrad: bool = False,
+    total_follows: bool = False,
 ) -> Tuple[Tensor, Tensor]:
-    """Rasterizes Gaussians to pixels. Returns (colors [C,H,W,channels], alphas [C,H,W,1])."""
+    """Rasterizes Gaussians to pixels. Returns (colors [C,H,W,channels], alphas [C,H,W,1]).
+
+    ``total_follows`` (not in the reference): ``isect_offsets`` is a view of a buffer that holds the
+    number of intersections right behind the last tile start (:meth:`DeferredIsect.offsets`) and
+    ``flatten_ids`` may be longer than that number; the kernels then read the end of the last tile
+    from the device instead of taking ``len(flatten_ids)``."""
     C = isect_offsets.size(0)
     device = means2d.device
     if packed:
@@ -1280,7 +1306,7 @@ def rasterize_to_pixels(
     args = (conics.contiguous(), opacities.contiguous(), pix_vels.contiguous(),
             rolling_shutter_time.contiguous())
     tail = (image_width, image_height, tile_size, isect_offsets.contiguous(), flatten_ids.contiguous(),
-            absgrad)
+            absgrad, total_follows)
     if channels <= _lib.MAX_CHANNELS:
         return _RasterizeToPixels.apply(means2d_c, args[0], colors.contiguous(), args[1], args[2],
                                         args[3], backgrounds, *tail)
@@ -1299,7 +1325,7 @@ def rasterize_to_pixels(
 class _RasterizeToPixels(torch.autograd.Function):
     @staticmethod
     def forward(ctx, means2d, conics, colors, opacities, pix_vels, rolling_shutter_time, backgrounds,
-                width, height, tile_size, isect_offsets, flatten_ids, absgrad):
+                width, height, tile_size, isect_offsets, flatten_ids, absgrad, total_follows=False):
         dev = means2d.device
         assert means2d.dtype == torch.float32, means2d.dtype
         C, tile_h, tile_w = isect_offsets.shape
@@ -1310,7 +1336,7 @@ class _RasterizeToPixels(torch.autograd.Function):
         render_colors = torch.empty((C, height, width, channels), dtype=torch.float32, device=dev)
         render_alphas = torch.empty((C, height, width, 1), dtype=torch.float32, device=dev)
         last_ids = torch.empty((C, height, width), dtype=torch.int32, device=dev)
-        n_isects = _n_isects_arg(isect_offsets, flatten_ids)
+        n_isects = _n_isects_arg(isect_offsets, flatten_ids, total_follows)
         ctx.n_isects_arg = n_isects
         _call(
             "splatad_rasterize_to_pixels_fwd", C, n_isects, _lib.ptr(means2d), _lib.ptr(conics_f),
@@ -1353,7 +1379,7 @@ class _RasterizeToPixels(torch.autograd.Function):
         if ctx.needs_input_grad[6]:
             v_backgrounds = (v_render_colors * (1.0 - render_alphas).float()).sum(dim=(1, 2))
         return (v_means2d, v_conics, v_colors, v_opacities, v_pix_vels, None, v_backgrounds, None,
-                None, None, None, None, None)
+                None, None, None, None, None, None)
 
 
 def rasterize_to_points(
@@ -1375,6 +1401,7 @@ def rasterize_to_points(
     backgrounds: Optional[Tensor] = None,  # [C, channels]
     packed: bool = False,
     absgrad: bool = False,
+    total_follows: bool = False,  # see rasterize_to_pixels
 ) -> Tuple[Tensor, Tensor, Optional[Tensor], Tensor]:
     """Rasterizes Gaussians to lidar points; the last feature channel is the Gaussian's range.
 
@@ -1419,7 +1446,7 @@ def rasterize_to_points(
             compute_alpha_sum_until_points_threshold, absgrad)
     if channels <= _lib.MAX_CHANNELS:
         return _RasterizeToPoints.apply(*fixed, lidar_features.contiguous(), None, *mid, backgrounds, *tail,
-                                        depth_channel_idx)
+                                        depth_channel_idx, total_follows)
     # more channels than one launch renders: every chunk carries the range as its last channel
     step = _lib.MAX_CHANNELS - 1
     n_feat = channels - 1
@@ -1431,7 +1458,8 @@ def rasterize_to_points(
         bg = None
         if backgrounds is not None:
             bg = torch.cat([backgrounds[..., lo:hi], backgrounds[..., -1:]], dim=-1).contiguous()
-        r, a, s, m = _RasterizeToPoints.apply(*fixed, feats, None, *mid, bg, *tail, feats.shape[-1] - 1)
+        r, a, s, m = _RasterizeToPoints.apply(*fixed, feats, None, *mid, bg, *tail, feats.shape[-1] - 1,
+                                              total_follows)
         if first is None:
             first = (a, s, m)
         outs.append(r if hi == n_feat else r[..., :-1])
@@ -1443,7 +1471,7 @@ def rasterize_to_points_split(
     pix_vels: Tensor, depth_compensations: Tensor, raster_pts: Tensor, image_width: int, image_height: int,
     tile_width: int, tile_height: int, isect_offsets: Tensor, flatten_ids: Tensor,
     compute_alpha_sum_until_points: bool, compute_alpha_sum_until_points_threshold: float,
-    absgrad: bool = False,
+    absgrad: bool = False, total_follows: bool = False,
 ) -> Tuple[Tensor, Tensor, Optional[Tensor], Tensor]:
     """:func:`rasterize_to_points` with the Gaussians' ranges given as their own [C,N] tensor instead
     of being concatenated to the features as last channel (what ``lidar_rasterization`` of the
@@ -1456,7 +1484,7 @@ def rasterize_to_points_split(
         opacities.contiguous(), pix_vels.contiguous(), depth_compensations.contiguous(), None,
         raster_pts.contiguous(), image_width, image_height, tile_width, tile_height,
         isect_offsets.contiguous(), flatten_ids.contiguous(), compute_alpha_sum_until_points,
-        compute_alpha_sum_until_points_threshold, absgrad, lidar_features.shape[-1])
+        compute_alpha_sum_until_points_threshold, absgrad, lidar_features.shape[-1], total_follows)
 
 
 class _RasterizeToPoints(torch.autograd.Function):
@@ -1464,7 +1492,7 @@ class _RasterizeToPoints(torch.autograd.Function):
     def forward(ctx, means2d, conics, colors, ranges, opacities, pix_vels, depth_compensations, backgrounds,
                 raster_pts, width, height, tile_width, tile_height, isect_offsets, flatten_ids,
                 compute_alpha_sum_until_points, compute_alpha_sum_until_points_threshold, absgrad,
-                depth_channel_idx):
+                depth_channel_idx, total_follows=False):
         # ``ranges`` (optional, [C,N] / [nnz]): the Gaussians' ranges as a separate array; the rendered
         # channel count is then colors.shape[-1] + 1 with the range as last channel.
         dev = means2d.device
@@ -1480,7 +1508,7 @@ class _RasterizeToPoints(torch.autograd.Function):
         median_depths = torch.empty((C, height, width, 1), **f32)
         alpha_sum = torch.empty((C, height, width, 1), **f32) if compute_alpha_sum_until_points else None
         last_ids = torch.empty((C, height, width), dtype=torch.int32, device=dev)
-        ctx.n_isects_arg = _n_isects_arg(isect_offsets, flatten_ids)
+        ctx.n_isects_arg = _n_isects_arg(isect_offsets, flatten_ids, total_follows)
         _call(
             "splatad_rasterize_to_points_fwd", C, ctx.n_isects_arg, _lib.ptr(means2d),
             _lib.ptr(conics_f), _lib.ptr(colors_f) if colors_f.numel() else None, _lib.ptr(ranges_f), channels,
@@ -1536,7 +1564,7 @@ class _RasterizeToPoints(torch.autograd.Function):
         if ctx.needs_input_grad[7]:
             v_backgrounds = (v_render_colors * (1.0 - render_alphas).float()).sum(dim=(1, 2))
         return (v_means2d, v_conics, v_colors, v_ranges, v_opacities, v_pix_vels, v_depth_comps,
-                v_backgrounds) + (None,) * 11
+                v_backgrounds) + (None,) * 12
 
 
 # =============================================================================================

@@ -59,14 +59,14 @@ def _sensor_motion(C: int, device, linear_velocity: Optional[Tensor], angular_ve
 
 
 def _composite_with_count_check(isect, grid: Tuple[int, int], composite):
-    """Runs ``composite(isect_offsets, flatten_ids)`` on a deferred tile intersection and returns
+    """Runs ``composite(isect_offsets, flatten_ids, total_follows)`` on a deferred tile intersection and returns
     (outputs, isect_ids, flatten_ids, isect_offsets): if the intersection count turns out to exceed
     the room it was given, intersection and compositing are repeated the two-step way."""
-    outputs = composite(isect.offsets(*grid), isect.flatten_ids)
+    outputs = composite(isect.offsets(*grid), isect.flatten_ids, isect.total_follows(*grid))
     resolved = isect.resolve()
     if resolved is None:
         isect = isect.redo()
-        outputs = composite(isect.offsets(*grid), isect.flatten_ids)
+        outputs = composite(isect.offsets(*grid), isect.flatten_ids, isect.total_follows(*grid))
         resolved = isect.resolve()
     return outputs, resolved[0], resolved[1], isect.offsets(*grid), isect.tiles_per_gauss
 
@@ -201,7 +201,7 @@ def _rasterization(means, quats, scales, opacities, colors, velocities, viewmats
         opacities, colors = opacities[:nnz], colors[:nnz]
         tiles_per_gauss_cut = nnz
 
-    def composite(isect_offsets, flatten_ids):
+    def composite(isect_offsets, flatten_ids, total_follows):
         if colors.shape[-1] > channel_chunk:
             n_chunks = (colors.shape[-1] + channel_chunk - 1) // channel_chunk
             chunk_colors, chunk_alphas = [], []
@@ -215,7 +215,7 @@ def _rasterization(means, quats, scales, opacities, colors, velocities, viewmats
                 render_colors_, render_alphas_ = rasterize_to_pixels(
                     means2d, conics, colors_chunk, opacities, pix_vels, width, height, tile_size,
                     isect_offsets, flatten_ids, rolling_shutter_time, backgrounds=backgrounds_chunk,
-                    packed=packed, absgrad=absgrad,
+                    packed=packed, absgrad=absgrad, total_follows=total_follows,
                 )
                 chunk_colors.append(render_colors_)
                 chunk_alphas.append(render_alphas_)
@@ -223,6 +223,7 @@ def _rasterization(means, quats, scales, opacities, colors, velocities, viewmats
         return rasterize_to_pixels(
             means2d, conics, colors, opacities, pix_vels, width, height, tile_size, isect_offsets,
             flatten_ids, rolling_shutter_time, backgrounds=backgrounds, packed=packed, absgrad=absgrad,
+            total_follows=total_follows,
         )
 
     (render_colors, render_alphas), isect_ids, flatten_ids, isect_offsets, tiles_per_gauss = (
@@ -327,11 +328,12 @@ def lidar_rasterization(
     image_width = raster_pts.shape[-2]
     image_height = raster_pts.shape[-3]
 
-    def composite(isect_offsets, flatten_ids):
+    def composite(isect_offsets, flatten_ids, total_follows):
         common = dict(
             compute_alpha_sum_until_points=compute_alpha_sum_until_points,
             compute_alpha_sum_until_points_threshold=compute_alpha_sum_until_points_threshold,
             absgrad=absgrad,
+            total_follows=total_follows,
         )
         geometry = (raster_pts, image_width, image_height, tile_width, tile_height, isect_offsets, flatten_ids)
         if (lidar_features.shape[-1] + 1) <= channel_chunk:

@@ -147,7 +147,10 @@ int splatad_projection_packed_fill(
  * message, and touches nothing. The call makes no cudaMalloc / cudaFree and uses no allocating
  * library routine; inputs and outputs are still the caller's.
  * The first call on each device looks the array's device address up (cudaGetSymbolAddress, with
- * that device current); make that first call outside any stream capture.
+ * that device current). Under lazy module loading that lookup is also what makes the CUDA runtime
+ * load this library's code onto the device and back the array with memory, so "allocates nothing"
+ * holds from the second call on: make one call per device at start-up, while allocation is still
+ * permitted, and outside any stream capture.
  * All calls on a device share the one array: nothing in it has to be cleared between calls
  * (every slot a call reads it has written first), but two calls that overlap on the GPU - on
  * different streams, or from different threads - race on it and corrupt each other's counts.

@@ -804,8 +804,9 @@ extern "C" int splatad_lidar_projection_bwd(
     const float *v_conics, const float *v_compensations, const float *v_pix_vels,
     const float *v_depth_compensations, float *v_means, float *v_covars, float *v_quats,
     float *v_scales, float *v_viewmats, float *v_velocities, void *stream) {
-    SPL_REQUIRE(means && viewmats && radii && conics && v_means2d && v_depths && v_conics &&
-                    v_pix_vels && v_depth_compensations,
+    SPL_REQUIRE(means && viewmats && linear_velocity && angular_velocity && rolling_shutter_time &&
+                    radii && conics && v_means2d && v_depths && v_conics && v_pix_vels &&
+                    v_depth_compensations,
                 SPLATAD_ERR_BAD_ARG, "lidar_projection_bwd: null input");
     SPL_REQUIRE(covars || (quats && scales), SPLATAD_ERR_BAD_ARG,
                 "lidar_projection_bwd: covars or (quats, scales) required");
@@ -857,7 +858,8 @@ extern "C" int splatad_projection_bwd(
     const float *v_means2d, const float *v_depths, const float *v_conics,
     const float *v_compensations, const float *v_pix_vels, float *v_means, float *v_covars,
     float *v_quats, float *v_scales, float *v_viewmats, float *v_velocities, void *stream) {
-    SPL_REQUIRE(means && viewmats && Ks && radii && conics && v_means2d && v_depths && v_conics &&
+    SPL_REQUIRE(means && viewmats && Ks && linear_velocity && angular_velocity &&
+                    rolling_shutter_time && radii && conics && v_means2d && v_depths && v_conics &&
                     v_pix_vels,
                 SPLATAD_ERR_BAD_ARG, "projection_bwd: null input");
     SPL_REQUIRE(covars || (quats && scales), SPLATAD_ERR_BAD_ARG,
@@ -888,8 +890,9 @@ extern "C" int splatad_projection_packed_count(
     const float *angular_velocity, const float *rolling_shutter_time, float eps2d,
     float near_plane, float far_plane, float radius_clip, void *workspace,
     size_t workspace_bytes, int32_t *indptr, int64_t *nnz_device, void *stream) {
-    SPL_REQUIRE(means && viewmats && Ks && indptr && nnz_device && workspace, SPLATAD_ERR_BAD_ARG,
-                "projection_packed_count: null argument");
+    SPL_REQUIRE(means && viewmats && Ks && linear_velocity && angular_velocity &&
+                    rolling_shutter_time && indptr && nnz_device && workspace,
+                SPLATAD_ERR_BAD_ARG, "projection_packed_count: null argument");
     SPL_REQUIRE(covars || (quats && scales), SPLATAD_ERR_BAD_ARG,
                 "projection_packed_count: covars or (quats, scales) required");
     SPL_REQUIRE(workspace_bytes >= splatad_projection_packed_workspace_bytes(C, N),
@@ -922,9 +925,12 @@ extern "C" int splatad_projection_packed_fill(
     float near_plane, float far_plane, float radius_clip, const void *workspace, int64_t capacity,
     int64_t *camera_ids, int64_t *gaussian_ids, int32_t *radii, float *means2d, float *depths,
     float *conics, float *compensations, float *pix_vels, void *stream) {
-    SPL_REQUIRE(means && viewmats && Ks && workspace && camera_ids && gaussian_ids && radii &&
+    SPL_REQUIRE(means && viewmats && Ks && linear_velocity && angular_velocity &&
+                    rolling_shutter_time && workspace && camera_ids && gaussian_ids && radii &&
                     means2d && depths && conics && pix_vels,
                 SPLATAD_ERR_BAD_ARG, "projection_packed_fill: null argument");
+    SPL_REQUIRE(covars || (quats && scales), SPLATAD_ERR_BAD_ARG,
+                "projection_packed_fill: covars or (quats, scales) required");
     SPL_REQUIRE(C > 0 && N > 0, SPLATAD_ERR_BAD_ARG, "projection_packed_fill: empty input");
     const uint32_t nblocks = div_up(N, kThreads);
     const int32_t *offsets = (const int32_t *)workspace + (size_t)C * nblocks;
@@ -949,7 +955,9 @@ extern "C" int splatad_projection_packed_bwd(
     const float *v_conics, const float *v_compensations, const float *v_pix_vels,
     int32_t sparse_grad, float *v_means, float *v_covars, float *v_quats, float *v_scales,
     float *v_viewmats, float *v_velocities, void *stream) {
-    SPL_REQUIRE(means && viewmats && Ks, SPLATAD_ERR_BAD_ARG, "projection_packed_bwd: null input");
+    SPL_REQUIRE(means && viewmats && Ks && linear_velocity && angular_velocity &&
+                    rolling_shutter_time,
+                SPLATAD_ERR_BAD_ARG, "projection_packed_bwd: null input");
     SPL_REQUIRE(covars || (quats && scales), SPLATAD_ERR_BAD_ARG,
                 "projection_packed_bwd: covars or (quats, scales) required");
     SPL_REQUIRE(!v_compensations || compensations, SPLATAD_ERR_BAD_ARG,

@@ -137,3 +137,53 @@ def test_isect_key_bits_error():
     with pytest.raises(RuntimeError):
         ops.isect_tiles(m, torch.ones(1, 10, 2, dtype=torch.int32, device=DEV), torch.rand(1, 10, device=DEV),
                         1, 1 << 16, 1 << 16)
+
+
+def test_two_deferred_intersections_outstanding():
+    """Two deferred tile intersections alive at once - a camera call and a lidar call of different
+    sizes, resolved in the opposite order: each reads ITS count (own pinned slot), so lengths, lists
+    and offsets equal those of the two-step calls. A second pair runs on another stream, which has
+    workspaces and capacity hints of its own."""
+    from splatad_b200 import ops, scenes
+    g = torch.Generator().manual_seed(5)
+    C, N, W, H, ts = 2, 30_000, 640, 480, 16
+    means2d = ((torch.rand(C, N, 2, generator=g) * 1.2 - 0.1) * torch.tensor([W, H])).to(DEV)
+    radii = torch.randint(1, 40, (C, N, 2), generator=g, dtype=torch.int32).to(DEV)
+    depths = (torch.rand(C, N, generator=g) * 50).to(DEV)
+    tw, th = math.ceil(W / ts), math.ceil(H / ts)
+    eb = scenes.elevation_boundaries(scenes.beams_128(), 8).to(DEV)
+    M = 50_000
+    l_means = torch.stack([torch.rand(1, M, generator=g) * 360 - 180, torch.rand(1, M, generator=g) * 44 - 27], -1).to(DEV)
+    l_radii = (torch.rand(1, M, 2, generator=g) * torch.tensor([12.0, 4.0])).to(DEV)
+    l_depths = (torch.rand(1, M, generator=g) * 80).to(DEV)
+    res, n_az = 0.2 * 32, math.ceil(360 / (0.2 * 32))
+
+    def cam():
+        return ops.isect_tiles_deferred(means2d, radii, depths, ts, tw, th)
+
+    def lid():
+        return ops.isect_lidar_tiles_deferred(l_means, l_radii, l_depths, eb, res, -180.0)
+
+    want_cam = ops.isect_tiles(means2d, radii, depths, ts, tw, th)
+    want_lid = ops.isect_lidar_tiles(l_means, l_radii, l_depths, eb, res, -180.0)
+    assert want_cam[1].numel() != want_lid[1].numel()
+
+    def check_pair():
+        cam().resolve(), lid().resolve()          # first frames of the two shapes: they leave the hints
+        d_cam, d_lid = cam(), lid()               # both enqueued ahead of their counts, both outstanding
+        assert d_cam._resolved is None and d_lid._resolved is None
+        offs_lid, offs_cam = d_lid.offsets(16, n_az).clone(), d_cam.offsets(th, tw).clone()
+        ids_l, flat_l = d_lid.resolve()           # opposite order
+        ids_c, flat_c = d_cam.resolve()
+        assert torch.equal(ids_c, want_cam[1]) and torch.equal(flat_c, want_cam[2])
+        assert torch.equal(ids_l, want_lid[1]) and torch.equal(flat_l, want_lid[2])
+        assert torch.equal(offs_cam, ops.isect_offset_encode(want_cam[1].clone(), C, tw, th))
+        assert torch.equal(offs_lid, ops.isect_offset_encode(want_lid[1].clone(), 1, n_az, 16))
+        assert torch.equal(d_cam.tiles_per_gauss, want_cam[0]) and torch.equal(d_lid.tiles_per_gauss, want_lid[0])
+
+    check_pair()
+    side = torch.cuda.Stream(DEV)
+    side.wait_stream(torch.cuda.current_stream(DEV))
+    with torch.cuda.stream(side):
+        check_pair()
+    side.synchronize()

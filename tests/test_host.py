@@ -38,6 +38,39 @@ def test_error_mapping():
     assert rc == _lib.ERR_CHANNELS
 
 
+def test_projection_entries_refuse_null_sensor_motion():
+    """Every projection entry point that reads the sensors' motion refuses NULL for it with
+    SPLATAD_ERR_BAD_ARG before anything is launched (a C caller may pass NULL for ``velocities``, not
+    for these)."""
+    from splatad_b200 import _lib
+    lib = _lib.load()
+    x = ctypes.c_void_p(256)   # never dereferenced: the argument check comes first
+    geom = (x, None, x, x, None, x, x, 640, 480)            # means, covars, quats, scales, velocities, viewmats, Ks, w, h
+    for missing in range(3):
+        motion = [x, x, x]
+        motion[missing] = None
+        tail = (*motion, 0.3, 0.01, 1e10, 0.0)
+        assert lib.splatad_projection_packed_count(1, 8, *geom, *tail, x, 1 << 20, x, x, None) == _lib.ERR_BAD_ARG
+        assert "projection_packed_count" in _lib.last_error()
+        assert lib.splatad_projection_packed_fill(1, 8, *geom, *tail, x, -1, x, x, x, x, x, x, None, x,
+                                                  None) == _lib.ERR_BAD_ARG
+        assert lib.splatad_projection_packed_bwd(1, 8, 4, *geom, *motion, 0.3, x, x, x, None, x, x, x, None, x, 0,
+                                                 x, None, x, x, None, None, None) == _lib.ERR_BAD_ARG
+        assert lib.splatad_projection_bwd(1, 8, *geom, *motion, 0.3, x, x, None, x, x, x, None, x, x, None, x, x,
+                                          None, None, None) == _lib.ERR_BAD_ARG
+        assert lib.splatad_lidar_projection_bwd(1, 8, x, None, x, x, None, x, *motion, 0.017, x, x, None, x, x, x,
+                                                None, x, x, x, None, x, x, None, None, None) == _lib.ERR_BAD_ARG
+
+
+def test_arguments_from_two_devices_are_refused_before_any_launch():
+    """The call wrapper makes the tensors' GPU current for the launch and raises when the arguments of
+    one call come from different GPUs (no GPU needed: the check is on the recorded device indices)."""
+    from splatad_b200 import _lib
+    a, b = _lib.DevPtr(256, 0), _lib.DevPtr(512, 1)
+    with pytest.raises(ValueError, match="cuda:0 and cuda:1"):
+        _lib.call("splatad_sh_fwd", 1, 1, 0, a, b, None, a, _lib.DevPtr(0, 0))
+
+
 def test_ops_refuse_cpu_tensors():
     import splatad_b200
     N = 8

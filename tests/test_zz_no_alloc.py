@@ -45,11 +45,29 @@ def _p(t):
     return ctypes.c_void_p(t.data_ptr())
 
 
-def _count_both(lib, N, C, seed):
+def _covars(quats, scales):
+    """Upper triangles [N, 6] of (R S)(R S)^T: the input the entry points take instead of quats / scales."""
+    q = torch.nn.functional.normalize(quats, dim=-1)
+    w, x, y, z = q.unbind(-1)
+    R = torch.stack([1 - 2 * (y * y + z * z), 2 * (x * y - w * z), 2 * (x * z + w * y),
+                     2 * (x * y + w * z), 1 - 2 * (x * x + z * z), 2 * (y * z - w * x),
+                     2 * (x * z - w * y), 2 * (y * z + w * x), 1 - 2 * (x * x + y * y)], -1).reshape(-1, 3, 3)
+    M = R * scales[:, None, :]
+    cov = M @ M.transpose(1, 2)
+    return torch.stack([cov[:, 0, 0], cov[:, 0, 1], cov[:, 0, 2], cov[:, 1, 1], cov[:, 1, 2], cov[:, 2, 2]],
+                       -1).contiguous()
+
+
+def _count_both(lib, N, C, seed, use_covars=False):
     from splatad_b200 import _lib
     means, quats, scales, vel, viewmats, Ks, lin, ang, rs = _scene(N, C, seed)
     stream = torch.cuda.current_stream().cuda_stream
-    head = (C, N, _p(means), None, _p(quats), _p(scales), _p(vel), _p(viewmats), _p(Ks), 640, 480, _p(lin),
+    if use_covars:
+        covars = _covars(quats, scales)
+        shape = (_p(covars), None, None)
+    else:
+        shape = (None, _p(quats), _p(scales))
+    head = (C, N, _p(means), *shape, _p(vel), _p(viewmats), _p(Ks), 640, 480, _p(lin),
             _p(ang), _p(rs), 0.3, 0.01, 1e10, 0.0)
     # regular entry point: the caller brings the workspace
     ws = torch.empty(lib.splatad_projection_packed_workspace_bytes(C, N), dtype=torch.uint8, device=DEV)
@@ -76,6 +94,33 @@ def test_noalloc_count_matches_workspace_count_twice_in_a_row():
     assert ref_nnz2 > 100 and ref_nnz2 != ref_nnz
     assert nnz2 == ref_nnz2 and torch.equal(ptr2, ref_ptr2)
     assert int(ptr2[0]) == 0 and int(ptr2[-1]) == nnz2
+
+
+def test_noalloc_count_takes_covariances_and_leaves_device_memory_alone():
+    """The covariance input path (no quaternions / scales), and the claim in the name: once the
+    first call on the device has happened, a call changes neither the free device memory the driver
+    reports nor what torch's allocator holds. Inputs and outputs are made before the measurement."""
+    from splatad_b200 import _lib
+    lib = _lib.load()
+    ref_ptr, ref_nnz, ptr, nnz = _count_both(lib, 9_000, 2, seed=13, use_covars=True)   # also the warm-up call
+    assert ref_nnz > 100 and nnz == ref_nnz and torch.equal(ptr, ref_ptr)
+    C, N = 2, 9_000
+    means, quats, scales, vel, viewmats, Ks, lin, ang, rs = _scene(N, C, 14)
+    covars = _covars(quats, scales)
+    indptr = torch.zeros(C + 1, dtype=torch.int32, device=DEV)
+    count = torch.zeros(1, dtype=torch.int64, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    held_before, reserved_before = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    _lib.check(lib.splatad_projection_packed_count_noalloc(
+        C, N, _p(means), _p(covars), None, None, _p(vel), _p(viewmats), _p(Ks), 640, 480, _p(lin), _p(ang), _p(rs),
+        0.3, 0.01, 1e10, 0.0, _p(indptr), _p(count), stream))
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
+    assert torch.cuda.memory_allocated() == held_before and torch.cuda.memory_reserved() == reserved_before
+    assert int(count) > 100 and int(indptr[-1]) == int(count)
 
 
 def test_noalloc_count_rejects_sizes_beyond_its_array():

@@ -511,6 +511,55 @@ int splatad_compute_relocation(uint32_t N, const float *opacities, const float *
                                const int32_t *ratios, const float *binoms, int32_t n_max,
                                float *new_opacities, float *new_scales, void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Gaussian-sharded exchange (one process per GPU): every rank projects its slice of the Gaussians
+ * for all sensors and sends the visible (sensor, Gaussian) records to the rank owning the sensor.
+ * The reference leaves this to torch code around its collectives (gsplat/distributed.py:170-257:
+ * all_to_all_int32 size exchange + all_to_all_tensor_list row exchange); these entry points build
+ * the fixed-width send rows on the device and place received rows in single-GPU order. The
+ * transport itself (one all-to-all of [rows, width] 32-bit words) stays with the caller.
+ * ---------------------------------------------------------------------------------------- */
+
+/* Which pairs of a [C, N] projection travel: those with radii[c, n, 0] > 0 (radii [C,N,2], float
+ * degrees or int32 pixels - the sign test is the same on either bit pattern). _count writes
+ * indptr [C+1] (first row of every sensor, total last) and *total_device (may be NULL); _fill
+ * writes row_index[k] = c * N + n of the k-th pair in (sensor, Gaussian) order, dropping rows at
+ * or beyond `capacity`. workspace: splatad_visible_rows_workspace_bytes(C, N) bytes, shared by
+ * the two calls. C * N must fit int32. */
+size_t splatad_visible_rows_workspace_bytes(uint32_t C, uint32_t N);
+int splatad_visible_rows_count(uint32_t C, uint32_t N, const void *radii, void *workspace,
+                               size_t workspace_bytes, int32_t *indptr, int64_t *total_device,
+                               void *stream);
+int splatad_visible_rows_fill(uint32_t C, uint32_t N, const void *radii, const void *workspace,
+                              int64_t capacity, int32_t *row_index, void *stream);
+
+/* out[i, :] = concatenation over the fields k of field_ptrs[k][index[i], 0:field_widths[k]]
+ * (index NULL: row i). Fields are arrays of 32-bit words (float or int32), at most 12; a NULL
+ * field pointer yields zeros. With sensor_table (int32 [C]) two id columns lead every row: the
+ * global sensor id sensor_table[index[i] / n_per_sensor] and the global Gaussian id
+ * gaussian_start + index[i] % n_per_sensor, as int32 bit patterns. field_ptrs / field_widths are
+ * HOST arrays read during the call. */
+int splatad_rows_gather(int64_t n_rows, const int32_t *index, int32_t n_fields,
+                        const void *const *field_ptrs, const int32_t *field_widths,
+                        const int32_t *sensor_table, uint32_t n_per_sensor, int32_t gaussian_start,
+                        void *out, void *stream);
+
+/* The inverse placement: field_ptrs[k][index[i], :] = columns of field k of in[i, :] (index NULL:
+ * row i; index must not repeat a row). id_cols = 2 widens the two leading id columns to int64
+ * into sensor_ids_out / gaussian_ids_out (either may be NULL), id_cols = 0 means rows without
+ * them. A NULL field pointer skips that field. */
+int splatad_rows_scatter(int64_t n_rows, const int32_t *index, int32_t n_fields,
+                         void *const *field_ptrs, const int32_t *field_widths, int32_t id_cols,
+                         int64_t *sensor_ids_out, int64_t *gaussian_ids_out, const void *in,
+                         void *stream);
+
+/* Received rows arrive as n_segments contiguous segments, one per (source rank, sensor);
+ * segment s begins at row src_start[s] of the receive buffer (ascending, device int64) and at
+ * row dst_start[s] of the final (sensor, source rank) order. row_map[i] = final row of received
+ * row i, for splatad_rows_scatter. */
+int splatad_segment_row_map(int32_t n_segments, const int64_t *src_start, const int64_t *dst_start,
+                            int64_t n_rows, int32_t *row_map, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

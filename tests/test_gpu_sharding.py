@@ -59,6 +59,11 @@ def test_exchange_kernels_with_two_emulated_ranks():
     cameras it owns (ids, order, values bit for bit), and gradients sent back through the row
     buffers equal those of the single-GPU packed projection."""
     from splatad_b200 import ops, sharding
+    with ops.velocity_grads(True):      # the projection decides in its forward pass whether to return them
+        _emulated_ranks(ops, sharding)
+
+
+def _emulated_ranks(ops, sharding):
     cfg = _to(_camera_scene(), DEV)
     N, C, world = cfg["means"].shape[0], 3, 2
     owners = [0, 1, 0]
@@ -110,9 +115,8 @@ def test_exchange_kernels_with_two_emulated_ranks():
             w = torch.randn(a.shape, generator=gen).to(DEV)
             loss_sharded = loss_sharded + (a * w).sum()
             loss_single = loss_single + (b * w).sum()
-    with ops.velocity_grads(True):
-        loss_sharded.backward()
-        loss_single.backward()
+    loss_sharded.backward()
+    loss_single.backward()
     for k in LEAVES[:3] + ("velocities",):
         got = torch.cat([L[k].grad for L in leaves])
         assert rel_l2(n(got), n(F[k].grad)) < 1e-5, k

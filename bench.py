@@ -19,9 +19,21 @@ prints ONE JSON line. Keys beyond the base contract:
   camera                config 1 (1920x1080 rolling-shutter camera, 500k Gaussians) in Mpix/s.
   cpu_baseline          the CPU oracle restatement of the same frame on the host cores (rank 0).
 
+  roofline_stages       every stage of the frame against its own bound: projection and tile ordering
+                        against the measured HBM copy peak, compositing against the FP32 probe.
+  config3               the multi-sensor rig (2 M Gaussians replicated, six 1920x1080 cameras + the
+                        lidar) with the sensors split over the ranks: per-frame latency = slowest
+                        rank, frames/s, camera Mpix/s.
+  config4               the Gaussian-sharded training step (1 M Gaussians per rank, one camera per
+                        rank + up to two lidars, forward + backward): step time, stage times, bytes
+                        on NVLink per step and the all-to-all's achieved GB/s per GPU.
+
 With --gpus N > 1 (launched through torch.distributed.run) every rank renders its own lidar
 sensor over replicated Gaussians: the path shards by sensor with no data-path collective, so
-scaling is "weak" and value is the sum over ranks divided by the slowest rank's time.
+scaling is "weak" and value is the sum over ranks divided by the slowest rank's time. In the
+end-to-end leg every rank uploads 1/N of the replicated scene from pinned memory and the ranks
+assemble it with an NCCL all-gather over NVLink, so the host link carries the scene once per step
+instead of N times.
 
 --impl reference times the reference's CPU implementation of the path. The reference has no CPU
 backend for its two render functions (its torch compositing calls CUDA kernels), so this arm
@@ -48,6 +60,7 @@ import numpy as np
 import torch
 
 POINTS_PER_FRAME = 128 * 1800
+N_GAUSSIANS = 1_000_000
 WORKLOAD = ("config2: 1,000,000 Gaussians (seed 2), one 128-beam x 1800-column rolling-shutter lidar "
             "(230,400 points), 16 features + range, alpha, alpha-sum, median range")
 
@@ -217,11 +230,11 @@ def training_step(render, cfg, leaves, flush, steps=5):
             "kernels": {k: {"launches": c, "ms": round(t, 4)} for k, (c, t) in prof.items()}}
 
 
-def fp32_probe(dev):
-    """Measured FP32 FMA rate (TFLOP/s): 148*16 blocks x 256 threads x iters x 128 FMAs."""
+def fp32_probe(dev, n_sms):
+    """Measured FP32 FMA rate (TFLOP/s): n_sms*16 blocks x 256 threads x iters x 128 FMAs."""
     from splatad_b200 import _lib
     lib = _lib.load()
-    grid, iters = 148 * 16, 4096
+    grid, iters = n_sms * 16, 4096
     out = torch.empty(grid * 256, device=dev)
     stream = torch.cuda.current_stream(dev).cuda_stream
     best = None
@@ -254,6 +267,25 @@ def count_row_records(meta, cfg):
     return int(torch.clamp(y1 - y0, min=0).sum())
 
 
+def count_pairs_lidar(meta, cfg):
+    """Tested / contributing (point, Gaussian) pairs of a rendered lidar frame (untimed kernel)."""
+    from splatad_b200 import ops
+    tested, contributing = ops.count_composited_pairs(
+        meta["means2d"], meta["conics"], meta["opacities"], meta["pix_vels"], meta["isect_offsets"],
+        meta["flatten_ids"], meta["width"], meta["height"], meta["tile_width"], meta["tile_height"],
+        raster_pts=cfg["raster_pts"])
+    return {"tested": tested, "contributing": contributing}
+
+
+def count_pairs_camera(meta, cfg):
+    from splatad_b200 import ops
+    tested, contributing = ops.count_composited_pairs(
+        meta["means2d"], meta["conics"], meta["opacities"], meta["pix_vels"], meta["isect_offsets"],
+        meta["flatten_ids"], meta["width"], meta["height"], meta["tile_size"], meta["tile_size"],
+        rolling_shutter_time=cfg["rolling_shutter_time"])
+    return {"tested": tested, "contributing": contributing}
+
+
 def to_device(cfg, dev):
     return {k: (v.to(dev, non_blocking=True) if isinstance(v, torch.Tensor) else v) for k, v in cfg.items()}
 
@@ -270,6 +302,247 @@ def sensor_pose_for_rank(cfg, rank):
     return dict(cfg, viewmats=vm)
 
 
+def _max_over_ranks(x, world, dev):
+    import torch.distributed as dist
+    if world == 1:
+        return float(x)
+    t = torch.tensor([float(x)], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _all_ranks(x, world, dev):
+    import torch.distributed as dist
+    if world == 1:
+        return [float(x)]
+    t = torch.tensor([float(x)], device=dev, dtype=torch.float64)
+    out = torch.empty(world, device=dev, dtype=torch.float64)
+    dist.all_gather_into_tensor(out, t)
+    return [float(v) for v in out.tolist()]
+
+
+def timed_frames(fn, n, flush):
+    """Mean milliseconds of n calls of fn() by per-call CUDA events, L2 flushed between calls, plus the
+    host's mean time inside the (unsynchronised) call."""
+    evs, host = [], 0.0
+    for _ in range(n):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        t0 = time.perf_counter()
+        out = fn()
+        host += time.perf_counter() - t0
+        b.record()
+        evs.append((a, b))
+    torch.cuda.synchronize()
+    return [a.elapsed_time(b) for a, b in evs], host / n * 1e3, out
+
+
+def measure_config3(world, rank, dev, flush, steps):
+    """Sensors split, Gaussians replicated: six 1920x1080 rolling-shutter cameras + the 128-beam lidar
+    over 2 M Gaussians; sensors assigned by pixel / point count, one render call per sensor."""
+    import splatad_b200
+    from splatad_b200 import scenes, sharding
+    cfg = scenes.config3()
+    cam, lid = cfg["camera"], cfg["lidar"]
+    costs = [1920 * 1080 * 1e-6] * 6 + [POINTS_PER_FRAME * 1e-6]
+    owners = sharding.sensor_owners(7, world, costs)
+    mine = sharding.local_sensors(owners, rank)
+    shared = {k: cam[k].to(dev) for k in ("means", "quats", "scales", "opacities")}
+    cam_calls = []
+    if any(c < 6 for c in mine):
+        colors = cam["colors"].to(dev)
+        for c in (c for c in mine if c < 6):
+            kw = dict(cam, **shared, colors=colors)
+            for k in ("viewmats", "Ks", "linear_velocity", "angular_velocity", "rolling_shutter_time"):
+                kw[k] = cam[k][c:c + 1].to(dev)
+            cam_calls.append(kw)
+    lid_kw = None
+    if 6 in mine:
+        lid_kw = dict(to_device(lid, dev), **shared)
+    marks = {}
+
+    def frame():
+        a = torch.cuda.Event(enable_timing=True)
+        a.record()
+        n_isects = 0
+        for kw in cam_calls:
+            n_isects += splatad_b200.rasterization(**kw)[2]["flatten_ids"].numel()
+        b = torch.cuda.Event(enable_timing=True)
+        b.record()
+        if lid_kw is not None:
+            n_isects += splatad_b200.lidar_rasterization(**lid_kw)[3]["flatten_ids"].numel()
+        marks.setdefault("cam", []).append((a, b))
+        return n_isects
+
+    for _ in range(3):
+        frame()
+    torch.cuda.synchronize()
+    marks.clear()
+    n = max(3, min(steps, 10))
+    ms, host_ms, n_isects = timed_frames(frame, n, flush)
+    cam_ms = float(np.mean([a.elapsed_time(b) for a, b in marks["cam"]])) if cam_calls else 0.0
+    per_rank = _all_ranks(float(np.mean(ms)), world, dev)
+    cam_max = _max_over_ranks(cam_ms, world, dev)
+    latency = max(per_rank)
+    return {
+        "workload": "config3: 2,000,000 Gaussians replicated (seed 3), six 1920x1080 rolling-shutter cameras (SH deg 3, "
+                    "RGB+D, packed) + one 128x1800 rolling-shutter lidar, sensors split over the ranks",
+        "sensor_owners": owners, "frames": n, "latency_ms": round(latency, 4),
+        "frames_per_s": round(1e3 / latency, 2),
+        "camera_mpix_per_s": round(6 * 1920 * 1080 * 1e-6 / (cam_max * 1e-3), 1) if cam_max > 0 else None,
+        "camera_ms_slowest_rank": round(cam_max, 4),
+        "lidar_points_per_s": round(POINTS_PER_FRAME / (latency * 1e-3), 1),
+        "per_rank_ms": [round(v, 4) for v in per_rank],
+        "n_isects_rank0": int(n_isects), "host_enqueue_ms_rank0": round(host_ms, 4),
+        "collectives_in_data_path": 0,
+    }
+
+
+def measure_config4(world, rank, dev, flush, steps):
+    """Gaussians split (1 M per rank), one camera per rank and up to two lidars, forward + backward:
+    every rank projects its slice for all sensors, one all-to-all routes the visible records to the
+    sensor owners, the backward pass mirrors it."""
+    import torch.distributed as dist
+    from splatad_b200 import scenes, sharding
+    shard = scenes.config4_shard(rank, world)
+    cam, lid = to_device(shard["camera"], dev), to_device(shard["lidar"], dev)
+    n_lidars = lid["viewmats"].shape[0]
+    owners_cam = [c % world for c in range(world)]
+    owners_lid = [c % world for c in range(n_lidars)]
+    leaves = {k: cam[k].detach().clone().requires_grad_(True) for k in ("means", "quats", "scales", "opacities")}
+    sh = cam["colors"].detach().clone().requires_grad_(True)
+    feats = lid["lidar_features"].detach().clone().requires_grad_(True)
+    gen = torch.Generator(device=dev).manual_seed(11 + rank)
+    cots = {}
+
+    def cot(key, t):
+        if key not in cots:
+            cots[key] = torch.randn(t.shape, device=dev, generator=gen)
+        return cots[key]
+
+    def step(stats_cam=None, stats_lid=None, bwd_marks=None):
+        out_c, out_a, m = sharding.rasterization_gaussian_sharded(
+            **dict(cam, **leaves, colors=sh), owners=owners_cam, stats=stats_cam)
+        lo_c, lo_a, lo_s, lm = sharding.lidar_rasterization_gaussian_sharded(
+            **dict(lid, **leaves, lidar_features=feats), owners=owners_lid, stats=stats_lid)
+        loss = (out_c * cot("c", out_c)).sum() + (out_a * cot("a", out_a)).sum()
+        loss = loss + (lo_c * cot("lc", lo_c)).sum() + (lo_a * cot("la", lo_a)).sum() + (lo_s * cot("ls", lo_s)).sum()
+        if bwd_marks is not None:
+            bwd_marks.append(torch.cuda.Event(enable_timing=True))
+            bwd_marks[-1].record()
+        loss.backward()
+        if bwd_marks is not None:
+            bwd_marks.append(torch.cuda.Event(enable_timing=True))
+            bwd_marks[-1].record()
+        for t in list(leaves.values()) + [sh, feats]:
+            t.grad = None
+        return int(m["flatten_ids"].numel()), int(lm["flatten_ids"].numel())
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    n = max(3, min(steps, 10))
+    if world > 1:
+        dist.barrier()
+    ms, host_ms, (isects_cam, isects_lid) = timed_frames(step, n, flush)
+    ms_step = _max_over_ranks(float(np.mean(ms)), world, dev)
+    # one more, instrumented step: stage boundaries by CUDA events on the render stream
+    s_cam, s_lid, bwd = {"time": True}, {"time": True}, []
+    step(s_cam, s_lid, bwd)
+    torch.cuda.synchronize()
+
+    def stage_ms(stats):
+        marks = stats["marks"]
+        return {name: round(prev_ev.elapsed_time(ev), 4) for (_, prev_ev), (name, ev) in zip(marks[:-1], marks[1:])}
+
+    stages = {"camera_forward": stage_ms(s_cam), "lidar_forward": stage_ms(s_lid),
+              "backward_all": round(bwd[0].elapsed_time(bwd[1]), 4)}
+    wire = s_cam["bytes_sent_off_rank"] + s_lid["bytes_sent_off_rank"]
+    a2a_ms = stages["camera_forward"]["all_to_all"] + stages["lidar_forward"]["all_to_all"]
+    a2a_max = _max_over_ranks(a2a_ms, world, dev)
+    wire_max = _max_over_ranks(wire, world, dev)
+    return {
+        "workload": f"config4 at {world} rank(s): {world} x 1,000,000 Gaussians split over the ranks, {world} "
+                    f"1920x1080 rolling-shutter cameras (one per rank, SH deg 3, RGB+D) + {n_lidars} 128x1800 lidar(s), "
+                    "forward + backward, loss = sum(output * seeded cotangent)",
+        "steps": n, "ms_per_step": round(ms_step, 4), "steps_per_s": round(1e3 / ms_step, 3),
+        "gaussians_per_s": round(world * 1_000_000 / (ms_step * 1e-3), 1),
+        "stage_ms_rank0": stages,
+        "row_bytes": {"camera": s_cam["row_bytes"], "lidar": s_lid["row_bytes"]},
+        "rows_sent_rank0": {"camera": s_cam["rows_sent"], "lidar": s_lid["rows_sent"]},
+        "nvlink_bytes_sent_per_step_per_gpu_max": int(2 * wire_max),   # forward rows + their gradients back
+        "all_to_all_forward": {
+            "ms_slowest_rank": round(a2a_max, 4),
+            "gb_per_s_per_gpu": round(wire_max / (a2a_max * 1e-3) / 1e9, 2) if (world > 1 and a2a_max > 0) else None,
+            "nvlink_peer_copy_gb_per_s": 770.0,
+            "share_of_step": round(a2a_max / ms_step, 4),
+        },
+        "n_isects_rank0": {"camera": isects_cam, "lidar": isects_lid},
+        "host_enqueue_ms_rank0": round(host_ms, 4),
+        "host_syncs_per_step": "one per exchange (NCCL split sizes) + the intersection counts read after compositing",
+    }
+
+
+def roofline_stages(prof, cam_prof, n_gauss, n_vis, n_isects, n_rec, pairs, cam_pairs, peak, tfl):
+    """Every stage of the lidar frame (and the camera compositing) against the bound that applies:
+    algorithmic bytes / measured time against the HBM copy peak, algorithmic flops against the FP32
+    probe. Algorithmic figures: projection 40 B read per Gaussian + 52 B written per (sensor,
+    Gaussian); tile ordering 24 B per intersection (one 8 B id read + 16 B written would be the floor
+    of any sort-free construction that reads keys once and writes ids + flatten ids once and an
+    8-byte record) over every kernel from the rectangle count to the final lists; depth sort 16 B per
+    visible Gaussian and pass; compositing tested * 36 + contributing * (12 + 2 D) flops."""
+    def ms_of(*names):
+        return sum(prof[k][1] for k in prof if any(k.startswith(nm) for nm in names))
+
+    out = []
+    t = ms_of("lidar_projection_fwd_kernel")
+    if t > 0:
+        b = n_gauss * 40 + n_gauss * 52
+        out.append({"stage": "projection", "bound": "hbm", "ms": round(t, 4), "algorithmic_bytes": int(b),
+                    "achieved": round(b / (t * 1e-3) / 1e9, 1), "peak": peak, "unit": "GB/s",
+                    "frac": round(b / (t * 1e-3) / 1e9 / peak, 4)})
+    t = ms_of("depthsort", "radix_")
+    n_pass = max(1, sum(prof[k][0] for k in prof if "downsweep" in k or "onesweep" in k))
+    if t > 0:
+        b = n_vis * 16 * n_pass
+        out.append({"stage": "depth sort", "bound": "hbm", "ms": round(t, 4), "passes": n_pass,
+                    "algorithmic_bytes": int(b), "achieved": round(b / (t * 1e-3) / 1e9, 1), "peak": peak,
+                    "unit": "GB/s", "frac": round(b / (t * 1e-3) / 1e9 / peak, 4)})
+    t = ms_of("isect_count", "depthsort", "radix_", "rowsplit", "colsplit", "init_counters", "emit", "tilesort")
+    if t > 0:
+        b = n_isects * 24
+        out.append({"stage": "tile ordering (count .. lists)", "bound": "hbm", "ms": round(t, 4),
+                    "algorithmic_bytes": int(b), "bytes_per_intersection": 24,
+                    "achieved": round(b / (t * 1e-3) / 1e9, 1), "peak": peak, "unit": "GB/s",
+                    "frac": round(b / (t * 1e-3) / 1e9 / peak, 4)})
+    t = ms_of("rasterize_to_points_fwd_kernel")
+    if t > 0 and pairs is not None:
+        D = 17
+        fl = pairs["tested"] * 36 + pairs["contributing"] * (12 + 2 * D)
+        out.append({"stage": "lidar compositing", "bound": "fp32", "ms": round(t, 4), "tested_pairs": pairs["tested"],
+                    "contributing_pairs": pairs["contributing"], "algorithmic_flops": int(fl),
+                    "achieved": round(fl / (t * 1e-3) / 1e12, 2), "peak": round(tfl, 2), "unit": "TFLOP/s",
+                    "frac": round(fl / (t * 1e-3) / 1e12 / tfl, 4)})
+    if cam_prof is not None and cam_pairs is not None:
+        t = sum(cam_prof[k][1] for k in cam_prof if k.startswith("rasterize_to_pixels_fwd_kernel"))
+        if t > 0:
+            D = 4
+            fl = cam_pairs["tested"] * 36 + cam_pairs["contributing"] * (12 + 2 * D)
+            out.append({"stage": "camera compositing (config1)", "bound": "fp32", "ms": round(t, 4),
+                        "tested_pairs": cam_pairs["tested"], "contributing_pairs": cam_pairs["contributing"],
+                        "algorithmic_flops": int(fl), "achieved": round(fl / (t * 1e-3) / 1e12, 2),
+                        "peak": round(tfl, 2), "unit": "TFLOP/s", "frac": round(fl / (t * 1e-3) / 1e12 / tfl, 4)})
+    return out
+
+
+# DRAM bytes (read + written) per launch on the headline frame, from the ncu captures summarised
+# under profiles/ (file named after the kernel); kernels without a committed capture give null.
+NCU_TRAFFIC = {
+    "colsplit_scatter_kernel": (229_227_008, "profiles/colsplit_and_rowsplit_scatter_config2.md"),
+}
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -283,9 +556,11 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     dev = torch.device(f"cuda:{local_rank}")
     torch.cuda.set_device(dev)
+    n_sms = torch.cuda.get_device_properties(dev).multi_processor_count
 
     cfg_host = sensor_pose_for_rank(scenes.config2(), rank)
     cfg = to_device(cfg_host, dev)
+    n_gauss = int(cfg["means"].shape[0])
     flush = torch.empty(256 * 1024 * 1024 // 4, device=dev)  # 256 MB > 126 MB of L2
 
     def step(c=cfg):
@@ -296,7 +571,8 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         out = step()
     torch.cuda.synchronize()
     n_isects = int(out[3]["flatten_ids"].numel())
@@ -306,34 +582,39 @@ def run_ours(args):
     sampler.start()
     barrier()
     t_wall = time.perf_counter()
-    evs = []
-    for _ in range(args.steps):
-        flush.zero_()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        out = step()
-        b.record()
-        evs.append((a, b))
+    ms_steps, host_ms, out = timed_frames(step, args.steps, flush)
     barrier()
     wall = time.perf_counter() - t_wall
-    ms_steps = [a.elapsed_time(b) for a, b in evs]
-    ms_total = float(np.sum(ms_steps))
-    if world > 1:
-        tt = torch.tensor([ms_total], device=dev, dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms_total = float(tt.item())
-    ms_per_step = ms_total / args.steps
+    per_rank_ms = _all_ranks(float(np.mean(ms_steps)), world, dev)
+    per_rank_host = _all_ranks(host_ms, world, dev)
+    ms_per_step = max(per_rank_ms)
     value = world * POINTS_PER_FRAME / (ms_per_step * 1e-3)
 
     # ---- end to end: host inputs in pinned memory, H2D + render + D2H every step ---------------
     # Three streams (copy-in, render, copy-out) and two sets of device input buffers: step i + 1's
     # host->device copy runs while step i renders and step i - 1's results go back. Every step
-    # still copies all of its inputs from pinned host memory and reads its result back.
+    # copies all of its inputs from pinned host memory and reads its result back. With N > 1 ranks
+    # the Gaussians are replicated: every rank uploads 1/N of each Gaussian tensor and an NCCL
+    # all-gather over NVLink assembles the full tensors, so the host link carries the scene once.
+    scene_keys = ("means", "quats", "scales", "opacities", "lidar_features")
     pinned = {k: (v.pin_memory() if isinstance(v, torch.Tensor) else v) for k, v in cfg_host.items()}
-    h2d_bytes = sum(v.numel() * v.element_size() for v in pinned.values() if isinstance(v, torch.Tensor))
+    split = world > 1 and n_gauss % world == 0
+    lo, hi = rank * (n_gauss // world), (rank + 1) * (n_gauss // world)
+
+    def rows_of(k, t):        # the [N, ...] view of a Gaussian tensor (lidar_features is [1, N, D])
+        return t[0] if k == "lidar_features" else t
+
+    if split:
+        pinned_slices = {k: rows_of(k, cfg_host[k])[lo:hi].contiguous().pin_memory() for k in scene_keys}
+        h2d_local = sum(v.numel() * v.element_size() for v in pinned_slices.values())
+        h2d_local += sum(v.numel() * v.element_size() for k, v in pinned.items()
+                         if isinstance(v, torch.Tensor) and k not in scene_keys)
+    else:
+        h2d_local = sum(v.numel() * v.element_size() for v in pinned.values() if isinstance(v, torch.Tensor))
     s_in, s_cmp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     dev_in = [{k: (torch.empty_like(v, device=dev) if isinstance(v, torch.Tensor) else v)
                for k, v in pinned.items()} for _ in range(2)]
+    dev_slice = [{k: torch.empty_like(v, device=dev) for k, v in pinned_slices.items()} for _ in range(2)] if split else None
     host_out = []
 
     def e2e_run(n_steps):
@@ -348,7 +629,12 @@ def run_ours(args):
                 if ev_cmp[b] is not None:      # the render that last read this buffer set
                     s_in.wait_event(ev_cmp[b])
                 for k, v in pinned.items():
-                    if isinstance(v, torch.Tensor):
+                    if not isinstance(v, torch.Tensor):
+                        continue
+                    if split and k in scene_keys:
+                        dev_slice[b][k].copy_(pinned_slices[k], non_blocking=True)
+                        dist.all_gather_into_tensor(rows_of(k, dev_in[b][k]), dev_slice[b][k])
+                    else:
                         dev_in[b][k].copy_(v, non_blocking=True)
                 ev_in[b] = torch.cuda.Event()
                 ev_in[b].record(s_in)
@@ -378,17 +664,21 @@ def run_ours(args):
         return start, end
 
     e2e_run(3)
-    d2h_bytes = sum(h.numel() * h.element_size() for h in host_out)
+    d2h_local = sum(h.numel() * h.element_size() for h in host_out)
     barrier()
     a, b = e2e_run(args.steps)
     barrier()
     clocks = sampler.stop()
-    e2e_ms = a.elapsed_time(b)
-    if world > 1:
-        tt = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        e2e_ms = float(tt.item())
+    e2e_ms = _max_over_ranks(a.elapsed_time(b), world, dev)
     e2e_value = world * POINTS_PER_FRAME * args.steps / (e2e_ms * 1e-3)
+    del dev_in, dev_slice
+    torch.cuda.empty_cache()
+
+    # ---- the two multi-GPU configurations (all ranks) ------------------------------------------
+    config3 = measure_config3(world, rank, dev, flush, args.steps)
+    torch.cuda.empty_cache()
+    config4 = measure_config4(world, rank, dev, flush, args.steps)
+    torch.cuda.empty_cache()
 
     result = None
     if rank == 0:
@@ -414,44 +704,40 @@ def run_ours(args):
             "emit_kernel": n_isects * 8 + n_vis * 20,
             "depthsort_downsweep": n_vis * 16,
             "depthsort_upsweep": n_vis * 4,
-            "lidar_projection_fwd_kernel": 1_000_000 * 40 + n_vis * 52 + (1_000_000 - n_vis) * 52,
+            "lidar_projection_fwd_kernel": n_gauss * 40 + n_gauss * 52,
             "rasterize_to_points_fwd_kernel": POINTS_PER_FRAME * (16 + 4 * 21),
-            "isect_count_kernel": 1_000_000 * 20,
+            "isect_count_kernel": n_gauss * 20,
         }.get(dom_name, None)
-        # DRAM bytes (read + written) per launch of the same kernel on this workload from the ncu
-        # capture summarised under profiles/
-        traffic = {"colsplit_scatter_kernel": 229_227_008}.get(dom_name)
+        traffic, traffic_src = NCU_TRAFFIC.get(dom_name, (None, "no ncu capture of this kernel is committed under profiles/"))
         roofline = None
         if bytes_per_launch is not None:
             achieved = bytes_per_launch / (dom_ms / dom_cnt * 1e-3) / 1e9
             roofline = {"kernel": dom_name, "bound": "hbm", "achieved": round(achieved, 1), "peak": peak,
                         "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": traffic,
+                        "traffic_source": traffic_src,
                         "peak_source": f"of {peak_src}", "launches_per_step": dom_cnt,
                         "ms_per_launch": round(dom_ms / dom_cnt, 4),
                         "algorithmic_bytes_per_launch": int(bytes_per_launch)}
-        tfl = fp32_probe(dev)
+        tfl = fp32_probe(dev, n_sms)
 
         # ---- camera config 1 ---------------------------------------------------------------
         cam_cfg = to_device(scenes.config1(), dev)
         for _ in range(3):
             cam_out = splatad_b200.rasterization(**cam_cfg)
         torch.cuda.synchronize()
-        cam_evs = []
-        for _ in range(max(3, min(args.steps, 20))):   # timed like the lidar steps: per-frame events, one wait
-            flush.zero_()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            cam_out = splatad_b200.rasterization(**cam_cfg)
-            b.record()
-            cam_evs.append((a, b))
-        torch.cuda.synchronize()
-        cam_ms = [a.elapsed_time(b) for a, b in cam_evs]
+        cam_ms, cam_host_ms, cam_out = timed_frames(lambda: splatad_b200.rasterization(**cam_cfg),
+                                                    max(3, min(args.steps, 20)), flush)
         cam_prof = kernel_profile(lambda: splatad_b200.rasterization(**cam_cfg))
         camera = {"workload": "config1: 500,000 Gaussians, 1920x1080 rolling-shutter camera, SH deg 3, RGB+D, packed",
                   "mpix_per_s": round(1920 * 1080 * 1e-6 / (np.mean(cam_ms) * 1e-3), 1),
                   "ms_per_frame": round(float(np.mean(cam_ms)), 4),
+                  "host_enqueue_ms": round(cam_host_ms, 4),
                   "n_isects": int(cam_out[2]["flatten_ids"].numel()),
                   "kernels": {k: {"launches": c, "ms": round(ms, 4)} for k, (c, ms) in cam_prof.items()}}
+
+        pairs = count_pairs_lidar(out[3], cfg)
+        cam_pairs = count_pairs_camera(cam_out[2], cam_cfg)
+        stages = roofline_stages(prof, cam_prof, n_gauss, n_vis, n_isects, n_rec, pairs, cam_pairs, peak, tfl)
 
         training = {"lidar": training_step(splatad_b200.lidar_rasterization, cfg,
                                             ("means", "quats", "scales", "opacities", "lidar_features"), flush),
@@ -461,24 +747,40 @@ def run_ours(args):
         cpu = cpu_baseline_sample()
         result = {
             "metric": "lidar_points_per_s", "value": round(value, 1), "unit": "points/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
+            "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 4),
             "frames_per_s": round(1e3 / ms_per_step * world, 1),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic", "impl": "ours",
-            "config": {"workload": WORKLOAD, "n_isects": n_isects, "n_visible": n_vis,
-                       "l2": "flushed between steps (256 MB write)",
-                       "e2e": "3 streams, double-buffered inputs: step i+1 copies in while step i renders",
-                       "sharding": "one lidar sensor per rank, Gaussians replicated, no collective"},
+            "config": {"workload": WORKLOAD},
+            "config_detail": {"n_isects": n_isects, "n_visible": n_vis, "n_gaussians": n_gauss,
+                              "l2": "flushed between steps (256 MB write)",
+                              "e2e": "3 streams, double-buffered inputs: step i+1 copies in while step i renders"
+                                     + ("; every rank uploads 1/N of the replicated Gaussians, NCCL all-gather over "
+                                        "NVLink assembles them" if split else ""),
+                              "sharding": "one lidar sensor per rank, Gaussians replicated, no collective in the "
+                                          "device-resident path"},
             "clocks": clocks,
-            "e2e": {"value": round(e2e_value, 1), "unit": "points/s", "h2d_bytes_per_step": int(h2d_bytes),
-                    "d2h_bytes_per_step": int(d2h_bytes), "ms_per_step": round(e2e_ms / args.steps, 4)},
+            "e2e": {"value": round(e2e_value, 1), "unit": "points/s",
+                    "h2d_bytes_per_step": int(h2d_local * world), "d2h_bytes_per_step": int(d2h_local * world),
+                    "h2d_bytes_per_step_per_rank": int(h2d_local), "d2h_bytes_per_step_per_rank": int(d2h_local),
+                    "ms_per_step": round(e2e_ms / args.steps, 4)},
+            "per_rank": {"ms_per_step": [round(v, 4) for v in per_rank_ms],
+                         "min_median_max_ms": [round(float(np.min(per_rank_ms)), 4),
+                                               round(float(np.median(per_rank_ms)), 4),
+                                               round(float(np.max(per_rank_ms)), 4)],
+                         "host_enqueue_ms_per_step": [round(v, 4) for v in per_rank_host]},
             "gpu_launches": launches * args.steps,
             "launches_per_step": launches,
             "kernels": kernels,
             "roofline": roofline,
-            "fp32_probe": {"tflops": round(tfl, 2), "how": "FMA chains, 148*16 blocks x 256 threads"},
+            "roofline_stages": stages,
+            "fp32_probe": {"tflops": round(tfl, 2), "how": f"FMA chains, {n_sms}*16 blocks x 256 threads"},
+            "camera_mpix_per_s": camera["mpix_per_s"],
+            "training_ms_per_step": {k: v["ms_per_step"] for k, v in training.items()},
             "camera": camera,
             "training": training,
+            "config3": config3,
+            "config4": config4,
             "cpu_baseline": cpu,
             "wall_s_timed_region": round(wall, 3),
         }
@@ -544,7 +846,7 @@ def cpu_baseline_sample():
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     cpu_frame(25_000)  # warm-up (imports, C oracle build)
-    best, stages = min((cpu_frame(1_000_000) for _ in range(2)), key=lambda r: r[0])   # the first pays for fresh pages
+    best, stages = min((cpu_frame(N_GAUSSIANS) for _ in range(2)), key=lambda r: r[0])   # the first pays for fresh pages
     value = POINTS_PER_FRAME / best
     return {"value": round(value, 1), "unit": "points/s", "cores": cores, "kind": "port",
             "sample": f"one full frame: 128x1800 sensor, 1,000,000 Gaussians (best of 2, {best:.2f} s); projection (torch) and "
@@ -564,9 +866,9 @@ def run_reference(args):
     # ids gets slower per item as the array outgrows the caches), so the scale factor from a sample
     # to the full frame is MEASURED once, in the warm-up, instead of assumed.
     fraction = 0.05
-    n = int(1_000_000 * fraction)
+    n = int(N_GAUSSIANS * fraction)
     cpu_frame(n)
-    t_full = min(cpu_frame(1_000_000)[0] for _ in range(2))   # the first one also pays for fresh pages
+    t_full = min(cpu_frame(N_GAUSSIANS)[0] for _ in range(2))   # the first one also pays for fresh pages
     t_sample = min(cpu_frame(n)[0] for _ in range(2))
     scale = t_full / t_sample
     for _ in range(max(0, min(args.warmup, 2) - 1)):

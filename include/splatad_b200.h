@@ -491,6 +491,25 @@ int splatad_rasterize_to_indices_in_range_lidar_write(
     const int32_t *tile_offsets, const int32_t *flatten_ids, const int64_t *chunk_starts,
     int64_t *gaussian_ids, int64_t *pixel_ids, int64_t *camera_ids, void *stream);
 
+/* Measurement aid (no counterpart in the reference): walks every pixel's (point's) whole tile list
+ * from transmittance `transmittances` [C,H,W] exactly as the compositing kernels do and adds up
+ * counters[0] = (pixel, Gaussian) pairs evaluated (the one a pixel stops at included) and
+ * counters[1] = pairs blended; pixel_counts [C*H*W] receives the blended pairs per pixel. These
+ * are the "tested" and "contributing" pair counts of the compositing flop model. counters is a
+ * device array of two uint64, zeroed by the call. */
+int splatad_count_composited_pairs(
+    uint32_t C, uint32_t N, int64_t n_isects, const float *transmittances, const float *means2d,
+    const float *conics, const float *opacities, const float *pix_vels, const float *rolling_shutter_time,
+    uint32_t image_width, uint32_t image_height, uint32_t tile_size, uint32_t tile_width, uint32_t tile_height,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, int32_t *pixel_counts, uint64_t *counters,
+    void *stream);
+int splatad_count_composited_pairs_lidar(
+    uint32_t C, uint32_t N, int64_t n_isects, const float *transmittances, const float *means2d,
+    const float *conics, const float *opacities, const float *pix_vels, const float *raster_pts,
+    uint32_t image_width, uint32_t image_height, uint32_t tile_width, uint32_t tile_height,
+    uint32_t tile_grid_width, uint32_t tile_grid_height, const int32_t *tile_offsets,
+    const int32_t *flatten_ids, int32_t *pixel_counts, uint64_t *counters, void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * Densification hooks: what the training strategies do with the render path's outputs.
  * ---------------------------------------------------------------------------------------- */

@@ -33,6 +33,7 @@ struct IndicesArgs {
     const int64_t *starts;    // write pass
     int32_t *cnts;            // count pass
     int64_t *gaussian_ids, *pixel_ids, *camera_ids;
+    unsigned long long *pair_counters;   // count pass, optional: [0] += tested, [1] += contributing pairs
 };
 
 template <bool kLidar, bool kWrite>
@@ -83,6 +84,7 @@ __global__ void indices_in_range_kernel(const IndicesArgs a) {
     }
     bool done = !inside;
     int32_t cnt = 0;
+    uint32_t tested = 0;   // entries this pixel evaluated, the one it stops at included
     const uint32_t b_end = min(a.range_end, num_batches);
     for (uint32_t b = a.range_start; b < b_end; ++b) {
         if (__syncthreads_count(done) >= (int)blockDim.x) break;
@@ -113,6 +115,7 @@ __global__ void indices_in_range_kernel(const IndicesArgs a) {
             }
             const float sigma = 0.5f * (B.x * dx * dx + B.z * dy * dy) + B.y * dx * dy;
             const float alpha = fminf(kAlphaMax, B.w * __expf(-sigma));
+            if (!kWrite) ++tested;
             if (sigma < 0.f || alpha < kAlphaMin) continue;
             const float next_T = T * (1.f - alpha);
             if (next_T <= kTStop) { done = true; break; }
@@ -126,6 +129,18 @@ __global__ void indices_in_range_kernel(const IndicesArgs a) {
         }
     }
     if (!kWrite && in_image) a.cnts[pix] = cnt;
+    if (!kWrite && a.pair_counters != nullptr) {
+        unsigned long long t = tested, c = (unsigned long long)cnt;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            t += __shfl_xor_sync(0xffffffffu, t, off);
+            c += __shfl_xor_sync(0xffffffffu, c, off);
+        }
+        if ((threadIdx.x & 31) == 0 && t) {
+            atomicAdd(a.pair_counters, t);
+            atomicAdd(a.pair_counters + 1, c);
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -425,4 +440,53 @@ extern "C" int splatad_rasterize_to_indices_in_range_lidar_write(
     a.gaussian_ids = gaussian_ids; a.pixel_ids = pixel_ids; a.camera_ids = camera_ids;
     return indices_write<true>(a, chunk_starts, (cudaStream_t)stream,
                                "rasterize_to_indices_in_range_lidar_write");
+}
+
+
+// ---------------------------------------------------------------------------------------
+// Pair counts of a whole frame (measurement aid)
+// ---------------------------------------------------------------------------------------
+template <bool kLidar>
+static int count_pairs(IndicesArgs a, int32_t *pixel_counts, unsigned long long *counters, cudaStream_t st,
+                       const char *what) {
+    int rc = check_indices_args(a, kLidar, what);
+    if (rc != SPLATAD_OK) return rc;
+    SPL_REQUIRE(pixel_counts && counters, SPLATAD_ERR_BAD_ARG, "%s: null output", what);
+    if (cudaMemsetAsync(counters, 0, 2 * sizeof(unsigned long long), st) != cudaSuccess) return check_launch(what);
+    if ((uint64_t)a.C * a.H * a.W == 0 || a.n_isects == 0 || a.C * a.grid_w * a.grid_h == 0) return SPLATAD_OK;
+    a.cnts = pixel_counts;
+    a.pair_counters = counters;
+    return launch_indices<kLidar, false>(a, st, what);
+}
+
+extern "C" int splatad_count_composited_pairs(
+    uint32_t C, uint32_t N, int64_t n_isects, const float *transmittances, const float *means2d,
+    const float *conics, const float *opacities, const float *pix_vels, const float *rolling_shutter_time,
+    uint32_t image_width, uint32_t image_height, uint32_t tile_size, uint32_t tile_width, uint32_t tile_height,
+    const int32_t *tile_offsets, const int32_t *flatten_ids, int32_t *pixel_counts, uint64_t *counters,
+    void *stream) {
+    IndicesArgs a = {};
+    a.range_start = 0; a.range_end = 0xffffffffu; a.C = C; a.N = N; a.n_isects = n_isects;
+    a.means2d = (const float2 *)means2d; a.conics = conics; a.opacities = opacities; a.pix_vels = pix_vels;
+    a.rs_time = rolling_shutter_time; a.W = image_width; a.H = image_height; a.tile_w = tile_size;
+    a.tile_h = tile_size; a.grid_w = tile_width; a.grid_h = tile_height; a.offsets = tile_offsets;
+    a.flatten_ids = flatten_ids; a.transmittances = transmittances;
+    return count_pairs<false>(a, pixel_counts, (unsigned long long *)counters, (cudaStream_t)stream,
+                              "count_composited_pairs");
+}
+
+extern "C" int splatad_count_composited_pairs_lidar(
+    uint32_t C, uint32_t N, int64_t n_isects, const float *transmittances, const float *means2d,
+    const float *conics, const float *opacities, const float *pix_vels, const float *raster_pts,
+    uint32_t image_width, uint32_t image_height, uint32_t tile_width, uint32_t tile_height,
+    uint32_t tile_grid_width, uint32_t tile_grid_height, const int32_t *tile_offsets,
+    const int32_t *flatten_ids, int32_t *pixel_counts, uint64_t *counters, void *stream) {
+    IndicesArgs a = {};
+    a.range_start = 0; a.range_end = 0xffffffffu; a.C = C; a.N = N; a.n_isects = n_isects;
+    a.means2d = (const float2 *)means2d; a.conics = conics; a.opacities = opacities; a.pix_vels = pix_vels;
+    a.raster_pts = (const float4 *)raster_pts; a.W = image_width; a.H = image_height; a.tile_w = tile_width;
+    a.tile_h = tile_height; a.grid_w = tile_grid_width; a.grid_h = tile_grid_height; a.offsets = tile_offsets;
+    a.flatten_ids = flatten_ids; a.transmittances = transmittances;
+    return count_pairs<true>(a, pixel_counts, (unsigned long long *)counters, (cudaStream_t)stream,
+                             "count_composited_pairs_lidar");
 }

@@ -1680,3 +1680,49 @@ def rasterize_to_indices_in_range_lidar(
     return _indices_in_range("lidar", range_start, range_end, transmittances, means2d, conics, opacities,
                              pix_vels, raster_pts, image_width, image_height, tile_width, tile_height,
                              isect_offsets, flatten_ids)
+
+
+@torch.no_grad()
+def count_composited_pairs(
+    means2d: Tensor,  # [C, N, 2] or [nnz, 2]
+    conics: Tensor,
+    opacities: Tensor,
+    pix_vels: Tensor,  # [..., 2] camera, [..., 3] lidar
+    isect_offsets: Tensor,  # [C, tile rows, tile columns]
+    flatten_ids: Tensor,
+    image_width: int,
+    image_height: int,
+    tile_width: int,
+    tile_height: int,
+    rolling_shutter_time: Optional[Tensor] = None,  # [C]: camera
+    raster_pts: Optional[Tensor] = None,  # [C, H, W, 4]: lidar
+) -> Tuple[int, int]:
+    """(tested, contributing) pair counts of a frame: how many (pixel, Gaussian) pairs the
+    compositing evaluates before every pixel has stopped, and how many of them it blends. A
+    measurement aid for the compositing flop model (not part of the reference's API); ``raster_pts``
+    selects the lidar rules, otherwise ``rolling_shutter_time`` (zeros if missing) the camera's."""
+    C, grid_h, grid_w = isect_offsets.shape
+    dev = means2d.device
+    lidar = raster_pts is not None
+    n_pix = C * image_height * image_width
+    counters = torch.zeros(2, dtype=torch.int64, device=dev)
+    if n_pix == 0 or flatten_ids.numel() == 0:
+        return 0, 0
+    ones = torch.ones((C, image_height, image_width), dtype=torch.float32, device=dev)
+    per_pixel = torch.empty(n_pix, dtype=torch.int32, device=dev)
+    flat = flatten_ids.to(torch.int32).contiguous()
+    offs = isect_offsets.to(torch.int32).contiguous()
+    n_rows = means2d.numel() // 2
+    head = (C, max(n_rows // max(C, 1), 1), flat.numel(), _lib.ptr(ones), _lib.ptr(_f(means2d)), _lib.ptr(_f(conics)),
+            _lib.ptr(_f(opacities)), _lib.ptr(_f(pix_vels)))
+    tail = (_lib.ptr(offs), _lib.ptr(flat), _lib.ptr(per_pixel), _lib.ptr(counters), _lib.stream_ptr(dev))
+    if lidar:
+        _call("splatad_count_composited_pairs_lidar", *head, _lib.ptr(_f(raster_pts)), image_width, image_height,
+              tile_width, tile_height, grid_w, grid_h, *tail)
+    else:
+        assert tile_width == tile_height
+        rs = _f(rolling_shutter_time) if rolling_shutter_time is not None else torch.zeros(C, device=dev)
+        _call("splatad_count_composited_pairs", *head, _lib.ptr(rs), image_width, image_height, tile_width, grid_w,
+              grid_h, *tail)
+    tested, contributing = counters.tolist()
+    return int(tested), int(contributing)

@@ -234,3 +234,30 @@ def config4(device="cpu", N: int = 8_000_000, seed: int = 4, n_cameras: int = 8,
         lk["viewmats"][i, 0, 3] = -float(i)  # sensor i sits at x = i metres: world->sensor shifts by -i
     lid.update(_to(lk, device))
     return {"camera": cam, "lidar": lid}
+
+
+def config4_shard(rank: int, world: int, n_local: int = 1_000_000, seed: int = 4) -> Dict:
+    """Rank ``rank``'s part of the Gaussian-sharded training configuration at ``world`` ranks:
+    ``n_local`` Gaussians of its own (lidar box, SH degree 3, 16 lidar features; seeded by
+    ``seed`` and the rank, so the scene of ``world * n_local`` Gaussians never has to exist on one
+    host), and ALL sensors - ``world`` cameras yawed 360 / world degrees apart and min(2, world)
+    lidars a metre apart - which every rank generates alike. Returns {"camera": kwargs, "lidar":
+    kwargs, "n_total", "start"} for the two ``*_gaussian_sharded`` render functions."""
+    g = _gen(seed * 1000 + rank)
+    means, quats, scales, opacities = lidar_box_gaussians(n_local, g)
+    sh = torch.randn(n_local, 16, 3, generator=g) * 0.3
+    features = torch.randn(n_local, 16, generator=g)
+    gs = _gen(seed)                                   # sensors: the same on every rank
+    n_lidars = min(2, world)
+    elev = beams_128()
+    pts = torch.cat([lidar_sensor(elev, 1800, gs, sweep_time=0.1) for _ in range(n_lidars)], dim=0)
+    base = dict(means=means, quats=quats, scales=scales, opacities=opacities, velocities=None,
+                n_gaussians_total=world * n_local, gaussian_start=rank * n_local)
+    cam = dict(base, colors=sh)
+    cam.update(_camera_kwargs(world, yawed_camera_viewmats([i * 360.0 / world for i in range(world)])))
+    lid = dict(base, lidar_features=features)
+    lk = _lidar_kwargs(elev, 1800, 0.2, pts, rolling=True, C=n_lidars)
+    for i in range(n_lidars):
+        lk["viewmats"][i, 0, 3] = -float(i)
+    lid.update(lk)
+    return {"camera": cam, "lidar": lid, "n_total": world * n_local, "start": rank * n_local}

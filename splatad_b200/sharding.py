@@ -310,17 +310,22 @@ def exchange_projected(
     tensors = [radii] + [fields[k] for k in sorted(fields)]
     for k, f in zip(names, tensors):
         assert f.shape[:2] == (C, n_local), (k, f.shape)
+    _mark(stats, "project", dev)
     row_index, indptr = visible_rows(radii)
     counts = gather_counts(indptr, group)                       # the step's host synchronisation
+    _mark(stats, "count", dev)
     plan = plan_exchange(counts, order, owners, rank)
     n_send = int(sum(counts[rank]))
     flat = [f.reshape(C * n_local, -1) for f in tensors]
     widths = [f.shape[1] for f in flat]
     sensor_table = torch.tensor(list(order), dtype=torch.int32).to(dev, non_blocking=True)
     rows = _PackRows.apply(row_index, n_send, sensor_table, n_local, int(gaussian_start), *flat)
+    _mark(stats, "pack", dev)
     received = exchange_rows(rows, plan.send_splits, plan.recv_splits, group)
+    _mark(stats, "all_to_all", dev)
     row_map = segment_row_map(plan, dev)
     out = _UnpackRows.apply(received, row_map, tuple(widths), tuple(f.dtype == torch.int32 for f in flat))
+    _mark(stats, "place", dev)
     sensor_ids, gaussian_ids = out[0], out[1]
     result = {}
     for k, f, o in zip(names, tensors, out[2:]):
@@ -331,6 +336,15 @@ def exchange_projected(
                      bytes_sent_off_rank=row_bytes * (n_send - plan.send_splits[rank]),
                      bytes_received_off_rank=row_bytes * (plan.src_start[-1] - plan.recv_splits[rank]))
     return result, sensor_ids, gaussian_ids, plan
+
+
+def _mark(stats: Optional[dict], name: str, device) -> None:
+    """With ``stats["time"]`` set, records a CUDA event named ``name`` on the current stream into
+    ``stats["marks"]``: the stage boundaries a benchmark turns into per-stage times."""
+    if stats is not None and stats.get("time"):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(torch.cuda.current_stream(device))
+        stats.setdefault("marks", []).append((name, ev))
 
 
 def _ordered(t: Optional[Tensor], order: Sequence[int]) -> Optional[Tensor]:
@@ -374,6 +388,7 @@ def rasterization_gaussian_sharded(
     if owners is None:
         owners = sensor_owners(C, world)
     order = sensor_send_order(owners)
+    _mark(stats, "start", dev)
     zeros = lambda *s: torch.zeros(*s, device=dev)  # noqa: E731
     viewmats_o, Ks_o = _ordered(viewmats, order), _ordered(Ks, order)
     lin = _ordered(linear_velocity if linear_velocity is not None else zeros(C, 3), order)
@@ -410,6 +425,7 @@ def rasterization_gaussian_sharded(
     opac_r = recv["opacities"].reshape(-1)
     isect = ops.isect_tiles_deferred(recv["means2d"], r_int, recv["depths"].reshape(-1), tile_size, tile_w, tile_h,
                                      packed=True, n_cameras=Cl, camera_ids=cam_local, gaussian_ids=gaussian_ids)
+    _mark(stats, "isect", dev)
     mine_t = torch.tensor(mine if mine else [0], dtype=torch.int64, device=dev)
     rs_mine = rs_all[mine_t]
     bg = None
@@ -427,6 +443,7 @@ def rasterization_gaussian_sharded(
 
     (render_colors, render_alphas), isect_ids, flatten_ids, offsets, tiles_per_gauss = _composite_with_count_check(
         isect, (tile_h, tile_w), composite)
+    _mark(stats, "composite", dev)
     if render_mode in ("ED", "RGB+ED"):
         render_colors = torch.cat(
             [render_colors[..., :-1], render_colors[..., -1:] / render_alphas.clamp(min=1e-10)], dim=-1)
@@ -470,6 +487,7 @@ def lidar_rasterization_gaussian_sharded(
     if owners is None:
         owners = sensor_owners(C, world)
     order = sensor_send_order(owners)
+    _mark(stats, "start", dev)
     zeros = lambda *s: torch.zeros(*s, device=dev)  # noqa: E731
     lin = _ordered(linear_velocity if linear_velocity is not None else zeros(C, 3), order)
     ang = _ordered(angular_velocity if angular_velocity is not None else zeros(C, 3), order)
@@ -503,6 +521,7 @@ def lidar_rasterization_gaussian_sharded(
     isect = ops.isect_lidar_tiles_deferred(recv["means2d"], recv["radii"], depths_r, tile_elevation_boundaries,
                                            tile_az, min_azimuth, packed=True, n_cameras=Cl, camera_ids=cam_local,
                                            gaussian_ids=gaussian_ids)
+    _mark(stats, "isect", dev)
 
     def composite(isect_offsets, flatten_ids, total_follows):
         return ops.rasterize_to_points_split(
@@ -513,6 +532,7 @@ def lidar_rasterization_gaussian_sharded(
 
     (feats_r, alphas, alpha_sum, median), isect_ids, flatten_ids, offsets, tiles_per_gauss = (
         _composite_with_count_check(isect, (n_el, n_az), composite))
+    _mark(stats, "composite", dev)
     meta = dict(sensor_ids=mine, camera_ids=cam_local, gaussian_ids=gaussian_ids, global_sensor_ids=sensor_ids,
                 means2d=recv["means2d"], radii=recv["radii"], depths=depths_r, conics=recv["conics"],
                 opacities=opac_r, pix_vels=recv["pix_vels"], tiles_per_gauss=tiles_per_gauss, isect_ids=isect_ids,

@@ -201,3 +201,33 @@ def test_batched_loop_reproduces_the_fused_render():
         # sits on 1/255 may be in one and not the other: 1e-3 of the pixels may differ
         assert_close(f"loop({per_iter}) colors", n(img), n(render), 1e-4, 2e-5, mask=sel, max_bad_frac=1e-3)
         assert_close(f"loop({per_iter}) alphas", n(acc), n(alphas), 1e-4, 2e-5, mask=sel, max_bad_frac=1e-3)
+
+
+def test_count_composited_pairs_against_the_oracle_counters():
+    """The pair counts behind the compositing flop model: the GPU count of evaluated and blended
+    (point, Gaussian) pairs of a frame equals the oracle's counters, up to the handful of pairs whose
+    threshold decision is within float32 rounding of flipping."""
+    import splatad_b200
+    from oracle import pipeline
+    from splatad_b200 import ops, scenes
+    cfg = scenes.config0(N=8000)
+    g = {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in cfg.items()}
+    _, _, _, m = splatad_b200.lidar_rasterization(**g)
+    tested, contributing = ops.count_composited_pairs(
+        m["means2d"], m["conics"], m["opacities"], m["pix_vels"], m["isect_offsets"], m["flatten_ids"],
+        m["width"], m["height"], m["tile_width"], m["tile_height"], raster_pts=g["raster_pts"])
+    _, _, _, meta = pipeline.lidar_rasterization(**cfg)
+    assert contributing > 10_000 and tested >= contributing
+    assert abs(tested - meta["tested"]) <= 2e-3 * meta["tested"], (tested, meta["tested"])
+    assert abs(contributing - meta["contributing"]) <= 2e-3 * meta["contributing"], (contributing, meta["contributing"])
+    cam = scenes.config1(N=5000)
+    cam.update(width=320, height=200)
+    cam["Ks"] = torch.tensor([[[250.0, 0.0, 160.0], [0.0, 250.0, 100.0], [0.0, 0.0, 1.0]]])
+    gc = {k: (v.to(DEV) if isinstance(v, torch.Tensor) else v) for k, v in cam.items()}
+    _, _, m = splatad_b200.rasterization(**gc)
+    tested, contributing = ops.count_composited_pairs(
+        m["means2d"], m["conics"], m["opacities"], m["pix_vels"], m["isect_offsets"], m["flatten_ids"],
+        m["width"], m["height"], m["tile_size"], m["tile_size"], rolling_shutter_time=gc["rolling_shutter_time"])
+    _, _, meta = pipeline.rasterization(**cam)
+    assert abs(tested - meta["tested"]) <= 2e-3 * meta["tested"], (tested, meta["tested"])
+    assert abs(contributing - meta["contributing"]) <= 2e-3 * meta["contributing"], (contributing, meta["contributing"])

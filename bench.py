@@ -572,7 +572,8 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     warmup = max(args.warmup, 3)
-    for _ in range(warmup):
+    for _ in range(warmup):          # the same loop body as the timed steps, L2 flush included
+        flush.zero_()
         out = step()
     torch.cuda.synchronize()
     n_isects = int(out[3]["flatten_ids"].numel())
@@ -585,6 +586,9 @@ def run_ours(args):
     ms_steps, host_ms, out = timed_frames(step, args.steps, flush)
     barrier()
     wall = time.perf_counter() - t_wall
+    if os.environ.get("SPLATAD_BENCH_VERBOSE"):
+        print(f"rank {rank}: first steps {[round(v, 3) for v in ms_steps[:12]]} median {np.median(ms_steps):.4f} "
+              f"mean {np.mean(ms_steps):.4f} host {host_ms:.4f}", file=sys.stderr)
     per_rank_ms = _all_ranks(float(np.mean(ms_steps)), world, dev)
     per_rank_host = _all_ranks(host_ms, world, dev)
     ms_per_step = max(per_rank_ms)

@@ -572,12 +572,15 @@ int splatad_rows_scatter(int64_t n_rows, const int32_t *index, int32_t n_fields,
                          int64_t *sensor_ids_out, int64_t *gaussian_ids_out, const void *in,
                          void *stream);
 
-/* Received rows arrive as n_segments contiguous segments, one per (source rank, sensor);
- * segment s begins at row src_start[s] of the receive buffer (ascending, device int64) and at
- * row dst_start[s] of the final (sensor, source rank) order. row_map[i] = final row of received
- * row i, for splatad_rows_scatter. */
-int splatad_segment_row_map(int32_t n_segments, const int64_t *src_start, const int64_t *dst_start,
-                            int64_t n_rows, int32_t *row_map, void *stream);
+/* Received rows arrive as n_segments <= 128 contiguous segments, one per (source rank, owned
+ * sensor) with the sensor index running fastest (n_sensors per source); segment s begins at row
+ * src_start[s] of the receive buffer (ascending) and at row dst_start[s] of the final (sensor,
+ * source rank) order. src_start / dst_start are HOST arrays read during the call. row_map[i] =
+ * final row of received row i, for splatad_rows_scatter; local_sensor_ids (optional, int64
+ * [n_rows]) receives, per FINAL row, the index of its sensor among the owned sensors. */
+int splatad_segment_row_map(int32_t n_segments, int32_t n_sensors, const int64_t *src_start,
+                            const int64_t *dst_start, int64_t n_rows, int32_t *row_map,
+                            int64_t *local_sensor_ids, void *stream);
 
 #ifdef __cplusplus
 }

@@ -165,19 +165,30 @@ rows_scatter_kernel(RowFields f, int64_t n_rows, const int32_t *__restrict__ ind
     }
 }
 
-// Received rows come as S contiguous segments; segment s starts at src_start[s] in the receive
-// buffer and at dst_start[s] in the final order. map[i] = final row of received row i.
+// Received rows come as S contiguous segments, one per (source rank, owned sensor) with the
+// sensor index running fastest; segment s starts at src_start[s] in the receive buffer and at
+// dst_start[s] in the final order. map[i] = final row of received row i; local_sensor[map[i]] =
+// s % n_sensors, the index of the row's sensor among the sensors this rank owns. The table travels
+// in the kernel's arguments (no copy to the device).
+constexpr int kMaxSegments = 128;
+struct SegmentTable {
+    int64_t src_start[kMaxSegments];
+    int64_t dst_start[kMaxSegments];
+};
+
 __global__ void __launch_bounds__(kThreads)
-segment_row_map_kernel(int32_t S, const int64_t *__restrict__ src_start,
-                       const int64_t *__restrict__ dst_start, int64_t n_rows, int32_t *__restrict__ map) {
+segment_row_map_kernel(const __grid_constant__ SegmentTable tab, int32_t S, int32_t n_sensors, int64_t n_rows,
+                       int32_t *__restrict__ map, int64_t *__restrict__ local_sensor) {
     const int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x;
     if (i >= n_rows) return;
     int32_t lo = 0, hi = S - 1;   // last segment whose start is <= i
     while (lo < hi) {
         const int32_t mid = (lo + hi + 1) >> 1;
-        if (__ldg(src_start + mid) <= i) lo = mid; else hi = mid - 1;
+        if (tab.src_start[mid] <= i) lo = mid; else hi = mid - 1;
     }
-    map[i] = (int32_t)(__ldg(dst_start + lo) + (i - __ldg(src_start + lo)));
+    const int64_t r = tab.dst_start[lo] + (i - tab.src_start[lo]);
+    map[i] = (int32_t)r;
+    if (local_sensor) local_sensor[r] = (int64_t)(lo % n_sensors);
 }
 
 static int fill_fields(RowFields &f, int32_t n_fields, const void *const *ptrs, const int32_t *widths,
@@ -293,17 +304,23 @@ extern "C" int splatad_rows_scatter(int64_t n_rows, const int32_t *index, int32_
     return check_launch("rows_scatter");
 }
 
-extern "C" int splatad_segment_row_map(int32_t n_segments, const int64_t *src_start, const int64_t *dst_start,
-                                       int64_t n_rows, int32_t *row_map, void *stream) {
+extern "C" int splatad_segment_row_map(int32_t n_segments, int32_t n_sensors, const int64_t *src_start,
+                                       const int64_t *dst_start, int64_t n_rows, int32_t *row_map,
+                                       int64_t *local_sensor_ids, void *stream) {
     SPL_REQUIRE(n_rows >= 0 && n_rows <= 0x7FFFFFFFll, SPLATAD_ERR_OVERFLOW,
                 "segment_row_map: %lld rows do not fit int32", (long long)n_rows);
     if (n_rows == 0) return SPLATAD_OK;
-    SPL_REQUIRE(n_segments > 0 && src_start && dst_start && row_map, SPLATAD_ERR_BAD_ARG,
-                "segment_row_map: null argument");
+    SPL_REQUIRE(n_segments > 0 && n_segments <= kMaxSegments && n_sensors > 0 && src_start && dst_start && row_map,
+                SPLATAD_ERR_BAD_ARG, "segment_row_map: 1..%d segments and their tables are required", kMaxSegments);
+    SegmentTable tab;
+    for (int s = 0; s < kMaxSegments; ++s) {
+        tab.src_start[s] = s < n_segments ? src_start[s] : 0x7FFFFFFFFFFFFFFFll;
+        tab.dst_start[s] = s < n_segments ? dst_start[s] : 0;
+    }
     {
         SPL_PROF("segment_row_map_kernel", (cudaStream_t)stream);
         segment_row_map_kernel<<<div_up(n_rows, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
-            n_segments, src_start, dst_start, n_rows, row_map);
+            tab, n_segments, n_sensors, n_rows, row_map, local_sensor_ids);
     }
     return check_launch("segment_row_map");
 }

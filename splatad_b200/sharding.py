@@ -272,18 +272,36 @@ class _UnpackRows(torch.autograd.Function):
         return v_rows, None, None, None
 
 
-def segment_row_map(plan: ExchangePlan, device) -> Tensor:
-    """int32 [n_received]: final row of every received row, from the plan's segment table."""
+def segment_row_map(plan: ExchangePlan, device) -> Tuple[Tensor, Tensor]:
+    """(row_map int32 [n_received]: final row of every received row; local_sensor_ids int64
+    [n_received]: per final row, the index of its sensor among the sensors this rank owns), from the
+    plan's segment table, which travels in the kernel's arguments."""
     from . import _lib
+    device = torch.device(device)
     n_rows = plan.src_start[-1]
     row_map = torch.empty(n_rows, dtype=torch.int32, device=device)
+    local_ids = torch.empty(n_rows, dtype=torch.int64, device=device)
     n_seg = len(plan.dst_start)
     if n_rows == 0 or n_seg == 0:
-        return row_map
-    table = torch.tensor([plan.src_start[:n_seg], plan.dst_start], dtype=torch.int64).to(device, non_blocking=True)
-    _lib.call("splatad_segment_row_map", n_seg, _lib.ptr(table[0]), _lib.ptr(table[1]), n_rows, _lib.ptr(row_map),
-              _lib.stream_ptr(torch.device(device)))
-    return row_map
+        return row_map, local_ids
+    src = (ctypes.c_int64 * n_seg)(*plan.src_start[:n_seg])
+    dst = (ctypes.c_int64 * n_seg)(*plan.dst_start)
+    _lib.call("splatad_segment_row_map", n_seg, max(len(plan.mine), 1), ctypes.addressof(src), ctypes.addressof(dst),
+              n_rows, _lib.ptr(row_map), _lib.ptr(local_ids), _lib.stream_ptr(device))
+    return row_map, local_ids
+
+
+_device_constants: Dict[tuple, Tensor] = {}
+
+
+def _device_ints(values: Sequence[int], dtype, device) -> Tensor:
+    """Small constant integer tables (sensor orders, owned sensor lists) on the device, uploaded once."""
+    key = (tuple(int(v) for v in values), dtype, str(device))
+    t = _device_constants.get(key)
+    if t is None:
+        t = torch.tensor(list(key[0]), dtype=dtype, device=device)
+        _device_constants[key] = t
+    return t
 
 
 def exchange_projected(
@@ -318,12 +336,12 @@ def exchange_projected(
     n_send = int(sum(counts[rank]))
     flat = [f.reshape(C * n_local, -1) for f in tensors]
     widths = [f.shape[1] for f in flat]
-    sensor_table = torch.tensor(list(order), dtype=torch.int32).to(dev, non_blocking=True)
+    sensor_table = _device_ints(order, torch.int32, dev)
     rows = _PackRows.apply(row_index, n_send, sensor_table, n_local, int(gaussian_start), *flat)
     _mark(stats, "pack", dev)
     received = exchange_rows(rows, plan.send_splits, plan.recv_splits, group)
     _mark(stats, "all_to_all", dev)
-    row_map = segment_row_map(plan, dev)
+    row_map, local_ids = segment_row_map(plan, dev)
     out = _UnpackRows.apply(received, row_map, tuple(widths), tuple(f.dtype == torch.int32 for f in flat))
     _mark(stats, "place", dev)
     sensor_ids, gaussian_ids = out[0], out[1]
@@ -350,12 +368,7 @@ def _mark(stats: Optional[dict], name: str, device) -> None:
 def _ordered(t: Optional[Tensor], order: Sequence[int]) -> Optional[Tensor]:
     if t is None or list(order) == list(range(len(order))):
         return t
-    return t[torch.as_tensor(list(order), dtype=torch.int64, device=t.device)]
-
-
-def _local_camera_ids(plan: ExchangePlan, device) -> Tensor:
-    counts = torch.tensor([b - a for a, b in zip(plan.sensor_start[:-1], plan.sensor_start[1:])], dtype=torch.int64)
-    return torch.repeat_interleave(torch.arange(len(plan.mine), dtype=torch.int64), counts).to(device, non_blocking=True)
+    return t[_device_ints(order, torch.int64, t.device)]
 
 
 def rasterization_gaussian_sharded(
@@ -419,14 +432,14 @@ def rasterization_gaussian_sharded(
                                                               stats)
     mine = plan.mine
     Cl = max(len(mine), 1)
-    cam_local = _local_camera_ids(plan, dev)
+    cam_local = recv["local_sensor_ids"]
     tile_w, tile_h = math.ceil(width / float(tile_size)), math.ceil(height / float(tile_size))
     r_int = recv["radii"]
     opac_r = recv["opacities"].reshape(-1)
     isect = ops.isect_tiles_deferred(recv["means2d"], r_int, recv["depths"].reshape(-1), tile_size, tile_w, tile_h,
                                      packed=True, n_cameras=Cl, camera_ids=cam_local, gaussian_ids=gaussian_ids)
     _mark(stats, "isect", dev)
-    mine_t = torch.tensor(mine if mine else [0], dtype=torch.int64, device=dev)
+    mine_t = _device_ints(mine if mine else [0], torch.int64, dev)
     rs_mine = rs_all[mine_t]
     bg = None
     if backgrounds is not None:
@@ -510,8 +523,8 @@ def lidar_rasterization_gaussian_sharded(
                                                               stats)
     mine = plan.mine
     Cl = max(len(mine), 1)
-    cam_local = _local_camera_ids(plan, dev)
-    mine_t = torch.tensor(mine if mine else [0], dtype=torch.int64, device=dev)
+    cam_local = recv["local_sensor_ids"]
+    mine_t = _device_ints(mine if mine else [0], torch.int64, dev)
     pts = raster_pts[mine_t].contiguous()
     n_el = math.ceil(n_elevation_channels / tile_height)
     tile_az = azimuth_resolution * tile_width

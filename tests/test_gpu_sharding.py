@@ -100,12 +100,13 @@ def _emulated_ranks(ops, sharding):
         starts = [[sum(sharding.plan_exchange(counts, order, owners, s).send_splits[:k]) for k in range(world)]
                   for s in range(world)]
         received = torch.cat([sends[s][starts[s][d]: starts[s][d] + plan.recv_splits[s]] for s in range(world)])
-        row_map = sharding.segment_row_map(plan, DEV)
+        row_map, local_ids = sharding.segment_row_map(plan, DEV)
         assert torch.equal(torch.sort(row_map).values, torch.arange(received.shape[0], device=DEV, dtype=torch.int32))
         sid, gid, radii, means2d, depths, conics, pix_vels = sharding._UnpackRows.apply(
             received, row_map, (2, 2, 1, 3, 2), (True, False, False, False, False))
         keep = listed & torch.isin(cam, torch.tensor(plan.mine, device=DEV))
         assert torch.equal(sid, cam[keep]) and torch.equal(gid, gau[keep])
+        assert torch.equal(torch.tensor(plan.mine, device=DEV)[local_ids], sid)
         assert torch.equal(radii, p_radii[keep]) and torch.equal(means2d, p_means2d[keep])
         assert torch.equal(depths[:, 0], p_depths[keep]) and torch.equal(conics, p_conics[keep])
         assert torch.equal(pix_vels, p_vels[keep])

@@ -531,6 +531,38 @@ int splatad_compute_relocation(uint32_t N, const float *opacities, const float *
                                float *new_opacities, float *new_scales, void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Whole frame in one call
+ * ---------------------------------------------------------------------------------------- */
+
+/* The forward pass of lidar_rasterization (gsplat/rendering.py:443-819, classic mode, quats /
+ * scales, D + 1 <= 32 channels) as ONE call: splatad_lidar_projection_fwd,
+ * splatad_isect_lidar_tiles_plan / _fill at the given `capacity` and
+ * splatad_rasterize_to_points_fwd (range channel taken from `depths`) enqueued back to back on
+ * `stream` - same kernels, same results, one crossing of the language boundary per frame.
+ * opacities_cn is [C, N] (the per-sensor opacities the compositing reads); lidar_features
+ * [C, N, D]; every output, intermediate and workspace is the caller's: radii .. tiles_per_gauss as
+ * in the projection / plan calls, isect_ids / flatten_ids [capacity], tile_offsets
+ * [C * tiles + 1], images [C, H, W, .]. host_counts (pinned, 4 x int64) receives
+ * {n_isects, n_visible, status, 0} once the stream has passed the plan: if n_isects > capacity the
+ * lists and images are incomplete and the frame has to be repeated with more room. count_event
+ * (optional cudaEvent_t) is recorded on the stream right behind the plan, so that the host can wait
+ * for the counts alone while fill and compositing are still running. */
+int splatad_lidar_frame_fwd(
+    uint32_t C, uint32_t N, const float *means, const float *quats, const float *scales,
+    const float *velocities, const float *opacities_cn, const float *lidar_features, uint32_t n_features,
+    const float *viewmats, const float *linear_velocity, const float *angular_velocity,
+    const float *rolling_shutter_time, const float *raster_pts, uint32_t image_width, uint32_t image_height,
+    const float *elev_boundaries, uint32_t n_boundaries, float azimuth_resolution, uint32_t tile_width,
+    uint32_t tile_height, float min_azimuth, float max_azimuth, float min_elevation, float max_elevation,
+    float eps2d, float near_plane, float far_plane, float radius_clip, int32_t compute_alpha_sum,
+    float alpha_sum_threshold, float *radii, float *means2d, float *depths, float *conics, float *pix_vels,
+    float *depth_compensations, int32_t *tiles_per_gauss, int64_t capacity, int64_t *isect_ids,
+    int32_t *flatten_ids, int32_t *tile_offsets, float *render_features, float *render_alphas,
+    float *alpha_sum_until_points, int32_t *last_ids, float *median_depths, void *plan_workspace,
+    size_t plan_workspace_bytes, void *fill_workspace, size_t fill_workspace_bytes, int64_t *host_counts,
+    void *count_event, void *stream);
+
+/* ------------------------------------------------------------------------------------------
  * Gaussian-sharded exchange (one process per GPU): every rank projects its slice of the Gaussians
  * for all sensors and sends the visible (sensor, Gaussian) records to the rank owning the sensor.
  * The reference leaves this to torch code around its collectives (gsplat/distributed.py:170-257:

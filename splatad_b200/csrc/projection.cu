@@ -57,6 +57,40 @@ __device__ __forceinline__ SensorLidar load_lidar(const float *viewmats, const f
     return s;
 }
 
+// Symmetric 3x3 (upper triangle). The forward kernels carry covariances in this form: only six
+// entries are ever computed, and the congruences A S A^T below produce only the entries their
+// callers read.
+struct Sym3 { float xx, xy, xz, yy, yz, zz; };
+
+__device__ __forceinline__ Sym3 to_sym(const M3 &m) {
+    Sym3 s;
+    s.xx = m.m[0][0]; s.xy = m.m[0][1]; s.xz = m.m[0][2];
+    s.yy = m.m[1][1]; s.yz = m.m[1][2]; s.zz = m.m[2][2];
+    return s;
+}
+
+// row^T S for a symmetric S
+__device__ __forceinline__ V3 row_times_sym(V3 r, const Sym3 &S) {
+    return v3(r.x * S.xx + r.y * S.xy + r.z * S.xz, r.x * S.xy + r.y * S.yy + r.z * S.yz,
+              r.x * S.xz + r.y * S.yz + r.z * S.zz);
+}
+
+// R S R^T (sensor-frame covariance), upper triangle
+__device__ __forceinline__ Sym3 rotate_sym(const M3 &R, const Sym3 &S) {
+    const V3 r0 = v3(R.m[0][0], R.m[0][1], R.m[0][2]);
+    const V3 r1 = v3(R.m[1][0], R.m[1][1], R.m[1][2]);
+    const V3 r2 = v3(R.m[2][0], R.m[2][1], R.m[2][2]);
+    const V3 t0 = row_times_sym(r0, S), t1 = row_times_sym(r1, S), t2 = row_times_sym(r2, S);
+    Sym3 o;
+    o.xx = dot(t0, r0); o.xy = dot(t0, r1); o.xz = dot(t0, r2);
+    o.yy = dot(t1, r1); o.yz = dot(t1, r2); o.zz = dot(t2, r2);
+    return o;
+}
+
+// One reciprocal (two units in the last place) where the result scales an output that is compared
+// with a tolerance, never a quantity that decides culling or a tile rectangle.
+__device__ __forceinline__ float fast_rcp(float x) { return __fdividef(1.f, x); }
+
 struct CamProj {
     bool valid;
     float ex, ey;   // extents (float, before int truncation)
@@ -67,42 +101,80 @@ struct CamProj {
     V2 pix_vel;
 };
 
-__device__ __forceinline__ CamProj project_cam(const SensorCam &s, V3 mean, const M3 &covar,
-                                               bool has_vel, V3 vel_w, int width, int height,
-                                               float eps2d, float near_plane, float far_plane,
-                                               float radius_clip) {
+// Per-sensor constants of the pinhole projection (the clamp limits of x/z, y/z need 1/fx, 1/fy).
+struct CamLimits { float x_pos, x_neg, y_pos, y_neg; };
+
+__device__ __forceinline__ CamLimits cam_limits(const Intrin &K, int width, int height) {
+    const float rfx = 1.f / K.fx, rfy = 1.f / K.fy;
+    const float tan_fovx = 0.5f * (float)width * rfx, tan_fovy = 0.5f * (float)height * rfy;
+    CamLimits l;
+    l.x_pos = ((float)width - K.cx) * rfx + 0.3f * tan_fovx;
+    l.x_neg = K.cx * rfx + 0.3f * tan_fovx;
+    l.y_pos = ((float)height - K.cy) * rfy + 0.3f * tan_fovy;
+    l.y_neg = K.cy * rfy + 0.3f * tan_fovy;
+    return l;
+}
+
+// Forward pinhole projection of one Gaussian. Same steps as persp_proj / add_blur / inverse2 of
+// splat_math.cuh (gsplat/cuda/csrc/utils.cuh:190-279, 491-550), written for the forward kernels:
+// symmetric covariances, the Jacobian's zeros never multiplied, one reciprocal of the blurred
+// determinant shared by the conic and the compensation, one of the depth shared by mean and
+// Jacobian. Radii and the culling comparisons keep correctly rounded sqrt / reciprocal.
+__device__ __forceinline__ CamProj project_cam(const SensorCam &s, const CamLimits &lim, V3 mean,
+                                               const Sym3 &covar, bool has_vel, V3 vel_w, int width,
+                                               int height, float eps2d, float near_plane,
+                                               float far_plane, float radius_clip) {
     CamProj o;
     o.valid = false;
     o.ex = o.ey = 0.f; o.mean2d = v2(0.f, 0.f); o.depth = 0.f;
     o.conic[0] = o.conic[1] = o.conic[2] = 0.f; o.comp = 0.f; o.pix_vel = v2(0.f, 0.f);
 
-    V3 p = mul(s.pose.R, mean) + s.pose.t;
+    const V3 p = mul(s.pose.R, mean) + s.pose.t;
     if (p.z < near_plane || p.z > far_plane) return o;
-    M3 covar_c = covar_world_to_cam(s.pose.R, covar);
-    M2 cov2d; V2 m2d; PerspJ J;
-    persp_proj(p, covar_c, s.K, width, height, cov2d, m2d, J);
-    float comp;
-    float det = add_blur(eps2d, cov2d, comp);
+    // everything that needs the sensor's pose and motion first, so that they are dead below
+    const bool rolling = s.rs_time > 0.f;
+    V3 tv = v3(0.f, 0.f, 0.f);   // velocity of the point relative to the sensor, sensor frame
+    if (rolling) {
+        tv = s.lin + cross(s.ang, p);
+        if (has_vel) tv = tv - mul(s.pose.R, vel_w);
+    }
+    const Sym3 S = rotate_sym(s.pose.R, covar);
+    const float rz = __frcp_rn(p.z);
+    const float xr = p.x * rz, yr = p.y * rz;
+    const float tx = p.z * fminf(lim.x_pos, fmaxf(-lim.x_neg, xr));
+    const float ty = p.z * fminf(lim.y_pos, fmaxf(-lim.y_neg, yr));
+    const float rz2 = rz * rz;
+    const float j00 = s.K.fx * rz, j11 = s.K.fy * rz;
+    const float j02 = -s.K.fx * tx * rz2, j12 = -s.K.fy * ty * rz2;
+    // rows of J: [j00 0 j02], [0 j11 j12]
+    const float a0 = j00 * S.xx + j02 * S.xz, a1 = j00 * S.xy + j02 * S.yz, a2 = j00 * S.xz + j02 * S.zz;
+    const float b1 = j11 * S.yy + j12 * S.yz, b2 = j11 * S.yz + j12 * S.zz;
+    const float c00 = a0 * j00 + a2 * j02;
+    const float c01 = a1 * j11 + a2 * j12;
+    const float c11 = b1 * j11 + b2 * j12;
+    const float det_orig = c00 * c11 - c01 * c01;
+    const float A = c00 + eps2d, B = c11 + eps2d;
+    const float det = A * B - c01 * c01;
     if (!(det > 0.f)) return o;
-    float ex = 3.f * sqrtf(cov2d.m[0][0]);
-    float ey = 3.f * sqrtf(cov2d.m[1][1]);
+    float ex = 3.f * sqrtf(A);
+    float ey = 3.f * sqrtf(B);
     if (ex <= radius_clip && ey <= radius_clip) return o;
+    const V2 m2d = v2(s.K.fx * xr + s.K.cx, s.K.fy * yr + s.K.cy);
     V2 pv = v2(0.f, 0.f);
-    if (s.rs_time > 0.f) {
-        V3 vel_c = has_vel ? mul(s.pose.R, vel_w) : v3(0.f, 0.f, 0.f);
-        pv = compute_pix_velocity(p, s.lin, s.ang, vel_c, J);
+    if (rolling) {
+        pv = v2(-(j00 * tv.x + j02 * tv.z), -(j11 * tv.y + j12 * tv.z));
         ex += fabsf(pv.x) * 0.5f * s.rs_time;
         ey += fabsf(pv.y) * 0.5f * s.rs_time;
     }
     if (m2d.x + ex <= 0.f || m2d.x - ex >= (float)width || m2d.y + ey <= 0.f ||
         m2d.y - ey >= (float)height)
         return o;
-    M2 inv;
-    inverse2(cov2d, det, inv);
+    const float inv_det = fast_rcp(det);
     o.valid = true;
     o.ex = ex; o.ey = ey; o.mean2d = m2d; o.depth = p.z;
-    o.conic[0] = inv.m[0][0]; o.conic[1] = inv.m[0][1]; o.conic[2] = inv.m[1][1];
-    o.comp = comp; o.pix_vel = pv;
+    o.conic[0] = B * inv_det; o.conic[1] = -c01 * inv_det; o.conic[2] = A * inv_det;
+    o.comp = sqrtf(fmaxf(0.f, det_orig * inv_det));
+    o.pix_vel = pv;
     return o;
 }
 
@@ -117,7 +189,16 @@ struct LidarProj {
     V2 depth_comp;
 };
 
-__device__ __forceinline__ LidarProj project_lidar(const SensorLidar &s, V3 mean, const M3 &covar,
+// Forward spherical projection of one Gaussian: the steps of lidar_proj / lidar_jacobian /
+// depth_compensation_from_cov3d / add_blur / inverse2 of splat_math.cuh
+// (gsplat/cuda/csrc/utils.cuh:12-31, 281-318, 491-550) with the work that only the forward pass
+// allows taken out: two reciprocal square roots (1/r, 1/sqrt(x^2 + y^2)) give every quotient of
+// the Jacobian; of J Sigma J^T only the 2x2 angular block and the two range-angle entries are
+// formed (the range row of J Sigma is never needed: by symmetry both entries are products of the
+// angular rows of J Sigma with the range row of J); the blurred determinant's reciprocal is shared
+// by the conic, the compensation and the depth compensation. Range, radii and every culling
+// comparison keep correctly rounded arithmetic.
+__device__ __forceinline__ LidarProj project_lidar(const SensorLidar &s, V3 mean, const Sym3 &covar,
                                                    bool has_vel, V3 vel_w, float min_el,
                                                    float max_el, float min_az, float max_az,
                                                    float eps2d, float near_plane, float far_plane,
@@ -128,33 +209,56 @@ __device__ __forceinline__ LidarProj project_lidar(const SensorLidar &s, V3 mean
     o.conic[0] = o.conic[1] = o.conic[2] = 0.f; o.comp = 0.f;
     o.pix_vel = v3(0.f, 0.f, 0.f); o.depth_comp = v2(0.f, 0.f);
 
-    V3 p = mul(s.pose.R, mean) + s.pose.t;
-    float dist = spl_norm3(p.x, p.y, p.z);
+    const V3 p = mul(s.pose.R, mean) + s.pose.t;
+    const float s2 = p.x * p.x + p.y * p.y;
+    const float r2 = s2 + p.z * p.z;
+    const float dist = sqrtf(r2);
     if (dist < near_plane || dist > far_plane) return o;
-    M3 covar_c = covar_world_to_cam(s.pose.R, covar);
-    M2 cov2d; V2 m2d; V2 dc; M3 J;
-    lidar_proj(p, covar_c, eps2d, m2d, cov2d, dc, J);
-    float comp;
-    float det = add_blur(eps2d, cov2d, comp);
+    // everything that needs the sensor's pose and motion first, so that they are dead below
+    const bool rolling = s.rs_time > 0.f;
+    V3 tv = v3(0.f, 0.f, 0.f);   // velocity of the point relative to the sensor, sensor frame
+    if (rolling) {
+        tv = s.lin + cross(s.ang, p);
+        if (has_vel) tv = tv - mul(s.pose.R, vel_w);
+    }
+    const Sym3 S = rotate_sym(s.pose.R, covar);
+    const float rinv = rsqrtf(r2), sinv = rsqrtf(s2);
+    const float inv_s2 = sinv * sinv, inv_r2 = rinv * rinv, sxy = s2 * sinv;
+    // rows of J (degrees): azimuth [ja0 ja1 0], elevation [jb0 jb1 jb2], range c = p / r
+    const float ka = inv_s2 * kRadToDeg;
+    const float ja0 = -p.y * ka, ja1 = p.x * ka;
+    const float kb = inv_r2 * sinv * kRadToDeg;
+    const float jb0 = -p.x * p.z * kb, jb1 = -p.y * p.z * kb, jb2 = sxy * inv_r2 * kRadToDeg;
+    const V3 c = v3(p.x * rinv, p.y * rinv, p.z * rinv);
+    const V3 ta = v3(ja0 * S.xx + ja1 * S.xy, ja0 * S.xy + ja1 * S.yy, ja0 * S.xz + ja1 * S.yz);
+    const V3 tb = row_times_sym(v3(jb0, jb1, jb2), S);
+    const float c00 = ta.x * ja0 + ta.y * ja1;
+    const float c01 = ta.x * jb0 + ta.y * jb1 + ta.z * jb2;
+    const float c11 = tb.x * jb0 + tb.y * jb1 + tb.z * jb2;
+    const float cr0 = dot(ta, c), cr1 = dot(tb, c);   // range-azimuth, range-elevation covariance
+    const float det_orig = c00 * c11 - c01 * c01;
+    const float A = c00 + eps2d, B = c11 + eps2d;
+    const float det = A * B - c01 * c01;
     if (!(det > 0.f)) return o;
-    float ex = 3.f * sqrtf(fmaxf(0.f, cov2d.m[0][0]));
-    float ey = 3.f * sqrtf(fmaxf(0.f, cov2d.m[1][1]));
+    float ex = 3.f * sqrtf(fmaxf(0.f, A));
+    float ey = 3.f * sqrtf(fmaxf(0.f, B));
     if (ex <= radius_clip && ey <= radius_clip) return o;
     V3 pv = v3(0.f, 0.f, 0.f);
-    if (s.rs_time > 0.f) {
-        V3 vel_c = has_vel ? mul(s.pose.R, vel_w) : v3(0.f, 0.f, 0.f);
-        pv = compute_lidar_velocity(p, s.lin, s.ang, vel_c, J);
+    if (rolling) {
+        pv = v3(-(ja0 * tv.x + ja1 * tv.y), -(jb0 * tv.x + jb1 * tv.y + jb2 * tv.z), -dot(c, tv));
         ex += fabsf(pv.x) * 0.5f * s.rs_time;
         ey += fabsf(pv.y) * 0.5f * s.rs_time;
     }
+    const V2 m2d = v2(atan2f(p.y, p.x) * kRadToDeg, asinf(p.z * rinv) * kRadToDeg);
     if (m2d.y + ey <= min_el || m2d.y - ey >= max_el || m2d.x + ex <= min_az || m2d.x - ex >= max_az)
         return o;
-    M2 inv;
-    inverse2(cov2d, det, inv);
+    const float inv_det = fast_rcp(det);
     o.valid = true;
     o.ex = ex; o.ey = ey; o.mean2d = m2d; o.depth = dist;
-    o.conic[0] = inv.m[0][0]; o.conic[1] = inv.m[0][1]; o.conic[2] = inv.m[1][1];
-    o.comp = comp; o.pix_vel = pv; o.depth_comp = dc;
+    o.conic[0] = B * inv_det; o.conic[1] = -c01 * inv_det; o.conic[2] = A * inv_det;
+    o.comp = sqrtf(fmaxf(0.f, det_orig * inv_det));
+    o.pix_vel = pv;
+    o.depth_comp = v2((c01 * cr1 - B * cr0) * inv_det, (c01 * cr0 - A * cr1) * inv_det);
     return o;
 }
 
@@ -214,7 +318,7 @@ __device__ __forceinline__ GaussIn load_gaussian(const float *__restrict__ means
 // ---------------------------------------------------------------------------------------
 // Lidar forward
 // ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, 4)
 lidar_projection_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ means,
                             const float *__restrict__ covars, const float *__restrict__ quats,
                             const float *__restrict__ scales, const float *__restrict__ velocities,
@@ -232,10 +336,11 @@ lidar_projection_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ me
     const uint32_t t = threadIdx.x;
     const bool live = t < n;
     GaussIn in = load_gaussian<false>(means, covars, quats, scales, velocities, N, g0, smem);
+    const Sym3 covar = to_sym(in.covar);
 
     for (uint32_t c = 0; c < C; ++c) {
         SensorLidar s = load_lidar(viewmats, lin_vel, ang_vel, rs_time, c);
-        LidarProj o = project_lidar(s, in.mean, in.covar, velocities != nullptr, in.vel, min_el,
+        LidarProj o = project_lidar(s, in.mean, covar, velocities != nullptr, in.vel, min_el,
                                     max_el, min_az, max_az, eps2d, near_plane, far_plane,
                                     radius_clip);
         const size_t base = (size_t)c * N + g0;
@@ -278,11 +383,12 @@ projection_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ means,
     const uint32_t t = threadIdx.x;
     const bool live = t < n;
     GaussIn in = load_gaussian<false>(means, covars, quats, scales, velocities, N, g0, smem);
+    const Sym3 covar = to_sym(in.covar);
 
     for (uint32_t c = 0; c < C; ++c) {
         SensorCam s = load_cam(viewmats, Ks, lin_vel, ang_vel, rs_time, c);
-        CamProj o = project_cam(s, in.mean, in.covar, velocities != nullptr, in.vel, width, height,
-                                eps2d, near_plane, far_plane, radius_clip);
+        CamProj o = project_cam(s, cam_limits(s.K, width, height), in.mean, covar, velocities != nullptr, in.vel,
+                                width, height, eps2d, near_plane, far_plane, radius_clip);
         const size_t base = (size_t)c * N + g0;
         if (live) {
             const size_t i = base + t;
@@ -328,11 +434,12 @@ projection_packed_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ m
     const bool live = t < n;
     const uint32_t lane = t & 31, warp = t >> 5;
     GaussIn in = load_gaussian<false>(means, covars, quats, scales, velocities, N, g0, smem);
+    const Sym3 covar = to_sym(in.covar);
 
     for (uint32_t c = 0; c < C; ++c) {
         SensorCam s = load_cam(viewmats, Ks, lin_vel, ang_vel, rs_time, c);
-        CamProj o = project_cam(s, in.mean, in.covar, velocities != nullptr, in.vel, width, height,
-                                eps2d, near_plane, far_plane, radius_clip);
+        CamProj o = project_cam(s, cam_limits(s.K, width, height), in.mean, covar, velocities != nullptr, in.vel,
+                                width, height, eps2d, near_plane, far_plane, radius_clip);
         const bool vis = live && o.valid;
         const uint32_t ballot = __ballot_sync(0xffffffffu, vis);
         if (lane == 0) warp_counts[warp] = __popc(ballot);

@@ -1073,6 +1073,97 @@ def _n_isects_arg(isect_offsets: Tensor, flatten_ids: Tensor, total_follows: boo
     return -1
 
 
+class LidarFrame:
+    """A lidar frame enqueued by :func:`lidar_frame_fwd`: the outputs are on their way, the
+    intersection count arrives in a pinned slot. ``finish()`` waits for the count and returns the
+    exact-length (isect_ids, flatten_ids), or None when the count outgrew the room the frame was
+    given (the frame then has to be rendered the ordinary way)."""
+
+    def __init__(self, tensors, capacity, counted, slot, key):
+        self.__dict__.update(tensors)
+        self._capacity, self._counted, self._slot, self._key = capacity, counted, slot, key
+
+    def finish(self):
+        self._counted.synchronize()
+        n_isects, status = int(self._slot[0]), int(self._slot[2])
+        _lib.release_pinned_slot(self._slot)
+        if status & 2 or n_isects > 0x7FFFFFFF:
+            raise RuntimeError(f"isect: {n_isects} intersections do not fit int32 flatten ids / offsets")
+        _isect_count_hint[self._key] = n_isects
+        if n_isects > self._capacity:
+            return None
+        isect_ids = self.isect_buf[:n_isects]
+        isect_ids._splatad_tile_offsets = (self.C, self.offsets_buf[:-1])
+        return isect_ids, self.flatten_buf[:n_isects]
+
+
+@torch.no_grad()
+def lidar_frame_fwd(means, quats, scales, velocities, opacities_cn, lidar_features, viewmats, linear_velocity,
+                    angular_velocity, rolling_shutter_time, raster_pts, tile_elevation_boundaries,
+                    azimuth_resolution, tile_width, tile_height, min_azimuth, max_azimuth, min_elevation,
+                    max_elevation, eps2d, near_plane, far_plane, radius_clip, compute_alpha_sum,
+                    alpha_sum_threshold, expected_grid=None) -> Optional["LidarFrame"]:
+    """Forward pass of a whole lidar frame (projection, tile intersection, compositing) through ONE
+    library call (``splatad_lidar_frame_fwd``), for frames that need no gradients: the host work
+    between the 22 launches of a frame, not the GPU, is what limits the frame rate of small frames.
+    Needs the intersection count of an earlier frame of the same shape on this stream to size the
+    lists (returns None when there is none yet: render that frame with the individual ops).
+    Not part of the reference's API; used by ``splatad_b200.lidar_rasterization``."""
+    C, N = viewmats.shape[0], means.shape[0]
+    D = lidar_features.shape[-1]
+    dev = means.device
+    if C * N == 0 or D + 1 > _lib.MAX_CHANNELS:
+        return None
+    lib = _lib.load()
+    eb = _f(tile_elevation_boundaries)
+    n_rows = int(eb.numel()) - 1
+    tile_az = float(azimuth_resolution) * int(tile_width)
+    n_cols = int(lib.splatad_lidar_azimuth_tiles(tile_az))
+    if expected_grid is not None and tuple(expected_grid) != (n_rows, n_cols):
+        return None   # the caller's tile grid is not the one the intersection builds
+    n_tiles_total = C * n_cols * n_rows
+    stream = _lib.stream_ptr(dev)
+    key = ("lidar_tiles", C, N, C * N, n_tiles_total, dev.index, int(stream))
+    hint = _isect_count_hint.get(key)
+    if hint is None:
+        return None
+    capacity = hint + hint // 8 + 65536
+    H, W = raster_pts.shape[1:3]
+    f32 = dict(dtype=torch.float32, device=dev)
+    i32 = dict(dtype=torch.int32, device=dev)
+    t = dict(
+        C=C, grid=(n_rows, n_cols),
+        radii=torch.empty((C, N, 2), **f32), means2d=torch.empty((C, N, 2), **f32),
+        depths=torch.empty((C, N), **f32), conics=torch.empty((C, N, 3), **f32),
+        pix_vels=torch.empty((C, N, 3), **f32), depth_compensations=torch.empty((C, N, 2), **f32),
+        tiles_per_gauss=torch.empty((C, N), **i32),
+        isect_buf=torch.empty(capacity, dtype=torch.int64, device=dev), flatten_buf=torch.empty(capacity, **i32),
+        offsets_buf=torch.empty(n_tiles_total + 1, **i32),
+        render=torch.empty((C, H, W, D + 1), **f32), alphas=torch.empty((C, H, W, 1), **f32),
+        alpha_sum=torch.empty((C, H, W, 1), **f32) if compute_alpha_sum else None,
+        last_ids=torch.empty((C, H, W), **i32), median_depths=torch.empty((C, H, W, 1), **f32),
+    )
+    plan_ws = _lib.workspace("isect_plan", lib.splatad_isect_plan_workspace_bytes(C * N), dev)
+    fill_ws = _lib.workspace("isect_fill", lib.splatad_isect_fill_workspace_bytes(capacity), dev)
+    slot = _lib.acquire_pinned_slot()
+    # the library records this event again behind the plan stage (an event has to have been recorded
+    # once to exist); waiting on it then waits for the counts only
+    counted = torch.cuda.Event()
+    counted.record(torch.cuda.current_stream(dev))
+    p = _lib.ptr
+    _call("splatad_lidar_frame_fwd", C, N, p(_f(means)), p(_f(quats)), p(_f(scales)), p(_f(velocities)),
+          p(_f(opacities_cn)), p(_f(lidar_features)), D, p(_f(viewmats)), p(_f(linear_velocity)),
+          p(_f(angular_velocity)), p(_f(rolling_shutter_time)), p(_f(raster_pts)), W, H, p(eb), n_rows + 1,
+          float(azimuth_resolution), int(tile_width), int(tile_height), float(min_azimuth), float(max_azimuth),
+          float(min_elevation), float(max_elevation), float(eps2d), float(near_plane), float(far_plane),
+          float(radius_clip), int(bool(compute_alpha_sum)), float(alpha_sum_threshold), p(t["radii"]),
+          p(t["means2d"]), p(t["depths"]), p(t["conics"]), p(t["pix_vels"]), p(t["depth_compensations"]),
+          p(t["tiles_per_gauss"]), capacity, p(t["isect_buf"]), p(t["flatten_buf"]), p(t["offsets_buf"]),
+          p(t["render"]), p(t["alphas"]), p(t["alpha_sum"]), p(t["last_ids"]), p(t["median_depths"]),
+          p(plan_ws), plan_ws.numel(), p(fill_ws), fill_ws.numel(), slot.data_ptr(), counted.cuda_event, stream)
+    return LidarFrame(t, capacity, counted, slot, key)
+
+
 @torch.no_grad()
 def isect_tiles(
     means2d: Tensor,  # [C, N, 2] or [nnz, 2]

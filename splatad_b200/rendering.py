@@ -21,6 +21,7 @@ except ImportError:  # pragma: no cover
 
 from .ops import (
     PendingPackedCount,
+    lidar_frame_fwd,
     camera_centers,
     fully_fused_lidar_projection,
     fully_fused_projection,
@@ -300,6 +301,36 @@ def lidar_rasterization(
         raise NotImplementedError("Packed mode is not supported for lidar_rasterization")
     linear_velocity, angular_velocity, rolling_shutter_time = _sensor_motion(
         C, means.device, linear_velocity, angular_velocity, rolling_shutter_time)
+
+    # A frame that needs no gradients, fits one compositing launch and has a predecessor of its shape
+    # goes through one library call that enqueues all of it (same kernels, same results).
+    needs_grad = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad
+        for t in (means, quats, scales, opacities, lidar_features, velocities, viewmats))
+    if (not needs_grad and rasterize_mode == "classic" and use_depth_compensation
+            and lidar_features.shape[-1] + 1 <= min(channel_chunk, 32) and N > 0 and C > 0
+            and raster_pts.shape[1] * raster_pts.shape[2] > 0):
+        frame = lidar_frame_fwd(
+            means, quats, scales, velocities, opacities[None] if C == 1 else opacities.repeat(C, 1),
+            lidar_features, viewmats, linear_velocity, angular_velocity, rolling_shutter_time, raster_pts,
+            tile_elevation_boundaries, azimuth_resolution, tile_width, tile_height, min_azimuth, max_azimuth,
+            min_elevation, max_elevation, eps2d, near_plane, far_plane, radius_clip,
+            compute_alpha_sum_until_points, compute_alpha_sum_until_points_threshold,
+            expected_grid=(n_elevation_tiles,
+                           math.ceil((max_azimuth - min_azimuth) / (azimuth_resolution * tile_width))))
+        lists = frame.finish() if frame is not None else None
+        if lists is not None:
+            n_elevation_tiles_, n_azimuth_tiles_ = frame.grid
+            meta = dict(
+                camera_ids=None, gaussian_ids=None, radii=frame.radii, means2d=frame.means2d, depths=frame.depths,
+                conics=frame.conics, opacities=opacities[None] if C == 1 else opacities.repeat(C, 1),
+                pix_vels=frame.pix_vels, tile_grid_width=n_azimuth_tiles_, tile_grid_height=n_elevation_tiles_,
+                tiles_per_gauss=frame.tiles_per_gauss, isect_ids=lists[0], flatten_ids=lists[1],
+                isect_offsets=frame.offsets_buf[:-1].view(C, n_elevation_tiles_, n_azimuth_tiles_),
+                width=raster_pts.shape[-2], height=raster_pts.shape[-3], tile_width=tile_width,
+                tile_height=tile_height, n_cameras=C, median_depths=frame.median_depths,
+            )
+            return frame.render, frame.alphas, frame.alpha_sum, meta
 
     radii, means2d, depths, conics, compensations, pix_vels, depth_compensations = fully_fused_lidar_projection(
         means, None, quats, scales, velocities, viewmats, linear_velocity, angular_velocity,

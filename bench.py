@@ -571,16 +571,19 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # the clock sampler's start-up (NVML initialisation, first queries) happens during the warm-up,
+    # not inside the first timed steps; it keeps sampling through both timed regions
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     warmup = max(args.warmup, 3)
     for _ in range(warmup):          # the same loop body as the timed steps, L2 flush included
         flush.zero_()
         out = step()
     torch.cuda.synchronize()
     n_isects = int(out[3]["flatten_ids"].numel())
+    del out     # a third live set of frame outputs would make the allocator fetch fresh memory in a timed step
 
     # ---- device-resident timing: per-step CUDA events, L2 flushed between steps ----------------
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     barrier()
     t_wall = time.perf_counter()
     ms_steps, host_ms, out = timed_frames(step, args.steps, flush)

@@ -315,8 +315,8 @@ def exchange_projected(
 ) -> Tuple[Dict[str, Tensor], Tensor, Tensor, ExchangePlan]:
     """Routes the visible records to the ranks owning their sensors.
 
-    Returns ``(received, sensor_ids, gaussian_ids, plan)``: for every field (and ``"radii"``) a
-    ``[nnz_r, ...]`` tensor of the rows this rank received, ordered by (global sensor id, global
+    Returns ``(received, sensor_ids, gaussian_ids, plan)``: for every field (and ``"radii"``, plus
+    ``"local_sensor_ids"``, int64) a ``[nnz_r, ...]`` tensor of the rows this rank received, ordered by (global sensor id, global
     Gaussian id) - the packed layout of a single-GPU run restricted to this rank's sensors -, the
     int64 global sensor / Gaussian ids of the rows, and the exchange plan. Differentiable with
     respect to every float field. ``stats`` (optional dict) receives the bytes put on the wire.
@@ -353,6 +353,7 @@ def exchange_projected(
         stats.update(row_bytes=row_bytes, rows_sent=n_send, rows_received=plan.src_start[-1],
                      bytes_sent_off_rank=row_bytes * (n_send - plan.send_splits[rank]),
                      bytes_received_off_rank=row_bytes * (plan.src_start[-1] - plan.recv_splits[rank]))
+    result["local_sensor_ids"] = local_ids   # per row: index of its sensor among this rank's sensors
     return result, sensor_ids, gaussian_ids, plan
 
 

@@ -336,6 +336,14 @@ int splatad_isect_lidar_tiles_fill(
     size_t fill_workspace_bytes, int64_t capacity, int64_t *isect_ids, int32_t *flatten_ids,
     int32_t *tile_offsets, int64_t *host_counts, void *stream);
 
+/* No counterpart in the reference. Arms a one-shot event (cudaEvent_t) for the NEXT _plan call of
+ * the calling thread: the plan records it on its stream as soon as host_counts[0] (the intersection
+ * count) is on its way to the host - right after the rectangle count when the lists are built by the
+ * row / column split, at the end of the plan otherwise - so that a host that only needs the count
+ * waits for a fraction of the plan. The remaining counters (n_visible, status) arrive with the copy at
+ * the end of the plan as usual. NULL disarms. */
+int splatad_isect_set_count_event(void *event);
+
 /* isect_offset_encode_tensor - gsplat/cuda/csrc/rasterization.cu:264-285.
  * offsets [C, tile_height, tile_width] int32. */
 int splatad_isect_offset_encode(const int64_t *isect_ids, int64_t n_isects, uint32_t C,
@@ -531,6 +539,22 @@ int splatad_compute_relocation(uint32_t N, const float *opacities, const float *
                                float *new_opacities, float *new_scales, void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Checks for hosts without a memory checker (no counterpart in the reference)
+ * ---------------------------------------------------------------------------------------- */
+
+/* Validates the index lists the compositing kernels follow, without following them: every
+ * flatten id of the listed part (up to tile_offsets[n_tiles] when total_follows, else n_isects)
+ * is in [0, n_rows); tile_offsets (optional, [n_tiles] or [n_tiles + 1] with total_follows) are
+ * non-decreasing and within [0, n_isects]; packed ids (optional, [n_packed]) are in range.
+ * report (device, 4 x uint64, zeroed by the caller) receives {violations, site, index, limit} with
+ * the last three describing the first violation seen (site 1 flatten id, 2 offsets out of order,
+ * 3 offset out of range, 4 Gaussian id, 5 sensor id). Nothing is dereferenced through a bad index. */
+int splatad_debug_validate_lists(int64_t n_isects, const int32_t *flatten_ids, uint64_t n_rows,
+                                 const int32_t *tile_offsets, uint32_t n_tiles, int32_t total_follows,
+                                 const int64_t *sensor_ids, const int64_t *gaussian_ids, uint64_t n_packed,
+                                 uint32_t n_sensors, uint64_t n_gaussians, uint64_t *report, void *stream);
+
+/* ------------------------------------------------------------------------------------------
  * Whole frame in one call
  * ---------------------------------------------------------------------------------------- */
 
@@ -545,8 +569,9 @@ int splatad_compute_relocation(uint32_t N, const float *opacities, const float *
  * [C * tiles + 1], images [C, H, W, .]. host_counts (pinned, 4 x int64) receives
  * {n_isects, n_visible, status, 0} once the stream has passed the plan: if n_isects > capacity the
  * lists and images are incomplete and the frame has to be repeated with more room. count_event
- * (optional cudaEvent_t) is recorded on the stream right behind the plan, so that the host can wait
- * for the counts alone while fill and compositing are still running. */
+ * (optional cudaEvent_t) is recorded on the stream as soon as host_counts[0] is on its way (see
+ * splatad_isect_set_count_event), so that the host can wait for the count alone while the depth
+ * sort, the fill and the compositing are still running. */
 int splatad_lidar_frame_fwd(
     uint32_t C, uint32_t N, const float *means, const float *quats, const float *scales,
     const float *velocities, const float *opacities_cn, const float *lidar_features, uint32_t n_features,

@@ -22,6 +22,15 @@ LIB_PATH = os.path.join(_PKG_DIR, "libsplatad_b200.so")
 HEADER_PATH = os.path.join(_REPO_DIR, "include", "splatad_b200.h")
 CSRC_DIR = os.path.join(_PKG_DIR, "csrc")
 
+# SPLATAD_DEBUG=1: the stand-in for a memory checker. Every workspace gets a tail of canary bytes
+# that is verified after each library call (a kernel that wrote past the size it was told shows up
+# as an exception naming the workspace), every call is followed by a synchronisation and an error
+# check, and ops.py validates the index lists before the compositing kernels follow them. Slow; for
+# test runs, not for production frames.
+DEBUG = os.environ.get("SPLATAD_DEBUG", "0") == "1"
+CANARY_BYTES = 512
+CANARY_VALUE = 0xA5
+
 OK = 0
 ERR_BAD_ARG = 1
 ERR_CHANNELS = 2
@@ -164,6 +173,9 @@ def call(name: str, *args) -> None:
     else:
         with torch.cuda.device(dev):
             check(fn(*args))
+    if DEBUG and dev is not None:
+        torch.cuda.synchronize(dev)     # raises here, with this call's name on the stack, if a kernel failed
+        check_canaries(name)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -171,7 +183,7 @@ def call(name: str, *args) -> None:
 # ---------------------------------------------------------------------------------------------
 _workspaces: Dict[Tuple[str, int, int], torch.Tensor] = {}
 _pinned: Dict[Tuple[str, int], torch.Tensor] = {}
-_free_slots: List[torch.Tensor] = []
+_free_slots: Dict[Tuple[int, int], List[torch.Tensor]] = {}
 
 
 def workspace(tag: str, nbytes: int, device: torch.device) -> torch.Tensor:
@@ -183,9 +195,29 @@ def workspace(tag: str, nbytes: int, device: torch.device) -> torch.Tensor:
     if buf is None or buf.numel() < nbytes:
         # grow with headroom so slowly growing scenes do not reallocate every frame
         size = max(int(nbytes * 1.25) + 1024, 1 << 16)
-        buf = torch.empty(size, dtype=torch.uint8, device=device)
+        if DEBUG:
+            # exactly the bytes asked for, canary bytes right behind them; the library is told the
+            # size without the canaries
+            whole = torch.empty(nbytes + CANARY_BYTES, dtype=torch.uint8, device=device)
+            whole[nbytes:].fill_(CANARY_VALUE)
+            _canaries[key] = whole[nbytes:]
+            buf = whole[:nbytes]
+        else:
+            buf = torch.empty(size, dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf
+
+
+_canaries: Dict[Tuple[str, int, int], torch.Tensor] = {}
+
+
+def check_canaries(after: str = "") -> None:
+    """Debug mode: raises if any workspace's canary bytes were overwritten."""
+    for key, tail in _canaries.items():
+        if not bool((tail == CANARY_VALUE).all()):
+            bad = int((tail != CANARY_VALUE).nonzero()[0])
+            raise RuntimeError(f"workspace '{key[0]}' on cuda:{key[1]} was written {bad} bytes past its end "
+                               f"(noticed after {after or 'a library call'})")
 
 
 def pinned_counts(tag: str, device: torch.device, n: int = 4) -> torch.Tensor:
@@ -198,20 +230,30 @@ def pinned_counts(tag: str, device: torch.device, n: int = 4) -> torch.Tensor:
     return buf
 
 
-def acquire_pinned_slot() -> torch.Tensor:
-    """A pinned 4 x int64 host slot owned by one outstanding call (its count arrives there
-    asynchronously); give it back with :func:`release_pinned_slot` once it has been read."""
-    if _free_slots:
-        return _free_slots.pop()
-    return torch.zeros(4, dtype=torch.int64).pin_memory()
+def _stream_key(device: torch.device) -> Tuple[int, int]:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    return index, torch.cuda.current_stream(device).cuda_stream
+
+
+def acquire_pinned_slot(device: torch.device) -> torch.Tensor:
+    """A pinned 4 x int64 host slot owned by one outstanding call (its counts arrive there
+    asynchronously); give it back with :func:`release_pinned_slot` once it has been read. Slots are
+    recycled per (device, stream): a plan copies its counters twice (the count early, everything at
+    its end), and only work enqueued later on the same stream is ordered behind the second copy."""
+    free = _free_slots.get(_stream_key(device))
+    slot = free.pop() if free else torch.zeros(4, dtype=torch.int64).pin_memory()
+    slot._splatad_stream_key = _stream_key(device)
+    return slot
 
 
 def release_pinned_slot(slot: torch.Tensor) -> None:
-    if len(_free_slots) < 64:
-        _free_slots.append(slot)
+    free = _free_slots.setdefault(slot._splatad_stream_key, [])
+    if len(free) < 16:
+        free.append(slot)
 
 
 def release_workspaces() -> None:
     _workspaces.clear()
+    _canaries.clear()
     _pinned.clear()
     _free_slots.clear()

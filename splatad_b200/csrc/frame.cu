@@ -37,19 +37,12 @@ extern "C" int splatad_lidar_frame_fwd(
     if (rc != SPLATAD_OK) return rc;
     const float tile_azim_res = azimuth_resolution * (float)tile_width;
     const uint64_t total = (uint64_t)C * N;
+    splatad_isect_set_count_event(count_event);
     rc = splatad_isect_lidar_tiles_plan(C, N, total, means2d, radii, depths, nullptr, elev_boundaries, n_boundaries,
                                         tile_azim_res, min_azimuth, 1, tiles_per_gauss, plan_workspace,
                                         plan_workspace_bytes, host_counts, stream);
+    splatad_isect_set_count_event(nullptr);
     if (rc != SPLATAD_OK) return rc;
-    if (count_event != nullptr) {
-        // the counts are on their way to the host: whoever waits on this event may read them while
-        // the rest of the frame is still running
-        const cudaError_t e = cudaEventRecord((cudaEvent_t)count_event, (cudaStream_t)stream);
-        if (e != cudaSuccess) {
-            set_last_error("lidar_frame_fwd: cudaEventRecord failed: %s", cudaGetErrorString(e));
-            return SPLATAD_ERR_CUDA;
-        }
-    }
     rc = splatad_isect_lidar_tiles_fill(C, N, total, means2d, radii, depths, nullptr, elev_boundaries, n_boundaries,
                                         tile_azim_res, min_azimuth, 1, tiles_per_gauss, plan_workspace,
                                         fill_workspace, fill_workspace_bytes, capacity, isect_ids, flatten_ids,

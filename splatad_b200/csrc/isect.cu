@@ -1552,6 +1552,24 @@ static bool use_split(const IsectGeom &g, int sort) {
     return rows <= kSplitMaxRows && rw <= kSplitMaxWidth;
 }
 
+// One-shot event of the calling thread's next plan (splatad_isect_set_count_event): recorded as soon
+// as the intersection count is on its way to the host.
+static thread_local cudaEvent_t t_count_event = nullptr;
+
+static int send_counts(const PlanWs &p, int64_t *host_counts, bool record, cudaStream_t st) {
+    if (host_counts != nullptr)
+        cudaMemcpyAsync(host_counts, p.counters, sizeof(int64_t) * CNT_SLOTS, cudaMemcpyDeviceToHost, st);
+    if (record && t_count_event != nullptr) {
+        const cudaError_t e = cudaEventRecord(t_count_event, st);
+        t_count_event = nullptr;
+        if (e != cudaSuccess) {
+            set_last_error("isect plan: cudaEventRecord failed: %s", cudaGetErrorString(e));
+            return SPLATAD_ERR_CUDA;
+        }
+    }
+    return SPLATAD_OK;
+}
+
 // plan: counts, depth order of visible Gaussians, n_isects.
 static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, void *workspace,
                       size_t workspace_bytes, int64_t *host_counts, cudaStream_t st) {
@@ -1581,6 +1599,12 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
         else
             launch_chained(isect_count_kernel<false>, cgrid, kThreads, 0, st, g.cam, g.total, tiles_per_gauss,
                            g.camera_ids, g.N, rx, ry, tot);
+    }
+    if (split && t_count_event != nullptr) {
+        // the row / column split knows the intersection count here already: a host that waits for it
+        // (to size or cut the lists) need not wait for the depth sort; the full counters follow below
+        const int rc = send_counts(p, host_counts, true, st);
+        if (rc != SPLATAD_OK) return rc;
     }
 
     EmitArgs e{};
@@ -1652,8 +1676,8 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
             emit_offsets_kernel<<<kSortGrid, kThreads, 0, st>>>(e, p.block_offs, p.eoff);
         }
     }
-    if (host_counts != nullptr)
-        cudaMemcpyAsync(host_counts, p.counters, sizeof(int64_t) * CNT_SLOTS, cudaMemcpyDeviceToHost, st);
+    const int rc = send_counts(p, host_counts, true, st);
+    if (rc != SPLATAD_OK) return rc;
     return check_launch("isect plan");
 }
 
@@ -2088,6 +2112,11 @@ extern "C" int splatad_isect_lidar_tiles_fill(
     return isect_fill(g, tiles_per_gauss, sort, plan_workspace, fill_workspace,
                       fill_workspace_bytes, capacity, isect_ids, flatten_ids, tile_offsets, host_counts,
                       (cudaStream_t)stream);
+}
+
+extern "C" int splatad_isect_set_count_event(void *event) {
+    t_count_event = (cudaEvent_t)event;
+    return SPLATAD_OK;
 }
 
 extern "C" int splatad_isect_offset_encode(const int64_t *isect_ids, int64_t n_isects, uint32_t C,

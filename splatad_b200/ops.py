@@ -989,10 +989,16 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
     # Enqueue plan and fill back to back with room for somewhat more intersections than last time;
     # the count is read when the caller asks for the exact tensors.
     capacity = hint + hint // 8 + 65536
-    slot = _lib.acquire_pinned_slot()
-    plan(slot)
+    slot = _lib.acquire_pinned_slot(dev)
+    # the plan records this event again as soon as the count is on its way to the host (an event has
+    # to have been recorded once to exist)
     counted = torch.cuda.Event()
     counted.record(torch.cuda.current_stream(dev))
+    lib.splatad_isect_set_count_event(counted.cuda_event)
+    try:
+        plan(slot)
+    finally:
+        lib.splatad_isect_set_count_event(None)
     isect_buf, flat_buf, offsets = fill(capacity)
     return DeferredIsect(tiles_per_gauss, isect_buf, flat_buf, offsets, C, n_tiles_total, capacity,
                          counted, lambda: read_count(slot), exact)
@@ -1059,6 +1065,36 @@ class DeferredIsect:
     def redo(self):
         tiles_per_gauss, isect_ids, flatten_ids = self._exact()
         return DeferredIsect.done(tiles_per_gauss, isect_ids, flatten_ids, self._C, self._n_tiles_total)
+
+
+def validate_lists(flatten_ids: Tensor, n_rows: int, isect_offsets: Optional[Tensor] = None,
+                   total_follows: bool = False, camera_ids: Optional[Tensor] = None,
+                   gaussian_ids: Optional[Tensor] = None, n_cameras: int = 0, n_gaussians: int = 0):
+    """Checks, without dereferencing anything through them, the indices the compositing kernels are
+    about to follow: flatten ids within ``n_rows``, tile offsets ordered and within the list, packed
+    ids within range. Returns (violations, site, index, limit) - all zero for consistent lists.
+    Called before every compositing launch when ``SPLATAD_DEBUG=1`` (where a violation raises)."""
+    dev = flatten_ids.device
+    report = torch.zeros(4, dtype=torch.int64, device=dev)
+    flat = flatten_ids.to(torch.int32).contiguous()
+    offs = None if isect_offsets is None else isect_offsets
+    n_tiles = 0 if offs is None else offs.numel()
+    n_packed = 0 if gaussian_ids is None else gaussian_ids.numel()
+    _call("splatad_debug_validate_lists", flat.numel(), _lib.ptr(flat) if flat.numel() else None, int(n_rows),
+          _lib.ptr(offs), n_tiles, int(bool(total_follows)),
+          _lib.ptr(camera_ids.to(torch.int64).contiguous()) if camera_ids is not None and n_packed else None,
+          _lib.ptr(gaussian_ids.to(torch.int64).contiguous()) if n_packed else None, n_packed, int(n_cameras),
+          int(n_gaussians), _lib.ptr(report), _lib.stream_ptr(dev))
+    return tuple(int(v) for v in report.tolist())
+
+
+def _debug_check_lists(what: str, flatten_ids: Tensor, n_rows: int, isect_offsets: Tensor, total_follows: bool):
+    if _lib.DEBUG and flatten_ids.numel():
+        bad, site, index, limit = validate_lists(flatten_ids, n_rows, isect_offsets.contiguous(), total_follows)
+        if bad:
+            names = {1: "flatten id", 2: "tile offsets out of order at tile", 3: "tile offset out of range at tile"}
+            raise RuntimeError(f"{what}: {bad} inconsistent list entries; first: {names.get(site, site)} {index} "
+                               f"(limit {limit})")
 
 
 def _n_isects_arg(isect_offsets: Tensor, flatten_ids: Tensor, total_follows: bool = False) -> int:
@@ -1145,9 +1181,9 @@ def lidar_frame_fwd(means, quats, scales, velocities, opacities_cn, lidar_featur
     )
     plan_ws = _lib.workspace("isect_plan", lib.splatad_isect_plan_workspace_bytes(C * N), dev)
     fill_ws = _lib.workspace("isect_fill", lib.splatad_isect_fill_workspace_bytes(capacity), dev)
-    slot = _lib.acquire_pinned_slot()
-    # the library records this event again behind the plan stage (an event has to have been recorded
-    # once to exist); waiting on it then waits for the counts only
+    slot = _lib.acquire_pinned_slot(dev)
+    # the library records this event again as soon as the count is on its way (an event has to have
+    # been recorded once to exist); waiting on it then waits for the count only
     counted = torch.cuda.Event()
     counted.record(torch.cuda.current_stream(dev))
     p = _lib.ptr
@@ -1428,6 +1464,7 @@ class _RasterizeToPixels(torch.autograd.Function):
         render_alphas = torch.empty((C, height, width, 1), dtype=torch.float32, device=dev)
         last_ids = torch.empty((C, height, width), dtype=torch.int32, device=dev)
         n_isects = _n_isects_arg(isect_offsets, flatten_ids, total_follows)
+        _debug_check_lists("rasterize_to_pixels", flatten_ids, means2d.numel() // 2, isect_offsets, total_follows)
         ctx.n_isects_arg = n_isects
         _call(
             "splatad_rasterize_to_pixels_fwd", C, n_isects, _lib.ptr(means2d), _lib.ptr(conics_f),
@@ -1600,6 +1637,7 @@ class _RasterizeToPoints(torch.autograd.Function):
         alpha_sum = torch.empty((C, height, width, 1), **f32) if compute_alpha_sum_until_points else None
         last_ids = torch.empty((C, height, width), dtype=torch.int32, device=dev)
         ctx.n_isects_arg = _n_isects_arg(isect_offsets, flatten_ids, total_follows)
+        _debug_check_lists("rasterize_to_points", flatten_ids, means2d.numel() // 2, isect_offsets, total_follows)
         _call(
             "splatad_rasterize_to_points_fwd", C, ctx.n_isects_arg, _lib.ptr(means2d),
             _lib.ptr(conics_f), _lib.ptr(colors_f) if colors_f.numel() else None, _lib.ptr(ranges_f), channels,

@@ -336,13 +336,15 @@ int splatad_isect_lidar_tiles_fill(
     size_t fill_workspace_bytes, int64_t capacity, int64_t *isect_ids, int32_t *flatten_ids,
     int32_t *tile_offsets, int64_t *host_counts, void *stream);
 
-/* No counterpart in the reference. Arms a one-shot event (cudaEvent_t) for the NEXT _plan call of
- * the calling thread: the plan records it on its stream as soon as host_counts[0] (the intersection
- * count) is on its way to the host - right after the rectangle count when the lists are built by the
- * row / column split, at the end of the plan otherwise - so that a host that only needs the count
- * waits for a fraction of the plan. The remaining counters (n_visible, status) arrive with the copy at
- * the end of the plan as usual. NULL disarms. */
-int splatad_isect_set_count_event(void *event);
+/* No counterpart in the reference. Arms a one-shot request for the NEXT _plan call of the calling
+ * thread: when the lists will be built by the row / column split (sorted output, at most 128 tile
+ * rows and 16384 tiles), the rectangle count kernel itself stores host_pair[0] = n_isects and then
+ * host_pair[1] = sequence into host_pair, two int64 of pinned (mapped) host memory, as soon as it
+ * has the count - before the depth sort, with no copy in the stream. A host that only needs the
+ * count polls host_pair[1] for `sequence` (a number it has not used for this pair before) instead of
+ * waiting for the end of the plan. Otherwise (other list construction, memory not mapped for the
+ * device) nothing is written and the host waits for host_counts as usual. NULL disarms. */
+int splatad_isect_set_early_count(int64_t *host_pair, int64_t sequence);
 
 /* isect_offset_encode_tensor - gsplat/cuda/csrc/rasterization.cu:264-285.
  * offsets [C, tile_height, tile_width] int32. */
@@ -568,10 +570,9 @@ int splatad_debug_validate_lists(int64_t n_isects, const int32_t *flatten_ids, u
  * in the projection / plan calls, isect_ids / flatten_ids [capacity], tile_offsets
  * [C * tiles + 1], images [C, H, W, .]. host_counts (pinned, 4 x int64) receives
  * {n_isects, n_visible, status, 0} once the stream has passed the plan: if n_isects > capacity the
- * lists and images are incomplete and the frame has to be repeated with more room. count_event
- * (optional cudaEvent_t) is recorded on the stream as soon as host_counts[0] is on its way (see
- * splatad_isect_set_count_event), so that the host can wait for the count alone while the depth
- * sort, the fill and the compositing are still running. */
+ * lists and images are incomplete and the frame has to be repeated with more room.
+ * early_count_pair / early_count_sequence (optional): see splatad_isect_set_early_count - the count
+ * reaches the host while the depth sort, the fill and the compositing are still running. */
 int splatad_lidar_frame_fwd(
     uint32_t C, uint32_t N, const float *means, const float *quats, const float *scales,
     const float *velocities, const float *opacities_cn, const float *lidar_features, uint32_t n_features,
@@ -585,7 +586,7 @@ int splatad_lidar_frame_fwd(
     int32_t *flatten_ids, int32_t *tile_offsets, float *render_features, float *render_alphas,
     float *alpha_sum_until_points, int32_t *last_ids, float *median_depths, void *plan_workspace,
     size_t plan_workspace_bytes, void *fill_workspace, size_t fill_workspace_bytes, int64_t *host_counts,
-    void *count_event, void *stream);
+    int64_t *early_count_pair, int64_t early_count_sequence, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Gaussian-sharded exchange (one process per GPU): every rank projects its slice of the Gaussians

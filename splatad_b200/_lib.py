@@ -12,6 +12,7 @@ import ctypes
 import os
 import re
 import subprocess
+import time
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -241,9 +242,36 @@ def acquire_pinned_slot(device: torch.device) -> torch.Tensor:
     recycled per (device, stream): a plan copies its counters twice (the count early, everything at
     its end), and only work enqueued later on the same stream is ordered behind the second copy."""
     free = _free_slots.get(_stream_key(device))
-    slot = free.pop() if free else torch.zeros(4, dtype=torch.int64).pin_memory()
+    slot = free.pop() if free else torch.zeros(8, dtype=torch.int64).pin_memory()
     slot._splatad_stream_key = _stream_key(device)
     return slot
+
+
+_sequence = 0
+
+
+def next_sequence() -> int:
+    """A number no earlier early-count request has used (see splatad_isect_set_early_count)."""
+    global _sequence
+    _sequence += 1
+    return _sequence
+
+
+def wait_for_count(slot: torch.Tensor, sequence: int, event: torch.cuda.Event, patience_s: float = 0.02):
+    """(n_isects, status) of a plan that was given ``slot`` (8 x int64 pinned: [0..3] the counters the
+    plan copies at its end, [4..5] the early pair). Polls the early pair for ``sequence`` - the count
+    kernel stores it there itself, long before the plan's own copy - and falls back to waiting for
+    ``event`` (recorded behind the plan) when it does not show up within ``patience_s``."""
+    view = slot.numpy()
+    if sequence:
+        deadline = time.perf_counter() + patience_s
+        while view[5] != sequence:
+            if time.perf_counter() > deadline:
+                break
+        else:
+            return int(view[4]), 0
+    event.synchronize()
+    return int(view[0]), int(view[2])
 
 
 def release_pinned_slot(slot: torch.Tensor) -> None:

@@ -21,7 +21,7 @@ extern "C" int splatad_lidar_frame_fwd(
     int32_t *flatten_ids, int32_t *tile_offsets, float *render_features, float *render_alphas,
     float *alpha_sum_until_points, int32_t *last_ids, float *median_depths, void *plan_workspace,
     size_t plan_workspace_bytes, void *fill_workspace, size_t fill_workspace_bytes, int64_t *host_counts,
-    void *count_event, void *stream) {
+    int64_t *early_count_pair, int64_t early_count_sequence, void *stream) {
     SPL_REQUIRE(C > 0 && N > 0 && image_width > 0 && image_height > 0, SPLATAD_ERR_BAD_ARG,
                 "lidar_frame_fwd: empty input");
     SPL_REQUIRE(n_features + 1 <= SPLATAD_MAX_CHANNELS, SPLATAD_ERR_CHANNELS,
@@ -37,11 +37,11 @@ extern "C" int splatad_lidar_frame_fwd(
     if (rc != SPLATAD_OK) return rc;
     const float tile_azim_res = azimuth_resolution * (float)tile_width;
     const uint64_t total = (uint64_t)C * N;
-    splatad_isect_set_count_event(count_event);
+    splatad_isect_set_early_count(early_count_pair, early_count_sequence);
     rc = splatad_isect_lidar_tiles_plan(C, N, total, means2d, radii, depths, nullptr, elev_boundaries, n_boundaries,
                                         tile_azim_res, min_azimuth, 1, tiles_per_gauss, plan_workspace,
                                         plan_workspace_bytes, host_counts, stream);
-    splatad_isect_set_count_event(nullptr);
+    splatad_isect_set_early_count(nullptr, 0);
     if (rc != SPLATAD_OK) return rc;
     rc = splatad_isect_lidar_tiles_fill(C, N, total, means2d, radii, depths, nullptr, elev_boundaries, n_boundaries,
                                         tile_azim_res, min_azimuth, 1, tiles_per_gauss, plan_workspace,

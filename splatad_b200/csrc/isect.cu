@@ -185,7 +185,10 @@ template <bool kLidar>
 __global__ void __launch_bounds__(kThreads)
 isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ tiles_per_gauss,
                    const int64_t *__restrict__ camera_ids, uint32_t N, uint32_t *__restrict__ rect_xw,
-                   uint32_t *__restrict__ rect_yh, int64_t *__restrict__ n_isects) {
+                   uint32_t *__restrict__ rect_yh, int64_t *__restrict__ n_isects,
+                   int64_t *__restrict__ ticket /* with early_host: a zeroed counter */,
+                   volatile int64_t *early_host /* optional, host-mapped: {count, sequence number} */,
+                   int64_t early_seq) {
     chain_enter();
     __shared__ float sb[kLidar ? kMaxElevSmem : 1];
     __shared__ unsigned long long wsum[kThreads / 32];
@@ -221,6 +224,20 @@ isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ til
         unsigned long long t = 0;
         for (int w = 0; w < kThreads / 32; ++w) t += wsum[w];
         if (t) atomicAdd((unsigned long long *)n_isects, t);
+        if (early_host != nullptr) {
+            // the block that finishes last hands the total straight to the host (a store to mapped
+            // pinned memory): nobody waits on anybody, and no copy sits between this kernel and the next
+            __threadfence();
+            if (atomicAdd((unsigned long long *)ticket, 1ull) + 1ull == (unsigned long long)gridDim.x) {
+                __threadfence();
+                const unsigned long long total_isects = atomicAdd((unsigned long long *)n_isects, 0ull);
+                *ticket = 0;
+                early_host[0] = (int64_t)total_isects;
+                __threadfence_system();
+                early_host[1] = early_seq;
+                __threadfence_system();
+            }
+        }
     }
 }
 
@@ -1552,23 +1569,10 @@ static bool use_split(const IsectGeom &g, int sort) {
     return rows <= kSplitMaxRows && rw <= kSplitMaxWidth;
 }
 
-// One-shot event of the calling thread's next plan (splatad_isect_set_count_event): recorded as soon
-// as the intersection count is on its way to the host.
-static thread_local cudaEvent_t t_count_event = nullptr;
-
-static int send_counts(const PlanWs &p, int64_t *host_counts, bool record, cudaStream_t st) {
-    if (host_counts != nullptr)
-        cudaMemcpyAsync(host_counts, p.counters, sizeof(int64_t) * CNT_SLOTS, cudaMemcpyDeviceToHost, st);
-    if (record && t_count_event != nullptr) {
-        const cudaError_t e = cudaEventRecord(t_count_event, st);
-        t_count_event = nullptr;
-        if (e != cudaSuccess) {
-            set_last_error("isect plan: cudaEventRecord failed: %s", cudaGetErrorString(e));
-            return SPLATAD_ERR_CUDA;
-        }
-    }
-    return SPLATAD_OK;
-}
+// One-shot request of the calling thread's next plan (splatad_isect_set_early_count): where the
+// rectangle count kernel writes the intersection count for the host, and the number it tags it with.
+static thread_local int64_t *t_early_host = nullptr;
+static thread_local int64_t t_early_seq = 0;
 
 // plan: counts, depth order of visible Gaussians, n_isects.
 static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, void *workspace,
@@ -1593,18 +1597,24 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
         SPL_PROF("isect_count_kernel", st);
         uint32_t *rx = split ? p.rect_xw : nullptr, *ry = split ? p.rect_yh : nullptr;
         int64_t *tot = split ? p.counters + CNT_NISECT : nullptr;
+        // the row / column split knows the intersection count when this kernel ends: a host that has
+        // asked for it (to size or cut its lists) gets it from the kernel itself and need not wait
+        // for the depth sort
+        int64_t *early = nullptr;
+        if (split && t_early_host != nullptr) {
+            void *dptr = nullptr;
+            if (cudaHostGetDevicePointer(&dptr, t_early_host, 0) == cudaSuccess) early = (int64_t *)dptr;
+            else (void)cudaGetLastError();   // not mapped for this device: the host falls back to the event
+        }
+        const int64_t seq = t_early_seq;
+        t_early_host = nullptr;
+        int64_t *ticket = p.counters + CNT_TICKET;
         if (g.lidar)
             launch_chained(isect_count_kernel<true>, cgrid, kThreads, 0, st, g.lid, g.total, tiles_per_gauss,
-                           g.camera_ids, g.N, rx, ry, tot);
+                           g.camera_ids, g.N, rx, ry, tot, ticket, early, seq);
         else
             launch_chained(isect_count_kernel<false>, cgrid, kThreads, 0, st, g.cam, g.total, tiles_per_gauss,
-                           g.camera_ids, g.N, rx, ry, tot);
-    }
-    if (split && t_count_event != nullptr) {
-        // the row / column split knows the intersection count here already: a host that waits for it
-        // (to size or cut the lists) need not wait for the depth sort; the full counters follow below
-        const int rc = send_counts(p, host_counts, true, st);
-        if (rc != SPLATAD_OK) return rc;
+                           g.camera_ids, g.N, rx, ry, tot, ticket, early, seq);
     }
 
     EmitArgs e{};
@@ -1676,8 +1686,8 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
             emit_offsets_kernel<<<kSortGrid, kThreads, 0, st>>>(e, p.block_offs, p.eoff);
         }
     }
-    const int rc = send_counts(p, host_counts, true, st);
-    if (rc != SPLATAD_OK) return rc;
+    if (host_counts != nullptr)
+        cudaMemcpyAsync(host_counts, p.counters, sizeof(int64_t) * CNT_SLOTS, cudaMemcpyDeviceToHost, st);
     return check_launch("isect plan");
 }
 
@@ -2114,8 +2124,9 @@ extern "C" int splatad_isect_lidar_tiles_fill(
                       (cudaStream_t)stream);
 }
 
-extern "C" int splatad_isect_set_count_event(void *event) {
-    t_count_event = (cudaEvent_t)event;
+extern "C" int splatad_isect_set_early_count(int64_t *host_pair, int64_t sequence) {
+    t_early_host = host_pair;
+    t_early_seq = sequence;
     return SPLATAD_OK;
 }
 

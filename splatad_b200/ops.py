@@ -963,10 +963,11 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
                   _lib.ptr(flatten_ids), _lib.ptr(offsets), None, stream)
         return isect_ids, flatten_ids, offsets
 
-    def read_count(slot=None):
-        src = host if slot is None else slot
-        n_isects, status = int(src[0]), int(src[2])
-        if slot is not None:
+    def read_count(slot=None, sequence=0, event=None):
+        if slot is None:
+            n_isects, status = int(host[0]), int(host[2])
+        else:
+            n_isects, status = _lib.wait_for_count(slot, sequence, event)
             _lib.release_pinned_slot(slot)
         if status & 2 or n_isects > 0x7FFFFFFF:
             raise RuntimeError(f"isect: {n_isects} intersections do not fit int32 flatten ids / offsets")
@@ -990,18 +991,19 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
     # the count is read when the caller asks for the exact tensors.
     capacity = hint + hint // 8 + 65536
     slot = _lib.acquire_pinned_slot(dev)
-    # the plan records this event again as soon as the count is on its way to the host (an event has
-    # to have been recorded once to exist)
-    counted = torch.cuda.Event()
-    counted.record(torch.cuda.current_stream(dev))
-    lib.splatad_isect_set_count_event(counted.cuda_event)
+    # the rectangle count kernel hands the count to the host itself (slot[4:6]) when the lists are
+    # built by the row / column split; the event behind the plan is the fallback
+    sequence = _lib.next_sequence()
+    lib.splatad_isect_set_early_count(slot.data_ptr() + 32, sequence)
     try:
         plan(slot)
     finally:
-        lib.splatad_isect_set_count_event(None)
+        lib.splatad_isect_set_early_count(None, 0)
+    counted = torch.cuda.Event()
+    counted.record(torch.cuda.current_stream(dev))
     isect_buf, flat_buf, offsets = fill(capacity)
     return DeferredIsect(tiles_per_gauss, isect_buf, flat_buf, offsets, C, n_tiles_total, capacity,
-                         counted, lambda: read_count(slot), exact)
+                         counted, lambda: read_count(slot, sequence, counted), exact)
 
 
 # (kind, shape, tile grid, device, stream) -> intersection count of the last frame of that shape on
@@ -1053,7 +1055,6 @@ class DeferredIsect:
 
     def resolve(self):
         if self._resolved is None:
-            self._counted.synchronize()
             n_isects = self._read_count()
             if n_isects > self._capacity:
                 return None
@@ -1115,13 +1116,13 @@ class LidarFrame:
     exact-length (isect_ids, flatten_ids), or None when the count outgrew the room the frame was
     given (the frame then has to be rendered the ordinary way)."""
 
-    def __init__(self, tensors, capacity, counted, slot, key):
+    def __init__(self, tensors, capacity, counted, slot, key, sequence):
         self.__dict__.update(tensors)
         self._capacity, self._counted, self._slot, self._key = capacity, counted, slot, key
+        self._sequence = sequence
 
     def finish(self):
-        self._counted.synchronize()
-        n_isects, status = int(self._slot[0]), int(self._slot[2])
+        n_isects, status = _lib.wait_for_count(self._slot, self._sequence, self._counted)
         _lib.release_pinned_slot(self._slot)
         if status & 2 or n_isects > 0x7FFFFFFF:
             raise RuntimeError(f"isect: {n_isects} intersections do not fit int32 flatten ids / offsets")
@@ -1182,10 +1183,7 @@ def lidar_frame_fwd(means, quats, scales, velocities, opacities_cn, lidar_featur
     plan_ws = _lib.workspace("isect_plan", lib.splatad_isect_plan_workspace_bytes(C * N), dev)
     fill_ws = _lib.workspace("isect_fill", lib.splatad_isect_fill_workspace_bytes(capacity), dev)
     slot = _lib.acquire_pinned_slot(dev)
-    # the library records this event again as soon as the count is on its way (an event has to have
-    # been recorded once to exist); waiting on it then waits for the count only
-    counted = torch.cuda.Event()
-    counted.record(torch.cuda.current_stream(dev))
+    sequence = _lib.next_sequence()   # the count kernel stores the count + this number into slot[4:6]
     p = _lib.ptr
     _call("splatad_lidar_frame_fwd", C, N, p(_f(means)), p(_f(quats)), p(_f(scales)), p(_f(velocities)),
           p(_f(opacities_cn)), p(_f(lidar_features)), D, p(_f(viewmats)), p(_f(linear_velocity)),
@@ -1196,8 +1194,11 @@ def lidar_frame_fwd(means, quats, scales, velocities, opacities_cn, lidar_featur
           p(t["means2d"]), p(t["depths"]), p(t["conics"]), p(t["pix_vels"]), p(t["depth_compensations"]),
           p(t["tiles_per_gauss"]), capacity, p(t["isect_buf"]), p(t["flatten_buf"]), p(t["offsets_buf"]),
           p(t["render"]), p(t["alphas"]), p(t["alpha_sum"]), p(t["last_ids"]), p(t["median_depths"]),
-          p(plan_ws), plan_ws.numel(), p(fill_ws), fill_ws.numel(), slot.data_ptr(), counted.cuda_event, stream)
-    return LidarFrame(t, capacity, counted, slot, key)
+          p(plan_ws), plan_ws.numel(), p(fill_ws), fill_ws.numel(), slot.data_ptr(), slot.data_ptr() + 32, sequence,
+          stream)
+    counted = torch.cuda.Event()      # fallback: the counters the plan copies at its end
+    counted.record(torch.cuda.current_stream(dev))
+    return LidarFrame(t, capacity, counted, slot, key, sequence)
 
 
 @torch.no_grad()

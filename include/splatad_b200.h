@@ -298,6 +298,12 @@ int splatad_compute_lidar_velocity_bwd(uint32_t C, uint32_t N, const float *p_vi
  *          compositing calls accept n_isects = -1 ("read the end of the last tile from
  *          tile_offsets[C * tiles]"), so a caller that passes a generous capacity can enqueue
  *          plan, fill and compositing without waiting for the count.
+ * `sort`: 0 = lists in flatten-index order; 1 = sorted, with the depth order of the visible
+ * Gaussians built by buckets (four kernels: count, scan, scatter, per-bucket order) - if more than
+ * 1024 depths fall into one of the 65536 buckets that span the scene's depth range, the plan sets
+ * status bit 4 in host_counts[2] and the order is not final: call _plan again with sort = 2;
+ * 2 = sorted, depth order by four radix passes (twelve kernels, any depth distribution). Pass the
+ * same value to _fill. Both give the same lists.
  * `total_elems` is C*N for the [C,N] layout (camera_ids NULL) or nnz for the packed layout
  * (camera_ids [nnz] int64 gives the sensor of each row, N is ignored).
  * Depths must be non-negative: their bit patterns are ordered as unsigned integers.
@@ -338,11 +344,11 @@ int splatad_isect_lidar_tiles_fill(
 
 /* No counterpart in the reference. Arms a one-shot request for the NEXT _plan call of the calling
  * thread: when the lists will be built by the row / column split (sorted output, at most 128 tile
- * rows and 16384 tiles), the rectangle count kernel itself stores host_pair[0] = n_isects and then
- * host_pair[1] = sequence into host_pair, two int64 of pinned (mapped) host memory, as soon as it
- * has the count - before the depth sort, with no copy in the stream. A host that only needs the
- * count polls host_pair[1] for `sequence` (a number it has not used for this pair before) instead of
- * waiting for the end of the plan. Otherwise (other list construction, memory not mapped for the
+ * rows and 16384 tiles), a kernel stores host_pair[0] = n_isects, host_pair[2] = status bits and
+ * then host_pair[1] = sequence into host_pair, three int64 of pinned (mapped) host memory, as soon
+ * as they are known - before the depth order is built, with no copy in the stream. A host that only
+ * needs the count polls host_pair[1] for `sequence` (a number it has not used for this triple
+ * before) instead of waiting for the end of the plan. Otherwise (other list construction, memory not mapped for the
  * device) nothing is written and the host waits for host_counts as usual. NULL disarms. */
 int splatad_isect_set_early_count(int64_t *host_pair, int64_t sequence);
 

@@ -259,8 +259,8 @@ def next_sequence() -> int:
 
 def wait_for_count(slot: torch.Tensor, sequence: int, event: torch.cuda.Event, patience_s: float = 0.02):
     """(n_isects, status) of a plan that was given ``slot`` (8 x int64 pinned: [0..3] the counters the
-    plan copies at its end, [4..5] the early pair). Polls the early pair for ``sequence`` - the count
-    kernel stores it there itself, long before the plan's own copy - and falls back to waiting for
+    plan copies at its end, [4..6] the early triple {count, sequence, status}). Polls the triple for
+    ``sequence`` - a kernel stores it there itself, long before the plan's own copy - and falls back to waiting for
     ``event`` (recorded behind the plan) when it does not show up within ``patience_s``."""
     view = slot.numpy()
     if sequence:
@@ -269,7 +269,7 @@ def wait_for_count(slot: torch.Tensor, sequence: int, event: torch.cuda.Event, p
             if time.perf_counter() > deadline:
                 break
         else:
-            return int(view[4]), 0
+            return int(view[4]), int(view[6])
     event.synchronize()
     return int(view[0]), int(view[2])
 

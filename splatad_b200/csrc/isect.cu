@@ -35,8 +35,10 @@ static_assert(kSortThreads == kRadixBins, "one thread per radix bin");
 static_assert(kSortGrid <= 1024, "row scan and emit scan use one thread per sort block");
 
 // counters[] slots (int64 each)
-enum { CNT_NISECT = 0, CNT_NVIS = 1, CNT_STATUS = 2, CNT_TICKET = 3, CNT_SLOTS = 4 };
-enum { ST_OVERFLOW_CAPACITY = 1, ST_OVERFLOW_INT32 = 2 };
+// The first CNT_SLOTS are what the plan copies to the host; the rest is device-side state.
+enum { CNT_NISECT = 0, CNT_NVIS = 1, CNT_STATUS = 2, CNT_TICKET = 3, CNT_SLOTS = 4,
+       CNT_DMIN = 4, CNT_DMAX = 5, CNT_DEV_SLOTS = 8 };
+enum { ST_OVERFLOW_CAPACITY = 1, ST_OVERFLOW_INT32 = 2, ST_DEPTH_BUCKETS = 4 };
 
 // ---------------------------------------------------------------------------------------
 // Block-wide exclusive scan for any blockDim.x that is a multiple of 32 (<= 1024).
@@ -181,20 +183,34 @@ __device__ __forceinline__ void stage_boundaries(GridArgs<kLidar> &a, float *sb)
 // rectangle is also stored, packed into two words per element (x0 | width << 16, first grid row |
 // height << 16 with grid row = sensor * tile rows + y; 16-bit fields, used only when
 // the geometry is within its limits) for the row / column split, and the total is added to *n_isects.
+// {count, sequence number, status bits} for a polling host, stored by whichever kernel knows them first
+// into mapped pinned memory: count and status, a system-wide fence, then the sequence number.
+__device__ __forceinline__ void tell_host(volatile int64_t *early_host, int64_t seq, int64_t n_isects,
+                                          int64_t status) {
+    early_host[0] = n_isects;
+    early_host[2] = status;
+    __threadfence_system();
+    early_host[1] = seq;
+    __threadfence_system();
+}
+
 template <bool kLidar>
 __global__ void __launch_bounds__(kThreads)
 isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ tiles_per_gauss,
                    const int64_t *__restrict__ camera_ids, uint32_t N, uint32_t *__restrict__ rect_xw,
                    uint32_t *__restrict__ rect_yh, int64_t *__restrict__ n_isects,
                    int64_t *__restrict__ ticket /* with early_host: a zeroed counter */,
-                   volatile int64_t *early_host /* optional, host-mapped: {count, sequence number} */,
-                   int64_t early_seq) {
+                   volatile int64_t *early_host /* optional, host-mapped: {count, sequence number, status} */,
+                   int64_t early_seq,
+                   const uint32_t *__restrict__ depth_bits /* optional: depth range of the listed elements */,
+                   int64_t *__restrict__ counters /* with depth_bits: CNT_DMIN / CNT_DMAX / CNT_NVIS */) {
     chain_enter();
     __shared__ float sb[kLidar ? kMaxElevSmem : 1];
     __shared__ unsigned long long wsum[kThreads / 32];
     stage_boundaries<kLidar>(a, sb);
     const uint32_t tile_rows = kLidar ? a.lidar.n_tiles_elev : a.cam.tile_height;
     unsigned long long sum = 0;
+    uint32_t dmin = 0xffffffffu, dmax = 0u, nvis = 0u;
     for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += gridDim.x * blockDim.x) {
         Rect r;
@@ -214,6 +230,31 @@ isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ til
             rect_yh[idx] = yh;
         }
         sum += (unsigned long long)(cnt > 0 ? cnt : 0);
+        if (depth_bits != nullptr && cnt > 0) {
+            const uint32_t d = __ldg(depth_bits + idx);
+            dmin = min(dmin, d);
+            dmax = max(dmax, d);
+            ++nvis;
+        }
+    }
+    if (depth_bits != nullptr) {
+        __shared__ uint32_t s_rng[3];
+        if (threadIdx.x == 0) { s_rng[0] = 0xffffffffu; s_rng[1] = 0u; s_rng[2] = 0u; }
+        __syncthreads();
+        dmin = __reduce_min_sync(0xffffffffu, dmin);
+        dmax = __reduce_max_sync(0xffffffffu, dmax);
+        nvis = __reduce_add_sync(0xffffffffu, nvis);
+        if ((threadIdx.x & 31) == 0 && nvis) {
+            atomicMin(&s_rng[0], dmin);
+            atomicMax(&s_rng[1], dmax);
+            atomicAdd(&s_rng[2], nvis);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0 && s_rng[2]) {
+            atomicMin(reinterpret_cast<unsigned int *>(counters + CNT_DMIN), s_rng[0]);
+            atomicMax(reinterpret_cast<unsigned int *>(counters + CNT_DMAX), s_rng[1]);
+            atomicAdd(reinterpret_cast<unsigned long long *>(counters + CNT_NVIS), (unsigned long long)s_rng[2]);
+        }
     }
     if (n_isects == nullptr) return;
 #pragma unroll
@@ -232,10 +273,7 @@ isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ til
                 __threadfence();
                 const unsigned long long total_isects = atomicAdd((unsigned long long *)n_isects, 0ull);
                 *ticket = 0;
-                early_host[0] = (int64_t)total_isects;
-                __threadfence_system();
-                early_host[1] = early_seq;
-                __threadfence_system();
+                tell_host(early_host, early_seq, (int64_t)total_isects, 0);
             }
         }
     }
@@ -495,6 +533,161 @@ radix_downsweep_kernel(PassSrc s, int shift, int nbits, uint32_t mask, const uin
         __syncthreads();
         digit_base[tid] += tile_cnt[tid];
         __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Depth order by buckets. The visible elements are ordered by (depth bits, flatten index) - what a
+// stable radix sort of the depth bits from flatten order gives - in four short kernels instead of
+// twelve. The depth range [dmin, dmax] of the listed elements comes with the rectangle count; an
+// element's bucket is its depth's position in that range, in 262144 equal steps of depth (equal
+// steps of the bit pattern would crowd the far half of the range into a few buckets): a weakly
+// monotone function of the depth, so buckets are ordered like the keys. Count per bucket (global
+// atomics), scan, scatter into bucket order with an atomic cursor per bucket (arbitrary order
+// inside a bucket), then every element finds its rank inside its bucket by counting the bucket's
+// elements that precede it in (bits, flatten index) order and is written to its final place: one
+// thread per element, neighbours share their bucket. For a million depths between 0.3 and 113 m a
+// bucket holds 4 elements on average and 17 where they are densest. Elements of a bucket with more than kBucketMax entries
+// (depths that agree to within half a millimetre by the thousand) are passed through unordered and reported
+// with status bit ST_DEPTH_BUCKETS: the caller repeats the plan with the radix sort (sort = 2).
+// ---------------------------------------------------------------------------------------
+constexpr uint32_t kDepthBuckets = 262144;
+constexpr uint32_t kBucketMax = 1024;
+constexpr uint32_t kBucketScanBlocks = kDepthBuckets / 1024;   // 256
+static_assert(kBucketScanBlocks % 32 == 0 && kBucketScanBlocks <= 1024, "block totals are scanned by one warp");
+
+struct DepthBuckets {
+    float dmin, scale;
+    __device__ __forceinline__ uint32_t operator()(uint32_t bits) const {
+        const float d = __uint_as_float(bits);
+        if (!(d == d)) return kDepthBuckets - 1;   // NaN patterns sort behind +infinity
+        const float x = (d - dmin) * scale;        // weakly monotone in d for finite dmin, scale >= 0
+        return x >= (float)(kDepthBuckets - 1) ? kDepthBuckets - 1 : (uint32_t)x;
+    }
+};
+
+__device__ __forceinline__ DepthBuckets depth_buckets(const int64_t *counters) {
+    const uint32_t lo = (uint32_t)counters[CNT_DMIN];
+    const uint32_t hi = min((uint32_t)counters[CNT_DMAX], 0x7f800000u);   // a NaN maximum counts as +infinity
+    DepthBuckets b;
+    b.dmin = __uint_as_float(min(lo, hi));
+    const float range = __uint_as_float(hi) - b.dmin;
+    b.scale = (range > 0.f) ? (float)(kDepthBuckets - 1) / range : 0.f;   // infinite range: scale 0, one bucket
+    return b;
+}
+
+__global__ void __launch_bounds__(kThreads)
+depth_bucket_count_kernel(const uint32_t *__restrict__ depth_bits, const int32_t *__restrict__ tiles_per_gauss,
+                          uint32_t total, const int64_t *__restrict__ counters, uint32_t *__restrict__ bcount) {
+    chain_enter();
+    const DepthBuckets bucket = depth_buckets(counters);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x)
+        if (tiles_per_gauss[i] > 0) atomicAdd(&bcount[bucket(__ldg(depth_bits + i))], 1u);
+}
+
+// Blocks of 1024 threads, one bucket per thread: starts within the block's 1024 buckets, counts
+// back to zero (they become the scatter's cursors), the block's total. The block that finishes
+// last turns the block totals into block offsets (a bucket's start = bstart[b] + boff[b >> 10]), sets
+// the status bit for oversized buckets and - when asked - tells the polling host.
+__global__ void __launch_bounds__(1024)
+depth_bucket_scan_kernel(uint32_t *__restrict__ bcount, uint32_t *__restrict__ bstart, uint32_t *__restrict__ boff,
+                         int64_t *__restrict__ counters, volatile int64_t *early_host, int64_t early_seq) {
+    chain_enter();
+    __shared__ uint32_t wt[33];
+    __shared__ bool s_last;
+    const uint32_t b = blockIdx.x * 1024 + threadIdx.x;
+    const uint32_t c = bcount[b];
+    bcount[b] = 0u;
+    uint32_t total;
+    bstart[b] = block_excl_scan(c, wt, total);
+    const bool big = __syncthreads_or(c > kBucketMax);
+    if (threadIdx.x == 0) {
+        boff[kBucketScanBlocks + 1 + blockIdx.x] = total;
+        if (big) atomicOr((unsigned long long *)&counters[CNT_STATUS], (unsigned long long)ST_DEPTH_BUCKETS);
+        __threadfence();
+        s_last = atomicAdd((unsigned long long *)&counters[CNT_TICKET], 1ull) + 1ull == (unsigned long long)gridDim.x;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (threadIdx.x < 32) {
+        // the block totals: kBucketScanBlocks / 32 consecutive ones per lane
+        constexpr uint32_t per = kBucketScanBlocks / 32;
+        const volatile uint32_t *tot = boff + kBucketScanBlocks + 1;
+        uint32_t v[per], sum = 0;
+#pragma unroll
+        for (uint32_t k = 0; k < per; ++k) {
+            v[k] = tot[per * threadIdx.x + k];
+            sum += v[k];
+        }
+        uint32_t inc = sum;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t o = __shfl_up_sync(0xffffffffu, inc, off);
+            if (threadIdx.x >= (uint32_t)off) inc += o;
+        }
+        uint32_t run = inc - sum;
+#pragma unroll
+        for (uint32_t k = 0; k < per; ++k) {
+            boff[per * threadIdx.x + k] = run;
+            run += v[k];
+        }
+        if (threadIdx.x == 31) {
+            boff[kBucketScanBlocks] = inc;
+            counters[CNT_TICKET] = 0;
+            __threadfence();
+            if (early_host != nullptr)
+                tell_host(early_host, early_seq, counters[CNT_NISECT],
+                          (int64_t)atomicOr((unsigned long long *)&counters[CNT_STATUS], 0ull));
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads)
+depth_bucket_scatter_kernel(const uint32_t *__restrict__ depth_bits, const int32_t *__restrict__ tiles_per_gauss,
+                            uint32_t total, const int64_t *__restrict__ counters,
+                            const uint32_t *__restrict__ bstart, const uint32_t *__restrict__ boff,
+                            uint32_t *__restrict__ bcursor, uint2 *__restrict__ pairs /* {bits, flatten index} */) {
+    chain_enter();
+    const DepthBuckets bucket = depth_buckets(counters);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        if (tiles_per_gauss[i] <= 0) continue;
+        const uint32_t d = __ldg(depth_bits + i);
+        const uint32_t b = bucket(d);
+        const uint32_t pos = bstart[b] + boff[b >> 10] + atomicAdd(&bcursor[b], 1u);
+        pairs[pos] = make_uint2(d, i);
+    }
+}
+
+// One thread per scattered element: its rank among the elements of its bucket in (bits, flatten
+// index) order, by counting, and the move to its final place. Neighbouring threads hold neighbouring
+// elements, almost always of the same bucket: the loads of the loop are broadcasts.
+__global__ void __launch_bounds__(kThreads)
+depth_bucket_rank_kernel(const int64_t *__restrict__ counters, const uint32_t *__restrict__ bstart,
+                         const uint32_t *__restrict__ boff, const uint2 *__restrict__ pairs,
+                         uint32_t *__restrict__ keys_out, uint32_t *__restrict__ vals_out) {
+    chain_enter();
+    const DepthBuckets bucket = depth_buckets(counters);
+    const uint32_t n = boff[kBucketScanBlocks];
+    for (uint32_t p = blockIdx.x * blockDim.x + threadIdx.x; p < n; p += gridDim.x * blockDim.x) {
+        const uint2 mine = __ldg(pairs + p);
+        const uint32_t key = mine.x, val = mine.y;
+        const uint32_t b = bucket(key);
+        const uint32_t lo = bstart[b] + boff[b >> 10];
+        const uint32_t hi = (b + 1 < kDepthBuckets && ((b + 1) & 1023u)) ? bstart[b + 1] + boff[b >> 10]
+                            : (b + 1 < kDepthBuckets ? boff[(b + 1) >> 10] : n);
+        uint32_t rank = p - lo;                      // crowded bucket: passed through as it is
+        if (hi - lo <= kBucketMax) {
+            rank = 0;
+            const unsigned long long me = ((unsigned long long)key << 32) | val;
+#pragma unroll 4
+            for (uint32_t j = lo; j < hi; ++j) {
+                const uint2 o = __ldg(pairs + j);
+                rank += ((((unsigned long long)o.x << 32) | o.y) < me) ? 1u : 0u;
+            }
+        }
+        keys_out[lo + rank] = key;
+        vals_out[lo + rank] = val;
     }
 }
 
@@ -1446,9 +1639,13 @@ offset_encode_kernel(const int64_t *__restrict__ isect_ids, const int64_t *n_ptr
     offsets[t] = (int32_t)l;
 }
 
-__global__ void init_counters_kernel(int64_t *counters) {
+// counters back to zero (depth range: empty) and, for the bucket depth sort, its 65536 cursors
+__global__ void init_counters_kernel(int64_t *counters, uint32_t *bcount) {
     chain_enter();
-    if (threadIdx.x < CNT_SLOTS) counters[threadIdx.x] = 0;
+    const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < CNT_DEV_SLOTS) counters[t] = (t == CNT_DMIN) ? 0xffffffffll : 0;
+    if (bcount != nullptr)
+        for (uint32_t i = t; i < kDepthBuckets; i += gridDim.x * blockDim.x) bcount[i] = 0u;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1467,6 +1664,8 @@ struct PlanWs {
     uint32_t *ha_cnt, *ha_out;   // row split: per (block of entries, grid row)
     uint32_t *hw_cnt, *hw_out;   // row split: per (warp of a block, grid row)
     uint32_t *rect_xw, *rect_yh; // row split: packed rectangles by flatten index
+    uint32_t *bcount, *bstart;   // bucket depth sort: [65536] counts / cursors, [65536] starts in their scan block
+    uint32_t *boff;              // [256] offsets of the scan blocks, [1] total, [256] block totals
     size_t bytes;
 };
 
@@ -1475,7 +1674,7 @@ static PlanWs carve_plan(void *ws, uint64_t total) {
     char *c = (char *)ws;
     size_t off = 0;
     auto take = [&](size_t b) { char *r = c ? c + off : nullptr; off += align256(b); return r; };
-    p.counters = (int64_t *)take(sizeof(int64_t) * CNT_SLOTS);
+    p.counters = (int64_t *)take(sizeof(int64_t) * CNT_DEV_SLOTS);
     p.hist = (uint32_t *)take(sizeof(uint32_t) * kRadixBins * kSortGrid);
     p.digit_totals = (uint32_t *)take(sizeof(uint32_t) * kRadixBins);
     p.block_sums = (unsigned long long *)take(sizeof(unsigned long long) * kSortGrid);
@@ -1493,6 +1692,9 @@ static PlanWs carve_plan(void *ws, uint64_t total) {
     p.hw_out = (uint32_t *)take(sizeof(uint32_t) * n_ha * kSplitWarps);
     p.rect_xw = (uint32_t *)take(sizeof(uint32_t) * total);
     p.rect_yh = (uint32_t *)take(sizeof(uint32_t) * total);
+    p.bcount = (uint32_t *)take(sizeof(uint32_t) * kDepthBuckets);
+    p.bstart = (uint32_t *)take(sizeof(uint32_t) * kDepthBuckets);
+    p.boff = (uint32_t *)take(sizeof(uint32_t) * (2 * kBucketScanBlocks + 1));
     p.bytes = off;
     return p;
 }
@@ -1585,36 +1787,42 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
                 "isect: tile bits (%u) + sensor bits (%u) exceed 32", g.tile_n_bits, cam_n_bits);
     SPL_REQUIRE((uint64_t)g.C * g.n_tiles <= 0xffffffffull, SPLATAD_ERR_KEY_BITS,
                 "isect: sensors * tiles does not fit 32 bits");
+    // sort: 0 = flatten order, 1 = sorted, depth order by buckets, 2 = sorted, depth order by radix passes
+    const bool buckets = sort == 1;
     {
         SPL_PROF("init_counters_kernel", st);
-        launch_chained(init_counters_kernel, 1, 32, 0, st, p.counters);
+        if (buckets) launch_chained(init_counters_kernel, kDepthBuckets / 1024, 1024, 0, st, p.counters, p.bcount);
+        else launch_chained(init_counters_kernel, 1, 32, 0, st, p.counters, (uint32_t *)nullptr);
     }
     // with few enough sensor-tiles the fill uses the row / column split: it wants the packed
     // rectangles and needs neither the emission offsets nor their block sums
     const bool split = use_split(g, sort);
     const uint32_t cgrid = min(div_up(g.total, kThreads), (uint32_t)(8 * kNumSMs));
+    // the row / column split knows the intersection count when the rectangle count ends: a host that
+    // has asked for it (to size or cut its lists) gets it from a kernel - the rectangle count itself,
+    // or the bucket scan right behind it, which also knows whether the bucket sort applies - and need
+    // not wait for the depth order
+    int64_t *early = nullptr;
+    if (split && t_early_host != nullptr) {
+        void *dptr = nullptr;
+        if (cudaHostGetDevicePointer(&dptr, t_early_host, 0) == cudaSuccess) early = (int64_t *)dptr;
+        else (void)cudaGetLastError();   // not mapped for this device: the host falls back to the event
+    }
+    const int64_t seq = t_early_seq;
+    t_early_host = nullptr;
     {
         SPL_PROF("isect_count_kernel", st);
         uint32_t *rx = split ? p.rect_xw : nullptr, *ry = split ? p.rect_yh : nullptr;
         int64_t *tot = split ? p.counters + CNT_NISECT : nullptr;
-        // the row / column split knows the intersection count when this kernel ends: a host that has
-        // asked for it (to size or cut its lists) gets it from the kernel itself and need not wait
-        // for the depth sort
-        int64_t *early = nullptr;
-        if (split && t_early_host != nullptr) {
-            void *dptr = nullptr;
-            if (cudaHostGetDevicePointer(&dptr, t_early_host, 0) == cudaSuccess) early = (int64_t *)dptr;
-            else (void)cudaGetLastError();   // not mapped for this device: the host falls back to the event
-        }
-        const int64_t seq = t_early_seq;
-        t_early_host = nullptr;
         int64_t *ticket = p.counters + CNT_TICKET;
+        int64_t *early_here = buckets ? nullptr : early;
+        const uint32_t *db = buckets ? g.depth_bits : nullptr;
         if (g.lidar)
             launch_chained(isect_count_kernel<true>, cgrid, kThreads, 0, st, g.lid, g.total, tiles_per_gauss,
-                           g.camera_ids, g.N, rx, ry, tot, ticket, early, seq);
+                           g.camera_ids, g.N, rx, ry, tot, ticket, early_here, seq, db, p.counters);
         else
             launch_chained(isect_count_kernel<false>, cgrid, kThreads, 0, st, g.cam, g.total, tiles_per_gauss,
-                           g.camera_ids, g.N, rx, ry, tot, ticket, early, seq);
+                           g.camera_ids, g.N, rx, ry, tot, ticket, early_here, seq, db, p.counters);
     }
 
     EmitArgs e{};
@@ -1622,7 +1830,36 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
     e.tiles_per_gauss = tiles_per_gauss;
     e.camera_ids = g.camera_ids;
     e.N = g.N;
-    if (sort) {
+    if (buckets) {
+        // depth order of the visible (count > 0) elements by buckets; result in keyB / valB
+        const uint32_t bgrid = div_up(g.total, kThreads);   // one element per thread: the atomics' latency needs the parallelism
+        // {bits, flatten index} pairs in bucket order: keyA and valA lie back to back in the workspace
+        // (each g.total words, 256-byte aligned), together room for g.total 8-byte pairs
+        uint2 *pairs = reinterpret_cast<uint2 *>(p.keyA);
+        {
+            SPL_PROF("depth_bucket_count_kernel", st);
+            launch_chained(depth_bucket_count_kernel, bgrid, kThreads, 0, st, g.depth_bits,
+                           (const int32_t *)tiles_per_gauss, g.total, (const int64_t *)p.counters, p.bcount);
+        }
+        {
+            SPL_PROF("depth_bucket_scan_kernel", st);
+            launch_chained(depth_bucket_scan_kernel, kBucketScanBlocks, 1024, 0, st, p.bcount, p.bstart, p.boff,
+                           p.counters, (volatile int64_t *)early, seq);
+        }
+        {
+            SPL_PROF("depth_bucket_scatter_kernel", st);
+            launch_chained(depth_bucket_scatter_kernel, bgrid, kThreads, 0, st, g.depth_bits,
+                           (const int32_t *)tiles_per_gauss, g.total, (const int64_t *)p.counters,
+                           (const uint32_t *)p.bstart, (const uint32_t *)p.boff, p.bcount, pairs);
+        }
+        {
+            SPL_PROF("depth_bucket_rank_kernel", st);
+            launch_chained(depth_bucket_rank_kernel, bgrid, kThreads, 0, st, (const int64_t *)p.counters,
+                           (const uint32_t *)p.bstart, (const uint32_t *)p.boff, (const uint2 *)pairs, p.keyB, p.valB);
+        }
+        e.order = p.valB;
+        e.n_order_ptr = p.counters + CNT_NVIS;
+    } else if (sort) {
         // stable sort of the visible (count > 0) elements by depth bits: 4 passes of 8 bits
         uint32_t *ka = p.keyA, *va = p.valA, *kb = p.keyB, *vb = p.valB;
         FinalOut nofin{};

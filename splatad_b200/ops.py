@@ -941,8 +941,12 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
     key = (kind, C, N, None if packed else total, n_tiles_total, dev.index, int(stream))
     hint = _isect_count_hint.get(key) if (deferred and sort) else None
 
+    # sorted lists: 1 = depth order by buckets (four kernels); 2 = by radix passes (twelve), for scenes
+    # whose depths crowd into few buckets (the plan says so with status bit 4; remembered per shape)
+    mode = [0 if not sort else _depth_sort_mode.get(key, 1)]
+
     def plan(slot=None):
-        _call(f"splatad_isect_{kind}_plan", *head, *geom_args, int(bool(sort)), _lib.ptr(tiles_per_gauss),
+        _call(f"splatad_isect_{kind}_plan", *head, *geom_args, mode[0], _lib.ptr(tiles_per_gauss),
               _lib.ptr(plan_ws), plan_ws.numel(), (host if slot is None else slot).data_ptr(), stream)
 
     def fill(capacity):
@@ -957,7 +961,7 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
                 # the fill knows where every tile starts (and appends the total); kept for
                 # isect_offset_encode on this tensor
                 offsets = torch.empty(n_tiles_total + 1, dtype=torch.int32, device=dev)
-            _call(f"splatad_isect_{kind}_fill", *head, *geom_args, int(bool(sort)),
+            _call(f"splatad_isect_{kind}_fill", *head, *geom_args, mode[0],
                   _lib.ptr(tiles_per_gauss), _lib.ptr(plan_ws), _lib.ptr(fill_ws),
                   fill_ws.numel() if fill_ws is not None else 0, capacity, _lib.ptr(isect_ids),
                   _lib.ptr(flatten_ids), _lib.ptr(offsets), None, stream)
@@ -972,12 +976,20 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
         if status & 2 or n_isects > 0x7FFFFFFF:
             raise RuntimeError(f"isect: {n_isects} intersections do not fit int32 flatten ids / offsets")
         _isect_count_hint[key] = n_isects
+        if status & 4 and mode[0] == 1:
+            _depth_sort_mode[key] = 2
+            return -1          # the depth buckets were too crowded: the order is not final
         return n_isects
 
     def exact():
         plan()
         torch.cuda.current_stream(dev).synchronize()
         n_isects = read_count()
+        if n_isects < 0:       # once more, with the radix depth sort
+            mode[0] = 2
+            plan()
+            torch.cuda.current_stream(dev).synchronize()
+            n_isects = read_count()
         isect_ids, flatten_ids, offsets = fill(n_isects)
         if offsets is not None:
             isect_ids._splatad_tile_offsets = (C, offsets[:n_tiles_total])
@@ -1009,6 +1021,7 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
 # (kind, shape, tile grid, device, stream) -> intersection count of the last frame of that shape on
 # that stream (see _packed_nnz_hint for why the stream is part of the key)
 _isect_count_hint: dict = {}
+_depth_sort_mode: dict = {}   # same keys -> 2 once a frame of the shape needed the radix depth sort
 
 
 class DeferredIsect:
@@ -1056,7 +1069,7 @@ class DeferredIsect:
     def resolve(self):
         if self._resolved is None:
             n_isects = self._read_count()
-            if n_isects > self._capacity:
+            if n_isects < 0 or n_isects > self._capacity:
                 return None
             isect_ids = self._isect_buf[:n_isects]
             isect_ids._splatad_tile_offsets = (self._C, self._offsets[: self._n_tiles_total])
@@ -1127,6 +1140,9 @@ class LidarFrame:
         if status & 2 or n_isects > 0x7FFFFFFF:
             raise RuntimeError(f"isect: {n_isects} intersections do not fit int32 flatten ids / offsets")
         _isect_count_hint[self._key] = n_isects
+        if status & 4:
+            _depth_sort_mode[self._key] = 2   # crowded depth buckets: this shape takes the radix sort from now on
+            return None
         if n_isects > self._capacity:
             return None
         isect_ids = self.isect_buf[:n_isects]
@@ -1162,7 +1178,7 @@ def lidar_frame_fwd(means, quats, scales, velocities, opacities_cn, lidar_featur
     stream = _lib.stream_ptr(dev)
     key = ("lidar_tiles", C, N, C * N, n_tiles_total, dev.index, int(stream))
     hint = _isect_count_hint.get(key)
-    if hint is None:
+    if hint is None or _depth_sort_mode.get(key, 1) != 1:
         return None
     capacity = hint + hint // 8 + 65536
     H, W = raster_pts.shape[1:3]

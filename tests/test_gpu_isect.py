@@ -187,3 +187,46 @@ def test_two_deferred_intersections_outstanding():
     with torch.cuda.stream(side):
         check_pair()
     side.synchronize()
+
+
+@pytest.mark.parametrize("distinct", [1, 7, 150, 3000])
+def test_depth_order_with_crowded_depths(distinct):
+    """Depth order of the visible Gaussians when many depths coincide: with `distinct` different
+    depths among 40,000 Gaussians a depth bucket holds from a dozen elements (ranked by counting) over
+    a few hundred (bitonic network in shared memory) to thousands (beyond what the bucket sort
+    orders: the plan says so and the lists come from the radix passes). All give the reference's
+    order - ties by flatten index - bit for bit, for the two-step call, for a second, hinted frame of
+    the same shape, and for the camera path."""
+    from oracle import isect
+    from splatad_b200 import ops, scenes
+    C, N = 2, 20_000
+    g = torch.Generator().manual_seed(100 + distinct)
+    eb = scenes.elevation_boundaries(scenes.beams_128(), 8)
+    means2d = torch.stack([torch.rand(C, N, generator=g) * 360 - 180, torch.rand(C, N, generator=g) * 44 - 27], -1)
+    radii = torch.rand(C, N, 2, generator=g) * torch.tensor([9.0, 3.0])
+    radii[:, ::13, 0] = 0
+    levels = torch.rand(distinct, generator=g) * 80 + 0.5
+    depths = levels[torch.randint(0, distinct, (C, N), generator=g)]
+    res, n_az = 0.2 * 32, math.ceil(360 / (0.2 * 32))
+    want = list(isect.isect_lidar_tiles(n(means2d), n(radii), n(depths), n(eb), res, -180.0))
+    want.append(isect.isect_offset_encode(want[1], C, n_az, len(eb) - 1))
+    ops._depth_sort_mode.clear()
+    _check(_run_lidar(means2d, radii, depths, eb, res, -180.0), want, f"lidar, {distinct} depths")
+    for _ in range(2):   # first deferred call leaves the hint, the second is enqueued ahead of its count
+        d = ops.isect_lidar_tiles_deferred(t(means2d), t(radii), t(depths), t(eb), res, -180.0)
+        got = d.resolve()
+        if got is None:
+            d = d.redo()
+            got = d.resolve()
+        _check((d.tiles_per_gauss, got[0], got[1]), want[:3], f"lidar deferred, {distinct} depths")
+    crowded = 2 * N * 12 // 13 / distinct > 1024
+    assert (2 in ops._depth_sort_mode.values()) == crowded
+    # camera rectangles (one 640 x 480 camera: the row / column split; packed: three cameras)
+    W, H, ts = 640, 480, 16
+    m2 = (torch.rand(1, N, 2, generator=g) * 1.2 - 0.1) * torch.tensor([W, H])
+    r2 = torch.randint(0, 40, (1, N, 2), generator=g, dtype=torch.int32)
+    d2 = depths[:1]
+    tw, th = math.ceil(W / ts), math.ceil(H / ts)
+    want = list(isect.isect_tiles(n(m2), n(r2), n(d2), ts, tw, th))
+    want.append(isect.isect_offset_encode(want[1], 1, tw, th))
+    _check(_run_cam(m2, r2, d2, ts, tw, th), want, f"camera, {distinct} depths")

@@ -188,7 +188,7 @@ def kernel_profile(fn):
     return out
 
 
-def training_step(render, cfg, leaves, flush, steps=5):
+def training_step(render, cfg, leaves, flush, steps=10):
     """Forward + backward of one frame with a fixed seeded cotangent on every float output (the
     training configuration's loss = sum(output * cotangent)): mean step time over `steps` steps by
     CUDA events, L2 flushed between steps, and the library's per-kernel timings of one step."""
@@ -211,7 +211,8 @@ def training_step(render, cfg, leaves, flush, steps=5):
         for k in leaves:
             kw[k].grad = None
 
-    for _ in range(2):
+    for _ in range(4):     # the allocator needs a few steps to hold every buffer of a step
+        flush.zero_()
         step()
     torch.cuda.synchronize()
     evs = []

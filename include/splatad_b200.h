@@ -550,6 +550,12 @@ int splatad_compute_relocation(uint32_t N, const float *opacities, const float *
  * Checks for hosts without a memory checker (no counterpart in the reference)
  * ---------------------------------------------------------------------------------------- */
 
+/* The lidar forward projection prefetches its next slab of Gaussians with bulk asynchronous copies
+ * and waits for them with a bounded number of polls; a wait that runs into its limit makes the
+ * thread block give up (its outputs stay unwritten) and is counted. *count receives the number of
+ * such give-ups since the last call, which resets it; 0 in any healthy run. Synchronises the device. */
+int splatad_async_copy_timeouts(int64_t *count);
+
 /* Validates the index lists the compositing kernels follow, without following them: every
  * flatten id of the listed part (up to tile_offsets[n_tiles] when total_follows, else n_isects)
  * is in [0, n_rows); tile_offsets (optional, [n_tiles] or [n_tiles + 1] with total_follows) are

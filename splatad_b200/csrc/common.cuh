@@ -79,6 +79,60 @@ inline void launch_chained(void (*kernel)(KP...), dim3 grid, dim3 block, size_t 
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KP>(args)...);   // errors surface in check_launch()
 }
 
+// ---------------------------------------------------------------------------------------------
+// Bulk asynchronous copies global -> shared (the TMA engine's one-dimensional form) completing on
+// an mbarrier, for kernels that prefetch their next slab of inputs while they compute on the
+// current one. Source, destination and size must be multiples of 16 bytes. Every wait is bounded:
+// after kAsyncWaitLimit polls the caller gives up, counts a timeout (splatad_async_copy_timeouts)
+// and leaves without touching the data.
+// ---------------------------------------------------------------------------------------------
+constexpr uint32_t kAsyncWaitLimit = 1u << 20;
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals) : "memory");
+}
+
+// makes the initialised barriers visible to the asynchronous proxy (follow with __syncthreads())
+__device__ __forceinline__ void mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void bulk_copy_g2s(void *dst_smem, const void *src_global, uint32_t bytes,
+                                              unsigned long long *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(dst_smem)),
+                 "l"(__cvta_generic_to_global(src_global)), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+
+// true when the barrier's phase `parity` has completed; false after kAsyncWaitLimit polls
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long *bar, uint32_t parity) {
+    const uint32_t addr = smem_addr(bar);
+    for (uint32_t i = 0; i < kAsyncWaitLimit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            "selp.u32 %0, 1, 0, p;\n"
+            "}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
 // Cooperative copy of `nfl` contiguous floats global -> shared with 128-bit loads when the
 // source is 16-byte aligned (it is whenever the tensor base is, because block slabs start at
 // multiples of 256 rows).

@@ -109,58 +109,83 @@ visible_rows_fill_kernel(uint32_t C, uint32_t N, const int32_t *__restrict__ rad
     }
 }
 
-// out[i, :] = fields gathered from row index[i] (or i). With `sensor_table`, the first two columns
-// are ids instead of gathered data: the global sensor id of pair index[i] (sensor_table[index / N])
-// and its global Gaussian id (gaussian_start + index % N), as int32 bit patterns.
+// Column of a packed row as seen by one lane: which field it belongs to and where inside it. A
+// lane keeps the same columns for every row it visits (column = lane + 32 k), so the lookup happens
+// once per kernel, not once per word.
+constexpr int kColsPerLane = 4;   // rows of up to 128 words
+struct LaneCols {
+    uint32_t *ptr[kColsPerLane];     // field base (source or destination); nullptr: no such field / column
+    int32_t width[kColsPerLane];     // words per row of that field
+    int32_t off[kColsPerLane];       // word inside the field's row
+    int32_t kind[kColsPerLane];      // 0 data, 1 sensor id column, 2 Gaussian id column, -1 beyond the row
+};
+
+__device__ __forceinline__ LaneCols lane_columns(const RowFields &f, int32_t id_cols, bool as_dst, uint32_t lane) {
+    LaneCols lc;
+    const int32_t W = f.col[f.n];
+#pragma unroll
+    for (int k = 0; k < kColsPerLane; ++k) {
+        const int32_t c = (int32_t)lane + 32 * k;
+        lc.ptr[k] = nullptr; lc.width[k] = 0; lc.off[k] = 0; lc.kind[k] = -1;
+        if (c >= W + id_cols) continue;
+        if (c < id_cols) { lc.kind[k] = 1 + c; continue; }
+        const int32_t cc = c - id_cols;
+        int q = 0;
+        for (int t = 1; t < kMaxFields; ++t) q += (t < f.n && cc >= f.col[t]) ? 1 : 0;
+        lc.kind[k] = 0;
+        lc.ptr[k] = as_dst ? f.dst[q] : const_cast<uint32_t *>(f.src[q]);
+        lc.width[k] = f.col[q + 1] - f.col[q];
+        lc.off[k] = cc - f.col[q];
+    }
+    return lc;
+}
+
+// out[i, :] = fields gathered from row index[i] (or i): one warp per row, one lane per column. With
+// `sensor_table`, the first two columns are ids instead of gathered data: the global sensor id of
+// pair index[i] (sensor_table[index / N]) and its global Gaussian id (gaussian_start + index % N),
+// as int32 bit patterns.
 __global__ void __launch_bounds__(kThreads)
 rows_gather_kernel(RowFields f, int64_t n_rows, const int32_t *__restrict__ index,
                    const int32_t *__restrict__ sensor_table, uint32_t N, int32_t gaussian_start,
                    uint32_t *__restrict__ out) {
-    const int32_t W = f.col[f.n];
+    const uint32_t lane = threadIdx.x & 31;
     const int32_t id_cols = sensor_table ? 2 : 0;
-    const int64_t total = n_rows * (W + id_cols);
-    for (int64_t e = (int64_t)blockIdx.x * kThreads + threadIdx.x; e < total;
-         e += (int64_t)gridDim.x * kThreads) {
-        const int64_t i = e / (W + id_cols);
-        const int32_t c = (int32_t)(e - i * (W + id_cols));
+    const int32_t Wt = f.col[f.n] + id_cols;
+    const LaneCols lc = lane_columns(f, id_cols, false, lane);
+    const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
+    for (int64_t i = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); i < n_rows; i += n_warps) {
         const int64_t r = index ? (int64_t)__ldg(index + i) : i;
-        uint32_t v = 0;
-        if (c < id_cols) {
-            v = (c == 0) ? (uint32_t)__ldg(sensor_table + r / N) : (uint32_t)(gaussian_start + (int32_t)(r % N));
-        } else {
-            const int32_t cc = c - id_cols;
-            int k = 0;
 #pragma unroll
-            for (int q = 1; q < kMaxFields; ++q) k += (q < f.n && cc >= f.col[q]) ? 1 : 0;
-            if (f.src[k]) v = __ldg(f.src[k] + r * (f.col[k + 1] - f.col[k]) + (cc - f.col[k]));
+        for (int k = 0; k < kColsPerLane; ++k) {
+            if (lc.kind[k] < 0) continue;
+            uint32_t v = 0;
+            if (lc.kind[k] == 1) v = (uint32_t)__ldg(sensor_table + r / N);
+            else if (lc.kind[k] == 2) v = (uint32_t)(gaussian_start + (int32_t)(r % N));
+            else if (lc.ptr[k]) v = __ldg(lc.ptr[k] + r * lc.width[k] + lc.off[k]);
+            out[i * Wt + lane + 32 * k] = v;
         }
-        out[e] = v;
     }
 }
 
-// dst_k[index[i] (or i), :] = in[i, columns of field k]; with `ids_out`, the two leading id columns
-// of the rows are widened to int64 into ids_out[0] (sensor) and ids_out[1] (Gaussian).
+// dst_k[index[i] (or i), :] = in[i, columns of field k]: one warp per row; the two leading id
+// columns of the rows (id_cols = 2) are widened to int64 into sensor_ids_out / gaussian_ids_out.
 __global__ void __launch_bounds__(kThreads)
 rows_scatter_kernel(RowFields f, int64_t n_rows, const int32_t *__restrict__ index, int32_t id_cols,
                     int64_t *__restrict__ sensor_ids_out, int64_t *__restrict__ gaussian_ids_out,
                     const uint32_t *__restrict__ in) {
-    const int32_t W = f.col[f.n];
-    const int64_t total = n_rows * (W + id_cols);
-    for (int64_t e = (int64_t)blockIdx.x * kThreads + threadIdx.x; e < total;
-         e += (int64_t)gridDim.x * kThreads) {
-        const int64_t i = e / (W + id_cols);
-        const int32_t c = (int32_t)(e - i * (W + id_cols));
+    const uint32_t lane = threadIdx.x & 31;
+    const int32_t Wt = f.col[f.n] + id_cols;
+    const LaneCols lc = lane_columns(f, id_cols, true, lane);
+    const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
+    for (int64_t i = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); i < n_rows; i += n_warps) {
         const int64_t r = index ? (int64_t)__ldg(index + i) : i;
-        const uint32_t v = __ldg(in + e);
-        if (c < id_cols) {
-            int64_t *o = (c == 0) ? sensor_ids_out : gaussian_ids_out;
-            if (o) o[r] = (int64_t)(int32_t)v;
-        } else {
-            const int32_t cc = c - id_cols;
-            int k = 0;
 #pragma unroll
-            for (int q = 1; q < kMaxFields; ++q) k += (q < f.n && cc >= f.col[q]) ? 1 : 0;
-            if (f.dst[k]) f.dst[k][r * (f.col[k + 1] - f.col[k]) + (cc - f.col[k])] = v;
+        for (int k = 0; k < kColsPerLane; ++k) {
+            if (lc.kind[k] < 0) continue;
+            const uint32_t v = __ldg(in + i * Wt + lane + 32 * k);
+            if (lc.kind[k] == 1) { if (sensor_ids_out) sensor_ids_out[r] = (int64_t)(int32_t)v; }
+            else if (lc.kind[k] == 2) { if (gaussian_ids_out) gaussian_ids_out[r] = (int64_t)(int32_t)v; }
+            else if (lc.ptr[k]) lc.ptr[k][r * lc.width[k] + lc.off[k]] = v;
         }
     }
 }
@@ -276,7 +301,9 @@ extern "C" int splatad_rows_gather(int64_t n_rows, const int32_t *index, int32_t
     SPL_REQUIRE(!sensor_table || (index && n_per_sensor > 0), SPLATAD_ERR_BAD_ARG,
                 "rows_gather: id columns need the pair index and the Gaussians per sensor");
     if (n_rows == 0) return SPLATAD_OK;
-    const int64_t elems = n_rows * (f.col[f.n] + (sensor_table ? 2 : 0));
+    SPL_REQUIRE(f.col[f.n] + (sensor_table ? 2 : 0) <= 32 * kColsPerLane, SPLATAD_ERR_BAD_ARG,
+                "rows_gather: rows of at most %d words", 32 * kColsPerLane);
+    const int64_t elems = n_rows * 32;   // one warp per row
     {
         SPL_PROF("rows_gather_kernel", (cudaStream_t)stream);
         rows_gather_kernel<<<grid_for(elems), kThreads, 0, (cudaStream_t)stream>>>(
@@ -295,7 +322,9 @@ extern "C" int splatad_rows_scatter(int64_t n_rows, const int32_t *index, int32_
     SPL_REQUIRE(id_cols == 0 || id_cols == 2, SPLATAD_ERR_BAD_ARG, "rows_scatter: id_cols must be 0 or 2");
     SPL_REQUIRE(n_rows >= 0 && (n_rows == 0 || in), SPLATAD_ERR_BAD_ARG, "rows_scatter: null input");
     if (n_rows == 0) return SPLATAD_OK;
-    const int64_t elems = n_rows * (f.col[f.n] + id_cols);
+    SPL_REQUIRE(f.col[f.n] + id_cols <= 32 * kColsPerLane, SPLATAD_ERR_BAD_ARG,
+                "rows_scatter: rows of at most %d words", 32 * kColsPerLane);
+    const int64_t elems = n_rows * 32;   // one warp per row
     {
         SPL_PROF("rows_scatter_kernel", (cudaStream_t)stream);
         rows_scatter_kernel<<<grid_for(elems), kThreads, 0, (cudaStream_t)stream>>>(

@@ -329,9 +329,9 @@ lidar_projection_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ me
                             float *__restrict__ radii, float *__restrict__ means2d,
                             float *__restrict__ depths, float *__restrict__ conics,
                             float *__restrict__ compensations, float *__restrict__ pix_vels,
-                            float *__restrict__ depth_comps) {
+                            float *__restrict__ depth_comps, uint32_t first_block) {
     __shared__ __align__(16) float smem[kStageFloats];
-    const uint32_t g0 = blockIdx.x * kThreads;
+    const uint32_t g0 = (blockIdx.x + first_block) * kThreads;
     const uint32_t n = min((uint32_t)kThreads, N - g0);
     const uint32_t t = threadIdx.x;
     const bool live = t < n;
@@ -360,6 +360,106 @@ lidar_projection_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ me
         stage_out(conics + base * 3, smem, n * 3);
         stage_out(pix_vels + base * 3, smem + kThreads * 3, n * 3);
         __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Lidar forward, pipelined: a persistent grid (four CTAs per SM) walks the full slabs of 256
+// Gaussians; while a CTA computes on one slab, the bulk-copy engine fetches its next one (means,
+// quats, scales, velocities: four one-dimensional bulk copies completing on an mbarrier) into the
+// other half of a double buffer. The profile of the one-slab-per-CTA kernel showed its largest
+// stalls at the slab loads and the barriers around them. Same arithmetic, same outputs; the tail
+// of fewer than 256 Gaussians and inputs that are not 16-byte aligned go through that kernel.
+// ---------------------------------------------------------------------------------------
+struct __align__(128) ProjSlab {
+    float mean[kThreads * 3];
+    float quat[kThreads * 4];
+    float scale[kThreads * 3];
+    float vel[kThreads * 3];
+};
+
+static __device__ unsigned long long g_async_copy_timeouts = 0ull;
+
+__global__ void __launch_bounds__(kThreads, 4)
+lidar_projection_fwd_pipelined_kernel(uint32_t C, uint32_t N, uint32_t n_slabs, const float *__restrict__ means,
+                                      const float *__restrict__ quats, const float *__restrict__ scales,
+                                      const float *__restrict__ velocities, const float *__restrict__ viewmats,
+                                      float min_el, float max_el, float min_az, float max_az,
+                                      const float *__restrict__ lin_vel, const float *__restrict__ ang_vel,
+                                      const float *__restrict__ rs_time, float eps2d, float near_plane,
+                                      float far_plane, float radius_clip, float *__restrict__ radii,
+                                      float *__restrict__ means2d, float *__restrict__ depths,
+                                      float *__restrict__ conics, float *__restrict__ compensations,
+                                      float *__restrict__ pix_vels, float *__restrict__ depth_comps) {
+    __shared__ ProjSlab slab[2];
+    __shared__ __align__(16) float s_out[kThreads * 6];
+    __shared__ __align__(8) unsigned long long bar[2];
+    const uint32_t t = threadIdx.x;
+    const bool has_vel = velocities != nullptr;
+    const uint32_t slab_bytes = (uint32_t)sizeof(float) * kThreads * (has_vel ? 13u : 10u);
+    if (t == 0) {
+        mbar_init(&bar[0], 1);
+        mbar_init(&bar[1], 1);
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    auto fetch = [&](uint32_t s, uint32_t b) {   // thread 0: slab s into buffer b
+        mbar_arrive_expect_tx(&bar[b], slab_bytes);
+        bulk_copy_g2s(slab[b].mean, means + (size_t)s * kThreads * 3, sizeof(float) * kThreads * 3, &bar[b]);
+        bulk_copy_g2s(slab[b].quat, quats + (size_t)s * kThreads * 4, sizeof(float) * kThreads * 4, &bar[b]);
+        bulk_copy_g2s(slab[b].scale, scales + (size_t)s * kThreads * 3, sizeof(float) * kThreads * 3, &bar[b]);
+        if (has_vel)
+            bulk_copy_g2s(slab[b].vel, velocities + (size_t)s * kThreads * 3, sizeof(float) * kThreads * 3, &bar[b]);
+    };
+
+    uint32_t parity[2] = {0u, 0u};
+    uint32_t b = 0;
+    if (t == 0 && blockIdx.x < n_slabs) fetch(blockIdx.x, 0);
+    for (uint32_t s = blockIdx.x; s < n_slabs; s += gridDim.x, b ^= 1u) {
+        const uint32_t next = s + gridDim.x;
+        // buffer b ^ 1 was read in the previous round, which ended with a barrier
+        if (t == 0 && next < n_slabs) fetch(next, b ^ 1u);
+        const bool arrived = mbar_wait_bounded(&bar[b], parity[b]);
+        if (!__syncthreads_and(arrived)) {
+            // a copy did not complete within the limit: count it, give the copies in flight one more
+            // bounded chance to land (their target is this CTA's shared memory), and leave
+            if (t == 0) atomicAdd(&g_async_copy_timeouts, 1ull);
+            mbar_wait_bounded(&bar[b], parity[b]);
+            if (next < n_slabs) mbar_wait_bounded(&bar[b ^ 1u], parity[b ^ 1u]);
+            return;
+        }
+        parity[b] ^= 1u;
+        const ProjSlab &in = slab[b];
+        const V3 mean = ld3(in.mean + 3 * t);
+        const V3 scale = ld3(in.scale + 3 * t);
+        const float4 q = reinterpret_cast<const float4 *>(in.quat)[t];
+        const V3 vel = has_vel ? ld3(in.vel + 3 * t) : v3(0.f, 0.f, 0.f);
+        __syncthreads();   // every thread has its inputs: the buffer may be refilled next round
+        V4 quat;
+        quat.x = q.x; quat.y = q.y; quat.z = q.z; quat.w = q.w;
+        const Sym3 covar = to_sym(quat_scale_to_covar(quat, scale));
+        const uint32_t g0 = s * kThreads;
+        for (uint32_t c = 0; c < C; ++c) {
+            SensorLidar sen = load_lidar(viewmats, lin_vel, ang_vel, rs_time, c);
+            LidarProj o = project_lidar(sen, mean, covar, has_vel, vel, min_el, max_el, min_az, max_az, eps2d,
+                                        near_plane, far_plane, radius_clip);
+            const size_t base = (size_t)c * N + g0;
+            const size_t i = base + t;
+            reinterpret_cast<float2 *>(radii)[i] = make_float2(o.ex, o.ey);
+            reinterpret_cast<float2 *>(means2d)[i] = make_float2(o.mean2d.x, o.mean2d.y);
+            reinterpret_cast<float2 *>(depth_comps)[i] = make_float2(o.depth_comp.x, o.depth_comp.y);
+            depths[i] = o.depth;
+            if (compensations != nullptr) compensations[i] = o.comp;
+            s_out[3 * t + 0] = o.conic[0]; s_out[3 * t + 1] = o.conic[1]; s_out[3 * t + 2] = o.conic[2];
+            s_out[kThreads * 3 + 3 * t + 0] = o.pix_vel.x;
+            s_out[kThreads * 3 + 3 * t + 1] = o.pix_vel.y;
+            s_out[kThreads * 3 + 3 * t + 2] = o.pix_vel.z;
+            __syncthreads();
+            stage_out(conics + base * 3, s_out, kThreads * 3);
+            stage_out(pix_vels + base * 3, s_out + kThreads * 3, kThreads * 3);
+            __syncthreads();
+        }
     }
 }
 
@@ -891,15 +991,48 @@ extern "C" int splatad_lidar_projection_fwd(
     SPL_REQUIRE(radii && means2d && depths && conics && pix_vels && depth_compensations,
                 SPLATAD_ERR_BAD_ARG, "lidar_projection_fwd: null output");
     if (C == 0 || N == 0) return SPLATAD_OK;
-    {
-        SPL_PROF("lidar_projection_fwd_kernel", (cudaStream_t)stream);
-        lidar_projection_fwd_kernel<<<div_up(N, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+    cudaStream_t st = (cudaStream_t)stream;
+    // full slabs of 256 Gaussians through the pipelined kernel when the bulk copies' 16-byte rule
+    // holds for every input (and, for the 128-bit output staging, for conics and pix_vels with every
+    // sensor's offset); the rest - a tail, covariance inputs, odd alignments - through the plain kernel
+    auto aligned16 = [](const void *ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
+    uint32_t n_slabs = 0;
+    if (covars == nullptr && aligned16(means) && aligned16(quats) && aligned16(scales) &&
+        (velocities == nullptr || aligned16(velocities)))
+        n_slabs = N / kThreads;
+    if (n_slabs > 0) {
+        SPL_PROF("lidar_projection_fwd_kernel", st);
+        const uint32_t grid = n_slabs < (uint32_t)(4 * kNumSMs) ? n_slabs : (uint32_t)(4 * kNumSMs);
+        lidar_projection_fwd_pipelined_kernel<<<grid, kThreads, 0, st>>>(
+            C, N, n_slabs, means, quats, scales, velocities, viewmats, min_elevation, max_elevation, min_azimuth,
+            max_azimuth, linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
+            radius_clip, radii, means2d, depths, conics, compensations, pix_vels, depth_compensations);
+    }
+    if ((uint64_t)n_slabs * kThreads < N) {
+        SPL_PROF("lidar_projection_fwd_kernel", st);
+        lidar_projection_fwd_kernel<<<div_up(N, kThreads) - n_slabs, kThreads, 0, st>>>(
             C, N, means, covars, quats, scales, velocities, viewmats, min_elevation, max_elevation,
             min_azimuth, max_azimuth, linear_velocity, angular_velocity, rolling_shutter_time, eps2d,
             near_plane, far_plane, radius_clip, radii, means2d, depths, conics, compensations,
-            pix_vels, depth_compensations);
+            pix_vels, depth_compensations, n_slabs);
     }
     return check_launch("lidar_projection_fwd");
+}
+
+// Number of bulk-copy waits that ran into their limit since the last call (then reset); the kernels
+// that use such copies leave their outputs unwritten when it happens. Synchronises the device.
+extern "C" int splatad_async_copy_timeouts(int64_t *count) {
+    SPL_REQUIRE(count != nullptr, SPLATAD_ERR_BAD_ARG, "async_copy_timeouts: null output");
+    unsigned long long v = 0ull;
+    const unsigned long long zero = 0ull;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_async_copy_timeouts, sizeof(v));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_async_copy_timeouts, &zero, sizeof(zero));
+    if (e != cudaSuccess) {
+        set_last_error("async_copy_timeouts: %s", cudaGetErrorString(e));
+        return SPLATAD_ERR_CUDA;
+    }
+    *count = (int64_t)v;
+    return SPLATAD_OK;
 }
 
 extern "C" int splatad_lidar_projection_bwd(

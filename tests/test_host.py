@@ -113,3 +113,27 @@ def test_scene_generators_are_seeded_and_shaped():
     vm = scenes.yawed_camera_viewmats([0, 60, 120])
     for R in vm[:, :3, :3]:
         assert torch.allclose(R @ R.T, torch.eye(3), atol=1e-6) and float(torch.det(R)) == pytest.approx(1.0)
+
+
+def test_wait_for_count_polls_the_early_triple_and_falls_back_to_the_event():
+    """The host side of the early intersection count: the triple {count, sequence, status} that a
+    kernel stores into slot[4:7] is taken as soon as the sequence number matches; a stale sequence
+    number (the kernel never wrote) ends in the plan's own counters after the event."""
+    from splatad_b200 import _lib
+
+    class Event:
+        def __init__(self):
+            self.waited = 0
+
+        def synchronize(self):
+            self.waited += 1
+
+    slot = torch.zeros(8, dtype=torch.int64)
+    slot[0], slot[2] = 111, 1            # what the plan copies at its end
+    slot[4], slot[5], slot[6] = 222, 7, 4
+    ev = Event()
+    assert _lib.wait_for_count(slot, 7, ev) == (222, 4) and ev.waited == 0
+    assert _lib.wait_for_count(slot, 8, ev, patience_s=0.01) == (111, 1) and ev.waited == 1
+    assert _lib.wait_for_count(slot, 0, ev) == (111, 1) and ev.waited == 2     # no early request armed
+    a, b = _lib.next_sequence(), _lib.next_sequence()
+    assert b == a + 1 and a > 0

@@ -56,6 +56,22 @@ __device__ __forceinline__ void axpy_staged(float (&acc)[CDIM], const float *__r
     }
 }
 
+// acc += row * w over a staged row of exactly CDIM floats (zero behind the channels in use).
+template <int CDIM>
+__device__ __forceinline__ void axpy_staged_full(float (&acc)[CDIM], const float *__restrict__ row, float w) {
+    const float4 *r4 = reinterpret_cast<const float4 *>(row);
+    const float2 w2 = make_float2(w, w);
+#pragma unroll
+    for (int k4 = 0; k4 < CDIM / 4; ++k4) {
+        const float4 v = r4[k4];
+        // two channels per instruction: the packed multiply-add rounds each half like fmaf does
+        const float2 lo = __ffma2_rn(make_float2(v.x, v.y), w2, make_float2(acc[4 * k4 + 0], acc[4 * k4 + 1]));
+        const float2 hi = __ffma2_rn(make_float2(v.z, v.w), w2, make_float2(acc[4 * k4 + 2], acc[4 * k4 + 3]));
+        acc[4 * k4 + 0] = lo.x; acc[4 * k4 + 1] = lo.y;
+        acc[4 * k4 + 2] = hi.x; acc[4 * k4 + 3] = hi.y;
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // Camera forward. __launch_bounds__(1024): a tile may have up to 1024 pixels, and 64 registers let
 // four 256-thread CTAs share an SM (with 66 the lidar kernel got three: 2.05 rounds of its 912 CTAs
@@ -241,7 +257,9 @@ __global__ void __launch_bounds__(1024) rasterize_to_points_fwd_kernel(
 
     // with a separate range array the feature rows hold channels - 1 columns
     const uint32_t fstride = ranges ? channels - 1 : channels;
-    const uint32_t fpad = (fstride + 3u) & ~3u;
+    // a staged row holds all CDIM accumulated channels: the features, behind them the range when it
+    // comes from its own array, then zeros, so that one unconditional multiply-add pass covers them
+    constexpr uint32_t fpad = (uint32_t)CDIM;
     const bool vec = (fstride % 4u == 0u) && ((reinterpret_cast<uintptr_t>(colors) & 15u) == 0u);
     bool done = !inside;
     float T = 1.f;
@@ -263,10 +281,22 @@ __global__ void __launch_bounds__(1024) rasterize_to_points_fwd_kernel(
             sA[tr] = make_float4(xy.x, xy.y, v[0], v[1]);
             sB[tr] = make_float4(conics[3 * (size_t)g], conics[3 * (size_t)g + 1],
                                  conics[3 * (size_t)g + 2], opacities[g]);
-            sC[tr] = make_float4(v[2], dc.x, dc.y,
-                                 ranges ? ranges[g] : colors[(size_t)g * channels + depth_idx]);
+            const float range = ranges ? ranges[g] : colors[(size_t)g * channels + depth_idx];
+            sC[tr] = make_float4(v[2], dc.x, dc.y, range);
             sId[tr] = g;
-            if (stage_features && fstride) stage_row(sFeat + tr * fpad, colors, (size_t)g, fstride, vec);
+            if (stage_features) {
+                float *row = sFeat + tr * fpad;
+                uint32_t filled = 0;
+                if (fstride) {
+                    stage_row(row, colors, (size_t)g, fstride, vec);
+                    filled = (fstride + 3u) & ~3u;
+                }
+                if (ranges) {
+                    row[fstride] = range;
+                    filled = max(filled, fstride + 1u);
+                }
+                for (uint32_t k = filled; k < fpad; ++k) row[k] = 0.f;
+            }
         }
         __syncthreads();
         if (__all_sync(0xffffffffu, done)) continue;
@@ -285,12 +315,7 @@ __global__ void __launch_bounds__(1024) rasterize_to_points_fwd_kernel(
             const float4 Cc = sC[t];
             if (stage_features) {
                 // the zero padding of a staged row adds nothing to the channels behind it
-                axpy_staged<CDIM>(pix_out, sFeat + t * fpad, fstride, vis);
-                if (ranges) {
-#pragma unroll
-                    for (int k = 0; k < CDIM; ++k)
-                        if ((uint32_t)k == fstride) pix_out[k] += Cc.w * vis;
-                }
+                axpy_staged_full<CDIM>(pix_out, sFeat + t * fpad, vis);
             } else {
                 const float *c_ptr = colors + (size_t)sId[t] * fstride;
 #pragma unroll
@@ -942,8 +967,8 @@ extern "C" int splatad_rasterize_to_points_fwd(
     const uint32_t bs = ((tile_width * tile_height + 31) / 32) * 32;   // whole warps
     size_t smem = (size_t)bs * (3 * sizeof(float4) + sizeof(int32_t));
     // the batch's feature rows ride along in shared memory while a block stays under 64 KB
-    const uint32_t fcols = gaussian_ranges ? channels - 1 : channels;
-    const size_t smem_feat = (size_t)bs * ((fcols + 3u) & ~3u) * sizeof(float);
+    const uint32_t cdim = channels <= 4 ? 4u : channels <= 8 ? 8u : channels <= 16 ? 16u : channels <= 20 ? 20u : 32u;
+    const size_t smem_feat = (size_t)bs * cdim * sizeof(float);   // rows of CDIM floats, see SPL_DISPATCH_CDIM
     const uint32_t stage_features = (smem + smem_feat <= 64 * 1024) ? 1u : 0u;
     if (stage_features) smem += smem_feat;
 #define CALL(D)                                                                                   \

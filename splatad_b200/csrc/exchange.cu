@@ -112,7 +112,8 @@ visible_rows_fill_kernel(uint32_t C, uint32_t N, const int32_t *__restrict__ rad
 // Column of a packed row as seen by one lane: which field it belongs to and where inside it. A
 // lane keeps the same columns for every row it visits (column = lane + 32 k), so the lookup happens
 // once per kernel, not once per word.
-constexpr int kColsPerLane = 4;   // rows of up to 128 words
+constexpr int kMaxColsPerLane = 4;   // rows of up to 128 words
+template <int kColsPerLane>
 struct LaneCols {
     uint32_t *ptr[kColsPerLane];     // field base (source or destination); nullptr: no such field / column
     int32_t width[kColsPerLane];     // words per row of that field
@@ -120,8 +121,10 @@ struct LaneCols {
     int32_t kind[kColsPerLane];      // 0 data, 1 sensor id column, 2 Gaussian id column, -1 beyond the row
 };
 
-__device__ __forceinline__ LaneCols lane_columns(const RowFields &f, int32_t id_cols, bool as_dst, uint32_t lane) {
-    LaneCols lc;
+template <int kColsPerLane>
+__device__ __forceinline__ LaneCols<kColsPerLane> lane_columns(const RowFields &f, int32_t id_cols, bool as_dst,
+                                                                uint32_t lane) {
+    LaneCols<kColsPerLane> lc;
     const int32_t W = f.col[f.n];
 #pragma unroll
     for (int k = 0; k < kColsPerLane; ++k) {
@@ -144,6 +147,7 @@ __device__ __forceinline__ LaneCols lane_columns(const RowFields &f, int32_t id_
 // `sensor_table`, the first two columns are ids instead of gathered data: the global sensor id of
 // pair index[i] (sensor_table[index / N]) and its global Gaussian id (gaussian_start + index % N),
 // as int32 bit patterns.
+template <int kColsPerLane, int kRowsPerStep>
 __global__ void __launch_bounds__(kThreads)
 rows_gather_kernel(RowFields f, int64_t n_rows, const int32_t *__restrict__ index,
                    const int32_t *__restrict__ sensor_table, uint32_t N, int32_t gaussian_start,
@@ -151,41 +155,70 @@ rows_gather_kernel(RowFields f, int64_t n_rows, const int32_t *__restrict__ inde
     const uint32_t lane = threadIdx.x & 31;
     const int32_t id_cols = sensor_table ? 2 : 0;
     const int32_t Wt = f.col[f.n] + id_cols;
-    const LaneCols lc = lane_columns(f, id_cols, false, lane);
+    const LaneCols<kColsPerLane> lc = lane_columns<kColsPerLane>(f, id_cols, false, lane);
+    // kRowsPerStep consecutive rows per warp and step, all their loads issued before the first store:
+    // with one row in flight per warp the kernel waited on its two dependent loads (index, then data)
     const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
-    for (int64_t i = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); i < n_rows; i += n_warps) {
-        const int64_t r = index ? (int64_t)__ldg(index + i) : i;
+    const int64_t w0 = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+    for (int64_t i0 = w0 * kRowsPerStep; i0 < n_rows; i0 += n_warps * kRowsPerStep) {
+        int64_t r[kRowsPerStep];
 #pragma unroll
-        for (int k = 0; k < kColsPerLane; ++k) {
-            if (lc.kind[k] < 0) continue;
-            uint32_t v = 0;
-            if (lc.kind[k] == 1) v = (uint32_t)__ldg(sensor_table + r / N);
-            else if (lc.kind[k] == 2) v = (uint32_t)(gaussian_start + (int32_t)(r % N));
-            else if (lc.ptr[k]) v = __ldg(lc.ptr[k] + r * lc.width[k] + lc.off[k]);
-            out[i * Wt + lane + 32 * k] = v;
+        for (int j = 0; j < kRowsPerStep; ++j)
+            r[j] = (i0 + j < n_rows) ? (index ? (int64_t)__ldg(index + i0 + j) : i0 + j) : -1;
+        uint32_t v[kRowsPerStep][kColsPerLane];
+#pragma unroll
+        for (int j = 0; j < kRowsPerStep; ++j) {
+#pragma unroll
+            for (int k = 0; k < kColsPerLane; ++k) {
+                v[j][k] = 0;
+                if (lc.kind[k] < 0 || r[j] < 0) continue;
+                if (lc.kind[k] == 1) v[j][k] = (uint32_t)__ldg(sensor_table + r[j] / N);
+                else if (lc.kind[k] == 2) v[j][k] = (uint32_t)(gaussian_start + (int32_t)(r[j] % N));
+                else if (lc.ptr[k]) v[j][k] = __ldg(lc.ptr[k] + r[j] * lc.width[k] + lc.off[k]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kRowsPerStep; ++j) {
+#pragma unroll
+            for (int k = 0; k < kColsPerLane; ++k)
+                if (lc.kind[k] >= 0 && r[j] >= 0) out[(i0 + j) * Wt + lane + 32 * k] = v[j][k];
         }
     }
 }
 
 // dst_k[index[i] (or i), :] = in[i, columns of field k]: one warp per row; the two leading id
 // columns of the rows (id_cols = 2) are widened to int64 into sensor_ids_out / gaussian_ids_out.
+template <int kColsPerLane, int kRowsPerStep>
 __global__ void __launch_bounds__(kThreads)
 rows_scatter_kernel(RowFields f, int64_t n_rows, const int32_t *__restrict__ index, int32_t id_cols,
                     int64_t *__restrict__ sensor_ids_out, int64_t *__restrict__ gaussian_ids_out,
                     const uint32_t *__restrict__ in) {
     const uint32_t lane = threadIdx.x & 31;
     const int32_t Wt = f.col[f.n] + id_cols;
-    const LaneCols lc = lane_columns(f, id_cols, true, lane);
+    const LaneCols<kColsPerLane> lc = lane_columns<kColsPerLane>(f, id_cols, true, lane);
     const int64_t n_warps = (int64_t)gridDim.x * (kThreads / 32);
-    for (int64_t i = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5); i < n_rows; i += n_warps) {
-        const int64_t r = index ? (int64_t)__ldg(index + i) : i;
+    const int64_t w0 = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+    for (int64_t i0 = w0 * kRowsPerStep; i0 < n_rows; i0 += n_warps * kRowsPerStep) {
+        int64_t r[kRowsPerStep];
+        uint32_t v[kRowsPerStep][kColsPerLane];
 #pragma unroll
-        for (int k = 0; k < kColsPerLane; ++k) {
-            if (lc.kind[k] < 0) continue;
-            const uint32_t v = __ldg(in + i * Wt + lane + 32 * k);
-            if (lc.kind[k] == 1) { if (sensor_ids_out) sensor_ids_out[r] = (int64_t)(int32_t)v; }
-            else if (lc.kind[k] == 2) { if (gaussian_ids_out) gaussian_ids_out[r] = (int64_t)(int32_t)v; }
-            else if (lc.ptr[k]) lc.ptr[k][r * lc.width[k] + lc.off[k]] = v;
+        for (int j = 0; j < kRowsPerStep; ++j) {
+            const bool live = i0 + j < n_rows;
+            r[j] = live ? (index ? (int64_t)__ldg(index + i0 + j) : i0 + j) : -1;
+#pragma unroll
+            for (int k = 0; k < kColsPerLane; ++k)
+                v[j][k] = (live && lc.kind[k] >= 0) ? __ldg(in + (i0 + j) * Wt + lane + 32 * k) : 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < kRowsPerStep; ++j) {
+            if (r[j] < 0) continue;
+#pragma unroll
+            for (int k = 0; k < kColsPerLane; ++k) {
+                if (lc.kind[k] < 0) continue;
+                if (lc.kind[k] == 1) { if (sensor_ids_out) sensor_ids_out[r[j]] = (int64_t)(int32_t)v[j][k]; }
+                else if (lc.kind[k] == 2) { if (gaussian_ids_out) gaussian_ids_out[r[j]] = (int64_t)(int32_t)v[j][k]; }
+                else if (lc.ptr[k]) lc.ptr[k][r[j] * lc.width[k] + lc.off[k]] = v[j][k];
+            }
         }
     }
 }
@@ -301,13 +334,21 @@ extern "C" int splatad_rows_gather(int64_t n_rows, const int32_t *index, int32_t
     SPL_REQUIRE(!sensor_table || (index && n_per_sensor > 0), SPLATAD_ERR_BAD_ARG,
                 "rows_gather: id columns need the pair index and the Gaussians per sensor");
     if (n_rows == 0) return SPLATAD_OK;
-    SPL_REQUIRE(f.col[f.n] + (sensor_table ? 2 : 0) <= 32 * kColsPerLane, SPLATAD_ERR_BAD_ARG,
-                "rows_gather: rows of at most %d words", 32 * kColsPerLane);
-    const int64_t elems = n_rows * 32;   // one warp per row
+    SPL_REQUIRE(f.col[f.n] + (sensor_table ? 2 : 0) <= 32 * kMaxColsPerLane, SPLATAD_ERR_BAD_ARG,
+                "rows_gather: rows of at most %d words", 32 * kMaxColsPerLane);
+    // rows of up to 64 words (all the rows the renderer exchanges): two columns per lane, eight rows
+    // in flight per warp; wider rows: four columns, four rows
+    const bool narrow = f.col[f.n] + (sensor_table ? 2 : 0) <= 64;
+    const int64_t per_warp = narrow ? 8 : 4;
+    const int64_t elems = (n_rows + per_warp - 1) / per_warp * 32;
     {
         SPL_PROF("rows_gather_kernel", (cudaStream_t)stream);
-        rows_gather_kernel<<<grid_for(elems), kThreads, 0, (cudaStream_t)stream>>>(
-            f, n_rows, index, sensor_table, n_per_sensor ? n_per_sensor : 1u, gaussian_start, (uint32_t *)out);
+        if (narrow)
+            rows_gather_kernel<2, 8><<<grid_for(elems), kThreads, 0, (cudaStream_t)stream>>>(
+                f, n_rows, index, sensor_table, n_per_sensor ? n_per_sensor : 1u, gaussian_start, (uint32_t *)out);
+        else
+            rows_gather_kernel<4, 4><<<grid_for(elems), kThreads, 0, (cudaStream_t)stream>>>(
+                f, n_rows, index, sensor_table, n_per_sensor ? n_per_sensor : 1u, gaussian_start, (uint32_t *)out);
     }
     return check_launch("rows_gather");
 }
@@ -322,13 +363,19 @@ extern "C" int splatad_rows_scatter(int64_t n_rows, const int32_t *index, int32_
     SPL_REQUIRE(id_cols == 0 || id_cols == 2, SPLATAD_ERR_BAD_ARG, "rows_scatter: id_cols must be 0 or 2");
     SPL_REQUIRE(n_rows >= 0 && (n_rows == 0 || in), SPLATAD_ERR_BAD_ARG, "rows_scatter: null input");
     if (n_rows == 0) return SPLATAD_OK;
-    SPL_REQUIRE(f.col[f.n] + id_cols <= 32 * kColsPerLane, SPLATAD_ERR_BAD_ARG,
-                "rows_scatter: rows of at most %d words", 32 * kColsPerLane);
-    const int64_t elems = n_rows * 32;   // one warp per row
+    SPL_REQUIRE(f.col[f.n] + id_cols <= 32 * kMaxColsPerLane, SPLATAD_ERR_BAD_ARG,
+                "rows_scatter: rows of at most %d words", 32 * kMaxColsPerLane);
+    const bool narrow = f.col[f.n] + id_cols <= 64;
+    const int64_t per_warp = narrow ? 8 : 4;
+    const int64_t elems = (n_rows + per_warp - 1) / per_warp * 32;
     {
         SPL_PROF("rows_scatter_kernel", (cudaStream_t)stream);
-        rows_scatter_kernel<<<grid_for(elems), kThreads, 0, (cudaStream_t)stream>>>(
-            f, n_rows, index, id_cols, sensor_ids_out, gaussian_ids_out, (const uint32_t *)in);
+        if (narrow)
+            rows_scatter_kernel<2, 8><<<grid_for(elems), kThreads, 0, (cudaStream_t)stream>>>(
+                f, n_rows, index, id_cols, sensor_ids_out, gaussian_ids_out, (const uint32_t *)in);
+        else
+            rows_scatter_kernel<4, 4><<<grid_for(elems), kThreads, 0, (cudaStream_t)stream>>>(
+                f, n_rows, index, id_cols, sensor_ids_out, gaussian_ids_out, (const uint32_t *)in);
     }
     return check_launch("rows_scatter");
 }

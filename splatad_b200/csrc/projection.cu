@@ -329,9 +329,9 @@ lidar_projection_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ me
                             float *__restrict__ radii, float *__restrict__ means2d,
                             float *__restrict__ depths, float *__restrict__ conics,
                             float *__restrict__ compensations, float *__restrict__ pix_vels,
-                            float *__restrict__ depth_comps, uint32_t first_block) {
+                            float *__restrict__ depth_comps) {
     __shared__ __align__(16) float smem[kStageFloats];
-    const uint32_t g0 = (blockIdx.x + first_block) * kThreads;
+    const uint32_t g0 = blockIdx.x * kThreads;
     const uint32_t n = min((uint32_t)kThreads, N - g0);
     const uint32_t t = threadIdx.x;
     const bool live = t < n;
@@ -368,8 +368,10 @@ lidar_projection_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ me
 // Gaussians; while a CTA computes on one slab, the bulk-copy engine fetches its next one (means,
 // quats, scales, velocities: four one-dimensional bulk copies completing on an mbarrier) into the
 // other half of a double buffer. The profile of the one-slab-per-CTA kernel showed its largest
-// stalls at the slab loads and the barriers around them. Same arithmetic, same outputs; the tail
-// of fewer than 256 Gaussians and inputs that are not 16-byte aligned go through that kernel.
+// stalls at the slab loads and the barriers around them. Same arithmetic, same outputs; a ragged
+// last slab is one more round filled with plain loads (a second launch for it cost as much as a
+// fifth of the whole projection). Inputs that are not 16-byte aligned, covariance inputs and scenes
+// of fewer than 256 Gaussians go through that kernel.
 // ---------------------------------------------------------------------------------------
 struct __align__(128) ProjSlab {
     float mean[kThreads * 3];
@@ -413,24 +415,42 @@ lidar_projection_fwd_pipelined_kernel(uint32_t C, uint32_t N, uint32_t n_slabs, 
             bulk_copy_g2s(slab[b].vel, velocities + (size_t)s * kThreads * 3, sizeof(float) * kThreads * 3, &bar[b]);
     };
 
+    // n_slabs counts the full slabs; a ragged last slab (N not a multiple of 256) is one more round
+    // for the CTA whose turn it is, filled with plain loads
+    const uint32_t n_rounds = n_slabs + ((uint64_t)n_slabs * kThreads < N ? 1u : 0u);
     uint32_t parity[2] = {0u, 0u};
     uint32_t b = 0;
     if (t == 0 && blockIdx.x < n_slabs) fetch(blockIdx.x, 0);
-    for (uint32_t s = blockIdx.x; s < n_slabs; s += gridDim.x, b ^= 1u) {
+    for (uint32_t s = blockIdx.x; s < n_rounds; s += gridDim.x, b ^= 1u) {
         const uint32_t next = s + gridDim.x;
+        const uint32_t n = min((uint32_t)kThreads, N - s * kThreads);
+        const bool live = t < n;
         // buffer b ^ 1 was read in the previous round, which ended with a barrier
         if (t == 0 && next < n_slabs) fetch(next, b ^ 1u);
-        const bool arrived = mbar_wait_bounded(&bar[b], parity[b]);
-        if (!__syncthreads_and(arrived)) {
-            // a copy did not complete within the limit: count it, give the copies in flight one more
-            // bounded chance to land (their target is this CTA's shared memory), and leave
-            if (t == 0) atomicAdd(&g_async_copy_timeouts, 1ull);
-            mbar_wait_bounded(&bar[b], parity[b]);
-            if (next < n_slabs) mbar_wait_bounded(&bar[b ^ 1u], parity[b ^ 1u]);
-            return;
+        if (s < n_slabs) {
+            const bool arrived = mbar_wait_bounded(&bar[b], parity[b]);
+            if (!__syncthreads_and(arrived)) {
+                // a copy did not complete within the limit: count it, give the copies in flight one more
+                // bounded chance to land (their target is this CTA's shared memory), and leave
+                if (t == 0) atomicAdd(&g_async_copy_timeouts, 1ull);
+                mbar_wait_bounded(&bar[b], parity[b]);
+                if (next < n_slabs) mbar_wait_bounded(&bar[b ^ 1u], parity[b ^ 1u]);
+                return;
+            }
+            parity[b] ^= 1u;
+        } else {
+            // no copy was issued into this buffer for the ragged slab
+            const size_t g = (size_t)s * kThreads;
+            for (uint32_t i = t; i < n * 3; i += kThreads) {
+                slab[b].mean[i] = means[g * 3 + i];
+                slab[b].scale[i] = scales[g * 3 + i];
+                if (has_vel) slab[b].vel[i] = velocities[g * 3 + i];
+            }
+            for (uint32_t i = t; i < n * 4; i += kThreads) slab[b].quat[i] = quats[g * 4 + i];
+            __syncthreads();
         }
-        parity[b] ^= 1u;
         const ProjSlab &in = slab[b];
+        // threads beyond a ragged slab's end compute on whatever the buffer holds and store nothing
         const V3 mean = ld3(in.mean + 3 * t);
         const V3 scale = ld3(in.scale + 3 * t);
         const float4 q = reinterpret_cast<const float4 *>(in.quat)[t];
@@ -446,18 +466,20 @@ lidar_projection_fwd_pipelined_kernel(uint32_t C, uint32_t N, uint32_t n_slabs, 
                                         near_plane, far_plane, radius_clip);
             const size_t base = (size_t)c * N + g0;
             const size_t i = base + t;
-            reinterpret_cast<float2 *>(radii)[i] = make_float2(o.ex, o.ey);
-            reinterpret_cast<float2 *>(means2d)[i] = make_float2(o.mean2d.x, o.mean2d.y);
-            reinterpret_cast<float2 *>(depth_comps)[i] = make_float2(o.depth_comp.x, o.depth_comp.y);
-            depths[i] = o.depth;
-            if (compensations != nullptr) compensations[i] = o.comp;
+            if (live) {
+                reinterpret_cast<float2 *>(radii)[i] = make_float2(o.ex, o.ey);
+                reinterpret_cast<float2 *>(means2d)[i] = make_float2(o.mean2d.x, o.mean2d.y);
+                reinterpret_cast<float2 *>(depth_comps)[i] = make_float2(o.depth_comp.x, o.depth_comp.y);
+                depths[i] = o.depth;
+                if (compensations != nullptr) compensations[i] = o.comp;
+            }
             s_out[3 * t + 0] = o.conic[0]; s_out[3 * t + 1] = o.conic[1]; s_out[3 * t + 2] = o.conic[2];
             s_out[kThreads * 3 + 3 * t + 0] = o.pix_vel.x;
             s_out[kThreads * 3 + 3 * t + 1] = o.pix_vel.y;
             s_out[kThreads * 3 + 3 * t + 2] = o.pix_vel.z;
             __syncthreads();
-            stage_out(conics + base * 3, s_out, kThreads * 3);
-            stage_out(pix_vels + base * 3, s_out + kThreads * 3, kThreads * 3);
+            stage_out(conics + base * 3, s_out, n * 3);
+            stage_out(pix_vels + base * 3, s_out + kThreads * 3, n * 3);
             __syncthreads();
         }
     }
@@ -992,9 +1014,8 @@ extern "C" int splatad_lidar_projection_fwd(
                 SPLATAD_ERR_BAD_ARG, "lidar_projection_fwd: null output");
     if (C == 0 || N == 0) return SPLATAD_OK;
     cudaStream_t st = (cudaStream_t)stream;
-    // full slabs of 256 Gaussians through the pipelined kernel when the bulk copies' 16-byte rule
-    // holds for every input (and, for the 128-bit output staging, for conics and pix_vels with every
-    // sensor's offset); the rest - a tail, covariance inputs, odd alignments - through the plain kernel
+    // the pipelined kernel when the bulk copies' 16-byte rule holds for every input; covariance
+    // inputs, odd alignments and scenes of fewer than 256 Gaussians through the plain kernel
     auto aligned16 = [](const void *ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; };
     uint32_t n_slabs = 0;
     if (covars == nullptr && aligned16(means) && aligned16(quats) && aligned16(scales) &&
@@ -1002,19 +1023,19 @@ extern "C" int splatad_lidar_projection_fwd(
         n_slabs = N / kThreads;
     if (n_slabs > 0) {
         SPL_PROF("lidar_projection_fwd_kernel", st);
-        const uint32_t grid = n_slabs < (uint32_t)(4 * kNumSMs) ? n_slabs : (uint32_t)(4 * kNumSMs);
+        const uint32_t n_rounds = div_up(N, kThreads);   // the ragged last slab rides along
+        const uint32_t grid = n_rounds < (uint32_t)(4 * kNumSMs) ? n_rounds : (uint32_t)(4 * kNumSMs);
         lidar_projection_fwd_pipelined_kernel<<<grid, kThreads, 0, st>>>(
             C, N, n_slabs, means, quats, scales, velocities, viewmats, min_elevation, max_elevation, min_azimuth,
             max_azimuth, linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
             radius_clip, radii, means2d, depths, conics, compensations, pix_vels, depth_compensations);
-    }
-    if ((uint64_t)n_slabs * kThreads < N) {
+    } else {
         SPL_PROF("lidar_projection_fwd_kernel", st);
-        lidar_projection_fwd_kernel<<<div_up(N, kThreads) - n_slabs, kThreads, 0, st>>>(
+        lidar_projection_fwd_kernel<<<div_up(N, kThreads), kThreads, 0, st>>>(
             C, N, means, covars, quats, scales, velocities, viewmats, min_elevation, max_elevation,
             min_azimuth, max_azimuth, linear_velocity, angular_velocity, rolling_shutter_time, eps2d,
             near_plane, far_plane, radius_clip, radii, means2d, depths, conics, compensations,
-            pix_vels, depth_compensations, n_slabs);
+            pix_vels, depth_compensations);
     }
     return check_launch("lidar_projection_fwd");
 }

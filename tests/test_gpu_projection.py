@@ -381,8 +381,8 @@ def test_spherical_harmonics(degree, golden):
 
 
 def test_lidar_projection_slab_pipeline_equals_plain_kernel():
-    """Full slabs of 256 Gaussians go through the kernel that prefetches its inputs with bulk
-    asynchronous copies, tails and inputs that are not 16-byte aligned through the plain one: the
+    """16-byte aligned inputs go through the kernel that prefetches slabs of 256 Gaussians with bulk
+    asynchronous copies (a ragged last slab included), other alignments through the plain one: the
     same Gaussians give bit-identical outputs either way, for one and several sensors, with and
     without velocities, and no copy ever ran into its wait limit."""
     import ctypes

@@ -168,14 +168,16 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi"}
 
 
-def kernel_profile(fn):
-    """Runs fn() once with the library's per-kernel event timing on; returns {name: (launches, ms)}."""
+def kernel_profile(fn, repeat=1):
+    """Runs fn() `repeat` times with the library's per-kernel event timing on; returns
+    {name: (launches, ms)} per call of fn (totals divided by `repeat`)."""
     from splatad_b200 import _lib
     lib = _lib.load()
     torch.cuda.synchronize()
     lib.splatad_profile_enable(1)
     try:
-        fn()
+        for _ in range(repeat):
+            fn()
         torch.cuda.synchronize()
         buf = ctypes.create_string_buffer(1 << 16)
         lib.splatad_profile_report(buf, len(buf))
@@ -184,7 +186,7 @@ def kernel_profile(fn):
     out = {}
     for line in buf.value.decode().splitlines():
         name, cnt, ms = line.split()
-        out[name] = (int(cnt), float(ms))
+        out[name] = (int(cnt) // repeat, float(ms) / repeat)
     return out
 
 
@@ -722,7 +724,7 @@ def run_ours(args):
     result = None
     if rank == 0:
         # ---- per-kernel breakdown and roofline of the dominant kernel (untimed extra step) -----
-        prof = kernel_profile(step)
+        prof = kernel_profile(step, repeat=N_POSES)   # one frame of every pose
         launches = int(sum(c for c, _ in prof.values()))
         kernels = {k: {"launches": c, "ms": round(ms, 4)} for k, (c, ms) in prof.items()}
         peak, peak_src = load_peaks()
@@ -774,7 +776,9 @@ def run_ours(args):
                   "n_isects": int(cam_out[2]["flatten_ids"].numel()),
                   "kernels": {k: {"launches": c, "ms": round(ms, 4)} for k, (c, ms) in cam_prof.items()}}
 
-        pairs = count_pairs_lidar(out[3], cfg)
+        # pair counts of every pose, averaged like the per-kernel times they are set against
+        per_pose = [count_pairs_lidar(splatad_b200.lidar_rasterization(**dict(cfg, viewmats=vm))[3], cfg) for vm in poses]
+        pairs = {k: int(round(sum(p[k] for p in per_pose) / len(per_pose))) for k in per_pose[0]}
         cam_pairs = count_pairs_camera(cam_out[2], cam_cfg)
         stages = roofline_stages(prof, cam_prof, n_gauss, n_vis, n_isects, n_rec, pairs, cam_pairs, peak, tfl)
 

@@ -64,7 +64,10 @@ int splatad_profile_report(char *buf, size_t cap);
  * rolling_shutter_time [C].
  * Outputs [C,N,..]: radii [.,2] float degrees, means2d [.,2], depths (range), conics [.,3],
  * compensations (NULL = not computed), pix_vels [.,3], depth_compensations [.,2].
- * Entries of culled pairs are zero. */
+ * Entries of culled pairs are zero. With quats / scales inputs whose arrays start on 16-byte
+ * boundaries the kernel prefetches slabs of 256 Gaussians with bulk asynchronous copies; any
+ * other alignment and covars inputs take a plain kernel with bit-identical outputs (see
+ * splatad_async_copy_timeouts for the copies' bounded waits). */
 int splatad_lidar_projection_fwd(
     uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,
     const float *scales, const float *velocities, const float *viewmats, float min_elevation,

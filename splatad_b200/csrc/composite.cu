@@ -420,7 +420,7 @@ __global__ void rasterize_to_pixels_bwd_kernel(
     float4 *sB = sA + bs;
     int32_t *sId = reinterpret_cast<int32_t *>(sB + bs);
     int32_t *sPos = sId + bs;                            // list position of the staged entry
-    float *sRgb = reinterpret_cast<float *>(sPos + bs);  // [bs * channels]
+    float *sRgb = reinterpret_cast<float *>(sPos + bs);  // [bs * CDIM]
     __shared__ uint32_t s_warp_kept[32];
 
     const uint32_t tiles_per_cam = tile_w * tile_h;
@@ -446,6 +446,7 @@ __global__ void rasterize_to_pixels_bwd_kernel(
     const float roll_lo = fminf(roll_a, roll_b), roll_hi = fmaxf(roll_a, roll_b);
 
     const TileRange range = tile_range(offsets, blockIdx.x, C * tiles_per_cam, n_isects);
+    const bool vec = (channels % 4u == 0u) && ((reinterpret_cast<uintptr_t>(colors) & 15u) == 0u);
 
     const float T_final = 1.f - render_alphas[pix];
     float T = T_final;
@@ -507,7 +508,10 @@ __global__ void rasterize_to_pixels_bwd_kernel(
             sB[pos] = B0;
             sId[pos] = g;
             sPos[pos] = idx;
-            for (uint32_t k = 0; k < channels; ++k) sRgb[pos * channels + k] = colors[(size_t)g * channels + k];
+            // rows of CDIM floats (channels, then zeros): the channel loops run in packed pairs
+            float *row = sRgb + pos * CDIM;
+            stage_row(row, colors, (size_t)g, channels, vec);
+            for (uint32_t k = (channels + 3u) & ~3u; k < (uint32_t)CDIM; ++k) row[k] = 0.f;
         }
         __syncthreads();
         for (uint32_t t = 0; t < n_kept; ++t) {
@@ -537,14 +541,29 @@ __global__ void rasterize_to_pixels_bwd_kernel(
                 const float ra = 1.f / (1.f - alpha);
                 T *= ra;
                 const float fac = alpha * T;
-                float v_alpha = 0.f;
-                const float *rgb = sRgb + (uint32_t)t * channels;
+                // two channels per instruction (packed FP32 multiply-adds); channels beyond the
+                // rendered ones have zero rows, zero cotangents and zero buffers
+                const float *rgb = sRgb + (uint32_t)t * CDIM;
+                const float2 fac2 = make_float2(fac, fac), T2 = make_float2(T, T), nra2 = make_float2(-ra, -ra);
+                float2 va2 = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int k = 0; k < CDIM; ++k)
-                    if ((uint32_t)k < channels) {
-                        v_rgb[k] = fac * v_render_c[k];
-                        v_alpha += (rgb[k] * T - buffer[k] * ra) * v_render_c[k];
+                for (int k = 0; k < CDIM; k += 4) {
+                    const float4 c4 = *reinterpret_cast<const float4 *>(rgb + k);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int q = k + 2 * h;
+                        const float2 c2 = h ? make_float2(c4.z, c4.w) : make_float2(c4.x, c4.y);
+                        const float2 vr2 = make_float2(v_render_c[q], v_render_c[q + 1]);
+                        const float2 b2 = make_float2(buffer[q], buffer[q + 1]);
+                        const float2 g2 = __fmul2_rn(fac2, vr2);
+                        v_rgb[q] = g2.x; v_rgb[q + 1] = g2.y;
+                        const float2 u2 = __ffma2_rn(c2, T2, __fmul2_rn(b2, nra2));   // rgb T - buffer ra
+                        va2 = __ffma2_rn(u2, vr2, va2);
+                        const float2 nb2 = __ffma2_rn(c2, fac2, b2);
+                        buffer[q] = nb2.x; buffer[q + 1] = nb2.y;
                     }
+                }
+                float v_alpha = va2.x + va2.y;
                 v_alpha += T_final * ra * v_render_a;
                 if (backgrounds != nullptr) v_alpha += -T_final * ra * bg_dot;
                 if (opac * vis <= kAlphaMax) {
@@ -560,9 +579,6 @@ __global__ void rasterize_to_pixels_bwd_kernel(
                     v_ay = fabsf(v_y);
                     v_o = vis * v_alpha;
                 }
-#pragma unroll
-                for (int k = 0; k < CDIM; ++k)
-                    if ((uint32_t)k < channels) buffer[k] += rgb[k] * fac;
             }
             // warp totals by multi-value butterflies; each total then sits on its own lane, which adds it in
             const size_t g = (size_t)sId[t];
@@ -651,6 +667,7 @@ __global__ void rasterize_to_points_bwd_kernel(
     const TileRange range = tile_range(offsets, blockIdx.x, C * tiles_per_cam, n_isects);
 
     const uint32_t fstride = ranges ? channels - 1 : channels;
+    const bool vec = (fstride % 4u == 0u) && ((reinterpret_cast<uintptr_t>(colors) & 15u) == 0u);
     const float T_final = 1.f - render_alphas[pix];
     float T = T_final;
     const int32_t bin_final = inside ? last_ids[pix] : 0;
@@ -693,8 +710,19 @@ __global__ void rasterize_to_points_bwd_kernel(
                                  conics[3 * (size_t)g + 2], opacities[g]);
             sC[tr] = make_float4(v[2], dc.x, dc.y, 0.f);
             sId[tr] = g;
-            for (uint32_t k = 0; k < fstride; ++k) sRgb[tr * channels + k] = colors[(size_t)g * fstride + k];
-            if (ranges) sRgb[tr * channels + channels - 1] = ranges[g];
+            // rows of CDIM floats: the channels, then zeros, so that the channel loops below run in
+            // packed pairs without tests
+            float *row = sRgb + tr * CDIM;
+            uint32_t filled = 0;
+            if (fstride) {
+                stage_row(row, colors, (size_t)g, fstride, vec);
+                filled = (fstride + 3u) & ~3u;
+            }
+            if (ranges) {
+                row[fstride] = ranges[g];
+                filled = max(filled, fstride + 1u);
+            }
+            for (uint32_t k = filled; k < (uint32_t)CDIM; ++k) row[k] = 0.f;
         }
         __syncthreads();
         for (int32_t t = max(0, batch_end - warp_bin_final); t < batch_size; ++t) {
@@ -725,16 +753,30 @@ __global__ void rasterize_to_points_bwd_kernel(
                 T *= ra;
                 const float fac = alpha * T;
                 const float dterm = Cc.y * dx + Cc.z * dy + Cc.x * roll;
-                float v_alpha = 0.f;
-                const float *rgb = sRgb + (uint32_t)t * channels;
+                // two channels per instruction (packed FP32 multiply-adds); channels beyond the
+                // rendered ones have zero rows, zero cotangents and zero buffers
+                const float *rgb = sRgb + (uint32_t)t * CDIM;
+                const float2 fac2 = make_float2(fac, fac), T2 = make_float2(T, T), nra2 = make_float2(-ra, -ra);
+                float2 va2 = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int k = 0; k < CDIM; ++k)
-                    if ((uint32_t)k < channels) {
-                        v_rgb[k] = fac * v_render_c[k];
-                        float bk = buffer[k];
-                        if ((uint32_t)k == depth_idx) bk += buffer_extra;
-                        v_alpha += (rgb[k] * T - bk * ra) * v_render_c[k];
+                for (int k = 0; k < CDIM; k += 4) {
+                    const float4 c4 = *reinterpret_cast<const float4 *>(rgb + k);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int q = k + 2 * h;
+                        const float2 c2 = h ? make_float2(c4.z, c4.w) : make_float2(c4.x, c4.y);
+                        const float2 vr2 = make_float2(v_render_c[q], v_render_c[q + 1]);
+                        const float2 b2 = make_float2(buffer[q], buffer[q + 1]);
+                        const float2 g2 = __fmul2_rn(fac2, vr2);
+                        v_rgb[q] = g2.x; v_rgb[q + 1] = g2.y;
+                        const float2 u2 = __ffma2_rn(c2, T2, __fmul2_rn(b2, nra2));   // rgb T - buffer ra
+                        va2 = __ffma2_rn(u2, vr2, va2);
+                        const float2 nb2 = __ffma2_rn(c2, fac2, b2);
+                        buffer[q] = nb2.x; buffer[q + 1] = nb2.y;
                     }
+                }
+                float v_alpha = va2.x + va2.y;
+                v_alpha -= buffer_extra * ra * v_depth_c;   // the depth channel's buffer also holds the compensation terms
                 const float v_rgb_depth = fac * v_depth_c;
                 v_alpha += dterm * T * v_depth_c;
                 v_alpha += T_final * ra * v_render_a;
@@ -755,9 +797,6 @@ __global__ void rasterize_to_points_bwd_kernel(
                     v_ay = fabsf(v_y);
                     v_o = vis * v_alpha;
                 }
-#pragma unroll
-                for (int k = 0; k < CDIM; ++k)
-                    if ((uint32_t)k < channels) buffer[k] += rgb[k] * fac;
                 buffer_extra += dterm * fac;
 
                 const float g_depth = rgb[depth_idx];
@@ -911,7 +950,8 @@ extern "C" int splatad_rasterize_to_pixels_bwd(
                     v_pix_vels && rolling_shutter_time,
                 SPLATAD_ERR_BAD_ARG, "rasterize_to_pixels_bwd: null argument");
     const uint32_t bs = ((tile_size * tile_size + 31) / 32) * 32;   // whole warps
-    const size_t smem = (size_t)bs * (2 * sizeof(float4) + 2 * sizeof(int32_t) + channels * sizeof(float));
+    const uint32_t cdim = channels <= 4 ? 4u : channels <= 8 ? 8u : channels <= 16 ? 16u : channels <= 20 ? 20u : 32u;
+    const size_t smem = (size_t)bs * (2 * sizeof(float4) + 2 * sizeof(int32_t) + cdim * sizeof(float));   // rows of CDIM floats
 #define CALL(D)                                                                                   \
     {                                                                                             \
         int rc = check_block_size(rasterize_to_pixels_bwd_kernel<D>, bs, channels, "rasterize_to_pixels_bwd"); \
@@ -1024,7 +1064,8 @@ extern "C" int splatad_rasterize_to_points_bwd(
     SPL_REQUIRE(!gaussian_ranges || (v_gaussian_ranges && depth_channel_idx == channels - 1),
                 SPLATAD_ERR_BAD_ARG, "rasterize_to_points_bwd: range array needs v_gaussian_ranges");
     const uint32_t bs = ((tile_width * tile_height + 31) / 32) * 32;   // whole warps
-    const size_t smem = (size_t)bs * (3 * sizeof(float4) + sizeof(int32_t) + channels * sizeof(float));
+    const uint32_t cdim = channels <= 4 ? 4u : channels <= 8 ? 8u : channels <= 16 ? 16u : channels <= 20 ? 20u : 32u;
+    const size_t smem = (size_t)bs * (3 * sizeof(float4) + sizeof(int32_t) + cdim * sizeof(float));   // rows of CDIM floats
 #define CALL(D)                                                                                   \
     {                                                                                             \
         int rc = check_block_size(rasterize_to_points_bwd_kernel<D>, bs, channels, "rasterize_to_points_bwd"); \

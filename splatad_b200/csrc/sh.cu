@@ -322,6 +322,30 @@ __device__ __forceinline__ void stage_rows_gather(const float *__restrict__ coef
     }
 }
 
+// Adds the first nfl floats of the staged rows (row stride row + 1) to the rows of dst listed in
+// rows[0 .. n) (negative = skip): consecutive threads add consecutive words of a row, four at a
+// time where the alignment allows, instead of every thread walking its own row with scalar atomics.
+__device__ __forceinline__ void scatter_rows_add(float *__restrict__ dst, const int64_t *rows, const float *smem,
+                                                 uint32_t n, uint32_t row, uint32_t nfl) {
+    if ((row & 3u) == 0 && (nfl & 3u) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+        const uint32_t per_row = nfl >> 2;
+        for (uint32_t i = threadIdx.x; i < n * per_row; i += blockDim.x) {
+            const uint32_t r = i / per_row, q = i - r * per_row;
+            const int64_t to = rows[r];
+            if (to < 0) continue;
+            const float *v = smem + r * (row + 1) + 4 * q;
+            atomicAdd(reinterpret_cast<float4 *>(dst + (size_t)to * row) + q, make_float4(v[0], v[1], v[2], v[3]));
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < n * nfl; i += blockDim.x) {
+            const uint32_t r = i / nfl, q = i - r * nfl;
+            const int64_t to = rows[r];
+            if (to < 0) continue;
+            atomicAdd(dst + (size_t)to * row + q, smem[r * (row + 1) + q]);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kShThreads)
 sh_colors_fwd_kernel(const ShColorArgs a, float *__restrict__ colors) {
     extern __shared__ __align__(16) float sm[];   // [kShThreads][3K+1] floats, then the row indices
@@ -441,15 +465,21 @@ sh_colors_bwd_kernel(const ShColorArgs a, const float *__restrict__ v_colors, fl
             }
         }
         if (v_coeffs) {
-            float *vrow = v_coeffs + (size_t)rows[t] * row;
+            // the coefficient row of this thread is no longer needed: its gradient takes its place
+            // and leaves with the block's cooperative scatter below
+            float *vrow = sm + t * (row + 1);
 #pragma unroll
             for (int i = 0; i < kShMaxBases; ++i)
                 if (i < nb) {
-                    atomicAdd(vrow + 3 * i, b[i] * vr);
-                    atomicAdd(vrow + 3 * i + 1, b[i] * vg);
-                    atomicAdd(vrow + 3 * i + 2, b[i] * vb);
+                    vrow[3 * i] = b[i] * vr;
+                    vrow[3 * i + 1] = b[i] * vg;
+                    vrow[3 * i + 2] = b[i] * vb;
                 }
         }
+    }
+    if (v_coeffs) {
+        __syncthreads();
+        scatter_rows_add(v_coeffs, rows, sm, n, row, 3 * nb);
     }
     if (v_campos) {
         // d dirs / d campos = -1: one atomic per warp when its lanes share a camera

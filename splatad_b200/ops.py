@@ -1111,6 +1111,22 @@ def _debug_check_lists(what: str, flatten_ids: Tensor, n_rows: int, isect_offset
                                f"(limit {limit})")
 
 
+def _zeros_like_many(*tensors: Optional[Tensor]) -> list:
+    """float32 zeros shaped like each given tensor (None stays None), as views of ONE zero-filled
+    buffer: one allocation and one fill for all the gradient accumulators of a backward call. Every
+    view starts on a 256-byte boundary."""
+    live = [t for t in tensors if t is not None]
+    if not live:
+        return [None] * len(tensors)
+    starts, total = [], 0
+    for t in live:
+        starts.append(total)
+        total += (t.numel() + 63) // 64 * 64
+    buf = torch.zeros(total, dtype=torch.float32, device=live[0].device)
+    views = iter(buf[s:s + t.numel()].view(t.shape) for s, t in zip(starts, live))
+    return [None if t is None else next(views) for t in tensors]
+
+
 def _n_isects_arg(isect_offsets: Tensor, flatten_ids: Tensor, total_follows: bool = False) -> int:
     """What the compositing entry points get as n_isects: the length of flatten_ids, or -1 when the
     caller states that the total sits behind the tile starts on the device (see DeferredIsect)."""
@@ -1503,12 +1519,8 @@ class _RasterizeToPixels(torch.autograd.Function):
         channels = colors.shape[-1]
         v_render_colors = _f(v_render_colors)
         v_render_alphas = _f(v_render_alphas)
-        v_means2d = torch.zeros_like(means2d, dtype=torch.float32)
-        v_conics = torch.zeros_like(conics)
-        v_colors = torch.zeros_like(colors)
-        v_opacities = torch.zeros_like(opacities)
-        v_pix_vels = torch.zeros_like(pix_vels)
-        v_abs = torch.zeros_like(v_means2d) if ctx.absgrad else None
+        v_means2d, v_conics, v_colors, v_opacities, v_pix_vels, v_abs = _zeros_like_many(
+            means2d, conics, colors, opacities, pix_vels, means2d if ctx.absgrad else None)
         _call(
             "splatad_rasterize_to_pixels_bwd", C, ctx.n_isects_arg, _lib.ptr(means2d),
             _lib.ptr(conics), _lib.ptr(colors), channels, _lib.ptr(opacities), _lib.ptr(pix_vels),
@@ -1681,17 +1693,11 @@ class _RasterizeToPoints(torch.autograd.Function):
         dev = means2d.device
         C, grid_h, grid_w = isect_offsets.shape
         channels = colors.shape[-1] + (1 if ranges is not None else 0)
-        v_ranges = torch.zeros_like(ranges) if ranges is not None else None
         v_render_colors = _f(v_render_colors)
         v_render_alphas = _f(v_render_alphas)
         v_asum = _f(v_alpha_sum) if (compute_asum and v_alpha_sum is not None) else None
-        v_means2d = torch.zeros_like(means2d, dtype=torch.float32)
-        v_conics = torch.zeros_like(conics)
-        v_colors = torch.zeros_like(colors)
-        v_opacities = torch.zeros_like(opacities)
-        v_pix_vels = torch.zeros_like(pix_vels)
-        v_depth_comps = torch.zeros_like(depth_comps)
-        v_abs = torch.zeros_like(v_means2d) if absgrad else None
+        v_means2d, v_conics, v_colors, v_opacities, v_pix_vels, v_depth_comps, v_ranges, v_abs = _zeros_like_many(
+            means2d, conics, colors, opacities, pix_vels, depth_comps, ranges, means2d if absgrad else None)
         _call(
             "splatad_rasterize_to_points_bwd", C, ctx.n_isects_arg, _lib.ptr(means2d),
             _lib.ptr(conics), _lib.ptr(colors) if colors.numel() else None, _lib.ptr(ranges), channels,

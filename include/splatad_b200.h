@@ -121,7 +121,8 @@ int splatad_projection_bwd(
  * The same workspace must be passed to both calls. _fill does not need the count on the host:
  * with outputs of `capacity` rows (from an earlier frame, say) it can be enqueued right behind
  * _count; rows at or beyond the capacity are dropped, the caller then sees nnz > capacity and
- * fills again. capacity < 0: the outputs hold nnz rows. */
+ * fills again; the rows between nnz and the capacity get camera id 0, Gaussian id 0 and radii 0
+ * (nothing lists or draws them). capacity < 0: the outputs hold nnz rows. */
 size_t splatad_projection_packed_workspace_bytes(uint32_t C, uint32_t N);
 int splatad_projection_packed_count(
     uint32_t C, uint32_t N, const float *means, const float *covars, const float *quats,

@@ -544,6 +544,7 @@ projection_packed_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ m
                              int32_t *__restrict__ block_counts,        // [C, nblocks] pass 1
                              const int32_t *__restrict__ block_offsets, // [C, nblocks] pass 2 (exclusive)
                              int64_t capacity /* rows the outputs hold; < 0: as many as needed */,
+                             const int32_t *__restrict__ counts_ro /* pass 2, capacity >= 0: pass 1's counts */,
                              int64_t *__restrict__ camera_ids, int64_t *__restrict__ gaussian_ids,
                              int32_t *__restrict__ radii, float *__restrict__ means2d,
                              float *__restrict__ depths, float *__restrict__ conics,
@@ -595,6 +596,18 @@ projection_packed_fwd_kernel(uint32_t C, uint32_t N, const float *__restrict__ m
             pix_vels[2 * row] = o.pix_vel.x;
             pix_vels[2 * row + 1] = o.pix_vel.y;
             if (compensations != nullptr) compensations[row] = o.comp;
+        }
+    }
+    // Outputs with room to spare (written before the host knows the row count): the rows behind the
+    // last packed one get ids 0 and radii 0, which every consumer skips.
+    if (block_counts == nullptr && capacity >= 0 && counts_ro != nullptr) {
+        const size_t last = (size_t)C * gridDim.x - 1;
+        const int64_t nnz = (int64_t)block_offsets[last] + counts_ro[last];
+        for (int64_t r = nnz + (int64_t)blockIdx.x * kThreads + t; r < capacity; r += (int64_t)gridDim.x * kThreads) {
+            camera_ids[r] = 0;
+            gaussian_ids[r] = 0;
+            radii[2 * r] = 0;
+            radii[2 * r + 1] = 0;
         }
     }
 }
@@ -1168,7 +1181,7 @@ extern "C" int splatad_projection_packed_count(
         projection_packed_fwd_kernel<<<nblocks, kThreads, 0, st>>>(
             C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
             linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
-            radius_clip, counts, nullptr, (int64_t)-1, nullptr, nullptr, nullptr, nullptr, nullptr,
+            radius_clip, counts, nullptr, (int64_t)-1, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
             nullptr, nullptr, nullptr);
     }
     {
@@ -1200,8 +1213,8 @@ extern "C" int splatad_projection_packed_fill(
         projection_packed_fwd_kernel<<<nblocks, kThreads, 0, (cudaStream_t)stream>>>(
             C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
             linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
-            radius_clip, nullptr, offsets, capacity, camera_ids, gaussian_ids, radii, means2d, depths,
-            conics, compensations, pix_vels);
+            radius_clip, nullptr, offsets, capacity, (const int32_t *)workspace, camera_ids, gaussian_ids, radii,
+            means2d, depths, conics, compensations, pix_vels);
     }
     return check_launch("projection_packed_fill");
 }
@@ -1309,7 +1322,7 @@ extern "C" int splatad_projection_packed_count_noalloc(
     projection_packed_fwd_kernel<<<(uint32_t)nblocks, kThreads, 0, st>>>(
         C, N, means, covars, quats, scales, velocities, viewmats, Ks, image_width, image_height,
         linear_velocity, angular_velocity, rolling_shutter_time, eps2d, near_plane, far_plane,
-        radius_clip, counts, nullptr, (int64_t)-1, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
+        radius_clip, counts, nullptr, (int64_t)-1, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr,
         nullptr, nullptr);
     packed_scan_kernel<<<1, 1024, 0, st>>>(counts, offsets, C, (uint32_t)nblocks, indptr, nnz_device);
     return check_launch("projection_packed_count_noalloc");

@@ -552,11 +552,12 @@ class _FullyFusedProjectionPacked(torch.autograd.Function):
         lib = _lib.load()
         indptr = torch.zeros(C + 1, dtype=torch.int32, device=dev)
 
-        def outputs(rows, padded=False):
-            ids = torch.zeros if padded else torch.empty   # padding rows: ids 0, radii 0
-            return (ids(rows, dtype=torch.int64, device=dev),
-                    ids(rows, dtype=torch.int64, device=dev),
-                    ids((rows, 2), dtype=torch.int32, device=dev),
+        def outputs(rows):
+            # with room to spare the fill kernel itself gives the rows behind the last packed one
+            # ids 0 and radii 0
+            return (torch.empty(rows, dtype=torch.int64, device=dev),
+                    torch.empty(rows, dtype=torch.int64, device=dev),
+                    torch.empty((rows, 2), dtype=torch.int32, device=dev),
                     torch.empty((rows, 2), dtype=torch.float32, device=dev),
                     torch.empty(rows, dtype=torch.float32, device=dev),
                     torch.empty((rows, 3), dtype=torch.float32, device=dev),
@@ -588,7 +589,7 @@ class _FullyFusedProjectionPacked(torch.autograd.Function):
             capacity = None
             if hint:
                 capacity = min((hint + hint // 8 + 4096 + 0xFFFF) & ~0xFFFF, C * N)
-                out = outputs(capacity, padded=pending is not None)
+                out = outputs(capacity)
                 fill(capacity, out)
             if pending is not None and capacity is not None:
                 # the caller carries on with padded outputs and asks for the count when it needs it

@@ -349,12 +349,24 @@ int splatad_isect_lidar_tiles_fill(
 /* No counterpart in the reference. Arms a one-shot request for the NEXT _plan call of the calling
  * thread: when the lists will be built by the row / column split (sorted output, at most 128 tile
  * rows and 16384 tiles), a kernel stores host_pair[0] = n_isects, host_pair[2] = status bits and
- * then host_pair[1] = sequence into host_pair, three int64 of pinned (mapped) host memory, as soon
+ * then host_pair[1] = sequence into host_pair, four int64 of pinned (mapped) host memory, as soon
  * as they are known - before the depth order is built, with no copy in the stream. A host that only
  * needs the count polls host_pair[1] for `sequence` (a number it has not used for this triple
  * before) instead of waiting for the end of the plan. Otherwise (other list construction, memory not mapped for the
  * device) nothing is written and the host waits for host_counts as usual. NULL disarms. */
 int splatad_isect_set_early_count(int64_t *host_pair, int64_t sequence);
+
+/* No counterpart in the reference. Arms a one-shot hint for the NEXT _plan call of the calling
+ * thread with sort = 1: the depths of the elements it will list are expected within
+ * [depth_lo, depth_hi], given as the bit patterns of two non-negative finite floats (the range the
+ * previous frame of the same sensor reported, widened a little). The depth buckets then span this
+ * range, the rectangle count fills them as it goes and the separate bucket-count kernel is not
+ * launched. The hint cannot change the result: depths outside it land in the end buckets and every
+ * bucket is put in order by its full keys; a hint so wrong that an end bucket overflows shows as
+ * status bit 4, exactly like crowded depths, and the caller repeats the plan without a hint. With
+ * an early count armed as well, host_pair[3] receives dmin bits | dmax bits << 32 of the listed
+ * elements of this plan (0 when the count comes from a kernel that does not know them). */
+int splatad_isect_set_depth_range_hint(uint32_t depth_lo_bits, uint32_t depth_hi_bits);
 
 /* isect_offset_encode_tensor - gsplat/cuda/csrc/rasterization.cu:264-285.
  * offsets [C, tile_height, tile_width] int32. */

@@ -259,7 +259,7 @@ def next_sequence() -> int:
 
 def wait_for_count(slot: torch.Tensor, sequence: int, event: torch.cuda.Event, patience_s: float = 0.02):
     """(n_isects, status) of a plan that was given ``slot`` (8 x int64 pinned: [0..3] the counters the
-    plan copies at its end, [4..6] the early triple {count, sequence, status}). Polls the triple for
+    plan copies at its end, [4..7] the early words {count, sequence, status, depth range}). Polls the triple for
     ``sequence`` - a kernel stores it there itself, long before the plan's own copy - and falls back to waiting for
     ``event`` (recorded behind the plan) when it does not show up within ``patience_s``."""
     view = slot.numpy()
@@ -272,6 +272,16 @@ def wait_for_count(slot: torch.Tensor, sequence: int, event: torch.cuda.Event, p
             return int(view[4]), int(view[6])
     event.synchronize()
     return int(view[0]), int(view[2])
+
+
+def early_depth_range(slot: torch.Tensor, sequence: int):
+    """(lo bits, hi bits) of the depth range a plan reported with its early count (slot[7], valid
+    once slot[5] holds ``sequence``), or None when it reported none."""
+    view = slot.numpy()
+    if not sequence or view[5] != sequence or view[7] == 0:
+        return None
+    word = int(view[7]) & 0xFFFFFFFFFFFFFFFF
+    return word & 0xFFFFFFFF, word >> 32
 
 
 def release_pinned_slot(slot: torch.Tensor) -> None:

@@ -37,7 +37,9 @@ static_assert(kSortGrid <= 1024, "row scan and emit scan use one thread per sort
 // counters[] slots (int64 each)
 // The first CNT_SLOTS are what the plan copies to the host; the rest is device-side state.
 enum { CNT_NISECT = 0, CNT_NVIS = 1, CNT_STATUS = 2, CNT_TICKET = 3, CNT_SLOTS = 4,
-       CNT_DMIN = 4, CNT_DMAX = 5, CNT_DEV_SLOTS = 8 };
+       CNT_DMIN = 4, CNT_DMAX = 5,   // depth range of the listed elements (float bit patterns)
+       CNT_BLO = 6, CNT_BHI = 7,     // depth range the buckets span when the caller gave one (BHI < BLO: none)
+       CNT_DEV_SLOTS = 8 };
 enum { ST_OVERFLOW_CAPACITY = 1, ST_OVERFLOW_INT32 = 2, ST_DEPTH_BUCKETS = 4 };
 
 // ---------------------------------------------------------------------------------------
@@ -179,6 +181,51 @@ __device__ __forceinline__ void stage_boundaries(GridArgs<kLidar> &a, float *sb)
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Depth order by buckets. The visible elements are ordered by (depth bits, flatten index) - what a
+// stable radix sort of the depth bits from flatten order gives - in four short kernels instead of
+// twelve. The depth range [dmin, dmax] of the listed elements comes with the rectangle count; an
+// element's bucket is its depth's position in that range, in 262144 equal steps of depth (equal
+// steps of the bit pattern would crowd the far half of the range into a few buckets): a weakly
+// monotone function of the depth, so buckets are ordered like the keys. Count per bucket (global
+// atomics), scan, scatter into bucket order with an atomic cursor per bucket (arbitrary order
+// inside a bucket), then every element finds its rank inside its bucket by counting the bucket's
+// elements that precede it in (bits, flatten index) order and is written to its final place: one
+// thread per element, neighbours share their bucket. For a million depths between 0.3 and 113 m a
+// bucket holds 4 elements on average and 17 where they are densest. Elements of a bucket with more than kBucketMax entries
+// (depths that agree to within half a millimetre by the thousand) are passed through unordered and reported
+// with status bit ST_DEPTH_BUCKETS: the caller repeats the plan with the radix sort (sort = 2).
+// ---------------------------------------------------------------------------------------
+constexpr uint32_t kDepthBuckets = 262144;
+constexpr uint32_t kBucketMax = 1024;
+constexpr uint32_t kBucketScanBlocks = kDepthBuckets / 1024;   // 256
+static_assert(kBucketScanBlocks % 32 == 0 && kBucketScanBlocks <= 1024, "block totals are scanned by one warp");
+
+struct DepthBuckets {
+    float dmin, scale;
+    __device__ __forceinline__ uint32_t operator()(uint32_t bits) const {
+        const float d = __uint_as_float(bits);
+        if (!(d == d)) return kDepthBuckets - 1;   // NaN patterns sort behind +infinity
+        const float x = (d - dmin) * scale;        // weakly monotone in d for finite dmin, scale >= 0
+        if (!(x > 0.f)) return 0u;                 // depths below a range given by the caller
+        return x >= (float)(kDepthBuckets - 1) ? kDepthBuckets - 1 : (uint32_t)x;
+    }
+};
+
+// The buckets span the range the caller gave for this frame (its last frame's, widened: depths
+// outside it fall into the end buckets, which keeps the bucket index monotone in depth, and the
+// ranks inside a bucket go by the full key) or, without one, the measured range of this frame.
+__device__ __forceinline__ DepthBuckets depth_buckets(const int64_t *counters) {
+    const bool given = (uint32_t)counters[CNT_BHI] >= (uint32_t)counters[CNT_BLO];
+    const uint32_t lo = (uint32_t)counters[given ? CNT_BLO : CNT_DMIN];
+    const uint32_t hi = min((uint32_t)counters[given ? CNT_BHI : CNT_DMAX], 0x7f800000u);   // a NaN maximum counts as +infinity
+    DepthBuckets b;
+    b.dmin = __uint_as_float(min(lo, hi));
+    const float range = __uint_as_float(hi) - b.dmin;
+    b.scale = (range > 0.f) ? (float)(kDepthBuckets - 1) / range : 0.f;   // infinite range: scale 0, one bucket
+    return b;
+}
+
 // tiles_per_gauss[idx] for every (sensor, Gaussian) / packed row. With rect_xw / rect_yh the
 // rectangle is also stored, packed into two words per element (x0 | width << 16, first grid row |
 // height << 16 with grid row = sensor * tile rows + y; 16-bit fields, used only when
@@ -186,9 +233,10 @@ __device__ __forceinline__ void stage_boundaries(GridArgs<kLidar> &a, float *sb)
 // {count, sequence number, status bits} for a polling host, stored by whichever kernel knows them first
 // into mapped pinned memory: count and status, a system-wide fence, then the sequence number.
 __device__ __forceinline__ void tell_host(volatile int64_t *early_host, int64_t seq, int64_t n_isects,
-                                          int64_t status) {
+                                          int64_t status, int64_t depth_range = 0) {
     early_host[0] = n_isects;
     early_host[2] = status;
+    early_host[3] = depth_range;   // dmin bits | dmax bits << 32 of the listed elements, 0: not known here
     __threadfence_system();
     early_host[1] = seq;
     __threadfence_system();
@@ -203,8 +251,11 @@ isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ til
                    volatile int64_t *early_host /* optional, host-mapped: {count, sequence number, status} */,
                    int64_t early_seq,
                    const uint32_t *__restrict__ depth_bits /* optional: depth range of the listed elements */,
-                   int64_t *__restrict__ counters /* with depth_bits: CNT_DMIN / CNT_DMAX / CNT_NVIS */) {
+                   int64_t *__restrict__ counters /* with depth_bits: CNT_DMIN / CNT_DMAX / CNT_NVIS */,
+                   uint32_t *__restrict__ bcount /* optional, with a given bucket range: the bucket counts */) {
     chain_enter();
+    DepthBuckets bucket{0.f, 0.f};
+    if (bcount != nullptr) bucket = depth_buckets(counters);
     __shared__ float sb[kLidar ? kMaxElevSmem : 1];
     __shared__ unsigned long long wsum[kThreads / 32];
     stage_boundaries<kLidar>(a, sb);
@@ -235,6 +286,7 @@ isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ til
             dmin = min(dmin, d);
             dmax = max(dmax, d);
             ++nvis;
+            if (bcount != nullptr) atomicAdd(&bcount[bucket(d)], 1u);
         }
     }
     if (depth_bits != nullptr) {
@@ -536,46 +588,6 @@ radix_downsweep_kernel(PassSrc s, int shift, int nbits, uint32_t mask, const uin
     }
 }
 
-// ---------------------------------------------------------------------------------------
-// Depth order by buckets. The visible elements are ordered by (depth bits, flatten index) - what a
-// stable radix sort of the depth bits from flatten order gives - in four short kernels instead of
-// twelve. The depth range [dmin, dmax] of the listed elements comes with the rectangle count; an
-// element's bucket is its depth's position in that range, in 262144 equal steps of depth (equal
-// steps of the bit pattern would crowd the far half of the range into a few buckets): a weakly
-// monotone function of the depth, so buckets are ordered like the keys. Count per bucket (global
-// atomics), scan, scatter into bucket order with an atomic cursor per bucket (arbitrary order
-// inside a bucket), then every element finds its rank inside its bucket by counting the bucket's
-// elements that precede it in (bits, flatten index) order and is written to its final place: one
-// thread per element, neighbours share their bucket. For a million depths between 0.3 and 113 m a
-// bucket holds 4 elements on average and 17 where they are densest. Elements of a bucket with more than kBucketMax entries
-// (depths that agree to within half a millimetre by the thousand) are passed through unordered and reported
-// with status bit ST_DEPTH_BUCKETS: the caller repeats the plan with the radix sort (sort = 2).
-// ---------------------------------------------------------------------------------------
-constexpr uint32_t kDepthBuckets = 262144;
-constexpr uint32_t kBucketMax = 1024;
-constexpr uint32_t kBucketScanBlocks = kDepthBuckets / 1024;   // 256
-static_assert(kBucketScanBlocks % 32 == 0 && kBucketScanBlocks <= 1024, "block totals are scanned by one warp");
-
-struct DepthBuckets {
-    float dmin, scale;
-    __device__ __forceinline__ uint32_t operator()(uint32_t bits) const {
-        const float d = __uint_as_float(bits);
-        if (!(d == d)) return kDepthBuckets - 1;   // NaN patterns sort behind +infinity
-        const float x = (d - dmin) * scale;        // weakly monotone in d for finite dmin, scale >= 0
-        return x >= (float)(kDepthBuckets - 1) ? kDepthBuckets - 1 : (uint32_t)x;
-    }
-};
-
-__device__ __forceinline__ DepthBuckets depth_buckets(const int64_t *counters) {
-    const uint32_t lo = (uint32_t)counters[CNT_DMIN];
-    const uint32_t hi = min((uint32_t)counters[CNT_DMAX], 0x7f800000u);   // a NaN maximum counts as +infinity
-    DepthBuckets b;
-    b.dmin = __uint_as_float(min(lo, hi));
-    const float range = __uint_as_float(hi) - b.dmin;
-    b.scale = (range > 0.f) ? (float)(kDepthBuckets - 1) / range : 0.f;   // infinite range: scale 0, one bucket
-    return b;
-}
-
 __global__ void __launch_bounds__(kThreads)
 depth_bucket_count_kernel(const uint32_t *__restrict__ depth_bits, const int32_t *__restrict__ tiles_per_gauss,
                           uint32_t total, const int64_t *__restrict__ counters, uint32_t *__restrict__ bcount) {
@@ -638,7 +650,9 @@ depth_bucket_scan_kernel(uint32_t *__restrict__ bcount, uint32_t *__restrict__ b
             __threadfence();
             if (early_host != nullptr)
                 tell_host(early_host, early_seq, counters[CNT_NISECT],
-                          (int64_t)atomicOr((unsigned long long *)&counters[CNT_STATUS], 0ull));
+                          (int64_t)atomicOr((unsigned long long *)&counters[CNT_STATUS], 0ull),
+                          (int64_t)(((unsigned long long)(uint32_t)counters[CNT_DMAX] << 32) |
+                                    (unsigned long long)(uint32_t)counters[CNT_DMIN]));
         }
     }
 }
@@ -1641,10 +1655,12 @@ offset_encode_kernel(const int64_t *__restrict__ isect_ids, const int64_t *n_ptr
 }
 
 // counters back to zero (depth range: empty) and, for the bucket depth sort, its 65536 cursors
-__global__ void init_counters_kernel(int64_t *counters, uint32_t *bcount) {
+__global__ void init_counters_kernel(int64_t *counters, uint32_t *bcount, uint32_t bucket_lo, uint32_t bucket_hi) {
     chain_enter();
     const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
-    if (t < CNT_DEV_SLOTS) counters[t] = (t == CNT_DMIN) ? 0xffffffffll : 0;
+    if (t < CNT_DEV_SLOTS)
+        counters[t] = (t == CNT_DMIN) ? 0xffffffffll : (t == CNT_BLO) ? (int64_t)bucket_lo
+                                                     : (t == CNT_BHI) ? (int64_t)bucket_hi : 0;
     if (bcount != nullptr)
         for (uint32_t i = t; i < kDepthBuckets; i += gridDim.x * blockDim.x) bcount[i] = 0u;
 }
@@ -1776,6 +1792,8 @@ static bool use_split(const IsectGeom &g, int sort) {
 // rectangle count kernel writes the intersection count for the host, and the number it tags it with.
 static thread_local int64_t *t_early_host = nullptr;
 static thread_local int64_t t_early_seq = 0;
+static thread_local bool t_range_given = false;
+static thread_local uint32_t t_range_lo = 0, t_range_hi = 0;
 
 // plan: counts, depth order of visible Gaussians, n_isects.
 static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, void *workspace,
@@ -1790,10 +1808,17 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
                 "isect: sensors * tiles does not fit 32 bits");
     // sort: 0 = flatten order, 1 = sorted, depth order by buckets, 2 = sorted, depth order by radix passes
     const bool buckets = sort == 1;
+    // a depth range handed over for this plan (splatad_isect_set_depth_range_hint): the rectangle count
+    // fills the buckets itself and the separate bucket count is not launched
+    const bool ranged = buckets && t_range_given && t_range_lo <= t_range_hi && t_range_hi < 0x7f800000u;
+    const uint32_t range_lo = ranged ? t_range_lo : 1u, range_hi = ranged ? t_range_hi : 0u;
+    t_range_given = false;
     {
         SPL_PROF("init_counters_kernel", st);
-        if (buckets) launch_chained(init_counters_kernel, kDepthBuckets / 1024, 1024, 0, st, p.counters, p.bcount);
-        else launch_chained(init_counters_kernel, 1, 32, 0, st, p.counters, (uint32_t *)nullptr);
+        if (buckets)
+            launch_chained(init_counters_kernel, kDepthBuckets / 1024, 1024, 0, st, p.counters, p.bcount, range_lo, range_hi);
+        else
+            launch_chained(init_counters_kernel, 1, 32, 0, st, p.counters, (uint32_t *)nullptr, 1u, 0u);
     }
     // with few enough sensor-tiles the fill uses the row / column split: it wants the packed
     // rectangles and needs neither the emission offsets nor their block sums
@@ -1820,10 +1845,12 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
         const uint32_t *db = buckets ? g.depth_bits : nullptr;
         if (g.lidar)
             launch_chained(isect_count_kernel<true>, cgrid, kThreads, 0, st, g.lid, g.total, tiles_per_gauss,
-                           g.camera_ids, g.N, rx, ry, tot, ticket, early_here, seq, db, p.counters);
+                           g.camera_ids, g.N, rx, ry, tot, ticket, early_here, seq, db, p.counters,
+                           ranged ? p.bcount : (uint32_t *)nullptr);
         else
             launch_chained(isect_count_kernel<false>, cgrid, kThreads, 0, st, g.cam, g.total, tiles_per_gauss,
-                           g.camera_ids, g.N, rx, ry, tot, ticket, early_here, seq, db, p.counters);
+                           g.camera_ids, g.N, rx, ry, tot, ticket, early_here, seq, db, p.counters,
+                           ranged ? p.bcount : (uint32_t *)nullptr);
     }
 
     EmitArgs e{};
@@ -1837,7 +1864,7 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
         // {bits, flatten index} pairs in bucket order: keyA and valA lie back to back in the workspace
         // (each g.total words, 256-byte aligned), together room for g.total 8-byte pairs
         uint2 *pairs = reinterpret_cast<uint2 *>(p.keyA);
-        {
+        if (!ranged) {
             SPL_PROF("depth_bucket_count_kernel", st);
             launch_chained(depth_bucket_count_kernel, bgrid, kThreads, 0, st, g.depth_bits,
                            (const int32_t *)tiles_per_gauss, g.total, (const int64_t *)p.counters, p.bcount);
@@ -2365,6 +2392,13 @@ extern "C" int splatad_isect_lidar_tiles_fill(
 extern "C" int splatad_isect_set_early_count(int64_t *host_pair, int64_t sequence) {
     t_early_host = host_pair;
     t_early_seq = sequence;
+    return SPLATAD_OK;
+}
+
+extern "C" int splatad_isect_set_depth_range_hint(uint32_t depth_lo_bits, uint32_t depth_hi_bits) {
+    t_range_given = true;
+    t_range_lo = depth_lo_bits;
+    t_range_hi = depth_hi_bits;
     return SPLATAD_OK;
 }
 

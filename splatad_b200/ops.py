@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import contextlib
 import ctypes
+import struct
 from typing import Optional, Tuple
 
 import torch
@@ -1022,6 +1023,7 @@ def _isect_common(kind, means2d, radii, depths, packed, n_cameras, camera_ids, g
 # (kind, shape, tile grid, device, stream) -> intersection count of the last frame of that shape on
 # that stream (see _packed_nnz_hint for why the stream is part of the key)
 _isect_count_hint: dict = {}
+_depth_range_hint: dict = {}    # per frame shape and stream: (lo bits, hi bits) of the last frame's listed depths
 _depth_sort_mode: dict = {}   # same keys -> 2 once a frame of the shape needed the radix depth sort
 
 
@@ -1146,20 +1148,28 @@ class LidarFrame:
     exact-length (isect_ids, flatten_ids), or None when the count outgrew the room the frame was
     given (the frame then has to be rendered the ordinary way)."""
 
-    def __init__(self, tensors, capacity, counted, slot, key, sequence):
+    def __init__(self, tensors, capacity, counted, slot, key, sequence, ranged=False):
         self.__dict__.update(tensors)
         self._capacity, self._counted, self._slot, self._key = capacity, counted, slot, key
-        self._sequence = sequence
+        self._sequence, self._ranged = sequence, ranged
 
     def finish(self):
         n_isects, status = _lib.wait_for_count(self._slot, self._sequence, self._counted)
+        depth_range = _lib.early_depth_range(self._slot, self._sequence)
         _lib.release_pinned_slot(self._slot)
         if status & 2 or n_isects > 0x7FFFFFFF:
             raise RuntimeError(f"isect: {n_isects} intersections do not fit int32 flatten ids / offsets")
         _isect_count_hint[self._key] = n_isects
         if status & 4:
-            _depth_sort_mode[self._key] = 2   # crowded depth buckets: this shape takes the radix sort from now on
+            if self._ranged:
+                # an end bucket overflowed under the depth range carried over from the last frame:
+                # the frame is rendered again without one
+                _depth_range_hint.pop(self._key, None)
+            else:
+                _depth_sort_mode[self._key] = 2   # crowded depth buckets: this shape takes the radix sort from now on
             return None
+        if depth_range is not None:
+            _depth_range_hint[self._key] = depth_range
         if n_isects > self._capacity:
             return None
         isect_ids = self.isect_buf[:n_isects]
@@ -1217,6 +1227,17 @@ def lidar_frame_fwd(means, quats, scales, velocities, opacities_cn, lidar_featur
     fill_ws = _lib.workspace("isect_fill", lib.splatad_isect_fill_workspace_bytes(capacity), dev)
     slot = _lib.acquire_pinned_slot(dev)
     sequence = _lib.next_sequence()   # the count kernel stores the count + this number into slot[4:6]
+    # the depth range of the last frame of this shape, widened by a tenth on either side, spans this
+    # frame's depth buckets: the rectangle count then fills them and one kernel less is launched
+    ranged = False
+    last_range = _depth_range_hint.get(key)
+    if last_range is not None:
+        lo, hi = (struct.unpack("<f", struct.pack("<I", b))[0] for b in last_range)
+        if 0.0 <= lo <= hi < float("inf"):
+            pad = 0.1 * (hi - lo) + 1e-3
+            lo_bits, hi_bits = (struct.unpack("<I", struct.pack("<f", v))[0] for v in (max(lo - pad, 0.0), hi + pad))
+            lib.splatad_isect_set_depth_range_hint(lo_bits, hi_bits)
+            ranged = True
     p = _lib.ptr
     _call("splatad_lidar_frame_fwd", C, N, p(_f(means)), p(_f(quats)), p(_f(scales)), p(_f(velocities)),
           p(_f(opacities_cn)), p(_f(lidar_features)), D, p(_f(viewmats)), p(_f(linear_velocity)),
@@ -1231,7 +1252,7 @@ def lidar_frame_fwd(means, quats, scales, velocities, opacities_cn, lidar_featur
           stream)
     counted = torch.cuda.Event()      # fallback: the counters the plan copies at its end
     counted.record(torch.cuda.current_stream(dev))
-    return LidarFrame(t, capacity, counted, slot, key, sequence)
+    return LidarFrame(t, capacity, counted, slot, key, sequence, ranged)
 
 
 @torch.no_grad()

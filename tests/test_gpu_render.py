@@ -273,6 +273,48 @@ def test_repeated_frames_skip_the_count_round_trip():
         assert_close(f"hinted grad {k}", n(grads[1][k]), n(grads[0][k]), 1e-4, 1e-7, max_bad_frac=1e-3)
 
 
+def test_depth_range_carried_over_between_lidar_frames():
+    """From the third frame of a shape on, the depth buckets span the previous frame's depth range
+    (widened) and the rectangle count fills them. Whatever that range is, the lists and the render are
+    those of a first frame; a range so wrong that an end bucket overflows is dropped, not mistaken for
+    crowded depths."""
+    import struct
+    import splatad_b200
+    from splatad_b200 import ops, scenes
+    bits = lambda v: struct.unpack("<I", struct.pack("<f", v))[0]   # noqa: E731
+    g = _to_gpu(scenes.config2(N=150_001))    # a shape of its own
+    ops._isect_count_hint.clear()
+    ops._depth_range_hint.clear()
+    first = splatad_b200.lidar_rasterization(**g)      # two-step protocol
+    second = splatad_b200.lidar_rasterization(**g)     # one call per frame; reports its depth range
+    assert len(ops._depth_range_hint) == 1
+    key = next(iter(ops._depth_range_hint))
+    lo, hi = ops._depth_range_hint[key]
+    depths = first[3]["depths"][first[3]["radii"][..., 0] > 0]
+    assert (lo, hi) == (bits(float(depths.min())), bits(float(depths.max())))
+
+    def same(frame):
+        for a, b in zip(first[:3], frame[:3]):
+            assert torch.equal(a, b)
+        for name in ("tiles_per_gauss", "isect_ids", "flatten_ids", "isect_offsets", "median_depths"):
+            assert torch.equal(first[3][name], frame[3][name]), name
+
+    same(second)
+    same(splatad_b200.lidar_rasterization(**g))        # buckets over the carried range
+    # a range that covers only the near fifth of the depths: everything else lands in the last bucket
+    ops._depth_range_hint[key] = (lo, bits(float(depths.min()) + 0.2 * float(depths.max() - depths.min())))
+    same(splatad_b200.lidar_rasterization(**g))
+    assert ops._depth_sort_mode.get(key, 1) == 1       # not taken for crowded depths
+    # the frame above dropped the range; the next one reports it again
+    assert key not in ops._depth_range_hint
+    same(splatad_b200.lidar_rasterization(**g))
+    assert ops._depth_range_hint[key] == (lo, hi)
+    # a range far beyond the scene: all depths share a few buckets at the low end
+    ops._depth_range_hint[key] = (bits(0.0), bits(1.0e6))
+    same(splatad_b200.lidar_rasterization(**g))
+    assert ops._depth_sort_mode.get(key, 1) == 1
+
+
 def test_repeated_camera_frames():
     import splatad_b200
     from splatad_b200 import ops, scenes

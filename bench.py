@@ -548,7 +548,7 @@ def roofline_stages(prof, cam_prof, n_gauss, n_vis, n_isects, n_rec, pairs, cam_
 NCU_TRAFFIC = {
     "colsplit_scatter_kernel": (229_227_008, "profiles/colsplit_and_rowsplit_scatter_config2.md"),
     "rowsplit_scatter_kernel": (64_200_000, "profiles/colsplit_and_rowsplit_scatter_config2.md"),
-    "lidar_projection_fwd_kernel": (48_988_416, "profiles/lidar_projection_fwd_config2.md"),
+    "lidar_projection_fwd_kernel": (45_829_376, "profiles/lidar_projection_fwd_config2.md"),
     "rasterize_to_points_fwd_kernel": (5_130_000, "profiles/rasterize_to_points_fwd_config2.md"),
     "depth_bucket_scatter_kernel": (11_567_616, "profiles/depth_bucket_kernels_config2.md"),
     "depth_bucket_count_kernel": (9_038_592, "profiles/depth_bucket_kernels_config2.md"),

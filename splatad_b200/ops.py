@@ -1239,17 +1239,23 @@ def lidar_frame_fwd(means, quats, scales, velocities, opacities_cn, lidar_featur
             lib.splatad_isect_set_depth_range_hint(lo_bits, hi_bits)
             ranged = True
     p = _lib.ptr
-    _call("splatad_lidar_frame_fwd", C, N, p(_f(means)), p(_f(quats)), p(_f(scales)), p(_f(velocities)),
-          p(_f(opacities_cn)), p(_f(lidar_features)), D, p(_f(viewmats)), p(_f(linear_velocity)),
-          p(_f(angular_velocity)), p(_f(rolling_shutter_time)), p(_f(raster_pts)), W, H, p(eb), n_rows + 1,
-          float(azimuth_resolution), int(tile_width), int(tile_height), float(min_azimuth), float(max_azimuth),
-          float(min_elevation), float(max_elevation), float(eps2d), float(near_plane), float(far_plane),
-          float(radius_clip), int(bool(compute_alpha_sum)), float(alpha_sum_threshold), p(t["radii"]),
-          p(t["means2d"]), p(t["depths"]), p(t["conics"]), p(t["pix_vels"]), p(t["depth_compensations"]),
-          p(t["tiles_per_gauss"]), capacity, p(t["isect_buf"]), p(t["flatten_buf"]), p(t["offsets_buf"]),
-          p(t["render"]), p(t["alphas"]), p(t["alpha_sum"]), p(t["last_ids"]), p(t["median_depths"]),
-          p(plan_ws), plan_ws.numel(), p(fill_ws), fill_ws.numel(), slot.data_ptr(), slot.data_ptr() + 32, sequence,
-          stream)
+    try:
+        _call("splatad_lidar_frame_fwd", C, N, p(_f(means)), p(_f(quats)), p(_f(scales)), p(_f(velocities)),
+              p(_f(opacities_cn)), p(_f(lidar_features)), D, p(_f(viewmats)), p(_f(linear_velocity)),
+              p(_f(angular_velocity)), p(_f(rolling_shutter_time)), p(_f(raster_pts)), W, H, p(eb), n_rows + 1,
+              float(azimuth_resolution), int(tile_width), int(tile_height), float(min_azimuth), float(max_azimuth),
+              float(min_elevation), float(max_elevation), float(eps2d), float(near_plane), float(far_plane),
+              float(radius_clip), int(bool(compute_alpha_sum)), float(alpha_sum_threshold), p(t["radii"]),
+              p(t["means2d"]), p(t["depths"]), p(t["conics"]), p(t["pix_vels"]), p(t["depth_compensations"]),
+              p(t["tiles_per_gauss"]), capacity, p(t["isect_buf"]), p(t["flatten_buf"]), p(t["offsets_buf"]),
+              p(t["render"]), p(t["alphas"]), p(t["alpha_sum"]), p(t["last_ids"]), p(t["median_depths"]),
+              p(plan_ws), plan_ws.numel(), p(fill_ws), fill_ws.numel(), slot.data_ptr(), slot.data_ptr() + 32, sequence,
+              stream)
+    except BaseException:
+        if ranged:
+            lib.splatad_isect_set_depth_range_hint(1, 0)   # disarm: no later plan of this thread inherits the range
+        _lib.release_pinned_slot(slot)
+        raise
     counted = torch.cuda.Event()      # fallback: the counters the plan copies at its end
     counted.record(torch.cuda.current_stream(dev))
     return LidarFrame(t, capacity, counted, slot, key, sequence, ranged)

@@ -710,6 +710,7 @@ def run_ours(args):
     a, b = e2e_run(args.steps)
     barrier()
     clocks = sampler.stop()
+    per_rank_sm_mhz = _all_ranks(float((clocks or {}).get("sm_mhz") or 0.0), world, dev)
     e2e_ms = _max_over_ranks(a.elapsed_time(b), world, dev)
     e2e_value = world * POINTS_PER_FRAME * args.steps / (e2e_ms * 1e-3)
     del dev_in, dev_slice
@@ -816,7 +817,9 @@ def run_ours(args):
                                                round(float(np.max(per_rank_ms)), 4)],
                          "host_in_call_ms_per_step": [round(v, 4) for v in per_rank_host],
                          "host_bound_ms_per_frame": [round(v, 4) for v in per_rank_host_bound],
-                         "what": "ms_per_step: CUDA events around each frame; host_in_call: wall time inside the "
+                         "sm_mhz": [round(v) for v in per_rank_sm_mhz],
+                         "what": "sm_mhz: every rank's median SM clock under load; "
+                                 "ms_per_step: CUDA events around each frame; host_in_call: wall time inside the "
                                  "render call (includes waiting for the frame's intersection count); host_bound: "
                                  "wall time per frame of the same call on a 2000-Gaussian scene, i.e. the host's "
                                  "own cost per frame with all ranks running"},

@@ -242,8 +242,10 @@ __device__ __forceinline__ void tell_host(volatile int64_t *early_host, int64_t 
     __threadfence_system();
 }
 
+constexpr int kCountThreads = 1024;   // few, large blocks: every block ends with a handful of same-address atomics
+
 template <bool kLidar>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kCountThreads)
 isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ tiles_per_gauss,
                    const int64_t *__restrict__ camera_ids, uint32_t N, uint32_t *__restrict__ rect_xw,
                    uint32_t *__restrict__ rect_yh, int64_t *__restrict__ n_isects,
@@ -257,7 +259,7 @@ isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ til
     DepthBuckets bucket{0.f, 0.f};
     if (bcount != nullptr) bucket = depth_buckets(counters);
     __shared__ float sb[kLidar ? kMaxElevSmem : 1];
-    __shared__ unsigned long long wsum[kThreads / 32];
+    __shared__ unsigned long long wsum[kCountThreads / 32];
     stage_boundaries<kLidar>(a, sb);
     const uint32_t tile_rows = kLidar ? a.lidar.n_tiles_elev : a.cam.tile_height;
     unsigned long long sum = 0;
@@ -315,7 +317,7 @@ isect_count_kernel(GridArgs<kLidar> a, uint32_t total, int32_t *__restrict__ til
     __syncthreads();
     if (threadIdx.x == 0) {
         unsigned long long t = 0;
-        for (int w = 0; w < kThreads / 32; ++w) t += wsum[w];
+        for (uint32_t w = 0; w < blockDim.x / 32; ++w) t += wsum[w];
         if (t) atomicAdd((unsigned long long *)n_isects, t);
         if (early_host != nullptr) {
             // the block that finishes last hands the total straight to the host (a store to mapped
@@ -1823,7 +1825,7 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
     // with few enough sensor-tiles the fill uses the row / column split: it wants the packed
     // rectangles and needs neither the emission offsets nor their block sums
     const bool split = use_split(g, sort);
-    const uint32_t cgrid = min(div_up(g.total, kThreads), (uint32_t)(8 * kNumSMs));
+    const uint32_t cgrid = min(div_up(g.total, kCountThreads), (uint32_t)(2 * kNumSMs));
     // the row / column split knows the intersection count when the rectangle count ends: a host that
     // has asked for it (to size or cut its lists) gets it from a kernel - the rectangle count itself,
     // or the bucket scan right behind it, which also knows whether the bucket sort applies - and need
@@ -1844,11 +1846,11 @@ static int isect_plan(const IsectGeom &g, int32_t *tiles_per_gauss, int sort, vo
         int64_t *early_here = buckets ? nullptr : early;
         const uint32_t *db = buckets ? g.depth_bits : nullptr;
         if (g.lidar)
-            launch_chained(isect_count_kernel<true>, cgrid, kThreads, 0, st, g.lid, g.total, tiles_per_gauss,
+            launch_chained(isect_count_kernel<true>, cgrid, kCountThreads, 0, st, g.lid, g.total, tiles_per_gauss,
                            g.camera_ids, g.N, rx, ry, tot, ticket, early_here, seq, db, p.counters,
                            ranged ? p.bcount : (uint32_t *)nullptr);
         else
-            launch_chained(isect_count_kernel<false>, cgrid, kThreads, 0, st, g.cam, g.total, tiles_per_gauss,
+            launch_chained(isect_count_kernel<false>, cgrid, kCountThreads, 0, st, g.cam, g.total, tiles_per_gauss,
                            g.camera_ids, g.N, rx, ry, tot, ticket, early_here, seq, db, p.counters,
                            ranged ? p.bcount : (uint32_t *)nullptr);
     }

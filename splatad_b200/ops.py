@@ -1117,7 +1117,7 @@ def _debug_check_lists(what: str, flatten_ids: Tensor, n_rows: int, isect_offset
 def _zeros_like_many(*tensors: Optional[Tensor]) -> list:
     """float32 zeros shaped like each given tensor (None stays None), as views of ONE zero-filled
     buffer: one allocation and one fill for all the gradient accumulators of a backward call. Every
-    view starts on a 256-byte boundary."""
+    view starts a multiple of 256 bytes behind the buffer's start."""
     live = [t for t in tensors if t is not None]
     if not live:
         return [None] * len(tensors)

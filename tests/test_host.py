@@ -137,3 +137,33 @@ def test_wait_for_count_polls_the_early_triple_and_falls_back_to_the_event():
     assert _lib.wait_for_count(slot, 0, ev) == (111, 1) and ev.waited == 2     # no early request armed
     a, b = _lib.next_sequence(), _lib.next_sequence()
     assert b == a + 1 and a > 0
+
+
+def test_early_depth_range_is_read_only_with_a_matching_sequence():
+    """slot[7] holds dmin bits | dmax bits << 32 of the frame's listed depths, valid once slot[5]
+    carries the frame's sequence number; 0 means the reporting kernel did not know the range."""
+    from splatad_b200 import _lib
+    slot = torch.zeros(8, dtype=torch.int64)
+    lo, hi = 0x3E99999A, 0x42E20000                    # 0.3 and 113.0 as float bit patterns
+    slot[5], slot[7] = 9, lo | (hi << 32)
+    assert _lib.early_depth_range(slot, 9) == (lo, hi)
+    assert _lib.early_depth_range(slot, 10) is None    # another frame's words
+    assert _lib.early_depth_range(slot, 0) is None     # nothing was armed
+    slot[7] = 0
+    assert _lib.early_depth_range(slot, 9) is None
+
+
+def test_gradient_accumulators_share_one_zeroed_buffer():
+    """The backward passes take all their zero-initialised accumulators as views of one buffer: the
+    shapes are those asked for, None stays None, every view starts a multiple of 256 bytes behind the
+    buffer's start (itself 512-byte aligned when it comes from the CUDA allocator) and the views do
+    not overlap."""
+    from splatad_b200 import ops
+    a, b, c = torch.empty(5, 2), torch.empty(7), torch.empty(0, 3)
+    va, none, vb, vc = ops._zeros_like_many(a, None, b, c)
+    assert none is None and va.shape == a.shape and vb.shape == b.shape and vc.shape == c.shape
+    assert float(va.abs().sum() + vb.abs().sum()) == 0.0
+    assert (vb.data_ptr() - va.data_ptr()) % 256 == 0 and (vc.data_ptr() - va.data_ptr()) % 256 == 0
+    va.fill_(1.0)
+    assert float(vb.abs().sum()) == 0.0 and vb.data_ptr() >= va.data_ptr() + va.numel() * 4
+    assert ops._zeros_like_many(None, None) == [None, None]

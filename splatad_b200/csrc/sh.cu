@@ -303,14 +303,30 @@ __device__ __forceinline__ void sh_entry(const ShColorArgs &a, size_t e, uint32_
 __device__ __forceinline__ void stage_rows_gather(const float *__restrict__ coeffs, const int64_t *rows,
                                                   float *smem, uint32_t n, uint32_t row, uint32_t nfl) {
     if ((row & 3u) == 0 && (nfl & 3u) == 0 && (reinterpret_cast<uintptr_t>(coeffs) & 15u) == 0) {
-        const uint32_t per_row = nfl >> 2;
-        for (uint32_t i = threadIdx.x; i < n * per_row; i += blockDim.x) {
-            const uint32_t r = i / per_row, q = i - r * per_row;
-            const int64_t src = rows[r];
-            if (src < 0) continue;
-            const float4 v = __ldg(reinterpret_cast<const float4 *>(coeffs + (size_t)src * row) + q);
-            float *d = smem + r * (row + 1) + 4 * q;
-            d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+        // four 16-byte loads in flight per thread before the first of them is stored: with a load and
+        // its store in one loop iteration every thread waited out the memory latency twelve times
+        const uint32_t per_row = nfl >> 2, total = n * per_row;
+        constexpr int kInFlight = 4;
+        for (uint32_t i0 = threadIdx.x; i0 < total; i0 += kInFlight * blockDim.x) {
+            float4 v[kInFlight];
+            uint32_t at[kInFlight];
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+                const uint32_t i = i0 + u * blockDim.x;
+                at[u] = 0xffffffffu;
+                if (i >= total) continue;
+                const uint32_t r = i / per_row, q = i - r * per_row;
+                const int64_t src = rows[r];
+                if (src < 0) continue;
+                v[u] = __ldg(reinterpret_cast<const float4 *>(coeffs + (size_t)src * row) + q);
+                at[u] = r * (row + 1) + 4 * q;
+            }
+#pragma unroll
+            for (int u = 0; u < kInFlight; ++u) {
+                if (at[u] == 0xffffffffu) continue;
+                float *d = smem + at[u];
+                d[0] = v[u].x; d[1] = v[u].y; d[2] = v[u].z; d[3] = v[u].w;
+            }
         }
     } else {
         for (uint32_t i = threadIdx.x; i < n * nfl; i += blockDim.x) {

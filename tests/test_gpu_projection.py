@@ -414,3 +414,25 @@ def test_lidar_projection_slab_pipeline_equals_plain_kernel():
     count = ctypes.c_int64(-1)
     _lib.check(_lib.load().splatad_async_copy_timeouts(ctypes.addressof(count)))
     assert count.value == 0
+
+
+@pytest.mark.parametrize("N", [255, 256, 257, 512, 1000])
+def test_lidar_projection_slab_boundaries(N):
+    """Scene sizes around the slab length of the pipelined kernel (one slab less one, exactly one, one
+    more, exactly two, ragged): the 16-byte aligned call and the same rows through the plain kernel
+    (a view that starts one row into its buffer) agree bit for bit."""
+    from splatad_b200 import ops
+
+    means, quats, scales, vel, g = _scene(N + 1, 5 + N)
+    vm, lin, ang, rs = _lidar_sensors(2, g)
+    sens = (t(vm), t(lin), t(ang), t(rs))
+    kw = dict(calc_compensations=True, **LIDAR_KW)
+    big = [t(x) for x in (means, quats, scales, vel)]
+    plain = ops.fully_fused_lidar_projection(big[0][1:], None, big[1][1:], big[2][1:], big[3][1:], *sens, **kw)
+    assert big[0][1:].data_ptr() % 16 != 0
+    aligned_in = [b[1:].clone() for b in big]
+    assert all(a.data_ptr() % 16 == 0 for a in aligned_in)
+    fast = ops.fully_fused_lidar_projection(aligned_in[0], None, aligned_in[1], aligned_in[2], aligned_in[3],
+                                            *sens, **kw)
+    for a, b in zip(fast, plain):
+        assert torch.equal(a, b)

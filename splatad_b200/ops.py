@@ -335,11 +335,16 @@ def fully_fused_lidar_projection(
     packed: bool = False,
     sparse_grad: bool = False,
     calc_compensations: bool = False,
+    frame: Optional["LidarFrame"] = None,
 ):
     """Projects Gaussians to a batch of spherical lidars (azimuth / elevation in degrees, range).
 
     Returns (radii [C,N,2] float degrees, means2d, depths (range), conics, compensations,
     pix_vels [C,N,3], depth_compensations [C,N,2]).
+
+    ``frame`` (not part of the reference's API): a :class:`LidarFrame` that has already projected
+    exactly these inputs; its outputs are returned with this op's backward attached and nothing is
+    launched.
     """
     C = viewmats.size(0)
     N = means.size(0)
@@ -367,7 +372,7 @@ def fully_fused_lidar_projection(
     return _FullyFusedLidarProjection.apply(
         means, covars, quats, scales, velocities, viewmats, min_elevation, max_elevation,
         min_azimuth, max_azimuth, linear_velocity, angular_velocity, rolling_shutter_time, eps2d,
-        near_plane, far_plane, radius_clip, calc_compensations,
+        near_plane, far_plane, radius_clip, calc_compensations, frame,
     )
 
 
@@ -445,28 +450,35 @@ class _FullyFusedLidarProjection(torch.autograd.Function):
     @staticmethod
     def forward(ctx, means, covars, quats, scales, velocities, viewmats, min_elevation,
                 max_elevation, min_azimuth, max_azimuth, linear_velocity, angular_velocity,
-                rolling_shutter_time, eps2d, near_plane, far_plane, radius_clip, calc_compensations):
+                rolling_shutter_time, eps2d, near_plane, far_plane, radius_clip, calc_compensations,
+                frame=None):
         means, covars, quats, scales, velocities, viewmats, lin, ang, rs = _proj_inputs(
             means, covars, quats, scales, velocities, viewmats, linear_velocity, angular_velocity,
             rolling_shutter_time)
         C, N = viewmats.shape[0], means.shape[0]
         dev = means.device
         f32 = dict(dtype=torch.float32, device=dev)
-        radii = torch.empty((C, N, 2), **f32)
-        means2d = torch.empty((C, N, 2), **f32)
-        depths = torch.empty((C, N), **f32)
-        conics = torch.empty((C, N, 3), **f32)
-        pix_vels = torch.empty((C, N, 3), **f32)
-        depth_comps = torch.empty((C, N, 2), **f32)
-        compensations = torch.empty((C, N), **f32) if calc_compensations else None
-        _call(
-            "splatad_lidar_projection_fwd", C, N, _lib.ptr(means), _lib.ptr(covars), _lib.ptr(quats),
-            _lib.ptr(scales), _lib.ptr(velocities), _lib.ptr(viewmats), min_elevation, max_elevation,
-            min_azimuth, max_azimuth, _lib.ptr(lin), _lib.ptr(ang), _lib.ptr(rs), eps2d, near_plane,
-            far_plane, radius_clip, _lib.ptr(radii), _lib.ptr(means2d), _lib.ptr(depths),
-            _lib.ptr(conics), _lib.ptr(compensations), _lib.ptr(pix_vels), _lib.ptr(depth_comps),
-            _lib.stream_ptr(dev),
-        )
+        if frame is not None:
+            # projected by the single-call frame already: only the graph node is made here
+            assert not calc_compensations and covars is None and frame.radii.shape == (C, N, 2)
+            radii, means2d, depths, conics = frame.radii, frame.means2d, frame.depths, frame.conics
+            pix_vels, depth_comps, compensations = frame.pix_vels, frame.depth_compensations, None
+        else:
+            radii = torch.empty((C, N, 2), **f32)
+            means2d = torch.empty((C, N, 2), **f32)
+            depths = torch.empty((C, N), **f32)
+            conics = torch.empty((C, N, 3), **f32)
+            pix_vels = torch.empty((C, N, 3), **f32)
+            depth_comps = torch.empty((C, N, 2), **f32)
+            compensations = torch.empty((C, N), **f32) if calc_compensations else None
+            _call(
+                "splatad_lidar_projection_fwd", C, N, _lib.ptr(means), _lib.ptr(covars), _lib.ptr(quats),
+                _lib.ptr(scales), _lib.ptr(velocities), _lib.ptr(viewmats), min_elevation, max_elevation,
+                min_azimuth, max_azimuth, _lib.ptr(lin), _lib.ptr(ang), _lib.ptr(rs), eps2d, near_plane,
+                far_plane, radius_clip, _lib.ptr(radii), _lib.ptr(means2d), _lib.ptr(depths),
+                _lib.ptr(conics), _lib.ptr(compensations), _lib.ptr(pix_vels), _lib.ptr(depth_comps),
+                _lib.stream_ptr(dev),
+            )
         ctx.save_for_backward(means, covars, quats, scales, velocities, viewmats, lin, ang, rs, radii,
                               conics, compensations)
         ctx.eps2d = eps2d
@@ -506,7 +518,7 @@ class _FullyFusedLidarProjection(torch.autograd.Function):
             v_quats = None
         if not ctx.needs_input_grad[3]:
             v_scales = None
-        return (v_means, v_covars, v_quats, v_scales, v_vel, v_viewmats) + (None,) * 12
+        return (v_means, v_covars, v_quats, v_scales, v_vel, v_viewmats) + (None,) * 13
 
 
 class PendingPackedCount:
@@ -1656,7 +1668,7 @@ def rasterize_to_points_split(
     pix_vels: Tensor, depth_compensations: Tensor, raster_pts: Tensor, image_width: int, image_height: int,
     tile_width: int, tile_height: int, isect_offsets: Tensor, flatten_ids: Tensor,
     compute_alpha_sum_until_points: bool, compute_alpha_sum_until_points_threshold: float,
-    absgrad: bool = False, total_follows: bool = False,
+    absgrad: bool = False, total_follows: bool = False, frame: Optional["LidarFrame"] = None,
 ) -> Tuple[Tensor, Tensor, Optional[Tensor], Tensor]:
     """:func:`rasterize_to_points` with the Gaussians' ranges given as their own [C,N] tensor instead
     of being concatenated to the features as last channel (what ``lidar_rasterization`` of the
@@ -1669,7 +1681,7 @@ def rasterize_to_points_split(
         opacities.contiguous(), pix_vels.contiguous(), depth_compensations.contiguous(), None,
         raster_pts.contiguous(), image_width, image_height, tile_width, tile_height,
         isect_offsets.contiguous(), flatten_ids.contiguous(), compute_alpha_sum_until_points,
-        compute_alpha_sum_until_points_threshold, absgrad, lidar_features.shape[-1], total_follows)
+        compute_alpha_sum_until_points_threshold, absgrad, lidar_features.shape[-1], total_follows, frame)
 
 
 class _RasterizeToPoints(torch.autograd.Function):
@@ -1677,7 +1689,9 @@ class _RasterizeToPoints(torch.autograd.Function):
     def forward(ctx, means2d, conics, colors, ranges, opacities, pix_vels, depth_compensations, backgrounds,
                 raster_pts, width, height, tile_width, tile_height, isect_offsets, flatten_ids,
                 compute_alpha_sum_until_points, compute_alpha_sum_until_points_threshold, absgrad,
-                depth_channel_idx, total_follows=False):
+                depth_channel_idx, total_follows=False, frame=None):
+        # ``frame`` (optional): a LidarFrame that has composited exactly these inputs over exactly
+        # these lists; its images are returned with this op's backward attached, nothing is launched.
         # ``ranges`` (optional, [C,N] / [nnz]): the Gaussians' ranges as a separate array; the rendered
         # channel count is then colors.shape[-1] + 1 with the range as last channel.
         dev = means2d.device
@@ -1688,23 +1702,28 @@ class _RasterizeToPoints(torch.autograd.Function):
         colors_f, conics_f, opac_f = _f(colors), _f(conics), _f(opacities)
         vels_f, dc_f, pts_f, bg = _f(pix_vels), _f(depth_compensations), _f(raster_pts), _f(backgrounds)
         f32 = dict(dtype=torch.float32, device=dev)
-        render_colors = torch.empty((C, height, width, channels), **f32)
-        render_alphas = torch.empty((C, height, width, 1), **f32)
-        median_depths = torch.empty((C, height, width, 1), **f32)
-        alpha_sum = torch.empty((C, height, width, 1), **f32) if compute_alpha_sum_until_points else None
-        last_ids = torch.empty((C, height, width), dtype=torch.int32, device=dev)
         ctx.n_isects_arg = _n_isects_arg(isect_offsets, flatten_ids, total_follows)
         _debug_check_lists("rasterize_to_points", flatten_ids, means2d.numel() // 2, isect_offsets, total_follows)
-        _call(
-            "splatad_rasterize_to_points_fwd", C, ctx.n_isects_arg, _lib.ptr(means2d),
-            _lib.ptr(conics_f), _lib.ptr(colors_f) if colors_f.numel() else None, _lib.ptr(ranges_f), channels,
-            _lib.ptr(opac_f), _lib.ptr(vels_f),
-            _lib.ptr(dc_f), _lib.ptr(bg), _lib.ptr(pts_f), width, height, tile_width, tile_height,
-            grid_w, grid_h, int(bool(compute_alpha_sum_until_points)),
-            float(compute_alpha_sum_until_points_threshold), _lib.ptr(isect_offsets),
-            _lib.ptr(flatten_ids), depth_channel_idx, _lib.ptr(render_colors), _lib.ptr(render_alphas),
-            _lib.ptr(alpha_sum), _lib.ptr(last_ids), _lib.ptr(median_depths), _lib.stream_ptr(dev),
-        )
+        if frame is not None:
+            render_colors, render_alphas, median_depths = frame.render, frame.alphas, frame.median_depths
+            alpha_sum, last_ids = frame.alpha_sum, frame.last_ids
+            assert render_colors.shape == (C, height, width, channels) and ranges is not None and bg is None
+        else:
+            render_colors = torch.empty((C, height, width, channels), **f32)
+            render_alphas = torch.empty((C, height, width, 1), **f32)
+            median_depths = torch.empty((C, height, width, 1), **f32)
+            alpha_sum = torch.empty((C, height, width, 1), **f32) if compute_alpha_sum_until_points else None
+            last_ids = torch.empty((C, height, width), dtype=torch.int32, device=dev)
+            _call(
+                "splatad_rasterize_to_points_fwd", C, ctx.n_isects_arg, _lib.ptr(means2d),
+                _lib.ptr(conics_f), _lib.ptr(colors_f) if colors_f.numel() else None, _lib.ptr(ranges_f), channels,
+                _lib.ptr(opac_f), _lib.ptr(vels_f),
+                _lib.ptr(dc_f), _lib.ptr(bg), _lib.ptr(pts_f), width, height, tile_width, tile_height,
+                grid_w, grid_h, int(bool(compute_alpha_sum_until_points)),
+                float(compute_alpha_sum_until_points_threshold), _lib.ptr(isect_offsets),
+                _lib.ptr(flatten_ids), depth_channel_idx, _lib.ptr(render_colors), _lib.ptr(render_alphas),
+                _lib.ptr(alpha_sum), _lib.ptr(last_ids), _lib.ptr(median_depths), _lib.stream_ptr(dev),
+            )
         ctx.save_for_backward(means2d, conics_f, colors_f, ranges_f, opac_f, vels_f, dc_f, bg, pts_f,
                               isect_offsets, flatten_ids, render_alphas, last_ids)
         ctx.meta = (width, height, tile_width, tile_height, absgrad,
@@ -1744,7 +1763,7 @@ class _RasterizeToPoints(torch.autograd.Function):
         if ctx.needs_input_grad[7]:
             v_backgrounds = (v_render_colors * (1.0 - render_alphas).float()).sum(dim=(1, 2))
         return (v_means2d, v_conics, v_colors, v_ranges, v_opacities, v_pix_vels, v_depth_comps,
-                v_backgrounds) + (None,) * 12
+                v_backgrounds) + (None,) * 13
 
 
 # =============================================================================================

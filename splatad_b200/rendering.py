@@ -302,23 +302,51 @@ def lidar_rasterization(
     linear_velocity, angular_velocity, rolling_shutter_time = _sensor_motion(
         C, means.device, linear_velocity, angular_velocity, rolling_shutter_time)
 
-    # A frame that needs no gradients, fits one compositing launch and has a predecessor of its shape
-    # goes through one library call that enqueues all of it (same kernels, same results).
+    # A frame that fits one compositing launch and has a predecessor of its shape goes through one
+    # library call that enqueues all of its forward pass (same kernels, same results). With gradients
+    # wanted, the projection and compositing ops then adopt the frame's outputs - they launch nothing
+    # and only put their backward passes into the graph, so that the graph, `meta` and the gradient
+    # slots of `meta["means2d"]` are those of the op-by-op path.
     needs_grad = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad
         for t in (means, quats, scales, opacities, lidar_features, velocities, viewmats))
-    if (not needs_grad and rasterize_mode == "classic" and use_depth_compensation
+    if (rasterize_mode == "classic" and use_depth_compensation
             and lidar_features.shape[-1] + 1 <= min(channel_chunk, 32) and N > 0 and C > 0
             and raster_pts.shape[1] * raster_pts.shape[2] > 0):
-        frame = lidar_frame_fwd(
-            means, quats, scales, velocities, opacities[None] if C == 1 else opacities.repeat(C, 1),
-            lidar_features, viewmats, linear_velocity, angular_velocity, rolling_shutter_time, raster_pts,
-            tile_elevation_boundaries, azimuth_resolution, tile_width, tile_height, min_azimuth, max_azimuth,
-            min_elevation, max_elevation, eps2d, near_plane, far_plane, radius_clip,
-            compute_alpha_sum_until_points, compute_alpha_sum_until_points_threshold,
-            expected_grid=(n_elevation_tiles,
-                           math.ceil((max_azimuth - min_azimuth) / (azimuth_resolution * tile_width))))
+        with torch.no_grad():
+            frame = lidar_frame_fwd(
+                means, quats, scales, velocities, opacities[None] if C == 1 else opacities.repeat(C, 1),
+                lidar_features, viewmats, linear_velocity, angular_velocity, rolling_shutter_time, raster_pts,
+                tile_elevation_boundaries, azimuth_resolution, tile_width, tile_height, min_azimuth, max_azimuth,
+                min_elevation, max_elevation, eps2d, near_plane, far_plane, radius_clip,
+                compute_alpha_sum_until_points, compute_alpha_sum_until_points_threshold,
+                expected_grid=(n_elevation_tiles,
+                               math.ceil((max_azimuth - min_azimuth) / (azimuth_resolution * tile_width))))
         lists = frame.finish() if frame is not None else None
+        if lists is not None and needs_grad:
+            n_elevation_tiles_, n_azimuth_tiles_ = frame.grid
+            isect_offsets = frame.offsets_buf[:-1].view(C, n_elevation_tiles_, n_azimuth_tiles_)
+            radii, means2d, depths, conics, _, pix_vels, depth_compensations = fully_fused_lidar_projection(
+                means, None, quats, scales, velocities, viewmats, linear_velocity, angular_velocity,
+                rolling_shutter_time, min_elevation=min_elevation, max_elevation=max_elevation,
+                min_azimuth=min_azimuth, max_azimuth=max_azimuth, eps2d=eps2d, packed=False,
+                near_plane=near_plane, far_plane=far_plane, radius_clip=radius_clip, sparse_grad=sparse_grad,
+                calc_compensations=False, frame=frame)
+            opacities_cn = opacities[None] if C == 1 else opacities.repeat(C, 1)
+            render, alphas, alpha_sum, median = rasterize_to_points_split(
+                means2d, conics, lidar_features, depths, opacities_cn, pix_vels, depth_compensations, raster_pts,
+                raster_pts.shape[-2], raster_pts.shape[-3], tile_width, tile_height, isect_offsets, lists[1],
+                compute_alpha_sum_until_points, compute_alpha_sum_until_points_threshold, absgrad=absgrad,
+                total_follows=True, frame=frame)
+            meta = dict(
+                camera_ids=None, gaussian_ids=None, radii=radii, means2d=means2d, depths=depths, conics=conics,
+                opacities=opacities_cn, pix_vels=pix_vels, tile_grid_width=n_azimuth_tiles_,
+                tile_grid_height=n_elevation_tiles_, tiles_per_gauss=frame.tiles_per_gauss, isect_ids=lists[0],
+                flatten_ids=lists[1], isect_offsets=isect_offsets, width=raster_pts.shape[-2],
+                height=raster_pts.shape[-3], tile_width=tile_width, tile_height=tile_height, n_cameras=C,
+                median_depths=median,
+            )
+            return render, alphas, alpha_sum, meta
         if lists is not None:
             n_elevation_tiles_, n_azimuth_tiles_ = frame.grid
             meta = dict(

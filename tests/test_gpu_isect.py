@@ -230,3 +230,33 @@ def test_depth_order_with_crowded_depths(distinct):
     want = list(isect.isect_tiles(n(m2), n(r2), n(d2), ts, tw, th))
     want.append(isect.isect_offset_encode(want[1], 1, tw, th))
     _check(_run_cam(m2, r2, d2, ts, tw, th), want, f"camera, {distinct} depths")
+
+
+@pytest.mark.parametrize("lo,hi", [(0.0, 80.0), (10.0, 30.0), (0.0, 1.0e7), (79.0, 200.0)])
+def test_depth_range_hint_never_changes_the_lists(lo, hi):
+    """`splatad_isect_set_depth_range_hint` makes the depth buckets of the next plan span the given
+    range instead of the measured one (and lets the rectangle count fill them): a range that fits, one
+    that covers a slice of the depths, one far too wide and one that starts where the depths end all
+    give the oracle's lists bit for bit - or, when an end bucket overflows, the status bit that sends
+    the caller back to a plan without a hint."""
+    import struct
+    from oracle import isect
+    from splatad_b200 import _lib, ops, scenes
+    bits = lambda v: struct.unpack("<I", struct.pack("<f", v))[0]   # noqa: E731
+    C, N = 1, 30_000
+    g = torch.Generator().manual_seed(7)
+    eb = scenes.elevation_boundaries(scenes.beams_128(), 8)
+    means2d = torch.stack([torch.rand(C, N, generator=g) * 360 - 180, torch.rand(C, N, generator=g) * 44 - 27], -1)
+    radii = torch.rand(C, N, 2, generator=g) * torch.tensor([9.0, 3.0])
+    radii[:, ::7, 0] = 0
+    depths = torch.rand(C, N, generator=g) * 80
+    res, n_az = 0.2 * 32, math.ceil(360 / (0.2 * 32))
+    want = list(isect.isect_lidar_tiles(n(means2d), n(radii), n(depths), n(eb), res, -180.0))
+    want.append(isect.isect_offset_encode(want[1], C, n_az, len(eb) - 1))
+    ops._depth_sort_mode.clear()
+    _lib.load().splatad_isect_set_depth_range_hint(bits(lo), bits(hi))
+    got = _run_lidar(means2d, radii, depths, eb, res, -180.0)   # an overflowing end bucket makes ops repeat the plan
+    _check(got, want, f"lidar, depth range hint [{lo}, {hi}]")
+    # a hint is consumed by one plan: the next call measures its own range again
+    _check(_run_lidar(means2d, radii, depths, eb, res, -180.0), want, "lidar, after the hint")
+    ops._depth_sort_mode.clear()   # an overflow above made this shape take the radix passes: not for other tests
